@@ -1,0 +1,113 @@
+"""In-tree build of the native libraries.
+
+    libmf_smem.so   host core (g++): util, RPC, config store, group engine, hybm, smem/zbal C APIs
+    libmf_cuda.so   device backend and every sm_100a kernel (nvcc, static cudart)
+
+Objects are cached under ``build/`` keyed by a hash of the source, its local includes and the
+flags, so a rebuild only recompiles what changed.  ``python -m memfabric_hybrid_b200._build``
+builds everything; ``--host`` / ``--cuda`` restrict it.
+"""
+from __future__ import annotations
+
+import concurrent.futures as cf
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIB = PKG / "lib"
+BUILD = PKG.parent / "build"
+
+HOST_DIRS = ["util", "net", "store", "group", "hybm", "smem", "zbal"]
+CXXFLAGS = ["-std=c++17", "-O2", "-g", "-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter", "-pthread",
+            "-fvisibility=default", "-fstack-protector-strong", "-D_FORTIFY_SOURCE=2"]
+NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
+              "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]
+
+
+def _hash(src: Path, flags: list[str]) -> str:
+    h = hashlib.sha1()
+    h.update(" ".join(flags).encode())
+    h.update(src.read_bytes())
+    # every header of the tree participates: cheap and always correct
+    for hdr in sorted(list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh"))):
+        h.update(hdr.read_bytes())
+    return h.hexdigest()[:16]
+
+
+def _compile(cmd: list[str], src: Path, obj: Path, log: Path) -> tuple[Path, int, str]:
+    p = subprocess.run(cmd + ["-c", str(src), "-o", str(obj)], capture_output=True, text=True)
+    log.write_text(p.stdout + p.stderr)
+    return src, p.returncode, p.stdout + p.stderr
+
+
+def _build_objs(srcs: list[Path], cmd: list[str], flags: list[str], tag: str, jobs: int) -> list[Path]:
+    BUILD.mkdir(exist_ok=True)
+    objs, todo = [], []
+    for s in srcs:
+        obj = BUILD / f"{tag}_{s.stem}_{_hash(s, flags)}.o"
+        objs.append(obj)
+        if not obj.exists():
+            todo.append((s, obj))
+    if todo:
+        with cf.ThreadPoolExecutor(max_workers=jobs) as ex:
+            futs = [ex.submit(_compile, cmd + flags, s, o, BUILD / f"{tag}_{s.stem}.log") for s, o in todo]
+            failed = False
+            for f in futs:
+                src, rc, out = f.result()
+                if rc != 0:
+                    failed = True
+                    sys.stderr.write(f"--- {src}\n{out}\n")
+            if failed:
+                raise RuntimeError(f"{tag}: compilation failed")
+    return objs
+
+
+def build_host(jobs: int | None = None) -> Path:
+    jobs = jobs or os.cpu_count() or 4
+    srcs = [p for d in HOST_DIRS for p in sorted((CSRC / d).glob("*.cpp"))]
+    flags = CXXFLAGS + [f"-I{CSRC / 'include'}", f"-I{CSRC}"]
+    objs = _build_objs(srcs, ["g++"], flags, "host", jobs)
+    LIB.mkdir(exist_ok=True)
+    out = LIB / "libmf_smem.so"
+    tmp = out.with_suffix(".so.tmp")
+    subprocess.run(["g++", "-shared", "-o", str(tmp)] + [str(o) for o in objs] +
+                   ["-pthread", "-ldl", "-lrt", "-Wl,-z,relro,-z,now"], check=True)
+    tmp.replace(out)
+    return out
+
+
+def build_cuda(jobs: int | None = None) -> Path | None:
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(nvcc).exists():
+        return None
+    jobs = jobs or os.cpu_count() or 4
+    srcs = sorted((CSRC / "kernels").glob("*.cu"))
+    if not srcs:
+        return None
+    flags = NVCC_FLAGS + [f"-I{CSRC / 'include'}", f"-I{CSRC}"]
+    objs = _build_objs(srcs, [nvcc], flags, "cuda", jobs)
+    LIB.mkdir(exist_ok=True)
+    out = LIB / "libmf_cuda.so"
+    tmp = out.with_suffix(".so.tmp")
+    subprocess.run([nvcc, "-shared", "-o", str(tmp)] + [str(o) for o in objs] +
+                   ["-cudart", "static", "-Xlinker", "-z,relro", "-lpthread", "-ldl", "-lrt"], check=True)
+    tmp.replace(out)
+    return out
+
+
+def build_all() -> None:
+    build_host()
+    build_cuda()
+
+
+if __name__ == "__main__":
+    args = set(sys.argv[1:])
+    if not args or "--host" in args:
+        print(build_host())
+    if not args or "--cuda" in args:
+        print(build_cuda())

@@ -1,0 +1,205 @@
+// URL parsing and per-URL store singletons.
+// tcp://ip:port            plain TCP store (server started by whoever asks for it)
+// etcd://ip:port[#inst]    HA store over the user-registered op table (the etcd client is supplied by the caller)
+// reg://name[#inst]        HA store over the user-registered op table, or over the in-process backend `name`
+// Parity: src/smem/csrc/config_store/smem_store_factory.cpp:50-125,174-251,292-310.
+#include "mf_store_backend.h"
+#include "mf_store_ha.h"
+
+namespace mf {
+namespace store {
+
+bool StoreUrl::Parse(const std::string &url, StoreUrl &out)
+{
+    out.raw = url;
+    std::string rest = url;
+    size_t p = rest.find("://");
+    std::string scheme = "tcp";
+    if (p != std::string::npos) {
+        scheme = rest.substr(0, p);
+        rest = rest.substr(p + 3);
+    }
+    if (scheme == "tcp") out.scheme = TCP;
+    else if (scheme == "etcd") out.scheme = ETCD;
+    else if (scheme == "reg") out.scheme = REG;
+    else return false;
+    p = rest.find('#');
+    if (p != std::string::npos) {
+        out.instance = rest.substr(p + 1);
+        rest = rest.substr(0, p);
+    }
+    if (out.scheme == REG && rest.find(':') == std::string::npos) {
+        out.ip = rest;  // registry name only
+        out.port = 0;
+        return !rest.empty();
+    }
+    return net::ParseIpPort(rest, out.ip, out.port);
+}
+
+namespace {
+struct Entry {
+    StorePtr client;
+    std::shared_ptr<StoreServer> server;
+    std::shared_ptr<HaConfigStore> ha;
+    uint32_t refs = 0;
+};
+std::mutex g_mu;
+std::map<std::string, Entry> g_stores;
+TlsOptions g_tls;
+}  // namespace
+
+int StoreFactory::SetTls(bool enable, const std::string &info)
+{
+    std::lock_guard<std::mutex> g(g_mu);
+    g_tls.enable = enable;
+    g_tls.info = info;
+    if (enable) {
+        // The TLS handshake would need OpenSSL, which is not linked; a caller that insists on TLS gets
+        // a clear refusal at store creation instead of a silent plaintext link.
+        MF_WARN("config-store TLS requested: not available in this build, stores will refuse to start");
+    }
+    return OK;
+}
+
+const TlsOptions &StoreFactory::Tls() { return g_tls; }
+
+std::shared_ptr<StoreServer> StoreFactory::ServerOf(const std::string &url)
+{
+    std::lock_guard<std::mutex> g(g_mu);
+    auto it = g_stores.find(url);
+    return it == g_stores.end() ? nullptr : it->second.server;
+}
+
+int StoreFactory::CreateServerOnly(const std::string &url, uint32_t worldSize, uint64_t flags)
+{
+    StoreUrl u;
+    if (!StoreUrl::Parse(url, u) || u.scheme != StoreUrl::TCP) return MF_FAIL(ERR_INVALID_PARAM, "bad store url %s", url.c_str());
+    std::lock_guard<std::mutex> g(g_mu);
+    if (g_tls.enable) return MF_FAIL(ERR, "TLS is enabled but not available in this build");
+    Entry &e = g_stores[url];
+    if (e.server) return OK;
+    auto s = std::make_shared<StoreServer>(u.ip, u.port, worldSize, flags);
+    int rc = s->Startup();
+    if (rc != OK) {
+        if (!e.client) g_stores.erase(url);
+        return rc;
+    }
+    e.server = s;
+    return OK;
+}
+
+StorePtr StoreFactory::CreateStore(const std::string &url, bool isServer, uint32_t worldSize, uint32_t rank,
+                                   uint32_t timeoutMs, uint64_t serverFlags, int *err)
+{
+    auto fail = [&](int code) -> StorePtr {
+        if (err != nullptr) *err = code;
+        return nullptr;
+    };
+    StoreUrl u;
+    if (!StoreUrl::Parse(url, u)) {
+        MF_FAIL(ERR_INVALID_PARAM, "bad store url %s", url.c_str());
+        return fail(ERR_INVALID_PARAM);
+    }
+    std::unique_lock<std::mutex> g(g_mu);
+    if (g_tls.enable) {
+        MF_FAIL(ERR, "TLS is enabled but not available in this build");
+        return fail(ERR);
+    }
+    Entry &e = g_stores[url];
+    if (e.client) {
+        e.refs++;
+        if (err != nullptr) *err = OK;
+        return e.client;
+    }
+    if (u.scheme != StoreUrl::TCP) {
+        BackendPtr backend;
+        smem_conf_store_backend_op_t ops;
+        if (GetExternalBackendOps(ops)) backend = std::make_shared<ExternalBackend>(ops, u.ip, u.instance);
+        else if (u.scheme == StoreUrl::REG) backend = std::make_shared<LocalMemoryBackend>(u.ip, true);
+        else {
+            g_stores.erase(url);
+            MF_FAIL(ERR_NOT_EXIST, "etcd:// needs a backend op table (smem_config_store_set_backend_op)");
+            return fail(ERR_NOT_EXIST);
+        }
+        std::string ip = EnvStr("MF_CONFIG_STORE_IP", nullptr, "127.0.0.1");
+        uint16_t port = u.port != 0 ? u.port : (uint16_t)EnvInt("MF_CONFIG_STORE_PORT", nullptr, 36100, 1024, 65000);
+        auto ha = std::make_shared<HaConfigStore>(ip, port, worldSize, rank, backend, isServer);
+        g.unlock();
+        int rc = ha->Startup(timeoutMs);
+        g.lock();
+        if (rc != OK) {
+            g_stores.erase(url);
+            return fail(rc);
+        }
+        Entry &e2 = g_stores[url];
+        e2.ha = ha;
+        e2.client = ha;
+        e2.refs = 1;
+        if (err != nullptr) *err = OK;
+        return ha;
+    }
+    if (isServer && !e.server) {
+        auto s = std::make_shared<StoreServer>(u.ip, u.port, worldSize, serverFlags);
+        int rc = s->Startup();
+        if (rc == OK) e.server = s;
+        else if (rc != ERR_IN_USE) {  // somebody else serving on that port is fine: we are a client then
+            g_stores.erase(url);
+            return fail(rc);
+        }
+    }
+    auto c = std::make_shared<TcpStoreClient>(u.ip, u.port, worldSize, rank);
+    g.unlock();
+    int rc = c->Startup(timeoutMs);
+    g.lock();
+    Entry &e3 = g_stores[url];
+    if (rc != OK) {
+        if (e3.server) e3.server->Shutdown();
+        g_stores.erase(url);
+        return fail(rc);
+    }
+    e3.client = c;
+    e3.refs = 1;
+    if (err != nullptr) *err = OK;
+    return c;
+}
+
+void StoreFactory::DestroyStore(const std::string &url)
+{
+    Entry e;
+    {
+        std::lock_guard<std::mutex> g(g_mu);
+        auto it = g_stores.find(url);
+        if (it == g_stores.end()) return;
+        if (it->second.refs > 1) {
+            it->second.refs--;
+            return;
+        }
+        e = it->second;
+        g_stores.erase(it);
+    }
+    if (e.ha) e.ha->Shutdown();
+    else if (e.client) std::static_pointer_cast<TcpStoreClient>(e.client)->Shutdown();
+    if (e.server) e.server->Shutdown();
+}
+
+void StoreFactory::DestroyAll()
+{
+    std::map<std::string, Entry> all;
+    {
+        std::lock_guard<std::mutex> g(g_mu);
+        all.swap(g_stores);
+    }
+    for (auto &kv : all) {
+        if (kv.second.ha) kv.second.ha->Shutdown();
+        else if (kv.second.client) std::static_pointer_cast<TcpStoreClient>(kv.second.client)->Shutdown();
+        if (kv.second.server) kv.second.server->Shutdown();
+    }
+}
+
+StorePtr StoreFactory::Prefixed(const StorePtr &base, const std::string &prefix)
+{
+    return std::make_shared<PrefixStore>(base, prefix);
+}
+
+}  // namespace store
+}  // namespace mf
