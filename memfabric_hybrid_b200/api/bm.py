@@ -1,0 +1,196 @@
+"""``memfabric_hybrid.bm``: Big Memory pools (see csrc/include/smem_bm.h for the C contract)."""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from typing import Callable, Sequence
+
+from .. import _native as N
+
+
+class BmMemType(enum.IntEnum):
+    LOCAL_DEVICE = 0
+    LOCAL_HOST = 1
+    DEVICE = 2
+    HOST = 3
+
+
+class BmCopyType(enum.IntEnum):
+    L2G = 0
+    G2L = 1
+    G2H = 2
+    H2G = 3
+    L2GH = 4
+    GH2L = 5
+    GH2H = 6
+    H2GH = 7
+    G2G = 8
+    AUTO = 9
+
+
+class BmDataOpType(enum.IntFlag):
+    SDMA = 1 << 0
+    HOST_RDMA = 1 << 1
+    HOST_TCP = 1 << 2
+    DEVICE_RDMA = 1 << 3
+    HOST_URMA = 1 << 4
+    HOST_SHM = 1 << 5
+    DEVICE_URMA = 1 << 6
+
+
+class BmGroupEvent(enum.IntEnum):
+    JOIN_EVENT = 0
+    LEAVE_EVENT = 1
+
+
+ASYNC_COPY_FLAG = 1 << 0
+COPY_EXTEND_FLAG = 1 << 1
+FLAG_USE_EXTERNAL_STREAM = 1 << 2
+
+
+class BmConfig:
+    """Mirror of ``smem_bm_config_t`` with the reference's Python attribute names."""
+
+    _MAP = {"init_timeout": "initTimeout", "create_timeout": "createTimeout",
+            "operation_timeout": "controlOperationTimeout", "start_store": "startConfigStoreServer",
+            "start_store_only": "startConfigStoreOnly", "dynamic_world_size": "dynamicWorldSize",
+            "unified_address_space": "unifiedAddressSpace", "auto_ranking": "autoRanking", "rank_id": "rankId",
+            "flags": "flags"}
+
+    def __init__(self) -> None:
+        object.__setattr__(self, "_c", N.BmConfigC())
+        N.lib().smem_bm_config_init(C.byref(self._c))
+
+    def __getattr__(self, name):
+        if name in BmConfig._MAP:
+            return getattr(self._c, BmConfig._MAP[name])
+        raise AttributeError(name)
+
+    def __setattr__(self, name, value):
+        if name in BmConfig._MAP:
+            setattr(self._c, BmConfig._MAP[name], value)
+        else:
+            raise AttributeError(name)
+
+    def set_nic(self, nic: str) -> None:
+        self._c.hcomUrl = nic.encode()[:63]
+
+
+def initialize(store_url: str, world_size: int, device_id: int, config: BmConfig) -> int:
+    return N.lib().smem_bm_init(store_url.encode(), world_size, device_id, C.byref(config._c))
+
+
+def uninitialize(flags: int = 0) -> None:
+    N.lib().smem_bm_uninit(flags)
+
+
+def bm_rank_id() -> int:
+    return N.lib().smem_bm_get_rank_id()
+
+
+def _ptr_array(values: Sequence[int]):
+    return (C.c_void_p * len(values))(*[int(v) for v in values])
+
+
+class BigMemory:
+    def __init__(self, handle: int):
+        self._h = handle
+        self._cb = None
+
+    # -- membership
+    def join(self, flags: int = 0) -> int:
+        return N.lib().smem_bm_join(self._h, flags)
+
+    def leave(self, flags: int = 0) -> int:
+        return N.lib().smem_bm_leave(self._h, flags)
+
+    def extend_local_mem(self, mem_type: BmMemType = BmMemType.HOST, size: int = 0) -> int:
+        return N.lib().smem_bm_extend_local_mem(self._h, int(mem_type), size)
+
+    def set_group_event_handler(self, cb: Callable[[int, BmGroupEvent], None]) -> int:
+        def tramp(_h, rank, ev, _ctx):
+            cb(rank, BmGroupEvent(ev))
+        self._cb = N.BM_EVENT_FN(tramp)
+        return N.lib().smem_bm_set_group_event_handler(self._h, self._cb, None)
+
+    # -- addressing
+    def local_mem_size(self, mem_type: BmMemType = BmMemType.DEVICE) -> int:
+        return N.lib().smem_bm_get_local_mem_size_by_mem_type(self._h, int(mem_type))
+
+    def peer_rank_ptr(self, peer_rank: int, mem_type: BmMemType = BmMemType.DEVICE) -> int:
+        return N.lib().smem_bm_ptr_by_mem_type(self._h, int(mem_type), peer_rank) or 0
+
+    def gva_to_va(self, gva: int, mem_type: BmMemType = BmMemType.LOCAL_HOST) -> int:
+        out = C.c_void_p()
+        rc = N.lib().smem_bm_gva_to_va(self._h, gva, int(mem_type), C.byref(out))
+        return (out.value or 0) if rc == 0 else 0
+
+    def get_rank_id_by_gva(self, gva: int) -> int:
+        return N.lib().smem_bm_get_rank_id_by_gva(self._h, gva)
+
+    def register(self, addr: int, size: int) -> int:
+        return N.lib().smem_bm_register_user_mem(self._h, addr, size)
+
+    def unregister(self, addr: int) -> int:
+        return N.lib().smem_bm_unregister_user_mem(self._h, addr)
+
+    # -- data
+    def copy_data(self, src_ptr: int, dst_ptr: int, size: int, type: BmCopyType, flags: int = 0, stream: int = 0) -> int:
+        p = N.CopyParamsC(src_ptr, dst_ptr, size, stream or None)
+        return N.lib().smem_bm_copy(self._h, C.byref(p), int(type), flags)
+
+    def _batch(self, src_addrs, dst_addrs, sizes, count, stream):
+        n = int(count)
+        srcs, dsts = _ptr_array(src_addrs[:n]), _ptr_array(dst_addrs[:n])
+        lens = (C.c_uint64 * n)(*[int(s) for s in sizes[:n]])
+        p = N.BatchCopyParamsC(srcs, dsts, lens, n, stream or None)
+        return p, (srcs, dsts, lens)
+
+    def copy_data_batch(self, src_addrs, dst_addrs, sizes, count, type: BmCopyType, flags: int = 0, stream: int = 0) -> int:
+        p, _keep = self._batch(src_addrs, dst_addrs, sizes, count, stream)
+        return N.lib().smem_bm_copy_batch(self._h, C.byref(p), int(type), flags)
+
+    def copy_data_batch_partial_succeed(self, src_addrs, dst_addrs, sizes, count, type: BmCopyType, flags: int = 0,
+                                        stream: int = 0):
+        """Returns (code, per-item list of codes)."""
+        p, _keep = self._batch(src_addrs, dst_addrs, sizes, count, stream)
+        res = (C.c_int32 * int(count))()
+        r = N.BatchCopyResultC(res, int(count))
+        rc = N.lib().smem_bm_copy_batch_partial_succeed(self._h, C.byref(p), int(type), flags, C.byref(r))
+        return rc, list(res)
+
+    def wait(self) -> int:
+        return N.lib().smem_bm_wait(self._h)
+
+    def destroy(self) -> None:
+        if self._h:
+            N.lib().smem_bm_destroy(self._h)
+            self._h = None
+
+    @property
+    def handle(self) -> int:
+        return self._h
+
+
+def create(id: int, local_dram_size: int, local_hbm_size: int = 0, data_op_type: BmDataOpType = BmDataOpType.SDMA,
+           flags: int = 0) -> BigMemory:
+    h = N.lib().smem_bm_create(id, 0, int(data_op_type), local_dram_size, local_hbm_size, flags)
+    if not h:
+        raise RuntimeError("bm.create failed: " + N.last_error())
+    return BigMemory(h)
+
+
+def create2(id: int, local_dram_size: int, max_dram_size: int, local_hbm_size: int = 0, max_hbm_size: int = 0,
+            data_op_type: BmDataOpType = BmDataOpType.SDMA, enable_56bits_gva: bool = False, flags: int = 0,
+            shm_fd: int = -1) -> BigMemory:
+    o = N.BmCreateOptionC()
+    o.maxDramSize, o.maxHbmSize = max_dram_size, max_hbm_size
+    o.localDRAMSize, o.localHBMSize = local_dram_size, local_hbm_size
+    o.dataOpType = int(data_op_type)
+    o.enable56BitsGva = enable_56bits_gva
+    o.flags = flags
+    o.dramShmFd = shm_fd
+    h = N.lib().smem_bm_create2(id, C.byref(o))
+    if not h:
+        raise RuntimeError("bm.create2 failed: " + N.last_error())
+    return BigMemory(h)

@@ -368,7 +368,7 @@ void GroupEngine::StopListen()
         std::lock_guard<std::mutex> g(qMu_);
         qCv_.notify_all();
     }
-    if (listener_.joinable()) listener_.join();
+    JoinOrDetach(listener_);
 }
 
 void GroupEngine::ListenLoop()
@@ -429,7 +429,8 @@ void GroupEngine::HandleEvent(const GroupInfo &ev)
     switch (ev.curEvent) {
         case EV_JOIN:
             // A rank that re-joins under an id we still hold is first dropped, then imported afresh.
-            if (hadTarget && opt_.leaveCb) opt_.leaveCb(ev.targetRank);
+            // (the link-down handler: it drops the imports without the leave protocol's barrier)
+            if (hadTarget && opt_.linkDownCb) opt_.linkDownCb(ev.targetRank);
             if (opt_.joinCb) rc = opt_.joinCb(ev.targetRank);
             break;
         case EV_UPDATE:

@@ -1,0 +1,83 @@
+// Data operators: how bytes move once both ends of a copy are resolved.
+//   SM kernel   — device<->device (local or peer HBM over NVLink) and device<->pinned pooled DRAM for
+//                 batches of small segments: items are cut into equal work chunks, written into a
+//                 pinned descriptor ring the kernel reads directly, one launch per batch
+//   copy engine — device<->host legs of large or unpinned buffers: one async memcpy per item
+//   host memcpy — host<->host through the mapped shared memory, split over a thread pool when large
+//   process VM  — a peer's registered *host* buffer: process_vm_readv / process_vm_writev
+// The compose operator picks per item, coalesces address-adjacent items first, and falls back from
+// the kernel to the copy engine when a launch fails.
+// Parity: src/hybm/csrc/data_operation/host/hybm_compose_data_op.cpp:26-291 (selection + fallback),
+// hybm_data_op_sdma.cpp:403-463,590-805 (coalescing, param ring, async/wait),
+// hybm_data_op_host_shm.cpp:41-178 (host memcpy leg).
+#pragma once
+#include <memory>
+#include <mutex>
+#include <vector>
+
+#include "mf_device.h"
+#include "mf_hybm_types.h"
+
+namespace mf {
+namespace hybm {
+
+enum EpKind : uint8_t {
+    EP_HOST = 0,         // ordinary host memory of this process
+    EP_HOST_PINNED = 1,  // pooled DRAM: mapped in this process, pinned and device-visible when a GPU is attached
+    EP_DEVICE = 2,       // device memory reachable from this process (local, pooled or IPC-mapped)
+    EP_REMOTE_VM = 3,    // host memory of another process, reached through process_vm_*
+};
+
+struct Endpoint {
+    uint64_t addr = 0;
+    EpKind kind = EP_HOST;
+    int32_t pid = 0;
+};
+
+struct ResolvedCopy {
+    Endpoint src, dst;
+    uint64_t len = 0;
+    uint32_t index = 0;  // position in the caller's batch (for per-item results)
+};
+
+struct DataOpStats {
+    uint64_t kernelLaunches = 0, kernelItems = 0, engineCopies = 0, hostCopies = 0, vmCopies = 0, coalesced = 0;
+};
+
+class ComposeDataOp {
+public:
+    ComposeDataOp(DeviceBackend *dev, uint32_t opMask);
+    ~ComposeDataOp();
+    // Runs the batch. perItem (optional) receives one code per original index.
+    int Submit(std::vector<ResolvedCopy> &items, void *userStream, uint32_t flags, int32_t *perItem);
+    int Quant(const std::vector<QuantItem> &items, uint32_t unit, int inputFp16, int mode, void *userStream);
+    int Wait();
+    DataOpStats Stats() const { return stats_; }
+    // Tunables (env MF_XCOPY_CHUNK_KB, MF_XCOPY_RING_MB, MF_HOST_COPY_THREADS).
+    uint64_t ChunkBytes() const { return chunk_; }
+
+private:
+    int RunHost(const ResolvedCopy &c);
+    int RunVm(const ResolvedCopy &c);
+    int RunKernel(const std::vector<const ResolvedCopy *> &items, void *stream);
+    int RunEngine(const ResolvedCopy &c, void *stream);
+    int EnsureRing();
+    void *StreamFor(void *userStream, uint32_t flags);
+
+    DeviceBackend *dev_;
+    uint32_t mask_;
+    std::mutex mu_;
+    void *stream_ = nullptr;  // internal stream
+    CopyItem *ring_ = nullptr;
+    uint64_t ringCap_ = 0;   // items
+    uint64_t ringHead_ = 0;
+    std::vector<void *> ringUsers_;  // streams with launches that may still read ring slots
+    uint64_t chunk_;
+    uint64_t hostSplit_;
+    std::unique_ptr<ThreadPool> pool_;
+    DataOpStats stats_;
+    bool pending_ = false;
+};
+
+}  // namespace hybm
+}  // namespace mf

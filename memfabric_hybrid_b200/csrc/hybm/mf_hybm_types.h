@@ -19,7 +19,7 @@ constexpr uint64_t kHbmGranule = 2ULL << 20;
 
 // GVA windows. Every process derives the same addresses from (space, entity id, attempt), so no
 // negotiation is needed unless a reservation collides with something already mapped; then all
-// ranks move to the next attempt together. Each space is 32 TiB cut into 64 windows of 512 GiB; a
+// ranks move to the next attempt together. Each space is 32 TiB cut into 128 windows of 256 GiB; a
 // pool larger than one window runs into the following ids' windows (the overlap check refuses a real
 // collision), so very large pools should use ids spaced accordingly. The spaces stay clear of where
 // Linux puts PIE executables and the heap (0x55..-0x56..) and of the top-down mmap area (0x7f..).
@@ -30,8 +30,9 @@ constexpr uint64_t kDramWindowBase = 0x100000000000ULL;
 constexpr uint64_t kHbmWindowBase = 0x300000000000ULL;
 constexpr uint64_t kTransWindowBase = 0x600000000000ULL;
 constexpr uint64_t kTransWindowEnd = 0x700000000000ULL;
-constexpr uint64_t kWindowStride = 512 * kGiB;
-constexpr uint32_t kMaxEntityId = 63;
+constexpr uint64_t kWindowStride = 256 * kGiB;
+constexpr uint32_t kMaxEntityId = 127;  // 0-63 Big Memory pools, 64-127 symmetric (SHM) heaps
+constexpr uint32_t kShmEntityBase = 64;
 constexpr uint32_t kReserveAttempts = 4;
 uint64_t WindowBase(hybm_mem_type t, uint32_t entityId, uint32_t attempt);
 

@@ -9,6 +9,7 @@
 #include <sys/un.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <random>
 
 #include "../util/mf_trace.h"
@@ -181,6 +182,26 @@ int Segment::Reserve(uint32_t attempt)
     return rc;
 }
 
+void Segment::RecomputeMapped(uint32_t rank)
+{
+    if (rank >= mappedBytes_.size()) return;
+    // slices are laid out back to back from offset 0, so the mapped prefix is the largest run without a hole
+    std::vector<std::pair<uint64_t, uint64_t>> spans;
+    if (rank == opt_.rank) {
+        for (auto &l : locals_) spans.emplace_back(l.slice->offset, l.slice->size);
+    } else {
+        for (auto &p : peers_)
+            if (p.rank == rank && p.mapped) spans.emplace_back(p.offset, p.size);
+    }
+    std::sort(spans.begin(), spans.end());
+    uint64_t end = 0;
+    for (auto &sp : spans) {
+        if (sp.first > end) break;
+        end = std::max(end, sp.first + sp.second);
+    }
+    mappedBytes_[rank].store(end, std::memory_order_release);
+}
+
 int Segment::Unreserve()
 {
     if (base_ == 0) return OK;
@@ -190,6 +211,7 @@ int Segment::Unreserve()
         for (auto &l : locals_) UnmapLocal(*l.slice);
         locals_.clear();
         localUsed_ = 0;
+        for (auto &m : mappedBytes_) m.store(0);
     }
     ReleaseRange(base_, opt_.slot * opt_.rankCount);
     VaManager::Get().RemoveReserved(base_);
@@ -218,6 +240,7 @@ int Segment::AllocLocal(uint64_t size, std::shared_ptr<MemSlice> &out)
     rec.slice = s;
     locals_.push_back(rec);
     localUsed_ += sz;
+    RecomputeMapped(opt_.rank);
     out = s;
     return OK;
 }
@@ -230,6 +253,7 @@ int Segment::FreeLocal(const std::shared_ptr<MemSlice> &s)
         UnmapLocal(*it->slice);
         if (it->slice->offset + it->slice->size == localUsed_) localUsed_ = it->slice->offset;
         locals_.erase(it);
+        RecomputeMapped(opt_.rank);
         return OK;
     }
     return ERR_NOT_EXIST;
@@ -308,6 +332,7 @@ int Segment::Mmap()
             break;
         }
         p.mapped = true;
+        RecomputeMapped(p.rank);
     }
     MF_TRACE_END(TP_HYBM_MMAP, rc);
     return rc;
@@ -322,6 +347,8 @@ void Segment::UnmapAll()
             p.mapped = false;
         }
     peers_.clear();
+    for (uint32_t r = 0; r < mappedBytes_.size(); r++)
+        if (r != opt_.rank) mappedBytes_[r].store(0);
 }
 
 int Segment::RemoveImported(uint32_t rank)
@@ -335,6 +362,7 @@ int Segment::RemoveImported(uint32_t rank)
         if (it->mapped) UnmapPeer(*it);
         it = peers_.erase(it);
     }
+    RecomputeMapped(rank);
     return OK;
 }
 

@@ -67,7 +67,7 @@ struct PeerSlice {
 
 class Segment {
 public:
-    explicit Segment(const SegmentOptions &o) : opt_(o) {}
+    explicit Segment(const SegmentOptions &o) : opt_(o), mappedBytes_(o.rankCount) {}
     virtual ~Segment() = default;
     static std::shared_ptr<Segment> Create(const SegmentOptions &o);
 
@@ -85,6 +85,12 @@ public:
     uint64_t LocalBytes() const { return localUsed_; }
     hybm_mem_type Type() const { return opt_.type; }
     bool RankMapped(uint32_t rank);
+    // Bytes of `rank`'s slot that are mapped here, contiguous from the slot start (lock-free read; the
+    // copy path uses it to refuse a range that would run into unmapped address space).
+    uint64_t MappedBytes(uint32_t rank) const
+    {
+        return rank < mappedBytes_.size() ? mappedBytes_[rank].load(std::memory_order_acquire) : 0;
+    }
     std::vector<std::shared_ptr<MemSlice>> LocalSlices();
 
 protected:
@@ -107,6 +113,8 @@ protected:
     };
     std::vector<LocalRec> locals_;
     std::vector<PeerSlice> peers_;
+    std::vector<std::atomic<uint64_t>> mappedBytes_;
+    void RecomputeMapped(uint32_t rank);  // mu_ held
 };
 using SegmentPtr = std::shared_ptr<Segment>;
 

@@ -348,7 +348,7 @@ void Endpoint::WorkerLoop(Worker *w)
 void Endpoint::Stop()
 {
     if (!running_.exchange(false)) return;
-    if (acceptor_.joinable()) acceptor_.join();
+    JoinOrDetach(acceptor_);
     if (listenFd_ >= 0) {
         ::close(listenFd_);
         listenFd_ = -1;
@@ -358,7 +358,7 @@ void Endpoint::Stop()
         (void)!::write(w->wakefd, &one, sizeof(one));
     }
     for (auto &w : workers_) {
-        if (w->th.joinable()) w->th.join();
+        JoinOrDetach(w->th);
         std::unordered_map<int, LinkPtr> links;
         {
             std::lock_guard<std::mutex> g(w->mu);

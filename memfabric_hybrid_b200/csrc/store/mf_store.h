@@ -325,6 +325,7 @@ public:
                                 uint32_t timeoutMs, uint64_t serverFlags = 0, int *err = nullptr);
     static int CreateServerOnly(const std::string &url, uint32_t worldSize, uint64_t flags);
     static void DestroyStore(const std::string &url);
+    static void DestroyServer(const std::string &url);  // counterpart of CreateServerOnly
     static void DestroyAll();
     static StorePtr Prefixed(const StorePtr &base, const std::string &prefix);
     static int SetTls(bool enable, const std::string &info);

@@ -83,8 +83,8 @@ void TcpStoreClient::Shutdown()
         std::lock_guard<std::mutex> g(hbMu_);
         hbCv_.notify_all();
     }
-    if (hb_.joinable()) hb_.join();
-    if (reconnector_.joinable()) reconnector_.join();
+    JoinOrDetach(hb_);
+    JoinOrDetach(reconnector_);
     {
         std::lock_guard<std::mutex> g(linkMu_);
         if (link_) link_->Shutdown();
@@ -187,7 +187,7 @@ void TcpStoreClient::OnBroken()
     }
     for (auto &f : fns) f();
     if (!running_ || reconnectTries_ == 0 || reconnecting_.exchange(true)) return;
-    if (reconnector_.joinable()) reconnector_.join();
+    JoinOrDetach(reconnector_);
     reconnector_ = std::thread([this] {
         pthread_setname_np(pthread_self(), "mf-store-redial");
         bool ok = false;

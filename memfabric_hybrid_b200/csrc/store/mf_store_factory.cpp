@@ -42,6 +42,7 @@ struct Entry {
     std::shared_ptr<StoreServer> server;
     std::shared_ptr<HaConfigStore> ha;
     uint32_t refs = 0;
+    bool pinnedServer = false;  // started by smem_create_config_store: outlives the clients of this process
 };
 std::mutex g_mu;
 std::map<std::string, Entry> g_stores;
@@ -85,7 +86,26 @@ int StoreFactory::CreateServerOnly(const std::string &url, uint32_t worldSize, u
         return rc;
     }
     e.server = s;
+    e.pinnedServer = true;
     return OK;
+}
+
+void StoreFactory::DestroyServer(const std::string &url)
+{
+    Entry e;
+    {
+        std::lock_guard<std::mutex> g(g_mu);
+        auto it = g_stores.find(url);
+        if (it == g_stores.end()) return;
+        it->second.pinnedServer = false;
+        if (it->second.client) {  // a client of this process still uses it: the last DestroyStore ends the server
+            return;
+        }
+        e = it->second;
+        g_stores.erase(it);
+    }
+    if (e.ha) e.ha->Shutdown();
+    if (e.server) e.server->Shutdown();
 }
 
 StorePtr StoreFactory::CreateStore(const std::string &url, bool isServer, uint32_t worldSize, uint32_t rank,
@@ -175,7 +195,13 @@ void StoreFactory::DestroyStore(const std::string &url)
             return;
         }
         e = it->second;
-        g_stores.erase(it);
+        if (e.pinnedServer && !e.ha) {  // keep serving other processes; only this process's client goes
+            it->second.client.reset();
+            it->second.refs = 0;
+            e.server.reset();
+        } else {
+            g_stores.erase(it);
+        }
     }
     if (e.ha) e.ha->Shutdown();
     else if (e.client) std::static_pointer_cast<TcpStoreClient>(e.client)->Shutdown();

@@ -56,7 +56,7 @@ void HaConfigStore::Shutdown()
         std::lock_guard<std::mutex> g(cvMu_);
         cv_.notify_all();
     }
-    if (health_.joinable()) health_.join();
+    JoinOrDetach(health_);
     std::shared_ptr<TcpStoreClient> c;
     std::shared_ptr<StoreServer> s;
     {

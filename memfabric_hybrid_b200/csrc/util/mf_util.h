@@ -149,6 +149,15 @@ private:
     bool stop_ = false;
 };
 
+// Joins a thread, unless the caller IS that thread (an object released from its own callback):
+// then the thread is detached, since joining oneself throws.
+inline void JoinOrDetach(std::thread &t)
+{
+    if (!t.joinable()) return;
+    if (t.get_id() == std::this_thread::get_id()) t.detach();
+    else t.join();
+}
+
 // Splits "a,b,c" on a delimiter, dropping empty pieces.
 std::vector<std::string> Split(const std::string &s, char delim);
 bool ParseU64(const std::string &s, uint64_t &out);
