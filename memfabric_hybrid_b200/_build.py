@@ -95,7 +95,8 @@ def build_cuda(jobs: int | None = None) -> Path | None:
     out = LIB / "libmf_cuda.so"
     tmp = out.with_suffix(".so.tmp")
     subprocess.run([nvcc, "-shared", "-o", str(tmp)] + [str(o) for o in objs] +
-                   ["-cudart", "static", "-Xlinker", "-z,relro", "-lpthread", "-ldl", "-lrt"], check=True)
+                   ["-cudart", "static", f"-L{LIB}", "-lmf_smem", "-Xlinker", "-rpath=$ORIGIN", "-Xlinker", "-z,relro",
+                    "-lpthread", "-ldl", "-lrt"], check=True)
     tmp.replace(out)
     return out
 

@@ -150,6 +150,16 @@ class BigMemory:
         p, _keep = self._batch(src_addrs, dst_addrs, sizes, count, stream)
         return N.lib().smem_bm_copy_batch(self._h, C.byref(p), int(type), flags)
 
+    def prepare_batch(self, src_addrs, dst_addrs, sizes, count=None):
+        """Extension: marshals a batch once so that repeated submissions skip the Python-side conversion."""
+        n = int(count if count is not None else len(sizes))
+        return self._batch(src_addrs, dst_addrs, sizes, n, 0)
+
+    def copy_prepared(self, prepared, type: BmCopyType, flags: int = 0, stream: int = 0) -> int:
+        p, _keep = prepared
+        p.stream = stream or None
+        return N.lib().smem_bm_copy_batch(self._h, C.byref(p), int(type), flags)
+
     def copy_data_batch_partial_succeed(self, src_addrs, dst_addrs, sizes, count, type: BmCopyType, flags: int = 0,
                                         stream: int = 0):
         """Returns (code, per-item list of codes)."""
@@ -161,6 +171,15 @@ class BigMemory:
 
     def wait(self) -> int:
         return N.lib().smem_bm_wait(self._h)
+
+    def copy_stats(self) -> dict:
+        """Counters of the copy paths (extension): kernel launches/chunks, engine, host, process-VM copies."""
+        out = (C.c_uint64 * 6)()
+        f = N.lib().mf_bm_copy_stats
+        f.restype, f.argtypes = C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64)]
+        f(self._h, out)
+        keys = ("kernel_launches", "kernel_chunks", "engine_copies", "host_copies", "vm_copies", "coalesced")
+        return dict(zip(keys, [int(v) for v in out]))
 
     def destroy(self) -> None:
         if self._h:

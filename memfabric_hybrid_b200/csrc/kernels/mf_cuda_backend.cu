@@ -1,0 +1,401 @@
+// CUDA implementation of the device backend: CUDA VMM for the pooled HBM (fixed-address reserve,
+// POSIX-FD shareable physical allocations, peer mapping), host registration of the pooled DRAM, CUDA
+// IPC for caller-registered device buffers, streams / copy engines, and the launches of the xcopy
+// kernels. Driver entry points are looked up through the runtime (no link-time libcuda), so this
+// library also loads on a machine without a GPU, where Init reports "no device".
+// Parity of role: src/hybm/csrc/under_api/dl_cuda_api.cpp:42-82 plus the driver calls of
+// src/hybm/csrc/mm/hybm_vmm_based_segment.cpp:71-101,252-336,395-445,551-631 restated for CUDA.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <unistd.h>
+
+#include <map>
+#include <mutex>
+
+#include "../hybm/mf_device.h"
+#include "../util/mf_util.h"
+#include "mf_xcopy.cuh"
+
+namespace mf {
+namespace hybm {
+namespace {
+
+#define DRV(name) decltype(&name) p_##name = nullptr
+struct DriverApi {
+    DRV(cuMemAddressReserve);
+    DRV(cuMemAddressFree);
+    DRV(cuMemCreate);
+    DRV(cuMemRelease);
+    DRV(cuMemMap);
+    DRV(cuMemUnmap);
+    DRV(cuMemSetAccess);
+    DRV(cuMemExportToShareableHandle);
+    DRV(cuMemImportFromShareableHandle);
+    DRV(cuMemGetAllocationGranularity);
+    DRV(cuMemGetAddressRange);
+    DRV(cuPointerGetAttribute);
+    DRV(cuGetErrorString);
+    bool ok = false;
+};
+#undef DRV
+
+template <typename F> bool Load(const char *name, F &fn)
+{
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || p == nullptr) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    fn = reinterpret_cast<F>(p);
+    return true;
+}
+
+#define CU_CHECK(call, what)                                                                         \
+    do {                                                                                             \
+        CUresult _r = (call);                                                                        \
+        if (_r != CUDA_SUCCESS) {                                                                    \
+            const char *_s = nullptr;                                                                \
+            if (drv_.p_cuGetErrorString) drv_.p_cuGetErrorString(_r, &_s);                           \
+            return MF_FAIL(ERR, "%s failed: %s (%d)", what, _s ? _s : "?", (int)_r);                 \
+        }                                                                                            \
+    } while (0)
+
+#define RT_CHECK(call, what)                                                                         \
+    do {                                                                                             \
+        cudaError_t _e = (call);                                                                     \
+        if (_e != cudaSuccess) {                                                                     \
+            (void)cudaGetLastError();                                                                \
+            return MF_FAIL(ERR, "%s failed: %s", what, cudaGetErrorString(_e));                      \
+        }                                                                                            \
+    } while (0)
+
+class CudaBackend : public DeviceBackend {
+public:
+    const char *Name() const override { return "cuda"; }
+
+    int Init(int deviceId) override
+    {
+        int n = 0;
+        if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+            (void)cudaGetLastError();
+            return ERR_NOT_EXIST;
+        }
+        if (deviceId < 0 || deviceId >= n) return MF_FAIL(ERR_INVALID_PARAM, "device %d outside [0, %d)", deviceId, n);
+        dev_ = deviceId;
+        RT_CHECK(cudaSetDevice(dev_), "cudaSetDevice");
+        RT_CHECK(cudaFree(nullptr), "context creation");
+        cudaDeviceProp prop;
+        RT_CHECK(cudaGetDeviceProperties(&prop, dev_), "cudaGetDeviceProperties");
+        caps_.present = true;
+        caps_.deviceCount = n;
+        caps_.smCount = prop.multiProcessorCount;
+        caps_.ccMajor = prop.major;
+        caps_.ccMinor = prop.minor;
+        caps_.totalMem = prop.totalGlobalMem;
+        snprintf(caps_.name, sizeof(caps_.name), "%s", prop.name);
+        cudaDriverGetVersion(&caps_.driverVersion);
+        cudaRuntimeGetVersion(&caps_.runtimeVersion);
+        bool ok = Load("cuMemAddressReserve", drv_.p_cuMemAddressReserve) && Load("cuMemAddressFree", drv_.p_cuMemAddressFree) &&
+                  Load("cuMemCreate", drv_.p_cuMemCreate) && Load("cuMemRelease", drv_.p_cuMemRelease) &&
+                  Load("cuMemMap", drv_.p_cuMemMap) && Load("cuMemUnmap", drv_.p_cuMemUnmap) &&
+                  Load("cuMemSetAccess", drv_.p_cuMemSetAccess) &&
+                  Load("cuMemExportToShareableHandle", drv_.p_cuMemExportToShareableHandle) &&
+                  Load("cuMemImportFromShareableHandle", drv_.p_cuMemImportFromShareableHandle) &&
+                  Load("cuMemGetAllocationGranularity", drv_.p_cuMemGetAllocationGranularity) &&
+                  Load("cuMemGetAddressRange", drv_.p_cuMemGetAddressRange) &&
+                  Load("cuPointerGetAttribute", drv_.p_cuPointerGetAttribute);
+        Load("cuGetErrorString", drv_.p_cuGetErrorString);
+        drv_.ok = ok;
+        // Every GPU this library targets (sm_100) has virtual memory management; the entry points being
+        // present is the remaining condition.
+        caps_.vmm = ok;
+        caps_.posixFd = ok;  // POSIX file descriptors are the handle type of every Linux driver
+        int hostPtr = 0;
+        cudaDeviceGetAttribute(&hostPtr, cudaDevAttrCanUseHostPointerForRegisteredMem, dev_);
+        caps_.hostPtrForRegistered = hostPtr != 0;
+        if (caps_.vmm) {
+            CUmemAllocationProp ap = AllocProp();
+            size_t g = 0;
+            if (drv_.p_cuMemGetAllocationGranularity(&g, &ap, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS && g != 0)
+                caps_.granularity = g;
+        }
+        grid_ = (int)EnvInt("MF_XCOPY_CTAS_PER_SM", nullptr, 2, 1, 4) * caps_.smCount;
+        return OK;
+    }
+
+    int DeviceId() const override { return dev_; }
+    const DeviceCaps &Caps() const override { return caps_; }
+    int BindThread() override
+    {
+        int cur = -1;
+        if (cudaGetDevice(&cur) == cudaSuccess && cur == dev_) return OK;
+        RT_CHECK(cudaSetDevice(dev_), "cudaSetDevice");
+        return OK;
+    }
+
+    // ---- VMM
+    int Reserve(uint64_t hint, uint64_t size, uint64_t *va) override
+    {
+        if (!caps_.vmm) return ERR_NOT_INIT;
+        CUdeviceptr p = 0;
+        CU_CHECK(drv_.p_cuMemAddressReserve(&p, size, caps_.granularity, (CUdeviceptr)hint, 0), "cuMemAddressReserve");
+        if (hint != 0 && (uint64_t)p != hint) {
+            drv_.p_cuMemAddressFree(p, size);
+            return MF_FAIL(ERR_NO_RESOURCES, "cuMemAddressReserve gave %#lx instead of %#lx", (unsigned long)p, (unsigned long)hint);
+        }
+        *va = (uint64_t)p;
+        return OK;
+    }
+    int ReleaseVa(uint64_t va, uint64_t size) override
+    {
+        CU_CHECK(drv_.p_cuMemAddressFree((CUdeviceptr)va, size), "cuMemAddressFree");
+        return OK;
+    }
+    int CreatePhys(uint64_t size, PhysHandle *h) override
+    {
+        CUmemAllocationProp ap = AllocProp();
+        CUmemGenericAllocationHandle handle;
+        CU_CHECK(drv_.p_cuMemCreate(&handle, size, &ap, 0), "cuMemCreate");
+        *h = (PhysHandle)handle;
+        return OK;
+    }
+    int ExportFd(PhysHandle h, int *fd) override
+    {
+        int out = -1;
+        CU_CHECK(drv_.p_cuMemExportToShareableHandle(&out, (CUmemGenericAllocationHandle)h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0),
+                 "cuMemExportToShareableHandle");
+        *fd = out;
+        return OK;
+    }
+    int ImportFd(int fd, uint64_t, PhysHandle *h) override
+    {
+        CUmemGenericAllocationHandle handle;
+        CUresult r = drv_.p_cuMemImportFromShareableHandle(&handle, (void *)(uintptr_t)fd, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+        close(fd);
+        CU_CHECK(r, "cuMemImportFromShareableHandle");
+        *h = (PhysHandle)handle;
+        return OK;
+    }
+    int Map(uint64_t va, uint64_t size, PhysHandle h) override
+    {
+        CU_CHECK(drv_.p_cuMemMap((CUdeviceptr)va, size, 0, (CUmemGenericAllocationHandle)h, 0), "cuMemMap");
+        CUmemAccessDesc ad{};
+        ad.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        ad.location.id = dev_;
+        ad.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+        CUresult r = drv_.p_cuMemSetAccess((CUdeviceptr)va, size, &ad, 1);
+        if (r != CUDA_SUCCESS) {
+            drv_.p_cuMemUnmap((CUdeviceptr)va, size);
+            CU_CHECK(r, "cuMemSetAccess");
+        }
+        return OK;
+    }
+    int Unmap(uint64_t va, uint64_t size) override
+    {
+        CU_CHECK(drv_.p_cuMemUnmap((CUdeviceptr)va, size), "cuMemUnmap");
+        return OK;
+    }
+    int ReleasePhys(PhysHandle h) override
+    {
+        CU_CHECK(drv_.p_cuMemRelease((CUmemGenericAllocationHandle)h), "cuMemRelease");
+        return OK;
+    }
+
+    // ---- plain memory
+    int Malloc(uint64_t size, uint64_t *ptr) override
+    {
+        void *p = nullptr;
+        RT_CHECK(cudaMalloc(&p, size), "cudaMalloc");
+        *ptr = (uint64_t)p;
+        return OK;
+    }
+    int Free(uint64_t ptr) override
+    {
+        RT_CHECK(cudaFree((void *)ptr), "cudaFree");
+        return OK;
+    }
+    int HostAlloc(uint64_t size, void **ptr) override
+    {
+        RT_CHECK(cudaHostAlloc(ptr, size, cudaHostAllocPortable | cudaHostAllocMapped), "cudaHostAlloc");
+        return OK;
+    }
+    int HostFree(void *ptr) override
+    {
+        RT_CHECK(cudaFreeHost(ptr), "cudaFreeHost");
+        return OK;
+    }
+    int HostRegister(void *ptr, uint64_t size) override
+    {
+        cudaError_t e = cudaHostRegister(ptr, size, cudaHostRegisterPortable | cudaHostRegisterMapped);
+        if (e == cudaErrorHostMemoryAlreadyRegistered) {
+            (void)cudaGetLastError();
+            return OK;
+        }
+        RT_CHECK(e, "cudaHostRegister");
+        return OK;
+    }
+    int HostUnregister(void *ptr) override
+    {
+        cudaError_t e = cudaHostUnregister(ptr);
+        if (e != cudaSuccess) (void)cudaGetLastError();
+        return OK;
+    }
+    int IpcExport(uint64_t ptr, uint8_t blob[64], uint64_t *base, uint64_t *size) override
+    {
+        CUdeviceptr b = 0;
+        size_t sz = 0;
+        CU_CHECK(drv_.p_cuMemGetAddressRange(&b, &sz, (CUdeviceptr)ptr), "cuMemGetAddressRange");
+        cudaIpcMemHandle_t h;
+        RT_CHECK(cudaIpcGetMemHandle(&h, (void *)b), "cudaIpcGetMemHandle");
+        static_assert(sizeof(h) == 64, "IPC handle is 64 bytes");
+        memcpy(blob, &h, sizeof(h));
+        *base = (uint64_t)b;
+        *size = sz;
+        return OK;
+    }
+    int IpcOpen(const uint8_t blob[64], uint64_t *ptr) override
+    {
+        cudaIpcMemHandle_t h;
+        memcpy(&h, blob, sizeof(h));
+        std::lock_guard<std::mutex> g(mu_);
+        std::string key(reinterpret_cast<const char *>(blob), 64);
+        auto it = ipc_.find(key);
+        if (it != ipc_.end()) {  // one allocation may carry several registered buffers: open it once
+            it->second.refs++;
+            *ptr = it->second.ptr;
+            return OK;
+        }
+        void *p = nullptr;
+        RT_CHECK(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+        ipc_[key] = IpcRec{(uint64_t)p, 1};
+        *ptr = (uint64_t)p;
+        return OK;
+    }
+    int IpcClose(uint64_t ptr) override
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        for (auto it = ipc_.begin(); it != ipc_.end(); ++it) {
+            if (it->second.ptr != ptr) continue;
+            if (--it->second.refs == 0) {
+                cudaIpcCloseMemHandle((void *)ptr);
+                ipc_.erase(it);
+            }
+            return OK;
+        }
+        return ERR_NOT_EXIST;
+    }
+    bool IsDevicePointer(uint64_t ptr) override
+    {
+        cudaPointerAttributes a;
+        if (cudaPointerGetAttributes(&a, (const void *)ptr) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return false;
+        }
+        return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+    }
+    int EnablePeerAccess(int peer) override
+    {
+        if (peer == dev_) return OK;
+        cudaError_t e = cudaDeviceEnablePeerAccess(peer, 0);
+        if (e == cudaErrorPeerAccessAlreadyEnabled) {
+            (void)cudaGetLastError();
+            return OK;
+        }
+        RT_CHECK(e, "cudaDeviceEnablePeerAccess");
+        return OK;
+    }
+    int CanAccessPeer(int peer) override
+    {
+        if (peer == dev_) return 1;
+        int can = 0;
+        if (cudaDeviceCanAccessPeer(&can, dev_, peer) != cudaSuccess) (void)cudaGetLastError();
+        return can;
+    }
+
+    // ---- execution
+    int StreamCreate(void **s) override
+    {
+        cudaStream_t st;
+        RT_CHECK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking), "cudaStreamCreate");
+        *s = st;
+        return OK;
+    }
+    int StreamDestroy(void *s) override
+    {
+        cudaStreamDestroy((cudaStream_t)s);
+        return OK;
+    }
+    int StreamSync(void *s) override
+    {
+        RT_CHECK(cudaStreamSynchronize((cudaStream_t)s), "cudaStreamSynchronize");
+        return OK;
+    }
+    int MemcpyAsync(uint64_t dst, uint64_t src, uint64_t len, MemcpyKind, void *s) override
+    {
+        RT_CHECK(cudaMemcpyAsync((void *)dst, (const void *)src, len, cudaMemcpyDefault, (cudaStream_t)s), "cudaMemcpyAsync");
+        return OK;
+    }
+    int MemsetAsync(uint64_t dst, int value, uint64_t len, void *s) override
+    {
+        RT_CHECK(cudaMemsetAsync((void *)dst, value, len, (cudaStream_t)s), "cudaMemsetAsync");
+        return OK;
+    }
+    int LaunchBatchCopy(const CopyItem *items, uint32_t count, void *s) override
+    {
+        if (count == 0) return OK;
+        static_assert(sizeof(CopyItem) == sizeof(mfk::CopyItem), "descriptor layout");
+        int grid = (int)std::min<uint32_t>(count, (uint32_t)grid_);
+        mfk::mf_xcopy_batch_kernel<<<grid, mfk::kCopyThreads, 0, (cudaStream_t)s>>>(reinterpret_cast<const mfk::CopyItem *>(items), count);
+        RT_CHECK(cudaGetLastError(), "xcopy batch launch");
+        return OK;
+    }
+    int LaunchQuantCopy(const QuantItem *items, uint32_t count, uint32_t unit, int inputFp16, int mode, void *s) override
+    {
+        if (count == 0) return OK;
+        if (unit == 0 || (mode == 1 && unit != 128) || mode < 0 || mode > 1) return MF_FAIL(ERR_INVALID_PARAM, "quant copy: unit %u / mode %d unsupported", unit, mode);
+        static_assert(sizeof(QuantItem) == sizeof(mfk::QuantItem), "descriptor layout");
+        auto *q = reinterpret_cast<const mfk::QuantItem *>(items);
+        for (uint32_t off = 0; off < count; off += 65535) {
+            uint32_t n = std::min<uint32_t>(65535, count - off);
+            dim3 grid((unsigned)std::max(1, grid_ / 2), n);
+            cudaStream_t st = (cudaStream_t)s;
+            if (inputFp16) {
+                if (mode == 0) mfk::mf_xcopy_quant_kernel<__half, 0><<<grid, 256, 0, st>>>(q + off, unit);
+                else mfk::mf_xcopy_quant_kernel<__half, 1><<<grid, 256, 0, st>>>(q + off, unit);
+            } else {
+                if (mode == 0) mfk::mf_xcopy_quant_kernel<__nv_bfloat16, 0><<<grid, 256, 0, st>>>(q + off, unit);
+                else mfk::mf_xcopy_quant_kernel<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(q + off, unit);
+            }
+            RT_CHECK(cudaGetLastError(), "xcopy quant launch");
+        }
+        return OK;
+    }
+
+private:
+    CUmemAllocationProp AllocProp() const
+    {
+        CUmemAllocationProp ap{};
+        ap.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+        ap.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+        ap.location.id = dev_;
+        ap.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+        return ap;
+    }
+    struct IpcRec {
+        uint64_t ptr;
+        int refs;
+    };
+    int dev_ = 0;
+    int grid_ = 296;
+    DeviceCaps caps_;
+    DriverApi drv_;
+    std::mutex mu_;
+    std::map<std::string, IpcRec> ipc_;
+};
+
+}  // namespace
+}  // namespace hybm
+}  // namespace mf
+
+extern "C" mf::hybm::DeviceBackend *mf_create_cuda_backend() { return new mf::hybm::CudaBackend(); }

@@ -1,0 +1,135 @@
+// sm_100a copy kernels of the data-operation layer ("xcopy"): every byte that moves between two
+// device-visible addresses (local HBM, a peer's HBM mapped over NVLink, pinned pooled DRAM) goes
+// through these, issued from inside the kernel as 16-byte vector loads and stores.
+//   mf_xcopy_batch_kernel : list of (src, dst, len) work chunks in a pinned, device-visible ring
+//   mf_xcopy_quant_kernel : bf16/fp16 -> int8 (per-unit scale) or fp8 e4m3 (1x128 scale) while pushing
+// Parity of role: src/hybm/csrc/copy_extend/hybm_copy_kernel.cpp:53-90 (contiguous), :114-136 (batch),
+// :163-235 (quantising batch).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <stdint.h>
+
+namespace mfk {
+
+struct CopyItem {
+    uint64_t src;
+    uint64_t dst;
+    uint64_t len;
+};
+
+struct QuantItem {
+    uint64_t src;
+    uint64_t dst;
+    uint64_t scale;
+    uint64_t elems;
+};
+
+constexpr int kCopyThreads = 512;
+constexpr int kCopyUnroll = 4;
+
+// Copies `len` bytes with all threads of the CTA. Fast path: both ends 16-byte aligned relative to
+// each other; the unaligned head and tail go byte-wise.
+__device__ __forceinline__ void cta_copy(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, uint64_t len)
+{
+    const int tid = threadIdx.x;
+    const int nt = blockDim.x;
+    if (((reinterpret_cast<uint64_t>(src) ^ reinterpret_cast<uint64_t>(dst)) & 15) != 0) {
+        // Mutually misaligned: 4-byte words when possible, else bytes. Rare (KV segments are aligned).
+        if ((((reinterpret_cast<uint64_t>(src) | reinterpret_cast<uint64_t>(dst)) | len) & 3) == 0) {
+            const uint32_t *s = reinterpret_cast<const uint32_t *>(src);
+            uint32_t *d = reinterpret_cast<uint32_t *>(dst);
+            for (uint64_t i = tid; i < len / 4; i += nt) d[i] = s[i];
+        } else {
+            for (uint64_t i = tid; i < len; i += nt) dst[i] = src[i];
+        }
+        return;
+    }
+    uint64_t head = (16 - (reinterpret_cast<uint64_t>(src) & 15)) & 15;
+    if (head > len) head = len;
+    if (tid < head) dst[tid] = src[tid];
+    const uint64_t body = (len - head) & ~15ULL;
+    const uint4 *s = reinterpret_cast<const uint4 *>(src + head);
+    uint4 *d = reinterpret_cast<uint4 *>(dst + head);
+    const uint64_t n16 = body >> 4;
+    uint64_t i = tid;
+    // main loop: kCopyUnroll independent 16-byte loads in flight per thread before the first store
+    for (; i + (uint64_t)(kCopyUnroll - 1) * nt < n16; i += (uint64_t)kCopyUnroll * nt) {
+        uint4 v[kCopyUnroll];
+#pragma unroll
+        for (int u = 0; u < kCopyUnroll; u++) v[u] = __ldcs(s + i + (uint64_t)u * nt);
+#pragma unroll
+        for (int u = 0; u < kCopyUnroll; u++) __stcs(d + i + (uint64_t)u * nt, v[u]);
+    }
+    for (; i < n16; i += nt) __stcs(d + i, __ldcs(s + i));
+    const uint64_t tail = len - head - body;
+    if (tid < tail) dst[head + body + tid] = src[head + body + tid];
+}
+
+__global__ void __launch_bounds__(kCopyThreads) mf_xcopy_batch_kernel(const CopyItem *__restrict__ items, uint32_t count)
+{
+    __shared__ CopyItem sh[2];
+    uint32_t i = blockIdx.x;
+    if (i >= count) return;
+    if (threadIdx.x == 0) sh[0] = items[i];
+    __syncthreads();
+    int buf = 0;
+    for (; i < count; i += gridDim.x) {
+        const CopyItem it = sh[buf];
+        // descriptor of the next chunk is fetched (from pinned host memory) while this one is copied
+        if (threadIdx.x == 0 && i + gridDim.x < count) sh[buf ^ 1] = items[i + gridDim.x];
+        cta_copy(reinterpret_cast<const uint8_t *>(it.src), reinterpret_cast<uint8_t *>(it.dst), it.len);
+        __syncthreads();
+        buf ^= 1;
+    }
+}
+
+// One CTA per (item, unit). Two passes over the unit: absolute maximum, then scale + round + store.
+// mode 0: int8, q = rint(x * 127 / amax), dequant factor amax / 127 written to scale[unitIndex]
+// mode 1: fp8 e4m3 (satfinite), q = x * 448 / amax, dequant factor amax / 448
+template <typename In> __device__ __forceinline__ float to_f32(In v);
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+
+template <typename In, int MODE>
+__global__ void __launch_bounds__(256) mf_xcopy_quant_kernel(const QuantItem *__restrict__ items, uint32_t unit)
+{
+    __shared__ float red[8];
+    __shared__ QuantItem it;
+    if (threadIdx.x == 0) it = items[blockIdx.y];
+    __syncthreads();
+    const uint64_t units = (it.elems + unit - 1) / unit;
+    const In *src = reinterpret_cast<const In *>(it.src);
+    float *scales = reinterpret_cast<float *>(it.scale);
+    for (uint64_t u = blockIdx.x; u < units; u += gridDim.x) {
+        const uint64_t b = u * unit;
+        const uint64_t e = min(it.elems, b + (uint64_t)unit);
+        float amax = 0.f;
+        for (uint64_t k = b + threadIdx.x; k < e; k += blockDim.x) amax = fmaxf(amax, fabsf(to_f32<In>(src[k])));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+        __syncthreads();
+        amax = red[0];
+#pragma unroll
+        for (int w = 1; w < 8; w++) amax = fmaxf(amax, red[w]);
+        const float qmax = MODE == 0 ? 127.f : 448.f;
+        const float mul = amax > 0.f ? qmax / amax : 1.f;
+        if (threadIdx.x == 0) scales[u] = amax > 0.f ? amax / qmax : 1.f;
+        if (MODE == 0) {
+            int8_t *dst = reinterpret_cast<int8_t *>(it.dst);
+            for (uint64_t k = b + threadIdx.x; k < e; k += blockDim.x) {
+                float q = rintf(to_f32<In>(src[k]) * mul);
+                dst[k] = (int8_t)fminf(127.f, fmaxf(-127.f, q));
+            }
+        } else {
+            __nv_fp8_storage_t *dst = reinterpret_cast<__nv_fp8_storage_t *>(it.dst);
+            for (uint64_t k = b + threadIdx.x; k < e; k += blockDim.x)
+                dst[k] = __nv_cvt_float_to_fp8(to_f32<In>(src[k]) * mul, __NV_SATFINITE, __NV_E4M3);
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace mfk

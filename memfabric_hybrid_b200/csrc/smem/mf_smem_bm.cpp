@@ -309,4 +309,20 @@ uint32_t smem_bm_get_rank_id_by_gva(smem_bm_t handle, void *gva)
     return e ? e->RankOfGva(gva) : UINT32_MAX;
 }
 
+// Extension (not in the reference ABI): counters of what the copy paths did since creation, in the order
+// kernel launches, kernel work chunks, copy-engine copies, host memcpys, process-VM copies, coalesced items.
+int32_t mf_bm_copy_stats(smem_bm_t handle, uint64_t out[6])
+{
+    auto e = H(handle);
+    if (!e || out == nullptr) return SMEM_INVALID_PARAM;
+    auto s = e->Entity()->CopyStats();
+    out[0] = s.kernelLaunches;
+    out[1] = s.kernelItems;
+    out[2] = s.engineCopies;
+    out[3] = s.hostCopies;
+    out[4] = s.vmCopies;
+    out[5] = s.coalesced;
+    return SMEM_OK;
+}
+
 }  // extern "C"

@@ -1,0 +1,74 @@
+"""The HBM-pool code path (VMM segment, fd channel, batch descriptors, partial results) on a machine
+without a GPU, against the fake device backend whose "device memory" is memfd-backed host memory."""
+import numpy as np
+
+from conftest import free_port
+from mp_util import run_ranks
+
+MiB = 1 << 20
+
+
+def _rank(rank, world, url, sync):
+    import memfabric_hybrid as mf
+    from memfabric_hybrid import bm
+    assert mf.initialize() == 0
+    cfg = bm.BmConfig()
+    cfg.auto_ranking = True        # ranks come from the store, every process races to host it
+    cfg.start_store = True
+    cfg.operation_timeout = 30
+    assert bm.initialize(url, world, 0, cfg) == 0, mf.get_last_err_msg()
+    me = bm.bm_rank_id()
+    assert me in (0, 1)
+    h = bm.create2(id=3, local_dram_size=4 * MiB, max_dram_size=8 * MiB, local_hbm_size=8 * MiB, max_hbm_size=16 * MiB)
+    events = []
+    h.set_group_event_handler(lambda r, ev: events.append((r, int(ev))))
+    assert h.join() == 0, mf.get_last_err_msg()
+    sync.wait(60)
+    peer = 1 - me
+    pdev = h.peer_rank_ptr(peer, bm.BmMemType.DEVICE)
+    mdev = h.peer_rank_ptr(me, bm.BmMemType.DEVICE)
+    assert abs(pdev - mdev) == 16 * MiB
+    src = np.random.default_rng(me).integers(0, 256, 2 * MiB, dtype=np.uint8)
+    n, seg = 16, 128 * 1024
+    rc = h.copy_data_batch([src.ctypes.data + i * seg for i in range(n)], [pdev + i * seg for i in range(n)], [seg] * n, n,
+                           bm.BmCopyType.H2G, 0)
+    assert rc == 0, mf.get_last_err_msg()
+    sync.wait(60)
+    got = np.zeros(2 * MiB, dtype=np.uint8)
+    assert h.copy_data(mdev, got.ctypes.data, 2 * MiB, bm.BmCopyType.G2H, 0) == 0, mf.get_last_err_msg()
+    want = np.random.default_rng(peer).integers(0, 256, 2 * MiB, dtype=np.uint8)
+    assert np.array_equal(got, want)
+    # beyond the 8 MiB that the peer contributed (its slot is 16 MiB): refused
+    assert h.copy_data(src.ctypes.data, pdev + 9 * MiB, 4096, bm.BmCopyType.H2G, 0) != 0
+    mf.get_and_clear_last_err_msg()
+    # the peer extends its slice; after the update the same address is valid
+    sync.wait(60)
+    if me == 0:
+        assert h.extend_local_mem(bm.BmMemType.DEVICE, 4 * MiB) == 0, mf.get_last_err_msg()
+    sync.wait(60)
+    if me == 1:
+        assert h.copy_data(src.ctypes.data, pdev + 9 * MiB, 4096, bm.BmCopyType.H2G, 0) == 0, mf.get_last_err_msg()
+    sync.wait(60)
+    # rank 1 leaves: rank 0 gets a LEAVE event and copies to rank 1 are refused afterwards
+    if me == 1:
+        assert h.leave() == 0
+    sync.wait(60)
+    if me == 0:
+        import time
+        t0 = time.time()
+        while (1, 1) not in events and time.time() - t0 < 20:
+            time.sleep(0.01)
+        assert (1, 1) in events, events
+        assert h.copy_data(src.ctypes.data, pdev, 4096, bm.BmCopyType.H2G, 0) != 0
+        mf.get_and_clear_last_err_msg()
+        assert h.leave() == 0
+    h.destroy()
+    bm.uninitialize(0)
+    mf.uninitialize()
+    return me
+
+
+def test_fake_device_two_ranks():
+    url = f"tcp://127.0.0.1:{free_port()}"
+    ranks = run_ranks(_rank, 2, (url,), timeout=180, env={"MF_DEVICE_BACKEND": "fake"}, with_barrier=True)
+    assert sorted(ranks) == [0, 1]

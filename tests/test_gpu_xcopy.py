@@ -1,0 +1,87 @@
+"""GPU tests of the pooled-HBM copy paths (bit-exact against the source data).
+
+Two processes on ONE device are a valid test of the inter-process mapping (VMM export over the fd
+channel, peer mapping, batched kernel) because the copy kernels never wait on one another."""
+import zlib
+
+import numpy as np
+import pytest
+
+from conftest import free_port
+from mp_util import run_ranks
+
+pytestmark = pytest.mark.gpu
+MiB = 1 << 20
+
+
+def test_smoke_single_rank():
+    from memfabric_hybrid_b200 import smoke
+    smoke.run()
+
+
+def _two_ranks(rank, world, url, sync):
+    import torch
+    import memfabric_hybrid as mf
+    from memfabric_hybrid import bm
+    ndev = torch.cuda.device_count()
+    dev_id = rank % ndev
+    torch.cuda.set_device(dev_id)
+    assert mf.initialize() == 0
+    cfg = bm.BmConfig()
+    cfg.rank_id = rank
+    cfg.start_store = rank == 0
+    cfg.operation_timeout = 60
+    assert bm.initialize(url, world, dev_id, cfg) == 0, mf.get_last_err_msg()
+    h = bm.create2(id=1, local_dram_size=32 * MiB, max_dram_size=32 * MiB, local_hbm_size=128 * MiB, max_hbm_size=128 * MiB)
+    assert h.join() == 0, mf.get_last_err_msg()
+    sync.wait(120)
+    peer = 1 - rank
+    g = torch.Generator("cuda").manual_seed(100 + rank)
+    x = torch.randint(0, 255, (64 * MiB,), dtype=torch.uint8, device="cuda", generator=g)
+    pdev = h.peer_rank_ptr(peer, bm.BmMemType.DEVICE)
+    mdev = h.peer_rank_ptr(rank, bm.BmMemType.DEVICE)
+    # D2RD: odd sizes and offsets on purpose (head/tail paths), plus big aligned segments
+    segs = [(0, 1 * MiB), (1 * MiB + 3, 4097), (2 * MiB + 16, 16 * 1024), (3 * MiB, 8 * MiB), (12 * MiB + 1, 777), (16 * MiB, 32 * MiB)]
+    srcs = [x.data_ptr() + o for o, _ in segs]
+    dsts = [pdev + o for o, _ in segs]
+    sizes = [s for _, s in segs]
+    assert h.copy_data_batch(srcs, dsts, sizes, len(segs), bm.BmCopyType.L2G, 0) == 0, mf.get_last_err_msg()
+    sync.wait(120)
+    # what the peer pushed into OUR slice
+    gp = torch.Generator("cuda").manual_seed(100 + peer)
+    want = torch.randint(0, 255, (64 * MiB,), dtype=torch.uint8, device="cuda", generator=gp)
+    got = torch.zeros(64 * MiB, dtype=torch.uint8, device="cuda")
+    assert h.copy_data_batch([mdev + o for o, _ in segs], [got.data_ptr() + o for o, _ in segs], sizes, len(segs),
+                             bm.BmCopyType.G2L, 0) == 0, mf.get_last_err_msg()
+    for o, s in segs:
+        assert torch.equal(got[o:o + s], want[o:o + s]), f"segment at {o} (+{s}) differs"
+    # RD2D pull from the peer's slice (it holds OUR data) and a D2H leg into the pooled DRAM, then GH2H
+    pulled = torch.zeros(8 * MiB, dtype=torch.uint8, device="cuda")
+    assert h.copy_data(pdev + 3 * MiB, pulled.data_ptr(), 8 * MiB, bm.BmCopyType.G2L, 0) == 0, mf.get_last_err_msg()
+    assert torch.equal(pulled, x[3 * MiB:11 * MiB])
+    mhost = h.peer_rank_ptr(rank, bm.BmMemType.HOST)
+    assert h.copy_data(x.data_ptr(), mhost, 8 * MiB, bm.BmCopyType.L2GH, 0) == 0, mf.get_last_err_msg()
+    back = np.empty(8 * MiB, dtype=np.uint8)
+    assert h.copy_data(mhost, back.ctypes.data, 8 * MiB, bm.BmCopyType.GH2H, 0) == 0
+    assert zlib.crc32(back.tobytes()) == zlib.crc32(x[:8 * MiB].cpu().numpy().tobytes())
+    # async + wait on the internal stream
+    assert h.copy_data(x.data_ptr(), pdev + 48 * MiB, 16 * MiB, bm.BmCopyType.L2G, bm.ASYNC_COPY_FLAG) == 0
+    assert h.wait() == 0
+    # per-item results: one bad item out of three
+    rc, res = h.copy_data_batch_partial_succeed([x.data_ptr(), x.data_ptr(), x.data_ptr()],
+                                                [pdev, pdev + 1024 * MiB, pdev + MiB], [4096, 4096, 4096], 3, bm.BmCopyType.L2G, 0)
+    assert rc == -2012 and res[0] == 0 and res[1] != 0 and res[2] == 0, (rc, res)
+    mf.get_and_clear_last_err_msg()
+    st = h.copy_stats()
+    sync.wait(120)
+    assert h.leave() == 0
+    h.destroy()
+    bm.uninitialize(0)
+    mf.uninitialize()
+    return st["kernel_launches"]
+
+
+def test_two_process_hbm_pool():
+    url = f"tcp://127.0.0.1:{free_port()}"
+    launches = run_ranks(_two_ranks, 2, (url,), timeout=300, with_barrier=True)
+    assert all(l > 0 for l in launches), f"SM copy kernel did not run: {launches}"
