@@ -288,6 +288,72 @@ int ComposeDataOp::Submit(std::vector<ResolvedCopy> &items, void *userStream, ui
     return firstErr != OK ? firstErr : rc;
 }
 
+// ------------------------------------------------------------------------------------------------
+KernelBatch::KernelBatch(ComposeDataOp &op, void *userStream, uint32_t flags, uint64_t totalBytes)
+    : op_(op), lock_(op.mu_), flags_(flags)
+{
+    if (op_.dev_ == nullptr) {
+        rc_ = ERR_NOT_INIT;
+        return;
+    }
+    op_.dev_->BindThread();
+    rc_ = op_.EnsureRing();
+    if (rc_ != OK) return;
+    stream_ = op_.StreamFor(userStream, flags);
+    uint64_t sms = std::max(1, op_.dev_->Caps().smCount);
+    uint64_t chunk = AlignUp(std::max<uint64_t>(totalBytes / (sms * 8), 1), 4096);
+    chunk_ = std::min(std::max<uint64_t>(chunk, 16 * kKiB), op_.chunk_);
+    if (op_.ringHead_ >= op_.ringCap_) Wrap();
+    first_ = op_.ringHead_;
+}
+
+int KernelBatch::Launch()
+{
+    uint64_t n = op_.ringHead_ - first_;
+    if (n == 0) return OK;
+    int rc = op_.dev_->LaunchBatchCopy(op_.ring_ + first_, (uint32_t)n, stream_);
+    if (rc != OK) return rc;
+    if (std::find(op_.ringUsers_.begin(), op_.ringUsers_.end(), stream_) == op_.ringUsers_.end()) op_.ringUsers_.push_back(stream_);
+    op_.stats_.kernelLaunches++;
+    op_.stats_.kernelItems += n;
+    first_ = op_.ringHead_;
+    return OK;
+}
+
+void KernelBatch::Wrap()
+{
+    // every slot is handed out: launch what this batch wrote, wait for all readers, start over
+    int rc = Launch();
+    if (rc != OK && rc_ == OK) rc_ = rc;
+    for (void *s : op_.ringUsers_) op_.dev_->StreamSync(s);
+    op_.ringUsers_.clear();
+    op_.ringHead_ = 0;
+    first_ = 0;
+}
+
+int KernelBatch::Finish()
+{
+    if (rc_ != OK) return rc_;
+    if (pendLen_ != 0) Emit();
+    MF_TRACE_BEGIN(TP_HYBM_BATCH_KERNEL);
+    int rc = Launch();
+    if (rc == OK && rc_ != OK) rc = rc_;
+    if (rc == OK) {
+        if ((flags_ & 1u) != 0) {
+            op_.pending_ = true;
+        } else {
+            rc = op_.dev_->StreamSync(stream_);
+            if (stream_ == op_.stream_) {
+                auto &u = op_.ringUsers_;
+                u.erase(std::remove(u.begin(), u.end(), stream_), u.end());
+                if (u.empty()) op_.ringHead_ = 0;
+            }
+        }
+    }
+    MF_TRACE_END(TP_HYBM_BATCH_KERNEL, rc);
+    return rc;
+}
+
 int ComposeDataOp::Quant(const std::vector<QuantItem> &items, uint32_t unit, int inputFp16, int mode, void *userStream)
 {
     if (dev_ == nullptr) return ERR_NOT_INIT;

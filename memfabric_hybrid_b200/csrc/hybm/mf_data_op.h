@@ -77,6 +77,53 @@ private:
     std::unique_ptr<ThreadPool> pool_;
     DataOpStats stats_;
     bool pending_ = false;
+    friend class KernelBatch;
+};
+
+// Streaming writer for the hot case (every item goes to the SM kernel): the caller validates an item
+// and hands it over; neighbours that continue one another are merged, the result is cut into work
+// chunks written straight into the descriptor ring, and one launch covers the batch. No per-item
+// allocation, no intermediate list. Holds the operator's lock for its lifetime.
+class KernelBatch {
+public:
+    KernelBatch(ComposeDataOp &op, void *userStream, uint32_t flags, uint64_t totalBytes);
+    bool Ready() const { return rc_ == OK; }
+    inline void Add(uint64_t src, uint64_t dst, uint64_t len)
+    {
+        if (pendLen_ != 0 && pendSrc_ + pendLen_ == src && pendDst_ + pendLen_ == dst) {
+            pendLen_ += len;
+            op_.stats_.coalesced++;
+            return;
+        }
+        if (pendLen_ != 0) Emit();
+        pendSrc_ = src;
+        pendDst_ = dst;
+        pendLen_ = len;
+    }
+    int Finish();
+
+private:
+    inline void Emit()
+    {
+        uint64_t off = 0;
+        while (off < pendLen_) {
+            if (op_.ringHead_ >= op_.ringCap_) Wrap();
+            uint64_t n = pendLen_ - off < chunk_ ? pendLen_ - off : chunk_;
+            op_.ring_[op_.ringHead_++] = CopyItem{pendSrc_ + off, pendDst_ + off, n};
+            off += n;
+        }
+        pendLen_ = 0;
+    }
+    void Wrap();
+    int Launch();
+    ComposeDataOp &op_;
+    std::unique_lock<std::mutex> lock_;
+    void *stream_ = nullptr;
+    uint32_t flags_;
+    uint64_t chunk_ = 0;
+    uint64_t first_ = 0;
+    uint64_t pendSrc_ = 0, pendDst_ = 0, pendLen_ = 0;
+    int rc_ = OK;
 };
 
 }  // namespace hybm

@@ -523,7 +523,38 @@ int Entity::BatchCopyData(const hybm_batch_copy_params &p, hybm_data_copy_direct
     if (p.sources == nullptr || p.destinations == nullptr || p.dataSizes == nullptr || p.batchSize == 0 ||
         dir >= HYBM_DATA_COPY_DIRECTION_BUTT)
         return MF_FAIL(ERR_INVALID_PARAM, "batch copy: null array, empty batch or bad direction %d", (int)dir);
-    // One pass: validate + resolve each item with arithmetic only (no map lookups, no locks).
+    // Hot path: every item is device<->device with at least one side in the HBM pool (KV-block put/get).
+    // Pass 1 validates with arithmetic only; pass 2 streams the items into the descriptor ring.
+    if (perItem == nullptr && dev_ != nullptr && hbm_ && hbm_->Base() != 0 &&
+        (dir == HYBM_LOCAL_DEVICE_TO_GLOBAL_DEVICE || dir == HYBM_GLOBAL_DEVICE_TO_GLOBAL_DEVICE ||
+         dir == HYBM_GLOBAL_DEVICE_TO_LOCAL_DEVICE)) {
+        const uint64_t base = hbm_->Base(), slot = hbm_->Slot();
+        const uint64_t end = base + slot * opt_.rankCount;
+        const bool srcPool = dir != HYBM_LOCAL_DEVICE_TO_GLOBAL_DEVICE, dstPool = dir != HYBM_GLOBAL_DEVICE_TO_LOCAL_DEVICE;
+        Segment *seg = hbm_.get();
+        auto poolOk = [&](uint64_t a, uint64_t len) {
+            if (a < base || a >= end) return false;
+            uint64_t rel = a - base;
+            uint32_t r = (uint32_t)(rel / slot);
+            return rel - (uint64_t)r * slot + len <= seg->MappedBytes(r);
+        };
+        uint64_t total = 0;
+        for (uint32_t i = 0; i < p.batchSize; i++) {
+            uint64_t s = reinterpret_cast<uint64_t>(p.sources[i]), d = reinterpret_cast<uint64_t>(p.destinations[i]);
+            uint64_t len = p.dataSizes[i];
+            if (s == 0 || d == 0 || len == 0 || (srcPool && !poolOk(s, len)) || (dstPool && !poolOk(d, len)))
+                return MF_FAIL(ERR_INVALID_PARAM, "batch copy item %u (%p -> %p, %lu bytes): null, empty or outside the mapped pool",
+                               i, p.sources[i], p.destinations[i], (unsigned long)len);
+            total += len;
+        }
+        KernelBatch kb(*ops_, stream, flags, total);
+        if (kb.Ready()) {
+            for (uint32_t i = 0; i < p.batchSize; i++)
+                kb.Add(reinterpret_cast<uint64_t>(p.sources[i]), reinterpret_cast<uint64_t>(p.destinations[i]), p.dataSizes[i]);
+            return kb.Finish();
+        }
+    }
+    // General path: validate + resolve each item with arithmetic only (no map lookups, no locks).
     std::vector<ResolvedCopy> items;
     items.reserve(p.batchSize);
     int firstErr = OK;

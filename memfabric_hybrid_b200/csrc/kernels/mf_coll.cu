@@ -1,0 +1,555 @@
+// Collectives on the symmetric heap: each kernel reads and writes peers' slots directly over NVLink
+// (plain loads/stores on mapped peer memory) and fuses the x scale and the output cast into the same
+// pass. One launch per collective; CTA b of every rank works on the same element ranges as CTA b of
+// every other rank and synchronises only with those (lane flags), so no grid-wide barrier is needed.
+//   allreduce  one-shot : stage -> sync -> every rank reads all W copies, reduces, writes its output
+//   allreduce  two-shot : stage -> sync -> reduce own 1/W -> push result to all -> sync -> unstage
+//   reduce_scatter      : stage -> sync -> reduce own 1/W straight into the output
+//   allgather           : push own shard into every peer's gather buffer -> sync -> unstage
+//   broadcast, all-to-all-v, send / recv
+// Staging buffers A (inputs) and B (results) live in the slot; the host alternates between two sets
+// per call so that no trailing synchronisation is needed (a rank can only start call k+2 after every
+// peer entered call k+1, i.e. finished reading the buffers of call k).
+// Parity of role: app/zbal/src/csrc/operators/npu/aicore/ops/classic/zbal_kernel_{allreduce,
+// reducescatter,allgather,alltoallv,broadcast,send,recv,barrier}.* of the reference.
+#include <cooperative_groups.h>
+
+#include "mf_coll.cuh"
+
+namespace mfk {
+
+struct CollArgs {
+    Team team;
+    uint64_t in;               // local input (rank 0's when emulating)
+    uint64_t out;              // local output
+    uint64_t in_rank_stride;   // emulation only: distance between consecutive ranks' local buffers
+    uint64_t out_rank_stride;
+    uint64_t n;                // elements: allreduce/broadcast total; reduce_scatter total input; allgather per-rank input
+    uint64_t stage_a;          // slot offset of staging A
+    uint64_t stage_b;          // slot offset of staging B
+    float scale;
+    int op;
+    uint32_t epoch;
+    uint32_t zero_copy;        // input already sits at stage_a of every slot
+    uint32_t root;
+    uint32_t algo;             // allreduce: 0 one-shot, 1 two-shot
+};
+
+struct Range {
+    uint64_t beg, end;
+};
+
+template <int VN> __device__ __forceinline__ Range cta_range(uint64_t count)
+{
+    uint64_t per = (count + gridDim.x - 1) / gridDim.x;
+    per = (per + VN - 1) / VN * VN;
+    Range r;
+    r.beg = min(count, (uint64_t)blockIdx.x * per);
+    r.end = min(count, r.beg + per);
+    return r;
+}
+
+__device__ __forceinline__ bool aligned16(const void *p) { return (reinterpret_cast<uint64_t>(p) & 15) == 0; }
+
+// dst[i] = (TD)(src[i] * scale) for i in [beg, end): 16-byte vectors where both ends allow it
+template <typename TS, typename TD>
+__device__ __forceinline__ void cta_convert_copy(const TS *src, TD *dst, uint64_t beg, uint64_t end, float scale)
+{
+    constexpr int G = 8;  // elements per step: one 16-byte vector of the narrower type
+    uint64_t vend = beg;
+    if (aligned16(src + beg) && aligned16(dst + beg)) {
+        vend = beg + (end - beg) / G * G;
+        for (uint64_t i = beg + (uint64_t)threadIdx.x * G; i < vend; i += (uint64_t)blockDim.x * G) {
+            float f[G];
+            if (Vec<TS>::N == G) {
+                float t[Vec<TS>::N];
+                Vec<TS>::load(src + i, t);
+#pragma unroll
+                for (int k = 0; k < Vec<TS>::N; k++) f[k] = t[k];
+            } else {
+#pragma unroll
+                for (int h = 0; h < G / Vec<TS>::N; h++) {
+                    float t[Vec<TS>::N];
+                    Vec<TS>::load(src + i + h * Vec<TS>::N, t);
+#pragma unroll
+                    for (int k = 0; k < Vec<TS>::N; k++) f[h * Vec<TS>::N + k] = t[k];
+                }
+            }
+            if (scale != 1.f) {
+#pragma unroll
+                for (int k = 0; k < G; k++) f[k] *= scale;
+            }
+#pragma unroll
+            for (int h = 0; h < G / Vec<TD>::N; h++) {
+                float t[Vec<TD>::N];
+#pragma unroll
+                for (int k = 0; k < Vec<TD>::N; k++) t[k] = f[h * Vec<TD>::N + k];
+                Vec<TD>::store(dst + i + h * Vec<TD>::N, t);
+            }
+        }
+    }
+    for (uint64_t i = vend + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = Vec<TS>::to_f(src[i]);
+        dst[i] = Vec<TD>::from_f(scale != 1.f ? v * scale : v);
+    }
+}
+
+// Raw copy of [beg, end) elements of T (no conversion).
+template <typename T> __device__ __forceinline__ void cta_raw_copy(const T *src, T *dst, uint64_t beg, uint64_t end)
+{
+    constexpr int VN = 16 / sizeof(T);
+    uint64_t vend = beg;
+    if (aligned16(src + beg) && aligned16(dst + beg)) {
+        vend = beg + (end - beg) / VN * VN;
+        for (uint64_t i = beg + (uint64_t)threadIdx.x * VN; i < vend; i += (uint64_t)blockDim.x * VN)
+            *reinterpret_cast<uint4 *>(dst + i) = __ldcg(reinterpret_cast<const uint4 *>(src + i));
+    }
+    for (uint64_t i = vend + threadIdx.x; i < end; i += blockDim.x) dst[i] = src[i];
+}
+
+// Reduces element range [beg, end) of staging A across all ranks (offset `base` elements into A) and
+// hands each result vector to `sink(i, values, count)`. Loads are issued in an order rotated by the
+// rank to spread the traffic over the peers; the accumulation order is fixed (rank 0 first) so that
+// every rank computes bit-identical results.
+template <typename T, bool INT, int W, typename Sink>
+__device__ __forceinline__ void reduce_ranks(const Team &t, uint32_t me, uint64_t stage_a, uint64_t base, uint64_t beg, uint64_t end,
+                                             int op, Sink sink)
+{
+    constexpr int VN = Vec<T>::N;
+    const uint32_t world = W > 0 ? (uint32_t)W : t.world;
+    uint64_t vend = beg;
+    if (((base + beg) * sizeof(T) & 15) == 0 && (stage_a & 15) == 0) {
+        vend = beg + (end - beg) / VN * VN;
+        for (uint64_t i = beg + (uint64_t)threadIdx.x * VN; i < vend; i += (uint64_t)blockDim.x * VN) {
+            float acc[VN];
+            if (W > 0) {
+                uint4 raw[W > 0 ? W : 1];
+#pragma unroll
+                for (int k = 0; k < W; k++) {
+                    const uint32_t r = (me + k) % W;
+                    const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(peer_ptr(t, r, stage_a)) + base + i));
+#pragma unroll
+                    for (int q = 0; q < W; q++)
+                        if (q == (int)r) raw[q] = v;  // static indexing keeps raw[] in registers
+                }
+#pragma unroll
+                for (int r = 0; r < W; r++) {
+                    float f[VN];
+                    Vec<T>::unpack(raw[r], f);
+#pragma unroll
+                    for (int k = 0; k < VN; k++) acc[k] = r == 0 ? f[k] : red_apply<INT>(acc[k], f[k], op);
+                }
+            } else {
+                for (uint32_t r = 0; r < world; r++) {
+                    float f[VN];
+                    Vec<T>::load(reinterpret_cast<const T *>(peer_ptr(t, r, stage_a)) + base + i, f);
+#pragma unroll
+                    for (int k = 0; k < VN; k++) acc[k] = r == 0 ? f[k] : red_apply<INT>(acc[k], f[k], op);
+                }
+            }
+            sink(i, acc, VN);
+        }
+    }
+    for (uint64_t i = vend + threadIdx.x; i < end; i += blockDim.x) {
+        float acc[VN];
+        for (uint32_t r = 0; r < world; r++) {
+            float f = Vec<T>::to_f(__ldcg(reinterpret_cast<const T *>(peer_ptr(t, r, stage_a)) + base + i));
+            acc[0] = r == 0 ? f : red_apply<INT>(acc[0], f, op);
+        }
+        sink(i, acc, 1);
+    }
+}
+
+// Epilogue: x scale (floating types), cast to TO, store `cnt` values at dst + i.
+template <typename TO, bool INT> __device__ __forceinline__ void emit(TO *dst, uint64_t i, float *acc, int cnt, float scale)
+{
+    constexpr int VN = Vec<TO>::N;
+    if (!INT && scale != 1.f)
+        for (int k = 0; k < cnt; k++) acc[k] *= scale;
+    if (cnt == VN && aligned16(dst + i)) {
+        float g[VN];
+#pragma unroll
+        for (int k = 0; k < VN; k++) g[k] = acc[k];
+        Vec<TO>::store(dst + i, g);
+    } else if (sizeof(TO) == 2 && cnt == 4 && (reinterpret_cast<uint64_t>(dst + i) & 7) == 0) {
+        // four 16-bit results of a 32-bit input vector: one 8-byte store
+        union {
+            uint2 u;
+            TO h[4];
+        } pk;
+#pragma unroll
+        for (int k = 0; k < 4; k++) pk.h[k] = Vec<TO>::from_f(acc[k]);
+        *reinterpret_cast<uint2 *>(dst + i) = pk.u;
+    } else {
+        for (int k = 0; k < cnt; k++) dst[i + k] = Vec<TO>::from_f(acc[k]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+template <typename T, typename TO, bool INT, int W> __global__ void __launch_bounds__(512) k_allreduce(CollArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const uint32_t world = t.world;
+    const T *in = reinterpret_cast<const T *>(a.in + (uint64_t)me * a.in_rank_stride);
+    TO *out = reinterpret_cast<TO *>(a.out + (uint64_t)me * a.out_rank_stride);
+    T *myA = reinterpret_cast<T *>(peer_ptr(t, me, a.stage_a));
+    constexpr int VN = Vec<T>::N;
+    if (a.algo == 0) {
+        const Range rg = cta_range<8>(a.n);
+        if (!a.zero_copy) cta_raw_copy<T>(in, myA, rg.beg, rg.end);
+        if (!lane_sync(t, me, 0, a.epoch, 0x100)) return;
+        reduce_ranks<T, INT, W>(t, me, a.stage_a, 0, rg.beg, rg.end, a.op,
+                                [&](uint64_t i, float *acc, int cnt) { emit<TO, INT>(out, i, acc, cnt, a.scale); });
+        return;
+    }
+    // two-shot: chunk c = elements [c * C, (c + 1) * C) belongs to rank c
+    uint64_t C = (a.n + world - 1) / world;
+    C = (C + 7) / 8 * 8;
+    const Range sub = cta_range<8>(C);
+    if (!a.zero_copy) {
+        for (uint32_t c = 0; c < world; c++) {
+            const uint64_t b = min(a.n, c * C + sub.beg), e = min(a.n, c * C + sub.end);
+            cta_raw_copy<T>(in, myA, b, e);
+        }
+    }
+    if (!lane_sync(t, me, 0, a.epoch, 0x110)) return;
+    {
+        const uint64_t b = min(a.n, me * C + sub.beg), e = min(a.n, me * C + sub.end);
+        reduce_ranks<T, INT, W>(t, me, a.stage_a, 0, b, e, a.op, [&](uint64_t i, float *acc, int cnt) {
+            if (!INT && a.scale != 1.f)
+                for (int k = 0; k < cnt; k++) acc[k] *= a.scale;
+            // push the finished values into every rank's result buffer (own included)
+            for (uint32_t k = 0; k < world; k++) {
+                const uint32_t r = (me + k) % world;
+                TO *dst = reinterpret_cast<TO *>(peer_ptr(t, r, a.stage_b));
+                float tmp[VN];
+#pragma unroll
+                for (int q = 0; q < VN; q++) tmp[q] = acc[q];
+                emit<TO, true>(dst, i, tmp, cnt, 1.f);
+            }
+        });
+    }
+    if (!lane_sync(t, me, 1, a.epoch, 0x111)) return;
+    const TO *myB = reinterpret_cast<const TO *>(peer_ptr(t, me, a.stage_b));
+    for (uint32_t c = 0; c < world; c++) {
+        const uint64_t b = min(a.n, c * C + sub.beg), e = min(a.n, c * C + sub.end);
+        cta_raw_copy<TO>(myB, out, b, e);
+    }
+}
+
+// reduce_scatter: input n = W * m elements, output m elements (rank r gets the reduction of chunk r)
+template <typename T, typename TO, bool INT, int W> __global__ void __launch_bounds__(512) k_reduce_scatter(CollArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const uint32_t world = t.world;
+    const T *in = reinterpret_cast<const T *>(a.in + (uint64_t)me * a.in_rank_stride);
+    TO *out = reinterpret_cast<TO *>(a.out + (uint64_t)me * a.out_rank_stride);
+    T *myA = reinterpret_cast<T *>(peer_ptr(t, me, a.stage_a));
+    constexpr int VN = Vec<T>::N;
+    const uint64_t m = a.n / world;
+    const Range sub = cta_range<8>(m);
+    if (!a.zero_copy)
+        for (uint32_t c = 0; c < world; c++) cta_raw_copy<T>(in, myA, c * m + sub.beg, c * m + sub.end);
+    if (!lane_sync(t, me, 0, a.epoch, 0x120)) return;
+    reduce_ranks<T, INT, W>(t, me, a.stage_a, (uint64_t)me * m, sub.beg, sub.end, a.op,
+                            [&](uint64_t i, float *acc, int cnt) { emit<TO, INT>(out, i, acc, cnt, a.scale); });
+}
+
+// allgather: every rank contributes n elements; output W * n. Shards are pushed (one NVLink crossing).
+template <typename T, typename TO> __global__ void __launch_bounds__(512) k_allgather(CollArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const uint32_t world = t.world;
+    const T *in = reinterpret_cast<const T *>(a.in + (uint64_t)me * a.in_rank_stride);
+    TO *out = reinterpret_cast<TO *>(a.out + (uint64_t)me * a.out_rank_stride);
+    constexpr int VN = Vec<T>::N;
+    const Range sub = cta_range<8>(a.n);
+    for (uint32_t k = 0; k < world; k++) {
+        const uint32_t r = (me + k) % world;
+        TO *dst = reinterpret_cast<TO *>(peer_ptr(t, r, a.stage_b)) + (uint64_t)me * a.n;
+        cta_convert_copy<T, TO>(in, dst, sub.beg, sub.end, a.scale);
+    }
+    if (!lane_sync(t, me, 0, a.epoch, 0x130)) return;
+    const TO *myB = reinterpret_cast<const TO *>(peer_ptr(t, me, a.stage_b));
+    for (uint32_t c = 0; c < world; c++) cta_raw_copy<TO>(myB + (uint64_t)c * a.n, out + (uint64_t)c * a.n, sub.beg, sub.end);
+}
+
+// broadcast of n elements from a.root
+template <typename T> __global__ void __launch_bounds__(512) k_broadcast(CollArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const uint32_t world = t.world;
+    const T *in = reinterpret_cast<const T *>(a.in + (uint64_t)me * a.in_rank_stride);
+    T *out = reinterpret_cast<T *>(a.out + (uint64_t)me * a.out_rank_stride);
+    const Range sub = cta_range<8>(a.n);
+    if (me == a.root) {
+        for (uint32_t k = 0; k < world; k++) {
+            const uint32_t r = (me + k) % world;
+            cta_raw_copy<T>(in, reinterpret_cast<T *>(peer_ptr(t, r, a.stage_b)), sub.beg, sub.end);
+        }
+    }
+    if (!lane_sync(t, me, 0, a.epoch, 0x140)) return;
+    cta_raw_copy<T>(reinterpret_cast<const T *>(peer_ptr(t, me, a.stage_b)), out, sub.beg, sub.end);
+}
+
+// all-to-all-v (bytes). Each rank stages its whole send buffer plus its (offset, count) table; after the
+// handshake every rank pulls its pieces from the peers' staging.
+//   table in staging A header: W x {u64 send_off, u64 send_cnt} toward each destination, bytes
+struct A2AArgs {
+    Team team;
+    uint64_t in, out, in_rank_stride, out_rank_stride;
+    uint64_t meta;       // device array [W][4] u64 per emulated rank: send_off, send_cnt, recv_off, recv_cnt (bytes)
+    uint64_t meta_rank_stride;
+    uint64_t in_bytes;   // total bytes of the send buffer
+    uint64_t stage_a;
+    uint32_t epoch;
+};
+constexpr uint64_t kA2AHeader = 4096;
+
+__global__ void __launch_bounds__(512) k_alltoallv(A2AArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const uint32_t world = t.world;
+    const uint8_t *in = reinterpret_cast<const uint8_t *>(a.in + (uint64_t)me * a.in_rank_stride);
+    uint8_t *out = reinterpret_cast<uint8_t *>(a.out + (uint64_t)me * a.out_rank_stride);
+    const uint64_t *meta = reinterpret_cast<const uint64_t *>(a.meta + (uint64_t)me * a.meta_rank_stride);
+    uint8_t *myA = peer_ptr(t, me, a.stage_a);
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    if (blockIdx.x == 0 && threadIdx.x < world) {
+        uint64_t *hdr = reinterpret_cast<uint64_t *>(myA);
+        hdr[2 * threadIdx.x] = meta[4 * threadIdx.x];
+        hdr[2 * threadIdx.x + 1] = meta[4 * threadIdx.x + 1];
+    }
+    const Range sub = cta_range<16>(a.in_bytes);
+    cta_raw_copy<uint8_t>(in, myA + kA2AHeader, sub.beg, sub.end);
+    // Lane b passing the handshake means lane b of every peer finished staging. A piece pulled below may
+    // have been staged by ANY lane of the peer, so all local lanes must have passed before anyone pulls:
+    // the grid-wide sync of this (cooperative) launch provides exactly that. A lane that timed out still
+    // joins the grid sync (leaving it would hang the others) and skips its pulls.
+    const bool ok = lane_sync(t, me, 0, a.epoch, 0x150);
+    grid.sync();
+    if (!ok) return;
+    for (uint32_t k = 0; k < world; k++) {
+        const uint32_t r = (me + k) % world;
+        const uint64_t *hdr = reinterpret_cast<const uint64_t *>(peer_ptr(t, r, a.stage_a));
+        const uint64_t soff = __ldcg(hdr + 2 * me), scnt = __ldcg(hdr + 2 * me + 1);
+        const uint64_t roff = meta[4 * r + 2], rcnt = meta[4 * r + 3];
+        const uint64_t bytes = min(scnt, rcnt);
+        const Range pr = cta_range<16>(bytes);
+        cta_raw_copy<uint8_t>(peer_ptr(t, r, a.stage_a) + kA2AHeader + soff, out + roff, pr.beg, pr.end);
+    }
+}
+
+// Point-to-point: the sender writes into the receiver's slot and raises a channel flag; the receiver
+// waits, copies out and acknowledges, which frees the landing area for the next message of that pair.
+struct P2PArgs {
+    Team team;
+    uint64_t buf;       // local send or receive buffer
+    uint64_t bytes;
+    uint64_t stage_off; // landing area in the RECEIVER's slot
+    uint32_t peer;
+    uint32_t epoch;     // per-pair message number, starts at 1
+    uint32_t channel;   // flag channel of this ordered pair
+};
+
+__global__ void __launch_bounds__(512) k_send(P2PArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = t.rank;
+    __shared__ int ok;
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    // CTA 0 waits until the receiver consumed the previous message of this pair (ack flag in OUR slot)
+    // and publishes the verdict through the slot so that every CTA takes the same branch.
+    uint32_t *verdict = reinterpret_cast<uint32_t *>(peer_ptr(t, me, kBarrierOff + (uint64_t)a.channel * 256)) + 16;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        int good = 1;
+        if (a.epoch > 1) {
+            const uint32_t *ack = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, kBarrierOff + (uint64_t)a.channel * 256)) + 32 + a.peer;  // one ack word per receiver
+            if (!wait_flag(ack, a.epoch - 1, t.spin_limit)) {
+                good = 0;
+                report_timeout(t, me, 0x160, a.epoch);
+            }
+        }
+        *verdict = good;
+        __threadfence();
+    }
+    grid.sync();
+    if (threadIdx.x == 0) ok = (int)__ldcg(verdict);
+    __syncthreads();
+    if (ok) {
+        const Range sub = cta_range<16>(a.bytes);
+        cta_raw_copy<uint8_t>(reinterpret_cast<const uint8_t *>(a.buf), peer_ptr(t, a.peer, a.stage_off), sub.beg, sub.end);
+        __threadfence_system();
+    }
+    grid.sync();
+    if (ok && blockIdx.x == 0 && threadIdx.x == 0)
+        st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, a.peer, kBarrierOff + (uint64_t)a.channel * 256)), a.epoch);
+}
+
+__global__ void __launch_bounds__(512) k_recv(P2PArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = t.rank;
+    __shared__ int ok;
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    uint32_t *verdict = reinterpret_cast<uint32_t *>(peer_ptr(t, me, kBarrierOff + (uint64_t)a.channel * 256)) + 17;
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        const uint32_t *flag = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, kBarrierOff + (uint64_t)a.channel * 256));
+        int good = wait_flag(flag, a.epoch, t.spin_limit) ? 1 : 0;
+        if (!good) report_timeout(t, me, 0x161, a.epoch);
+        *verdict = good;
+        __threadfence();
+    }
+    grid.sync();
+    if (threadIdx.x == 0) ok = (int)__ldcg(verdict);
+    __syncthreads();
+    if (ok) {
+        const Range sub = cta_range<16>(a.bytes);
+        cta_raw_copy<uint8_t>(peer_ptr(t, me, a.stage_off), reinterpret_cast<uint8_t *>(a.buf), sub.beg, sub.end);
+    }
+    grid.sync();
+    if (ok && blockIdx.x == 0 && threadIdx.x == 0)
+        st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, a.peer, kBarrierOff + (uint64_t)a.channel * 256)) + 32 + me, a.epoch);
+}
+
+__global__ void k_barrier(Team t, uint32_t channel, uint32_t epoch)
+{
+    team_barrier(t, team_rank(t), channel, epoch);
+}
+
+// Waits on a flag of the caller's own slot that the caller names; used to show that a wait which
+// nothing satisfies ends with a status, not a hang.
+__global__ void k_wait_flag(Team t, uint64_t flag_off, uint32_t epoch)
+{
+    const uint32_t me = team_rank(t);
+    if (threadIdx.x == 0 && !wait_flag(reinterpret_cast<const uint32_t *>(peer_ptr(t, me, flag_off)), epoch, t.spin_limit))
+        report_timeout(t, me, 0x1ff, epoch);
+}
+
+}  // namespace mfk
+
+// ------------------------------------------------------------------------------------------------
+using namespace mfk;
+
+namespace {
+template <typename K, typename A> int launch(K kernel, const A &args, int ctas, int threads, cudaStream_t s, bool coop)
+{
+    dim3 grid((unsigned)ctas, args.team.emu ? args.team.world : 1);
+    if (coop || args.team.emu) {
+        void *params[] = {const_cast<A *>(&args)};
+        cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(kernel), grid, dim3(threads), params, 0, s);
+        return e == cudaSuccess ? 0 : (int)e;
+    }
+    kernel<<<grid, threads, 0, s>>>(args);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+template <typename T, typename TO, bool INT> int launch_allreduce(const CollArgs &a, int ctas, int threads, cudaStream_t s)
+{
+    switch (a.team.world) {
+        case 2: return launch(k_allreduce<T, TO, INT, 2>, a, ctas, threads, s, false);
+        case 4: return launch(k_allreduce<T, TO, INT, 4>, a, ctas, threads, s, false);
+        case 8: return launch(k_allreduce<T, TO, INT, 8>, a, ctas, threads, s, false);
+        default: return launch(k_allreduce<T, TO, INT, 0>, a, ctas, threads, s, false);
+    }
+}
+template <typename T, typename TO, bool INT> int launch_rs(const CollArgs &a, int ctas, int threads, cudaStream_t s)
+{
+    switch (a.team.world) {
+        case 2: return launch(k_reduce_scatter<T, TO, INT, 2>, a, ctas, threads, s, false);
+        case 4: return launch(k_reduce_scatter<T, TO, INT, 4>, a, ctas, threads, s, false);
+        case 8: return launch(k_reduce_scatter<T, TO, INT, 8>, a, ctas, threads, s, false);
+        default: return launch(k_reduce_scatter<T, TO, INT, 0>, a, ctas, threads, s, false);
+    }
+}
+}  // namespace
+
+extern "C" {
+
+// kind: 0 allreduce, 1 reduce_scatter, 2 allgather, 3 broadcast. dtypes as mfk::DType. Returns 0 or a CUDA error.
+int mf_coll_launch(int kind, int in_dtype, int out_dtype, const CollArgs *args, int ctas, int threads, void *stream)
+{
+    if (args == nullptr || ctas <= 0 || ctas > kMaxCtas || threads <= 0 || threads > 512 || args->team.world == 0 ||
+        args->team.world > kMaxRanks || (int)args->team.world > threads)
+        return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const CollArgs &a = *args;
+    const bool same = in_dtype == out_dtype;
+    const bool to_bf16 = out_dtype == DT_BF16;
+    if (!same && !to_bf16) return -2;
+    switch (kind) {
+        case 0:
+            if (in_dtype == DT_BF16) return launch_allreduce<__nv_bfloat16, __nv_bfloat16, false>(a, ctas, threads, s);
+            if (in_dtype == DT_F16) return same ? launch_allreduce<__half, __half, false>(a, ctas, threads, s) : -2;
+            if (in_dtype == DT_F32)
+                return same ? launch_allreduce<float, float, false>(a, ctas, threads, s)
+                            : launch_allreduce<float, __nv_bfloat16, false>(a, ctas, threads, s);
+            if (in_dtype == DT_I32) return same ? launch_allreduce<int, int, true>(a, ctas, threads, s) : -2;
+            return -2;
+        case 1:
+            if (in_dtype == DT_BF16) return launch_rs<__nv_bfloat16, __nv_bfloat16, false>(a, ctas, threads, s);
+            if (in_dtype == DT_F16) return same ? launch_rs<__half, __half, false>(a, ctas, threads, s) : -2;
+            if (in_dtype == DT_F32)
+                return same ? launch_rs<float, float, false>(a, ctas, threads, s) : launch_rs<float, __nv_bfloat16, false>(a, ctas, threads, s);
+            if (in_dtype == DT_I32) return same ? launch_rs<int, int, true>(a, ctas, threads, s) : -2;
+            return -2;
+        case 2:
+            if (in_dtype == DT_BF16) return launch(k_allgather<__nv_bfloat16, __nv_bfloat16>, a, ctas, threads, s, false);
+            if (in_dtype == DT_F16) return same ? launch(k_allgather<__half, __half>, a, ctas, threads, s, false) : -2;
+            if (in_dtype == DT_F32)
+                return same ? launch(k_allgather<float, float>, a, ctas, threads, s, false)
+                            : launch(k_allgather<float, __nv_bfloat16>, a, ctas, threads, s, false);
+            if (in_dtype == DT_I32) return same ? launch(k_allgather<int, int>, a, ctas, threads, s, false) : -2;
+            return -2;
+        case 3:
+            // broadcast moves bytes: n is in units of the element size chosen by the caller
+            if (in_dtype == DT_F32 || in_dtype == DT_I32) return launch(k_broadcast<float>, a, ctas, threads, s, false);
+            return launch(k_broadcast<__nv_bfloat16>, a, ctas, threads, s, false);
+        default:
+            return -3;
+    }
+}
+
+int mf_coll_alltoallv(const A2AArgs *args, int ctas, int threads, void *stream)
+{
+    if (args == nullptr || ctas <= 0 || ctas > kMaxCtas || threads < (int)args->team.world || threads > 512) return -1;
+    // lanes of one rank wait on a shared counter: the grid must be co-resident
+    return launch(k_alltoallv, *args, ctas, threads, (cudaStream_t)stream, true);
+}
+
+int mf_coll_send(const P2PArgs *args, int ctas, void *stream) { return args ? launch(k_send, *args, ctas, 512, (cudaStream_t)stream, true) : -1; }
+int mf_coll_recv(const P2PArgs *args, int ctas, void *stream) { return args ? launch(k_recv, *args, ctas, 512, (cudaStream_t)stream, true) : -1; }
+
+int mf_coll_barrier(const Team *team, uint32_t channel, uint32_t epoch, void *stream)
+{
+    if (team == nullptr || channel >= 64) return -1;
+    dim3 grid(1, team->emu ? team->world : 1);
+    if (team->emu) {
+        void *params[] = {const_cast<Team *>(team), &channel, &epoch};
+        cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(k_barrier), grid, dim3(32), params, 0, (cudaStream_t)stream);
+        return e == cudaSuccess ? 0 : (int)e;
+    }
+    k_barrier<<<grid, 32, 0, (cudaStream_t)stream>>>(*team, channel, epoch);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int mf_coll_wait_flag(const Team *team, uint64_t flag_off, uint32_t epoch, void *stream)
+{
+    if (team == nullptr) return -1;
+    k_wait_flag<<<1, 32, 0, (cudaStream_t)stream>>>(*team, flag_off, epoch);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+unsigned mf_coll_signal_bytes(void) { return kSignalBytes; }
+unsigned mf_coll_max_ctas(void) { return kMaxCtas; }
+unsigned mf_coll_args_size(void) { return (unsigned)sizeof(CollArgs); }
+
+}  // extern "C"

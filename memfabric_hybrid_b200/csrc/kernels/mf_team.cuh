@@ -1,0 +1,140 @@
+// Device-side view of the symmetric heap and the cross-GPU signalling primitives every multi-GPU
+// kernel here is built from.
+//
+// Addressing: each rank owns one slot of `stride` bytes in a range mapped at the same address by all
+// ranks; an object at offset `off` of rank r lives at heap_base + r * stride + off. One multiply-add,
+// no table (the rule the reference's kernels use: zbal_kernel_base.h:35-42).
+//
+// Signals: 32-bit epoch-numbered flags written with st.release.sys into the peer's slot and polled with
+// ld.acquire.sys. Every wait is bounded: when the budget runs out the waiter records where it gave up
+// in the status words of its own slot and the kernel returns normally (no trap, no endless spin), so a
+// peer that never arrives costs a time-out, not a hung GPU. Epochs only grow, so a flag left over from
+// an earlier call can never satisfy a later wait (the reference's `waitSymbol`,
+// zbal_comm_host_device_struct.h:235).
+//
+// Emulation: with team.emu != 0 the rank is taken from blockIdx.y, so ONE cooperative launch runs all
+// ranks of a protocol on one GPU (ranks must never be separate launches on one device: nothing would
+// guarantee they run at the same time).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mfk {
+
+constexpr int kMaxRanks = 16;           // NVSwitch domain of one box (8) with head-room
+constexpr int kMaxCtas = 256;           // CTAs of one collective launch that own private flag lanes
+constexpr uint32_t kSignalBytes = 1u << 20;  // signal area at the start of every slot
+
+// Layout of the signal area (all offsets relative to the slot start):
+//   [0, 64)                      status words: [0] error code, [1] where, [2] epoch, [3] count
+//   [4 KiB, 4 KiB + 64 KiB)      barrier flags   [channel 0..63][rank 0..15] x u32 (padded to 256 B rows)
+//   [128 KiB, ...)               lane flags      [phase 0..3][cta 0..255][rank 0..15] x u32
+constexpr uint32_t kStatusOff = 0;
+constexpr uint32_t kBarrierOff = 4096;
+constexpr uint32_t kLaneOff = 128 * 1024;
+constexpr int kPhases = 4;
+
+enum MfStatus : uint32_t { ST_OK = 0, ST_TIMEOUT = 1, ST_BAD_ARG = 2 };
+
+struct Team {
+    uint64_t heap_base;   // address of rank 0's slot
+    uint64_t stride;      // bytes between consecutive ranks' slots
+    uint64_t mc_base;     // multicast alias of the heap (0 when NVLS is not bound)
+    uint32_t rank;
+    uint32_t world;
+    uint32_t emu;         // 1: rank = blockIdx.y (single-GPU emulation of all ranks)
+    uint32_t spin_limit;  // polls before a wait gives up
+};
+
+__device__ __forceinline__ uint32_t team_rank(const Team &t) { return t.emu ? blockIdx.y : t.rank; }
+
+__device__ __forceinline__ uint8_t *peer_ptr(const Team &t, uint32_t r, uint64_t off)
+{
+    return reinterpret_cast<uint8_t *>(t.heap_base + (uint64_t)r * t.stride + off);
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void report_timeout(const Team &t, uint32_t me, uint32_t where, uint32_t epoch)
+{
+    uint32_t *st = reinterpret_cast<uint32_t *>(peer_ptr(t, me, kStatusOff));
+    if (atomicCAS(st, ST_OK, ST_TIMEOUT) == ST_OK) {
+        st[1] = where;
+        st[2] = epoch;
+    }
+    atomicAdd(st + 3, 1u);
+}
+
+// Polls until *flag >= epoch (wrap-safe). Returns false when the budget ran out.
+__device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t epoch, uint32_t limit)
+{
+    for (uint32_t i = 0; i < limit; i++) {
+        if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
+        if (i > 64) __nanosleep(i > 4096 ? 256 : 32);
+    }
+    return false;
+}
+
+// CTA-lane handshake: CTA b of every rank tells CTA b of every other rank that its stores of `phase`
+// are visible, then waits for the same from all of them. All threads of the CTA must call it.
+// Returns false on time-out (uniform across the CTA).
+__device__ __forceinline__ bool lane_sync(const Team &t, uint32_t me, int phase, uint32_t epoch, uint32_t where)
+{
+    __shared__ int ok_sh;
+    __threadfence_system();  // this thread's earlier stores (possibly to peers) before the flag
+    __syncthreads();
+    const uint32_t lane = blockIdx.x;
+    const uint64_t off = kLaneOff + (((uint64_t)phase * kMaxCtas + lane) * kMaxRanks) * sizeof(uint32_t);
+    if (threadIdx.x == 0) ok_sh = 1;
+    __syncthreads();
+    if (threadIdx.x < t.world) {
+        const uint32_t r = threadIdx.x;
+        st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, off)) + me, epoch);
+        const uint32_t *mine = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, off)) + r;
+        if (!wait_flag(mine, epoch, t.spin_limit)) {
+            ok_sh = 0;
+            report_timeout(t, me, where, epoch);
+        }
+    }
+    __syncthreads();
+    return ok_sh != 0;
+}
+
+// Whole-rank barrier on a numbered channel; call from ONE CTA (all its threads).
+__device__ __forceinline__ bool team_barrier(const Team &t, uint32_t me, uint32_t channel, uint32_t epoch)
+{
+    __shared__ int ok_sh;
+    __threadfence_system();
+    __syncthreads();
+    const uint64_t off = kBarrierOff + (uint64_t)channel * 256;
+    if (threadIdx.x == 0) ok_sh = 1;
+    __syncthreads();
+    if (threadIdx.x < t.world) {
+        const uint32_t r = threadIdx.x;
+        st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, off)) + me, epoch);
+        const uint32_t *mine = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, off)) + r;
+        if (!wait_flag(mine, epoch, t.spin_limit)) {
+            ok_sh = 0;
+            report_timeout(t, me, 0x1000 | channel, epoch);
+        }
+    }
+    __syncthreads();
+    return ok_sh != 0;
+}
+
+}  // namespace mfk

@@ -1,0 +1,177 @@
+"""Collective kernels against a plain PyTorch fp32 reference.
+
+Single-GPU tests emulate all ranks in ONE cooperative launch (rank = blockIdx.y); the multi-GPU test runs
+real ranks as child processes over NVLink peer mappings."""
+import pytest
+import torch
+
+from conftest import free_port
+from mp_util import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _tol(dtype):
+    return dict(rtol=2e-2, atol=2e-2) if dtype in (torch.bfloat16, torch.float16) else dict(rtol=1e-5, atol=1e-5)
+
+
+@pytest.fixture(scope="module")
+def comms():
+    from memfabric_hybrid_b200.ops.heap import EmulatedHeap
+    from memfabric_hybrid_b200.ops.collectives import Communicator
+    out = {}
+    for w in (2, 4, 8):
+        heap = EmulatedHeap(w, (1 << 20) + 4 * (2 << 20) + (1 << 20))
+        out[w] = Communicator(heap, stage_bytes=2 << 20)
+    yield out
+    for c in out.values():
+        torch.cuda.synchronize()
+        assert c.heap.status()[0] == 0, f"a device wait gave up: {c.heap.status()}"
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("n", [8, 1000, 4096 + 24, 300_000, 1_500_000])
+def test_all_reduce(comms, world, dtype, n):
+    c = comms[world]
+    torch.manual_seed(n + world)
+    x = torch.randn(world, n, device="cuda", dtype=torch.float32).to(dtype)
+    ref = x.float().sum(0) / world
+    for algo in ("oneshot", "twoshot", None):
+        if algo == "oneshot" and n * x.element_size() > c.stage_bytes:
+            continue
+        out = c.all_reduce(x, scale=1.0 / world, algo=algo)
+        torch.cuda.synchronize()
+        assert out.shape == (world, n)
+        for r in range(world):
+            torch.testing.assert_close(out[r].float(), ref, **_tol(dtype))
+        assert torch.equal(out[0], out[world - 1]), "ranks must hold bit-identical results"
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_all_reduce_fused_cast_and_ops(comms, world):
+    c = comms[world]
+    x = torch.randn(world, 70_000, device="cuda")
+    out = c.all_reduce(x, scale=1.0 / world, out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    assert out.dtype == torch.bfloat16
+    torch.testing.assert_close(out[1].float(), (x.sum(0) / world), rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(c.all_reduce(x, op="max")[0], x.max(0).values)
+    torch.testing.assert_close(c.all_reduce(x, op="min")[0], x.min(0).values)
+    xi = torch.randint(-1000, 1000, (world, 5000), device="cuda", dtype=torch.int32)
+    assert torch.equal(c.all_reduce(xi)[0], xi.sum(0).to(torch.int32))
+    assert torch.equal(c.all_reduce(xi, op="max", algo="twoshot")[world - 1], xi.max(0).values)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m", [8, 1024, 50_000, 400_000])
+def test_reduce_scatter_all_gather(comms, world, dtype, m):
+    c = comms[world]
+    x = torch.randn(world, world * m, device="cuda").to(dtype)
+    rs = c.reduce_scatter(x, scale=1.0 / world)
+    torch.cuda.synchronize()
+    ref = x.float().sum(0).view(world, m) / world
+    for r in range(world):
+        torch.testing.assert_close(rs[r].float(), ref[r], **_tol(dtype))
+    shard = torch.randn(world, m, device="cuda").to(dtype)
+    ag = c.all_gather(shard)
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert torch.equal(ag[r].view(world, m), shard), f"rank {r}"
+    if dtype == torch.float32:
+        agc = c.all_gather(shard, out_dtype=torch.bfloat16)
+        assert torch.equal(agc[0].view(world, m), shard.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_broadcast_scatter_alltoallv(comms, world):
+    c = comms[world]
+    x = torch.randn(world, 100_003, device="cuda")
+    ref = x[world - 1].clone()
+    c.broadcast(x, root=world - 1)
+    torch.cuda.synchronize()
+    for r in range(world):
+        assert torch.equal(x[r], ref)
+    # all-to-all-v with uneven counts: rank s sends (s + d + 1) * 16 elements to rank d
+    cnt = [[(s + d + 1) * 16 + 3 for d in range(world)] for s in range(world)]
+    soff = [[sum(cnt[s][:d]) for d in range(world)] for s in range(world)]
+    rcnt = [[cnt[s][d] for s in range(world)] for d in range(world)]
+    roff = [[sum(rcnt[d][:s]) for s in range(world)] for d in range(world)]
+    nsend = max(sum(r) for r in cnt)
+    nrecv = max(sum(r) for r in rcnt)
+    xs = torch.randn(world, nsend, device="cuda").to(torch.bfloat16)
+    out = torch.zeros(world, nrecv, device="cuda", dtype=torch.bfloat16)
+    c.all_to_all_v(xs, out, cnt, soff, rcnt, roff)
+    torch.cuda.synchronize()
+    for d in range(world):
+        for s in range(world):
+            got = out[d, roff[d][s]:roff[d][s] + rcnt[d][s]]
+            want = xs[s, soff[s][d]:soff[s][d] + cnt[s][d]]
+            assert torch.equal(got, want), f"{s}->{d}"
+
+
+def test_barrier_and_bounded_wait():
+    """A wait that nothing satisfies ends with a status word, not a hang, and the context stays usable."""
+    from memfabric_hybrid_b200.ops.heap import EmulatedHeap
+    from memfabric_hybrid_b200.ops.collectives import Communicator
+    heap = EmulatedHeap(4, 8 << 20)
+    heap.spin_limit = 20_000  # a few milliseconds
+    c = Communicator(heap, stage_bytes=1 << 20)
+    c.barrier()
+    c.barrier(channel=3)
+    torch.cuda.synchronize()
+    assert heap.status()[0] == 0
+    flag = heap.alloc(64)
+    c.wait_flag_probe(flag, epoch=7)  # nobody ever writes this flag
+    torch.cuda.synchronize()
+    code, where, epoch, count = heap.status()
+    assert code == 1 and where == 0x1ff and epoch == 7 and count == 1
+    heap.clear_status()
+    x = torch.ones(4, 64, device="cuda")
+    assert torch.equal(c.all_reduce(x)[0], torch.full((64,), 4.0, device="cuda"))  # still healthy
+
+
+def _real_ranks(rank, world, url, sync):
+    import torch
+    from memfabric_hybrid_b200.ops.heap import SymmetricHeap
+    from memfabric_hybrid_b200.ops.collectives import Communicator
+    heap = SymmetricHeap(url, world, rank, rank % torch.cuda.device_count(), 64 << 20)
+    c = Communicator(heap, stage_bytes=8 << 20)
+    g = torch.Generator("cuda").manual_seed(rank)
+    for n in (64, 10_000, 3_000_000):
+        x = torch.randn(n, device="cuda", generator=g).to(torch.bfloat16)
+        out = c.all_reduce(x, scale=1.0 / world)
+        ref = sum(torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(r)).to(torch.bfloat16).float()
+                  for r in range(world)) / world
+        torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    x = torch.full((world * 1024,), float(rank + 1), device="cuda")
+    rs = c.reduce_scatter(x)
+    assert torch.equal(rs, torch.full((1024,), float(sum(range(1, world + 1))), device="cuda"))
+    ag = c.all_gather(torch.full((512,), float(rank), device="cuda"))
+    assert torch.equal(ag.view(world, 512)[:, 0].cpu(), torch.arange(world, dtype=torch.float32))
+    # ring send/recv
+    msg = torch.full((100_000,), float(rank), device="cuda")
+    got = torch.empty_like(msg)
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    if rank % 2 == 0:
+        c.send(msg, nxt)
+        c.recv(got, prv)
+    else:
+        c.recv(got, prv)
+        c.send(msg, nxt)
+    torch.cuda.synchronize()
+    assert torch.equal(got, torch.full_like(got, float(prv)))
+    c.barrier()
+    torch.cuda.synchronize()
+    st = heap.status()
+    heap.close()
+    SymmetricHeap.shutdown()
+    return st[0]
+
+
+@pytest.mark.multigpu
+def test_real_ranks_over_nvlink():
+    n = min(torch.cuda.device_count(), 4)
+    url = f"127.0.0.1:{free_port()}"
+    assert run_ranks(_real_ranks, n, (url,), timeout=300, with_barrier=True) == [0] * n
