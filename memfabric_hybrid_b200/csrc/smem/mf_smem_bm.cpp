@@ -10,7 +10,9 @@ using namespace mf::smem;
 namespace {
 std::mutex g_mu;
 BmGlobals g_bm;
-HandleTable<BmEntry> g_handles;
+// leaked on purpose: tearing pools down from static destructors would call into a CUDA driver that
+// is already shutting down
+HandleTable<BmEntry> &g_handles = *new HandleTable<BmEntry>();
 constexpr uint32_t kInitTries = 5;
 
 BmEntryPtr H(smem_bm_t h)

@@ -138,7 +138,9 @@ public:
 
 std::mutex g_mu;
 ShmGlobals g_shm;
-HandleTable<ShmEntry> g_handles;
+// leaked on purpose: tearing pools down from static destructors would call into a CUDA driver that
+// is already shutting down
+HandleTable<ShmEntry> &g_handles = *new HandleTable<ShmEntry>();
 
 std::shared_ptr<ShmEntry> H(smem_shm_t h)
 {

@@ -332,7 +332,9 @@ private:
     std::atomic<bool> closed_{false};
 };
 
-HandleTable<TransEntry> g_handles;
+// leaked on purpose: tearing pools down from static destructors would call into a CUDA driver that
+// is already shutting down
+HandleTable<TransEntry> &g_handles = *new HandleTable<TransEntry>();
 
 std::shared_ptr<TransEntry> H(smem_trans_t h)
 {

@@ -1,0 +1,63 @@
+"""tcgen05 / TMEM GEMMs (csrc/kernels/mf_gemm.cu, mf_gemm_fp8.cu).
+
+    gemm_bf16(a, b)                  C[M,N] = A[M,K] . B[N,K]^T   (bf16 in, fp32 accumulate in TMEM, bf16 out)
+
+The status word is a device int that a kernel sets when one of its bounded pipeline waits gives up;
+``check_status`` turns that into an exception."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from .. import _native as N
+
+_lib = None
+_status = {}
+
+
+def _cu():
+    global _lib
+    if _lib is None:
+        l = N.cuda()
+        l.mf_gemm_bf16.restype = C.c_int
+        l.mf_gemm_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64,
+                                   C.c_void_p, C.c_int, C.c_void_p]
+        _lib = l
+    return _lib
+
+
+def status_word(device=None) -> torch.Tensor:
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    t = _status.get(dev)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=dev)
+        _status[dev] = t
+    return t
+
+
+def check_status(device=None) -> None:
+    st = status_word(device)
+    v = int(st.item())
+    if v != 0:
+        st.zero_()
+        raise RuntimeError(f"a GEMM pipeline wait gave up (code {v:#x})")
+
+
+def sm_count(device=None) -> int:
+    return torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device()).multi_processor_count
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, sms: int | None = None) -> torch.Tensor:
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_cuda and b.is_cuda
+    assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1], "A[M,K] and B[N,K] must share K"
+    assert a.stride(1) == 1 and b.stride(1) == 1, "K must be the contiguous dimension"
+    M, K = a.shape
+    Nn = b.shape[0]
+    if out is None:
+        out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a.device)
+    rc = _cu().mf_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, Nn, K, a.stride(0), b.stride(0), out.stride(0),
+                            status_word(a.device).data_ptr(), sms or sm_count(a.device), torch.cuda.current_stream().cuda_stream)
+    if rc != 0:
+        raise RuntimeError(f"mf_gemm_bf16 failed to launch ({rc})")
+    return out

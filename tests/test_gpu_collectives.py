@@ -138,12 +138,13 @@ def _real_ranks(rank, world, url, sync):
     from memfabric_hybrid_b200.ops.collectives import Communicator
     heap = SymmetricHeap(url, world, rank, rank % torch.cuda.device_count(), 64 << 20)
     c = Communicator(heap, stage_bytes=8 << 20)
-    g = torch.Generator("cuda").manual_seed(rank)
+    def draw(r, n):
+        return torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(1000 * r + n % 997)).to(torch.bfloat16)
+
     for n in (64, 10_000, 3_000_000):
-        x = torch.randn(n, device="cuda", generator=g).to(torch.bfloat16)
+        x = draw(rank, n)
         out = c.all_reduce(x, scale=1.0 / world)
-        ref = sum(torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(r)).to(torch.bfloat16).float()
-                  for r in range(world)) / world
+        ref = sum(draw(r, n).float() for r in range(world)) / world
         torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
     x = torch.full((world * 1024,), float(rank + 1), device="cuda")
     rs = c.reduce_scatter(x)
