@@ -2,14 +2,19 @@
 // Persistent kernel, one CTA per SM, 128 x 256 tiles, 4-stage TMA ring, two TMEM accumulators so that
 // the epilogue of tile i overlaps the main loop of tile i+1.
 //
-// The same kernel carries the two tensor-parallel fusions:
-//   all-gather -> GEMM : the A operand is a gather buffer in THIS GPU's memory that peers' copy warps
-//                        fill shard by shard; the producer warp waits on a per-shard ready flag before
-//                        the first TMA load of a tile whose rows belong to that shard (no TMA load ever
-//                        touches a peer's memory)
-//   GEMM -> reduce-scatter : the epilogue sends each finished 128-row x 256-col block of partial sums to
-//                        the rank that owns those rows (plain peer stores into its landing zone), and the
-//                        owner adds the W partial blocks in a fixed order
+// The same kernel carries the two tensor-parallel fusions (template parameter MODE):
+//   MODE 1, all-gather -> GEMM : the A operand is a gather buffer in THIS GPU's slot of the symmetric
+//       heap. Four extra "copy" warps per CTA push this rank's activation shard into every peer's
+//       gather buffer with plain stores over NVLink and raise a per-shard ready flag there; the TMA
+//       producer waits on the flag of the shard a tile's rows belong to before its first load, and
+//       tiles are visited in the order in which shards arrive. No TMA load ever touches a peer's
+//       memory, and none uses cluster multicast.
+//   MODE 2, GEMM -> reduce-scatter : the epilogue sends each finished tile of partial sums to the rank
+//       that owns those rows (peer stores into its landing zone) and bumps a per-tile arrival counter
+//       there; when a CTA runs out of GEMM tiles it adds the W partial tiles of owned rows in a fixed
+//       order, applies the scale and writes the output shard.
+// EPI 1 fuses SwiGLU: B holds, per 256-row tile, 128 gate rows followed by their 128 up rows, and the
+// epilogue writes silu(gate) * up (128 columns per tile).
 #include <cuda_bf16.h>
 
 #include "mf_gemm.cuh"
@@ -55,19 +60,55 @@ struct GemmArgs {
     int64_t ldc;
     int M, N, K;
     int *status;
-    // all-gather fusion (0 = off): rows [r * shard_rows, (r + 1) * shard_rows) of A become valid when
-    // ready[r] >= epoch (flags in this GPU's memory, written by the gather kernel)
-    const uint32_t *ready;
-    uint32_t ready_epoch;
-    int shard_rows;
-    uint32_t spin_limit;
-    // reduce-scatter fusion (0 = off): partial tiles are pushed to the owner of their rows
     Team team;
-    uint64_t rs_land_off;   // slot offset of the landing zone [world][rows_per_rank][N] bf16... (see mf_tp.cu)
-    int rs_rows_per_rank;
+    uint32_t epoch;          // flag value of this call (grows by one per call)
+    uint32_t seq;            // number of fused calls so far including this one (targets of the counters)
+    // MODE 1
+    const __nv_bfloat16 *x_local;  // this rank's shard [shard_rows, K]
+    int64_t ldx;
+    int shard_rows;
+    uint64_t ag_buf_off;     // slot offset of the gather buffer [W * shard_rows, K]
+    uint64_t ag_ready_off;   // slot offset of W ready flags (u32)
+    uint32_t *push_count;    // local device counters [W], monotonic
+    // MODE 2
+    uint64_t rs_land_off;    // slot offset of the landing zone [W][rows_per_rank][N] bf16
+    uint64_t rs_count_off;   // slot offset of per-owned-tile arrival counters (u32), monotonic
+    int rows_per_rank;
+    __nv_bfloat16 *y_out;    // [rows_per_rank, N]
+    int64_t ldy;
+    float scale;
 };
 
-template <int BN, int STAGES> __global__ void __launch_bounds__(kGemmThreads, 1) k_gemm_bf16(const __grid_constant__ GemmArgs g)
+constexpr int kCopyWarps = 4;
+
+// Maps the t-th tile of this CTA's walk to (row tile, column tile).
+template <int MODE, int BN> __device__ __forceinline__ void tile_mn(const GemmArgs &g, int t, int m_tiles, int n_tiles, int &mt, int &nt)
+{
+    if (MODE == 0) {
+        // bands of 8 row tiles; inside a band the column varies slowest so that CTAs running together share B tiles
+        const int band = 8;
+        const int per_band = band * n_tiles;
+        const int b = t / per_band;
+        const int rows_in_band = min(band, m_tiles - b * band);
+        const int r = t - b * per_band;
+        nt = r / rows_in_band;
+        mt = b * band + r % rows_in_band;
+    } else {
+        // blocks of rows owned by one rank, visited starting with this rank (MODE 1: the order in which shards
+        // arrive) or with the next rank (MODE 2: remote owners first, own rows last)
+        const int rows = MODE == 1 ? g.shard_rows : g.rows_per_rank;
+        const int mt_per = rows / BM;
+        const int per_block = mt_per * n_tiles;
+        const int i = t / per_block;
+        const int owner = (int)((g.team.rank + (MODE == 2 ? 1 : 0) + i) % g.team.world);
+        const int r = t - i * per_block;
+        nt = r / mt_per;
+        mt = owner * mt_per + r % mt_per;
+    }
+}
+
+template <int MODE, int EPI, int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 0), 1) k_gemm_bf16(const __grid_constant__ GemmArgs g)
 {
     extern __shared__ uint8_t smem_raw[];
     GemmSmem<BN, STAGES> sm(smem_raw);
@@ -77,6 +118,7 @@ template <int BN, int STAGES> __global__ void __launch_bounds__(kGemmThreads, 1)
     const int n_tiles = (g.N + BN - 1) / BN;
     const int total = m_tiles * n_tiles;
     const int k_iters = (g.K * 2 + KSPAN - 1) / KSPAN;
+    const uint32_t me = g.team.rank;
     AbortCtl ac{sm.abort_flag(), g.status};
 
     if (threadIdx.x == 0) {
@@ -102,38 +144,25 @@ template <int BN, int STAGES> __global__ void __launch_bounds__(kGemmThreads, 1)
     tc_fence_after();
     const uint32_t tmem_base = *sm.tmem_slot();
 
-    // tile order: bands of 8 row-tiles, columns inside a band vary slowest, so CTAs running together share B tiles
-    auto tile_mn = [&](int t, int &mt, int &nt) {
-        const int band = 8;
-        const int per_band = band * n_tiles;
-        const int b = t / per_band;
-        const int rows_in_band = min(band, m_tiles - b * band);
-        const int r = t - b * per_band;
-        nt = r / rows_in_band;
-        mt = b * band + r % rows_in_band;
-    };
-
     if (warp == 0) {
         if (elect_one()) {
             PipeState ps;
             for (int t = blockIdx.x; t < total; t += gridDim.x) {
                 int mt, nt;
-                tile_mn(t, mt, nt);
-                if (g.ready != nullptr) {
-                    // every shard that this tile's rows touch must have landed in local memory
-                    const int r0 = mt * BM / g.shard_rows, r1 = min(g.M - 1, mt * BM + BM - 1) / g.shard_rows;
-                    bool ok = true;
-                    for (int r = r0; r <= r1 && ok; r++) ok = wait_flag(g.ready + r, g.ready_epoch, g.spin_limit);
-                    if (!ok) {
+                tile_mn<MODE, BN>(g, t, m_tiles, n_tiles, mt, nt);
+                if (MODE == 1) {
+                    // the shard holding this tile's rows must have landed in this GPU's gather buffer
+                    const int r = mt * BM / g.shard_rows;
+                    const uint32_t *ready = reinterpret_cast<const uint32_t *>(peer_ptr(g.team, me, g.ag_ready_off)) + r;
+                    if (!wait_flag(ready, g.epoch, g.team.spin_limit)) {
                         *ac.abort_smem = 1;
                         atomicCAS(g.status, 0, 0x301);
                         break;
                     }
-                    fence_proxy_async_smem();
-                    asm volatile("fence.proxy.async.global;" ::: "memory");  // generic-proxy stores -> TMA reads
+                    asm volatile("fence.proxy.async.global;" ::: "memory");  // peers' generic-proxy stores before our TMA reads
                 }
                 bool fine = true;
-                for (int kb = 0; kb < k_iters && fine; kb++) {
+                for (int kb = 0; kb < k_iters; kb++) {
                     fine = mbar_wait(sm.empty(ps.stage), ps.phase ^ 1, ac, 0x302);
                     if (!fine) break;
                     mbar_expect_tx(sm.full(ps.stage), GemmSmem<BN, STAGES>::kStageBytes);
@@ -174,48 +203,124 @@ template <int BN, int STAGES> __global__ void __launch_bounds__(kGemmThreads, 1)
                 if (acc == 0) acc_phase ^= 1;
             }
         }
-    } else {
+    } else if (warp < 6) {
         const int quad = warp & 3;  // TMEM lane quadrant this warp may read
         int acc = 0;
         uint32_t acc_phase = 0;
         for (int t = blockIdx.x; t < total; t += gridDim.x) {
             int mt, nt;
-            tile_mn(t, mt, nt);
+            tile_mn<MODE, BN>(g, t, m_tiles, n_tiles, mt, nt);
             // the whole warp must take the same branch: the TMEM loads below are warp-collective
             if (!__all_sync(0xffffffffu, mbar_wait(sm.tfull(acc), acc_phase, ac, 0x305))) break;
             tc_fence_after();
             const int row = mt * BM + quad * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+            if (EPI == 1) {
+                // columns [0,128) of the tile are gate, [128,256) the matching up projections
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
-                uint32_t v[32];
-                tmem_ld32(taddr + (uint32_t)(c * 32), v);
-                tmem_ld_wait();
-                const int col = nt * BN + c * 32;
-                if (row < g.M && col < g.N) {
-                    __nv_bfloat16 *dst = g.C + (int64_t)row * g.ldc + col;
-                    if (col + 32 <= g.N && ((g.ldc & 7) == 0)) {
+                for (int c = 0; c < BN / 64; c++) {
+                    uint32_t gt[32], up[32];
+                    tmem_ld32(taddr + (uint32_t)(c * 32), gt);
+                    tmem_ld32(taddr + (uint32_t)(BN / 2 + c * 32), up);
+                    tmem_ld_wait();
+                    const int col = nt * (BN / 2) + c * 32;
+                    if (row < g.M && col < g.N / 2) {
+                        __nv_bfloat16 *dst = g.C + (int64_t)row * g.ldc + col;
 #pragma unroll
                         for (int q = 0; q < 4; q++) {
                             uint4 pk;
                             __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
 #pragma unroll
-                            for (int e = 0; e < 4; e++)
-                                h[e] = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 2 * e]), __uint_as_float(v[q * 8 + 2 * e + 1]));
+                            for (int e = 0; e < 4; e++) {
+                                const float g0 = __uint_as_float(gt[q * 8 + 2 * e]), g1 = __uint_as_float(gt[q * 8 + 2 * e + 1]);
+                                const float u0 = __uint_as_float(up[q * 8 + 2 * e]), u1 = __uint_as_float(up[q * 8 + 2 * e + 1]);
+                                h[e] = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+                            }
                             *reinterpret_cast<uint4 *>(dst + q * 8) = pk;
                         }
-                    } else {
+                    }
+                }
+            } else {
+                __nv_bfloat16 *dst_row;
+                if (MODE == 2) {
+                    const int owner = mt * BM / g.rows_per_rank;
+                    const int lrow = row - owner * g.rows_per_rank;
+                    dst_row = reinterpret_cast<__nv_bfloat16 *>(peer_ptr(g.team, owner, g.rs_land_off)) +
+                              ((int64_t)me * g.rows_per_rank + lrow) * g.N;
+                } else {
+                    dst_row = g.C + (int64_t)row * g.ldc;
+                }
+                const bool vec_ok = MODE == 2 ? (g.N & 7) == 0 : (g.ldc & 7) == 0;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; c++) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + (uint32_t)(c * 32), v);
+                    tmem_ld_wait();
+                    const int col = nt * BN + c * 32;
+                    if (row < g.M && col < g.N) {
+                        __nv_bfloat16 *dst = dst_row + col;
+                        if (col + 32 <= g.N && vec_ok) {
 #pragma unroll
-                        for (int e = 0; e < 32; e++)
-                            if (col + e < g.N) dst[e] = __float2bfloat16_rn(__uint_as_float(v[e]));
+                            for (int q = 0; q < 4; q++) {
+                                uint4 pk;
+                                __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+                                for (int e = 0; e < 4; e++)
+                                    h[e] = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 2 * e]), __uint_as_float(v[q * 8 + 2 * e + 1]));
+                                *reinterpret_cast<uint4 *>(dst + q * 8) = pk;
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 32; e++)
+                                if (col + e < g.N) dst[e] = __float2bfloat16_rn(__uint_as_float(v[e]));
+                        }
                     }
                 }
             }
             tc_fence_before();
+            if (MODE == 2) {
+                // all four epilogue warps have stored their rows of the tile: tell the owner
+                __threadfence_system();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    const int owner = mt * BM / g.rows_per_rank;
+                    const int ltile = (mt - owner * (g.rows_per_rank / BM)) * n_tiles + nt;
+                    uint32_t *cnt = reinterpret_cast<uint32_t *>(peer_ptr(g.team, owner, g.rs_count_off)) + ltile;
+                    asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+                }
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(sm.tempty(acc));
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
+        }
+    } else if (MODE == 1) {
+        // copy warps: push rows [b*per, (b+1)*per) of the local shard to every rank's gather buffer, nearest
+        // consumer first (own buffer, then rank me-1 which needs our shard second, ...)
+        const int ct = threadIdx.x - kGemmThreads;  // 0..127
+        const int per = (g.shard_rows + gridDim.x - 1) / gridDim.x;
+        const int r0 = min(g.shard_rows, (int)blockIdx.x * per), r1 = min(g.shard_rows, r0 + per);
+        const int vec_per_row = g.K / 8;  // 16-byte vectors per row
+        for (uint32_t i = 0; i < g.team.world; i++) {
+            const uint32_t p = (me + g.team.world - i) % g.team.world;
+            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(peer_ptr(g.team, p, g.ag_buf_off)) + (int64_t)me * g.shard_rows * g.K;
+            const int64_t nvec = (int64_t)(r1 - r0) * vec_per_row;
+            for (int64_t v = ct; v < nvec; v += kCopyWarps * 32) {
+                const int rr = r0 + (int)(v / vec_per_row);
+                const int cc = (int)(v % vec_per_row) * 8;
+                const uint4 val = __ldg(reinterpret_cast<const uint4 *>(g.x_local + (int64_t)rr * g.ldx + cc));
+                *reinterpret_cast<uint4 *>(dst + (int64_t)rr * g.K + cc) = val;
+            }
+            __threadfence_system();
+            asm volatile("bar.sync 2, 128;" ::: "memory");
+            if (ct == 0) {
+                // the CTA that completes the shard for peer p raises the flag there
+                const uint32_t done = atomicAdd(g.push_count + p, 1u) + 1;
+                if (done == gridDim.x * g.seq) {
+                    __threadfence_system();
+                    st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(g.team, p, g.ag_ready_off)) + me, g.epoch);
+                }
+            }
         }
     }
     tc_fence_before();
@@ -224,43 +329,152 @@ template <int BN, int STAGES> __global__ void __launch_bounds__(kGemmThreads, 1)
         tc_fence_after();
         tmem_dealloc(tmem_base, 2 * BN);
     }
+    if (MODE == 2) {
+        // reduce the W partial tiles of every tile whose rows this rank owns
+        __shared__ int ok_sh;
+        const int own_tiles = (g.rows_per_rank / BM) * n_tiles;
+        const uint32_t *cnt = reinterpret_cast<const uint32_t *>(peer_ptr(g.team, me, g.rs_count_off));
+        const __nv_bfloat16 *land = reinterpret_cast<const __nv_bfloat16 *>(peer_ptr(g.team, me, g.rs_land_off));
+        for (int t = blockIdx.x; t < own_tiles; t += gridDim.x) {
+            if (threadIdx.x == 0) {
+                ok_sh = (!*ac.abort_smem && wait_flag(cnt + t, g.team.world * g.seq, g.team.spin_limit)) ? 1 : 0;
+                if (!ok_sh) atomicCAS(g.status, 0, 0x306);
+            }
+            __syncthreads();
+            if (!ok_sh) break;
+            const int ml = t / n_tiles, nt = t % n_tiles;
+            const int cols = min(BN, g.N - nt * BN);
+            const int vecs = BM * (cols / 8);
+            for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+                const int lr = ml * BM + v / (cols / 8);
+                const int col = nt * BN + (v % (cols / 8)) * 8;
+                float accv[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) accv[e] = 0.f;
+                for (uint32_t s = 0; s < g.team.world; s++) {
+                    const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(land + ((int64_t)s * g.rows_per_rank + lr) * g.N + col));
+                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float2 f = __bfloat1622float2(h[e]);
+                        accv[2 * e] += f.x;
+                        accv[2 * e + 1] += f.y;
+                    }
+                }
+                uint4 pk;
+                __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+                for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(accv[2 * e] * g.scale, accv[2 * e + 1] * g.scale);
+                *reinterpret_cast<uint4 *>(g.y_out + (int64_t)lr * g.ldy + col) = pk;
+            }
+            __syncthreads();
+        }
+    }
 }
 
 }  // namespace mfk
 
 using namespace mfk;
 
-extern "C" {
+namespace {
+constexpr int kBN = 256, kStages = 4;
 
-// C[M,N] (bf16, row stride ldc) = A[M,K] . B[N,K]^T, all bf16 row-major with K contiguous.
-// status: device int, must be zero on entry; non-zero afterwards means a pipeline wait gave up.
-int mf_gemm_bf16(const void *A, const void *B, void *C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int *status,
-                 int sms, void *stream)
+template <int MODE, int EPI> int launch_gemm(const GemmArgs &g, int grid, cudaStream_t s)
+{
+    auto kern = k_gemm_bf16<MODE, EPI, kBN, kStages>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<kBN, kStages>::kDynBytes) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return -2;
+        }
+        attr_set = true;
+    }
+    const int threads = kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 0);
+    kern<<<grid, threads, GemmSmem<kBN, kStages>::kDynBytes, s>>>(g);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int fill_common(GemmArgs &g, const void *A, const void *B, int M, int N, int K, int64_t lda, int64_t ldb, int *status)
 {
     if (M <= 0 || N <= 0 || K <= 0 || (K & 7) != 0) return -1;
-    constexpr int BN = 256, STAGES = 4;
-    GemmArgs g{};
     int rc = make_tmap_2d(&g.tm.a, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, false);
-    if (rc == 0) rc = make_tmap_2d(&g.tm.b, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, BN, false);
-    if (rc != 0) return rc;
-    g.C = static_cast<__nv_bfloat16 *>(C);
-    g.ldc = ldc;
+    if (rc == 0) rc = make_tmap_2d(&g.tm.b, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, kBN, false);
     g.M = M;
     g.N = N;
     g.K = K;
     g.status = status;
-    g.ready = nullptr;
-    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    return rc;
+}
+}  // namespace
+
+extern "C" {
+
+// C = A[M,K] . B[N,K]^T (bf16, K contiguous). swiglu != 0: B is tile-interleaved (128 gate rows, 128 up rows per
+// 256) and C is [M, N/2] = silu(gate) * up. status: device int, zero on entry; non-zero = a pipeline wait gave up.
+int mf_gemm_bf16(const void *A, const void *B, void *C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int *status,
+                 int sms, int swiglu, void *stream)
+{
+    GemmArgs g{};
+    int rc = fill_common(g, A, B, M, N, K, lda, ldb, status);
+    if (rc != 0) return rc;
+    if (swiglu && (N % kBN) != 0) return -3;
+    g.C = static_cast<__nv_bfloat16 *>(C);
+    g.ldc = ldc;
+    const int tiles = ((M + BM - 1) / BM) * ((N + kBN - 1) / kBN);
     const int grid = tiles < sms ? tiles : sms;
-    auto kern = k_gemm_bf16<BN, STAGES>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<BN, STAGES>::kDynBytes) != cudaSuccess) return -2;
-        attr_set = true;
-    }
-    kern<<<grid, kGemmThreads, GemmSmem<BN, STAGES>::kDynBytes, (cudaStream_t)stream>>>(g);
-    cudaError_t e = cudaGetLastError();
-    return e == cudaSuccess ? 0 : (int)e;
+    return swiglu ? launch_gemm<0, 1>(g, grid, (cudaStream_t)stream) : launch_gemm<0, 0>(g, grid, (cudaStream_t)stream);
+}
+
+// All-gather -> GEMM. x_local [shard_rows, K] is this rank's sequence shard; the gather buffer
+// [world * shard_rows, K] sits at ag_buf_off of every slot. C [world * shard_rows, N or N/2].
+int mf_ag_gemm_bf16(const Team *team, const void *x_local, int64_t ldx, int shard_rows, const void *B, int64_t ldb, void *C, int64_t ldc,
+                    int N, int K, uint64_t ag_buf_off, uint64_t ag_ready_off, uint32_t *push_count, uint32_t epoch, uint32_t seq,
+                    int *status, int sms, int swiglu, void *stream)
+{
+    if (team == nullptr || shard_rows <= 0 || (shard_rows % BM) != 0 || team->emu) return -1;
+    GemmArgs g{};
+    const int M = shard_rows * (int)team->world;
+    const void *A = reinterpret_cast<const void *>(team->heap_base + (uint64_t)team->rank * team->stride + ag_buf_off);
+    int rc = fill_common(g, A, B, M, N, K, K, ldb, status);
+    if (rc != 0) return rc;
+    if (swiglu && (N % kBN) != 0) return -3;
+    g.C = static_cast<__nv_bfloat16 *>(C);
+    g.ldc = ldc;
+    g.team = *team;
+    g.epoch = epoch;
+    g.seq = seq;
+    g.x_local = static_cast<const __nv_bfloat16 *>(x_local);
+    g.ldx = ldx;
+    g.shard_rows = shard_rows;
+    g.ag_buf_off = ag_buf_off;
+    g.ag_ready_off = ag_ready_off;
+    g.push_count = push_count;
+    // every CTA carries copy warps whose work peers wait for: the grid must be fully resident
+    return swiglu ? launch_gemm<1, 1>(g, sms, (cudaStream_t)stream) : launch_gemm<1, 0>(g, sms, (cudaStream_t)stream);
+}
+
+// GEMM -> reduce-scatter. A [M, K] (M = world * rows_per_rank), B [N, K]; y_out [rows_per_rank, N] = scale * sum over ranks.
+int mf_gemm_rs_bf16(const Team *team, const void *A, int64_t lda, const void *B, int64_t ldb, void *y_out, int64_t ldy, int rows_per_rank,
+                    int N, int K, uint64_t rs_land_off, uint64_t rs_count_off, uint32_t epoch, uint32_t seq, float scale, int *status,
+                    int sms, void *stream)
+{
+    if (team == nullptr || rows_per_rank <= 0 || (rows_per_rank % BM) != 0 || (N & 7) != 0 || team->emu) return -1;
+    GemmArgs g{};
+    const int M = rows_per_rank * (int)team->world;
+    int rc = fill_common(g, A, B, M, N, K, lda, ldb, status);
+    if (rc != 0) return rc;
+    g.team = *team;
+    g.epoch = epoch;
+    g.seq = seq;
+    g.rs_land_off = rs_land_off;
+    g.rs_count_off = rs_count_off;
+    g.rows_per_rank = rows_per_rank;
+    g.y_out = static_cast<__nv_bfloat16 *>(y_out);
+    g.ldy = ldy;
+    g.scale = scale;
+    return launch_gemm<2, 0>(g, sms, (cudaStream_t)stream);
 }
 
 }  // extern "C"

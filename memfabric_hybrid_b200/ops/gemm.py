@@ -22,7 +22,7 @@ def _cu():
         l = N.cuda()
         l.mf_gemm_bf16.restype = C.c_int
         l.mf_gemm_bf16.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_int64,
-                                   C.c_void_p, C.c_int, C.c_void_p]
+                                   C.c_void_p, C.c_int, C.c_int, C.c_void_p]
         _lib = l
     return _lib
 
@@ -48,16 +48,26 @@ def sm_count(device=None) -> int:
     return torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device()).multi_processor_count
 
 
-def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, sms: int | None = None) -> torch.Tensor:
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, tile: int = 128) -> torch.Tensor:
+    """[F,K] gate and up weights -> [2F,K] with, per 256 rows, 128 gate rows followed by their 128 up rows: the
+    layout the fused SwiGLU epilogue expects (F must divide by 128)."""
+    F, K = w_gate.shape
+    assert w_up.shape == (F, K) and F % tile == 0
+    return torch.stack([w_gate.view(F // tile, tile, K), w_up.view(F // tile, tile, K)], dim=1).reshape(2 * F, K).contiguous()
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None, sms: int | None = None,
+              swiglu: bool = False) -> torch.Tensor:
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.is_cuda and b.is_cuda
     assert a.dim() == 2 and b.dim() == 2 and a.shape[1] == b.shape[1], "A[M,K] and B[N,K] must share K"
     assert a.stride(1) == 1 and b.stride(1) == 1, "K must be the contiguous dimension"
     M, K = a.shape
     Nn = b.shape[0]
     if out is None:
-        out = torch.empty((M, Nn), dtype=torch.bfloat16, device=a.device)
+        out = torch.empty((M, Nn // 2 if swiglu else Nn), dtype=torch.bfloat16, device=a.device)
     rc = _cu().mf_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, Nn, K, a.stride(0), b.stride(0), out.stride(0),
-                            status_word(a.device).data_ptr(), sms or sm_count(a.device), torch.cuda.current_stream().cuda_stream)
+                            status_word(a.device).data_ptr(), sms or sm_count(a.device), 1 if swiglu else 0,
+                            torch.cuda.current_stream().cuda_stream)
     if rc != 0:
         raise RuntimeError(f"mf_gemm_bf16 failed to launch ({rc})")
     return out

@@ -1,0 +1,59 @@
+"""Fused tensor-parallel MLP (all-gather->GEMM+SwiGLU, GEMM->reduce-scatter) against an fp32 reference."""
+import pytest
+import torch
+
+from conftest import free_port
+from mp_util import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _ranks(rank, world, url, T, H, F, sync):
+    import torch
+    from memfabric_hybrid_b200.ops import gemm
+    from memfabric_hybrid_b200.ops.heap import SymmetricHeap
+    from memfabric_hybrid_b200.models.llama_mlp import TensorParallelMLP
+    dev = rank % torch.cuda.device_count()
+    need = (1 << 20) + 2 * T * H * 2 + 2 * T * H * 2 + (8 << 20)
+    heap = SymmetricHeap(url, world, rank, dev, need)
+    mlp = TensorParallelMLP(heap, H, F, T, seed=3)
+    rows = T // world
+    worst = 0.0
+    for it in range(3):  # several calls: exercises the double buffering and the monotonic counters
+        xs = [torch.randn(rows, H, device="cuda", generator=torch.Generator("cuda").manual_seed(50 * it + r)).to(torch.bfloat16)
+              for r in range(world)]
+        y = mlp.forward(xs[rank])
+        torch.cuda.synchronize()
+        gemm.check_status()
+        # fp32 reference with every rank's weights regenerated locally
+        x = torch.cat(xs).float()
+        ref = torch.zeros(T, H, device="cuda")
+        for r in range(world):
+            g = torch.Generator("cuda").manual_seed(3 * 1000 + r)
+            wg = (torch.randn(F // world, H, device="cuda", generator=g) * 0.02).to(torch.bfloat16).float()
+            wu = (torch.randn(F // world, H, device="cuda", generator=g) * 0.02).to(torch.bfloat16).float()
+            wd = (torch.randn(H, F // world, device="cuda", generator=g) * 0.02).to(torch.bfloat16).float()
+            h = (torch.nn.functional.silu(x @ wg.t()) * (x @ wu.t())).to(torch.bfloat16).float()
+            ref += h @ wd.t()
+        mine = ref[rank * rows:(rank + 1) * rows]
+        err = (y.float() - mine).abs().max().item()
+        worst = max(worst, err / (mine.abs().max().item() + 1e-6))
+    st = heap.status()[0]
+    heap.close()
+    SymmetricHeap.shutdown()
+    return worst, st
+
+
+def test_tp_mlp_world1():
+    url = f"127.0.0.1:{free_port()}"
+    (worst, st), = run_ranks(_ranks, 1, (url, 512, 512, 1024), timeout=300, with_barrier=True)
+    assert st == 0 and worst < 3e-2, (worst, st)
+
+
+@pytest.mark.multigpu
+def test_tp_mlp_multi_gpu():
+    n = 2 if torch.cuda.device_count() < 4 else 4
+    url = f"127.0.0.1:{free_port()}"
+    res = run_ranks(_ranks, n, (url, 1024, 512, 2048), timeout=300, with_barrier=True)
+    for worst, st in res:
+        assert st == 0 and worst < 3e-2, res
