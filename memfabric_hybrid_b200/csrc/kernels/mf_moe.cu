@@ -1,0 +1,402 @@
+// Expert-parallel MoE communication kernels (DeepEP-style) on the symmetric heap.
+//   moe_layout   : from topk_idx[T,K]: tokens per expert, tokens per rank, per-(token,k) index inside its
+//                  expert (token order), token-in-rank mask
+//   moe_notify   : all ranks exchange their per-expert send counts (peer stores + one barrier); every rank
+//                  derives, on the device, the receive layout [local expert][source rank] of its own buffer
+//                  and the offset at which each of ITS expert groups starts in the destination's buffer.
+//                  Nothing is copied to the host: counts stay on the device.
+//   moe_dispatch : FUSES the 1x128 block-scaled fp8 e4m3 quantisation of a token with the all-to-all: the
+//                  quantised row, its 56 scales, its routing weight and its origin are stored straight into
+//                  the receive buffers of the ranks that own its experts (peer stores over NVLink)
+//   moe_combine_reduce : sums the K weighted expert outputs that peers pushed into this rank's combine
+//                  slots (the push itself happens in the epilogue of the down-projection GEMM)
+// Parity of role: app/zbal/src/csrc/operators/npu/aicore/ops/dispatch_combine_normal/
+// zbal_kernel_{dispatch_layout,notify_dispatch,dispatch_normal,combine_normal}.h of the reference.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "mf_team.cuh"
+
+namespace mfk {
+
+constexpr int kQuantGroup = 128;
+
+struct MoeShape {
+    int T;        // tokens of this rank
+    int K;        // experts per token
+    int E;        // experts in total
+    int H;        // hidden size (multiple of 128)
+    int max_recv; // rows of the receive buffers
+};
+
+// Offsets (in each rank's slot) of the MoE communication area.
+struct MoeHeap {
+    uint64_t counts;      // int32 [W][E]           send counts, row s written by rank s
+    uint64_t recv_x;      // fp8   [max_recv][H]
+    uint64_t recv_scale;  // f32   [max_recv][H/128]
+    uint64_t recv_info;   // int4  [max_recv]        {source rank, token, k slot, weight bits}
+    uint64_t comb;        // bf16  [T_max * K][H]    combine slots of this rank's own tokens
+    uint64_t flags;       // u32   [4][kMaxRanks]    0 dispatch done, 1 combine done
+};
+
+// ---- layout --------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) k_moe_layout_expert(const int *__restrict__ topk_idx, int n_entries, int *tokens_per_expert,
+                                                            int *send_idx)
+{
+    // one CTA per expert: positions in token order by a block-wide running prefix
+    const int e = blockIdx.x;
+    __shared__ int warp_cnt[32];
+    __shared__ int running;
+    if (threadIdx.x == 0) running = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int base = 0; base < n_entries; base += blockDim.x) {
+        const int i = base + threadIdx.x;
+        const bool hit = i < n_entries && topk_idx[i] == e;
+        const unsigned m = __ballot_sync(0xffffffffu, hit);
+        if (lane == 0) warp_cnt[warp] = __popc(m);
+        __syncthreads();
+        int before = running;
+        for (int w = 0; w < warp; w++) before += warp_cnt[w];
+        if (hit) send_idx[i] = before + __popc(m & ((1u << lane) - 1));
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int s = 0;
+            for (int w = 0; w < (int)(blockDim.x >> 5); w++) s += warp_cnt[w];
+            running += s;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) tokens_per_expert[e] = running;
+}
+
+__global__ void k_moe_layout_rank(const int *__restrict__ topk_idx, int T, int K, int experts_per_rank, int world, int *tokens_per_rank,
+                                  uint8_t *is_token_in_rank)
+{
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    uint32_t mask = 0;
+    for (int k = 0; k < K; k++) {
+        const int e = topk_idx[t * K + k];
+        if (e >= 0) mask |= 1u << (e / experts_per_rank);
+    }
+    for (int r = 0; r < world; r++) {
+        const bool in = (mask >> r) & 1u;
+        is_token_in_rank[t * world + r] = in ? 1 : 0;
+        if (in) atomicAdd(tokens_per_rank + r, 1);
+    }
+}
+
+// ---- notify ---------------------------------------------------------------------------------------
+// outputs (device, local): recv_per_expert[El], row_off[El + 1], put_off[E], src_off[El][W]
+__global__ void __launch_bounds__(1024) k_moe_notify(Team team, MoeHeap hp, int E, const int *tokens_per_expert, int *recv_per_expert,
+                                                     int *row_off, int *put_off, int *src_off, uint32_t epoch)
+{
+    const uint32_t me = team_rank(team);
+    const uint32_t W = team.world;
+    const int El = E / (int)W;
+    // 1. my counts into row `me` of everybody's table
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int c = tokens_per_expert[e];
+        for (uint32_t k = 0; k < W; k++) {
+            const uint32_t r = (me + k) % W;
+            reinterpret_cast<int *>(peer_ptr(team, r, hp.counts))[me * E + e] = c;
+        }
+    }
+    if (!team_barrier(team, me, 8, epoch)) return;
+    const int *tbl = reinterpret_cast<const int *>(peer_ptr(team, me, hp.counts));
+    __shared__ int per_expert[1024];  // totals of every expert over all sources
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int s = 0;
+        for (uint32_t r = 0; r < W; r++) s += __ldcg(tbl + r * E + e);
+        per_expert[e] = s;
+    }
+    __syncthreads();
+    // 2. my receive layout
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int le = 0; le < El; le++) {
+            row_off[le] = run;
+            recv_per_expert[le] = per_expert[me * El + le];
+            run += per_expert[me * El + le];
+        }
+        row_off[El] = run;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < El * (int)W; i += blockDim.x) {
+        const int le = i / (int)W, s = i % (int)W;
+        int off = row_off[le];
+        for (int r = 0; r < s; r++) off += __ldcg(tbl + r * E + me * El + le);
+        src_off[i] = off;
+    }
+    // 3. where my group for expert e starts in its owner's buffer
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int d = e / El, le = e % El;
+        int off = 0;
+        for (int l2 = 0; l2 < le; l2++) off += per_expert[d * El + l2];
+        for (uint32_t r = 0; r < me; r++) off += __ldcg(tbl + r * E + e);
+        put_off[e] = off;
+    }
+}
+
+// ---- dispatch -------------------------------------------------------------------------------------
+// 448 threads per token row: thread i owns elements [16 i, 16 i + 16); 8 consecutive threads form a 128-group.
+struct DispatchArgs {
+    Team team;
+    MoeHeap hp;
+    MoeShape sh;
+    const __nv_bfloat16 *x;     // [T, H]
+    const int *topk_idx;        // [T, K]
+    const float *topk_w;        // [T, K]
+    const int *send_idx;        // [T, K]
+    const int *put_off;         // [E]
+    uint32_t *done_count;       // local counter, monotonic
+    uint32_t epoch;
+    uint32_t seq;
+    int *status;
+};
+
+__global__ void __launch_bounds__(448) k_moe_dispatch(DispatchArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const int H = a.sh.H, K = a.sh.K, El = a.sh.E / (int)t.world;
+    const int groups = H / kQuantGroup;
+    const int vec = threadIdx.x;          // 16-element vector index inside the row
+    const int vecs = H / 16;
+    __shared__ int dst_rank[16];
+    __shared__ int dst_pos[16];
+    __shared__ float dst_w[16];
+    for (int tok = blockIdx.x; tok < a.sh.T; tok += gridDim.x) {
+        if (threadIdx.x < K) {
+            const int e = a.topk_idx[tok * K + threadIdx.x];
+            if (e >= 0) {
+                const int pos = a.put_off[e] + a.send_idx[tok * K + threadIdx.x];
+                dst_rank[threadIdx.x] = pos < a.sh.max_recv ? e / El : -1;
+                if (pos >= a.sh.max_recv) atomicCAS(a.status, 0, 0x401);  // receive buffer too small: dropped, reported
+                dst_pos[threadIdx.x] = pos;
+                dst_w[threadIdx.x] = a.topk_w[tok * K + threadIdx.x];
+            } else {
+                dst_rank[threadIdx.x] = -1;
+            }
+        }
+        __syncthreads();
+        uint4 q;
+        float scale;
+        {
+            float f[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) f[i] = 0.f;
+            if (vec < vecs) {
+                const uint4 *src = reinterpret_cast<const uint4 *>(a.x + (int64_t)tok * H + vec * 16);
+                const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+                const __nv_bfloat162 *h0 = reinterpret_cast<const __nv_bfloat162 *>(&lo);
+                const __nv_bfloat162 *h1 = reinterpret_cast<const __nv_bfloat162 *>(&hi);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    float2 p = __bfloat1622float2(h0[i]);
+                    f[2 * i] = p.x;
+                    f[2 * i + 1] = p.y;
+                    p = __bfloat1622float2(h1[i]);
+                    f[8 + 2 * i] = p.x;
+                    f[8 + 2 * i + 1] = p.y;
+                }
+            }
+            float amax = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(f[i]));
+            // the 8 threads of a 128-group are consecutive lanes of one warp; every lane takes part
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            const float mul = amax > 0.f ? 448.f / amax : 1.f;
+            scale = amax > 0.f ? amax / 448.f : 1.f;
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                uint32_t b = 0;
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    b |= (uint32_t)__nv_cvt_float_to_fp8(f[4 * i + j] * mul, __NV_SATFINITE, __NV_E4M3) << (8 * j);
+                w[i] = b;
+            }
+            q = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        for (int k = 0; k < K; k++) {
+            const int d = dst_rank[k];
+            if (d < 0) continue;
+            const int64_t pos = dst_pos[k];
+            if (vec < vecs) {
+                uint8_t *row = peer_ptr(t, d, a.hp.recv_x) + pos * H;
+                *reinterpret_cast<uint4 *>(row + vec * 16) = q;
+                if ((vec & 7) == 0)
+                    reinterpret_cast<float *>(peer_ptr(t, d, a.hp.recv_scale))[pos * groups + (vec >> 3)] = scale;
+            }
+            if (threadIdx.x == 0) {
+                int4 info = make_int4((int)me, tok, k, __float_as_int(dst_w[k]));
+                reinterpret_cast<int4 *>(peer_ptr(t, d, a.hp.recv_info))[pos] = info;
+            }
+        }
+        __syncthreads();
+    }
+    // the CTA that finishes last tells every peer that all of this rank's rows have been stored
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t done = atomicAdd(a.done_count, 1u) + 1;
+        if (done == gridDim.x * a.seq) {
+            __threadfence_system();
+            for (uint32_t r = 0; r < t.world; r++)
+                st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, a.hp.flags)) + me, a.epoch);
+        }
+    }
+}
+
+// Waits until every rank raised flag row `which` (0 dispatch, 1 combine) to `epoch`.
+__global__ void k_moe_wait_all(Team t, MoeHeap hp, int which, uint32_t epoch, int *status)
+{
+    const uint32_t me = team_rank(t);
+    if (threadIdx.x < t.world) {
+        const uint32_t *f = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, hp.flags)) + which * kMaxRanks + threadIdx.x;
+        if (!wait_flag(f, epoch, t.spin_limit)) {
+            report_timeout(t, me, 0x410 + which, epoch);
+            atomicCAS(status, 0, 0x410 + which);
+        }
+    }
+}
+
+// Raises flag row `which` on every peer once all CTAs of the preceding kernel on this stream are done
+// (stream order makes this launch the "last CTA").
+__global__ void k_moe_signal_all(Team t, MoeHeap hp, int which, uint32_t epoch)
+{
+    const uint32_t me = team_rank(t);
+    __threadfence_system();
+    if (threadIdx.x < t.world)
+        st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, threadIdx.x, hp.flags)) + which * kMaxRanks + me, epoch);
+}
+
+// out[t, :] = sum over the valid k slots of comb[t * K + k, :]; the rows were already multiplied by the
+// routing weights when they were pushed.
+__global__ void __launch_bounds__(256) k_moe_combine_reduce(Team t, MoeHeap hp, MoeShape sh, const int *topk_idx, __nv_bfloat16 *out)
+{
+    const uint32_t me = team_rank(t);
+    const __nv_bfloat16 *comb = reinterpret_cast<const __nv_bfloat16 *>(peer_ptr(t, me, hp.comb));
+    const int vecs = sh.H / 8;
+    for (int tok = blockIdx.x; tok < sh.T; tok += gridDim.x) {
+        for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int k = 0; k < sh.K; k++) {
+                if (topk_idx[tok * sh.K + k] < 0) continue;
+                const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(comb + ((int64_t)tok * sh.K + k) * sh.H) + v);
+                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __bfloat1622float2(h[e]);
+                    acc[2 * e] += f.x;
+                    acc[2 * e + 1] += f.y;
+                }
+            }
+            uint4 pk;
+            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+            *(reinterpret_cast<uint4 *>(out + (int64_t)tok * sh.H) + v) = pk;
+        }
+    }
+}
+
+// Rows of bf16 -> fp8 e4m3 with one scale per 128 elements (the activation format of the expert GEMMs).
+// rows_dev: device int with the number of valid rows (the receive count), read here so the host never waits.
+__global__ void __launch_bounds__(256) k_quant_rows_fp8(const __nv_bfloat16 *__restrict__ x, int64_t ldx, const int *rows_dev, int cols,
+                                                        uint8_t *__restrict__ q, float *__restrict__ scales)
+{
+    const int rows = *rows_dev;
+    const int groups = cols / kQuantGroup;
+    const int lane = threadIdx.x & 31;
+    const int warps_total = gridDim.x * (blockDim.x >> 5);
+    for (int64_t g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); g < (int64_t)rows * groups; g += warps_total) {
+        const int64_t r = g / groups;
+        const int gi = (int)(g % groups);
+        const uint2 raw = __ldg(reinterpret_cast<const uint2 *>(x + r * ldx + gi * kQuantGroup) + lane);
+        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+        const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+        float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const float mul = amax > 0.f ? 448.f / amax : 1.f;
+        uint32_t w = (uint32_t)__nv_cvt_float_to_fp8(a.x * mul, __NV_SATFINITE, __NV_E4M3) |
+                     (uint32_t)__nv_cvt_float_to_fp8(a.y * mul, __NV_SATFINITE, __NV_E4M3) << 8 |
+                     (uint32_t)__nv_cvt_float_to_fp8(b.x * mul, __NV_SATFINITE, __NV_E4M3) << 16 |
+                     (uint32_t)__nv_cvt_float_to_fp8(b.y * mul, __NV_SATFINITE, __NV_E4M3) << 24;
+        reinterpret_cast<uint32_t *>(q + r * cols + gi * kQuantGroup)[lane] = w;
+        if (lane == 0) scales[r * groups + gi] = amax > 0.f ? amax / 448.f : 1.f;
+    }
+}
+
+}  // namespace mfk
+
+using namespace mfk;
+
+extern "C" {
+
+int mf_moe_layout(const int *topk_idx, int T, int K, int E, int world, int *tokens_per_expert, int *tokens_per_rank, int *send_idx,
+                  uint8_t *is_token_in_rank, void *stream)
+{
+    if (T <= 0 || K <= 0 || K > 16 || E <= 0 || E > 1024 || world <= 0 || E % world != 0) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaMemsetAsync(tokens_per_rank, 0, sizeof(int) * world, s);
+    k_moe_layout_expert<<<E, 1024, 0, s>>>(topk_idx, T * K, tokens_per_expert, send_idx);
+    k_moe_layout_rank<<<(T + 255) / 256, 256, 0, s>>>(topk_idx, T, K, E / world, world, tokens_per_rank, is_token_in_rank);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int mf_moe_notify(const Team *team, const MoeHeap *hp, int E, const int *tokens_per_expert, int *recv_per_expert, int *row_off,
+                  int *put_off, int *src_off, uint32_t epoch, void *stream)
+{
+    if (team == nullptr || hp == nullptr || team->emu || E > 1024 || E % (int)team->world != 0) return -1;
+    k_moe_notify<<<1, 1024, 0, (cudaStream_t)stream>>>(*team, *hp, E, tokens_per_expert, recv_per_expert, row_off, put_off, src_off, epoch);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int mf_moe_dispatch(const DispatchArgs *a, int ctas, void *stream)
+{
+    if (a == nullptr || a->team.emu || a->sh.H % 128 != 0 || a->sh.H / 16 > 448 || a->sh.K > 16) return -1;
+    k_moe_dispatch<<<ctas, 448, 0, (cudaStream_t)stream>>>(*a);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int mf_moe_wait_all(const Team *team, const MoeHeap *hp, int which, uint32_t epoch, int *status, void *stream)
+{
+    k_moe_wait_all<<<1, 32, 0, (cudaStream_t)stream>>>(*team, *hp, which, epoch, status);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int mf_moe_signal_all(const Team *team, const MoeHeap *hp, int which, uint32_t epoch, void *stream)
+{
+    k_moe_signal_all<<<1, 32, 0, (cudaStream_t)stream>>>(*team, *hp, which, epoch);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int mf_moe_combine_reduce(const Team *team, const MoeHeap *hp, const MoeShape *sh, const int *topk_idx, void *out, int ctas, void *stream)
+{
+    if (sh->H % 8 != 0) return -1;
+    k_moe_combine_reduce<<<ctas, 256, 0, (cudaStream_t)stream>>>(*team, *hp, *sh, topk_idx, static_cast<__nv_bfloat16 *>(out));
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int mf_quant_rows_fp8(const void *x, int64_t ldx, const int *rows_dev, int cols, void *q, float *scales, int ctas, void *stream)
+{
+    if (cols % 128 != 0) return -1;
+    k_quant_rows_fp8<<<ctas, 256, 0, (cudaStream_t)stream>>>(static_cast<const __nv_bfloat16 *>(x), ldx, rows_dev, cols,
+                                                             static_cast<uint8_t *>(q), scales);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+}  // extern "C"

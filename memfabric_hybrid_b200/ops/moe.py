@@ -1,0 +1,220 @@
+"""Expert-parallel MoE on the symmetric heap: layout -> notify -> fused fp8 dispatch -> grouped expert
+GEMMs (tcgen05, fp8 block-scaled) with SwiGLU and combine fused into their epilogues -> slot reduce.
+
+    moe = MoEComm(heap, max_tokens=4096, hidden=7168, experts=256, topk=8)
+    st  = moe.dispatch(x, topk_idx, topk_w)                  # device-resident counts, no host sync
+    moe.expert_ffn(st, w1, w1_scale, w2, w2_scale)           # gate/up+SwiGLU, requant, down+weighted push
+    y   = moe.combine(st)                                    # [T, hidden] bf16
+
+Calls must alternate dispatch ... combine on every rank: the wait inside combine is what guarantees that
+peers finished reading the receive buffers before the next dispatch overwrites them.
+Kernels: csrc/kernels/mf_moe.cu, csrc/kernels/mf_gemm_fp8.cu.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import torch
+
+from .. import _native as N
+from .gemm import sm_count, status_word
+from .heap import TeamC, _HeapBase
+
+
+class MoeShapeC(C.Structure):
+    _fields_ = [("T", C.c_int), ("K", C.c_int), ("E", C.c_int), ("H", C.c_int), ("max_recv", C.c_int)]
+
+
+class MoeHeapC(C.Structure):
+    _fields_ = [("counts", C.c_uint64), ("recv_x", C.c_uint64), ("recv_scale", C.c_uint64), ("recv_info", C.c_uint64),
+                ("comb", C.c_uint64), ("flags", C.c_uint64)]
+
+
+class DispatchArgsC(C.Structure):
+    _fields_ = [("team", TeamC), ("hp", MoeHeapC), ("sh", MoeShapeC), ("x", C.c_void_p), ("topk_idx", C.c_void_p),
+                ("topk_w", C.c_void_p), ("send_idx", C.c_void_p), ("put_off", C.c_void_p), ("done_count", C.c_void_p),
+                ("epoch", C.c_uint32), ("seq", C.c_uint32), ("status", C.c_void_p)]
+
+
+_lib = None
+
+
+def _cu():
+    global _lib
+    if _lib is None:
+        l = N.cuda()
+        P, vp, ci = C.POINTER, C.c_void_p, C.c_int
+        l.mf_moe_layout.restype = ci
+        l.mf_moe_layout.argtypes = [vp, ci, ci, ci, ci, vp, vp, vp, vp, vp]
+        l.mf_moe_notify.restype = ci
+        l.mf_moe_notify.argtypes = [P(TeamC), P(MoeHeapC), ci, vp, vp, vp, vp, vp, C.c_uint32, vp]
+        l.mf_moe_dispatch.restype = ci
+        l.mf_moe_dispatch.argtypes = [P(DispatchArgsC), ci, vp]
+        l.mf_moe_wait_all.restype = ci
+        l.mf_moe_wait_all.argtypes = [P(TeamC), P(MoeHeapC), ci, C.c_uint32, vp, vp]
+        l.mf_moe_signal_all.restype = ci
+        l.mf_moe_signal_all.argtypes = [P(TeamC), P(MoeHeapC), ci, C.c_uint32, vp]
+        l.mf_moe_combine_reduce.restype = ci
+        l.mf_moe_combine_reduce.argtypes = [P(TeamC), P(MoeHeapC), P(MoeShapeC), vp, vp, ci, vp]
+        l.mf_quant_rows_fp8.restype = ci
+        l.mf_quant_rows_fp8.argtypes = [vp, C.c_int64, vp, ci, vp, vp, ci, vp]
+        l.mf_grouped_gemm_fp8.restype = ci
+        l.mf_grouped_gemm_fp8.argtypes = [vp, vp, ci, vp, vp, vp, ci, ci, ci, vp, C.c_int64, ci, P(TeamC), vp, C.c_uint64, ci, vp, ci, vp]
+        _lib = l
+    return _lib
+
+
+def _s() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ok(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what}: launch failed ({rc})")
+
+
+def quantize_weight_fp8(w: torch.Tensor):
+    """[..., N, K] bf16/fp32 -> (fp8 e4m3 [..., N, K], fp32 scales [..., N/128, K/128]); 128 x 128 blocks."""
+    *lead, Nn, K = w.shape
+    assert Nn % 128 == 0 and K % 128 == 0
+    blk = w.float().reshape(*lead, Nn // 128, 128, K // 128, 128)
+    amax = blk.abs().amax(dim=(-3, -1), keepdim=True).clamp_min(1e-12)
+    scale = amax / 448.0
+    q = (blk / scale).clamp(-448, 448).to(torch.float8_e4m3fn).reshape(*lead, Nn, K)
+    return q.contiguous(), scale.reshape(*lead, Nn // 128, K // 128).contiguous()
+
+
+def interleave_gate_up_fp8(w1q: torch.Tensor, tile: int = 64) -> torch.Tensor:
+    """[G, 2I, K] (gate rows then up rows) -> per 128 rows: 64 gate rows followed by their 64 up rows."""
+    G, two_i, K = w1q.shape
+    i = two_i // 2
+    assert i % tile == 0
+    gate = w1q[:, :i].reshape(G, i // tile, tile, K)
+    up = w1q[:, i:].reshape(G, i // tile, tile, K)
+    return torch.stack([gate, up], dim=2).reshape(G, two_i, K).contiguous()
+
+
+@dataclass
+class DispatchState:
+    T: int
+    topk_idx: torch.Tensor       # [T, K] int32
+    send_idx: torch.Tensor
+    tokens_per_expert: torch.Tensor
+    tokens_per_rank: torch.Tensor
+    is_token_in_rank: torch.Tensor
+    recv_per_expert: torch.Tensor  # [El] int32, device
+    row_off: torch.Tensor          # [El + 1] int32, device; row_off[-1] = rows received
+    put_off: torch.Tensor
+    src_off: torch.Tensor
+    epoch: int
+
+
+class MoEComm:
+    def __init__(self, heap: _HeapBase, max_tokens: int, hidden: int, experts: int, topk: int, max_recv: int | None = None,
+                 intermediate: int | None = None):
+        assert not heap.emu and hidden % 128 == 0 and experts % heap.world == 0
+        self.heap, self.world, self.rank = heap, heap.world, heap.rank
+        self.T, self.H, self.E, self.K = max_tokens, hidden, experts, topk
+        self.El = experts // self.world
+        self.max_recv = max_recv or max_tokens * self.world * min(topk, self.El)
+        self.dev = torch.device("cuda", torch.cuda.current_device())
+        hp = MoeHeapC()
+        hp.counts = heap.alloc(self.world * experts * 4, 256)
+        hp.flags = heap.alloc(4 * 16 * 4, 256)
+        hp.recv_x = heap.alloc(self.max_recv * hidden, 1024)
+        hp.recv_scale = heap.alloc(self.max_recv * (hidden // 128) * 4, 256)
+        hp.recv_info = heap.alloc(self.max_recv * 16, 256)
+        hp.comb = heap.alloc(max_tokens * topk * hidden * 2, 1024)
+        self.hp = hp
+        heap.view(hp.flags, (4 * 16,), torch.int32).zero_()
+        heap.view(hp.counts, (self.world * experts,), torch.int32).zero_()
+        self._epoch = 0
+        self._done = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self._dispatches = 0
+        self._grid = sm_count(self.dev)
+        self._inter = intermediate
+        self._h = self._hq = self._hs = None
+        torch.cuda.synchronize()
+        if hasattr(heap, "host_barrier"):
+            heap.host_barrier()
+
+    # views of the receive area (valid rows: state.row_off[-1])
+    def recv_x(self) -> torch.Tensor:
+        return self.heap.view(self.hp.recv_x, (self.max_recv, self.H), torch.uint8).view(torch.float8_e4m3fn)
+
+    def recv_scale(self) -> torch.Tensor:
+        return self.heap.view(self.hp.recv_scale, (self.max_recv, self.H // 128), torch.float32)
+
+    def recv_info(self) -> torch.Tensor:
+        return self.heap.view(self.hp.recv_info, (self.max_recv, 4), torch.int32)
+
+    def _shape(self, T: int) -> MoeShapeC:
+        return MoeShapeC(T, self.K, self.E, self.H, self.max_recv)
+
+    # ------------------------------------------------------------------ stages
+    def get_dispatch_layout(self, topk_idx: torch.Tensor):
+        T = topk_idx.shape[0]
+        idx = topk_idx.to(torch.int32).contiguous()
+        tpe = torch.empty(self.E, dtype=torch.int32, device=self.dev)
+        tpr = torch.empty(self.world, dtype=torch.int32, device=self.dev)
+        sidx = torch.zeros(T * self.K, dtype=torch.int32, device=self.dev)
+        inr = torch.empty((T, self.world), dtype=torch.uint8, device=self.dev)
+        _ok(_cu().mf_moe_layout(idx.data_ptr(), T, self.K, self.E, self.world, tpe.data_ptr(), tpr.data_ptr(), sidx.data_ptr(),
+                                inr.data_ptr(), _s()), "moe_layout")
+        return idx, tpe, tpr, sidx, inr
+
+    def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor) -> DispatchState:
+        assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == self.H and x.shape[0] <= self.T
+        T = x.shape[0]
+        idx, tpe, tpr, sidx, inr = self.get_dispatch_layout(topk_idx)
+        self._epoch += 1
+        team = self.heap.team()
+        rpe = torch.empty(self.El, dtype=torch.int32, device=self.dev)
+        row_off = torch.empty(self.El + 1, dtype=torch.int32, device=self.dev)
+        put_off = torch.empty(self.E, dtype=torch.int32, device=self.dev)
+        src_off = torch.empty(self.El * self.world, dtype=torch.int32, device=self.dev)
+        _ok(_cu().mf_moe_notify(C.byref(team), C.byref(self.hp), self.E, tpe.data_ptr(), rpe.data_ptr(), row_off.data_ptr(),
+                                put_off.data_ptr(), src_off.data_ptr(), self._epoch, _s()), "moe_notify")
+        w = topk_w.to(torch.float32).contiguous()
+        self._dispatches += 1
+        a = DispatchArgsC(team, self.hp, self._shape(T), x.data_ptr(), idx.data_ptr(), w.data_ptr(), sidx.data_ptr(), put_off.data_ptr(),
+                          self._done.data_ptr(), self._epoch, self._dispatches, status_word(self.dev).data_ptr())
+        self._keep = (w, idx)
+        # one CTA per SM on every call: the completion counter of the kernel counts CTAs
+        _ok(_cu().mf_moe_dispatch(C.byref(a), self._grid, _s()), "moe_dispatch")
+        _ok(_cu().mf_moe_wait_all(C.byref(team), C.byref(self.hp), 0, self._epoch, status_word(self.dev).data_ptr(), _s()), "moe_wait")
+        return DispatchState(T, idx, sidx, tpe, tpr, inr, rpe, row_off, put_off, src_off, self._epoch)
+
+    def expert_ffn(self, st: DispatchState, w1q: torch.Tensor, w1s: torch.Tensor, w2q: torch.Tensor, w2s: torch.Tensor) -> None:
+        """w1q [El, 2I, H] fp8 tile-interleaved (interleave_gate_up_fp8), w1s [El, 2I/128, H/128] in ORIGINAL row order;
+        w2q [El, H, I] fp8, w2s [El, H/128, I/128]. The result rows are pushed, weighted, to the tokens' home ranks."""
+        El, two_i, H = w1q.shape
+        I = two_i // 2
+        assert El == self.El and H == self.H and w2q.shape == (El, H, I)
+        if self._h is None or self._h.shape[1] != I:
+            self._h = torch.empty((self.max_recv, I), dtype=torch.bfloat16, device=self.dev)
+            self._hq = torch.empty((self.max_recv, I), dtype=torch.uint8, device=self.dev)
+            self._hs = torch.empty((self.max_recv, I // 128), dtype=torch.float32, device=self.dev)
+        team = self.heap.team()
+        stw = status_word(self.dev).data_ptr()
+        cu = _cu()
+        _ok(cu.mf_grouped_gemm_fp8(self.heap.ptr(self.rank, self.hp.recv_x), self.heap.ptr(self.rank, self.hp.recv_scale), self.max_recv,
+                                   w1q.data_ptr(), w1s.data_ptr(), st.row_off.data_ptr(), El, two_i, H, self._h.data_ptr(), I, 1, None, None,
+                                   0, self.K, stw, self._grid, _s()), "grouped_gemm_fp8 (gate/up)")
+        _ok(cu.mf_quant_rows_fp8(self._h.data_ptr(), I, st.row_off[El:].data_ptr(), I, self._hq.data_ptr(), self._hs.data_ptr(),
+                                 self._grid * 4, _s()), "quant_rows_fp8")
+        _ok(cu.mf_grouped_gemm_fp8(self._hq.data_ptr(), self._hs.data_ptr(), self.max_recv, w2q.data_ptr(), w2s.data_ptr(),
+                                   st.row_off.data_ptr(), El, H, I, None, 0, 2, C.byref(team), self.heap.ptr(self.rank, self.hp.recv_info),
+                                   self.hp.comb, self.K, stw, self._grid, _s()), "grouped_gemm_fp8 (down+combine)")
+        _ok(cu.mf_moe_signal_all(C.byref(team), C.byref(self.hp), 1, st.epoch, _s()), "moe_signal")
+
+    def combine(self, st: DispatchState, out: torch.Tensor | None = None) -> torch.Tensor:
+        team = self.heap.team()
+        if out is None:
+            out = torch.empty((st.T, self.H), dtype=torch.bfloat16, device=self.dev)
+        _ok(_cu().mf_moe_wait_all(C.byref(team), C.byref(self.hp), 1, st.epoch, status_word(self.dev).data_ptr(), _s()), "moe_wait")
+        sh = self._shape(st.T)
+        _ok(_cu().mf_moe_combine_reduce(C.byref(team), C.byref(self.hp), C.byref(sh), st.topk_idx.data_ptr(), out.data_ptr(),
+                                        min(st.T, self._grid * 4), _s()), "moe_combine_reduce")
+        return out
