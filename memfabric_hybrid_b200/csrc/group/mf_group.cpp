@@ -405,7 +405,9 @@ void GroupEngine::HandleEvent(const GroupInfo &ev)
         // finalised: adopt the membership view
         if (joined_) {
             std::lock_guard<std::mutex> g(mu_);
-            if (ev.Has(opt_.rank)) {
+            // a notification can arrive after this rank already posted a NEWER event of its own
+            // (its main thread does not wait for the watch): never step back to an older record
+            if (ev.Has(opt_.rank) && ev.version > info_.version) {
                 info_ = ev;
                 eventOpVersion_ = 0;
             }
@@ -421,9 +423,11 @@ void GroupEngine::HandleEvent(const GroupInfo &ev)
     {
         std::lock_guard<std::mutex> g(mu_);
         hadTarget = info_.Has(ev.targetRank);
-        info_ = ev;
-        eventOpVersion_ = ev.version;
-        eventOpSn_ = 0;
+        if (ev.version > info_.version) {
+            info_ = ev;
+            eventOpVersion_ = ev.version;
+            eventOpSn_ = 0;
+        }
     }
     int rc = OK;
     switch (ev.curEvent) {
