@@ -553,3 +553,97 @@ unsigned mf_coll_max_ctas(void) { return kMaxCtas; }
 unsigned mf_coll_args_size(void) { return (unsigned)sizeof(CollArgs); }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// All-reduce without allocation (declared in include/mf_noalloc.h; no counterpart in the reference).
+// The staging buffers and flags of the emulated group live in this file-scope array instead of a heap
+// that somebody had to allocate. In host code the array's name is only a handle: the device address
+// comes from cudaGetSymbolAddress, once per device, with that device current.
+#include <mutex>
+
+#include "../include/mf_noalloc.h"
+
+namespace {
+constexpr uint64_t kNaSlot = (uint64_t)kSignalBytes + 2ull * MF_NOALLOC_MAX_BYTES;  // flags | staging A | staging B
+static __device__ __align__(256) unsigned char g_noalloc_scratch[MF_NOALLOC_MAX_WORLD * kNaSlot];
+
+struct NaDevice {
+    void *base = nullptr;  // device address of g_noalloc_scratch on that device
+    uint32_t epoch = 0;
+};
+std::mutex g_na_mu;
+NaDevice g_na_dev[64];
+}  // namespace
+
+extern "C" {
+
+const char *mf_noalloc_strerror(int code)
+{
+    switch (code) {
+        case MF_NOALLOC_OK: return "ok";
+        case MF_NOALLOC_E_ARG: return "bad argument: null pointer, or dtype / op / world out of range";
+        case MF_NOALLOC_E_TOO_LARGE: return "vector larger than MF_NOALLOC_MAX_BYTES (1 MiB): the built-in scratch cannot stage it";
+        case MF_NOALLOC_E_SETUP: return "could not obtain the device address of the built-in scratch array";
+        case MF_NOALLOC_E_LAUNCH: return "kernel launch refused";
+        default: return "unknown code";
+    }
+}
+
+int mf_allreduce_stacked_noalloc(const void *in, void *out, int world, uint64_t n, int dtype, int op, float scale, void *stream)
+{
+    if (in == nullptr || out == nullptr || world < 1 || world > MF_NOALLOC_MAX_WORLD || n == 0 || dtype < 0 || dtype > 3 || op < 0 || op > 3)
+        return MF_NOALLOC_E_ARG;
+    const uint64_t es = (dtype == DT_F32 || dtype == DT_I32) ? 4 : 2;
+    if (n > MF_NOALLOC_MAX_BYTES / es) return MF_NOALLOC_E_TOO_LARGE;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MF_NOALLOC_E_SETUP;
+    uint32_t epoch;
+    void *base;
+    {
+        std::lock_guard<std::mutex> lock(g_na_mu);
+        NaDevice &d = g_na_dev[dev];
+        if (d.base == nullptr) {
+            // first call on this device: resolve the symbol here (its host-side name is not a device
+            // pointer) and start from clean status words and flags
+            void *p = nullptr;
+            if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) {
+                (void)cudaGetLastError();
+                return MF_NOALLOC_E_SETUP;
+            }
+            for (int r = 0; r < MF_NOALLOC_MAX_WORLD; r++)
+                if (cudaMemset(static_cast<unsigned char *>(p) + r * kNaSlot, 0, kSignalBytes) != cudaSuccess) {
+                    (void)cudaGetLastError();
+                    return MF_NOALLOC_E_SETUP;
+                }
+            d.base = p;
+        }
+        base = d.base;
+        epoch = ++d.epoch;
+    }
+    CollArgs a{};
+    a.team.heap_base = reinterpret_cast<uint64_t>(base);
+    a.team.stride = kNaSlot;
+    a.team.mc_base = 0;
+    a.team.rank = 0;
+    a.team.world = (uint32_t)world;
+    a.team.emu = 1;
+    a.team.spin_limit = 1u << 22;
+    a.in = reinterpret_cast<uint64_t>(in);
+    a.out = reinterpret_cast<uint64_t>(out);
+    a.in_rank_stride = n * es;
+    a.out_rank_stride = n * es;
+    a.n = n;
+    a.stage_a = kSignalBytes;
+    a.stage_b = kSignalBytes + MF_NOALLOC_MAX_BYTES;
+    a.scale = scale;
+    a.op = op;
+    a.epoch = epoch;
+    a.zero_copy = 0;
+    a.root = 0;
+    a.algo = 0;  // one-shot: a single set of staging buffers is enough because calls are serialised
+    const int ctas = n * es <= (32u << 10) ? 1 : (n * es <= (256u << 10) ? 4 : 8);
+    int rc = mf_coll_launch(0, dtype, dtype, &a, ctas, 512, stream);
+    return rc == 0 ? MF_NOALLOC_OK : MF_NOALLOC_E_LAUNCH;
+}
+
+}  // extern "C"
