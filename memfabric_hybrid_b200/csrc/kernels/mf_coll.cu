@@ -101,8 +101,17 @@ template <typename T> __device__ __forceinline__ void cta_raw_copy(const T *src,
     uint64_t vend = beg;
     if (aligned16(src + beg) && aligned16(dst + beg)) {
         vend = beg + (end - beg) / VN * VN;
-        for (uint64_t i = beg + (uint64_t)threadIdx.x * VN; i < vend; i += (uint64_t)blockDim.x * VN)
-            *reinterpret_cast<uint4 *>(dst + i) = __ldcg(reinterpret_cast<const uint4 *>(src + i));
+        const uint64_t step = (uint64_t)blockDim.x * VN;
+        uint64_t i = beg + (uint64_t)threadIdx.x * VN;
+        // four independent 16-byte loads in flight per thread before the first store (NVLink latency)
+        for (; i + 3 * step < vend; i += 4 * step) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = __ldcg(reinterpret_cast<const uint4 *>(src + i + u * step));
+#pragma unroll
+            for (int u = 0; u < 4; u++) *reinterpret_cast<uint4 *>(dst + i + u * step) = v[u];
+        }
+        for (; i < vend; i += step) *reinterpret_cast<uint4 *>(dst + i) = __ldcg(reinterpret_cast<const uint4 *>(src + i));
     }
     for (uint64_t i = vend + threadIdx.x; i < end; i += blockDim.x) dst[i] = src[i];
 }

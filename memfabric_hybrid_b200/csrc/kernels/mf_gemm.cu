@@ -305,7 +305,23 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
             const uint32_t p = (me + g.team.world - i) % g.team.world;
             __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(peer_ptr(g.team, p, g.ag_buf_off)) + (int64_t)me * g.shard_rows * g.K;
             const int64_t nvec = (int64_t)(r1 - r0) * vec_per_row;
-            for (int64_t v = ct; v < nvec; v += kCopyWarps * 32) {
+            constexpr int kStep = kCopyWarps * 32;
+            int64_t v = ct;
+            // eight independent 16-byte loads in flight per thread, then eight peer stores
+            for (; v + 7 * kStep < nvec; v += 8 * kStep) {
+                uint4 val[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int64_t q = v + u * kStep;
+                    val[u] = __ldg(reinterpret_cast<const uint4 *>(g.x_local + (int64_t)(r0 + (int)(q / vec_per_row)) * g.ldx + (q % vec_per_row) * 8));
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const int64_t q = v + u * kStep;
+                    *reinterpret_cast<uint4 *>(dst + (int64_t)(r0 + (int)(q / vec_per_row)) * g.K + (q % vec_per_row) * 8) = val[u];
+                }
+            }
+            for (; v < nvec; v += kStep) {
                 const int rr = r0 + (int)(v / vec_per_row);
                 const int cc = (int)(v % vec_per_row) * 8;
                 const uint4 val = __ldg(reinterpret_cast<const uint4 *>(g.x_local + (int64_t)rr * g.ldx + cc));
@@ -351,14 +367,23 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
                 float accv[8];
 #pragma unroll
                 for (int e = 0; e < 8; e++) accv[e] = 0.f;
-                for (uint32_t s = 0; s < g.team.world; s++) {
-                    const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(land + ((int64_t)s * g.rows_per_rank + lr) * g.N + col));
-                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+                // partials are fetched eight at a time (independent loads in flight), added in rank order
+                for (uint32_t s0 = 0; s0 < g.team.world; s0 += 8) {
+                    uint4 raw[8];
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const float2 f = __bfloat1622float2(h[e]);
-                        accv[2 * e] += f.x;
-                        accv[2 * e + 1] += f.y;
+                    for (int u = 0; u < 8; u++)
+                        if (s0 + u < g.team.world)
+                            raw[u] = __ldcg(reinterpret_cast<const uint4 *>(land + ((int64_t)(s0 + u) * g.rows_per_rank + lr) * g.N + col));
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        if (s0 + u >= g.team.world) continue;
+                        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[u]);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float2 f = __bfloat1622float2(h[e]);
+                            accv[2 * e] += f.x;
+                            accv[2 * e + 1] += f.y;
+                        }
                     }
                 }
                 uint4 pk;

@@ -86,6 +86,7 @@ class Communicator:
         # two sets of (A, B): calls alternate so that no trailing synchronisation is needed
         self._sets = [(heap.alloc(self.stage_bytes), heap.alloc(self.stage_bytes)) for _ in range(2)]
         self._p2p_stage = None  # landing areas for send/recv, allocated on first use
+        self._p2p_bytes = 4 << 20
         self._epoch = 0
         self._p2p_epochs = {}
         sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
@@ -261,7 +262,6 @@ class Communicator:
     def _p2p(self, peer: int, sending: bool):
         assert not self.heap.emu, "send/recv need separate ranks"
         if self._p2p_stage is None:
-            self._p2p_bytes = 8 << 20
             # one landing area per possible sender, same layout on every rank
             self._p2p_stage = self.heap.alloc(self._p2p_bytes * self.world)
         src, dst = (self.rank, peer) if sending else (peer, self.rank)
@@ -275,7 +275,7 @@ class Communicator:
         nbytes = x.numel() * x.element_size()
         done = 0
         while done < nbytes:
-            cnt = min(8 << 20, nbytes - done)
+            cnt = min(self._p2p_bytes, nbytes - done)
             epoch, channel, stage = self._p2p(peer, True)
             args = P2PArgsC(self.heap.team(), x.data_ptr() + done, cnt, stage, peer, epoch, channel)
             _check(_cu().mf_coll_send(C.byref(args), min(self._ctas(cnt), 32), _stream()), "send")
@@ -285,7 +285,7 @@ class Communicator:
         nbytes = x.numel() * x.element_size()
         done = 0
         while done < nbytes:
-            cnt = min(8 << 20, nbytes - done)
+            cnt = min(self._p2p_bytes, nbytes - done)
             epoch, channel, stage = self._p2p(peer, False)
             args = P2PArgsC(self.heap.team(), x.data_ptr() + done, cnt, stage, peer, epoch, channel)
             _check(_cu().mf_coll_recv(C.byref(args), min(self._ctas(cnt), 32), _stream()), "recv")

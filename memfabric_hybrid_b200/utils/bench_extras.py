@@ -113,8 +113,13 @@ def tp_mlp(heap, world, flush):
     gemm.check_status()
     base = _timed(lambda: mlp.forward_baseline(x), 6, 3, flush)
     flops = 2.0 * S * H * (3 * F // world)
+    h = mlp.tp.ag_gemm(x, mlp.w_gate_up, swiglu=True)
+    ag = _timed(lambda: mlp.tp.ag_gemm(x, mlp.w_gate_up, swiglu=True), 6, 2, flush)
+    rs = _timed(lambda: mlp.tp.gemm_rs(h, mlp.w_down), 6, 2, flush)
+    gemm.check_status()
     return {"tokens": S, "hidden": H, "ffn": F, "fused_us": round(ms * 1e3, 1), "nccl_cublas_us": round(base * 1e3, 1),
-            "fused_tflops_per_gpu": round(flops / (ms * 1e-3) / 1e12, 1)}
+            "fused_tflops_per_gpu": round(flops / (ms * 1e-3) / 1e12, 1), "ag_gemm_swiglu_us": round(ag * 1e3, 1),
+            "gemm_rs_us": round(rs * 1e3, 1)}
 
 
 def run(rank, world, local, _bm_handle):

@@ -136,7 +136,7 @@ def _real_ranks(rank, world, url, sync):
     import torch
     from memfabric_hybrid_b200.ops.heap import SymmetricHeap
     from memfabric_hybrid_b200.ops.collectives import Communicator
-    heap = SymmetricHeap(url, world, rank, rank % torch.cuda.device_count(), 64 << 20)
+    heap = SymmetricHeap(url, world, rank, rank % torch.cuda.device_count(), 128 << 20)
     c = Communicator(heap, stage_bytes=8 << 20)
     def draw(r, n):
         return torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(1000 * r + n % 997)).to(torch.bfloat16)
