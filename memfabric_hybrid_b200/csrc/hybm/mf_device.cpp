@@ -271,6 +271,20 @@ DeviceBackend *AcquireBackend(int deviceId, std::string *why)
     return g_backend;
 }
 
+void *CudaSymbol(const char *name)
+{
+    std::lock_guard<std::mutex> g(g_mu);
+    if (g_cudaLib == nullptr) {
+        std::string path = EnvStr("MF_CUDA_BACKEND_LIB", nullptr, (SelfDir() + "/libmf_cuda.so").c_str());
+        g_cudaLib = dlopen(path.c_str(), RTLD_NOW | RTLD_GLOBAL);
+        if (g_cudaLib == nullptr) {
+            MF_WARN("cannot load %s: %s", path.c_str(), dlerror());
+            return nullptr;
+        }
+    }
+    return dlsym(g_cudaLib, name);
+}
+
 void ReleaseBackend()
 {
     std::lock_guard<std::mutex> g(g_mu);

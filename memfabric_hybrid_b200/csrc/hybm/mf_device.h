@@ -105,6 +105,9 @@ DeviceBackend *CreateFakeBackend();
 DeviceBackend *AcquireBackend(int deviceId, std::string *why = nullptr);
 DeviceBackend *CurrentBackend();
 void ReleaseBackend();
+// Address of an exported function of the CUDA library (kernel launchers), loading the library if it is not
+// loaded yet; nullptr when the library or the symbol is missing.
+void *CudaSymbol(const char *name);
 
 // Symbol exported by libmf_cuda.so.
 extern "C" typedef DeviceBackend *(*MfCreateCudaBackendFn)();

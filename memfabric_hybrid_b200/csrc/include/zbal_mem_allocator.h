@@ -1,0 +1,52 @@
+/*
+ * SMA, the allocator that hands out device memory from the symmetric heap so that tensors allocated in
+ * the same order on every rank sit at the same offset of every rank's slice. The zbal_pluggable_* pair
+ * has the signature PyTorch's pluggable CUDA allocator expects
+ * (parity: app/zbal/src/include/zbal_mem_allocator.h of the reference).
+ */
+#ifndef MF_B200_ZBAL_MEM_ALLOCATOR_H
+#define MF_B200_ZBAL_MEM_ALLOCATOR_H
+
+#include "zbal_def.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int32_t zbal_sma_init(zbal_allocator_options_t *options, int32_t flags);
+void zbal_sma_uninit(int32_t flags);
+
+void zbal_pluggable_init(int32_t device_count);
+void *zbal_pluggable_malloc(size_t size, int32_t device, zbal_stream_t stream);
+void zbal_pluggable_free(void *ptr, size_t size, int32_t device, zbal_stream_t stream);
+/* Returns every cached block to the heap. With check_error a block still in use is reported as an error. */
+void zbal_pluggable_empty_cache(bool check_error);
+
+/* Runs the allocator over a made-up address range with no device behind it (replay, tests). */
+void zbal_simulate_init(int64_t addr, int64_t size);
+
+typedef struct {
+    uint64_t heapSize;
+    uint64_t inUseBytes;       /* handed out to callers now */
+    uint64_t cachedBytes;      /* free blocks kept per stream for reuse */
+    uint64_t peakInUseBytes;
+    uint64_t largestFreeBlock; /* in the heap, caches not counted */
+    uint64_t mallocCalls;
+    uint64_t freeCalls;
+    uint64_t cacheHits;
+    uint64_t heapCarves;       /* mallocs that had to go to the heap */
+    uint64_t failedMallocs;
+} zbal_sma_stats_t;
+
+int32_t zbal_sma_get_stats(zbal_sma_stats_t *stats);
+void zbal_sma_reset_peak(void);
+/* History of malloc/free events (bounded ring) for the offline replay tool. Recording is off by default. */
+void zbal_sma_record_history(bool enable, uint32_t max_entries);
+/* Writes a JSON snapshot {"heap":…, "blocks":[…], "history":[…]} into buf; returns the bytes needed (call
+ * with buf == NULL to size the buffer). */
+int64_t zbal_sma_snapshot(char *buf, int64_t cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -32,7 +32,9 @@ struct CollArgs {
     uint32_t epoch;
     uint32_t zero_copy;        // input already sits at stage_a of every slot
     uint32_t root;
-    uint32_t algo;             // allreduce: 0 one-shot, 1 two-shot
+    uint32_t algo;             // allreduce: 0 one-shot, 1 two-shot; rooted copy: 0 broadcast, 1 scatter
+    uint64_t part_stride;      // elements between consecutive members' parts in the user buffer (0: packed):
+                               // reduce_scatter input rows, allgather output rows, scatter source parts
 };
 
 struct Range {
@@ -259,8 +261,9 @@ template <typename T, typename TO, bool INT, int W> __global__ void __launch_bou
     constexpr int VN = Vec<T>::N;
     const uint64_t m = a.n / world;
     const Range sub = cta_range<8>(m);
+    const uint64_t ps = a.part_stride ? a.part_stride : m;
     if (!a.zero_copy)
-        for (uint32_t c = 0; c < world; c++) cta_raw_copy<T>(in, myA, c * m + sub.beg, c * m + sub.end);
+        for (uint32_t c = 0; c < world; c++) cta_raw_copy<T>(in + c * ps, myA + c * m, sub.beg, sub.end);
     if (!lane_sync(t, me, 0, a.epoch, 0x120)) return;
     reduce_ranks<T, INT, W>(t, me, a.stage_a, (uint64_t)me * m, sub.beg, sub.end, a.op,
                             [&](uint64_t i, float *acc, int cnt) { emit<TO, INT>(out, i, acc, cnt, a.scale); });
@@ -283,7 +286,8 @@ template <typename T, typename TO> __global__ void __launch_bounds__(512) k_allg
     }
     if (!lane_sync(t, me, 0, a.epoch, 0x130)) return;
     const TO *myB = reinterpret_cast<const TO *>(peer_ptr(t, me, a.stage_b));
-    for (uint32_t c = 0; c < world; c++) cta_raw_copy<TO>(myB + (uint64_t)c * a.n, out + (uint64_t)c * a.n, sub.beg, sub.end);
+    const uint64_t ps = a.part_stride ? a.part_stride : a.n;
+    for (uint32_t c = 0; c < world; c++) cta_raw_copy<TO>(myB + (uint64_t)c * a.n, out + (uint64_t)c * ps, sub.beg, sub.end);
 }
 
 // broadcast of n elements from a.root
@@ -298,7 +302,9 @@ template <typename T> __global__ void __launch_bounds__(512) k_broadcast(CollArg
     if (me == a.root) {
         for (uint32_t k = 0; k < world; k++) {
             const uint32_t r = (me + k) % world;
-            cta_raw_copy<T>(in, reinterpret_cast<T *>(peer_ptr(t, r, a.stage_b)), sub.beg, sub.end);
+            // scatter mode: member r gets part r of the root's buffer
+            const T *src = a.algo == 1 ? in + (uint64_t)r * (a.part_stride ? a.part_stride : a.n) : in;
+            cta_raw_copy<T>(src, reinterpret_cast<T *>(peer_ptr(t, r, a.stage_b)), sub.beg, sub.end);
         }
     }
     if (!lane_sync(t, me, 0, a.epoch, 0x140)) return;

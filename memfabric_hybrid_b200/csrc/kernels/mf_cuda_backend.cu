@@ -399,3 +399,19 @@ private:
 }  // namespace mf
 
 extern "C" mf::hybm::DeviceBackend *mf_create_cuda_backend() { return new mf::hybm::CudaBackend(); }
+
+// Small runtime helpers for the host-only library, which does not link the CUDA runtime itself.
+extern "C" int mf_cuda_device_sync(int device)
+{
+    (void)device;  // one device per process: the current device is the one in use
+    return (int)cudaDeviceSynchronize();
+}
+extern "C" int mf_cuda_memset(void *ptr, int value, size_t bytes) { return (int)cudaMemset(ptr, value, bytes); }
+extern "C" int mf_cuda_copy_d2h(void *dst, const void *src, size_t bytes) { return (int)cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost); }
+extern "C" int mf_cuda_sm_count(void)
+{
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return sms;
+}

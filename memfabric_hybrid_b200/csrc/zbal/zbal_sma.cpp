@@ -1,0 +1,372 @@
+// SMA: the caching allocator that serves PyTorch (through its pluggable-allocator hooks) from the
+// symmetric heap.
+//
+//   malloc(size, stream): round the size (512 B steps below the small threshold, 2 MiB steps above), look
+//     for a cached block of that stream that fits without wasting more than `max_split`, else carve from
+//     the SplitMemoryHeap; when the heap is exhausted, wait for the device (hook), return every cached
+//     block of every stream to the heap and try once more.
+//   free(ptr, stream): the block goes to the cache of the stream it was allocated on. Work already queued
+//     on that stream may still touch it, and a later malloc on the SAME stream is ordered behind that
+//     work, so reuse needs no event. Blocks never move between streams without a device-wide wait.
+//
+// Because the policy depends only on the call sequence, ranks that allocate in lockstep get identical
+// offsets inside their slices (a symmetric tensor needs no address exchange).
+//
+// Configuration (environment ZBAL_ALLOC_CONF, "key:value,key:value" as in PyTorch's allocator settings):
+//   small_heap_threshold   bytes; requests below it grow from the low end (default 1 MiB)
+//   max_split_size_mb      a cached block may serve a request only if it wastes less than this (default 20)
+//   round_large_mb         rounding step of large requests (default 2)
+//   garbage_collection_threshold   fraction of the heap in use+cached above which free() of a large block
+//                          returns it to the heap at once instead of caching it (default 0 = off)
+//
+// Not provided: private pools for CUDA-graph capture (a capture that allocates must use PyTorch's native
+// allocator with a MemPool over zbal_pluggable_malloc, which keeps the pool's blocks alive itself).
+//
+// Parity of role: app/zbal/src/csrc/sma/zbal_sma_device.cpp, zbal_sma_config.h:20-102,
+// app/zbal/src/include/zbal_mem_allocator.h of the reference.
+#include <dlfcn.h>
+
+#include <deque>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <sstream>
+#include <unordered_map>
+
+#include "../include/zbal_mem_allocator.h"
+#include "../util/mf_util.h"
+#include "../hybm/mf_device.h"
+#include "zbal_sma_heap.h"
+
+namespace zbal {
+namespace {
+
+struct Config {
+    uint64_t smallThreshold = 1ull << 20;
+    uint64_t maxSplit = 20ull << 20;
+    uint64_t roundLarge = 2ull << 20;
+    double gcThreshold = 0.0;
+};
+
+Config ParseConf(uint64_t optThreshold)
+{
+    Config c;
+    if (optThreshold) c.smallThreshold = optThreshold;
+    const std::string s = mf::EnvStr("ZBAL_ALLOC_CONF", "ZBAL_NPU_ALLOC_CONF", "");
+    for (const auto &kv : mf::Split(s, ',')) {
+        const auto p = kv.find(':');
+        if (p == std::string::npos) continue;
+        const std::string k = kv.substr(0, p), v = kv.substr(p + 1);
+        uint64_t u = 0;
+        if (k == "small_heap_threshold" && mf::ParseU64(v, u) && u >= 4096) c.smallThreshold = u;
+        else if (k == "max_split_size_mb" && mf::ParseU64(v, u) && u >= 1) c.maxSplit = u << 20;
+        else if (k == "round_large_mb" && mf::ParseU64(v, u) && u >= 1 && u <= 1024) c.roundLarge = u << 20;
+        else if (k == "garbage_collection_threshold") c.gcThreshold = atof(v.c_str());
+        else MF_WARN("ZBAL_ALLOC_CONF: ignoring '%s'", kv.c_str());
+    }
+    return c;
+}
+
+struct HistoryEntry {
+    uint8_t kind;  // 0 malloc from heap, 1 malloc from cache, 2 free to cache, 3 free to heap, 4 empty_cache, 5 failed malloc
+    uint64_t addr, size, requested, stream;
+};
+
+class Sma {
+public:
+    Sma(uint64_t base, uint64_t size, const Config &cfg, int device, bool simulated)
+        : heap_(base, size, cfg.smallThreshold), cfg_(cfg), device_(device), simulated_(simulated)
+    {
+    }
+
+    uint64_t Round(uint64_t size) const
+    {
+        if (size == 0) size = 1;
+        if (size < cfg_.smallThreshold) return mf::AlignUp(size, SplitMemoryHeap::kMinBlock);
+        return mf::AlignUp(size, cfg_.roundLarge);
+    }
+
+    void *Malloc(uint64_t requested, uint64_t stream)
+    {
+        const uint64_t size = Round(requested);
+        std::lock_guard<std::mutex> g(mu_);
+        st_.mallocCalls++;
+        auto &cache = cache_[stream];
+        auto it = cache.lower_bound(size);
+        if (it != cache.end()) {
+            // small classes are multiples of 512 B and must match exactly; a large cached block may serve a
+            // request up to 25 % smaller, as long as the waste stays under max_split
+            const uint64_t waste = it->first - size;
+            const bool hit = size < cfg_.smallThreshold ? waste == 0 : (waste < cfg_.maxSplit && waste <= it->first / 4);
+            if (hit) {
+                const uint64_t addr = it->second, bsz = it->first;
+                cache.erase(it);
+                cached_ -= bsz;
+                Hand(addr, bsz, stream);
+                st_.cacheHits++;
+                Note(1, addr, bsz, requested, stream);
+                return reinterpret_cast<void *>(addr);
+            }
+        }
+        uint64_t addr = heap_.AlignedAllocate(size, size < cfg_.smallThreshold ? 512 : 4096);
+        if (addr == 0 && cached_ > 0) {
+            DeviceWait();
+            FlushLocked();
+            addr = heap_.AlignedAllocate(size, size < cfg_.smallThreshold ? 512 : 4096);
+        }
+        if (addr == 0) {
+            st_.failedMallocs++;
+            Note(5, 0, size, requested, stream);
+            mf::LastError::Set(Z_NO_MEMORY, "symmetric heap exhausted: %lu bytes requested, %lu in use of %lu, largest free block %lu",
+                               (unsigned long)size, (unsigned long)inUse_, (unsigned long)heap_.TotalSize(),
+                               (unsigned long)heap_.LargestFree());
+            return nullptr;
+        }
+        st_.heapCarves++;
+        Hand(addr, size, stream);
+        Note(0, addr, size, requested, stream);
+        return reinterpret_cast<void *>(addr);
+    }
+
+    bool Free(void *ptr)
+    {
+        const uint64_t addr = reinterpret_cast<uint64_t>(ptr);
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = live_.find(addr);
+        if (it == live_.end()) return false;
+        const uint64_t size = it->second.first, stream = it->second.second;
+        live_.erase(it);
+        inUse_ -= size;
+        st_.freeCalls++;
+        const bool gc = cfg_.gcThreshold > 0.0 && size >= cfg_.smallThreshold &&
+                        (double)(inUse_ + cached_ + size) > cfg_.gcThreshold * (double)heap_.TotalSize();
+        if (gc) {
+            // the block may still be in use by queued work: wait before it can be carved for another stream
+            DeviceWait();
+            heap_.Release(addr);
+            Note(3, addr, size, 0, stream);
+        } else {
+            cache_[stream].emplace(size, addr);
+            cached_ += size;
+            Note(2, addr, size, 0, stream);
+        }
+        return true;
+    }
+
+    void EmptyCache(bool checkError)
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        DeviceWait();
+        FlushLocked();
+        Note(4, 0, 0, 0, 0);
+        if (checkError && !live_.empty())
+            mf::LastError::Set(Z_ERROR, "empty_cache: %zu blocks (%lu bytes) are still in use", live_.size(), (unsigned long)inUse_);
+    }
+
+    void Stats(zbal_sma_stats_t &o)
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        o = st_;
+        o.heapSize = heap_.TotalSize();
+        o.inUseBytes = inUse_;
+        o.cachedBytes = cached_;
+        o.peakInUseBytes = peak_;
+        o.largestFreeBlock = heap_.LargestFree();
+    }
+    void ResetPeak()
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        peak_ = inUse_;
+    }
+    void Record(bool on, uint32_t maxEntries)
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        record_ = on;
+        maxHistory_ = maxEntries ? maxEntries : 65536;
+        if (!on) history_.clear();
+    }
+
+    std::string Snapshot()
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        std::ostringstream o;
+        o << "{\"heap\":{\"base\":" << heap_.Base() << ",\"size\":" << heap_.TotalSize() << ",\"threshold\":" << heap_.Threshold()
+          << ",\"round_large\":" << cfg_.roundLarge << ",\"max_split\":" << cfg_.maxSplit << ",\"device\":" << device_
+          << ",\"simulated\":" << (simulated_ ? "true" : "false") << ",\"in_use\":" << inUse_ << ",\"cached\":" << cached_
+          << ",\"peak\":" << peak_ << "},\"blocks\":[";
+        bool first = true;
+        for (const auto &b : heap_.Blocks()) {
+            const char *state = "free";
+            uint64_t stream = 0;
+            if (b.used) {
+                auto it = live_.find(b.addr);
+                state = it != live_.end() ? "active" : "cached";
+                if (it != live_.end()) stream = it->second.second;
+            }
+            o << (first ? "" : ",") << "{\"addr\":" << b.addr << ",\"size\":" << b.size << ",\"state\":\"" << state << "\",\"stream\":" << stream
+              << "}";
+            first = false;
+        }
+        o << "],\"history\":[";
+        first = true;
+        static const char *kinds[] = {"malloc_heap", "malloc_cache", "free_cache", "free_heap", "empty_cache", "malloc_failed"};
+        for (const auto &h : history_) {
+            o << (first ? "" : ",") << "{\"op\":\"" << kinds[h.kind] << "\",\"addr\":" << h.addr << ",\"size\":" << h.size
+              << ",\"requested\":" << h.requested << ",\"stream\":" << h.stream << "}";
+            first = false;
+        }
+        o << "]}";
+        return o.str();
+    }
+
+    bool Owns(uint64_t addr) const { return addr >= heap_.Base() && addr < heap_.Base() + heap_.TotalSize(); }
+
+private:
+    void Hand(uint64_t addr, uint64_t size, uint64_t stream)
+    {
+        live_[addr] = {size, stream};
+        inUse_ += size;
+        if (inUse_ > peak_) peak_ = inUse_;
+    }
+    void FlushLocked()
+    {
+        for (auto &s : cache_)
+            for (auto &kv : s.second) heap_.Release(kv.second);
+        cache_.clear();
+        cached_ = 0;
+    }
+    void Note(uint8_t kind, uint64_t addr, uint64_t size, uint64_t requested, uint64_t stream)
+    {
+        if (!record_) return;
+        if (history_.size() >= maxHistory_) history_.pop_front();
+        history_.push_back({kind, addr, size, requested, stream});
+    }
+    void DeviceWait()
+    {
+        if (simulated_) return;
+        // exported by the CUDA library once it is loaded; without it there is no device work to wait for
+        using Fn = int (*)(int);
+        static Fn fn = reinterpret_cast<Fn>(mf::hybm::CudaSymbol("mf_cuda_device_sync"));
+        if (fn != nullptr) fn(device_);
+    }
+
+    SplitMemoryHeap heap_;
+    const Config cfg_;
+    const int device_;
+    const bool simulated_;
+    std::mutex mu_;
+    std::unordered_map<uint64_t, std::multimap<uint64_t, uint64_t>> cache_;  // stream -> size -> addr
+    std::unordered_map<uint64_t, std::pair<uint64_t, uint64_t>> live_;      // addr -> (size, stream)
+    uint64_t inUse_ = 0, cached_ = 0, peak_ = 0;
+    zbal_sma_stats_t st_{};
+    bool record_ = false;
+    size_t maxHistory_ = 65536;
+    std::deque<HistoryEntry> history_;
+};
+
+std::mutex g_mu;
+std::shared_ptr<Sma> g_sma;
+
+std::shared_ptr<Sma> Get()
+{
+    std::lock_guard<std::mutex> g(g_mu);
+    return g_sma;
+}
+
+}  // namespace
+}  // namespace zbal
+
+using namespace zbal;
+
+extern "C" {
+
+int32_t zbal_sma_init(zbal_allocator_options_t *options, int32_t flags)
+{
+    (void)flags;
+    if (options == nullptr || options->size < (1ull << 20) || options->baseAddress == 0)
+        return MF_FAIL(Z_INVALID_PARAM, "zbal_sma_init: need a base address and at least 1 MiB");
+    std::lock_guard<std::mutex> g(g_mu);
+    if (g_sma) return MF_FAIL(Z_ALREADY_INITIALIZED, "zbal_sma_init: allocator already initialised");
+    g_sma = std::make_shared<Sma>(options->baseAddress, options->size, ParseConf(options->smallThreshold), options->deviceId, false);
+    return Z_OK;
+}
+
+void zbal_sma_uninit(int32_t flags)
+{
+    (void)flags;
+    std::lock_guard<std::mutex> g(g_mu);
+    g_sma.reset();
+}
+
+void zbal_simulate_init(int64_t addr, int64_t size)
+{
+    std::lock_guard<std::mutex> g(g_mu);
+    g_sma = std::make_shared<Sma>((uint64_t)addr, (uint64_t)size, ParseConf(0), 0, true);
+}
+
+void zbal_pluggable_init(int32_t device_count)
+{
+    (void)device_count;  // one device per process: nothing to size
+}
+
+void *zbal_pluggable_malloc(size_t size, int32_t device, zbal_stream_t stream)
+{
+    (void)device;
+    auto s = Get();
+    if (!s) {
+        mf::LastError::Set(Z_NOT_INITIALIZED, "zbal_pluggable_malloc before zbal_sma_init");
+        return nullptr;
+    }
+    return s->Malloc(size, reinterpret_cast<uint64_t>(stream));
+}
+
+void zbal_pluggable_free(void *ptr, size_t size, int32_t device, zbal_stream_t stream)
+{
+    (void)size;
+    (void)device;
+    (void)stream;
+    auto s = Get();
+    if (!s || ptr == nullptr) return;
+    if (!s->Free(ptr)) MF_WARN("zbal_pluggable_free: %p was not allocated by this allocator", ptr);
+}
+
+void zbal_pluggable_empty_cache(bool check_error)
+{
+    auto s = Get();
+    if (s) s->EmptyCache(check_error);
+}
+
+int32_t zbal_sma_get_stats(zbal_sma_stats_t *stats)
+{
+    auto s = Get();
+    if (!s || stats == nullptr) return Z_NOT_INITIALIZED;
+    s->Stats(*stats);
+    return Z_OK;
+}
+
+void zbal_sma_reset_peak(void)
+{
+    auto s = Get();
+    if (s) s->ResetPeak();
+}
+
+void zbal_sma_record_history(bool enable, uint32_t max_entries)
+{
+    auto s = Get();
+    if (s) s->Record(enable, max_entries);
+}
+
+int64_t zbal_sma_snapshot(char *buf, int64_t cap)
+{
+    auto s = Get();
+    if (!s) return Z_NOT_INITIALIZED;
+    const std::string j = s->Snapshot();
+    if (buf != nullptr && cap > 0) {
+        const size_t n = std::min<size_t>(j.size(), (size_t)cap - 1);
+        memcpy(buf, j.data(), n);
+        buf[n] = 0;
+    }
+    return (int64_t)j.size() + 1;
+}
+
+}  // extern "C"

@@ -29,7 +29,7 @@ class CollArgsC(C.Structure):
     _fields_ = [("team", TeamC), ("inp", C.c_uint64), ("out", C.c_uint64), ("in_rank_stride", C.c_uint64),
                 ("out_rank_stride", C.c_uint64), ("n", C.c_uint64), ("stage_a", C.c_uint64), ("stage_b", C.c_uint64),
                 ("scale", C.c_float), ("op", C.c_int), ("epoch", C.c_uint32), ("zero_copy", C.c_uint32),
-                ("root", C.c_uint32), ("algo", C.c_uint32)]
+                ("root", C.c_uint32), ("algo", C.c_uint32), ("part_stride", C.c_uint64)]
 
 
 class A2AArgsC(C.Structure):
@@ -125,7 +125,7 @@ class Communicator:
     def _args(self, x, out, n, epoch, stage, scale=1.0, op="sum", root=0, algo=0) -> CollArgsC:
         xin, xs, _ = self._local(x)
         xo, os_, _ = self._local(out)
-        return CollArgsC(self.heap.team(), xin, xo, xs, os_, n, stage[0], stage[1], float(scale), OPS[op], epoch, 0, root, algo)
+        return CollArgsC(self.heap.team(), xin, xo, xs, os_, n, stage[0], stage[1], float(scale), OPS[op], epoch, 0, root, algo, 0)
 
     def _empty_like(self, x: torch.Tensor, per_rank_numel: int, dtype: torch.dtype) -> torch.Tensor:
         if self.heap.emu:

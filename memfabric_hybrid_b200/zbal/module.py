@@ -1,0 +1,195 @@
+"""zbal life cycle and allocator control.
+
+    zbal_init(world_size, device_id, rank_id, device_mem_size, ip_port="127.0.0.1:7000", start_config_server=True)
+    with switch_to_allocator():           # tensors created here live in the symmetric heap
+        x = torch.empty(...)
+    zbal_uninit()
+
+Parity: app/zbal/src/python/zbal/zbal_module.py:19-161 of the reference. Differences: the allocator switch
+is a scoped ``torch.cuda.MemPool`` by default (PyTorch's native caching allocator asks zbal for its
+segments), because a CUDA process can swap its global allocator only before the first allocation;
+``switch_to_allocator(globally=True)`` does that swap and must be called first thing.
+"""
+from __future__ import annotations
+
+import contextlib
+import ctypes as C
+import enum
+import json
+import os
+
+import torch
+
+from .. import _native as N
+from . import _capi as K
+
+__version__ = "1.0.0"
+
+
+class ZBALBootstrapType(enum.IntEnum):
+    BOOT_BY_MEMFABRIC = 0
+
+
+_state = {"output": None, "allocator": None, "pool": None}
+
+
+def zbal_set_logger_level(level: int) -> int:
+    return K.lib().zbal_set_logger_level(level)
+
+
+def is_initialized() -> bool:
+    return bool(K.lib().zbal_is_bootstrapped())
+
+
+def zbal_init(world_size: int, device_id: int, rank_id: int, device_mem_size: int,
+              bootstrap_type: ZBALBootstrapType = ZBALBootstrapType.BOOT_BY_MEMFABRIC, start_config_server: bool = False,
+              data_op_type: int = 0, comm_meta_space_size: int = 0, comm_group_cap: int = 16, flags: int = 0, ip_port: str = "") -> bool:
+    """Collective over all ranks. ``comm_meta_space_size`` is in KiB per communicator (0 = derive from the slice).
+    ``ip_port`` defaults to $ZBAL_IP_PORT or MASTER_ADDR:(MASTER_PORT + 7); rank 0 hosts the store when
+    ``start_config_server`` is set or no address was given. Returns True on success."""
+    l = K.lib()
+    if torch.cuda.is_available():
+        N.cuda()  # kernels and the CUDA device backend
+        torch.cuda.set_device(device_id)
+        torch.zeros(1, device="cuda")  # a context must exist before the VMM calls
+    auto = False
+    if not ip_port:
+        ip_port = os.environ.get("ZBAL_IP_PORT", "")
+    if not ip_port:
+        ip_port = f"{os.environ.get('MASTER_ADDR', '127.0.0.1')}:{int(os.environ.get('MASTER_PORT', '29500')) + 7}"
+        auto = True
+    if "://" not in ip_port:
+        ip_port = "tcp://" + ip_port
+    o = K.BootstrapOptionsC()
+    l.zbal_bootstrap_options_init(C.byref(o))
+    o.flags = flags
+    o.btType = int(bootstrap_type)
+    o.ipPort = ip_port.encode()
+    o.worldSize, o.rankId, o.deviceId = world_size, rank_id, device_id
+    o.startConfigServer = bool(start_config_server or auto)
+    o.deviceMemorySize = device_mem_size
+    o.dataOperationType = data_op_type
+    o.commMetaSpaceSize = comm_meta_space_size << 10
+    o.commGroupCap = comm_group_cap
+    out = K.BootstrapOutputC()
+    rc = l.zbal_bootstrap(C.byref(o), C.byref(out))
+    if rc != K.Z_OK:
+        raise K.ZbalError("zbal_bootstrap", rc)
+    _state["output"] = out
+    return True
+
+
+def zbal_uninit(flags: int = 0) -> bool:
+    l = K.lib()
+    if not l.zbal_is_bootstrapped():
+        return False
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    from . import process_group
+    process_group._forget_all()
+    _state["pool"] = None
+    l.zbal_comm_destroy_all(flags)
+    l.zbal_unbootstrap(flags)
+    _state["output"] = None
+    return True
+
+
+def bootstrap_output() -> K.BootstrapOutputC:
+    out = K.BootstrapOutputC()
+    K.check(K.lib().zbal_bootstrap_get_output(C.byref(out)), "zbal_bootstrap_get_output")
+    return out
+
+
+def zbal_get_symm_base_addr() -> int:
+    """Start of this rank's allocator heap (device address)."""
+    return int(bootstrap_output().heapGva)
+
+
+def _pluggable():
+    if _state["allocator"] is None:
+        path = str(N._LIB_DIR / "libmf_smem.so")
+        K.lib()
+        _state["allocator"] = torch.cuda.memory.CUDAPluggableAllocator(path, "zbal_pluggable_malloc", "zbal_pluggable_free")
+    return _state["allocator"]
+
+
+def switch_to_allocator(globally: bool = False):
+    """Routes tensor allocations to the symmetric heap.
+
+    Default: returns a context manager; allocations made inside come from a ``torch.cuda.MemPool`` whose
+    segments zbal provides. ``globally=True`` replaces the process-wide allocator instead (only possible
+    before the first CUDA allocation of the process) and returns None."""
+    alloc = _pluggable()
+    if globally:
+        torch.cuda.memory.change_current_allocator(alloc)
+        return None
+    if _state["pool"] is None:
+        _state["pool"] = torch.cuda.MemPool(alloc.allocator())
+    return torch.cuda.use_mem_pool(_state["pool"])
+
+
+@contextlib.contextmanager
+def symmetric_tensors():
+    """Alias of ``switch_to_allocator()`` that reads better at call sites."""
+    with switch_to_allocator():
+        yield
+
+
+def in_symmetric_heap(t: torch.Tensor) -> bool:
+    out = _state["output"]
+    if out is None or not t.is_cuda:
+        return False
+    p = t.data_ptr()
+    return out.heapGva <= p < out.heapGva + out.heapSize
+
+
+def get_heap_stats():
+    """(bytes in use, heap size)."""
+    s = K.SmaStatsC()
+    K.check(K.lib().zbal_sma_get_stats(C.byref(s)), "zbal_sma_get_stats")
+    return int(s.inUseBytes), int(s.heapSize)
+
+
+def heap_stats() -> dict:
+    s = K.SmaStatsC()
+    K.check(K.lib().zbal_sma_get_stats(C.byref(s)), "zbal_sma_get_stats")
+    return {n: int(getattr(s, n)) for n, _ in K.SmaStatsC._fields_}
+
+
+def mem_get_info():
+    """(free, total) of the symmetric heap, the shape of ``torch.cuda.mem_get_info``."""
+    used, total = get_heap_stats()
+    return total - used, total
+
+
+def empty_cache(check_error: bool = False) -> None:
+    K.lib().zbal_pluggable_empty_cache(check_error)
+
+
+def record_memory_history(enabled: bool = True, max_entries: int = 65536) -> None:
+    K.lib().zbal_sma_record_history(enabled, max_entries)
+
+
+def snapshot() -> dict:
+    l = K.lib()
+    need = l.zbal_sma_snapshot(None, 0)
+    if need <= 0:
+        raise K.ZbalError("zbal_sma_snapshot", int(need))
+    buf = C.create_string_buffer(int(need) + 64)
+    l.zbal_sma_snapshot(buf, len(buf))
+    return json.loads(buf.value.decode())
+
+
+def dump_snapshot(path: str) -> None:
+    with open(path, "w") as f:
+        json.dump(snapshot(), f)
+
+
+def simulate_init(addr: int, size: int) -> None:
+    """Runs the allocator over a made-up address range (no device): for replaying traces offline."""
+    K.lib().zbal_simulate_init(addr, size)
+
+
+def is_mix_alloc() -> bool:
+    """True when a symmetric pool is in use next to PyTorch's own allocator."""
+    return _state["pool"] is not None
