@@ -12,6 +12,7 @@
 //                  slots (the push itself happens in the epilogue of the down-projection GEMM)
 // Parity of role: app/zbal/src/csrc/operators/npu/aicore/ops/dispatch_combine_normal/
 // zbal_kernel_{dispatch_layout,notify_dispatch,dispatch_normal,combine_normal}.h of the reference.
+#include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -89,8 +90,9 @@ __global__ void k_moe_layout_rank(const int *__restrict__ topk_idx, int T, int K
 
 // ---- notify ---------------------------------------------------------------------------------------
 // outputs (device, local): recv_per_expert[El], row_off[El + 1], put_off[E], src_off[El][W]
-__global__ void __launch_bounds__(1024) k_moe_notify(Team team, MoeHeap hp, int E, const int *tokens_per_expert, int *recv_per_expert,
-                                                     int *row_off, int *put_off, int *src_off, uint32_t epoch)
+// All threads of ONE CTA call it. Returns false (uniformly) when the count exchange timed out.
+__device__ __forceinline__ bool notify_body(const Team &team, const MoeHeap &hp, int E, const int *tokens_per_expert, int *recv_per_expert,
+                                            int *row_off, int *put_off, int *src_off, uint32_t epoch)
 {
     const uint32_t me = team_rank(team);
     const uint32_t W = team.world;
@@ -103,7 +105,7 @@ __global__ void __launch_bounds__(1024) k_moe_notify(Team team, MoeHeap hp, int 
             reinterpret_cast<int *>(peer_ptr(team, r, hp.counts))[me * E + e] = c;
         }
     }
-    if (!team_barrier(team, me, 8, epoch)) return;
+    if (!team_barrier(team, me, 8, epoch)) return false;
     const int *tbl = reinterpret_cast<const int *>(peer_ptr(team, me, hp.counts));
     __shared__ int per_expert[1024];  // totals of every expert over all sources
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -137,6 +139,13 @@ __global__ void __launch_bounds__(1024) k_moe_notify(Team team, MoeHeap hp, int 
         for (uint32_t r = 0; r < me; r++) off += __ldcg(tbl + r * E + e);
         put_off[e] = off;
     }
+    return true;
+}
+
+__global__ void __launch_bounds__(1024) k_moe_notify(Team team, MoeHeap hp, int E, const int *tokens_per_expert, int *recv_per_expert,
+                                                     int *row_off, int *put_off, int *src_off, uint32_t epoch)
+{
+    notify_body(team, hp, E, tokens_per_expert, recv_per_expert, row_off, put_off, src_off, epoch);
 }
 
 // ---- dispatch -------------------------------------------------------------------------------------
@@ -154,9 +163,10 @@ struct DispatchArgs {
     uint32_t epoch;
     uint32_t seq;
     int *status;
+    int raw_bf16;               // 1: rows travel as bf16 (receive rows are 2 H bytes, no scales)
 };
 
-__global__ void __launch_bounds__(448) k_moe_dispatch(DispatchArgs a)
+__device__ __forceinline__ void dispatch_body(const DispatchArgs &a)
 {
     const Team &t = a.team;
     const uint32_t me = team_rank(t);
@@ -182,6 +192,7 @@ __global__ void __launch_bounds__(448) k_moe_dispatch(DispatchArgs a)
         }
         __syncthreads();
         uint4 q;
+        uint4 raw_lo = make_uint4(0, 0, 0, 0), raw_hi = make_uint4(0, 0, 0, 0);
         float scale;
         {
             float f[16];
@@ -190,6 +201,8 @@ __global__ void __launch_bounds__(448) k_moe_dispatch(DispatchArgs a)
             if (vec < vecs) {
                 const uint4 *src = reinterpret_cast<const uint4 *>(a.x + (int64_t)tok * H + vec * 16);
                 const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+                raw_lo = lo;
+                raw_hi = hi;
                 const __nv_bfloat162 *h0 = reinterpret_cast<const __nv_bfloat162 *>(&lo);
                 const __nv_bfloat162 *h1 = reinterpret_cast<const __nv_bfloat162 *>(&hi);
 #pragma unroll
@@ -227,10 +240,16 @@ __global__ void __launch_bounds__(448) k_moe_dispatch(DispatchArgs a)
             if (d < 0) continue;
             const int64_t pos = dst_pos[k];
             if (vec < vecs) {
-                uint8_t *row = peer_ptr(t, d, a.hp.recv_x) + pos * H;
-                *reinterpret_cast<uint4 *>(row + vec * 16) = q;
-                if ((vec & 7) == 0)
-                    reinterpret_cast<float *>(peer_ptr(t, d, a.hp.recv_scale))[pos * groups + (vec >> 3)] = scale;
+                if (a.raw_bf16) {
+                    uint4 *row = reinterpret_cast<uint4 *>(peer_ptr(t, d, a.hp.recv_x) + pos * H * 2 + vec * 32);
+                    row[0] = raw_lo;
+                    row[1] = raw_hi;
+                } else {
+                    uint8_t *row = peer_ptr(t, d, a.hp.recv_x) + pos * H;
+                    *reinterpret_cast<uint4 *>(row + vec * 16) = q;
+                    if ((vec & 7) == 0)
+                        reinterpret_cast<float *>(peer_ptr(t, d, a.hp.recv_scale))[pos * groups + (vec >> 3)] = scale;
+                }
             }
             if (threadIdx.x == 0) {
                 int4 info = make_int4((int)me, tok, k, __float_as_int(dst_w[k]));
@@ -251,6 +270,8 @@ __global__ void __launch_bounds__(448) k_moe_dispatch(DispatchArgs a)
         }
     }
 }
+
+__global__ void __launch_bounds__(448) k_moe_dispatch(DispatchArgs a) { dispatch_body(a); }
 
 // Waits until every rank raised flag row `which` (0 dispatch, 1 combine) to `epoch`.
 __global__ void k_moe_wait_all(Team t, MoeHeap hp, int which, uint32_t epoch, int *status)
@@ -277,32 +298,11 @@ __global__ void k_moe_signal_all(Team t, MoeHeap hp, int which, uint32_t epoch)
 
 // out[t, :] = sum over the valid k slots of comb[t * K + k, :]; the rows were already multiplied by the
 // routing weights when they were pushed.
+__device__ __forceinline__ void combine_reduce_body(const Team &t, const MoeHeap &hp, const MoeShape &sh, const int *topk_idx, __nv_bfloat16 *out,
+                                                    const float *topk_w);
 __global__ void __launch_bounds__(256) k_moe_combine_reduce(Team t, MoeHeap hp, MoeShape sh, const int *topk_idx, __nv_bfloat16 *out)
 {
-    const uint32_t me = team_rank(t);
-    const __nv_bfloat16 *comb = reinterpret_cast<const __nv_bfloat16 *>(peer_ptr(t, me, hp.comb));
-    const int vecs = sh.H / 8;
-    for (int tok = blockIdx.x; tok < sh.T; tok += gridDim.x) {
-        for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int k = 0; k < sh.K; k++) {
-                if (topk_idx[tok * sh.K + k] < 0) continue;
-                const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(comb + ((int64_t)tok * sh.K + k) * sh.H) + v);
-                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
-#pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float2 f = __bfloat1622float2(h[e]);
-                    acc[2 * e] += f.x;
-                    acc[2 * e + 1] += f.y;
-                }
-            }
-            uint4 pk;
-            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
-#pragma unroll
-            for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-            *(reinterpret_cast<uint4 *>(out + (int64_t)tok * sh.H) + v) = pk;
-        }
-    }
+    combine_reduce_body(t, hp, sh, topk_idx, out, nullptr);
 }
 
 // Rows of bf16 -> fp8 e4m3 with one scale per 128 elements (the activation format of the expert GEMMs).
@@ -331,6 +331,160 @@ __global__ void __launch_bounds__(256) k_quant_rows_fp8(const __nv_bfloat16 *__r
         reinterpret_cast<uint32_t *>(q + r * cols + gi * kQuantGroup)[lane] = w;
         if (lane == 0) scales[r * groups + gi] = amax > 0.f ? amax / 448.f : 1.f;
     }
+}
+
+// ---- standalone combine (push) ---------------------------------------------------------------------
+// Expert outputs y[r, :] (bf16, local, row r of the receive layout) go back to the token's home rank:
+// slot (token, k) of its combine area, multiplied by the routing weight that travelled with the row
+// (weighted != 0) or as they are. The number of valid rows is read from the device.
+struct CombinePushArgs {
+    Team team;
+    MoeHeap hp;
+    const __nv_bfloat16 *y;
+    int64_t ldy;
+    const int *rows_dev;
+    int H, K, weighted;
+};
+
+__device__ __forceinline__ void combine_push_body(const CombinePushArgs &a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const int rows = *a.rows_dev;
+    const int vecs = a.H / 8;
+    const int4 *info = reinterpret_cast<const int4 *>(peer_ptr(t, me, a.hp.recv_info));
+    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+        const int4 in = __ldcg(info + r);
+        const uint32_t home = (uint32_t)in.x;
+        if (home >= t.world) continue;
+        const float w = a.weighted ? __int_as_float(in.w) : 1.f;
+        __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(peer_ptr(t, home, a.hp.comb)) + ((int64_t)in.y * a.K + in.z) * a.H;
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.y + (int64_t)r * a.ldy);
+        for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+            uint4 raw = __ldg(src + v);
+            if (w != 1.f) {
+                __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    float2 f = __bfloat1622float2(h[e]);
+                    h[e] = __floats2bfloat162_rn(f.x * w, f.y * w);
+                }
+            }
+            *(reinterpret_cast<uint4 *>(dst) + v) = raw;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) k_moe_combine_push(CombinePushArgs a) { combine_push_body(a); }
+
+// topk_w: optional [T, K] weights applied here (rows that were pushed unweighted); NULL = plain sum
+__device__ __forceinline__ void combine_reduce_body(const Team &t, const MoeHeap &hp, const MoeShape &sh, const int *topk_idx, __nv_bfloat16 *out,
+                                                    const float *topk_w)
+{
+    const uint32_t me = team_rank(t);
+    const __nv_bfloat16 *comb = reinterpret_cast<const __nv_bfloat16 *>(peer_ptr(t, me, hp.comb));
+    const int vecs = sh.H / 8;
+    for (int tok = blockIdx.x; tok < sh.T; tok += gridDim.x) {
+        for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int k = 0; k < sh.K; k++) {
+                if (topk_idx[tok * sh.K + k] < 0) continue;
+                const float wk = topk_w != nullptr ? topk_w[tok * sh.K + k] : 1.f;
+                const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(comb + ((int64_t)tok * sh.K + k) * sh.H) + v);
+                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __bfloat1622float2(h[e]);
+                    acc[2 * e] += f.x * wk;
+                    acc[2 * e + 1] += f.y * wk;
+                }
+            }
+            uint4 pk;
+            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+            *(reinterpret_cast<uint4 *>(out + (int64_t)tok * sh.H) + v) = pk;
+        }
+    }
+}
+
+// ---- low-latency pair (decode) -----------------------------------------------------------------------
+// One cooperative launch per direction instead of six: the launches, not the bytes, dominate at 128
+// tokens. Dispatch: CTA 0 builds the layout (shared-memory histogram; the order of rows inside an expert
+// group is the order in which the atomics land) and runs the count exchange, the grid then pushes the
+// tokens and CTA 0 waits for every peer's rows. Combine: the grid pushes the expert outputs home, CTA 0
+// signals and waits for all peers, the grid reduces the K slots of each token.
+// A wait that runs out is recorded in the status word; the kernel still reaches every grid-wide
+// synchronisation and returns (the results of that call are then unspecified).
+struct LLDispatchArgs {
+    DispatchArgs d;          // d.send_idx and d.put_off are OUTPUTS here (device scratch of T*K and E ints)
+    int *tokens_per_expert;  // [E] scratch
+    int *recv_per_expert;    // [El]
+    int *row_off;            // [El + 1]
+    int *src_off;            // [El * W]
+};
+
+__global__ void __launch_bounds__(448) k_moe_ll_dispatch(LLDispatchArgs a)
+{
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    const Team &t = a.d.team;
+    const uint32_t me = team_rank(t);
+    const int E = a.d.sh.E, n = a.d.sh.T * a.d.sh.K;
+    __shared__ int cnt[1024];
+    if (blockIdx.x == 0) {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
+        __syncthreads();
+        int *send_idx = const_cast<int *>(a.d.send_idx);
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const int e = a.d.topk_idx[i];
+            send_idx[i] = (e >= 0 && e < E) ? atomicAdd(&cnt[e], 1) : 0;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < E; e += blockDim.x) a.tokens_per_expert[e] = cnt[e];
+        __syncthreads();
+        if (!notify_body(t, a.d.hp, E, a.tokens_per_expert, a.recv_per_expert, a.row_off, const_cast<int *>(a.d.put_off), a.src_off, a.d.epoch))
+            if (threadIdx.x == 0) atomicCAS(a.d.status, 0, 0x420);
+        __threadfence();
+    }
+    grid.sync();
+    dispatch_body(a.d);
+    if (blockIdx.x == 0 && threadIdx.x < t.world) {
+        const uint32_t *f = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, a.d.hp.flags)) + threadIdx.x;
+        if (!wait_flag(f, a.d.epoch, t.spin_limit)) {
+            report_timeout(t, me, 0x421, a.d.epoch);
+            atomicCAS(a.d.status, 0, 0x421);
+        }
+    }
+}
+
+struct LLCombineArgs {
+    CombinePushArgs p;
+    MoeShape sh;
+    const int *topk_idx;   // [T, K] of this rank's own tokens
+    __nv_bfloat16 *out;    // [T, H]
+    uint32_t epoch;
+    int *status;
+    const float *topk_w;   // optional [T, K]: weights applied on the home side
+};
+
+__global__ void __launch_bounds__(256) k_moe_ll_combine(LLCombineArgs a)
+{
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    const Team &t = a.p.team;
+    const uint32_t me = team_rank(t);
+    combine_push_body(a.p);
+    __threadfence_system();
+    grid.sync();
+    if (blockIdx.x == 0 && threadIdx.x < t.world) {
+        st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, threadIdx.x, a.p.hp.flags)) + kMaxRanks + me, a.epoch);
+        const uint32_t *f = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, a.p.hp.flags)) + kMaxRanks + threadIdx.x;
+        if (!wait_flag(f, a.epoch, t.spin_limit)) {
+            report_timeout(t, me, 0x422, a.epoch);
+            atomicCAS(a.status, 0, 0x422);
+        }
+    }
+    grid.sync();
+    combine_reduce_body(t, a.p.hp, a.sh, a.topk_idx, a.out, a.topk_w);
 }
 
 }  // namespace mfk
@@ -387,6 +541,41 @@ int mf_moe_combine_reduce(const Team *team, const MoeHeap *hp, const MoeShape *s
     if (sh->H % 8 != 0) return -1;
     k_moe_combine_reduce<<<ctas, 256, 0, (cudaStream_t)stream>>>(*team, *hp, *sh, topk_idx, static_cast<__nv_bfloat16 *>(out));
     cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int mf_moe_combine_push(const Team *team, const MoeHeap *hp, const void *y, int64_t ldy, const int *rows_dev, int H, int K, int weighted,
+                        int ctas, void *stream)
+{
+    if (team == nullptr || hp == nullptr || team->emu || H % 8 != 0 || ctas <= 0) return -1;
+    CombinePushArgs a{*team, *hp, static_cast<const __nv_bfloat16 *>(y), ldy, rows_dev, H, K, weighted};
+    k_moe_combine_push<<<ctas, 256, 0, (cudaStream_t)stream>>>(a);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+// Cooperative: ctas must not exceed what the device can hold at once (one CTA per SM is always safe).
+int mf_moe_ll_dispatch(const DispatchArgs *d, int *tokens_per_expert, int *recv_per_expert, int *row_off, int *src_off, int ctas, void *stream)
+{
+    if (d == nullptr || d->team.emu || d->sh.H % 128 != 0 || d->sh.H / 16 > 448 || d->sh.K > 16 || d->sh.E > 1024 ||
+        d->sh.E % (int)d->team.world != 0 || ctas <= 0)
+        return -1;
+    LLDispatchArgs a{*d, tokens_per_expert, recv_per_expert, row_off, src_off};
+    void *params[] = {&a};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(k_moe_ll_dispatch), dim3(ctas), dim3(448), params, 0,
+                                                (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
+int mf_moe_ll_combine(const Team *team, const MoeHeap *hp, const MoeShape *sh, const void *y, int64_t ldy, const int *rows_dev, int weighted,
+                      const int *topk_idx, const float *topk_w, void *out, uint32_t epoch, int *status, int ctas, void *stream)
+{
+    if (team == nullptr || hp == nullptr || sh == nullptr || team->emu || sh->H % 8 != 0 || ctas <= 0) return -1;
+    LLCombineArgs a{{*team, *hp, static_cast<const __nv_bfloat16 *>(y), ldy, rows_dev, sh->H, sh->K, weighted}, *sh, topk_idx,
+                    static_cast<__nv_bfloat16 *>(out), epoch, status, topk_w};
+    void *params[] = {&a};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(k_moe_ll_combine), dim3(ctas), dim3(256), params, 0,
+                                                (cudaStream_t)stream);
     return e == cudaSuccess ? 0 : (int)e;
 }
 

@@ -34,7 +34,7 @@ class MoeHeapC(C.Structure):
 class DispatchArgsC(C.Structure):
     _fields_ = [("team", TeamC), ("hp", MoeHeapC), ("sh", MoeShapeC), ("x", C.c_void_p), ("topk_idx", C.c_void_p),
                 ("topk_w", C.c_void_p), ("send_idx", C.c_void_p), ("put_off", C.c_void_p), ("done_count", C.c_void_p),
-                ("epoch", C.c_uint32), ("seq", C.c_uint32), ("status", C.c_void_p)]
+                ("epoch", C.c_uint32), ("seq", C.c_uint32), ("status", C.c_void_p), ("raw_bf16", C.c_int)]
 
 
 _lib = None
@@ -57,6 +57,12 @@ def _cu():
         l.mf_moe_signal_all.argtypes = [P(TeamC), P(MoeHeapC), ci, C.c_uint32, vp]
         l.mf_moe_combine_reduce.restype = ci
         l.mf_moe_combine_reduce.argtypes = [P(TeamC), P(MoeHeapC), P(MoeShapeC), vp, vp, ci, vp]
+        l.mf_moe_combine_push.restype = ci
+        l.mf_moe_combine_push.argtypes = [P(TeamC), P(MoeHeapC), vp, C.c_int64, vp, ci, ci, ci, ci, vp]
+        l.mf_moe_ll_dispatch.restype = ci
+        l.mf_moe_ll_dispatch.argtypes = [P(DispatchArgsC), vp, vp, vp, vp, ci, vp]
+        l.mf_moe_ll_combine.restype = ci
+        l.mf_moe_ll_combine.argtypes = [P(TeamC), P(MoeHeapC), P(MoeShapeC), vp, C.c_int64, vp, ci, vp, vp, vp, C.c_uint32, vp, ci, vp]
         l.mf_quant_rows_fp8.restype = ci
         l.mf_quant_rows_fp8.argtypes = [vp, C.c_int64, vp, ci, vp, vp, ci, vp]
         l.mf_grouped_gemm_fp8.restype = ci
@@ -112,7 +118,7 @@ class DispatchState:
 
 class MoEComm:
     def __init__(self, heap: _HeapBase, max_tokens: int, hidden: int, experts: int, topk: int, max_recv: int | None = None,
-                 intermediate: int | None = None):
+                 intermediate: int | None = None, raw_bf16: bool = False):
         assert not heap.emu and hidden % 128 == 0 and experts % heap.world == 0
         self.heap, self.world, self.rank = heap, heap.world, heap.rank
         self.T, self.H, self.E, self.K = max_tokens, hidden, experts, topk
@@ -122,7 +128,8 @@ class MoEComm:
         hp = MoeHeapC()
         hp.counts = heap.alloc(self.world * experts * 4, 256)
         hp.flags = heap.alloc(4 * 16 * 4, 256)
-        hp.recv_x = heap.alloc(self.max_recv * hidden, 1024)
+        self.raw_bf16 = raw_bf16  # rows travel as bf16 instead of block-scaled fp8
+        hp.recv_x = heap.alloc(self.max_recv * hidden * (2 if raw_bf16 else 1), 1024)
         hp.recv_scale = heap.alloc(self.max_recv * (hidden // 128) * 4, 256)
         hp.recv_info = heap.alloc(self.max_recv * 16, 256)
         hp.comb = heap.alloc(max_tokens * topk * hidden * 2, 1024)
@@ -132,6 +139,9 @@ class MoEComm:
         self._epoch = 0
         self._done = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self._dispatches = 0
+        self._ll_done = torch.zeros(1, dtype=torch.int32, device=self.dev)
+        self._ll_calls = 0
+        self._ll_grid = None
         self._grid = sm_count(self.dev)
         self._inter = intermediate
         self._h = self._hq = self._hs = None
@@ -141,6 +151,8 @@ class MoEComm:
 
     # views of the receive area (valid rows: state.row_off[-1])
     def recv_x(self) -> torch.Tensor:
+        if self.raw_bf16:
+            return self.heap.view(self.hp.recv_x, (self.max_recv, self.H), torch.bfloat16)
         return self.heap.view(self.hp.recv_x, (self.max_recv, self.H), torch.uint8).view(torch.float8_e4m3fn)
 
     def recv_scale(self) -> torch.Tensor:
@@ -179,7 +191,7 @@ class MoEComm:
         w = topk_w.to(torch.float32).contiguous()
         self._dispatches += 1
         a = DispatchArgsC(team, self.hp, self._shape(T), x.data_ptr(), idx.data_ptr(), w.data_ptr(), sidx.data_ptr(), put_off.data_ptr(),
-                          self._done.data_ptr(), self._epoch, self._dispatches, status_word(self.dev).data_ptr())
+                          self._done.data_ptr(), self._epoch, self._dispatches, status_word(self.dev).data_ptr(), 1 if self.raw_bf16 else 0)
         self._keep = (w, idx)
         # one CTA per SM on every call: the completion counter of the kernel counts CTAs
         _ok(_cu().mf_moe_dispatch(C.byref(a), self._grid, _s()), "moe_dispatch")
@@ -217,4 +229,51 @@ class MoEComm:
         sh = self._shape(st.T)
         _ok(_cu().mf_moe_combine_reduce(C.byref(team), C.byref(self.hp), C.byref(sh), st.topk_idx.data_ptr(), out.data_ptr(),
                                         min(st.T, self._grid * 4), _s()), "moe_combine_reduce")
+        return out
+
+    # ------------------------------------------------------------------ standalone combine (caller ran its own expert FFN)
+    def combine_push(self, y: torch.Tensor, st: DispatchState, weighted: bool = True) -> None:
+        """y: [>= rows received, hidden] bf16, row r answering row r of the receive buffers. Pushes every row to
+        the combine slot of its token on the token's home rank and raises the combine flag."""
+        assert y.dtype == torch.bfloat16 and y.shape[1] == self.H and y.stride(1) == 1
+        team = self.heap.team()
+        _ok(_cu().mf_moe_combine_push(C.byref(team), C.byref(self.hp), y.data_ptr(), y.stride(0), st.row_off[self.El:].data_ptr(), self.H,
+                                      self.K, 1 if weighted else 0, self._grid * 2, _s()), "moe_combine_push")
+        _ok(_cu().mf_moe_signal_all(C.byref(team), C.byref(self.hp), 1, st.epoch, _s()), "moe_signal")
+
+    # ------------------------------------------------------------------ low-latency pair (one cooperative launch each)
+    def ll_dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor) -> DispatchState:
+        assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == self.H and x.shape[0] <= self.T
+        T = x.shape[0]
+        idx = topk_idx.to(torch.int32).contiguous()
+        w = topk_w.to(torch.float32).contiguous()
+        self._epoch += 1
+        self._ll_calls += 1
+        if self._ll_grid is None:
+            self._ll_grid = max(1, min(self.T, self._grid))  # fixed for the life of the object: the completion counter counts CTAs
+        sidx = torch.empty(T * self.K, dtype=torch.int32, device=self.dev)
+        tpe = torch.empty(self.E, dtype=torch.int32, device=self.dev)
+        rpe = torch.empty(self.El, dtype=torch.int32, device=self.dev)
+        row_off = torch.empty(self.El + 1, dtype=torch.int32, device=self.dev)
+        put_off = torch.empty(self.E, dtype=torch.int32, device=self.dev)
+        src_off = torch.empty(self.El * self.world, dtype=torch.int32, device=self.dev)
+        a = DispatchArgsC(self.heap.team(), self.hp, self._shape(T), x.data_ptr(), idx.data_ptr(), w.data_ptr(), sidx.data_ptr(),
+                          put_off.data_ptr(), self._ll_done.data_ptr(), self._epoch, self._ll_calls, status_word(self.dev).data_ptr(),
+                          1 if self.raw_bf16 else 0)
+        self._keep = (w, idx)
+        _ok(_cu().mf_moe_ll_dispatch(C.byref(a), tpe.data_ptr(), rpe.data_ptr(), row_off.data_ptr(), src_off.data_ptr(), self._ll_grid, _s()),
+            "moe_ll_dispatch")
+        return DispatchState(T, idx, sidx, tpe, None, None, rpe, row_off, put_off, src_off, self._epoch)
+
+    def ll_combine(self, y: torch.Tensor, st: DispatchState, weighted: bool = True, out: torch.Tensor | None = None,
+                   home_weights: torch.Tensor | None = None) -> torch.Tensor:
+        """weighted: multiply each row by the weight that travelled with it; home_weights: [T, K] fp32 applied on the home rank instead."""
+        assert y.dtype == torch.bfloat16 and y.shape[1] == self.H and y.stride(1) == 1
+        if out is None:
+            out = torch.empty((st.T, self.H), dtype=torch.bfloat16, device=self.dev)
+        team, sh = self.heap.team(), self._shape(st.T)
+        hw = home_weights.to(torch.float32).contiguous() if home_weights is not None else None
+        _ok(_cu().mf_moe_ll_combine(C.byref(team), C.byref(self.hp), C.byref(sh), y.data_ptr(), y.stride(0), st.row_off[self.El:].data_ptr(),
+                                    1 if weighted else 0, st.topk_idx.data_ptr(), hw.data_ptr() if hw is not None else None, out.data_ptr(), st.epoch, status_word(self.dev).data_ptr(),
+                                    self._ll_grid or self._grid, _s()), "moe_ll_combine")
         return out

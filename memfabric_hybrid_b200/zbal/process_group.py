@@ -89,6 +89,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         self._comm = None
         self._p2p = {}
         self._nccl = None
+        self._gloo = None
         self._stream = None
         self._strided = self._check_strided()
         self._forced = {s.strip() for s in os.environ.get("ZBAL_NCCL_OP", "").split(",") if s.strip()}
@@ -167,7 +168,17 @@ class ProcessGroupZBAL(dist.ProcessGroup):
             self._p2p[(lo, hi)] = h
         return self._p2p[(lo, hi)], (0 if me_w == lo else 1), (1 if me_w == lo else 0)
 
-    def _fallback(self):
+    def _fallback(self, t=None):
+        """NCCL for CUDA tensors; gloo for host tensors (object collectives of torch.distributed use them)."""
+        if isinstance(t, (list, tuple)):
+            t = t[0] if t else None
+            if isinstance(t, (list, tuple)):
+                t = t[0] if t else None
+        if t is not None and not t.is_cuda:
+            if self._gloo is None:
+                self._gloo = dist.ProcessGroupGloo(dist.PrefixStore("zbal_gloo_fallback/", self._store), self._rank, self._size,
+                                                   timeout=self._timeout)
+            return self._gloo
         if self._nccl is None:
             opts = dist.ProcessGroupNCCL.Options()
             self._nccl = dist.ProcessGroupNCCL(dist.PrefixStore("zbal_nccl_fallback/", self._store), self._rank, self._size, opts)
@@ -206,7 +217,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         if avg:
             op = K.OP_SUM
         if len(tensors) != 1 or op is None or t.dtype not in K.REDUCIBLE or not self._use_zbal("allreduce", t):
-            return self._fallback().allreduce(tensors, opts) if opts is not None else self._fallback().allreduce(tensors)
+            return self._fallback(tensors).allreduce(tensors, opts) if opts is not None else self._fallback(tensors).allreduce(tensors)
         comm, l = self._communicator(), K.lib()
         scale = 1.0 / self._size if avg else 1.0
 
@@ -216,11 +227,11 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         return self._run([t], go, tensors)
 
     def allreduce_coalesced(self, tensors, opts=None):
-        return self._fallback().allreduce_coalesced(tensors, opts)
+        return self._fallback(tensors).allreduce_coalesced(tensors, opts)
 
     def _allgather_base(self, output, input, opts=None):
         if not self._use_zbal("_allgather_base", output, input) or (input.numel() * input.element_size()) % 2:
-            return self._fallback()._allgather_base(output, input, opts) if opts is not None else self._fallback()._allgather_base(output, input)
+            return self._fallback(input)._allgather_base(output, input, opts) if opts is not None else self._fallback(input)._allgather_base(output, input)
         comm, l = self._communicator(), K.lib()
 
         def go(s):
@@ -231,8 +242,8 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         inp, outs = input_tensors[0], output_tensors[0]
         if len(input_tensors) != 1 or inp.dtype not in K.DT or not self._use_zbal("allgather", inp) or (inp.numel() * inp.element_size()) % 2 or \
                 any(o.numel() != inp.numel() for o in outs):
-            return self._fallback().allgather(output_tensors, input_tensors, opts) if opts is not None else \
-                self._fallback().allgather(output_tensors, input_tensors)
+            return self._fallback(input_tensors).allgather(output_tensors, input_tensors, opts) if opts is not None else \
+                self._fallback(input_tensors).allgather(output_tensors, input_tensors)
         comm, l = self._communicator(), K.lib()
         flat = torch.empty((self._size, inp.numel()), dtype=inp.dtype, device=inp.device)
 
@@ -244,13 +255,13 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         return self._run([inp, flat] + list(outs), go, output_tensors)
 
     def allgather_into_tensor_coalesced(self, outputs, inputs, opts=None):
-        return self._fallback().allgather_into_tensor_coalesced(outputs, inputs, opts)
+        return self._fallback(inputs).allgather_into_tensor_coalesced(outputs, inputs, opts)
 
     def gather(self, output_tensors, input_tensors, opts=None):
         inp = input_tensors[0]
         root = opts.rootRank if opts is not None else 0
         if inp.dtype not in K.DT or not self._use_zbal("gather", inp) or (inp.numel() * inp.element_size()) % 2:
-            return self._fallback().gather(output_tensors, input_tensors, opts)
+            return self._fallback(input_tensors).gather(output_tensors, input_tensors, opts)
         comm, l = self._communicator(), K.lib()
         flat = torch.empty((self._size, inp.numel()), dtype=inp.dtype, device=inp.device)
         outs = output_tensors[0] if (self._rank == root and output_tensors) else []
@@ -266,7 +277,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         t = tensors[0]
         root = opts.rootRank if opts is not None else 0
         if len(tensors) != 1 or t.dtype not in K.DT or not self._use_zbal("broadcast", t) or (t.numel() * t.element_size()) % 2:
-            return self._fallback().broadcast(tensors, opts) if opts is not None else self._fallback().broadcast(tensors)
+            return self._fallback(tensors).broadcast(tensors, opts) if opts is not None else self._fallback(tensors).broadcast(tensors)
         comm, l = self._communicator(), K.lib()
 
         def go(s):
@@ -277,7 +288,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         out = output_tensors[0]
         root = opts.rootRank if opts is not None else 0
         if out.dtype not in K.DT or not self._use_zbal("scatter", out) or (out.numel() * out.element_size()) % 2:
-            return self._fallback().scatter(output_tensors, input_tensors, opts)
+            return self._fallback(output_tensors).scatter(output_tensors, input_tensors, opts)
         comm, l = self._communicator(), K.lib()
         src = None
         if self._rank == root:
@@ -292,8 +303,8 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         op = _OPS.get(opts.reduceOp if opts is not None else ReduceOp.SUM)
         if op is None or input.dtype not in K.REDUCIBLE or not self._use_zbal("_reduce_scatter_base", output, input) or \
                 input.numel() != output.numel() * self._size:
-            return self._fallback()._reduce_scatter_base(output, input, opts) if opts is not None else \
-                self._fallback()._reduce_scatter_base(output, input)
+            return self._fallback(input)._reduce_scatter_base(output, input, opts) if opts is not None else \
+                self._fallback(input)._reduce_scatter_base(output, input)
         comm, l = self._communicator(), K.lib()
 
         def go(s):
@@ -305,7 +316,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         out, parts = output_tensors[0], input_tensors[0]
         op = _OPS.get(opts.reduceOp if opts is not None else ReduceOp.SUM)
         if op is None or out.dtype not in K.REDUCIBLE or not self._use_zbal("reduce_scatter", out) or any(p.numel() != out.numel() for p in parts):
-            return self._fallback().reduce_scatter(output_tensors, input_tensors, opts)
+            return self._fallback(output_tensors).reduce_scatter(output_tensors, input_tensors, opts)
         comm, l = self._communicator(), K.lib()
         flat = torch.stack([p.reshape(-1) for p in parts]).contiguous()
 
@@ -314,13 +325,13 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         return self._run([flat, out], go, output_tensors)
 
     def reduce_scatter_tensor_coalesced(self, outputs, inputs, opts=None):
-        return self._fallback().reduce_scatter_tensor_coalesced(outputs, inputs, opts)
+        return self._fallback(inputs).reduce_scatter_tensor_coalesced(outputs, inputs, opts)
 
     def reduce(self, tensors, opts=None):
-        return self._fallback().reduce(tensors, opts)
+        return self._fallback(tensors).reduce(tensors, opts)
 
     def alltoall(self, output_tensors, input_tensors, opts=None):
-        return self._fallback().alltoall(output_tensors, input_tensors, opts)
+        return self._fallback(input_tensors).alltoall(output_tensors, input_tensors, opts)
 
     def barrier(self, opts=None):
         if "barrier" in self._forced or not self._strided:
@@ -336,7 +347,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
     def alltoall_base(self, output, input, output_split_sizes, input_split_sizes, opts=None):
         es = input.element_size()
         if not self._use_zbal("alltoall_base", output, input) or input.dtype not in K.DT:
-            return self._fallback().alltoall_base(output, input, output_split_sizes, input_split_sizes, opts)
+            return self._fallback(input).alltoall_base(output, input, output_split_sizes, input_split_sizes, opts)
         row_in = input[0].numel() if input.dim() > 1 else 1
         row_out = output[0].numel() if output.dim() > 1 else 1
         ins = list(input_split_sizes) if input_split_sizes else [input.shape[0] // self._size] * self._size
@@ -344,7 +355,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         nbytes = input.numel() * es
         stage = self._stage_bytes()
         if nbytes + 4096 > stage or nbytes % 2:
-            return self._fallback().alltoall_base(output, input, output_split_sizes, input_split_sizes, opts)
+            return self._fallback(input).alltoall_base(output, input, output_split_sizes, input_split_sizes, opts)
         meta = torch.empty((self._size, 4), dtype=torch.int64).pin_memory()
         so = ro = 0
         for p in range(self._size):
@@ -370,7 +381,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
     def send(self, tensors, dst_rank, tag=0):
         t = tensors[0]
         if not self._use_zbal("send", t) or t.dtype not in K.DT:
-            return self._fallback().send(tensors, dst_rank, tag)
+            return self._fallback(tensors).send(tensors, dst_rank, tag)
         comm, _, peer = self._p2p_comm(dst_rank)
         l = K.lib()
 
@@ -381,7 +392,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
     def recv(self, tensors, src_rank, tag=0):
         t = tensors[0]
         if not self._use_zbal("recv", t) or t.dtype not in K.DT:
-            return self._fallback().recv(tensors, src_rank, tag)
+            return self._fallback(tensors).recv(tensors, src_rank, tag)
         comm, _, peer = self._p2p_comm(src_rank)
         l = K.lib()
 
@@ -390,7 +401,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         return self._run([t], go, tensors)
 
     def recv_anysource(self, tensors, tag=0):
-        return self._fallback().recv_anysource(tensors, tag)
+        return self._fallback(tensors).recv_anysource(tensors, tag)
 
     # ------------------------------------------------------------------ diagnostics
     def device_status(self):

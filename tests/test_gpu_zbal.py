@@ -1,0 +1,214 @@
+"""zbal on a GPU: the torch.distributed backend, the symmetric allocator under PyTorch, the MoE Buffer.
+
+Each scenario runs in child processes (zbal bootstraps once per process). With one GPU the world has one
+rank, which still drives every kernel; the multi-GPU test runs real ranks over NVLink and compares with
+values computed locally from the ranks' seeds."""
+import os
+
+import pytest
+import torch
+
+from conftest import free_port
+from mp_util import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _draw(r, n, dtype=torch.float32):
+    import torch
+    return torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(77 * r + 5)).to(dtype)
+
+
+def _pg_scenario(rank, world, port, sync):
+    import torch
+    import torch.distributed as dist
+    import memfabric_hybrid_b200.zbal as zbal
+    dev = rank % torch.cuda.device_count()
+    torch.cuda.set_device(dev)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    assert zbal.zbal_init(world, dev, rank, 512 << 20, ip_port=f"127.0.0.1:{port}", start_config_server=True)
+    dist.init_process_group("zbal", init_method=f"tcp://127.0.0.1:{port + 1}", rank=rank, world_size=world)
+    pg = dist.group.WORLD
+    assert isinstance(pg, zbal.ProcessGroupZBAL)
+
+    # all_reduce: sum, avg, max, in place, several sizes (one-shot and two-shot), async handle
+    for n in (1, 1000, 70_000, 2_000_000):
+        for dtype in (torch.float32, torch.bfloat16):
+            x = _draw(rank, n, dtype)
+            ref = sum(_draw(r, n, dtype).float() for r in range(world))
+            dist.all_reduce(x)
+            torch.testing.assert_close(x.float(), ref, rtol=2e-2, atol=2e-2 * world)
+    x = _draw(rank, 4096)
+    w = dist.all_reduce(x, op=dist.ReduceOp.MAX, async_op=True)
+    w.wait()
+    torch.testing.assert_close(x, torch.stack([_draw(r, 4096) for r in range(world)]).max(0).values)
+    x = _draw(rank, 4096)
+    dist.all_reduce(x, op=dist.ReduceOp.AVG)
+    torch.testing.assert_close(x, sum(_draw(r, 4096) for r in range(world)) / world, rtol=1e-5, atol=1e-5)
+
+    # all_gather (tensor and list forms), reduce_scatter (tensor form), broadcast, scatter, gather
+    shard = _draw(rank, 3000)
+    full = torch.empty(world * 3000, device="cuda")
+    dist.all_gather_into_tensor(full, shard)
+    assert torch.equal(full, torch.cat([_draw(r, 3000) for r in range(world)]))
+    parts = [torch.empty(3000, device="cuda") for _ in range(world)]
+    dist.all_gather(parts, shard)
+    assert all(torch.equal(parts[r], _draw(r, 3000)) for r in range(world))
+    big = _draw(rank, world * 5000)
+    mine = torch.empty(5000, device="cuda")
+    dist.reduce_scatter_tensor(mine, big)
+    ref = sum(_draw(r, world * 5000) for r in range(world))[rank * 5000:(rank + 1) * 5000]
+    torch.testing.assert_close(mine, ref, rtol=1e-5, atol=1e-5)
+    b = _draw(rank, 10_000).to(torch.int64) if False else _draw(rank, 10_000)
+    dist.broadcast(b, src=world - 1)
+    assert torch.equal(b, _draw(world - 1, 10_000))
+    got = torch.empty(777 * 2, device="cuda")
+    src = [(_draw(0, 777 * 2) + r) for r in range(world)] if rank == 0 else None
+    dist.scatter(got, src, src=0)
+    assert torch.equal(got, _draw(0, 777 * 2) + rank)
+    outs = [torch.empty(100, device="cuda") for _ in range(world)] if rank == 0 else None
+    dist.gather(_draw(rank, 100), outs, dst=0)
+    if rank == 0:
+        assert all(torch.equal(outs[r], _draw(r, 100)) for r in range(world))
+
+    # all_to_all_single with uneven splits: rank r sends (p + 1) rows of 8 to peer p
+    rows_out = [p + 1 for p in range(world)]
+    send = torch.cat([torch.full((p + 1, 8), float(rank * 100 + p), device="cuda") for p in range(world)])
+    recv = torch.empty(((rank + 1) * world, 8), device="cuda")
+    dist.all_to_all_single(recv, send, output_split_sizes=[rank + 1] * world, input_split_sizes=rows_out)
+    exp = torch.cat([torch.full((rank + 1, 8), float(p * 100 + rank), device="cuda") for p in range(world)])
+    assert torch.equal(recv, exp)
+
+    # an int64 tensor is not reducible by the kernels: the NCCL fallback must give the right answer
+    if world > 1:
+        cnt = torch.full((5,), rank + 1, device="cuda", dtype=torch.int64)
+        dist.all_reduce(cnt)
+        assert cnt[0].item() == sum(range(1, world + 1))
+        # point to point around the ring, and a strided sub-group
+        msg, box = torch.full((50_000,), float(rank), device="cuda"), torch.empty(50_000, device="cuda")
+        nxt, prv = (rank + 1) % world, (rank - 1) % world
+        if rank % 2 == 0:
+            dist.send(msg, nxt)
+            dist.recv(box, prv)
+        else:
+            dist.recv(box, prv)
+            dist.send(msg, nxt)
+        assert torch.equal(box, torch.full_like(box, float(prv)))
+        if world >= 4:
+            groups = [dist.new_group([0, 2]), dist.new_group([1, 3])] if world == 4 else [dist.new_group(list(range(0, world, 2))),
+                                                                                         dist.new_group(list(range(1, world, 2)))]
+            g = groups[rank % 2]
+            y = torch.full((3000,), float(rank), device="cuda")
+            dist.all_reduce(y, group=g)
+            members = dist.get_process_group_ranks(g)
+            assert torch.equal(y, torch.full_like(y, float(sum(members))))
+    dist.barrier()
+
+    # tensors from the symmetric allocator: same offset on every rank, usable by torch, reused after free
+    with zbal.switch_to_allocator():
+        t = torch.arange(1 << 20, device="cuda", dtype=torch.float32)
+        off = t.data_ptr() - zbal.zbal_get_symm_base_addr()
+        assert zbal.in_symmetric_heap(t) and float(t.sum()) == float((1 << 20) * ((1 << 20) - 1) / 2)
+        dist.all_reduce(t)
+        assert float(t[5]) == 5.0 * world
+    offs = [None] * world
+    dist.all_gather_object(offs, off) if world > 1 else offs.__setitem__(0, off)
+    assert len(set(offs)) == 1, f"allocation offsets differ across ranks: {offs}"
+    used, total = zbal.get_heap_stats()
+    assert 0 < used <= total and zbal.mem_get_info()[1] == total
+    del t
+    torch.cuda.synchronize()
+    status = pg.device_status()
+    dist.destroy_process_group()
+    zbal.zbal_uninit()
+    return status[0]
+
+
+def test_process_group_single_gpu():
+    port = free_port()
+    assert run_ranks(_pg_scenario, 1, (port,), timeout=300, with_barrier=True) == [0]
+
+
+@pytest.mark.multigpu
+def test_process_group_multi_gpu():
+    n = min(torch.cuda.device_count(), 4)
+    port = free_port()
+    assert run_ranks(_pg_scenario, n, (port,), timeout=420, with_barrier=True) == [0] * n
+
+
+def _buffer_scenario(rank, world, port, sync):
+    import torch
+    import memfabric_hybrid_b200.zbal as zbal
+    from memfabric_hybrid_b200.ops import gemm
+    dev = rank % torch.cuda.device_count()
+    torch.cuda.set_device(dev)
+    assert zbal.zbal_init(world, dev, rank, 1 << 30, ip_port=f"127.0.0.1:{port}", start_config_server=True)
+    T, H, K = 96, 1024, 4
+    E = 8 * world
+    g = torch.Generator("cuda").manual_seed(rank)
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    logits = torch.randn(T, E, device="cuda", generator=g)
+    w, idx = torch.softmax(logits, -1).topk(K, dim=-1)
+    idx[0, 1] = -1  # an unselected slot must be skipped everywhere
+    expect = (x.float() * torch.where(idx >= 0, w, torch.zeros_like(w)).sum(-1, keepdim=True))
+
+    for use_fp8 in (True, False):
+        buf = zbal.Buffer(None, hidden=H, num_experts=E, num_topk=K, num_max_tokens=128, use_fp8=use_fp8)
+        tpr, _, tpe, inr, _ = buf.get_dispatch_layout(idx, E)
+        assert int(tpe.sum()) == int((idx >= 0).sum()) and inr.shape == (T, world)
+        recv, recv_e, recv_w, counts, handle, _ = buf.dispatch(x, num_tokens_per_rank=tpr, is_token_in_rank=inr, num_tokens_per_expert=tpe,
+                                                               topk_idx=idx, topk_weights=w)
+        rows = sum(counts)
+        assert len(counts) == E // world and recv_e.shape[0] == rows and recv_w.shape[0] == rows
+        if use_fp8:
+            q, s = recv
+            rx = (q.float().view(rows, H // 128, 128) * s.view(rows, H // 128, 1)).view(rows, H)
+        else:
+            rx = recv.float()
+        if world == 1:
+            assert rows == int((idx >= 0).sum())
+            # rows of local expert 0 are the tokens that chose expert 0, in token order
+            toks = (idx == 0).any(-1).nonzero().flatten()
+            assert counts[0] == toks.numel() and bool((recv_e[:counts[0]] == 0).all())
+            torch.testing.assert_close(rx[:counts[0]], x[toks].float(), rtol=0.08 if use_fp8 else 0, atol=0.08 if use_fp8 else 0)
+        # identity experts: the combined output is x times the sum of the selected weights
+        out, _, _ = buf.combine(rx.to(torch.bfloat16), handle)
+        torch.testing.assert_close(out.float(), expect, rtol=0.06, atol=0.06)
+
+        # low-latency pair, weights travelling with the rows and weights applied at home
+        (lrecv, lcount, lh, _, _) = buf.low_latency_dispatch(x, idx, 128, E, use_fp8=use_fp8, topk_weights=w)
+        n = int(lh[1][-1])
+        assert n == int(lcount.sum())
+        if use_fp8:
+            q, s = lrecv
+            ly = (q[:n].float().view(n, H // 128, 128) * s[:n].view(n, H // 128, 1)).view(n, H).to(torch.bfloat16)
+        else:
+            ly = lrecv[:n].clone()
+        lout, _, _ = buf.low_latency_combine(ly, idx, w, lh)
+        torch.testing.assert_close(lout.float(), expect, rtol=0.06, atol=0.06)
+        (lrecv, lcount, lh, _, _) = buf.low_latency_dispatch(x, idx, 128, E, use_fp8=use_fp8)
+        n = int(lh[1][-1])
+        if use_fp8:
+            q, s = lrecv
+            ly = (q[:n].float().view(n, H // 128, 128) * s[:n].view(n, H // 128, 1)).view(n, H).to(torch.bfloat16)
+        else:
+            ly = lrecv[:n].clone()
+        lout, _, _ = buf.low_latency_combine(ly, idx, w, lh)
+        torch.testing.assert_close(lout.float(), expect, rtol=0.06, atol=0.06)
+        torch.cuda.synchronize()
+        gemm.check_status()
+        buf.destroy()
+    zbal.zbal_uninit()
+    return 0
+
+
+def test_buffer_single_gpu():
+    port = free_port()
+    assert run_ranks(_buffer_scenario, 1, (port,), timeout=300, with_barrier=True) == [0]
+
+
+@pytest.mark.multigpu
+def test_buffer_multi_gpu():
+    n = min(torch.cuda.device_count(), 4)
+    port = free_port()
+    assert run_ranks(_buffer_scenario, n, (port,), timeout=420, with_barrier=True) == [0] * n

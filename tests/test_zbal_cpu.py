@@ -1,0 +1,156 @@
+"""zbal host side without a GPU: the split heap and the caching allocator on a made-up address range, and
+bootstrap / communicator bookkeeping over the fake device backend with real processes."""
+import ctypes as C
+import json
+import os
+
+import pytest
+
+from conftest import free_port
+from mp_util import run_ranks
+
+BASE = 0x7000_0000_0000
+MiB = 1 << 20
+
+
+@pytest.fixture()
+def sma():
+    from memfabric_hybrid_b200.zbal import _capi as K
+    l = K.lib()
+    l.zbal_simulate_init(BASE, 256 * MiB)
+    yield l
+    l.zbal_sma_uninit(0)
+
+
+def _stats(l):
+    from memfabric_hybrid_b200.zbal import _capi as K
+    s = K.SmaStatsC()
+    assert l.zbal_sma_get_stats(C.byref(s)) == 0
+    return s
+
+
+def test_small_low_large_high_and_rounding(sma):
+    a = sma.zbal_pluggable_malloc(1000, 0, None)
+    b = sma.zbal_pluggable_malloc(100, 0, None)
+    big = sma.zbal_pluggable_malloc(3 * MiB + 1, 0, None)
+    assert a == BASE and b == BASE + 1024          # 1000 -> 1024, packed from the low end
+    assert big == BASE + 256 * MiB - 4 * MiB       # rounded to 2 MiB steps, carved from the high end
+    s = _stats(sma)
+    assert s.inUseBytes == 1024 + 512 + 4 * MiB and s.heapCarves == 3 and s.cacheHits == 0
+    for p in (a, b, big):
+        sma.zbal_pluggable_free(p, 0, 0, None)
+    assert _stats(sma).inUseBytes == 0 and _stats(sma).cachedBytes == 1024 + 512 + 4 * MiB
+
+
+def test_cache_is_per_stream_and_flush_on_exhaustion(sma):
+    s1, s2 = C.c_void_p(0x10), C.c_void_p(0x20)
+    p = sma.zbal_pluggable_malloc(8 * MiB, 0, s1)
+    sma.zbal_pluggable_free(p, 0, 0, s1)
+    q = sma.zbal_pluggable_malloc(8 * MiB, 0, s2)   # another stream must not take the cached block
+    assert q != p
+    r = sma.zbal_pluggable_malloc(7 * MiB, 0, s1)   # same stream: a slightly smaller request reuses it
+    assert r == p and _stats(sma).cacheHits == 1
+    sma.zbal_pluggable_free(q, 0, 0, s2)
+    sma.zbal_pluggable_free(r, 0, 0, s1)
+    # 16 MiB sit in the caches; a request that only fits once they are returned must succeed
+    huge = sma.zbal_pluggable_malloc(250 * MiB, 0, s1)
+    assert huge != 0 and _stats(sma).cachedBytes == 0
+    assert sma.zbal_pluggable_malloc(64 * MiB, 0, s1) is None and _stats(sma).failedMallocs == 1
+    from memfabric_hybrid_b200.zbal import _capi as K
+    assert "exhausted" in K.last_error()
+    sma.zbal_pluggable_free(huge, 0, 0, s1)
+    sma.zbal_pluggable_empty_cache(True)
+    assert _stats(sma).largestFreeBlock == 256 * MiB   # everything coalesced back into one block
+
+
+def test_same_sequence_gives_same_offsets_and_snapshot(sma):
+    import random
+    from memfabric_hybrid_b200.zbal import module as M
+
+    def run(seed):
+        rnd = random.Random(seed)
+        live, trace = [], []
+        for _ in range(400):
+            if live and rnd.random() < 0.45:
+                sma.zbal_pluggable_free(live.pop(rnd.randrange(len(live))), 0, 0, None)
+            else:
+                size = rnd.choice([64, 700, 4096, 100_000, 3 * MiB, 9 * MiB])
+                p = sma.zbal_pluggable_malloc(size, 0, None)
+                assert p
+                live.append(p)
+                trace.append(p - BASE)
+        for p in live:
+            sma.zbal_pluggable_free(p, 0, 0, None)
+        sma.zbal_pluggable_empty_cache(True)
+        return trace
+
+    sma.zbal_sma_record_history(True, 100)
+    first = run(3)
+    snap = M.snapshot()
+    assert snap["heap"]["size"] == 256 * MiB and snap["heap"]["in_use"] == 0
+    assert len(snap["history"]) == 100 and snap["history"][-1]["op"] == "empty_cache"
+    assert [b["state"] for b in snap["blocks"]] == ["free"]
+    assert run(3) == first                       # determinism is what makes the heap symmetric across ranks
+    json.dumps(snap)
+
+
+def test_replay_tool_reports_fragmentation(tmp_path, sma):
+    from memfabric_hybrid_b200.zbal import module as M, simulator
+    sma.zbal_sma_record_history(True, 0)
+    ps = [sma.zbal_pluggable_malloc(3 * MiB, 0, None) for _ in range(8)]
+    for p in ps[::2]:
+        sma.zbal_pluggable_free(p, 0, 0, None)
+    path = tmp_path / "snap.json"
+    M.dump_snapshot(str(path))
+    rep = simulator.analyse(json.loads(path.read_text()))
+    assert rep["active_bytes"] == 4 * 4 * MiB and rep["cached_bytes"] == 4 * 4 * MiB and rep["blocks"] >= 9
+    # replaying the recorded history on a fresh heap reproduces the addresses
+    out = simulator.replay(json.loads(path.read_text()))
+    assert out["mismatches"] == 0 and out["events"] == 12
+    txt = simulator.render(json.loads(path.read_text()), width=64)
+    assert "#" in txt and "." in txt
+
+
+def _boot(rank, world, port):
+    os.environ["MF_DEVICE_BACKEND"] = "fake"
+    import memfabric_hybrid_b200.zbal as z
+    from memfabric_hybrid_b200.zbal import _capi as K
+    l = K.lib()
+    assert not z.is_initialized()
+    assert z.zbal_init(world, 0, rank, 256 << 20, ip_port=f"127.0.0.1:{port}", start_config_server=True, comm_group_cap=4)
+    with pytest.raises(K.ZbalError):
+        z.zbal_init(world, 0, rank, 256 << 20, ip_port=f"127.0.0.1:{port}")
+    out = z.module.bootstrap_output()
+    assert out.localGva == out.baseGva + rank * out.symmetricSize and out.heapGva == out.localGva + out.commAreaSize
+    p = K.CommPropertyC()
+    g = l.zbal_comm_get_global()
+    assert l.zbal_comm_get_property(g, C.byref(p)) == 0
+    assert (p.name, p.groupId, p.groupSize, p.groupRank) == (b"zbal_world", 0, world, rank)
+    # two strided sub-groups created at the same time agree on different slots
+    first = rank % 2
+    o = K.CommOptionsC()
+    o.name, o.firstRank, o.rankStep, o.groupSize = f"zbal_{first}:{first + 2}:2_group_0".encode(), first, 2, 2
+    h = C.c_void_p()
+    assert l.zbal_comm_create(C.byref(o), C.byref(h)) == 0
+    assert l.zbal_comm_get_property(h, C.byref(p)) == 0
+    slot, grank = p.groupId, p.groupRank
+    assert grank == rank // 2 and 1 <= slot <= 3 and l.zbal_comm_get_by_name(o.name) == h.value
+    # not a member / duplicate name / leaves the world
+    bad = K.CommOptionsC()
+    bad.name, bad.firstRank, bad.rankStep, bad.groupSize = b"x", 1 - first, 2, 2
+    assert l.zbal_comm_create(C.byref(bad), C.byref(C.c_void_p())) != 0
+    assert l.zbal_comm_create(C.byref(o), C.byref(C.c_void_p())) != 0
+    bad.firstRank, bad.groupSize = first, 3
+    assert l.zbal_comm_create(C.byref(bad), C.byref(C.c_void_p())) != 0
+    # allocations land at the same offset of every rank's heap
+    a = l.zbal_pluggable_malloc(5000, 0, None) - out.heapGva
+    assert l.zbal_comm_destroy(h, 0) == 0 and l.zbal_comm_get_by_name(o.name) is None
+    assert z.zbal_uninit() and not z.is_initialized()
+    return slot, a
+
+
+def test_bootstrap_and_communicators_over_fake_backend():
+    res = run_ranks(_boot, 4, (free_port(),), timeout=120)
+    slots = [r[0] for r in res]
+    assert slots[0] == slots[2] and slots[1] == slots[3] and slots[0] != slots[1]
+    assert len({r[1] for r in res}) == 1
