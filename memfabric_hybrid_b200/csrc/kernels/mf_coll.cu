@@ -30,7 +30,7 @@ struct CollArgs {
     float scale;
     int op;
     uint32_t epoch;
-    uint32_t zero_copy;        // input already sits at stage_a of every slot
+    uint32_t zero_copy;        // 1: input already sits at stage_a of every slot; 2: direct mode (buffers inside the slices)
     uint32_t root;
     uint32_t algo;             // allreduce: 0 one-shot, 1 two-shot; rooted copy: 0 broadcast, 1 scatter
     uint64_t part_stride;      // elements between consecutive members' parts in the user buffer (0: packed):
@@ -311,6 +311,152 @@ template <typename T> __global__ void __launch_bounds__(512) k_broadcast(CollArg
     cta_raw_copy<T>(reinterpret_cast<const T *>(peer_ptr(t, me, a.stage_b)), out, sub.beg, sub.end);
 }
 
+// ------------------------------------------------------------------------------------------------
+// Direct ("zero-copy") variants for buffers that live inside the ranks' own slices of the symmetric
+// heap (tensors from the symmetric allocator): no staging copy on either side. The ranks swap the slot
+// offsets of their buffers in the opening handshake, so the buffers need not sit at the same offset on
+// every rank. A closing handshake keeps every input intact until all peers have read it and tells each
+// rank that the peers' stores into its output have landed.
+template <typename T, bool INT, int W, typename Sink>
+__device__ __forceinline__ void reduce_direct(const Team &t, uint32_t me, const uint64_t *src_off, uint64_t base, uint64_t beg, uint64_t end,
+                                              int op, Sink sink)
+{
+    constexpr int VN = Vec<T>::N;
+    const uint32_t world = W > 0 ? (uint32_t)W : t.world;
+    bool vec_ok = true;
+    for (uint32_t r = 0; r < world; r++) vec_ok = vec_ok && (((src_off[r] + (base + beg) * sizeof(T)) & 15) == 0);
+    uint64_t vend = beg;
+    if (vec_ok) {
+        vend = beg + (end - beg) / VN * VN;
+        for (uint64_t i = beg + (uint64_t)threadIdx.x * VN; i < vend; i += (uint64_t)blockDim.x * VN) {
+            float acc[VN];
+            if (W > 0) {
+                uint4 raw[W > 0 ? W : 1];
+#pragma unroll
+                for (int k = 0; k < W; k++) {
+                    const uint32_t r = (me + k) % W;
+                    const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(reinterpret_cast<const T *>(peer_ptr(t, r, src_off[r])) + base + i));
+#pragma unroll
+                    for (int q = 0; q < W; q++)
+                        if (q == (int)r) raw[q] = v;
+                }
+#pragma unroll
+                for (int r = 0; r < W; r++) {
+                    float f[VN];
+                    Vec<T>::unpack(raw[r], f);
+#pragma unroll
+                    for (int k = 0; k < VN; k++) acc[k] = r == 0 ? f[k] : red_apply<INT>(acc[k], f[k], op);
+                }
+            } else {
+                for (uint32_t r = 0; r < world; r++) {
+                    float f[VN];
+                    Vec<T>::load(reinterpret_cast<const T *>(peer_ptr(t, r, src_off[r])) + base + i, f);
+#pragma unroll
+                    for (int k = 0; k < VN; k++) acc[k] = r == 0 ? f[k] : red_apply<INT>(acc[k], f[k], op);
+                }
+            }
+            sink(i, acc, VN);
+        }
+    }
+    for (uint64_t i = vend + threadIdx.x; i < end; i += blockDim.x) {
+        float acc[VN];
+        for (uint32_t r = 0; r < world; r++) {
+            float f = Vec<T>::to_f(__ldcg(reinterpret_cast<const T *>(peer_ptr(t, r, src_off[r])) + base + i));
+            acc[0] = r == 0 ? f : red_apply<INT>(acc[0], f, op);
+        }
+        sink(i, acc, 1);
+    }
+}
+
+// all-reduce: rank r reduces chunk r straight from every rank's input and stores the result straight
+// into every rank's output. In place (out == in) is fine: chunk r is read and written by rank r only.
+template <typename T, typename TO, bool INT, int W> __global__ void __launch_bounds__(512) k_allreduce_zc(CollArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const uint32_t world = t.world;
+    __shared__ uint64_t p_in[kMaxRanks], p_out[kMaxRanks];
+    const uint64_t slot = t.heap_base + (uint64_t)me * t.stride;
+    if (!lane_sync_xchg(t, me, 0, a.epoch, 0x180, a.in - slot, a.out - slot, p_in, p_out)) return;
+    constexpr int VN = Vec<T>::N;
+    uint64_t C = (a.n + world - 1) / world;
+    C = (C + 7) / 8 * 8;
+    const Range sub = cta_range<8>(C);
+    const uint64_t b = min(a.n, me * C + sub.beg), e = min(a.n, me * C + sub.end);
+    reduce_direct<T, INT, W>(t, me, p_in, 0, b, e, a.op, [&](uint64_t i, float *acc, int cnt) {
+        if (!INT && a.scale != 1.f)
+            for (int k = 0; k < cnt; k++) acc[k] *= a.scale;
+        for (uint32_t k = 0; k < world; k++) {
+            const uint32_t r = (me + k) % world;
+            TO *dst = reinterpret_cast<TO *>(peer_ptr(t, r, p_out[r]));
+            float tmp[VN];
+#pragma unroll
+            for (int q = 0; q < VN; q++) tmp[q] = acc[q];
+            emit<TO, true>(dst, i, tmp, cnt, 1.f);
+        }
+    });
+    lane_sync(t, me, 1, a.epoch, 0x181);
+}
+
+// reduce-scatter: rank r reduces part r of every rank's input into its local output.
+template <typename T, typename TO, bool INT, int W> __global__ void __launch_bounds__(512) k_reduce_scatter_zc(CollArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    __shared__ uint64_t p_in[kMaxRanks], p_unused[kMaxRanks];
+    const uint64_t slot = t.heap_base + (uint64_t)me * t.stride;
+    if (!lane_sync_xchg(t, me, 0, a.epoch, 0x182, a.in - slot, 0, p_in, p_unused)) return;
+    TO *out = reinterpret_cast<TO *>(a.out);
+    const uint64_t m = a.n / t.world;
+    const uint64_t ps = a.part_stride ? a.part_stride : m;
+    const Range sub = cta_range<8>(m);
+    reduce_direct<T, INT, W>(t, me, p_in, (uint64_t)me * ps, sub.beg, sub.end, a.op,
+                             [&](uint64_t i, float *acc, int cnt) { emit<TO, INT>(out, i, acc, cnt, a.scale); });
+    lane_sync(t, me, 1, a.epoch, 0x183);
+}
+
+// all-gather: every rank stores its shard straight into every rank's output.
+template <typename T, typename TO> __global__ void __launch_bounds__(512) k_allgather_zc(CollArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const uint32_t world = t.world;
+    __shared__ uint64_t p_out[kMaxRanks], p_unused[kMaxRanks];
+    const uint64_t slot = t.heap_base + (uint64_t)me * t.stride;
+    if (!lane_sync_xchg(t, me, 0, a.epoch, 0x184, a.out - slot, 0, p_out, p_unused)) return;
+    const T *in = reinterpret_cast<const T *>(a.in);
+    const uint64_t ps = a.part_stride ? a.part_stride : a.n;
+    const Range sub = cta_range<8>(a.n);
+    for (uint32_t k = 0; k < world; k++) {
+        const uint32_t r = (me + k) % world;
+        TO *dst = reinterpret_cast<TO *>(peer_ptr(t, r, p_out[r])) + (uint64_t)me * ps;
+        cta_convert_copy<T, TO>(in, dst, sub.beg, sub.end, a.scale);
+    }
+    lane_sync(t, me, 1, a.epoch, 0x185);
+}
+
+// rooted copy: the root stores straight into every rank's output (scatter mode: part r to rank r).
+template <typename T> __global__ void __launch_bounds__(512) k_broadcast_zc(CollArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const uint32_t world = t.world;
+    __shared__ uint64_t p_out[kMaxRanks], p_unused[kMaxRanks];
+    const uint64_t slot = t.heap_base + (uint64_t)me * t.stride;
+    if (!lane_sync_xchg(t, me, 0, a.epoch, 0x186, a.out - slot, 0, p_out, p_unused)) return;
+    if (me == a.root) {
+        const T *in = reinterpret_cast<const T *>(a.in);
+        const Range sub = cta_range<8>(a.n);
+        for (uint32_t k = 0; k < world; k++) {
+            const uint32_t r = (me + k) % world;
+            const T *src = a.algo == 1 ? in + (uint64_t)r * (a.part_stride ? a.part_stride : a.n) : in;
+            T *dst = reinterpret_cast<T *>(peer_ptr(t, r, p_out[r]));
+            if (src != dst) cta_raw_copy<T>(src, dst, sub.beg, sub.end);
+        }
+    }
+    lane_sync(t, me, 1, a.epoch, 0x187);
+}
+
 // all-to-all-v (bytes). Each rank stages its whole send buffer plus its (offset, count) table; after the
 // handshake every rank pulls its pieces from the peers' staging.
 //   table in staging A header: W x {u64 send_off, u64 send_cnt} toward each destination, bytes
@@ -474,6 +620,24 @@ template <typename T, typename TO, bool INT> int launch_allreduce(const CollArgs
         default: return launch(k_allreduce<T, TO, INT, 0>, a, ctas, threads, s, false);
     }
 }
+template <typename T, typename TO, bool INT> int launch_allreduce_zc(const CollArgs &a, int ctas, int threads, cudaStream_t s)
+{
+    switch (a.team.world) {
+        case 2: return launch(k_allreduce_zc<T, TO, INT, 2>, a, ctas, threads, s, false);
+        case 4: return launch(k_allreduce_zc<T, TO, INT, 4>, a, ctas, threads, s, false);
+        case 8: return launch(k_allreduce_zc<T, TO, INT, 8>, a, ctas, threads, s, false);
+        default: return launch(k_allreduce_zc<T, TO, INT, 0>, a, ctas, threads, s, false);
+    }
+}
+template <typename T, typename TO, bool INT> int launch_rs_zc(const CollArgs &a, int ctas, int threads, cudaStream_t s)
+{
+    switch (a.team.world) {
+        case 2: return launch(k_reduce_scatter_zc<T, TO, INT, 2>, a, ctas, threads, s, false);
+        case 4: return launch(k_reduce_scatter_zc<T, TO, INT, 4>, a, ctas, threads, s, false);
+        case 8: return launch(k_reduce_scatter_zc<T, TO, INT, 8>, a, ctas, threads, s, false);
+        default: return launch(k_reduce_scatter_zc<T, TO, INT, 0>, a, ctas, threads, s, false);
+    }
+}
 template <typename T, typename TO, bool INT> int launch_rs(const CollArgs &a, int ctas, int threads, cudaStream_t s)
 {
     switch (a.team.world) {
@@ -498,6 +662,42 @@ int mf_coll_launch(int kind, int in_dtype, int out_dtype, const CollArgs *args, 
     const bool same = in_dtype == out_dtype;
     const bool to_bf16 = out_dtype == DT_BF16;
     if (!same && !to_bf16) return -2;
+    if (a.zero_copy == 2) {
+        // direct mode: the buffers named by the operation live inside the callers' own slices; emulation
+        // keeps its per-rank buffers outside the emulated slots, so it has no direct mode
+        if (a.team.emu) return -4;
+        switch (kind) {
+            case 0:
+                if (in_dtype == DT_BF16) return launch_allreduce_zc<__nv_bfloat16, __nv_bfloat16, false>(a, ctas, threads, s);
+                if (in_dtype == DT_F16) return same ? launch_allreduce_zc<__half, __half, false>(a, ctas, threads, s) : -2;
+                if (in_dtype == DT_F32)
+                    return same ? launch_allreduce_zc<float, float, false>(a, ctas, threads, s)
+                                : launch_allreduce_zc<float, __nv_bfloat16, false>(a, ctas, threads, s);
+                if (in_dtype == DT_I32) return same ? launch_allreduce_zc<int, int, true>(a, ctas, threads, s) : -2;
+                return -2;
+            case 1:
+                if (in_dtype == DT_BF16) return launch_rs_zc<__nv_bfloat16, __nv_bfloat16, false>(a, ctas, threads, s);
+                if (in_dtype == DT_F16) return same ? launch_rs_zc<__half, __half, false>(a, ctas, threads, s) : -2;
+                if (in_dtype == DT_F32)
+                    return same ? launch_rs_zc<float, float, false>(a, ctas, threads, s)
+                                : launch_rs_zc<float, __nv_bfloat16, false>(a, ctas, threads, s);
+                if (in_dtype == DT_I32) return same ? launch_rs_zc<int, int, true>(a, ctas, threads, s) : -2;
+                return -2;
+            case 2:
+                if (in_dtype == DT_BF16) return launch(k_allgather_zc<__nv_bfloat16, __nv_bfloat16>, a, ctas, threads, s, false);
+                if (in_dtype == DT_F16) return same ? launch(k_allgather_zc<__half, __half>, a, ctas, threads, s, false) : -2;
+                if (in_dtype == DT_F32)
+                    return same ? launch(k_allgather_zc<float, float>, a, ctas, threads, s, false)
+                                : launch(k_allgather_zc<float, __nv_bfloat16>, a, ctas, threads, s, false);
+                if (in_dtype == DT_I32) return same ? launch(k_allgather_zc<int, int>, a, ctas, threads, s, false) : -2;
+                return -2;
+            case 3:
+                if (in_dtype == DT_F32 || in_dtype == DT_I32) return launch(k_broadcast_zc<float>, a, ctas, threads, s, false);
+                return launch(k_broadcast_zc<__nv_bfloat16>, a, ctas, threads, s, false);
+            default:
+                return -3;
+        }
+    }
     switch (kind) {
         case 0:
             if (in_dtype == DT_BF16) return launch_allreduce<__nv_bfloat16, __nv_bfloat16, false>(a, ctas, threads, s);

@@ -92,7 +92,7 @@ __global__ void k_moe_layout_rank(const int *__restrict__ topk_idx, int T, int K
 // outputs (device, local): recv_per_expert[El], row_off[El + 1], put_off[E], src_off[El][W]
 // All threads of ONE CTA call it. Returns false (uniformly) when the count exchange timed out.
 __device__ __forceinline__ bool notify_body(const Team &team, const MoeHeap &hp, int E, const int *tokens_per_expert, int *recv_per_expert,
-                                            int *row_off, int *put_off, int *src_off, uint32_t epoch)
+                                            int *row_off, int *put_off, int *src_off, uint32_t epoch, uint32_t channel = 8)
 {
     const uint32_t me = team_rank(team);
     const uint32_t W = team.world;
@@ -105,7 +105,7 @@ __device__ __forceinline__ bool notify_body(const Team &team, const MoeHeap &hp,
             reinterpret_cast<int *>(peer_ptr(team, r, hp.counts))[me * E + e] = c;
         }
     }
-    if (!team_barrier(team, me, 8, epoch)) return false;
+    if (!team_barrier(team, me, channel, epoch)) return false;
     const int *tbl = reinterpret_cast<const int *>(peer_ptr(team, me, hp.counts));
     __shared__ int per_expert[1024];  // totals of every expert over all sources
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
@@ -263,7 +263,11 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs &a)
     __syncthreads();
     if (threadIdx.x == 0) {
         const uint32_t done = atomicAdd(a.done_count, 1u) + 1;
-        if (done == gridDim.x * a.seq) {
+        // seq > 0: the counter only grows and the host numbers the calls; seq == 0: the last CTA puts it back
+        // to zero, so the same launch parameters work again (CUDA-graph replay)
+        const bool last = a.seq != 0 ? done == gridDim.x * a.seq : done == gridDim.x;
+        if (last) {
+            if (a.seq == 0) *a.done_count = 0;
             __threadfence_system();
             for (uint32_t r = 0; r < t.world; r++)
                 st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, a.hp.flags)) + me, a.epoch);
@@ -353,24 +357,35 @@ __device__ __forceinline__ void combine_push_body(const CombinePushArgs &a)
     const int rows = *a.rows_dev;
     const int vecs = a.H / 8;
     const int4 *info = reinterpret_cast<const int4 *>(peer_ptr(t, me, a.hp.recv_info));
-    for (int r = blockIdx.x; r < rows; r += gridDim.x) {
+    // one warp per row, four 16-byte loads in flight per lane before the first store: at decode sizes the
+    // push is bound by NVLink latency, so rows must overlap rather than queue behind one another
+    const int lane = threadIdx.x & 31;
+    const int warps = gridDim.x * (blockDim.x >> 5);
+    for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
         const int4 in = __ldcg(info + r);
         const uint32_t home = (uint32_t)in.x;
         if (home >= t.world) continue;
         const float w = a.weighted ? __int_as_float(in.w) : 1.f;
-        __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(peer_ptr(t, home, a.hp.comb)) + ((int64_t)in.y * a.K + in.z) * a.H;
+        uint4 *dst = reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(peer_ptr(t, home, a.hp.comb)) + ((int64_t)in.y * a.K + in.z) * a.H);
         const uint4 *src = reinterpret_cast<const uint4 *>(a.y + (int64_t)r * a.ldy);
-        for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
-            uint4 raw = __ldg(src + v);
-            if (w != 1.f) {
-                __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
+        for (int v0 = lane; v0 < vecs; v0 += 128) {
+            uint4 raw[4];
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    float2 f = __bfloat1622float2(h[e]);
-                    h[e] = __floats2bfloat162_rn(f.x * w, f.y * w);
+            for (int u = 0; u < 4; u++)
+                if (v0 + 32 * u < vecs) raw[u] = __ldg(src + v0 + 32 * u);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (v0 + 32 * u >= vecs) continue;
+                if (w != 1.f) {
+                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw[u]);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        float2 f = __bfloat1622float2(h[e]);
+                        h[e] = __floats2bfloat162_rn(f.x * w, f.y * w);
+                    }
                 }
+                dst[v0 + 32 * u] = raw[u];
             }
-            *(reinterpret_cast<uint4 *>(dst) + v) = raw;
         }
     }
 }
@@ -414,6 +429,9 @@ __device__ __forceinline__ void combine_reduce_body(const Team &t, const MoeHeap
 // group is the order in which the atomics land) and runs the count exchange, the grid then pushes the
 // tokens and CTA 0 waits for every peer's rows. Combine: the grid pushes the expert outputs home, CTA 0
 // signals and waits for all peers, the grid reduces the K slots of each token.
+// The pair numbers its calls with a counter in device memory and uses flag rows and a barrier channel of
+// its own (the caller passes MoeHeap.flags advanced by two rows), so a captured launch can be replayed
+// as a CUDA graph and may be mixed with the multi-launch path on the same buffers.
 // A wait that runs out is recorded in the status word; the kernel still reaches every grid-wide
 // synchronisation and returns (the results of that call are then unspecified).
 struct LLDispatchArgs {
@@ -422,11 +440,14 @@ struct LLDispatchArgs {
     int *recv_per_expert;    // [El]
     int *row_off;            // [El + 1]
     int *src_off;            // [El * W]
+    uint32_t *epoch_dev;     // call counter in device memory: this call uses *epoch_dev + 1 and stores it back at the
+                             // end, so a captured launch can be replayed (d.epoch is ignored, d.seq must be 0)
 };
 
 __global__ void __launch_bounds__(448) k_moe_ll_dispatch(LLDispatchArgs a)
 {
     cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    a.d.epoch = *reinterpret_cast<volatile uint32_t *>(a.epoch_dev) + 1;
     const Team &t = a.d.team;
     const uint32_t me = team_rank(t);
     const int E = a.d.sh.E, n = a.d.sh.T * a.d.sh.K;
@@ -442,11 +463,12 @@ __global__ void __launch_bounds__(448) k_moe_ll_dispatch(LLDispatchArgs a)
         __syncthreads();
         for (int e = threadIdx.x; e < E; e += blockDim.x) a.tokens_per_expert[e] = cnt[e];
         __syncthreads();
-        if (!notify_body(t, a.d.hp, E, a.tokens_per_expert, a.recv_per_expert, a.row_off, const_cast<int *>(a.d.put_off), a.src_off, a.d.epoch))
+        if (!notify_body(t, a.d.hp, E, a.tokens_per_expert, a.recv_per_expert, a.row_off, const_cast<int *>(a.d.put_off), a.src_off, a.d.epoch, 9))
             if (threadIdx.x == 0) atomicCAS(a.d.status, 0, 0x420);
         __threadfence();
     }
-    grid.sync();
+    grid.sync();  // every CTA has read the call counter before this point
+    if (blockIdx.x == 0 && threadIdx.x == 0) *a.epoch_dev = a.d.epoch;
     dispatch_body(a.d);
     if (blockIdx.x == 0 && threadIdx.x < t.world) {
         const uint32_t *f = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, a.d.hp.flags)) + threadIdx.x;
@@ -462,9 +484,10 @@ struct LLCombineArgs {
     MoeShape sh;
     const int *topk_idx;   // [T, K] of this rank's own tokens
     __nv_bfloat16 *out;    // [T, H]
-    uint32_t epoch;
+    uint32_t epoch;        // used when epoch_dev is NULL
     int *status;
     const float *topk_w;   // optional [T, K]: weights applied on the home side
+    const uint32_t *epoch_dev;  // the call counter the matching k_moe_ll_dispatch left behind
 };
 
 __global__ void __launch_bounds__(256) k_moe_ll_combine(LLCombineArgs a)
@@ -472,6 +495,7 @@ __global__ void __launch_bounds__(256) k_moe_ll_combine(LLCombineArgs a)
     cooperative_groups::grid_group grid = cooperative_groups::this_grid();
     const Team &t = a.p.team;
     const uint32_t me = team_rank(t);
+    if (a.epoch_dev != nullptr) a.epoch = *reinterpret_cast<const volatile uint32_t *>(a.epoch_dev);
     combine_push_body(a.p);
     __threadfence_system();
     grid.sync();
@@ -555,12 +579,14 @@ int mf_moe_combine_push(const Team *team, const MoeHeap *hp, const void *y, int6
 }
 
 // Cooperative: ctas must not exceed what the device can hold at once (one CTA per SM is always safe).
-int mf_moe_ll_dispatch(const DispatchArgs *d, int *tokens_per_expert, int *recv_per_expert, int *row_off, int *src_off, int ctas, void *stream)
+int mf_moe_ll_dispatch(const DispatchArgs *d, int *tokens_per_expert, int *recv_per_expert, int *row_off, int *src_off, uint32_t *epoch_dev,
+                       int ctas, void *stream)
 {
+    if (epoch_dev == nullptr || d == nullptr || d->seq != 0) return -1;
     if (d == nullptr || d->team.emu || d->sh.H % 128 != 0 || d->sh.H / 16 > 448 || d->sh.K > 16 || d->sh.E > 1024 ||
         d->sh.E % (int)d->team.world != 0 || ctas <= 0)
         return -1;
-    LLDispatchArgs a{*d, tokens_per_expert, recv_per_expert, row_off, src_off};
+    LLDispatchArgs a{*d, tokens_per_expert, recv_per_expert, row_off, src_off, epoch_dev};
     void *params[] = {&a};
     cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(k_moe_ll_dispatch), dim3(ctas), dim3(448), params, 0,
                                                 (cudaStream_t)stream);
@@ -568,11 +594,12 @@ int mf_moe_ll_dispatch(const DispatchArgs *d, int *tokens_per_expert, int *recv_
 }
 
 int mf_moe_ll_combine(const Team *team, const MoeHeap *hp, const MoeShape *sh, const void *y, int64_t ldy, const int *rows_dev, int weighted,
-                      const int *topk_idx, const float *topk_w, void *out, uint32_t epoch, int *status, int ctas, void *stream)
+                      const int *topk_idx, const float *topk_w, void *out, uint32_t epoch, const uint32_t *epoch_dev, int *status, int ctas,
+                      void *stream)
 {
     if (team == nullptr || hp == nullptr || sh == nullptr || team->emu || sh->H % 8 != 0 || ctas <= 0) return -1;
     LLCombineArgs a{{*team, *hp, static_cast<const __nv_bfloat16 *>(y), ldy, rows_dev, sh->H, sh->K, weighted}, *sh, topk_idx,
-                    static_cast<__nv_bfloat16 *>(out), epoch, status, topk_w};
+                    static_cast<__nv_bfloat16 *>(out), epoch, status, topk_w, epoch_dev};
     void *params[] = {&a};
     cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(k_moe_ll_combine), dim3(ctas), dim3(256), params, 0,
                                                 (cudaStream_t)stream);

@@ -33,6 +33,8 @@ constexpr uint32_t kStatusOff = 0;
 constexpr uint32_t kBarrierOff = 4096;
 constexpr uint32_t kLaneOff = 128 * 1024;
 constexpr int kPhases = 4;
+//   [256 KiB, 256 KiB + 64 KiB)  address exchange [cta 0..255][rank 0..15] x {u64, u64}
+constexpr uint32_t kXchgOff = 256 * 1024;
 
 enum MfStatus : uint32_t { ST_OK = 0, ST_TIMEOUT = 1, ST_BAD_ARG = 2 };
 
@@ -109,6 +111,42 @@ __device__ __forceinline__ bool lane_sync(const Team &t, uint32_t me, int phase,
         if (!wait_flag(mine, epoch, t.spin_limit)) {
             ok_sh = 0;
             report_timeout(t, me, where, epoch);
+        }
+    }
+    __syncthreads();
+    return ok_sh != 0;
+}
+
+// lane_sync that also swaps two 64-bit values (buffer offsets inside the senders' slots) between the
+// CTAs of one lane: thread r stores this rank's pair into rank r's exchange row before it raises the
+// flag there (the release orders the two), and reads rank r's pair from the own row after the acquire.
+// peer_a / peer_b are shared-memory arrays of kMaxRanks entries, valid for every thread on return.
+// The row is reused by the next call: callers end with another lane_sync, after which nobody reads it.
+__device__ __forceinline__ bool lane_sync_xchg(const Team &t, uint32_t me, int phase, uint32_t epoch, uint32_t where, uint64_t my_a,
+                                               uint64_t my_b, uint64_t *peer_a, uint64_t *peer_b)
+{
+    __shared__ int ok_sh;
+    __threadfence_system();
+    __syncthreads();
+    const uint32_t lane = blockIdx.x;
+    const uint64_t off = kLaneOff + (((uint64_t)phase * kMaxCtas + lane) * kMaxRanks) * sizeof(uint32_t);
+    const uint64_t xoff = kXchgOff + ((uint64_t)lane * kMaxRanks) * sizeof(ulonglong2);
+    if (threadIdx.x == 0) ok_sh = 1;
+    __syncthreads();
+    if (threadIdx.x < t.world) {
+        const uint32_t r = threadIdx.x;
+        *(reinterpret_cast<ulonglong2 *>(peer_ptr(t, r, xoff)) + me) = make_ulonglong2(my_a, my_b);
+        st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, off)) + me, epoch);
+        const uint32_t *mine = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, off)) + r;
+        if (!wait_flag(mine, epoch, t.spin_limit)) {
+            ok_sh = 0;
+            report_timeout(t, me, where, epoch);
+            peer_a[r] = 0;
+            peer_b[r] = 0;
+        } else {
+            const volatile ulonglong2 *row = reinterpret_cast<const volatile ulonglong2 *>(peer_ptr(t, me, xoff)) + r;
+            peer_a[r] = row->x;
+            peer_b[r] = row->y;
         }
     }
     __syncthreads();

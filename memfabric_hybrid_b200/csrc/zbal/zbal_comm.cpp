@@ -27,10 +27,11 @@ namespace zbal {
 int Comm::Ctas(uint64_t bytes) const
 {
     int c;
-    if (bytes <= (32u << 10)) c = 1;
-    else if (bytes <= (256u << 10)) c = 4;
-    else if (bytes <= (2u << 20)) c = 16;
-    else if (bytes <= (16u << 20)) c = 64;
+    if (bytes <= (16u << 10)) c = 1;
+    else if (bytes <= (64u << 10)) c = 4;
+    else if (bytes <= (256u << 10)) c = 16;
+    else if (bytes <= (1u << 20)) c = 32;
+    else if (bytes <= (8u << 20)) c = 64;
     else c = maxCtas;
     return std::max(1, std::min(c, maxCtas));
 }
@@ -124,11 +125,31 @@ MfCollArgs BaseArgs(Comm &c, const void *in, void *out, uint64_t n, float scale,
 
 constexpr uint64_t kOneShotMax = 256u << 10;
 
+// Direct mode: a buffer that lies inside this rank's slice of the symmetric heap (a tensor from the
+// symmetric allocator) is reachable by the peers, so the kernels skip the staging copies. Small payloads
+// stay on the staged path: it needs one handshake where direct mode needs two.
+bool InSlice(const void *p, uint64_t bytes)
+{
+    State &st = S();
+    const uint64_t a = reinterpret_cast<uint64_t>(p);
+    return p != nullptr && a >= st.out.localGva && a + bytes <= st.out.localGva + st.opts.deviceMemorySize;
+}
+uint64_t DirectMin()
+{
+    static const uint64_t v = (uint64_t)mf::EnvInt("ZBAL_DIRECT_MIN_BYTES", nullptr, 256 << 10, 0, INT64_MAX);
+    return v;
+}
+
 int AllReduce(Comm &c, const void *in, void *out, uint64_t n, int kdt, int odt, uint32_t es, uint32_t oes, int op, float scale, void *stream)
 {
     const Launchers *L = GetLaunchers();
     if (L == nullptr) return Z_NOT_SUPPORTED;
     std::lock_guard<std::mutex> g(c.mu);
+    if (n * es > DirectMin() && InSlice(in, n * es) && InSlice(out, n * oes)) {
+        MfCollArgs a = BaseArgs(c, in, out, n, scale, op, 0, 1);
+        a.zero_copy = 2;
+        return Launched(L->coll(0, kdt, odt, &a, c.Ctas(n * es), 512, stream), "all_reduce (direct)");
+    }
     uint64_t piece = c.stageBytes / std::max(es, oes);
     piece -= piece % (8ull * c.size);
     uint64_t done = 0;
@@ -154,6 +175,11 @@ int AllGatherBytes(Comm &c, const void *in, void *out, uint64_t bytes, void *str
         return MF_FAIL(Z_NOT_SUPPORTED, "all_gather: %lu bytes per member at odd addresses or of odd size", (unsigned long)bytes);
     std::lock_guard<std::mutex> g(c.mu);
     const uint64_t m = bytes / unit;
+    if (bytes * c.size > DirectMin() && InSlice(out, bytes * c.size)) {
+        MfCollArgs a = BaseArgs(c, in, out, m, 1.f, 0, 0, 0);
+        a.zero_copy = 2;
+        return Launched(L->coll(2, kdt, kdt, &a, c.Ctas(bytes * c.size), 512, stream), "all_gather (direct)");
+    }
     uint64_t piece = c.stageBytes / unit / c.size;
     piece -= piece % 8;
     // a payload larger than the staging is gathered piece by piece: piece [done, done + cnt) of member r
@@ -180,6 +206,11 @@ int BroadcastBytes(Comm &c, const void *in, void *out, uint64_t bytes, uint32_t 
         return MF_FAIL(Z_NOT_SUPPORTED, "broadcast: %lu bytes at odd addresses or of odd size", (unsigned long)bytes);
     std::lock_guard<std::mutex> g(c.mu);
     const uint64_t total = bytes / unit;
+    if (bytes > DirectMin() && InSlice(out, bytes)) {
+        MfCollArgs a = BaseArgs(c, in, out, total, 1.f, 0, root, 0);
+        a.zero_copy = 2;
+        return Launched(L->coll(3, kdt, kdt, &a, c.Ctas(bytes), 512, stream), "broadcast (direct)");
+    }
     uint64_t piece = c.stageBytes / unit;
     piece -= piece % 8;
     uint64_t done = 0;
@@ -431,6 +462,11 @@ int32_t zbal_reduce_scatter(const void *send, void *recv, size_t recv_count, zba
     if (L == nullptr) return Z_NOT_SUPPORTED;
     std::lock_guard<std::mutex> g(c->mu);
     const uint64_t m = recv_count;
+    if (m * c->size * ti.size > DirectMin() && InSlice(send, m * c->size * ti.size)) {
+        MfCollArgs a = BaseArgs(*c, send, recv, m * c->size, 1.f, kop, 0, 0);
+        a.zero_copy = 2;
+        return Launched(L->coll(1, ti.kdt, ti.kdt, &a, c->Ctas(m * c->size * ti.size), 512, stream), "reduce_scatter (direct)");
+    }
     uint64_t piece = c->stageBytes / ti.size / c->size;
     piece -= piece % 8;
     // pieces are column blocks of the [members, m] view of the input: rows stay m apart (part_stride)

@@ -23,6 +23,7 @@ from .heap import TeamC, _HeapBase
 DT = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2, torch.int32: 3}
 OPS = {"sum": 0, "max": 1, "min": 2, "prod": 3}
 ONE_SHOT_MAX = 256 << 10
+DIRECT_MIN = 256 << 10  # above this, buffers that live in the heap are used in place (no staging copies)
 
 
 class CollArgsC(C.Structure):
@@ -102,13 +103,15 @@ class Communicator:
         return self._epoch, self._sets[self._epoch & 1]
 
     def _ctas(self, nbytes: int) -> int:
-        if nbytes <= 32 << 10:
+        if nbytes <= 16 << 10:
             c = 1
-        elif nbytes <= 256 << 10:
+        elif nbytes <= 64 << 10:
             c = 4
-        elif nbytes <= 2 << 20:
+        elif nbytes <= 256 << 10:
             c = 16
-        elif nbytes <= 16 << 20:
+        elif nbytes <= 1 << 20:
+            c = 32
+        elif nbytes <= 8 << 20:
             c = 64
         else:
             c = self.max_ctas
@@ -126,6 +129,14 @@ class Communicator:
         xin, xs, _ = self._local(x)
         xo, os_, _ = self._local(out)
         return CollArgsC(self.heap.team(), xin, xo, xs, os_, n, stage[0], stage[1], float(scale), OPS[op], epoch, 0, root, algo, 0)
+
+    def _in_heap(self, t: torch.Tensor) -> bool:
+        """True when the tensor lies inside this rank's slice of a real symmetric heap (peers can reach it)."""
+        if self.heap.emu:
+            return False
+        lo = self.heap.base + self.rank * self.heap.stride
+        p = t.data_ptr()
+        return lo <= p and p + t.numel() * t.element_size() <= lo + getattr(self.heap, "usable", self.heap.stride)
 
     def _empty_like(self, x: torch.Tensor, per_rank_numel: int, dtype: torch.dtype) -> torch.Tensor:
         if self.heap.emu:
@@ -145,6 +156,13 @@ class Communicator:
         if out is None:
             out = self._empty_like(x, n, od)
         es = x.element_size()
+        if algo in (None, "direct") and n * es > DIRECT_MIN and self._in_heap(x) and self._in_heap(out):
+            epoch, stage = self._next()
+            args = self._args(x, out, n, epoch, stage, scale, op, 0, 1)
+            args.zero_copy = 2
+            _check(_cu().mf_coll_launch(0, DT[x.dtype], DT[od], C.byref(args), self._ctas(n * es), 512, _stream()), "all_reduce (direct)")
+            return out
+        assert algo != "direct", "direct mode needs input and output inside the symmetric heap"
         piece = self.stage_bytes // max(es, out.element_size())
         piece -= piece % (8 * self.world)
         a = {"oneshot": 0, "twoshot": 1, None: None}[algo]
@@ -169,6 +187,12 @@ class Communicator:
         if out is None:
             out = self._empty_like(x, m, od)
         es = x.element_size()
+        if n * es > DIRECT_MIN and self._in_heap(x):
+            epoch, stage = self._next()
+            args = self._args(x, out, n, epoch, stage, scale, op)
+            args.zero_copy = 2
+            _check(_cu().mf_coll_launch(1, DT[x.dtype], DT[od], C.byref(args), self._ctas(n * es), 512, _stream()), "reduce_scatter (direct)")
+            return out
         # a piece is a column block [c0, c1) of the [world, m] view: staged as world rows of (c1 - c0)
         piece = self.stage_bytes // es // self.world
         piece -= piece % 8
@@ -194,6 +218,13 @@ class Communicator:
         if out is None:
             out = self._empty_like(x, m * self.world, od)
         oes = out.element_size()
+        if m * self.world * oes > DIRECT_MIN and self._in_heap(out):
+            epoch, stage = self._next()
+            args = self._args(x, out, m, epoch, stage, scale)
+            args.zero_copy = 2
+            _check(_cu().mf_coll_launch(2, DT[x.dtype], DT[od], C.byref(args), self._ctas(m * self.world * oes), 512, _stream()),
+                   "all_gather (direct)")
+            return out
         piece = self.stage_bytes // oes // self.world
         piece -= piece % 8
         if m <= piece:

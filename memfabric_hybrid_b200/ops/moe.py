@@ -60,9 +60,9 @@ def _cu():
         l.mf_moe_combine_push.restype = ci
         l.mf_moe_combine_push.argtypes = [P(TeamC), P(MoeHeapC), vp, C.c_int64, vp, ci, ci, ci, ci, vp]
         l.mf_moe_ll_dispatch.restype = ci
-        l.mf_moe_ll_dispatch.argtypes = [P(DispatchArgsC), vp, vp, vp, vp, ci, vp]
+        l.mf_moe_ll_dispatch.argtypes = [P(DispatchArgsC), vp, vp, vp, vp, vp, ci, vp]
         l.mf_moe_ll_combine.restype = ci
-        l.mf_moe_ll_combine.argtypes = [P(TeamC), P(MoeHeapC), P(MoeShapeC), vp, C.c_int64, vp, ci, vp, vp, vp, C.c_uint32, vp, ci, vp]
+        l.mf_moe_ll_combine.argtypes = [P(TeamC), P(MoeHeapC), P(MoeShapeC), vp, C.c_int64, vp, ci, vp, vp, vp, C.c_uint32, vp, vp, ci, vp]
         l.mf_quant_rows_fp8.restype = ci
         l.mf_quant_rows_fp8.argtypes = [vp, C.c_int64, vp, ci, vp, vp, ci, vp]
         l.mf_grouped_gemm_fp8.restype = ci
@@ -140,7 +140,6 @@ class MoEComm:
         self._done = torch.zeros(1, dtype=torch.int32, device=self.dev)
         self._dispatches = 0
         self._ll_done = torch.zeros(1, dtype=torch.int32, device=self.dev)
-        self._ll_calls = 0
         self._ll_grid = None
         self._grid = sm_count(self.dev)
         self._inter = intermediate
@@ -242,28 +241,35 @@ class MoEComm:
         _ok(_cu().mf_moe_signal_all(C.byref(team), C.byref(self.hp), 1, st.epoch, _s()), "moe_signal")
 
     # ------------------------------------------------------------------ low-latency pair (one cooperative launch each)
+    def _ll_setup(self):
+        if self._ll_grid is None:
+            self._ll_grid = max(1, min(self.T, self._grid))  # fixed for the life of the object
+            d = self.dev
+            i32 = torch.int32
+            self._ll_epoch = torch.zeros(1, dtype=i32, device=d)   # call counter of the pair, advanced by the kernel
+            self._ll_bufs = dict(sidx=torch.zeros(self.T * self.K, dtype=i32, device=d), tpe=torch.zeros(self.E, dtype=i32, device=d),
+                                 rpe=torch.zeros(self.El, dtype=i32, device=d), row_off=torch.zeros(self.El + 1, dtype=i32, device=d),
+                                 put_off=torch.zeros(self.E, dtype=i32, device=d), src_off=torch.zeros(self.El * self.world, dtype=i32, device=d))
+            hp = MoeHeapC.from_buffer_copy(self.hp)
+            hp.flags += 2 * 16 * 4  # flag rows 2 and 3 belong to the low-latency pair
+            self._ll_hp = hp
+
     def ll_dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor) -> DispatchState:
+        """One cooperative launch. The outputs live in buffers owned by this object (overwritten by the next call)
+        and nothing depends on host-side counters, so the call may be captured in a CUDA graph and replayed."""
         assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == self.H and x.shape[0] <= self.T
         T = x.shape[0]
-        idx = topk_idx.to(torch.int32).contiguous()
-        w = topk_w.to(torch.float32).contiguous()
-        self._epoch += 1
-        self._ll_calls += 1
-        if self._ll_grid is None:
-            self._ll_grid = max(1, min(self.T, self._grid))  # fixed for the life of the object: the completion counter counts CTAs
-        sidx = torch.empty(T * self.K, dtype=torch.int32, device=self.dev)
-        tpe = torch.empty(self.E, dtype=torch.int32, device=self.dev)
-        rpe = torch.empty(self.El, dtype=torch.int32, device=self.dev)
-        row_off = torch.empty(self.El + 1, dtype=torch.int32, device=self.dev)
-        put_off = torch.empty(self.E, dtype=torch.int32, device=self.dev)
-        src_off = torch.empty(self.El * self.world, dtype=torch.int32, device=self.dev)
-        a = DispatchArgsC(self.heap.team(), self.hp, self._shape(T), x.data_ptr(), idx.data_ptr(), w.data_ptr(), sidx.data_ptr(),
-                          put_off.data_ptr(), self._ll_done.data_ptr(), self._epoch, self._ll_calls, status_word(self.dev).data_ptr(),
+        self._ll_setup()
+        idx = topk_idx if topk_idx.dtype == torch.int32 and topk_idx.is_contiguous() else topk_idx.to(torch.int32).contiguous()
+        w = topk_w if topk_w.dtype == torch.float32 and topk_w.is_contiguous() else topk_w.to(torch.float32).contiguous()
+        b = self._ll_bufs
+        a = DispatchArgsC(self.heap.team(), self._ll_hp, self._shape(T), x.data_ptr(), idx.data_ptr(), w.data_ptr(), b["sidx"].data_ptr(),
+                          b["put_off"].data_ptr(), self._ll_done.data_ptr(), 0, 0, status_word(self.dev).data_ptr(),
                           1 if self.raw_bf16 else 0)
         self._keep = (w, idx)
-        _ok(_cu().mf_moe_ll_dispatch(C.byref(a), tpe.data_ptr(), rpe.data_ptr(), row_off.data_ptr(), src_off.data_ptr(), self._ll_grid, _s()),
-            "moe_ll_dispatch")
-        return DispatchState(T, idx, sidx, tpe, None, None, rpe, row_off, put_off, src_off, self._epoch)
+        _ok(_cu().mf_moe_ll_dispatch(C.byref(a), b["tpe"].data_ptr(), b["rpe"].data_ptr(), b["row_off"].data_ptr(), b["src_off"].data_ptr(),
+                                     self._ll_epoch.data_ptr(), self._ll_grid, _s()), "moe_ll_dispatch")
+        return DispatchState(T, idx, b["sidx"], b["tpe"], None, None, b["rpe"], b["row_off"], b["put_off"], b["src_off"], -1)
 
     def ll_combine(self, y: torch.Tensor, st: DispatchState, weighted: bool = True, out: torch.Tensor | None = None,
                    home_weights: torch.Tensor | None = None) -> torch.Tensor:
@@ -273,7 +279,8 @@ class MoEComm:
             out = torch.empty((st.T, self.H), dtype=torch.bfloat16, device=self.dev)
         team, sh = self.heap.team(), self._shape(st.T)
         hw = home_weights.to(torch.float32).contiguous() if home_weights is not None else None
-        _ok(_cu().mf_moe_ll_combine(C.byref(team), C.byref(self.hp), C.byref(sh), y.data_ptr(), y.stride(0), st.row_off[self.El:].data_ptr(),
-                                    1 if weighted else 0, st.topk_idx.data_ptr(), hw.data_ptr() if hw is not None else None, out.data_ptr(), st.epoch, status_word(self.dev).data_ptr(),
+        _ok(_cu().mf_moe_ll_combine(C.byref(team), C.byref(self._ll_hp), C.byref(sh), y.data_ptr(), y.stride(0), st.row_off[self.El:].data_ptr(),
+                                    1 if weighted else 0, st.topk_idx.data_ptr(), hw.data_ptr() if hw is not None else None, out.data_ptr(), 0, self._ll_epoch.data_ptr(),
+                                    status_word(self.dev).data_ptr(),
                                     self._ll_grid or self._grid, _s()), "moe_ll_combine")
         return out

@@ -151,6 +151,25 @@ def _real_ranks(rank, world, url, sync):
     assert torch.equal(rs, torch.full((1024,), float(sum(range(1, world + 1))), device="cuda"))
     ag = c.all_gather(torch.full((512,), float(rank), device="cuda"))
     assert torch.equal(ag.view(world, 512)[:, 0].cpu(), torch.arange(world, dtype=torch.float32))
+    # direct mode: tensors that live in the heap are read and written in place by the peers (no staging)
+    n = 1_000_000
+    hx = heap.view(heap.alloc(n * 2), (n,), torch.bfloat16)
+    ho = heap.view(heap.alloc(n * 2), (n,), torch.bfloat16)
+    hx.copy_(draw(rank, n))
+    ref = sum(draw(r, n).float() for r in range(world)) / world
+    c.all_reduce(hx, out=ho, scale=1.0 / world, algo="direct")
+    torch.testing.assert_close(ho.float(), ref, rtol=2e-2, atol=2e-2)
+    c.all_reduce(hx, out=hx, scale=1.0 / world)  # in place
+    torch.testing.assert_close(hx.float(), ref, rtol=2e-2, atol=2e-2)
+    m = 200_000
+    fx = heap.view(heap.alloc(world * m * 4), (world * m,), torch.float32)
+    fx.copy_(torch.arange(world * m, device="cuda", dtype=torch.float32) % 1000 + rank)
+    rs = c.reduce_scatter(fx)
+    exp = (torch.arange(rank * m, (rank + 1) * m, device="cuda", dtype=torch.float32) % 1000) * world + sum(range(world))
+    torch.testing.assert_close(rs, exp, rtol=1e-6, atol=1e-3)
+    go = heap.view(heap.alloc(world * m * 4), (world * m,), torch.float32)
+    c.all_gather(torch.full((m,), float(rank), device="cuda"), out=go)
+    assert torch.equal(go.view(world, m)[:, m - 1].cpu(), torch.arange(world, dtype=torch.float32))
     # ring send/recv
     msg = torch.full((100_000,), float(rank), device="cuda")
     got = torch.empty_like(msg)
