@@ -1,0 +1,92 @@
+"""Resharding plans (pure functions) and the three executors on CPU: gloo ranks for the process-group
+executors, a host-DRAM BigMemory pool for the memory-fabric executor."""
+import os
+
+import pytest
+import torch
+
+from conftest import free_port
+from mp_util import run_ranks
+
+
+def test_overlaps_cover_everything_once():
+    from memfabric_hybrid_b200.tensor_rtl import overlaps, shard_bounds
+    for size, old, new in ((4096, [0, 1, 2, 3], [4, 5]), (10, [0, 1, 2], [0, 1, 2, 3]), (7, [3], [0, 1, 2]), (12, [0, 1], [1, 0])):
+        pieces = overlaps(size, old, new)
+        cover = sorted((lo, hi) for _, _, lo, hi in pieces)
+        assert cover[0][0] == 0 and cover[-1][1] == size
+        assert all(cover[i][1] == cover[i + 1][0] for i in range(len(cover) - 1))
+        for src, dst, lo, hi in pieces:
+            a = shard_bounds(size, len(old), old.index(src))
+            b = shard_bounds(size, len(new), new.index(dst))
+            assert a[0] <= lo < hi <= a[1] and b[0] <= lo < hi <= b[1]
+
+
+def test_validation_and_pack_roundtrip():
+    from memfabric_hybrid_b200.tensor_rtl import PTensor, pack_tensors, unpack_tensors
+    t = torch.zeros(4, 6)
+    with pytest.raises(ValueError):
+        PTensor(t, torch.float32, 2, [0, 1], (8, 6), 0, rank=0, backend="smoke signals")
+    with pytest.raises(ValueError):
+        PTensor(t, torch.float32, 2, [0, 0], (8, 6), 0, rank=0)
+    with pytest.raises(ValueError):
+        PTensor(t, torch.float32, 2, [0, 1], (12, 6), 0, rank=0)   # rank 0 would hold 6 rows, not 4
+    ts = [torch.arange(7, dtype=torch.int32), torch.randn(3, 5).to(torch.bfloat16), torch.tensor([1.5], dtype=torch.float64)]
+    packed, meta = pack_tensors(ts, torch.int32)
+    assert packed.dtype == torch.int32
+    back = unpack_tensors(packed, meta)
+    assert all(torch.equal(a, b) and a.dtype == b.dtype for a, b in zip(ts, back))
+
+
+def _global(shape, seed):
+    return torch.arange(int(torch.tensor(shape).prod()), dtype=torch.float32).reshape(shape) + seed * 1000
+
+
+def _reshard(rank, world, port, kind):
+    import torch.distributed as dist
+    from memfabric_hybrid_b200.tensor_rtl import (All2AllVExcutor, BatchP2PExecutor, MemoryFabricExecutor, MfBmConfig, PTensor, PTensorSet)
+    os.environ["MF_DEVICE_BACKEND"] = "none"
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    # three tensors: rows TP4 (ranks 0-3) -> TP2 (ranks 2, 3); columns TP2 (0, 1) -> TP4 (all, uneven 10 columns); replicated -> rank 3
+    specs = [((8, 6), 0, [0, 1, 2, 3], [2, 3]), ((4, 10), 1, [0, 1], [0, 1, 2, 3]), ((5,), -1, [0, 1], [3])]
+    backend = "mf" if kind == "mf" else "gloo"
+    pts = []
+    for i, (shape, dim, old, new) in enumerate(specs):
+        full = _global(shape, i)
+        shard = None
+        if rank in old:
+            shard = full if dim < 0 else full.chunk(len(old), dim)[old.index(rank)].contiguous()
+        pts.append(PTensor(shard, torch.float32, len(shape), old, shape, dim, rank=rank, backend=backend))
+    ps = PTensorSet(pts)
+    ps.transfer_map([s[3] for s in specs])
+    if kind == "p2p":
+        ex = BatchP2PExecutor()
+    elif kind == "a2a":
+        ex = All2AllVExcutor()
+    else:
+        ex = MemoryFabricExecutor(MfBmConfig(url=f"tcp://127.0.0.1:{port + 1}", local_dram_size=8 << 20, rank_world_size=world), rank_id=rank)
+    ex.execute(ps.get_transfer_list())
+    ex.wait()
+    got = ps.collect_tensor()
+    for i, (shape, dim, old, new) in enumerate(specs):
+        full = _global(shape, i)
+        if rank in new:
+            if dim < 0:
+                exp = full
+            else:
+                n, j = len(new), new.index(rank)
+                lo, hi = shape[dim] * j // n, shape[dim] * (j + 1) // n
+                exp = full.narrow(dim, lo, hi - lo)
+            assert got[i] is not None and torch.equal(got[i], exp), f"tensor {i} on rank {rank}: {got[i]} vs {exp}"
+        else:
+            assert got[i] is None
+    dist.barrier()
+    if kind == "mf":
+        MemoryFabricExecutor.shutdown()
+    dist.destroy_process_group()
+    return True
+
+
+@pytest.mark.parametrize("kind", ["p2p", "a2a", "mf"])
+def test_reshard_executors(kind):
+    assert run_ranks(_reshard, 4, (free_port(), kind), timeout=180) == [True] * 4
