@@ -129,6 +129,9 @@ public:
         reconnectTries_ = tries;
         reconnectIntervalMs_ = intervalMs;
     }
+    // The first dial of Startup announces itself as a reconnect: for a process that was a member before
+    // and now reaches a NEW server (HA fail-over), which admits only returning ranks while it recovers.
+    void SetDialAsReconnect(bool on) { dialAsReconnect_ = on; }
 
 private:
     struct Pending {
@@ -174,6 +177,7 @@ private:
     std::atomic<bool> reconnecting_{false};
     uint32_t reconnectTries_ = 60;
     uint32_t reconnectIntervalMs_ = 1000;
+    bool dialAsReconnect_ = false;
 };
 
 // -------------------------------------------------------------------------------------------------

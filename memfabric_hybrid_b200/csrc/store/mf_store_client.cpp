@@ -57,7 +57,7 @@ int TcpStoreClient::Startup(uint32_t timeoutMs, uint32_t maxRetry)
     uint64_t deadline = NowMs() + timeoutMs;
     uint32_t tries = 0;
     for (;;) {
-        rc = Dial(false, std::min<uint32_t>(timeoutMs == 0 ? 1000 : timeoutMs, 3000));
+        rc = Dial(dialAsReconnect_, std::min<uint32_t>(timeoutMs == 0 ? 1000 : timeoutMs, 3000));
         if (rc == OK) break;
         tries++;
         if (NowMs() >= deadline || (maxRetry != 0 && tries >= maxRetry)) {

@@ -91,6 +91,7 @@ int HaConfigStore::FollowLeader(const std::string &addr)
     if (!net::ParseIpPort(addr, ip, port)) return ERR_INVALID_PARAM;
     auto c = std::make_shared<TcpStoreClient>(ip, port, worldSize_, rank_);
     c->SetReconnectPolicy(0, 0);  // the HA layer re-elects instead of re-dialling a dead leader
+    c->SetDialAsReconnect(everFollowed_.load());  // a returning member: admitted while the new leader recovers
     int rc = c->Startup(2000);
     if (rc != OK) return rc;
     std::weak_ptr<HaConfigStore> weak = weak_from_this();
@@ -104,6 +105,7 @@ int HaConfigStore::FollowLeader(const std::string &addr)
         leaderAddr_ = addr;
         ws = watches_;
     }
+    everFollowed_ = true;
     for (auto &kv : ws) {  // re-arm watches on the new leader
         uint32_t inner = 0;
         if (kv.second.rankFn) c->WatchRankState(kv.second.rankFn, inner);

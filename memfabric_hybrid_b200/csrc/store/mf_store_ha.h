@@ -74,6 +74,7 @@ private:
     std::mutex cvMu_;
     std::condition_variable cv_;
     std::atomic<bool> reelect_{false};
+    std::atomic<bool> everFollowed_{false};
     std::vector<ReconnectFn> reconnectFns_;
     std::vector<BrokenFn> brokenFns_;
     struct SavedWatch {
