@@ -65,7 +65,8 @@ def _rank(rank, world, url, sync):
     assert bad != 0
     mf.get_and_clear_last_err_msg()
     sync.wait(60)
-    assert h.leave() == 0
+    rc = h.leave()
+    assert rc == 0, f"leave returned {rc}: {mf.get_last_err_msg()}"
     h.destroy()
     bm.uninitialize(0)
     mf.uninitialize()

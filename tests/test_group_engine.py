@@ -8,7 +8,6 @@ import time
 
 import pytest
 
-os.environ.setdefault("MF_STORE_HEARTBEAT_MS", "100")
 
 import hooks as H  # noqa: E402
 from conftest import free_port  # noqa: E402

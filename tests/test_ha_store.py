@@ -5,7 +5,6 @@ import ctypes as C
 import os
 import time
 
-os.environ.setdefault("MF_STORE_HEARTBEAT_MS", "100")
 
 import hooks as H  # noqa: E402
 from conftest import free_port  # noqa: E402
