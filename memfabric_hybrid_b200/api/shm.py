@@ -29,6 +29,7 @@ def _decls(l):
     N._sig(l, "smem_shm_atomic_release_value", N.i32, N.vp, N.i32)
     N._sig(l, "smem_shm_register_exit", N.i32, N.vp, N.EXIT_FN)
     N._sig(l, "smem_shm_global_exit", None, N.vp, C.c_int)
+    N._sig(l, "smem_shm_get_device_context", N.i32, N.vp, N.vp, N.u32)
 
 
 class ShmDataOpType(enum.IntFlag):
@@ -62,6 +63,15 @@ def initialize(store_url: str, world_size: int, rank_id: int, device_id: int, co
 
 def uninitialize(flags: int = 0) -> None:
     N.lib().smem_shm_uninit(flags)
+
+
+class ShmDeviceContext(C.Structure):
+    """Mirror of ``smem_shm_device_ctx_t``."""
+    _fields_ = [("base", C.c_uint64), ("symmetric_size", C.c_uint64), ("mc_base", C.c_uint64), ("rank", C.c_uint32),
+                ("rank_size", C.c_uint32), ("reserved", C.c_uint32), ("spin_limit", C.c_uint32)]
+
+
+USER_OFFSET = 1 << 20  # the first MiB of every slice holds the flags of the device API
 
 
 class ShareMemory:
@@ -136,6 +146,14 @@ class ShareMemory:
 
     def atomic_release_value(self, value: int) -> int:
         return N.lib().smem_shm_atomic_release_value(self._h, value)
+
+    def device_context(self) -> "ShmDeviceContext":
+        """The block a kernel takes by value to use the device API (csrc/include/smem_shm_device.cuh)."""
+        ctx = ShmDeviceContext()
+        rc = N.lib().smem_shm_get_device_context(self._h, C.byref(ctx), C.sizeof(ctx))
+        if rc != 0:
+            raise RuntimeError(f"smem_shm_get_device_context failed ({rc}): {N.last_error()}")
+        return ctx
 
     def register_exit(self, fn) -> int:
         self._exit_cb = N.EXIT_FN(fn)

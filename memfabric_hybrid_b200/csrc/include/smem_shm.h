@@ -55,6 +55,9 @@ int32_t smem_shm_atomic_alloc_value(smem_shm_t handle, uint32_t limit, int32_t *
 int32_t smem_shm_atomic_release_value(smem_shm_t handle, int32_t value);
 int32_t smem_shm_register_exit(smem_shm_t handle, void (*exit)(int));
 void smem_shm_global_exit(smem_shm_t handle, int status);
+/* Fills the block a kernel takes by value to use the device API (smem_shm_device.cuh: smem_shm_device_ctx_t,
+ * 40 bytes). The reference publishes the same facts in a meta region at a fixed address instead. */
+int32_t smem_shm_get_device_context(smem_shm_t handle, void *ctx, uint32_t ctxSize);
 
 #ifdef __cplusplus
 }

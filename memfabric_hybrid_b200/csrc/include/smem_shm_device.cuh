@@ -1,0 +1,87 @@
+/*
+ * Device-side API of the symmetric shared memory (SHM): what a user kernel needs to reach its peers'
+ * slices and to synchronise with them.
+ *
+ *   __global__ void k(smem_shm_device_ctx_t ctx, float *mine, ...)   // ctx comes from smem_shm_get_device_context()
+ *   {
+ *       float *theirs = smem_shm_peer_ptr(ctx, mine, peer);          // same object in the peer's slice
+ *       ...
+ *       if (!smem_shm_barrier(ctx, epoch)) return;                   // bounded: false = a peer did not arrive
+ *   }
+ *
+ * Addressing rule: an object at address p of this rank's slice lives at p + (peer - my_rank) * symmetric_size
+ * on the peer (the rule of the reference's device API, src/smem/include/device/ of the reference, and of
+ * examples/hbm_share_memory there). Loads and stores to that address travel over NVLink.
+ * Synchronisation: the first 1 MiB of every slice is reserved for flags (status words, barrier rows);
+ * user data starts at SMEM_SHM_USER_OFFSET. Flags carry call numbers ("epochs") that the caller
+ * increases by one per call, so nothing has to be cleared between calls. Every wait gives up after
+ * ctx.spin_limit polls, writes a status code into the slice's status words (read them with
+ * smem_shm_device_status on the host) and returns false; nothing traps and nothing spins forever.
+ */
+#ifndef MF_B200_SMEM_SHM_DEVICE_CUH
+#define MF_B200_SMEM_SHM_DEVICE_CUH
+
+#include <stdint.h>
+
+#define SMEM_SHM_USER_OFFSET (1u << 20)
+
+typedef struct {
+    uint64_t base;           /* address of rank 0's slice */
+    uint64_t symmetric_size; /* bytes between consecutive ranks' slices */
+    uint64_t mc_base;        /* multicast alias, 0 when not bound */
+    uint32_t rank;
+    uint32_t rank_size;
+    uint32_t reserved;       /* must be 0 */
+    uint32_t spin_limit;     /* polls before a wait gives up (about 0.5 us each once it backs off) */
+} smem_shm_device_ctx_t;
+
+#ifdef __CUDACC__
+#include "../kernels/mf_team.cuh"
+
+__device__ __forceinline__ uint32_t smem_shm_get_global_rank(const smem_shm_device_ctx_t &c) { return c.rank; }
+__device__ __forceinline__ uint32_t smem_shm_get_global_rank_size(const smem_shm_device_ctx_t &c) { return c.rank_size; }
+__device__ __forceinline__ uint64_t smem_shm_get_symmetric_size(const smem_shm_device_ctx_t &c) { return c.symmetric_size; }
+
+/* The peer's copy of an object of this rank's slice. */
+template <typename T> __device__ __forceinline__ T *smem_shm_peer_ptr(const smem_shm_device_ctx_t &c, T *local, uint32_t peer)
+{
+    return reinterpret_cast<T *>(reinterpret_cast<uint64_t>(local) + ((int64_t)peer - (int64_t)c.rank) * (int64_t)c.symmetric_size);
+}
+/* Address of byte `offset` of a rank's slice. */
+__device__ __forceinline__ void *smem_shm_slice_ptr(const smem_shm_device_ctx_t &c, uint32_t rank, uint64_t offset)
+{
+    return reinterpret_cast<void *>(c.base + (uint64_t)rank * c.symmetric_size + offset);
+}
+
+__device__ __forceinline__ mfk::Team smem_shm_team(const smem_shm_device_ctx_t &c)
+{
+    mfk::Team t;
+    t.heap_base = c.base, t.stride = c.symmetric_size, t.mc_base = c.mc_base;
+    t.rank = c.rank, t.world = c.rank_size, t.emu = 0, t.spin_limit = c.spin_limit;
+    return t;
+}
+
+/* All ranks meet; call from ONE block with all its threads (blockDim.x >= rank_size). channel 32..63 is
+ * free for user kernels. Orders this rank's earlier stores (to any slice) before the peers' later loads. */
+__device__ __forceinline__ bool smem_shm_barrier(const smem_shm_device_ctx_t &c, uint32_t epoch, uint32_t channel = 32)
+{
+    return mfk::team_barrier(smem_shm_team(c), c.rank, channel, epoch);
+}
+
+/* One-way signal: raise flag word `index` (0..15) of `channel` in the peer's slice to `epoch`. */
+__device__ __forceinline__ void smem_shm_signal(const smem_shm_device_ctx_t &c, uint32_t peer, uint32_t channel, uint32_t index, uint32_t epoch)
+{
+    __threadfence_system();
+    uint32_t *f = reinterpret_cast<uint32_t *>(smem_shm_slice_ptr(c, peer, mfk::kBarrierOff + (uint64_t)channel * 256)) + 16 + (index & 15);
+    mfk::st_release_sys(f, epoch);
+}
+/* Waits until flag word `index` of `channel` in the own slice reaches `epoch`; false on time-out. */
+__device__ __forceinline__ bool smem_shm_wait(const smem_shm_device_ctx_t &c, uint32_t channel, uint32_t index, uint32_t epoch)
+{
+    const uint32_t *f = reinterpret_cast<const uint32_t *>(smem_shm_slice_ptr(c, c.rank, mfk::kBarrierOff + (uint64_t)channel * 256)) + 16 + (index & 15);
+    if (mfk::wait_flag(f, epoch, c.spin_limit)) return true;
+    mfk::report_timeout(smem_shm_team(c), c.rank, 0x2000 | channel, epoch);
+    return false;
+}
+#endif /* __CUDACC__ */
+#endif

@@ -1,0 +1,52 @@
+// Example user kernel on the public device API of the symmetric shared memory: an all-reduce (sum) of
+// fp32 vectors that live in the ranks' slices. Every rank reads all peers' inputs over NVLink after a
+// barrier and writes its own output; a closing barrier keeps the inputs intact until all have read.
+// The counterpart of the reference's examples/hbm_share_memory/AllReduce. The tuned collectives are
+// in mf_coll.cu; this file shows what a few lines of user code on smem_shm_device.cuh look like.
+#include <cooperative_groups.h>
+
+#include "../include/smem_shm_device.cuh"
+
+namespace {
+
+__global__ void __launch_bounds__(256) k_example_allreduce(smem_shm_device_ctx_t ctx, const float *in, float *out, uint64_t n, uint32_t epoch,
+                                                            int *status)
+{
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    __shared__ int ok;
+    if (blockIdx.x == 0) {
+        const bool good = smem_shm_barrier(ctx, 2 * epoch - 1);   // everybody's input is in place
+        if (threadIdx.x == 0) {
+            ok = good;
+            if (!good) atomicExch(status, 1);
+        }
+    }
+    grid.sync();
+    if (*reinterpret_cast<volatile int *>(status) == 0) {
+        for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+            float acc = 0.f;
+            for (uint32_t r = 0; r < ctx.rank_size; r++) acc += __ldcg(smem_shm_peer_ptr(ctx, in, r) + i);
+            out[i] = acc;
+        }
+    }
+    grid.sync();
+    if (blockIdx.x == 0) smem_shm_barrier(ctx, 2 * epoch);        // nobody overwrites its input before all have read it
+}
+
+}  // namespace
+
+// in: inside this rank's slice (at the same offset on every rank); out: anywhere on this device.
+// epoch: 1, 2, 3, ... one per call, the same on every rank. status: device int, 0 on entry; 1 = a peer did not arrive.
+extern "C" int mf_example_shm_allreduce(const smem_shm_device_ctx_t *ctx, const float *in, float *out, uint64_t n, uint32_t epoch, int *status,
+                                        void *stream)
+{
+    if (ctx == nullptr || ctx->rank_size == 0 || ctx->rank_size > 16) return -1;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    smem_shm_device_ctx_t c = *ctx;
+    void *params[] = {&c, &in, &out, &n, &epoch, &status};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(k_example_allreduce), dim3(sms > 0 ? sms : 64), dim3(256),
+                                                params, 0, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : (int)e;
+}

@@ -8,6 +8,7 @@
 // Parity: src/smem/csrc/smem_shm/smem_shm.cpp:23-80, smem_shm_entry.cpp:23-38,83-119,151-281,
 // src/smem/include/host/smem_shm.h:28-222.
 #include "../include/smem_shm.h"
+#include "../include/smem_shm_device.cuh"
 #include "../util/mf_trace.h"
 #include "mf_smem_common.h"
 
@@ -254,6 +255,22 @@ uint64_t smem_shm_get_symmetric_size(smem_shm_t handle)
 {
     auto e = H(handle);
     return e ? e->symmetric_ : 0;
+}
+
+int32_t smem_shm_get_device_context(smem_shm_t handle, void *ctx, uint32_t ctxSize)
+{
+    auto e = H(handle);
+    if (!e || ctx == nullptr) return MF_FAIL(SMEM_INVALID_PARAM, "bad handle or NULL context");
+    smem_shm_device_ctx_t c{};
+    if (ctxSize < sizeof(c)) return MF_FAIL(SMEM_INVALID_PARAM, "context block of %u bytes, %zu needed", ctxSize, sizeof(c));
+    c.base = reinterpret_cast<uint64_t>(e->gva_);
+    c.symmetric_size = e->symmetric_;
+    c.mc_base = 0;
+    c.rank = e->rank_;
+    c.rank_size = e->rankSize_;
+    c.spin_limit = (uint32_t)EnvInt("MF_SHM_SPIN_LIMIT", nullptr, 1 << 22, 1024, 1u << 30);
+    memcpy(ctx, &c, sizeof(c));
+    return SMEM_OK;
 }
 
 int32_t smem_shm_destroy(smem_shm_t handle, uint32_t)

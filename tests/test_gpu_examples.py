@@ -1,0 +1,33 @@
+"""The shipped examples run as written (each in child processes)."""
+import importlib.util
+import os
+
+import pytest
+import torch
+
+from conftest import free_port
+from mp_util import run_ranks
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _load(path):
+    spec = importlib.util.spec_from_file_location("example_" + os.path.basename(path)[:-3], os.path.join(ROOT, path))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _shm_allreduce(rank, world, url):
+    return _load("examples/hbm_share_memory/allreduce.py").run(rank, world, rank % torch.cuda.device_count(), url, n=300_000)
+
+
+def test_shm_user_kernel_single_gpu():
+    assert run_ranks(_shm_allreduce, 1, (f"tcp://127.0.0.1:{free_port()}",), timeout=180) == [0.0]
+
+
+@pytest.mark.multigpu
+def test_shm_user_kernel_multi_gpu():
+    n = min(torch.cuda.device_count(), 4)
+    assert run_ranks(_shm_allreduce, n, (f"tcp://127.0.0.1:{free_port()}",), timeout=240) == [0.0] * n
