@@ -94,7 +94,7 @@ def build_cuda(jobs: int | None = None) -> Path | None:
     LIB.mkdir(exist_ok=True)
     out = LIB / "libmf_cuda.so"
     tmp = out.with_suffix(".so.tmp")
-    subprocess.run([nvcc, "-shared", "-o", str(tmp)] + [str(o) for o in objs] +
+    subprocess.run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(tmp)] + [str(o) for o in objs] +
                    ["-cudart", "static", f"-L{LIB}", "-lmf_smem", "-Xlinker", "-rpath=$ORIGIN", "-Xlinker", "-z,relro",
                     "-lpthread", "-ldl", "-lrt"], check=True)
     tmp.replace(out)

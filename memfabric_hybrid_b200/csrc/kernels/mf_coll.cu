@@ -15,6 +15,7 @@
 #include <cooperative_groups.h>
 
 #include "mf_coll.cuh"
+#include "mf_devtrace.cuh"
 
 namespace mfk {
 
@@ -218,13 +219,18 @@ template <typename T, typename TO, bool INT, int W> __global__ void __launch_bou
     uint64_t C = (a.n + world - 1) / world;
     C = (C + 7) / 8 * 8;
     const Range sub = cta_range<8>(C);
+    MF_PROF_START(PF_STAGE_IN);
     if (!a.zero_copy) {
         for (uint32_t c = 0; c < world; c++) {
             const uint64_t b = min(a.n, c * C + sub.beg), e = min(a.n, c * C + sub.end);
             cta_raw_copy<T>(in, myA, b, e);
         }
     }
+    MF_PROF_STOP(PF_STAGE_IN);
+    MF_PROF_START(PF_SYNC);
     if (!lane_sync(t, me, 0, a.epoch, 0x110)) return;
+    MF_PROF_STOP(PF_SYNC);
+    MF_PROF_START(PF_REDUCE);
     {
         const uint64_t b = min(a.n, me * C + sub.beg), e = min(a.n, me * C + sub.end);
         reduce_ranks<T, INT, W>(t, me, a.stage_a, 0, b, e, a.op, [&](uint64_t i, float *acc, int cnt) {
@@ -241,12 +247,17 @@ template <typename T, typename TO, bool INT, int W> __global__ void __launch_bou
             }
         });
     }
+    MF_PROF_STOP(PF_REDUCE);
+    MF_PROF_START(PF_SYNC);
     if (!lane_sync(t, me, 1, a.epoch, 0x111)) return;
+    MF_PROF_STOP(PF_SYNC);
+    MF_PROF_START(PF_COPY_OUT);
     const TO *myB = reinterpret_cast<const TO *>(peer_ptr(t, me, a.stage_b));
     for (uint32_t c = 0; c < world; c++) {
         const uint64_t b = min(a.n, c * C + sub.beg), e = min(a.n, c * C + sub.end);
         cta_raw_copy<TO>(myB, out, b, e);
     }
+    MF_PROF_STOP(PF_COPY_OUT);
 }
 
 // reduce_scatter: input n = W * m elements, output m elements (rank r gets the reduction of chunk r)
@@ -377,7 +388,10 @@ template <typename T, typename TO, bool INT, int W> __global__ void __launch_bou
     const uint32_t world = t.world;
     __shared__ uint64_t p_in[kMaxRanks], p_out[kMaxRanks];
     const uint64_t slot = t.heap_base + (uint64_t)me * t.stride;
+    MF_PROF_START(PF_SYNC);
     if (!lane_sync_xchg(t, me, 0, a.epoch, 0x180, a.in - slot, a.out - slot, p_in, p_out)) return;
+    MF_PROF_STOP(PF_SYNC);
+    MF_PROF_START(PF_REDUCE);
     constexpr int VN = Vec<T>::N;
     uint64_t C = (a.n + world - 1) / world;
     C = (C + 7) / 8 * 8;
@@ -395,7 +409,10 @@ template <typename T, typename TO, bool INT, int W> __global__ void __launch_bou
             emit<TO, true>(dst, i, tmp, cnt, 1.f);
         }
     });
+    MF_PROF_STOP(PF_REDUCE);
+    MF_PROF_START(PF_SYNC);
     lane_sync(t, me, 1, a.epoch, 0x181);
+    MF_PROF_STOP(PF_SYNC);
 }
 
 // reduce-scatter: rank r reduces part r of every rank's input into its local output.
@@ -763,6 +780,9 @@ int mf_coll_wait_flag(const Team *team, uint64_t flag_off, uint32_t epoch, void 
     return e == cudaSuccess ? 0 : (int)e;
 }
 
+}  // extern "C"
+MF_DEVTRACE_DEFINE_SETTER(mf_coll_set_devtrace)
+extern "C" {
 unsigned mf_coll_signal_bytes(void) { return kSignalBytes; }
 unsigned mf_coll_max_ctas(void) { return kMaxCtas; }
 unsigned mf_coll_args_size(void) { return (unsigned)sizeof(CollArgs); }

@@ -16,6 +16,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
+#include "mf_devtrace.cuh"
 #include "mf_team.cuh"
 
 namespace mfk {
@@ -453,6 +454,7 @@ __global__ void __launch_bounds__(448) k_moe_ll_dispatch(LLDispatchArgs a)
     const int E = a.d.sh.E, n = a.d.sh.T * a.d.sh.K;
     __shared__ int cnt[1024];
     if (blockIdx.x == 0) {
+        MF_PROF_START(PF_LAYOUT);
         for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
         __syncthreads();
         int *send_idx = const_cast<int *>(a.d.send_idx);
@@ -466,16 +468,24 @@ __global__ void __launch_bounds__(448) k_moe_ll_dispatch(LLDispatchArgs a)
         if (!notify_body(t, a.d.hp, E, a.tokens_per_expert, a.recv_per_expert, a.row_off, const_cast<int *>(a.d.put_off), a.src_off, a.d.epoch, 9))
             if (threadIdx.x == 0) atomicCAS(a.d.status, 0, 0x420);
         __threadfence();
+        MF_PROF_STOP(PF_LAYOUT);
     }
     grid.sync();  // every CTA has read the call counter before this point
     if (blockIdx.x == 0 && threadIdx.x == 0) *a.epoch_dev = a.d.epoch;
+    MF_PROF_START(PF_DISPATCH);
     dispatch_body(a.d);
+    MF_PROF_STOP(PF_DISPATCH);
+    if (blockIdx.x == 0) MF_PROF_START(PF_WAIT_PEERS);
     if (blockIdx.x == 0 && threadIdx.x < t.world) {
         const uint32_t *f = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, a.d.hp.flags)) + threadIdx.x;
         if (!wait_flag(f, a.d.epoch, t.spin_limit)) {
             report_timeout(t, me, 0x421, a.d.epoch);
             atomicCAS(a.d.status, 0, 0x421);
         }
+    }
+    if (blockIdx.x == 0) {
+        __syncthreads();
+        MF_PROF_STOP(PF_WAIT_PEERS);
     }
 }
 
@@ -496,9 +506,12 @@ __global__ void __launch_bounds__(256) k_moe_ll_combine(LLCombineArgs a)
     const Team &t = a.p.team;
     const uint32_t me = team_rank(t);
     if (a.epoch_dev != nullptr) a.epoch = *reinterpret_cast<const volatile uint32_t *>(a.epoch_dev);
+    MF_PROF_START(PF_PUSH);
     combine_push_body(a.p);
     __threadfence_system();
+    MF_PROF_STOP(PF_PUSH);
     grid.sync();
+    if (blockIdx.x == 0) MF_PROF_START(PF_WAIT_PEERS);
     if (blockIdx.x == 0 && threadIdx.x < t.world) {
         st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, threadIdx.x, a.p.hp.flags)) + kMaxRanks + me, a.epoch);
         const uint32_t *f = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, a.p.hp.flags)) + kMaxRanks + threadIdx.x;
@@ -507,13 +520,21 @@ __global__ void __launch_bounds__(256) k_moe_ll_combine(LLCombineArgs a)
             atomicCAS(a.status, 0, 0x422);
         }
     }
+    if (blockIdx.x == 0) {
+        __syncthreads();
+        MF_PROF_STOP(PF_WAIT_PEERS);
+    }
     grid.sync();
+    MF_PROF_START(PF_COMBINE);
     combine_reduce_body(t, a.p.hp, a.sh, a.topk_idx, a.out, a.topk_w);
+    MF_PROF_STOP(PF_COMBINE);
 }
 
 }  // namespace mfk
 
 using namespace mfk;
+
+MF_DEVTRACE_DEFINE_SETTER(mf_moe_set_devtrace)
 
 extern "C" {
 

@@ -132,6 +132,27 @@ def test_barrier_and_bounded_wait():
     assert torch.equal(c.all_reduce(x)[0], torch.full((64,), 4.0, device="cuda"))  # still healthy
 
 
+def test_device_timeline_of_a_collective(tmp_path, comms):
+    import json
+    from memfabric_hybrid_b200.utils import devtrace
+    devtrace.enable(lanes=64, per_lane=256)
+    try:
+        c = comms[4]
+        x = torch.randn(4, 400_000, device="cuda")
+        c.all_reduce(x, algo="twoshot")
+        torch.cuda.synchronize()
+        assert devtrace.count() > 0
+        path = tmp_path / "t.json"
+        n = devtrace.dump(str(path), rank=0)
+        ev = json.loads(path.read_text())["traceEvents"]
+        names = {e["name"] for e in ev}
+        assert n == len(ev) and {"stage_in", "sync", "reduce", "copy_out"} <= names
+        assert all(e["dur"] >= 0 and e["ph"] == "X" for e in ev)
+        assert devtrace.count() == 0          # dump emptied the lanes
+    finally:
+        devtrace.disable()
+
+
 def _real_ranks(rank, world, url, sync):
     import torch
     from memfabric_hybrid_b200.ops.heap import SymmetricHeap
