@@ -251,6 +251,48 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
                     dst_row = g.C + (int64_t)row * g.ldc;
                 }
                 const bool vec_ok = MODE == 2 ? (g.N & 7) == 0 : (g.ldc & 7) == 0;
+                if (vec_ok && nt * BN + BN <= g.N) {
+                    // full tile: 64 columns at a time through shared memory, so that every store instruction
+                    // writes 4 rows x 128 contiguous bytes instead of 32 rows x 16 bytes (what counts on NVLink)
+                    using SM = GemmSmem<BN, STAGES>;
+                    uint8_t *stg = sm.out_stage(warp - 2);
+                    const int64_t ld = MODE == 2 ? (int64_t)g.N : g.ldc;
+                    __nv_bfloat16 *tile_dst;
+                    if (MODE == 2) {
+                        const int owner = mt * BM / g.rows_per_rank;
+                        tile_dst = reinterpret_cast<__nv_bfloat16 *>(peer_ptr(g.team, owner, g.rs_land_off)) +
+                                   ((int64_t)me * g.rows_per_rank + (mt * BM + quad * 32 - owner * g.rows_per_rank)) * g.N;
+                    } else {
+                        tile_dst = g.C + (int64_t)(mt * BM + quad * 32) * g.ldc;
+                    }
+#pragma unroll 1
+                    for (int c2 = 0; c2 < BN / 64; c2++) {
+#pragma unroll
+                        for (int half = 0; half < 2; half++) {
+                            uint32_t v[32];
+                            tmem_ld32(taddr + (uint32_t)(c2 * 64 + half * 32), v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int q = 0; q < 4; q++) {
+                                uint4 pk;
+                                __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+                                for (int e = 0; e < 4; e++)
+                                    h[e] = __floats2bfloat162_rn(__uint_as_float(v[q * 8 + 2 * e]), __uint_as_float(v[q * 8 + 2 * e + 1]));
+                                *reinterpret_cast<uint4 *>(stg + lane * SM::kOutRowBytes + half * 64 + q * 16) = pk;
+                            }
+                        }
+                        __syncwarp();
+                        const int col = nt * BN + c2 * 64 + (lane & 7) * 8;
+#pragma unroll
+                        for (int it = 0; it < 8; it++) {
+                            const int r = it * 4 + (lane >> 3);
+                            const uint4 val = *reinterpret_cast<const uint4 *>(stg + r * SM::kOutRowBytes + (lane & 7) * 16);
+                            if (mt * BM + quad * 32 + r < g.M) *reinterpret_cast<uint4 *>(tile_dst + (int64_t)r * ld + col) = val;
+                        }
+                        __syncwarp();
+                    }
+                } else {
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; c++) {
                     uint32_t v[32];
@@ -275,6 +317,7 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
                                 if (col + e < g.N) dst[e] = __float2bfloat16_rn(__uint_as_float(v[e]));
                         }
                     }
+                }
                 }
             }
             tc_fence_before();

@@ -29,7 +29,14 @@ template <int BN, int STAGES> struct GemmSmem {
     static constexpr int kBBytes = BN * KSPAN;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarOff = STAGES * kStageBytes;
-    static constexpr int kTotal = kBarOff + 1024;
+    // epilogue staging: each of the 4 epilogue warps turns 32 rows x 64 columns of bf16 around (one row per lane
+    // out of TMEM -> 128 contiguous bytes per row on the way to memory); rows are padded to 144 bytes so that
+    // both the per-lane row writes and the 8-lanes-per-row reads are free of bank conflicts
+    static constexpr int kOutRowBytes = 144;
+    static constexpr int kOutWarpBytes = 32 * kOutRowBytes;
+    static constexpr int kOutOff = kBarOff + 1024;
+    static constexpr int kOutBytes = 20480;  // >= 4 x kOutWarpBytes (bf16 GEMM) and >= 8 x 32 x 80 (fp8 GEMM, 8 warps x 32 columns)
+    static constexpr int kTotal = kOutOff + kOutBytes;
     uint8_t *base;
     __device__ explicit GemmSmem(uint8_t *raw) : base(reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023)) {}
     __device__ uint8_t *a(int s) const { return base + s * kStageBytes; }
@@ -39,6 +46,7 @@ template <int BN, int STAGES> struct GemmSmem {
     __device__ uint64_t *tfull(int i) const { return reinterpret_cast<uint64_t *>(base + kBarOff) + 2 * STAGES + i; }
     __device__ uint64_t *tempty(int i) const { return reinterpret_cast<uint64_t *>(base + kBarOff) + 2 * STAGES + 4 + i; }
     __device__ uint32_t *tmem_slot() const { return reinterpret_cast<uint32_t *>(base + kBarOff + 512); }
+    __device__ uint8_t *out_stage(int epi_warp) const { return base + kOutOff + epi_warp * kOutWarpBytes; }
     __device__ volatile int *abort_flag() const { return reinterpret_cast<volatile int *>(base + kBarOff + 520); }
     static constexpr int kDynBytes = kTotal + 1024;  // slack for the 1024-byte alignment
 };

@@ -45,7 +45,9 @@ struct Fp8Args {
     int topk;
 };
 
-template <int EPI> __global__ void __launch_bounds__(kGemmThreads, 1) k_grouped_fp8(const __grid_constant__ Fp8Args g)
+constexpr int kFp8Threads = 64 + 8 * 32;  // TMA warp, MMA warp, eight epilogue warps
+
+template <int EPI> __global__ void __launch_bounds__(kFp8Threads, 1) k_grouped_fp8(const __grid_constant__ Fp8Args g)
 {
     extern __shared__ uint8_t smem_raw[];
     GemmSmem<FBN, FSTAGES> sm(smem_raw);
@@ -66,7 +68,7 @@ template <int EPI> __global__ void __launch_bounds__(kGemmThreads, 1) k_grouped_
         }
         for (int i = 0; i < kAccBufs; i++) {
             mbar_init(sm.tfull(i), 1);
-            mbar_init(sm.tempty(i), 4);
+            mbar_init(sm.tempty(i), 8);
         }
         mbar_fence_init();
         tma_prefetch_desc(&g.tm.a);
@@ -149,11 +151,23 @@ template <int EPI> __global__ void __launch_bounds__(kGemmThreads, 1) k_grouped_
             }
         }
     } else {
+        // eight epilogue warps: warp w reads TMEM lane quadrant w % 4 (the hardware's rule) and one half of
+        // the tile's columns, so a thread carries 64 fp32 accumulators and the per-K-block promotion
+        // (TMEM -> registers, x scale, add) is spread over twice the threads of a 4-warp epilogue.
+        // EPI 1 keeps a gate column and its up column in the same thread: half h owns gate columns
+        // [32h, 32h+32) and up columns [64+32h, 64+32h+32).
         const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int col0 = EPI == 1 ? half * 32 : half * 64;
+        const int col1 = EPI == 1 ? 64 + half * 32 : half * 64 + 32;
         int buf = 0;
         uint32_t buf_phase = 0;
         const int kgroups = g.K / 128;
         const int nblocks = g.N / 128;
+        using SM = GemmSmem<FBN, FSTAGES>;
+        constexpr int kRowB = 80;  // staged row: 64 bytes of bf16 + 16 of padding (conflict-free 16-byte writes)
+        uint8_t *stg = sm.out_stage(0) + (warp - 2) * (32 * kRowB);
+        static_assert(8 * 32 * kRowB <= SM::kOutBytes, "epilogue staging does not fit");
         for (int t = blockIdx.x; t < total; t += gridDim.x) {
             int grp, row0, row_end, nt;
             locate(t, grp, row0, row_end, nt);
@@ -170,9 +184,9 @@ template <int EPI> __global__ void __launch_bounds__(kGemmThreads, 1) k_grouped_
             }
             const float *bs0 = g.b_scale + ((int64_t)grp * nblocks + nb0) * kgroups;
             const float *bs1 = g.b_scale + ((int64_t)grp * nblocks + nb1) * kgroups;
-            float acc[FBN];
+            float acc[64];
 #pragma unroll
-            for (int i = 0; i < FBN; i++) acc[i] = 0.f;
+            for (int i = 0; i < 64; i++) acc[i] = 0.f;
             bool fine = true;
             for (int kb = 0; kb < k_blocks; kb++) {
                 fine = __all_sync(0xffffffffu, mbar_wait(sm.tfull(buf), buf_phase, ac, 0x505));
@@ -181,57 +195,75 @@ template <int EPI> __global__ void __launch_bounds__(kGemmThreads, 1) k_grouped_
                 const float sa = __ldg(as + kb);
                 const float s0 = sa * __ldg(bs0 + kb), s1 = sa * __ldg(bs1 + kb);
                 const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * FBN);
-#pragma unroll
-                for (int c = 0; c < FBN / 32; c++) {
-                    uint32_t v[32];
-                    tmem_ld32(taddr + (uint32_t)(c * 32), v);
-                    tmem_ld_wait();
-                    const float s = c < 2 ? s0 : s1;
-#pragma unroll
-                    for (int j = 0; j < 32; j++) acc[c * 32 + j] = fmaf(__uint_as_float(v[j]), s, acc[c * 32 + j]);
-                }
+                uint32_t v0[32], v1[32];
+                tmem_ld32(taddr + (uint32_t)col0, v0);   // both loads in flight before the wait
+                tmem_ld32(taddr + (uint32_t)col1, v1);
+                tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(sm.tempty(buf));
+                if (lane == 0) mbar_arrive(sm.tempty(buf));  // the data is in registers: the tensor core may reuse the buffer
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    acc[j] = fmaf(__uint_as_float(v0[j]), s0, acc[j]);
+                    acc[32 + j] = fmaf(__uint_as_float(v1[j]), s1, acc[32 + j]);
+                }
                 if (++buf == kAccBufs) {
                     buf = 0;
                     buf_phase ^= 1;
                 }
             }
             if (!fine) break;
-            if (!row_ok) continue;
             if (EPI == 1) {
-                __nv_bfloat16 *dst = g.out + (int64_t)row * g.ldo + nt * 64;
+                if (row_ok) {
+                    __nv_bfloat16 *dst = g.out + (int64_t)row * g.ldo + nt * 64 + half * 32;
 #pragma unroll
-                for (int q = 0; q < 8; q++) {
-                    uint4 pk;
-                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+                    for (int q = 0; q < 4; q++) {
+                        uint4 pk;
+                        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const float g0 = acc[q * 8 + 2 * e], g1 = acc[q * 8 + 2 * e + 1];
-                        const float u0 = acc[64 + q * 8 + 2 * e], u1 = acc[64 + q * 8 + 2 * e + 1];
-                        h[e] = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+                        for (int e = 0; e < 4; e++) {
+                            const float g0 = acc[q * 8 + 2 * e], g1 = acc[q * 8 + 2 * e + 1];
+                            const float u0 = acc[32 + q * 8 + 2 * e], u1 = acc[32 + q * 8 + 2 * e + 1];
+                            h[e] = __floats2bfloat162_rn(g0 / (1.f + __expf(-g0)) * u0, g1 / (1.f + __expf(-g1)) * u1);
+                        }
+                        *reinterpret_cast<uint4 *>(dst + q * 8) = pk;
                     }
-                    *reinterpret_cast<uint4 *>(dst + q * 8) = pk;
                 }
             } else {
-                __nv_bfloat16 *dst;
+                // rows leave through shared memory: lane = row on the way in, 4 lanes x 16 bytes per row on the
+                // way out, so that one store instruction writes 8 rows x 64 contiguous bytes (peer stores of
+                // 16-byte fragments are what made this epilogue slow)
+                unsigned long long dst = 0;
                 float w = 1.f;
-                if (EPI == 2) {
-                    const int4 info = __ldg(g.recv_info + row);
-                    w = __int_as_float(info.w);
-                    dst = reinterpret_cast<__nv_bfloat16 *>(peer_ptr(g.team, (uint32_t)info.x, g.comb_off)) +
-                          ((int64_t)info.y * g.topk + info.z) * g.N + nt * FBN;
-                } else {
-                    dst = g.out + (int64_t)row * g.ldo + nt * FBN;
+                if (row_ok) {
+                    if (EPI == 2) {
+                        const int4 info = __ldg(g.recv_info + row);
+                        w = __int_as_float(info.w);
+                        dst = reinterpret_cast<unsigned long long>(reinterpret_cast<__nv_bfloat16 *>(peer_ptr(g.team, (uint32_t)info.x, g.comb_off)) +
+                                                                   ((int64_t)info.y * g.topk + info.z) * g.N + nt * FBN + half * 64);
+                    } else {
+                        dst = reinterpret_cast<unsigned long long>(g.out + (int64_t)row * g.ldo + nt * FBN + half * 64);
+                    }
                 }
 #pragma unroll
-                for (int q = 0; q < 16; q++) {
-                    uint4 pk;
-                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+                for (int c = 0; c < 2; c++) {
 #pragma unroll
-                    for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(acc[q * 8 + 2 * e] * w, acc[q * 8 + 2 * e + 1] * w);
-                    *reinterpret_cast<uint4 *>(dst + q * 8) = pk;
+                    for (int q = 0; q < 4; q++) {
+                        uint4 pk;
+                        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(acc[c * 32 + q * 8 + 2 * e] * w, acc[c * 32 + q * 8 + 2 * e + 1] * w);
+                        *reinterpret_cast<uint4 *>(stg + lane * kRowB + q * 16) = pk;
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int it = 0; it < 4; it++) {
+                        const int r = it * 8 + (lane >> 2);
+                        const unsigned long long d = __shfl_sync(0xffffffffu, dst, r);
+                        const uint4 val = *reinterpret_cast<const uint4 *>(stg + r * kRowB + (lane & 3) * 16);
+                        if (d != 0) *reinterpret_cast<uint4 *>(d + (unsigned long long)(c * 64 + (lane & 3) * 16)) = val;
+                    }
+                    __syncwarp();
                 }
             }
         }
@@ -261,7 +293,7 @@ template <int EPI> int launch_fp8(const Fp8Args &g, int grid, cudaStream_t s)
         }
         attr_set = true;
     }
-    kern<<<grid, kGemmThreads, GemmSmem<FBN, FSTAGES>::kDynBytes, s>>>(g);
+    kern<<<grid, kFp8Threads, GemmSmem<FBN, FSTAGES>::kDynBytes, s>>>(g);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : (int)e;
 }

@@ -94,7 +94,7 @@ class Communicator:
         self.max_ctas = min(max_ctas or sms, 256)
         if heap.emu:
             # a cooperative launch of world x ctas blocks must be co-resident
-            self.max_ctas = max(1, min(self.max_ctas, (sms * 2) // heap.world))
+            self.max_ctas = max(1, min(self.max_ctas, sms // heap.world))  # one 512-thread CTA per SM is always resident
         self._meta = None
 
     # ------------------------------------------------------------------ helpers
