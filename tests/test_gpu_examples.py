@@ -31,3 +31,20 @@ def test_shm_user_kernel_single_gpu():
 def test_shm_user_kernel_multi_gpu():
     n = min(torch.cuda.device_count(), 4)
     assert run_ranks(_shm_allreduce, n, (f"tcp://127.0.0.1:{free_port()}",), timeout=240) == [0.0] * n
+
+
+def test_hbm_pool_example():
+    import subprocess
+    import sys
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples/memory_pool/03_hbm_pool_external_stream.py")], capture_output=True, text=True,
+                       timeout=240)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_zbal_backend_example_single_process():
+    import subprocess
+    import sys
+    env = dict(os.environ, RANK="0", WORLD_SIZE="1", LOCAL_RANK="0", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(free_port()))
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "examples/zbal/allreduce_backend.py")], env=env, capture_output=True, text=True,
+                       timeout=240)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
