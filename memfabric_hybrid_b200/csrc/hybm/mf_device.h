@@ -70,6 +70,16 @@ public:
     virtual int Unmap(uint64_t va, uint64_t size) = 0;
     virtual int ReleasePhys(PhysHandle h) = 0;
 
+    // ---- NVLink multicast objects (in-switch reduction / broadcast, "NVLS"); optional: a backend without
+    // them returns an error from McCreate and Caps().multicast is false
+    virtual int McGranularity(uint64_t size, uint32_t devices, uint64_t *gran) { (void)size, (void)devices, (void)gran; return -1; }
+    virtual int McCreate(uint64_t size, uint32_t devices, PhysHandle *h) { (void)size, (void)devices, (void)h; return -1; }
+    virtual int McAddDevice(PhysHandle h) { (void)h; return -1; }
+    // binds [va, va + size) of THIS device's mapped memory at mcOffset of the object; every device must have
+    // been added (by every process) before the first bind
+    virtual int McBindAddr(PhysHandle h, uint64_t mcOffset, uint64_t va, uint64_t size) { (void)h, (void)mcOffset, (void)va, (void)size; return -1; }
+    virtual int McUnbind(PhysHandle h, uint64_t mcOffset, uint64_t size) { (void)h, (void)mcOffset, (void)size; return -1; }
+
     // ---- plain allocations, host registration, IPC of caller-owned device buffers
     virtual int Malloc(uint64_t size, uint64_t *ptr) = 0;
     virtual int Free(uint64_t ptr) = 0;

@@ -34,6 +34,12 @@ struct DriverApi {
     DRV(cuMemGetAllocationGranularity);
     DRV(cuMemGetAddressRange);
     DRV(cuPointerGetAttribute);
+    DRV(cuMulticastCreate);
+    DRV(cuMulticastAddDevice);
+    DRV(cuMulticastBindAddr);
+    DRV(cuMulticastUnbind);
+    DRV(cuMulticastGetGranularity);
+    DRV(cuDeviceGet);
     DRV(cuGetErrorString);
     bool ok = false;
 };
@@ -107,6 +113,12 @@ public:
                   Load("cuPointerGetAttribute", drv_.p_cuPointerGetAttribute);
         Load("cuGetErrorString", drv_.p_cuGetErrorString);
         drv_.ok = ok;
+        {
+            const bool have = Load("cuMulticastCreate", drv_.p_cuMulticastCreate) && Load("cuMulticastAddDevice", drv_.p_cuMulticastAddDevice) &&
+                              Load("cuMulticastBindAddr", drv_.p_cuMulticastBindAddr) && Load("cuMulticastUnbind", drv_.p_cuMulticastUnbind) &&
+                              Load("cuMulticastGetGranularity", drv_.p_cuMulticastGetGranularity) && Load("cuDeviceGet", drv_.p_cuDeviceGet);
+            caps_.multicast = have && ok && McSupported();
+        }
         // Every GPU this library targets (sm_100) has virtual memory management; the entry points being
         // present is the remaining condition.
         caps_.vmm = ok;
@@ -121,6 +133,64 @@ public:
                 caps_.granularity = g;
         }
         grid_ = (int)EnvInt("MF_XCOPY_CTAS_PER_SM", nullptr, 2, 1, 4) * caps_.smCount;
+        return OK;
+    }
+
+    bool McSupported()
+    {
+        // CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED through the driver attribute query
+        using AttrFn = CUresult (*)(int *, CUdevice_attribute, CUdevice);
+        AttrFn fn = nullptr;
+        if (!Load("cuDeviceGetAttribute", fn)) return false;
+        CUdevice d;
+        if (drv_.p_cuDeviceGet(&d, dev_) != CUDA_SUCCESS) return false;
+        int v = 0;
+        return fn(&v, CU_DEVICE_ATTRIBUTE_MULTICAST_SUPPORTED, d) == CUDA_SUCCESS && v != 0;
+    }
+    CUmulticastObjectProp McProp(uint64_t size, uint32_t devices) const
+    {
+        CUmulticastObjectProp p;
+        memset(&p, 0, sizeof(p));
+        p.numDevices = devices;
+        p.size = size;
+        p.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+        return p;
+    }
+    int McGranularity(uint64_t size, uint32_t devices, uint64_t *gran) override
+    {
+        if (!caps_.multicast) return ERR;
+        CUmulticastObjectProp p = McProp(size, devices);
+        size_t g = 0;
+        CU_CHECK(drv_.p_cuMulticastGetGranularity(&g, &p, CU_MULTICAST_GRANULARITY_MINIMUM), "cuMulticastGetGranularity");
+        *gran = g;
+        return OK;
+    }
+    int McCreate(uint64_t size, uint32_t devices, PhysHandle *h) override
+    {
+        if (!caps_.multicast) return ERR;
+        CUmulticastObjectProp p = McProp(size, devices);
+        CUmemGenericAllocationHandle mc;
+        CU_CHECK(drv_.p_cuMulticastCreate(&mc, &p), "cuMulticastCreate");
+        *h = (PhysHandle)mc;
+        return OK;
+    }
+    int McAddDevice(PhysHandle h) override
+    {
+        CUdevice d;
+        CU_CHECK(drv_.p_cuDeviceGet(&d, dev_), "cuDeviceGet");
+        CU_CHECK(drv_.p_cuMulticastAddDevice((CUmemGenericAllocationHandle)h, d), "cuMulticastAddDevice");
+        return OK;
+    }
+    int McBindAddr(PhysHandle h, uint64_t mcOffset, uint64_t va, uint64_t size) override
+    {
+        CU_CHECK(drv_.p_cuMulticastBindAddr((CUmemGenericAllocationHandle)h, mcOffset, (CUdeviceptr)va, size, 0), "cuMulticastBindAddr");
+        return OK;
+    }
+    int McUnbind(PhysHandle h, uint64_t mcOffset, uint64_t size) override
+    {
+        CUdevice d;
+        CU_CHECK(drv_.p_cuDeviceGet(&d, dev_), "cuDeviceGet");
+        CU_CHECK(drv_.p_cuMulticastUnbind((CUmemGenericAllocationHandle)h, d, mcOffset, size), "cuMulticastUnbind");
         return OK;
     }
 

@@ -7,6 +7,8 @@
 // exit broadcast, all on the config store.
 // Parity: src/smem/csrc/smem_shm/smem_shm.cpp:23-80, smem_shm_entry.cpp:23-38,83-119,151-281,
 // src/smem/include/host/smem_shm.h:28-222.
+#include <unistd.h>
+
 #include "../include/smem_shm.h"
 #include "../include/smem_shm_device.cuh"
 #include "../util/mf_trace.h"
@@ -36,8 +38,110 @@ public:
     }
     ~ShmEntry()
     {
+        TeardownMulticast();
         if (group_) group_->StopListen();
         entity_.reset();
+    }
+
+    // NVLink multicast ("NVLS") view of the object: ONE multicast object of the slice size to which every
+    // rank binds its own slice at offset 0, mapped at mcBase_. A multimem load-reduce at mcBase_ + off sums
+    // (in the switch) the values at offset off of ALL ranks' slices; a multimem store writes all of them.
+    // Opt-in (MF_SHM_MULTICAST=1): a process that dies while its memory is bound to a multicast object
+    // disturbs its peers' NVLink traffic, so jobs that may lose ranks should stay on plain peer mappings.
+    // Order: create (rank 0) -> hand out the handle -> every rank adds its device -> barrier -> bind -> barrier
+    // -> map. A rank that cannot take part says so in the all-gather and everybody skips the set-up.
+    int SetupMulticast()
+    {
+        mcBase_ = 0;
+        auto *dev = CurrentBackend();
+        const bool want = EnvInt("MF_SHM_MULTICAST", "ZBAL_NVLS", 0, 0, 1) != 0;
+        int32_t can = (want && rankSize_ > 1 && dev != nullptr && dev->Caps().multicast) ? 1 : 0;
+        uint64_t gran = 0;
+        if (can && dev->McGranularity(localSize_, rankSize_, &gran) != OK) can = 0;
+        // the bound range must be backed by this rank's own allocation: sizes that are not a multiple of the
+        // multicast granularity (2 MiB on current parts) stay on peer mappings
+        if (can && (gran == 0 || localSize_ % gran != 0)) can = 0;
+        const uint64_t size = can ? localSize_ : 0;
+        struct Blob {
+            int32_t can;
+            int32_t pid;
+            uint64_t token;
+            char name[112];
+        } mine{}, zero{};
+        mine.can = can;
+        PhysHandle mc = 0;
+        uint64_t token = 0;
+        if (can && rank_ == 0) {
+            int fd = -1;
+            if (dev->McCreate(size, rankSize_, &mc) != OK || dev->ExportFd(mc, &fd) != OK) {
+                mine.can = 0;
+                if (mc) dev->ReleasePhys(mc);
+                mc = 0;
+            } else {
+                token = FdChannel::Get().Publish(fd);
+                mine.token = token;
+                mine.pid = (int32_t)getpid();
+                snprintf(mine.name, sizeof(mine.name), "%s", FdChannel::Get().Name().c_str());
+            }
+        }
+        std::vector<Blob> all(rankSize_, zero);
+        int rc = group_->AllGather(reinterpret_cast<const char *>(&mine), sizeof(mine), reinterpret_cast<char *>(all.data()),
+                                   (uint32_t)(all.size() * sizeof(Blob)));
+        bool everyone = rc == OK;
+        for (auto &b : all) everyone = everyone && b.can == 1;
+        int32_t step = everyone ? OK : ERR;
+        if (everyone && rank_ != 0) {
+            int fd = -1;
+            step = FdChannel::Fetch(all[0].name, all[0].token, &fd);
+            if (step == OK) step = dev->ImportFd(fd, size, &mc);
+        }
+        if (step == OK && everyone) step = dev->McAddDevice(mc);
+        step = GatherOk(step);  // doubles as the barrier "every device was added"
+        if (step == OK && everyone) {
+            const uint64_t local = reinterpret_cast<uint64_t>(gva_) + (uint64_t)rank_ * symmetric_;
+            step = dev->McBindAddr(mc, 0, local, size);
+            if (step == OK) mcBound_ = true;
+        }
+        step = GatherOk(step);
+        if (step == OK && everyone) {
+            uint64_t va = 0;
+            step = dev->Reserve(0, size, &va);
+            if (step == OK) {
+                step = dev->Map(va, size, mc);
+                if (step != OK) dev->ReleaseVa(va, size);
+                else mcBase_ = va;
+            }
+        }
+        step = GatherOk(step);
+        if (token) FdChannel::Get().Withdraw(token);
+        mcHandle_ = mc;
+        mcSize_ = size;
+        if (step != OK || !everyone) {
+            TeardownMulticast();
+            if (want) MF_WARN("shm %u: NVLink multicast not set up (%s); collectives use peer loads and stores", id_,
+                              everyone ? "a step failed" : "not supported or refused by a rank");
+            return OK;  // optional feature: the object works without it
+        }
+        MF_INFO("shm %u: NVLink multicast view of %lu MiB per rank at %#lx", id_, (unsigned long)(size >> 20), (unsigned long)mcBase_);
+        return OK;
+    }
+
+    void TeardownMulticast()
+    {
+        auto *dev = CurrentBackend();
+        if (dev == nullptr || mcHandle_ == 0) return;
+        dev->StreamSync(nullptr);
+        if (mcBase_) {
+            dev->Unmap(mcBase_, mcSize_);
+            dev->ReleaseVa(mcBase_, mcSize_);
+            mcBase_ = 0;
+        }
+        if (mcBound_) {
+            dev->McUnbind(mcHandle_, 0, mcSize_);
+            mcBound_ = false;
+        }
+        dev->ReleasePhys(mcHandle_);
+        mcHandle_ = 0;
     }
 
     int Initialize()
@@ -112,7 +216,7 @@ public:
         all = GatherOk(rc);
         if (all != OK) return rc != OK ? rc : all;
         gva_ = entity_->MemoryPtr(HYBM_MEM_TYPE_DEVICE);
-        return OK;
+        return SetupMulticast();
     }
 
     int GatherOk(int32_t mine)
@@ -135,6 +239,9 @@ public:
     group::GroupPtr group_;
     EntityPtr entity_;
     void *gva_ = nullptr;
+    uint64_t mcBase_ = 0, mcSize_ = 0;
+    PhysHandle mcHandle_ = 0;
+    bool mcBound_ = false;
 };
 
 std::mutex g_mu;
@@ -265,7 +372,7 @@ int32_t smem_shm_get_device_context(smem_shm_t handle, void *ctx, uint32_t ctxSi
     if (ctxSize < sizeof(c)) return MF_FAIL(SMEM_INVALID_PARAM, "context block of %u bytes, %zu needed", ctxSize, sizeof(c));
     c.base = reinterpret_cast<uint64_t>(e->gva_);
     c.symmetric_size = e->symmetric_;
-    c.mc_base = 0;
+    c.mc_base = e->mcBase_;
     c.rank = e->rank_;
     c.rank_size = e->rankSize_;
     c.spin_limit = (uint32_t)EnvInt("MF_SHM_SPIN_LIMIT", nullptr, 1 << 22, 1024, 1u << 30);

@@ -14,6 +14,7 @@
 
 #include "../hybm/mf_device.h"
 #include "../include/smem.h"
+#include "../include/smem_shm_device.cuh"
 #include "../util/mf_util.h"
 #include "zbal_state.h"
 
@@ -151,6 +152,8 @@ int32_t zbal_bootstrap(zbal_bootstrap_options_t *o, zbal_bootstrap_output_t *out
     out.heapSize = o->deviceMemorySize - commArea;
     out.worldSize = o->worldSize;
     out.rankId = o->rankId;
+    smem_shm_device_ctx_t dctx{};
+    const uint64_t mcBase = smem_shm_get_device_context(shm, &dctx, sizeof(dctx)) == 0 ? dctx.mc_base : 0;
 
     // the communicator area starts zeroed on every rank before anybody may signal
     auto *be = mf::hybm::CurrentBackend();
@@ -178,6 +181,7 @@ int32_t zbal_bootstrap(zbal_bootstrap_options_t *o, zbal_bootstrap_output_t *out
         st.shm = shm;
         st.commSlotBytes = slot;
         st.ownSma = ownSma;
+        st.mcBase = mcBase;
         st.spinLimit = (uint32_t)mf::EnvInt("ZBAL_SPIN_LIMIT", nullptr, 1 << 22, 1024, 1u << 30);
         st.up = true;
     }

@@ -147,7 +147,7 @@ int AllReduce(Comm &c, const void *in, void *out, uint64_t n, int kdt, int odt, 
     std::lock_guard<std::mutex> g(c.mu);
     if (n * es > DirectMin() && InSlice(in, n * es) && InSlice(out, n * oes)) {
         MfCollArgs a = BaseArgs(c, in, out, n, scale, op, 0, 1);
-        a.zero_copy = 2;
+        a.zero_copy = (c.team.mc_base != 0 && op == 0 && kdt == odt && kdt != 3) ? 3 : 2;  // the switch adds when it can
         return Launched(L->coll(0, kdt, odt, &a, c.Ctas(n * es), 512, stream), "all_reduce (direct)");
     }
     uint64_t piece = c.stageBytes / std::max(es, oes);
@@ -265,6 +265,7 @@ int32_t zbal_comm_create(zbal_comm_options_t *o, zbal_comm_t *comm)
     smem_shm_t shm;
     uint64_t slotBytes;
     uint32_t cap, spin;
+    uint64_t mcBase;
     {
         std::lock_guard<std::mutex> g(st.mu);
         if (!st.up) return MF_FAIL(Z_NOT_INITIALIZED, "zbal is not bootstrapped");
@@ -274,6 +275,7 @@ int32_t zbal_comm_create(zbal_comm_options_t *o, zbal_comm_t *comm)
         slotBytes = st.commSlotBytes;
         cap = st.opts.commGroupCap;
         spin = st.spinLimit;
+        mcBase = st.mcBase;
     }
     if (o->name[0] == 0) return MF_FAIL(Z_INVALID_PARAM, "communicator name is empty");
     if (o->groupSize == 0 || o->groupSize > 16) return MF_FAIL(Z_INVALID_PARAM, "group size %u is outside 1..16", o->groupSize);
@@ -318,7 +320,8 @@ int32_t zbal_comm_create(zbal_comm_options_t *o, zbal_comm_t *comm)
     const uint64_t slotOff = (uint64_t)slot * slotBytes;
     c->team.heap_base = bo.baseGva + (uint64_t)o->firstRank * bo.symmetricSize + slotOff;
     c->team.stride = (uint64_t)step * bo.symmetricSize;
-    c->team.mc_base = 0;
+    // a multimem access reaches EVERY rank of the job, so only a communicator over all of them may use the alias
+    c->team.mc_base = (o->groupSize == bo.worldSize && step == 1) ? (mcBase ? mcBase + slotOff : 0) : 0;
     c->team.rank = groupRank;
     c->team.world = o->groupSize;
     c->team.emu = 0;

@@ -92,6 +92,7 @@ struct State {
     std::map<std::string, std::shared_ptr<Comm>> comms;
     std::shared_ptr<Comm> world;
     uint32_t spinLimit = 1u << 22;
+    uint64_t mcBase = 0;  // NVLink multicast alias of a slice (0: not set up); only the world communicator can use it
 };
 State &S();
 

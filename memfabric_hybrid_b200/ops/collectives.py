@@ -96,6 +96,7 @@ class Communicator:
             # a cooperative launch of world x ctas blocks must be co-resident
             self.max_ctas = max(1, min(self.max_ctas, sms // heap.world))  # one 512-thread CTA per SM is always resident
         self._meta = None
+        self.no_multicast = False  # set to keep all-reduce on peer loads/stores even when the heap has a multicast alias
 
     # ------------------------------------------------------------------ helpers
     def _next(self):
@@ -159,7 +160,9 @@ class Communicator:
         if algo in (None, "direct") and n * es > DIRECT_MIN and self._in_heap(x) and self._in_heap(out):
             epoch, stage = self._next()
             args = self._args(x, out, n, epoch, stage, scale, op, 0, 1)
-            args.zero_copy = 2
+            # with a multicast alias of the heap the switch does the adding (sum of one floating type, no cast)
+            mc = self.heap.mc_base != 0 and op == "sum" and od == x.dtype and x.dtype != torch.int32 and not self.no_multicast
+            args.zero_copy = 3 if mc else 2
             _check(_cu().mf_coll_launch(0, DT[x.dtype], DT[od], C.byref(args), self._ctas(n * es), 512, _stream()), "all_reduce (direct)")
             return out
         assert algo != "direct", "direct mode needs input and output inside the symmetric heap"

@@ -125,6 +125,7 @@ class SymmetricHeap(_HeapBase):
         self.base = self._shm.gva
         self.stride = self._shm.symmetric_size
         self.usable = slot_bytes
+        self.mc_base = int(self._shm.device_context().mc_base)  # multicast alias of a slice, 0 unless MF_SHM_MULTICAST=1 took effect
         # the signal area must start at zero on every rank before anybody signals
         self.view(0, (SIGNAL_BYTES,), torch.uint8).zero_()
         torch.cuda.synchronize()

@@ -50,6 +50,12 @@ def collectives(comm, world, flush):
         staged = _timed(lambda: comm.all_reduce(x, scale=1.0 / world), iters, 3, fl)
         row = {"op": "allreduce_scaled_bf16", "bytes": nbytes, "us": round(ms * 1e3, 1), "staged_us": round(staged * 1e3, 1),
                "busbw_GBps": round(nbytes * 2 * (world - 1) / max(world, 1) / (ms * 1e-3) / 1e9, 1)}
+        if heap.mc_base:
+            # "us" went through the NVLink multicast alias (MF_SHM_MULTICAST=1); the same call on peer loads and stores:
+            comm.no_multicast = True
+            row["peer_ld_st_us"] = round(_timed(lambda: comm.all_reduce(hx, out=ho, scale=1.0 / world), iters, 3, fl) * 1e3, 1)
+            comm.no_multicast = False
+            row["multicast"] = True
         if world > 1:
             y = x.clone()
 

@@ -2,6 +2,8 @@
 
 Single-GPU tests emulate all ranks in ONE cooperative launch (rank = blockIdx.y); the multi-GPU test runs
 real ranks as child processes over NVLink peer mappings."""
+import os
+
 import pytest
 import torch
 
@@ -206,9 +208,10 @@ def _real_ranks(rank, world, url, sync):
     c.barrier()
     torch.cuda.synchronize()
     st = heap.status()
+    mc = heap.mc_base != 0
     heap.close()
     SymmetricHeap.shutdown()
-    return st[0]
+    return st[0] if not os.environ.get("MF_SHM_MULTICAST") else (st[0], mc)
 
 
 @pytest.mark.multigpu
@@ -216,3 +219,15 @@ def test_real_ranks_over_nvlink():
     n = min(torch.cuda.device_count(), 4)
     url = f"127.0.0.1:{free_port()}"
     assert run_ranks(_real_ranks, n, (url,), timeout=300, with_barrier=True) == [0] * n
+
+
+@pytest.mark.multigpu
+def test_real_ranks_with_nvlink_multicast():
+    """The same scenario with the multicast alias of the heap switched on: large all-reduces of heap tensors go
+    through multimem load-reduce / store. No rank leaves early (a rank that dies while bound to a multicast
+    object disturbs its peers)."""
+    n = min(torch.cuda.device_count(), 4)
+    url = f"127.0.0.1:{free_port()}"
+    res = run_ranks(_real_ranks, n, (url,), timeout=300, with_barrier=True, env={"MF_SHM_MULTICAST": "1"})
+    assert [r[0] for r in res] == [0] * n
+    assert len({r[1] for r in res}) == 1      # every rank took the same decision about the alias
