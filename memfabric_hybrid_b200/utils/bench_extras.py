@@ -199,6 +199,62 @@ def tp_mlp(heap, world, flush):
             "gemm_rs_us": round(rs * 1e3, 1)}
 
 
+def xcopy_sweep(h, rank, world, flush):
+    """KV-block puts / gets of 1-64 blocks, one contiguous 512 MiB copy in both directions, the host legs, and NCCL
+    send/recv of the same bytes as the library baseline. Pool copies are enqueued on a stream and timed with events."""
+    from ..api import bm
+    peer = (rank + 1) % world
+    mine, theirs = h.peer_rank_ptr(rank, bm.BmMemType.DEVICE), h.peer_rank_ptr(peer, bm.BmMemType.DEVICE)
+    big = 512 << 20
+    src = torch.empty(big, dtype=torch.uint8, device="cuda").random_(0, 255)
+    dst = torch.empty(big, dtype=torch.uint8, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    fl = bm.ASYNC_COPY_FLAG | bm.FLAG_USE_EXTERNAL_STREAM
+    out = []
+
+    def timed(fn, iters=5):
+        return _timed(fn, iters, 2, None)
+
+    for blocks in (1, 8, 64):
+        segs = bu.kv_block_segments(blocks)
+        nbytes = blocks * bu.KV_BLOCK_BYTES
+        put = h.prepare_batch([src.data_ptr() + o for o, _ in segs], [theirs + o for o, _ in segs], [s for _, s in segs])
+        get = h.prepare_batch([theirs + o for o, _ in segs], [dst.data_ptr() + o for o, _ in segs], [s for _, s in segs])
+        p_ms = timed(lambda: h.copy_prepared(put, bm.BmCopyType.L2G, fl, stream))
+        bu.barrier()
+        g_ms = timed(lambda: h.copy_prepared(get, bm.BmCopyType.G2L, fl, stream))
+        bu.barrier()
+        out.append({"op": "kv_blocks", "blocks": blocks, "bytes": nbytes, "put_us": round(p_ms * 1e3, 1), "put_GBps": round(nbytes / p_ms / 1e6, 1),
+                    "get_us": round(g_ms * 1e3, 1), "get_GBps": round(nbytes / g_ms / 1e6, 1)})
+    p_ms = timed(lambda: h.copy_data(src.data_ptr(), theirs, big, bm.BmCopyType.L2G, fl, stream))
+    bu.barrier()
+    g_ms = timed(lambda: h.copy_data(theirs, dst.data_ptr(), big, bm.BmCopyType.G2L, fl, stream))
+    bu.barrier()
+    row = {"op": "contiguous", "bytes": big, "d2rd_GBps": round(big / p_ms / 1e6, 1), "rd2d_GBps": round(big / g_ms / 1e6, 1)}
+    if world > 1:
+        prev = (rank - 1) % world
+
+        def nccl():
+            ops = [dist.P2POp(dist.isend, src, peer), dist.P2POp(dist.irecv, dst, prev)]
+            for r in dist.batch_isend_irecv(ops):
+                r.wait()
+        row["nccl_send_recv_GBps"] = round(big / timed(nccl) / 1e6, 1)
+    out.append(row)
+    # host legs: pinned host memory <-> the pool (PCIe)
+    host = torch.empty(256 << 20, dtype=torch.uint8).pin_memory()
+    n = host.numel()
+    h2d = timed(lambda: h.copy_data(host.data_ptr(), mine, n, bm.BmCopyType.H2G, fl, stream))
+    d2h = timed(lambda: h.copy_data(mine, host.data_ptr(), n, bm.BmCopyType.G2H, fl, stream))
+    row = {"op": "host_legs", "bytes": n, "h2d_GBps": round(n / h2d / 1e6, 1), "d2h_GBps": round(n / d2h / 1e6, 1)}
+    if world > 1:
+        rh2d = timed(lambda: h.copy_data(host.data_ptr(), theirs, n, bm.BmCopyType.H2G, fl, stream))
+        bu.barrier()
+        row["h2rd_GBps"] = round(n / rh2d / 1e6, 1)
+    out.append(row)
+    torch.cuda.synchronize()
+    return out
+
+
 def run(rank, world, local, _bm_handle):
     from ..ops.collectives import Communicator
     from ..ops.heap import SymmetricHeap
@@ -213,6 +269,10 @@ def run(rank, world, local, _bm_handle):
     heap = SymmetricHeap(f"{addr}:{port}", world, rank, local, 7 << 30)
     flush = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
     out = {}
+    try:
+        out["xcopy"] = xcopy_sweep(_bm_handle, rank, world, flush)
+    except Exception as e:  # noqa: BLE001
+        out["xcopy"] = {"error": repr(e)[:200]}
     comm = Communicator(heap, stage_bytes=64 << 20)
     out["collectives"] = collectives(comm, world, flush)
     mark = heap.mark()
