@@ -41,6 +41,15 @@ def _rank(rank, world, url, sync):
     # beyond the 8 MiB that the peer contributed (its slot is 16 MiB): refused
     assert h.copy_data(src.ctypes.data, pdev + 9 * MiB, 4096, bm.BmCopyType.H2G, 0) != 0
     mf.get_and_clear_last_err_msg()
+    # a batch with one bad destination: the good items are copied and every item reports its own result
+    rc, res = h.copy_data_batch_partial_succeed([src.ctypes.data, src.ctypes.data + 4096, src.ctypes.data + 8192],
+                                                [pdev + 4 * MiB, pdev + 9 * MiB, pdev + 4 * MiB + 8192], [4096] * 3, 3,
+                                                bm.BmCopyType.H2G, 0)
+    assert rc != 0 and res[0] == 0 and res[1] != 0 and res[2] == 0, (rc, res)
+    mf.get_and_clear_last_err_msg()
+    back = np.zeros(4096, dtype=np.uint8)
+    assert h.copy_data(pdev + 4 * MiB + 8192, back.ctypes.data, 4096, bm.BmCopyType.G2H, 0) == 0
+    assert np.array_equal(back, src[8192:12288])
     # the peer extends its slice; after the update the same address is valid
     sync.wait(60)
     if me == 0:
