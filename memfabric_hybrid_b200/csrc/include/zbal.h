@@ -9,6 +9,7 @@
 #include "zbal_bootstrap.h"
 #include "zbal_mem_allocator.h"
 #include "zbal_operations.h"
+#include "zbal_moe.h"
 
 #ifdef __cplusplus
 extern "C" {

@@ -44,6 +44,14 @@ class CommPropertyC(C.Structure):
                 ("rankStep", u32), ("signalGva", u64), ("stageBytes", u64), ("epoch", u64)]
 
 
+class MoeOptionsC(C.Structure):
+    _fields_ = [("maxTokens", u32), ("hidden", u32), ("experts", u32), ("topk", u32), ("maxRecv", u32), ("rawBf16", u32)]
+
+
+class MoeBuffersC(C.Structure):
+    _fields_ = [("recvTokens", vp), ("recvScales", vp), ("recvInfo", vp), ("maxRecv", u32), ("localExperts", u32)]
+
+
 class SmaStatsC(C.Structure):
     _fields_ = [(n, u64) for n in ("heapSize", "inUseBytes", "cachedBytes", "peakInUseBytes", "largestFreeBlock", "mallocCalls",
                                    "freeCalls", "cacheHits", "heapCarves", "failedMallocs")]
@@ -92,6 +100,18 @@ def _declare(l):
     s(l, "zbal_gather", i32, vp, vp, u64, C.c_int, C.c_uint16, vp, vp)
     s(l, "zbal_barrier", i32, vp, vp)
     s(l, "zbal_send", i32, vp, C.c_size_t, C.c_int, u32, vp, vp)
+    s(l, "zbal_moe_create", i32, vp, P(MoeOptionsC), P(vp))
+    s(l, "zbal_moe_destroy", i32, vp)
+    s(l, "zbal_moe_get_buffers", i32, vp, P(MoeBuffersC))
+    s(l, "zbal_moe_get_status", i32, vp, P(i32))
+    s(l, "zbal_dispatch_normal_layout", i32, vp, vp, i64, vp, vp, vp, vp, vp)
+    s(l, "zbal_dispatch_normal_notify", i32, vp, vp, vp, vp, vp, vp, vp)
+    s(l, "zbal_dispatch_normal", i32, vp, vp, i64, vp, vp, vp, vp, vp)
+    s(l, "zbal_combine_normal", i32, vp, vp, i64, vp, i32, vp, i64, vp, vp)
+    s(l, "zbal_dispatch_low_latency", i32, vp, vp, i64, vp, vp, vp, vp, vp, vp, vp, vp, vp)
+    s(l, "zbal_combine_low_latency", i32, vp, vp, i64, vp, i32, vp, vp, i64, vp, vp)
+    s(l, "zbal_fused_deep_moe_workspace", u64, vp, u32)
+    s(l, "zbal_fused_deep_moe", i32, vp, vp, i64, vp, vp, vp, vp, vp, vp, u32, vp, vp, vp)
     s(l, "zbal_recv", i32, vp, C.c_size_t, C.c_int, u32, vp, vp)
 
 

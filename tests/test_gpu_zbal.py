@@ -212,3 +212,98 @@ def test_buffer_multi_gpu():
     n = min(torch.cuda.device_count(), 4)
     port = free_port()
     assert run_ranks(_buffer_scenario, n, (port,), timeout=420, with_barrier=True) == [0] * n
+
+
+def _moe_capi_scenario(rank, world, port, sync):
+    """The C entry points of the MoE path (zbal_moe_create, zbal_dispatch_*, zbal_combine_*, zbal_fused_deep_moe) through ctypes."""
+    import ctypes as C
+    import torch
+    import memfabric_hybrid_b200.zbal as zbal
+    from memfabric_hybrid_b200.zbal import _capi as K
+    from memfabric_hybrid_b200.ops import moe as M
+    from memfabric_hybrid_b200.ops.heap import tensor_at
+    dev = rank % torch.cuda.device_count()
+    torch.cuda.set_device(dev)
+    assert zbal.zbal_init(world, dev, rank, 1 << 30, ip_port=f"127.0.0.1:{port}", start_config_server=True)
+    l = K.lib()
+    T, H, I, Kk = 64, 1024, 512, 2
+    E = 4 * world
+    El = E // world
+    o = K.MoeOptionsC(T, H, E, Kk, 0, 0)
+    moe = C.c_void_p()
+    K.check(l.zbal_moe_create(l.zbal_comm_get_global(), C.byref(o), C.byref(moe)), "zbal_moe_create")
+    bufs = K.MoeBuffersC()
+    K.check(l.zbal_moe_get_buffers(moe, C.byref(bufs)), "get_buffers")
+    assert bufs.localExperts == El and bufs.maxRecv == T * world * min(Kk, El)
+    g = torch.Generator("cuda").manual_seed(rank)
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    w, idx = torch.softmax(torch.randn(T, E, device="cuda", generator=g), -1).topk(Kk, dim=-1)
+    idx, w = idx.to(torch.int32).contiguous(), (w / w.sum(-1, keepdim=True)).float().contiguous()
+    i32 = dict(dtype=torch.int32, device="cuda")
+    tpr, tpe, sidx = torch.empty(world, **i32), torch.empty(E, **i32), torch.zeros(T * Kk, **i32)
+    inr = torch.empty(T, world, dtype=torch.uint8, device="cuda")
+    rpe, row_off, put_off, src_off = torch.empty(El, **i32), torch.empty(El + 1, **i32), torch.empty(E, **i32), torch.empty(El * world, **i32)
+    s = torch.cuda.current_stream().cuda_stream
+    K.check(l.zbal_dispatch_normal_layout(moe, idx.data_ptr(), T, tpr.data_ptr(), tpe.data_ptr(), sidx.data_ptr(), inr.data_ptr(), s), "layout")
+    K.check(l.zbal_dispatch_normal_notify(moe, tpe.data_ptr(), rpe.data_ptr(), row_off.data_ptr(), put_off.data_ptr(), src_off.data_ptr(), s), "notify")
+    K.check(l.zbal_dispatch_normal(moe, x.data_ptr(), T, idx.data_ptr(), w.data_ptr(), sidx.data_ptr(), put_off.data_ptr(), s), "dispatch")
+    torch.cuda.synchronize()
+    assert int(tpe.sum()) == T * Kk
+    rows = int(row_off[-1])
+    q = tensor_at(bufs.recvTokens, (rows, H), torch.uint8).view(torch.float8_e4m3fn)
+    sc = tensor_at(bufs.recvScales, (rows, H // 128), torch.float32)
+    y = (q.float().view(rows, H // 128, 128) * sc.view(rows, H // 128, 1)).view(rows, H).to(torch.bfloat16)   # identity experts
+    out = torch.empty(T, H, dtype=torch.bfloat16, device="cuda")
+    K.check(l.zbal_combine_normal(moe, y.data_ptr(), H, row_off[El:].data_ptr(), 1, idx.data_ptr(), T, out.data_ptr(), s), "combine")
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.float(), x.float(), rtol=0.08, atol=0.08)     # the routing weights of a token sum to one
+    # low-latency pair
+    out.zero_()
+    K.check(l.zbal_dispatch_low_latency(moe, x.data_ptr(), T, idx.data_ptr(), w.data_ptr(), sidx.data_ptr(), tpe.data_ptr(), rpe.data_ptr(),
+                                        row_off.data_ptr(), put_off.data_ptr(), src_off.data_ptr(), s), "ll dispatch")
+    torch.cuda.synchronize()
+    rows = int(row_off[-1])
+    q = tensor_at(bufs.recvTokens, (rows, H), torch.uint8).view(torch.float8_e4m3fn)
+    sc = tensor_at(bufs.recvScales, (rows, H // 128), torch.float32)
+    y = (q.float().view(rows, H // 128, 128) * sc.view(rows, H // 128, 1)).view(rows, H).to(torch.bfloat16)
+    K.check(l.zbal_combine_low_latency(moe, y.data_ptr(), H, row_off[El:].data_ptr(), 1, idx.data_ptr(), None, T, out.data_ptr(), s), "ll combine")
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out.float(), x.float(), rtol=0.08, atol=0.08)
+    # fused path against an fp32 reference from the bf16 master weights of ALL experts (every rank can regenerate them)
+    def weights(r):
+        gg = torch.Generator("cuda").manual_seed(1000 + r)
+        return ((torch.randn(El, 2 * I, H, device="cuda", generator=gg) * 0.02).to(torch.bfloat16),
+                (torch.randn(El, H, I, device="cuda", generator=gg) * 0.02).to(torch.bfloat16))
+    w1, w2 = weights(rank)
+    w1q, w1s = M.quantize_weight_fp8(w1)
+    w1q = M.interleave_gate_up_fp8(w1q)
+    w2q, w2s = M.quantize_weight_fp8(w2)
+    ws = torch.empty(int(l.zbal_fused_deep_moe_workspace(moe, I)), dtype=torch.uint8, device="cuda")
+    K.check(l.zbal_fused_deep_moe(moe, x.data_ptr(), T, idx.data_ptr(), w.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), I,
+                                  ws.data_ptr(), out.data_ptr(), s), "fused")
+    torch.cuda.synchronize()
+    allw = [weights(r) for r in range(world)]
+    ref = torch.zeros(T, H, device="cuda")
+    for t in range(T):
+        for k in range(Kk):
+            e = int(idx[t, k])
+            a1, a2 = allw[e // El][0][e % El].float(), allw[e // El][1][e % El].float()
+            h = a1 @ x[t].float()
+            ref[t] += w[t, k] * (a2 @ (torch.nn.functional.silu(h[:I]) * h[I:]))
+    err = (out.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
+    assert err < 0.1, f"fused MoE differs from the fp32 reference: {err}"
+    st = C.c_int32(-1)
+    K.check(l.zbal_moe_get_status(moe, C.byref(st)), "status")
+    K.check(l.zbal_moe_destroy(moe), "destroy")
+    zbal.zbal_uninit()
+    return st.value
+
+
+def test_moe_c_api_single_gpu():
+    assert run_ranks(_moe_capi_scenario, 1, (free_port(),), timeout=300, with_barrier=True) == [0]
+
+
+@pytest.mark.multigpu
+def test_moe_c_api_multi_gpu():
+    n = min(torch.cuda.device_count(), 4)
+    assert run_ranks(_moe_capi_scenario, n, (free_port(),), timeout=420, with_barrier=True) == [0] * n
