@@ -86,6 +86,11 @@ int32_t zbal_fused_deep_moe(zbal_moe_t moe, const void *x, int64_t tokens, const
                             const void *gmm1Weight, const float *gmm1Scale, const void *gmm2Weight, const float *gmm2Scale, uint32_t inter,
                             void *workspace, void *xOut, zbal_stream_t stream);
 
+/* Host-side plan of the reference's load balancing (which helper rank pushes which range of which rank's tokens);
+ * counts: [ranks, experts] send counts, matrix: [ranks, ranks * 2] int32 out. Not used by the kernels here. */
+int32_t zbal_moe_balance_matrix(const int32_t *counts, uint32_t ranks, uint32_t experts, uint32_t topk, float factorHigh, float factorLow,
+                                uint32_t minTokens, int32_t *matrix);
+
 #ifdef __cplusplus
 }
 #endif

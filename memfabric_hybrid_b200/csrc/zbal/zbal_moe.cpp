@@ -5,6 +5,7 @@
 // Parity of role: app/zbal/src/csrc/operators/zbal_operations.cpp (dispatch / combine / fused entry points) and
 // app/zbal/src/csrc/adaptor/deepep/zbal_deepep.cpp:210-700 (buffer ownership, call sequencing) of the reference.
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <memory>
 #include <mutex>
@@ -405,3 +406,62 @@ int32_t zbal_fused_deep_moe(zbal_moe_t moe, const void *x, int64_t tokens, const
 }
 
 }  // extern "C"
+
+// ---- load-balance matrix -----------------------------------------------------------------------------
+// The plan the reference's notify kernel derives from the gathered send counts
+// (ops/dispatch_combine_normal/zbal_kernel_notify_dispatch.h:421-498): row = helper rank, column pair
+// (2c, 2c + 1) = [start, end) of rank c's tokens that the helper pushes on c's behalf, -1 = none. Every rank
+// computes the same matrix from the same counts. tokens[r] = sum(counts[r]) / topk; avg = total / ranks; a rank
+// above the average may handle ceil(avg * factorHigh) tokens, the others ceil(avg * factorLow); when
+// avg <= minTokens every rank handles only itself; otherwise each rank first takes min(tokens, capacity) of its
+// own and the overflow of overloaded ranks goes, in rank order, to ranks with spare capacity.
+// The dispatch kernels of this library do not use the plan (on NVSwitch a token routed through a helper crosses
+// NVLink twice); the function exists for schedulers that want the same numbers the reference would produce.
+extern "C" int32_t zbal_moe_balance_matrix(const int32_t *counts, uint32_t ranks, uint32_t experts, uint32_t topk, float factorHigh, float factorLow,
+                                           uint32_t minTokens, int32_t *matrix)
+{
+    if (counts == nullptr || matrix == nullptr || ranks == 0 || experts == 0 || topk == 0) return MF_FAIL(Z_INVALID_PARAM, "balance matrix: bad argument");
+    std::vector<int64_t> tokens(ranks, 0), cap(ranks, 0), taken(ranks, 0);
+    int64_t total = 0;
+    for (uint32_t r = 0; r < ranks; r++) {
+        int64_t s = 0;
+        for (uint32_t e = 0; e < experts; e++) s += counts[(size_t)r * experts + e];
+        tokens[r] = s / topk;
+        total += tokens[r];
+    }
+    for (size_t i = 0; i < (size_t)ranks * ranks * 2; i++) matrix[i] = -1;
+    const double avg = (double)total / ranks;
+    auto put = [&](uint32_t helper, uint32_t owner, int64_t b, int64_t e) {
+        matrix[((size_t)helper * ranks + owner) * 2] = (int32_t)b;
+        matrix[((size_t)helper * ranks + owner) * 2 + 1] = (int32_t)e;
+    };
+    if (avg <= (double)minTokens) {
+        for (uint32_t r = 0; r < ranks; r++)
+            if (tokens[r] > 0) put(r, r, 0, tokens[r]);
+        return Z_OK;
+    }
+    for (uint32_t r = 0; r < ranks; r++) {
+        const double f = (double)tokens[r] > avg ? factorHigh : factorLow;
+        cap[r] = (int64_t)std::ceil(avg * f - 1e-3);  // the factors arrive as floats: 1.2f is a hair above 1.2
+        taken[r] = std::min(tokens[r], cap[r]);
+        if (taken[r] > 0) put(r, r, 0, taken[r]);
+    }
+    uint32_t helper = 0;
+    for (uint32_t owner = 0; owner < ranks; owner++) {
+        int64_t next = taken[owner];
+        while (next < tokens[owner]) {
+            while (helper < ranks && (helper == owner || taken[helper] >= cap[helper])) helper++;
+            if (helper >= ranks) {
+                // nobody has room left: the owner keeps the rest itself
+                put(owner, owner, 0, tokens[owner]);
+                next = tokens[owner];
+                break;
+            }
+            const int64_t n = std::min(tokens[owner] - next, cap[helper] - taken[helper]);
+            put(helper, owner, next, next + n);
+            taken[helper] += n;
+            next += n;
+        }
+    }
+    return Z_OK;
+}

@@ -154,3 +154,32 @@ def test_bootstrap_and_communicators_over_fake_backend():
     slots = [r[0] for r in res]
     assert slots[0] == slots[2] and slots[1] == slots[3] and slots[0] != slots[1]
     assert len({r[1] for r in res}) == 1
+
+
+def test_balance_matrix_plan():
+    """The helper plan: nothing to do below the threshold; an overloaded rank's overflow goes to ranks with room."""
+    import numpy as np
+    from memfabric_hybrid_b200.zbal import _capi as K
+    l = K.lib()
+    f = l.zbal_moe_balance_matrix
+    f.restype = C.c_int32
+    f.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_float, C.c_uint32, C.c_void_p]
+    ranks, experts, topk = 4, 8, 2
+
+    def plan(tokens, min_tokens=128):
+        counts = np.zeros((ranks, experts), dtype=np.int32)
+        for r, t in enumerate(tokens):
+            counts[r, 0] = t * topk
+        m = np.empty((ranks, ranks * 2), dtype=np.int32)
+        assert f(counts.ctypes.data, ranks, experts, topk, 1.2, 1.0, min_tokens, m.ctypes.data) == 0
+        return m.reshape(ranks, ranks, 2)
+    small = plan([100, 50, 10, 0])
+    for r, t in enumerate([100, 50, 10, 0]):
+        assert tuple(small[r, r]) == ((0, t) if t else (-1, -1))
+    assert (small[~np.eye(ranks, dtype=bool)] == -1).all()
+    big = plan([4000, 400, 400, 400])                       # avg 1300: rank 0 may keep 1560, others may hold 1300
+    assert tuple(big[0, 0]) == (0, 1560)
+    covered = sorted(tuple(big[h, 0]) for h in range(ranks) if big[h, 0, 0] >= 0)
+    assert covered[0][0] == 0 and covered[-1][1] == 4000 and all(covered[i][1] == covered[i + 1][0] for i in range(len(covered) - 1))
+    load = [sum(int(big[h, o, 1] - big[h, o, 0]) for o in range(ranks) if big[h, o, 0] >= 0) for h in range(ranks)]
+    assert load[0] == 1560 and max(load[1:]) <= 1300 and sum(load) == 5200
