@@ -208,12 +208,15 @@ def xcopy_sweep(h, rank, world, flush):
     big = 512 << 20
     src = torch.empty(big, dtype=torch.uint8, device="cuda").random_(0, 255)
     dst = torch.empty(big, dtype=torch.uint8, device="cuda")
-    stream = torch.cuda.current_stream().cuda_stream
+    side = torch.cuda.Stream()          # the copies and the timing events share this stream
+    side.wait_stream(torch.cuda.current_stream())
+    stream = side.cuda_stream
     fl = bm.ASYNC_COPY_FLAG | bm.FLAG_USE_EXTERNAL_STREAM
     out = []
 
     def timed(fn, iters=5):
-        return _timed(fn, iters, 2, None)
+        with torch.cuda.stream(side):
+            return _timed(fn, iters, 2, None)
 
     for blocks in (1, 8, 64):
         segs = bu.kv_block_segments(blocks)
