@@ -592,6 +592,99 @@ template <typename T> __global__ void __launch_bounds__(512) k_broadcast_zc(Coll
     lane_sync(t, me, 1, a.epoch, 0x187);
 }
 
+// Raw 16-byte multimem store (any element type: the bits travel unchanged).
+__device__ __forceinline__ void multimem_st16(uint64_t p, const uint4 &v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)),
+                 "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
+}
+
+// all-gather through the multicast alias: every rank writes its shard ONCE and the switch delivers it to all
+// ranks' outputs (send traffic n per rank instead of (W-1) n). Needs the output at the same slot offset on every
+// rank; otherwise, all together, the ranks fall back to one peer store per destination.
+template <typename T, typename TO> __global__ void __launch_bounds__(512) k_allgather_mc(CollArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const uint32_t world = t.world;
+    __shared__ uint64_t p_out[kMaxRanks], p_unused[kMaxRanks];
+    const uint64_t slot = t.heap_base + (uint64_t)me * t.stride;
+    if (!lane_sync_xchg(t, me, 0, a.epoch, 0x18a, a.out - slot, 0, p_out, p_unused)) return;
+    const T *in = reinterpret_cast<const T *>(a.in);
+    const uint64_t ps = a.part_stride ? a.part_stride : a.n;
+    constexpr int G = 16 / sizeof(TO);  // output elements per 16-byte store
+    bool same = t.mc_base != 0 && (a.n % G) == 0 && (ps % G) == 0 && (p_out[0] & 15) == 0 && (reinterpret_cast<uint64_t>(in) & 15) == 0;
+    for (uint32_t r = 1; r < world; r++) same = same && p_out[r] == p_out[0];
+    const Range sub = cta_range<8>(a.n);
+    if (same) {
+        const uint64_t dst = t.mc_base + p_out[0] + (uint64_t)me * ps * sizeof(TO);
+        for (uint64_t i = sub.beg + (uint64_t)threadIdx.x * G; i < sub.end; i += (uint64_t)blockDim.x * G) {
+            float f[G];
+#pragma unroll
+            for (int h = 0; h < G / Vec<T>::N; h++) {
+                float tmp[Vec<T>::N];
+                Vec<T>::load(in + i + h * Vec<T>::N, tmp);
+#pragma unroll
+                for (int k = 0; k < Vec<T>::N; k++) f[h * Vec<T>::N + k] = a.scale != 1.f ? tmp[k] * a.scale : tmp[k];
+            }
+            uint4 v;
+            {
+                float g[Vec<TO>::N];
+#pragma unroll
+                for (int k = 0; k < Vec<TO>::N; k++) g[k] = f[k];
+                Vec<TO>::store(reinterpret_cast<TO *>(&v), g);
+            }
+            multimem_st16(dst + i * sizeof(TO), v);
+        }
+    } else {
+        for (uint32_t k = 0; k < world; k++) {
+            const uint32_t r = (me + k) % world;
+            TO *dst = reinterpret_cast<TO *>(peer_ptr(t, r, p_out[r])) + (uint64_t)me * ps;
+            cta_convert_copy<T, TO>(in, dst, sub.beg, sub.end, a.scale);
+        }
+    }
+    lane_sync(t, me, 1, a.epoch, 0x18b);
+}
+
+// rooted copy through the multicast alias: the root writes once, the switch fans out.
+template <typename T> __global__ void __launch_bounds__(512) k_broadcast_mc(CollArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const uint32_t world = t.world;
+    __shared__ uint64_t p_out[kMaxRanks], p_unused[kMaxRanks];
+    const uint64_t slot = t.heap_base + (uint64_t)me * t.stride;
+    if (!lane_sync_xchg(t, me, 0, a.epoch, 0x18c, a.out - slot, 0, p_out, p_unused)) return;
+    constexpr int G = 16 / sizeof(T);
+    const T *in = reinterpret_cast<const T *>(a.in);
+    bool same = t.mc_base != 0 && a.algo == 0 && (a.n % G) == 0 && (p_out[0] & 15) == 0;
+    for (uint32_t r = 1; r < world; r++) same = same && p_out[r] == p_out[0];
+    if (me == a.root) {
+        const Range sub = cta_range<8>(a.n);
+        if (same && (reinterpret_cast<uint64_t>(in) & 15) == 0) {
+            const uint64_t dst = t.mc_base + p_out[0];
+            const uint64_t step = (uint64_t)blockDim.x * G;
+            uint64_t i = sub.beg + (uint64_t)threadIdx.x * G;
+            for (; i + 3 * step < sub.end; i += 4 * step) {
+                uint4 v[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) v[u] = __ldcg(reinterpret_cast<const uint4 *>(in + i + u * step));
+#pragma unroll
+                for (int u = 0; u < 4; u++) multimem_st16(dst + (i + u * step) * sizeof(T), v[u]);
+            }
+            for (; i < sub.end; i += step) multimem_st16(dst + i * sizeof(T), __ldcg(reinterpret_cast<const uint4 *>(in + i)));
+        } else {
+            for (uint32_t k = 0; k < world; k++) {
+                const uint32_t r = (me + k) % world;
+                const T *src = a.algo == 1 ? in + (uint64_t)r * (a.part_stride ? a.part_stride : a.n) : in;
+                T *dst = reinterpret_cast<T *>(peer_ptr(t, r, p_out[r]));
+                if (src != dst) cta_raw_copy<T>(src, dst, sub.beg, sub.end);
+            }
+        }
+    }
+    lane_sync(t, me, 1, a.epoch, 0x18d);
+}
+
 // all-to-all-v (bytes). Each rank stages its whole send buffer plus its (offset, count) table; after the
 // handshake every rank pulls its pieces from the peers' staging.
 //   table in staging A header: W x {u64 send_off, u64 send_cnt} toward each destination, bytes
@@ -807,12 +900,29 @@ int mf_coll_launch(int kind, int in_dtype, int out_dtype, const CollArgs *args, 
     const bool to_bf16 = out_dtype == DT_BF16;
     if (!same && !to_bf16) return -2;
     if (a.zero_copy == 3) {
-        // direct mode through the NVLink multicast alias (all-reduce, sum, same type in and out)
-        if (a.team.emu || kind != 0 || !same || a.team.mc_base == 0) return -4;
-        if (in_dtype == DT_BF16) return launch_allreduce_mc<__nv_bfloat16>(a, ctas, threads, s);
-        if (in_dtype == DT_F16) return launch_allreduce_mc<__half>(a, ctas, threads, s);
-        if (in_dtype == DT_F32) return launch_allreduce_mc<float>(a, ctas, threads, s);
-        return -2;
+        // direct mode through the NVLink multicast alias: all-reduce (sum, same type in and out), all-gather, rooted copy
+        if (a.team.emu || a.team.mc_base == 0) return -4;
+        if (kind == 0) {
+            if (!same) return -4;
+            if (in_dtype == DT_BF16) return launch_allreduce_mc<__nv_bfloat16>(a, ctas, threads, s);
+            if (in_dtype == DT_F16) return launch_allreduce_mc<__half>(a, ctas, threads, s);
+            if (in_dtype == DT_F32) return launch_allreduce_mc<float>(a, ctas, threads, s);
+            return -2;
+        }
+        if (kind == 2) {
+            if (in_dtype == DT_BF16) return launch(k_allgather_mc<__nv_bfloat16, __nv_bfloat16>, a, ctas, threads, s, false);
+            if (in_dtype == DT_F16) return same ? launch(k_allgather_mc<__half, __half>, a, ctas, threads, s, false) : -2;
+            if (in_dtype == DT_F32)
+                return same ? launch(k_allgather_mc<float, float>, a, ctas, threads, s, false)
+                            : launch(k_allgather_mc<float, __nv_bfloat16>, a, ctas, threads, s, false);
+            if (in_dtype == DT_I32) return same ? launch(k_allgather_mc<int, int>, a, ctas, threads, s, false) : -2;
+            return -2;
+        }
+        if (kind == 3) {
+            if (in_dtype == DT_F32 || in_dtype == DT_I32) return launch(k_broadcast_mc<float>, a, ctas, threads, s, false);
+            return launch(k_broadcast_mc<__nv_bfloat16>, a, ctas, threads, s, false);
+        }
+        return -4;
     }
     if (a.zero_copy == 2) {
         // direct mode: the buffers named by the operation live inside the callers' own slices; emulation

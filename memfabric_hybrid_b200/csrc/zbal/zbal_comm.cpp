@@ -177,7 +177,7 @@ int AllGatherBytes(Comm &c, const void *in, void *out, uint64_t bytes, void *str
     const uint64_t m = bytes / unit;
     if (bytes * c.size > DirectMin() && InSlice(out, bytes * c.size)) {
         MfCollArgs a = BaseArgs(c, in, out, m, 1.f, 0, 0, 0);
-        a.zero_copy = 2;
+        a.zero_copy = c.team.mc_base != 0 ? 3 : 2;  // one multicast store per 16 bytes instead of one store per peer
         return Launched(L->coll(2, kdt, kdt, &a, c.Ctas(bytes * c.size), 512, stream), "all_gather (direct)");
     }
     uint64_t piece = c.stageBytes / unit / c.size;
@@ -208,7 +208,7 @@ int BroadcastBytes(Comm &c, const void *in, void *out, uint64_t bytes, uint32_t 
     const uint64_t total = bytes / unit;
     if (bytes > DirectMin() && InSlice(out, bytes)) {
         MfCollArgs a = BaseArgs(c, in, out, total, 1.f, 0, root, 0);
-        a.zero_copy = 2;
+        a.zero_copy = c.team.mc_base != 0 ? 3 : 2;
         return Launched(L->coll(3, kdt, kdt, &a, c.Ctas(bytes), 512, stream), "broadcast (direct)");
     }
     uint64_t piece = c.stageBytes / unit;

@@ -224,7 +224,7 @@ class Communicator:
         if m * self.world * oes > DIRECT_MIN and self._in_heap(out):
             epoch, stage = self._next()
             args = self._args(x, out, m, epoch, stage, scale)
-            args.zero_copy = 2
+            args.zero_copy = 3 if (self.heap.mc_base != 0 and not self.no_multicast) else 2
             _check(_cu().mf_coll_launch(2, DT[x.dtype], DT[od], C.byref(args), self._ctas(m * self.world * oes), 512, _stream()),
                    "all_gather (direct)")
             return out

@@ -83,6 +83,11 @@ def collectives(comm, world, flush):
     ho = heap.view(ho_off, (n,), torch.bfloat16)
     ms = _timed(lambda: comm.all_gather(shard, out=ho, out_dtype=torch.bfloat16), 6, 2, flush)
     row = {"op": "all_gather_f32_to_bf16", "bytes": 64 << 20, "us": round(ms * 1e3, 1)}
+    if heap.mc_base:
+        comm.no_multicast = True
+        row["peer_st_us"] = round(_timed(lambda: comm.all_gather(shard, out=ho, out_dtype=torch.bfloat16), 6, 2, flush) * 1e3, 1)
+        comm.no_multicast = False
+        row["multicast"] = True
     if world > 1:
         g = torch.empty(n, device="cuda")
 
