@@ -197,7 +197,9 @@ def main() -> int:
             "config": {"model": "DeepSeek-R1 KV block: 61 layers x (128 KiB + 16 KiB) = 122 segments, 8784 KiB",
                        "global_batch": world * nblk, "seq_len": bu.KV_SEGMENTS, "parallelism": f"ring-put x{world}",
                        "blocks_per_step": nblk, "bytes_per_step_per_gpu": step_bytes,
-                       "l2": "inputs larger than L2 (549 MiB per step)", "api": "smem_bm_copy_batch L2G, async on a CUDA stream"},
+                       "l2": "inputs larger than L2 (549 MiB per step)", "api": "smem_bm_copy_batch L2G, async on a CUDA stream",
+                       "scaling_note": "with 1 GPU the 'remote' slice is the GPU's own HBM (no NVLink); from 2 GPUs on every put "
+                                       "crosses NVLink and the per-GPU rate is flat (about 670 GB/s of the 770 GB/s measured peer copy)"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": step_bytes, "d2h_bytes_per_step": 8,
                     "ms_per_step": round(e2e_ms, 4)},
