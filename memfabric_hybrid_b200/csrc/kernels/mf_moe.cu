@@ -178,6 +178,14 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs &a)
     __shared__ int dst_rank[16];
     __shared__ int dst_pos[16];
     __shared__ float dst_w[16];
+    // the row of the NEXT token is fetched while the stores of the current one drain: the loop is otherwise a chain
+    // of HBM latency (row load) and NVLink issue (eight peer stores per thread)
+    uint4 nxt_lo = make_uint4(0, 0, 0, 0), nxt_hi = make_uint4(0, 0, 0, 0);
+    if (vec < vecs && (int)blockIdx.x < a.sh.T) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.x + (int64_t)blockIdx.x * H + vec * 16);
+        nxt_lo = __ldg(src);
+        nxt_hi = __ldg(src + 1);
+    }
     for (int tok = blockIdx.x; tok < a.sh.T; tok += gridDim.x) {
         if (threadIdx.x < K) {
             const int e = a.topk_idx[tok * K + threadIdx.x];
@@ -200,10 +208,15 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs &a)
 #pragma unroll
             for (int i = 0; i < 16; i++) f[i] = 0.f;
             if (vec < vecs) {
-                const uint4 *src = reinterpret_cast<const uint4 *>(a.x + (int64_t)tok * H + vec * 16);
-                const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+                const uint4 lo = nxt_lo, hi = nxt_hi;
                 raw_lo = lo;
                 raw_hi = hi;
+                const int nxt = tok + (int)gridDim.x;
+                if (nxt < a.sh.T) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(a.x + (int64_t)nxt * H + vec * 16);
+                    nxt_lo = __ldg(src);
+                    nxt_hi = __ldg(src + 1);
+                }
                 const __nv_bfloat162 *h0 = reinterpret_cast<const __nv_bfloat162 *>(&lo);
                 const __nv_bfloat162 *h1 = reinterpret_cast<const __nv_bfloat162 *>(&hi);
 #pragma unroll
