@@ -42,6 +42,8 @@ def main(rank: int, world: int, url: str) -> str:
     assert h.copy_data(mine + 8 * MiB, dst.ctypes.data, dst.nbytes, bm.BmCopyType.G2H, 0) == 0    # pool -> host
     ok = bool((dst == peer_value(rank, world)).all())
     h.leave()
+    if rank == 0:
+        time.sleep(1.0)                              # this rank hosts the config store: it leaves the stage last
     h.destroy()
     bm.uninitialize()
     mf.uninitialize()

@@ -67,6 +67,7 @@ def _rank(rank, world, url, sync):
     sync.wait(60)
     rc = h.leave()
     assert rc == 0, f"leave returned {rc}: {mf.get_last_err_msg()}"
+    sync.wait(60)  # rank 0 hosts the config store: it must not tear it down while the peer is still leaving
     h.destroy()
     bm.uninitialize(0)
     mf.uninitialize()
