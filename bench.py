@@ -208,6 +208,7 @@ def main() -> int:
         }
         print(json.dumps(out))
     h.leave()
+    bu.barrier()  # rank 0 hosts the config store: nobody tears down while a peer is still leaving
     h.destroy()
     bm.uninitialize(0)
     mf.uninitialize()
