@@ -416,16 +416,26 @@ __device__ __forceinline__ void combine_reduce_body(const Team &t, const MoeHeap
     for (int tok = blockIdx.x; tok < sh.T; tok += gridDim.x) {
         for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int k = 0; k < sh.K; k++) {
-                if (topk_idx[tok * sh.K + k] < 0) continue;
-                const float wk = topk_w != nullptr ? topk_w[tok * sh.K + k] : 1.f;
-                const uint4 raw = __ldcg(reinterpret_cast<const uint4 *>(comb + ((int64_t)tok * sh.K + k) * sh.H) + v);
-                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+            // the slots of a token are fetched eight at a time (independent loads in flight), then added in slot order
+            for (int k0 = 0; k0 < sh.K; k0 += 8) {
+                uint4 raw[8];
+                float wk[8];
 #pragma unroll
-                for (int e = 0; e < 4; e++) {
-                    const float2 f = __bfloat1622float2(h[e]);
-                    acc[2 * e] += f.x * wk;
-                    acc[2 * e + 1] += f.y * wk;
+                for (int u = 0; u < 8; u++) {
+                    const int k = k0 + u;
+                    const bool on = k < sh.K && topk_idx[tok * sh.K + k] >= 0;
+                    wk[u] = on ? (topk_w != nullptr ? topk_w[tok * sh.K + k] : 1.f) : 0.f;
+                    raw[u] = on ? __ldcg(reinterpret_cast<const uint4 *>(comb + ((int64_t)tok * sh.K + k) * sh.H) + v) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[u]);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float2 f = __bfloat1622float2(h[e]);
+                        acc[2 * e] += f.x * wk[u];
+                        acc[2 * e + 1] += f.y * wk[u];
+                    }
                 }
             }
             uint4 pk;

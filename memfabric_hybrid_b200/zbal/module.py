@@ -76,6 +76,9 @@ def zbal_init(world_size: int, device_id: int, rank_id: int, device_mem_size: in
     if rc != K.Z_OK:
         raise K.ZbalError("zbal_bootstrap", rc)
     _state["output"] = out
+    if torch.cuda.is_available():
+        from ..utils import devtrace
+        devtrace.enable_from_env()  # ZBAL_PROF_ENABLE=1: device timeline, written at exit and on SIGUSR1
     return True
 
 
