@@ -167,7 +167,21 @@ struct DispatchArgs {
     int raw_bf16;               // 1: rows travel as bf16 (receive rows are 2 H bytes, no scales)
 };
 
-__device__ __forceinline__ void dispatch_body(const DispatchArgs &a)
+// Loads this thread's 32 bytes of the first token row a CTA will handle (callers may do it early, e.g. while
+// another CTA still computes the layout).
+__device__ __forceinline__ void dispatch_preload(const DispatchArgs &a, uint4 &lo, uint4 &hi)
+{
+    lo = make_uint4(0, 0, 0, 0);
+    hi = make_uint4(0, 0, 0, 0);
+    const int vec = threadIdx.x;
+    if (vec < a.sh.H / 16 && (int)blockIdx.x < a.sh.T) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.x + (int64_t)blockIdx.x * a.sh.H + vec * 16);
+        lo = __ldg(src);
+        hi = __ldg(src + 1);
+    }
+}
+
+__device__ __forceinline__ void dispatch_body(const DispatchArgs &a, uint4 nxt_lo, uint4 nxt_hi)
 {
     const Team &t = a.team;
     const uint32_t me = team_rank(t);
@@ -180,12 +194,6 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs &a)
     __shared__ float dst_w[16];
     // the row of the NEXT token is fetched while the stores of the current one drain: the loop is otherwise a chain
     // of HBM latency (row load) and NVLink issue (eight peer stores per thread)
-    uint4 nxt_lo = make_uint4(0, 0, 0, 0), nxt_hi = make_uint4(0, 0, 0, 0);
-    if (vec < vecs && (int)blockIdx.x < a.sh.T) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(a.x + (int64_t)blockIdx.x * H + vec * 16);
-        nxt_lo = __ldg(src);
-        nxt_hi = __ldg(src + 1);
-    }
     for (int tok = blockIdx.x; tok < a.sh.T; tok += gridDim.x) {
         if (threadIdx.x < K) {
             const int e = a.topk_idx[tok * K + threadIdx.x];
@@ -289,7 +297,12 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs &a)
     }
 }
 
-__global__ void __launch_bounds__(448) k_moe_dispatch(DispatchArgs a) { dispatch_body(a); }
+__global__ void __launch_bounds__(448) k_moe_dispatch(DispatchArgs a)
+{
+    uint4 lo, hi;
+    dispatch_preload(a, lo, hi);
+    dispatch_body(a, lo, hi);
+}
 
 // Waits until every rank raised flag row `which` (0 dispatch, 1 combine) to `epoch`.
 __global__ void k_moe_wait_all(Team t, MoeHeap hp, int which, uint32_t epoch, int *status)
@@ -476,6 +489,8 @@ __global__ void __launch_bounds__(448) k_moe_ll_dispatch(LLDispatchArgs a)
     const uint32_t me = team_rank(t);
     const int E = a.d.sh.E, n = a.d.sh.T * a.d.sh.K;
     __shared__ int cnt[1024];
+    uint4 pre_lo, pre_hi;
+    dispatch_preload(a.d, pre_lo, pre_hi);  // every CTA fetches its first row while CTA 0 works out the layout
     if (blockIdx.x == 0) {
         MF_PROF_START(PF_LAYOUT);
         for (int e = threadIdx.x; e < E; e += blockDim.x) cnt[e] = 0;
@@ -496,7 +511,7 @@ __global__ void __launch_bounds__(448) k_moe_ll_dispatch(LLDispatchArgs a)
     grid.sync();  // every CTA has read the call counter before this point
     if (blockIdx.x == 0 && threadIdx.x == 0) *a.epoch_dev = a.d.epoch;
     MF_PROF_START(PF_DISPATCH);
-    dispatch_body(a.d);
+    dispatch_body(a.d, pre_lo, pre_hi);
     MF_PROF_STOP(PF_DISPATCH);
     if (blockIdx.x == 0) MF_PROF_START(PF_WAIT_PEERS);
     if (blockIdx.x == 0 && threadIdx.x < t.world) {
