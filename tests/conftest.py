@@ -9,7 +9,6 @@ ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-os.environ.setdefault("MF_STORE_HEARTBEAT_MS", "100")  # fast failure detection in tests
 
 
 def pytest_configure(config):
