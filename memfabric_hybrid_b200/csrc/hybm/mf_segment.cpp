@@ -507,8 +507,13 @@ public:
 
 protected:
     uint64_t Granule() const override { return std::max<uint64_t>(opt_.dev->Caps().granularity, kHbmGranule); }
+    // The driver honours a fixed-address request reliably only for large ranges (observed on B200, driver 580:
+    // below 512 MiB the hint is ignored once another allocator of the process has initialised), so the
+    // reservation, not the slot, is rounded up to a whole GiB; address space inside a window is plentiful.
+    static uint64_t ReserveBytes(uint64_t size) { return AlignUp(size, 1ULL << 30); }
     int ReserveRange(uint64_t hint, uint64_t size) override
     {
+        size = ReserveBytes(size);
         uint64_t va = 0;
         int rc = opt_.dev->Reserve(hint, size, &va);
         if (rc != OK || va != hint) {
@@ -518,7 +523,7 @@ protected:
         }
         return OK;
     }
-    int ReleaseRange(uint64_t base, uint64_t size) override { return opt_.dev->ReleaseVa(base, size); }
+    int ReleaseRange(uint64_t base, uint64_t size) override { return opt_.dev->ReleaseVa(base, ReserveBytes(size)); }
     int MapLocal(MemSlice &s, std::string &source, uint64_t &token) override
     {
         PhysHandle h = 0;
