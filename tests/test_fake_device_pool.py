@@ -71,6 +71,7 @@ def _rank(rank, world, url, sync):
         assert h.copy_data(src.ctypes.data, pdev, 4096, bm.BmCopyType.H2G, 0) != 0
         mf.get_and_clear_last_err_msg()
         assert h.leave() == 0
+    sync.wait(60)  # whichever process hosts the config store must not tear it down while the other still leaves
     h.destroy()
     bm.uninitialize(0)
     mf.uninitialize()

@@ -75,6 +75,7 @@ def _two_ranks(rank, world, url, sync):
     st = h.copy_stats()
     sync.wait(120)
     assert h.leave() == 0
+    sync.wait(120)  # rank 0 hosts the config store: no teardown while the peer is still leaving
     h.destroy()
     bm.uninitialize(0)
     mf.uninitialize()
