@@ -136,6 +136,10 @@ class BigMemory:
 
     # -- data
     def copy_data(self, src_ptr: int, dst_ptr: int, size: int, type: BmCopyType, flags: int = 0, stream: int = 0) -> int:
+        """One copy. Without ``FLAG_USE_EXTERNAL_STREAM`` it runs on the pool's own non-blocking stream, which is
+        not ordered with PyTorch's streams: a tensor that a PyTorch kernel is still filling (``torch.zeros``,
+        ``randn``, the output of a layer) must be complete first (synchronise its stream), or pass that stream
+        with the flag so that the copy is enqueued behind the producer."""
         p = N.CopyParamsC(src_ptr, dst_ptr, size, stream or None)
         return N.lib().smem_bm_copy(self._h, C.byref(p), int(type), flags)
 

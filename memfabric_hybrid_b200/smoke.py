@@ -33,6 +33,7 @@ def run() -> None:
     dev = h.peer_rank_ptr(0, bm.BmMemType.DEVICE)
     hst = h.peer_rank_ptr(0, bm.BmMemType.HOST)
     x = torch.randn(4 * MiB // 2, dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()  # the pool copies on its own stream: x must be complete first
     n, seg = 32, 128 * 1024
     srcs = [x.data_ptr() + i * seg for i in range(n)]
     dsts = [dev + (n - 1 - i) * seg for i in range(n)]  # scattered: reversed order

@@ -40,6 +40,9 @@ def _two_ranks(rank, world, url, sync):
     x = torch.randint(0, 255, (64 * MiB,), dtype=torch.uint8, device="cuda", generator=g)
     pdev = h.peer_rank_ptr(peer, bm.BmMemType.DEVICE)
     mdev = h.peer_rank_ptr(rank, bm.BmMemType.DEVICE)
+    # The pool's internal stream is not ordered with PyTorch's: tensors that a PyTorch kernel fills must be
+    # complete before a copy that runs there reads or overwrites them.
+    torch.cuda.synchronize()
     # D2RD: odd sizes and offsets on purpose (head/tail paths), plus big aligned segments
     segs = [(0, 1 * MiB), (1 * MiB + 3, 4097), (2 * MiB + 16, 16 * 1024), (3 * MiB, 8 * MiB), (12 * MiB + 1, 777), (16 * MiB, 32 * MiB)]
     srcs = [x.data_ptr() + o for o, _ in segs]
@@ -51,12 +54,13 @@ def _two_ranks(rank, world, url, sync):
     gp = torch.Generator("cuda").manual_seed(100 + peer)
     want = torch.randint(0, 255, (64 * MiB,), dtype=torch.uint8, device="cuda", generator=gp)
     got = torch.zeros(64 * MiB, dtype=torch.uint8, device="cuda")
+    pulled = torch.zeros(8 * MiB, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
     assert h.copy_data_batch([mdev + o for o, _ in segs], [got.data_ptr() + o for o, _ in segs], sizes, len(segs),
                              bm.BmCopyType.G2L, 0) == 0, mf.get_last_err_msg()
     for o, s in segs:
         assert torch.equal(got[o:o + s], want[o:o + s]), f"segment at {o} (+{s}) differs"
     # RD2D pull from the peer's slice (it holds OUR data) and a D2H leg into the pooled DRAM, then GH2H
-    pulled = torch.zeros(8 * MiB, dtype=torch.uint8, device="cuda")
     assert h.copy_data(pdev + 3 * MiB, pulled.data_ptr(), 8 * MiB, bm.BmCopyType.G2L, 0) == 0, mf.get_last_err_msg()
     assert torch.equal(pulled, x[3 * MiB:11 * MiB])
     mhost = h.peer_rank_ptr(rank, bm.BmMemType.HOST)
