@@ -2,6 +2,7 @@
 
     libmf_smem.so   host core (g++): util, RPC, config store, group engine, hybm, smem/zbal C APIs
     libmf_cuda.so   device backend and every sm_100a kernel (nvcc, static cudart)
+    _zbal_c10d.so   the torch.distributed backend "zbal" as a c10d::Backend (g++ against libtorch, links libmf_smem)
 
 Objects are cached under ``build/`` keyed by a hash of the source, its local includes and the
 flags, so a rebuild only recompiles what changed.  ``python -m memfabric_hybrid_b200._build``
@@ -101,9 +102,43 @@ def build_cuda(jobs: int | None = None) -> Path | None:
     return out
 
 
+def build_c10d() -> Path | None:
+    """The c10d extension module. Needs PyTorch's headers and a CUDA include tree; returns None without them."""
+    try:
+        import torch
+        from torch.utils import cpp_extension as ce
+    except Exception:
+        return None
+    cuda_inc = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
+    if not (cuda_inc / "cuda_runtime_api.h").exists():
+        return None
+    import sysconfig
+    tdir = Path(torch.__file__).resolve().parent
+    srcs = sorted((CSRC / "c10d").glob("*.cpp"))
+    incs = [str(tdir / "include"), str(tdir / "include" / "torch" / "csrc" / "api" / "include"), str(cuda_inc),
+            sysconfig.get_paths()["include"], str(CSRC / "include"), str(CSRC)]
+    abi = int(getattr(torch._C, "_GLIBCXX_USE_CXX11_ABI", True))
+    flags = ["-std=c++17", "-O2", "-fPIC", "-pthread", "-fvisibility=hidden", "-Wall", "-Wno-unused-parameter", "-Wno-interference-size",
+             f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-DTORCH_EXTENSION_NAME=_zbal_c10d", "-DTORCH_API_INCLUDE_EXTENSION_H",
+             "-DUSE_C10D", "-DUSE_CUDA", f"-DTORCH_VERSION_TAG={torch.__version__.replace('+', '_').replace('.', '_')}"] + \
+            [f"-I{i}" for i in incs]
+    objs = _build_objs(srcs, ["g++"], flags, "c10d", os.cpu_count() or 4)
+    LIB.mkdir(exist_ok=True)
+    build_host()
+    out = LIB / "_zbal_c10d.so"
+    tmp = out.with_suffix(".so.tmp")
+    tlib = tdir / "lib"
+    subprocess.run(["g++", "-shared", "-o", str(tmp)] + [str(o) for o in objs] +
+                   [f"-L{tlib}", "-ltorch_python", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",
+                    f"-L{LIB}", "-lmf_smem", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{tlib}", "-pthread"], check=True)
+    tmp.replace(out)
+    return out
+
+
 def build_all() -> None:
     build_host()
     build_cuda()
+    build_c10d()
 
 
 if __name__ == "__main__":
@@ -112,3 +147,5 @@ if __name__ == "__main__":
         print(build_host())
     if not args or "--cuda" in args:
         print(build_cuda())
+    if not args or "--c10d" in args:
+        print(build_c10d())

@@ -17,6 +17,10 @@ it first waits on an event recorded on the caller's stream, the operation is enq
 recorded into the returned Work; ``Work.wait()`` makes the CALLER's stream wait on that event, the host
 does not block. With ZBAL_OP_DEFAULT_STREAM=1 operations run on the caller's stream directly.
 
+Two implementations with the same behaviour: the native ``c10d::Backend`` (csrc/c10d/zbal_process_group.cpp, built as
+``lib/_zbal_c10d.so``; the default) and the ``ProcessGroup`` subclass below (``ZBAL_PG_IMPL=python``, or when the
+extension is not built). The native one builds its NCCL / gloo fallbacks through a factory given by ``_create_native``.
+
 Group naming: ``zbal_<first>:<last>:<stride>_group_<n>``; point-to-point communicators are 2-member
 groups named ``"<low>:<high>"`` created on first use, the lower world rank being member 0.
 """
@@ -36,9 +40,12 @@ from . import module as M
 _OPS = {ReduceOp.SUM: K.OP_SUM, ReduceOp.MAX: K.OP_MAX, ReduceOp.MIN: K.OP_MIN, ReduceOp.PRODUCT: K.OP_PROD}
 _group_counters: dict = {}
 _live = []
+_native_ext = None
 
 
 def _forget_all() -> None:
+    if _native_ext:
+        _native_ext.forget_all()
     for pg in list(_live):
         pg._comm = None
         pg._p2p.clear()
@@ -411,11 +418,56 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         return tuple(int(v) for v in st)
 
 
+def native_extension():
+    """The C++ ``c10d::Backend`` module (csrc/c10d/zbal_process_group.cpp), or None when it was not built."""
+    global _native_ext
+    if _native_ext is None:
+        import importlib.util
+        from .. import _native as N
+        path = N._LIB_DIR / "_zbal_c10d.so"
+        if not path.exists():
+            _native_ext = False
+        else:
+            K.lib()  # libmf_smem.so first, so that both sides share one copy of the library's state
+            spec = importlib.util.spec_from_file_location("_zbal_c10d", str(path))
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            _native_ext = mod
+    return _native_ext or None
+
+
+def implementation() -> str:
+    """"native" (C++ c10d::Backend, the default when built) or "python" (``ZBAL_PG_IMPL=python``, or no extension)."""
+    want = os.environ.get("ZBAL_PG_IMPL", "native").lower()
+    if want == "python":
+        return "python"
+    if native_extension() is None:
+        if want == "native" and "ZBAL_PG_IMPL" in os.environ:
+            raise RuntimeError("ZBAL_PG_IMPL=native but lib/_zbal_c10d.so is not built (python -m memfabric_hybrid_b200._build --c10d)")
+        return "python"
+    return "native"
+
+
+def _create_native(o):
+    ext = native_extension()
+    store, rank, size, timeout = o.store, o.group_rank, o.group_size, o.timeout
+    pg = ext.ProcessGroupZBAL(store, rank, size, [int(r) for r in (o.global_ranks_in_group or [])], timeout)
+
+    def fallback(cuda: bool):
+        if cuda:
+            return dist.ProcessGroupNCCL(dist.PrefixStore("zbal_nccl_fallback/", store), rank, size, dist.ProcessGroupNCCL.Options())
+        return dist.ProcessGroupGloo(dist.PrefixStore("zbal_gloo_fallback/", store), rank, size, timeout=timeout)
+    pg.set_fallback_factory(fallback)
+    return pg
+
+
 def _create(dist_backend_opts, pg_options):
+    if implementation() == "native":
+        return _create_native(dist_backend_opts)
     return ProcessGroupZBAL(dist_backend_opts.store, dist_backend_opts.group_rank, dist_backend_opts.group_size,
                             dist_backend_opts.global_ranks_in_group, dist_backend_opts.timeout)
 
 
 def register() -> None:
     if "ZBAL" not in getattr(dist.Backend, "_plugins", {}):
-        dist.Backend.register_backend("zbal", _create, extended_api=True, devices=["cuda"])
+        dist.Backend.register_backend("zbal", _create, extended_api=True, devices=["cuda", "cpu"])

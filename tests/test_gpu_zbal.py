@@ -19,17 +19,22 @@ def _draw(r, n, dtype=torch.float32):
     return torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(77 * r + 5)).to(dtype)
 
 
-def _pg_scenario(rank, world, port, sync):
+def _pg_scenario(rank, world, port, impl, sync):
     import torch
     import torch.distributed as dist
+    os.environ["ZBAL_PG_IMPL"] = impl
     import memfabric_hybrid_b200.zbal as zbal
     dev = rank % torch.cuda.device_count()
     torch.cuda.set_device(dev)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     assert zbal.zbal_init(world, dev, rank, 512 << 20, ip_port=f"127.0.0.1:{port}", start_config_server=True)
     dist.init_process_group("zbal", init_method=f"tcp://127.0.0.1:{port + 1}", rank=rank, world_size=world)
-    pg = dist.group.WORLD
-    assert isinstance(pg, zbal.ProcessGroupZBAL)
+    if impl == "native":   # a c10d::Backend from lib/_zbal_c10d.so under torch's own ProcessGroup
+        pg = dist.group.WORLD._get_backend(torch.device("cuda"))
+        assert type(pg).__module__ == "_zbal_c10d" and pg.comm_name() == "zbal_world"
+    else:
+        pg = dist.group.WORLD
+        assert isinstance(pg, zbal.ProcessGroupZBAL)
 
     # all_reduce: sum, avg, max, in place, several sizes (one-shot and two-shot), async handle
     for n in (1, 1000, 70_000, 2_000_000):
@@ -119,21 +124,24 @@ def _pg_scenario(rank, world, port, sync):
     del t
     torch.cuda.synchronize()
     status = pg.device_status()
+    del pg
     dist.destroy_process_group()
     zbal.zbal_uninit()
     return status[0]
 
 
-def test_process_group_single_gpu():
+@pytest.mark.parametrize("impl", ["native", "python"])
+def test_process_group_single_gpu(impl):
     port = free_port()
-    assert run_ranks(_pg_scenario, 1, (port,), timeout=300, with_barrier=True) == [0]
+    assert run_ranks(_pg_scenario, 1, (port, impl), timeout=300, with_barrier=True) == [0]
 
 
 @pytest.mark.multigpu
-def test_process_group_multi_gpu():
+@pytest.mark.parametrize("impl", ["native", "python"])
+def test_process_group_multi_gpu(impl):
     n = min(torch.cuda.device_count(), 4)
     port = free_port()
-    assert run_ranks(_pg_scenario, n, (port,), timeout=420, with_barrier=True) == [0] * n
+    assert run_ranks(_pg_scenario, n, (port, impl), timeout=420, with_barrier=True) == [0] * n
 
 
 def _buffer_scenario(rank, world, port, sync):

@@ -183,3 +183,44 @@ def test_balance_matrix_plan():
     assert covered[0][0] == 0 and covered[-1][1] == 4000 and all(covered[i][1] == covered[i + 1][0] for i in range(len(covered) - 1))
     load = [sum(int(big[h, o, 1] - big[h, o, 0]) for o in range(ranks) if big[h, o, 0] >= 0) for h in range(ranks)]
     assert load[0] == 1560 and max(load[1:]) <= 1300 and sum(load) == 5200
+
+
+def _native_pg(rank, world, port):
+    """The C++ c10d backend over the fake device backend: routing, naming and fall-backs, no GPU needed."""
+    os.environ.update(MF_DEVICE_BACKEND="fake", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    import torch
+    import torch.distributed as dist
+    import memfabric_hybrid_b200.zbal as z
+    from memfabric_hybrid_b200.zbal import process_group as P
+    assert P.implementation() == "native", "lib/_zbal_c10d.so is not built"
+    assert z.zbal_init(world, 0, rank, 256 << 20, ip_port=f"127.0.0.1:{port + 7}", start_config_server=True, comm_group_cap=8)
+    dist.init_process_group("zbal", rank=rank, world_size=world, init_method=f"tcp://127.0.0.1:{port}")
+    be = dist.group.WORLD._get_backend(torch.device("cpu"))
+    assert type(be).__name__ == "ProcessGroupZBAL" and type(be).__module__ == "_zbal_c10d"
+    assert be.strided and be.comm_name() == "zbal_world" and dist.get_backend() == "zbal"
+    t = torch.full((4,), rank + 1.0)
+    dist.all_reduce(t)                                   # host tensor: the gloo fall-back built through the factory
+    assert t.tolist() == [float(sum(range(1, world + 1)))] * 4
+    objs = [None] * world
+    dist.all_gather_object(objs, {"r": rank})
+    assert [o["r"] for o in objs] == list(range(world))
+    dist.barrier()
+    names = []
+    for ranks in ([0, 2], [1, 3], [0, 1, 3]):
+        g = dist.new_group(ranks)
+        if rank in ranks:
+            b = g._get_backend(torch.device("cpu"))
+            names.append(b.comm_name() if b.strided else "irregular")
+            x = torch.tensor([float(rank)])
+            dist.all_reduce(x, group=g)
+            assert x.item() == float(sum(ranks))
+    dist.barrier()
+    dist.destroy_process_group()
+    assert z.zbal_uninit()
+    return names
+
+
+def test_native_c10d_backend_routing_and_group_names():
+    res = run_ranks(_native_pg, 4, (free_port(),), timeout=180)
+    assert res[0] == ["zbal_0:2:2_group_0", "irregular"] and res[2] == ["zbal_0:2:2_group_0"]
+    assert res[1] == ["zbal_1:3:2_group_0", "irregular"] and res[3] == ["zbal_1:3:2_group_0", "irregular"]
