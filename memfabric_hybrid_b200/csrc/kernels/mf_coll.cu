@@ -550,6 +550,53 @@ template <typename T, typename TO, bool INT, int W> __global__ void __launch_bou
     lane_sync(t, me, 1, a.epoch, 0x183);
 }
 
+// reduce-scatter through the multicast alias: rank r pulls part r with ONE multimem.ld_reduce per 16 bytes (the
+// switch adds all ranks' values), so each GPU receives n/W bytes instead of (W-1) n/W. Needs the input at the
+// same slot offset on every rank and 16-byte aligned parts; otherwise, all together, the ranks fall back to
+// peer loads.
+template <typename T, typename TO, int W> __global__ void __launch_bounds__(512) k_reduce_scatter_mc(CollArgs a)
+{
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const uint32_t world = t.world;
+    __shared__ uint64_t p_in[kMaxRanks], p_unused[kMaxRanks];
+    const uint64_t slot = t.heap_base + (uint64_t)me * t.stride;
+    if (!lane_sync_xchg(t, me, 0, a.epoch, 0x18e, a.in - slot, 0, p_in, p_unused)) return;
+    TO *out = reinterpret_cast<TO *>(a.out);
+    const uint64_t m = a.n / world;
+    const uint64_t ps = a.part_stride ? a.part_stride : m;
+    constexpr int VN = Vec<T>::N;
+    bool same = t.mc_base != 0 && a.op == OP_SUM && (m % VN) == 0 && (ps % VN) == 0 && (p_in[0] & 15) == 0;
+    for (uint32_t r = 1; r < world; r++) same = same && p_in[r] == p_in[0];
+    const Range sub = cta_range<8>(m);
+    if (same) {
+        const uint64_t src = t.mc_base + p_in[0] + (uint64_t)me * ps * sizeof(T);
+        const uint64_t step = (uint64_t)blockDim.x * VN;
+        uint64_t i = sub.beg + (uint64_t)threadIdx.x * VN;
+        for (; i + 3 * step < sub.end; i += 4 * step) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = MultiMem<T>::ld_add(src + (i + u * step) * sizeof(T));
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                float f[VN];
+                Vec<T>::unpack(v[u], f);
+                emit<TO, false>(out, i + u * step, f, VN, a.scale);
+            }
+        }
+        for (; i < sub.end; i += step) {
+            uint4 v0 = MultiMem<T>::ld_add(src + i * sizeof(T));
+            float f[VN];
+            Vec<T>::unpack(v0, f);
+            emit<TO, false>(out, i, f, VN, a.scale);
+        }
+    } else {
+        reduce_direct<T, false, W>(t, me, p_in, (uint64_t)me * ps, sub.beg, sub.end, a.op,
+                                   [&](uint64_t i, float *acc, int cnt) { emit<TO, false>(out, i, acc, cnt, a.scale); });
+    }
+    lane_sync(t, me, 1, a.epoch, 0x18f);
+}
+
 // all-gather: every rank stores its shard straight into every rank's output.
 template <typename T, typename TO> __global__ void __launch_bounds__(512) k_allgather_zc(CollArgs a)
 {
@@ -875,6 +922,15 @@ template <typename T, typename TO, bool INT> int launch_rs_zc(const CollArgs &a,
         default: return launch(k_reduce_scatter_zc<T, TO, INT, 0>, a, ctas, threads, s, false);
     }
 }
+template <typename T, typename TO> int launch_rs_mc(const CollArgs &a, int ctas, int threads, cudaStream_t s)
+{
+    switch (a.team.world) {
+        case 2: return launch(k_reduce_scatter_mc<T, TO, 2>, a, ctas, threads, s, false);
+        case 4: return launch(k_reduce_scatter_mc<T, TO, 4>, a, ctas, threads, s, false);
+        case 8: return launch(k_reduce_scatter_mc<T, TO, 8>, a, ctas, threads, s, false);
+        default: return launch(k_reduce_scatter_mc<T, TO, 0>, a, ctas, threads, s, false);
+    }
+}
 template <typename T, typename TO, bool INT> int launch_rs(const CollArgs &a, int ctas, int threads, cudaStream_t s)
 {
     switch (a.team.world) {
@@ -900,13 +956,20 @@ int mf_coll_launch(int kind, int in_dtype, int out_dtype, const CollArgs *args, 
     const bool to_bf16 = out_dtype == DT_BF16;
     if (!same && !to_bf16) return -2;
     if (a.zero_copy == 3) {
-        // direct mode through the NVLink multicast alias: all-reduce (sum, same type in and out), all-gather, rooted copy
+        // direct mode through the NVLink multicast alias: all-reduce (sum, same type in and out), reduce-scatter (sum), all-gather, rooted copy
         if (a.team.emu || a.team.mc_base == 0) return -4;
         if (kind == 0) {
             if (!same) return -4;
             if (in_dtype == DT_BF16) return launch_allreduce_mc<__nv_bfloat16>(a, ctas, threads, s);
             if (in_dtype == DT_F16) return launch_allreduce_mc<__half>(a, ctas, threads, s);
             if (in_dtype == DT_F32) return launch_allreduce_mc<float>(a, ctas, threads, s);
+            return -2;
+        }
+        if (kind == 1) {
+            if (in_dtype == DT_BF16) return launch_rs_mc<__nv_bfloat16, __nv_bfloat16>(a, ctas, threads, s);
+            if (in_dtype == DT_F16) return same ? launch_rs_mc<__half, __half>(a, ctas, threads, s) : -2;
+            if (in_dtype == DT_F32)
+                return same ? launch_rs_mc<float, float>(a, ctas, threads, s) : launch_rs_mc<float, __nv_bfloat16>(a, ctas, threads, s);
             return -2;
         }
         if (kind == 2) {

@@ -467,7 +467,7 @@ int32_t zbal_reduce_scatter(const void *send, void *recv, size_t recv_count, zba
     const uint64_t m = recv_count;
     if (m * c->size * ti.size > DirectMin() && InSlice(send, m * c->size * ti.size)) {
         MfCollArgs a = BaseArgs(*c, send, recv, m * c->size, 1.f, kop, 0, 0);
-        a.zero_copy = 2;
+        a.zero_copy = (c->team.mc_base != 0 && kop == 0 && ti.kdt != 3) ? 3 : 2;  // the switch adds when it can
         return Launched(L->coll(1, ti.kdt, ti.kdt, &a, c->Ctas(m * c->size * ti.size), 512, stream), "reduce_scatter (direct)");
     }
     uint64_t piece = c->stageBytes / ti.size / c->size;

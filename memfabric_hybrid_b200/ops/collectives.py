@@ -193,7 +193,9 @@ class Communicator:
         if n * es > DIRECT_MIN and self._in_heap(x):
             epoch, stage = self._next()
             args = self._args(x, out, n, epoch, stage, scale, op)
-            args.zero_copy = 2
+            mc = self.heap.mc_base != 0 and op == "sum" and x.dtype != torch.int32 and not self.no_multicast and \
+                (od == x.dtype or (x.dtype == torch.float32 and od == torch.bfloat16))
+            args.zero_copy = 3 if mc else 2
             _check(_cu().mf_coll_launch(1, DT[x.dtype], DT[od], C.byref(args), self._ctas(n * es), 512, _stream()), "reduce_scatter (direct)")
             return out
         # a piece is a column block [c0, c1) of the [world, m] view: staged as world rows of (c1 - c0)

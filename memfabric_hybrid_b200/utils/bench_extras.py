@@ -70,6 +70,11 @@ def collectives(comm, world, flush):
     hx.copy_(torch.randn(n, device="cuda"))
     ms = _timed(lambda: comm.reduce_scatter(hx, scale=1.0 / world, out_dtype=torch.bfloat16), 6, 2, flush)
     row = {"op": "reduce_scatter_f32_to_bf16", "bytes": 64 << 20, "us": round(ms * 1e3, 1)}
+    if heap.mc_base:
+        comm.no_multicast = True
+        row["peer_ld_us"] = round(_timed(lambda: comm.reduce_scatter(hx, scale=1.0 / world, out_dtype=torch.bfloat16), 6, 2, flush) * 1e3, 1)
+        comm.no_multicast = False
+        row["multicast"] = True
     if world > 1:
         y = torch.randn(n, device="cuda")
         o = torch.empty(n // world, device="cuda")

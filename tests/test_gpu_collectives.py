@@ -190,6 +190,8 @@ def _real_ranks(rank, world, url, sync):
     rs = c.reduce_scatter(fx)
     exp = (torch.arange(rank * m, (rank + 1) * m, device="cuda", dtype=torch.float32) % 1000) * world + sum(range(world))
     torch.testing.assert_close(rs, exp, rtol=1e-6, atol=1e-3)
+    rs16 = c.reduce_scatter(fx, scale=0.5, out_dtype=torch.bfloat16)   # fused scale and cast in the epilogue
+    torch.testing.assert_close(rs16.float(), exp * 0.5, rtol=1e-2, atol=1e-2)
     go = heap.view(heap.alloc(world * m * 4), (world * m,), torch.float32)
     c.all_gather(torch.full((m,), float(rank), device="cuda"), out=go)
     assert torch.equal(go.view(world, m)[:, m - 1].cpu(), torch.arange(world, dtype=torch.float32))
