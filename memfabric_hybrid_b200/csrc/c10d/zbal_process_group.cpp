@@ -522,7 +522,7 @@ private:
         o.deviceId = CudaReady() ? (int32_t)c10::cuda::current_device() : 0;
         o.startConfigServer = true;
         o.deviceMemorySize = std::stoull(EnvOr("ZBAL_DEVICE_MEM_SIZE", "4294967296"));
-        if (CudaReady()) at::zeros({1}, at::TensorOptions().device(at::kCUDA));  // a context must exist before the VMM calls
+        if (CudaReady()) c10::cuda::device_synchronize();  // a context must exist before the VMM calls
         zbal_bootstrap_output_t out;
         Check(zbal_bootstrap(&o, &out), "zbal_bootstrap");
     }
@@ -623,6 +623,8 @@ private:
     uint64_t seq_ = 0;
 };
 
+void BindAllocator(py::module_ &m);  // zbal_torch_allocator.cpp
+
 }  // namespace zbal_c10d
 
 PYBIND11_MODULE(_zbal_c10d, m)
@@ -642,4 +644,5 @@ PYBIND11_MODULE(_zbal_c10d, m)
         .def("comm_handle", &ProcessGroupZBAL::CommHandle, py::call_guard<py::gil_scoped_release>())
         .def_property_readonly("strided", &ProcessGroupZBAL::Strided);
     m.def("forget_all", &ProcessGroupZBAL::ForgetAll);
+    zbal_c10d::BindAllocator(m);
 }

@@ -36,7 +36,23 @@ typedef struct {
     uint64_t cacheHits;
     uint64_t heapCarves;       /* mallocs that had to go to the heap */
     uint64_t failedMallocs;
+    uint64_t poolCount;        /* private pools that exist (capturing or kept alive by a CUDA graph) */
+    uint64_t poolCachedBytes;  /* free blocks parked in private pools (not counted in cachedBytes) */
 } zbal_sma_stats_t;
+
+/* Private pools for CUDA-graph capture. A graph replays with the addresses it saw while it was captured, so
+ * what it allocated must never be handed to anyone else while the graph exists:
+ *   begin   allocations on streams the filter accepts (NULL: every stream) are served from the pool's own blocks,
+ *           else carved from the heap and tagged with the pool;
+ *   end     stops routing (capture finished); the pool and its blocks stay;
+ *   release the graphs that used the pool are gone: parked blocks return to the heap, blocks still in use
+ *           become ordinary blocks.
+ * A tagged block that is freed is parked in its pool (reused only by the same pool); zbal_pluggable_empty_cache
+ * leaves pools alone. The pool id is PyTorch's MempoolId_t pair. */
+typedef bool (*zbal_pool_filter_t)(void *ctx, zbal_stream_t stream);
+int32_t zbal_sma_begin_pool(uint64_t pool_hi, uint64_t pool_lo, zbal_pool_filter_t filter, void *ctx);
+int32_t zbal_sma_end_pool(uint64_t pool_hi, uint64_t pool_lo);
+int32_t zbal_sma_release_pool(uint64_t pool_hi, uint64_t pool_lo);
 
 int32_t zbal_sma_get_stats(zbal_sma_stats_t *stats);
 void zbal_sma_reset_peak(void);

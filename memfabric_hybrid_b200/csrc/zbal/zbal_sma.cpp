@@ -19,8 +19,10 @@
 //   garbage_collection_threshold   fraction of the heap in use+cached above which free() of a large block
 //                          returns it to the heap at once instead of caching it (default 0 = off)
 //
-// Not provided: private pools for CUDA-graph capture (a capture that allocates must use PyTorch's native
-// allocator with a MemPool over zbal_pluggable_malloc, which keeps the pool's blocks alive itself).
+// Private pools (CUDA-graph capture): between begin_pool and end_pool, allocations of the capturing stream are
+// tagged with the pool; a tagged block that is freed is parked in the pool and only that pool may reuse it,
+// until release_pool returns the parked blocks to the heap. Neither empty_cache nor heap exhaustion touches a
+// pool, because a graph replays with the addresses it captured.
 //
 // Parity of role: app/zbal/src/csrc/sma/zbal_sma_device.cpp, zbal_sma_config.h:20-102,
 // app/zbal/src/include/zbal_mem_allocator.h of the reference.
@@ -72,6 +74,22 @@ struct HistoryEntry {
     uint64_t addr, size, requested, stream;
 };
 
+using PoolId = std::pair<uint64_t, uint64_t>;
+const PoolId kNoPool{0, 0};
+
+struct Pool {
+    std::multimap<uint64_t, uint64_t> parked;  // size -> addr
+    uint64_t parkedBytes = 0;
+    bool routing = false;
+    zbal_pool_filter_t filter = nullptr;
+    void *ctx = nullptr;
+};
+
+struct LiveBlock {
+    uint64_t size, stream;
+    PoolId pool;
+};
+
 class Sma {
 public:
     Sma(uint64_t base, uint64_t size, const Config &cfg, int device, bool simulated)
@@ -91,6 +109,8 @@ public:
         const uint64_t size = Round(requested);
         std::lock_guard<std::mutex> g(mu_);
         st_.mallocCalls++;
+        const PoolId pool = RoutedPool(stream);
+        if (pool != kNoPool) return PoolMalloc(pool, size, requested, stream);
         auto &cache = cache_[stream];
         auto it = cache.lower_bound(size);
         if (it != cache.end()) {
@@ -102,7 +122,7 @@ public:
                 const uint64_t addr = it->second, bsz = it->first;
                 cache.erase(it);
                 cached_ -= bsz;
-                Hand(addr, bsz, stream);
+                Hand(addr, bsz, stream, kNoPool);
                 st_.cacheHits++;
                 Note(1, addr, bsz, requested, stream);
                 return reinterpret_cast<void *>(addr);
@@ -123,9 +143,45 @@ public:
             return nullptr;
         }
         st_.heapCarves++;
-        Hand(addr, size, stream);
+        Hand(addr, size, stream, kNoPool);
         Note(0, addr, size, requested, stream);
         return reinterpret_cast<void *>(addr);
+    }
+
+    int BeginPool(PoolId id, zbal_pool_filter_t filter, void *ctx)
+    {
+        if (id == kNoPool) return Z_INVALID_PARAM;
+        std::lock_guard<std::mutex> g(mu_);
+        Pool &p = pools_[id];
+        p.routing = true;
+        p.filter = filter;
+        p.ctx = ctx;
+        return Z_OK;
+    }
+    int EndPool(PoolId id)
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = pools_.find(id);
+        if (it == pools_.end()) return Z_INVALID_PARAM;
+        it->second.routing = false;
+        it->second.filter = nullptr;
+        it->second.ctx = nullptr;
+        return Z_OK;
+    }
+    int ReleasePool(PoolId id)
+    {
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = pools_.find(id);
+        if (it == pools_.end()) return Z_INVALID_PARAM;
+        if (!it->second.parked.empty()) DeviceWait();  // a replay in flight may still touch the parked blocks
+        for (auto &kv : it->second.parked) {
+            heap_.Release(kv.second);
+            Note(3, kv.second, kv.first, 0, 0);
+        }
+        pools_.erase(it);
+        for (auto &kv : live_)
+            if (kv.second.pool == id) kv.second.pool = kNoPool;
+        return Z_OK;
     }
 
     bool Free(void *ptr)
@@ -134,10 +190,20 @@ public:
         std::lock_guard<std::mutex> g(mu_);
         auto it = live_.find(addr);
         if (it == live_.end()) return false;
-        const uint64_t size = it->second.first, stream = it->second.second;
+        const uint64_t size = it->second.size, stream = it->second.stream;
+        const PoolId pool = it->second.pool;
         live_.erase(it);
         inUse_ -= size;
         st_.freeCalls++;
+        if (pool != kNoPool) {
+            auto pit = pools_.find(pool);
+            if (pit != pools_.end()) {
+                pit->second.parked.emplace(size, addr);
+                pit->second.parkedBytes += size;
+                Note(2, addr, size, 0, stream);
+                return true;
+            }
+        }
         const bool gc = cfg_.gcThreshold > 0.0 && size >= cfg_.smallThreshold &&
                         (double)(inUse_ + cached_ + size) > cfg_.gcThreshold * (double)heap_.TotalSize();
         if (gc) {
@@ -172,6 +238,9 @@ public:
         o.cachedBytes = cached_;
         o.peakInUseBytes = peak_;
         o.largestFreeBlock = heap_.LargestFree();
+        o.poolCount = pools_.size();
+        o.poolCachedBytes = 0;
+        for (const auto &kv : pools_) o.poolCachedBytes += kv.second.parkedBytes;
     }
     void ResetPeak()
     {
@@ -201,7 +270,7 @@ public:
             if (b.used) {
                 auto it = live_.find(b.addr);
                 state = it != live_.end() ? "active" : "cached";
-                if (it != live_.end()) stream = it->second.second;
+                if (it != live_.end()) stream = it->second.stream;
             }
             o << (first ? "" : ",") << "{\"addr\":" << b.addr << ",\"size\":" << b.size << ",\"state\":\"" << state << "\",\"stream\":" << stream
               << "}";
@@ -222,9 +291,53 @@ public:
     bool Owns(uint64_t addr) const { return addr >= heap_.Base() && addr < heap_.Base() + heap_.TotalSize(); }
 
 private:
-    void Hand(uint64_t addr, uint64_t size, uint64_t stream)
+    PoolId RoutedPool(uint64_t stream) const
     {
-        live_[addr] = {size, stream};
+        for (const auto &kv : pools_)
+            if (kv.second.routing && (kv.second.filter == nullptr || kv.second.filter(kv.second.ctx, reinterpret_cast<zbal_stream_t>(stream))))
+                return kv.first;
+        return kNoPool;
+    }
+    // Exact size classes inside a pool: a capture repeats the same shapes, and a replay must never see a block split.
+    void *PoolMalloc(const PoolId &id, uint64_t size, uint64_t requested, uint64_t stream)
+    {
+        Pool &p = pools_[id];
+        auto it = p.parked.find(size);
+        uint64_t addr = 0;
+        if (it != p.parked.end()) {
+            addr = it->second;
+            p.parked.erase(it);
+            p.parkedBytes -= size;
+            st_.cacheHits++;
+            Note(1, addr, size, requested, stream);
+        } else {
+            addr = heap_.AlignedAllocate(size, size < cfg_.smallThreshold ? 512 : 4096);
+            if (addr == 0 && cached_ > 0) {
+                // no device-wide wait here: it is illegal while a stream is capturing. The stream caches are
+                // flushed only if nothing is capturing work that could still touch them, which the caller
+                // guarantees by emptying the cache before the capture (torch.cuda.graph does).
+                st_.failedMallocs++;
+                Note(5, 0, size, requested, stream);
+                mf::LastError::Set(Z_NO_MEMORY, "symmetric heap exhausted inside a private pool: %lu bytes requested, %lu cached outside "
+                                   "the pool (empty the cache before capturing)", (unsigned long)size, (unsigned long)cached_);
+                return nullptr;
+            }
+            if (addr == 0) {
+                st_.failedMallocs++;
+                Note(5, 0, size, requested, stream);
+                mf::LastError::Set(Z_NO_MEMORY, "symmetric heap exhausted: %lu bytes requested, %lu in use of %lu", (unsigned long)size,
+                                   (unsigned long)inUse_, (unsigned long)heap_.TotalSize());
+                return nullptr;
+            }
+            st_.heapCarves++;
+            Note(0, addr, size, requested, stream);
+        }
+        Hand(addr, size, stream, id);
+        return reinterpret_cast<void *>(addr);
+    }
+    void Hand(uint64_t addr, uint64_t size, uint64_t stream, const PoolId &pool)
+    {
+        live_[addr] = {size, stream, pool};
         inUse_ += size;
         if (inUse_ > peak_) peak_ = inUse_;
     }
@@ -256,7 +369,8 @@ private:
     const bool simulated_;
     std::mutex mu_;
     std::unordered_map<uint64_t, std::multimap<uint64_t, uint64_t>> cache_;  // stream -> size -> addr
-    std::unordered_map<uint64_t, std::pair<uint64_t, uint64_t>> live_;      // addr -> (size, stream)
+    std::unordered_map<uint64_t, LiveBlock> live_;                           // addr -> (size, stream, pool)
+    std::map<PoolId, Pool> pools_;
     uint64_t inUse_ = 0, cached_ = 0, peak_ = 0;
     zbal_sma_stats_t st_{};
     bool record_ = false;
@@ -334,6 +448,24 @@ void zbal_pluggable_empty_cache(bool check_error)
 {
     auto s = Get();
     if (s) s->EmptyCache(check_error);
+}
+
+int32_t zbal_sma_begin_pool(uint64_t pool_hi, uint64_t pool_lo, zbal_pool_filter_t filter, void *ctx)
+{
+    auto s = Get();
+    return s ? s->BeginPool({pool_hi, pool_lo}, filter, ctx) : (int32_t)Z_NOT_INITIALIZED;
+}
+
+int32_t zbal_sma_end_pool(uint64_t pool_hi, uint64_t pool_lo)
+{
+    auto s = Get();
+    return s ? s->EndPool({pool_hi, pool_lo}) : (int32_t)Z_NOT_INITIALIZED;
+}
+
+int32_t zbal_sma_release_pool(uint64_t pool_hi, uint64_t pool_lo)
+{
+    auto s = Get();
+    return s ? s->ReleasePool({pool_hi, pool_lo}) : (int32_t)Z_NOT_INITIALIZED;
 }
 
 int32_t zbal_sma_get_stats(zbal_sma_stats_t *stats)

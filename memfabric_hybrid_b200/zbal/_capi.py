@@ -54,7 +54,7 @@ class MoeBuffersC(C.Structure):
 
 class SmaStatsC(C.Structure):
     _fields_ = [(n, u64) for n in ("heapSize", "inUseBytes", "cachedBytes", "peakInUseBytes", "largestFreeBlock", "mallocCalls",
-                                   "freeCalls", "cacheHits", "heapCarves", "failedMallocs")]
+                                   "freeCalls", "cacheHits", "heapCarves", "failedMallocs", "poolCount", "poolCachedBytes")]
 
 
 _declared = False
@@ -79,6 +79,9 @@ def _declare(l):
     s(l, "zbal_pluggable_free", None, vp, C.c_size_t, i32, vp)
     s(l, "zbal_pluggable_empty_cache", None, C.c_bool)
     s(l, "zbal_simulate_init", None, i64, i64)
+    s(l, "zbal_sma_begin_pool", i32, u64, u64, vp, vp)
+    s(l, "zbal_sma_end_pool", i32, u64, u64)
+    s(l, "zbal_sma_release_pool", i32, u64, u64)
     s(l, "zbal_sma_get_stats", i32, P(SmaStatsC))
     s(l, "zbal_sma_reset_peak", None)
     s(l, "zbal_sma_record_history", None, C.c_bool, u32)

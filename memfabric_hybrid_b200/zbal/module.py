@@ -8,7 +8,9 @@
 Parity: app/zbal/src/python/zbal/zbal_module.py:19-161 of the reference. Differences: the allocator switch
 is a scoped ``torch.cuda.MemPool`` by default (PyTorch's native caching allocator asks zbal for its
 segments), because a CUDA process can swap its global allocator only before the first allocation;
-``switch_to_allocator(globally=True)`` does that swap and must be called first thing.
+``switch_to_allocator(globally=True)`` does that swap and must be called first thing: before PyTorch initialises
+CUDA (``torch.cuda.set_device`` already does) and before ``zbal_init``; allocations made before the heap exists fail. Under the
+global allocator a ``torch.cuda.graph`` capture allocates from a private pool of the symmetric heap.
 """
 from __future__ import annotations
 
@@ -30,7 +32,7 @@ class ZBALBootstrapType(enum.IntEnum):
     BOOT_BY_MEMFABRIC = 0
 
 
-_state = {"output": None, "allocator": None, "pool": None}
+_state = {"output": None, "allocator": None, "py_allocator": None, "pool": None, "global": False}
 
 
 def zbal_set_logger_level(level: int) -> int:
@@ -51,7 +53,7 @@ def zbal_init(world_size: int, device_id: int, rank_id: int, device_mem_size: in
     if torch.cuda.is_available():
         N.cuda()  # kernels and the CUDA device backend
         torch.cuda.set_device(device_id)
-        torch.zeros(1, device="cuda")  # a context must exist before the VMM calls
+        torch.cuda.synchronize()  # a context must exist before the VMM calls (no allocation: the heap may be the allocator)
     auto = False
     if not ip_port:
         ip_port = os.environ.get("ZBAL_IP_PORT", "")
@@ -108,11 +110,23 @@ def zbal_get_symm_base_addr() -> int:
     return int(bootstrap_output().heapGva)
 
 
+def _native():
+    from . import process_group
+    return process_group.native_extension()
+
+
 def _pluggable():
+    """The torch._C allocator object over zbal_pluggable_malloc / free. With the native extension it also carries the
+    CUDA-graph hooks (private pools: csrc/c10d/zbal_torch_allocator.cpp); the Python-only fallback has malloc / free."""
     if _state["allocator"] is None:
-        path = str(N._LIB_DIR / "libmf_smem.so")
         K.lib()
-        _state["allocator"] = torch.cuda.memory.CUDAPluggableAllocator(path, "zbal_pluggable_malloc", "zbal_pluggable_free")
+        ext = _native()
+        if ext is not None:
+            _state["allocator"] = ext.allocator()
+        else:
+            path = str(N._LIB_DIR / "libmf_smem.so")
+            _state["py_allocator"] = torch.cuda.memory.CUDAPluggableAllocator(path, "zbal_pluggable_malloc", "zbal_pluggable_free")
+            _state["allocator"] = _state["py_allocator"].allocator()
     return _state["allocator"]
 
 
@@ -124,10 +138,15 @@ def switch_to_allocator(globally: bool = False):
     before the first CUDA allocation of the process) and returns None."""
     alloc = _pluggable()
     if globally:
-        torch.cuda.memory.change_current_allocator(alloc)
+        ext = _native()
+        if ext is not None:
+            ext.install_global_allocator()   # CUDA graphs captured from here on get private pools of the symmetric heap
+        else:
+            torch.cuda.memory.change_current_allocator(_state["py_allocator"])
+        _state["global"] = True
         return None
     if _state["pool"] is None:
-        _state["pool"] = torch.cuda.MemPool(alloc.allocator())
+        _state["pool"] = torch.cuda.MemPool(alloc)
     return torch.cuda.use_mem_pool(_state["pool"])
 
 

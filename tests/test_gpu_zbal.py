@@ -144,6 +144,56 @@ def test_process_group_multi_gpu(impl):
     assert run_ranks(_pg_scenario, n, (port, impl), timeout=420, with_barrier=True) == [0] * n
 
 
+def _graph_pool_scenario(rank, world, port, sync):
+    """The symmetric heap as the process-wide allocator: a CUDA graph captured under it allocates from a private
+    pool, replays with the captured addresses, and nobody else is handed the graph's blocks."""
+    import gc
+    import torch
+    import memfabric_hybrid_b200.zbal as zbal
+    zbal.switch_to_allocator(globally=True)          # first thing: before PyTorch initialises CUDA in this process
+    torch.cuda.set_device(0)
+    assert zbal.zbal_init(world, 0, rank, 1 << 30, ip_port=f"127.0.0.1:{port}", start_config_server=True)
+    x = torch.ones(1 << 20, device="cuda")
+    assert zbal.in_symmetric_heap(x)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        y = x * 2 + 1                                # temporaries and outputs of the capture: the private pool
+        z = y.sum()
+    st = zbal.heap_stats()
+    assert st["poolCount"] == 1 and zbal.in_symmetric_heap(y)
+    others = [torch.empty(1 << 20, device="cuda") for _ in range(16)]
+    mine = {y.data_ptr(), z.data_ptr()}
+    assert not any(o.data_ptr() in mine for o in others)
+    x.fill_(3.0)
+    g.replay()
+    torch.cuda.synchronize()
+    assert z.item() == 7.0 * (1 << 20)
+    for o in others:
+        o.fill_(-1.0)                                # must not disturb what the graph owns
+    x.fill_(4.0)
+    g.replay()
+    torch.cuda.synchronize()
+    assert z.item() == 9.0 * (1 << 20) and float(y[12345]) == 9.0
+    parked = zbal.heap_stats()["poolCachedBytes"]    # the temporary of x * 2 was freed inside the capture
+    torch.cuda.empty_cache()
+    assert zbal.heap_stats()["poolCachedBytes"] == parked and zbal.heap_stats()["poolCount"] == 1
+    del g, y, z
+    gc.collect()
+    torch.cuda.synchronize()
+    assert zbal.heap_stats()["poolCount"] == 0
+    del x, others, o
+    torch.cuda.empty_cache()
+    used, _ = zbal.get_heap_stats()
+    zbal.zbal_uninit()
+    return int(used > (1 << 20))   # nothing of the scenario is still held (library workspaces aside)
+
+
+def test_cuda_graph_private_pool_under_global_allocator():
+    port = free_port()
+    assert run_ranks(_graph_pool_scenario, 1, (port,), timeout=300, with_barrier=True) == [0]
+
+
 def _buffer_scenario(rank, world, port, sync):
     import torch
     import memfabric_hybrid_b200.zbal as zbal

@@ -63,6 +63,40 @@ def test_cache_is_per_stream_and_flush_on_exhaustion(sma):
     assert _stats(sma).largestFreeBlock == 256 * MiB   # everything coalesced back into one block
 
 
+def test_private_pool_keeps_graph_blocks_apart(sma):
+    """Capture-style pools: tagged blocks are parked in their pool when freed, survive empty_cache, are reused only
+    by the same pool, and return to the heap when the pool is released."""
+    cap, other = C.c_void_p(0x10), C.c_void_p(0x20)
+    FILTER = C.CFUNCTYPE(C.c_bool, C.c_void_p, C.c_void_p)
+    only_cap = FILTER(lambda ctx, stream: stream == cap.value)
+    pool = (0, 7)
+    assert sma.zbal_sma_begin_pool(*pool, C.cast(only_cap, C.c_void_p), None) == 0
+    a = sma.zbal_pluggable_malloc(4 * MiB, 0, cap)       # tagged
+    b = sma.zbal_pluggable_malloc(4 * MiB, 0, other)     # the filter rejects this stream: ordinary block
+    sma.zbal_pluggable_free(a, 0, 0, cap)
+    s = _stats(sma)
+    assert s.poolCount == 1 and s.poolCachedBytes == 4 * MiB and s.cachedBytes == 0
+    a2 = sma.zbal_pluggable_malloc(4 * MiB, 0, cap)      # the same pool reuses its parked block
+    assert a2 == a
+    assert sma.zbal_sma_end_pool(*pool) == 0             # capture over: the graph now owns a2's address
+    sma.zbal_pluggable_free(a2, 0, 0, cap)
+    sma.zbal_pluggable_free(b, 0, 0, other)
+    sma.zbal_pluggable_empty_cache(True)                 # returns b, must leave the pool alone
+    assert _stats(sma).poolCachedBytes == 4 * MiB and _stats(sma).cachedBytes == 0
+    got = [sma.zbal_pluggable_malloc(4 * MiB, 0, cap) for _ in range(8)]
+    assert a not in got                                  # nobody else gets the graph's block
+    for p in got:
+        sma.zbal_pluggable_free(p, 0, 0, cap)
+    assert sma.zbal_sma_begin_pool(*pool, None, None) == 0    # a second capture into the same pool (NULL filter: all streams)
+    assert sma.zbal_pluggable_malloc(4 * MiB, 0, other) == a
+    sma.zbal_pluggable_free(a, 0, 0, other)
+    assert sma.zbal_sma_end_pool(*pool) == 0
+    assert sma.zbal_sma_release_pool(*pool) == 0 and sma.zbal_sma_release_pool(*pool) != 0
+    sma.zbal_pluggable_empty_cache(True)
+    s = _stats(sma)
+    assert s.poolCount == 0 and s.poolCachedBytes == 0 and s.largestFreeBlock == 256 * MiB
+
+
 def test_same_sequence_gives_same_offsets_and_snapshot(sma):
     import random
     from memfabric_hybrid_b200.zbal import module as M
