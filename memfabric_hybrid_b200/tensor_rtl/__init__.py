@@ -4,3 +4,4 @@ from .executor import (All2AllVExcutor, All2AllVExecutor, BatchP2PExecutor, Exec
                        Planner)
 from .pack import pack_tensors, unpack_tensors  # noqa: F401
 from .plan import MFCommTask, P2PCommTask, PTensor, PTensorSet, overlaps, shard_bounds  # noqa: F401
+from .eplb import ExpertMigrator, pair_slots  # noqa: F401

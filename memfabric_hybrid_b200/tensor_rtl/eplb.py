@@ -1,0 +1,114 @@
+"""Expert re-placement for MoE load balancing (EPLB): moves expert weights between expert-parallel ranks when
+the placement of logical experts onto physical slots changes.
+
+A placement is a list ``placement[slot] = logical expert`` over all physical slots of one layer; rank r owns the
+slots ``[r * local, (r + 1) * local)``. Redundant copies of a hot expert are allowed (a logical id may appear in
+several slots). ``ExpertMigrator.plan`` pairs every slot of the new placement with a source slot of the old one
+(a copy already on the destination rank first, else the copies round-robin, so that replicas of one expert do
+not all pull from one rank), packs the tensors of a moving expert (w13, w2, scales, ...) into ONE flat buffer,
+and describes each move as a ``PTensor`` living on ``[src_rank]`` that must end up on ``[dst_rank]``; any
+executor of this package carries the plan out. ``apply`` writes the received experts into their slots.
+
+Parity: app/tensorRTL/examples/eplb/experts_transform_manager.py:236-420 of the reference (pack, plan with one
+PTensor per moving expert, execute, local moves through temporaries, unpack). The serving-engine hooks of that
+example (load statistics, the planner process) are the caller's: this class starts from the two placements.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .pack import pack_tensors, unpack_tensors
+from .plan import PTensor, PTensorSet
+
+
+def pair_slots(old: Sequence[int], new: Sequence[int], local: int) -> List[Tuple[int, int]]:
+    """[(source slot in ``old``, destination slot in ``new``)] for every slot whose expert changes.
+    Deterministic, so every rank computes the same pairing."""
+    if len(old) != len(new) or local <= 0 or len(old) % local:
+        raise ValueError("placements must have the same length, a multiple of the experts per rank")
+    holders: Dict[int, List[int]] = {}
+    for slot, e in enumerate(old):
+        holders.setdefault(e, []).append(slot)
+    turn: Dict[int, int] = {}
+    pairs = []
+    for dst, e in enumerate(new):
+        if old[dst] == e:
+            continue                       # already in place
+        if e not in holders:
+            raise KeyError(f"expert {e} of the new placement is held by no slot of the old one")
+        same_rank = [s for s in holders[e] if s // local == dst // local]
+        if same_rank:
+            src = same_rank[0]
+        else:
+            k = turn.get(e, 0)
+            turn[e] = k + 1
+            src = holders[e][k % len(holders[e])]
+        pairs.append((src, dst))
+    return pairs
+
+
+class ExpertMigrator:
+    def __init__(self, rank: int, ep_size: int, experts_per_rank: int, backend: str = "nccl"):
+        self.rank, self.ep_size, self.local = rank, ep_size, experts_per_rank
+        self.backend = backend
+        self._moves: List[Tuple[int, int]] = []
+        self._remote: List[Tuple[int, PTensor, Optional[dict]]] = []   # (destination slot, tensor, pack metadata)
+        self._local: List[Tuple[int, torch.Tensor, dict]] = []         # (destination slot, packed copy, metadata)
+        self._set: Optional[PTensorSet] = None
+
+    def plan(self, old: Sequence[int], new: Sequence[int], experts: Sequence[torch.Tensor]) -> List:
+        """``experts``: this rank's weight tensors, each of shape [experts_per_rank, ...]. Returns the transfer list
+        for an executor (empty when nothing crosses ranks)."""
+        for w in experts:
+            if w.shape[0] != self.local:
+                raise ValueError(f"expert tensor of shape {tuple(w.shape)} does not have {self.local} local experts")
+        self._moves = pair_slots(old, new, self.local)
+        self._remote, self._local = [], []
+        # the layout of a packed expert is the same on every rank: take it from local slot 0
+        probe, meta = pack_tensors([w[0] for w in experts], torch.int8)
+        numel = probe.numel()
+        pts = []
+        for src, dst in self._moves:
+            sr, dr = src // self.local, dst // self.local
+            if sr == dr:
+                if sr == self.rank:    # a move inside this rank: keep a copy now, slots may be overwritten in any order
+                    packed, m = pack_tensors([w[src % self.local] for w in experts], torch.int8)
+                    self._local.append((dst % self.local, packed, m))
+                continue
+            if self.rank not in (sr, dr):
+                continue
+            shard = pack_tensors([w[src % self.local] for w in experts], torch.int8)[0] if self.rank == sr else None
+            pt = PTensor(shard, torch.int8, 1, [sr], (numel,), 0, rank=self.rank, backend=self.backend)
+            pts.append((pt, [dr]))
+            self._remote.append((dst % self.local, pt, meta))
+        self._set = None
+        if not pts:
+            return []
+        self._set = PTensorSet([p for p, _ in pts])
+        self._set.transfer_map([m for _, m in pts])
+        return self._set.get_transfer_list()
+
+    def apply(self, experts: Sequence[torch.Tensor]) -> int:
+        """After the executor finished: writes received and locally moved experts into their slots. Returns the
+        number of slots of this rank that changed."""
+        changed = 0
+        for slot, packed, meta in self._local:
+            for w, t in zip(experts, unpack_tensors(packed, meta)):
+                w[slot].copy_(t)
+            changed += 1
+        for slot, pt, meta in self._remote:
+            got = pt.collect_tensor()
+            if got is None:            # this rank was the source of the move
+                continue
+            for w, t in zip(experts, unpack_tensors(got, meta)):
+                w[slot].copy_(t)
+            changed += 1
+        self._local, self._remote = [], []
+        return changed
+
+    @property
+    def moves(self) -> List[Tuple[int, int]]:
+        return list(self._moves)
+

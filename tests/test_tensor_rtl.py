@@ -90,3 +90,17 @@ def _reshard(rank, world, port, kind):
 @pytest.mark.parametrize("kind", ["p2p", "a2a", "mf"])
 def test_reshard_executors(kind):
     assert run_ranks(_reshard, 4, (free_port(), kind), timeout=180) == [True] * 4
+
+
+def test_eplb_slot_pairing():
+    from memfabric_hybrid_b200.tensor_rtl import pair_slots
+    old = [0, 1, 2, 3, 0, 1]
+    # nothing moves / a swap inside one rank / a replica pulled from the copy on its own rank / round-robin over holders
+    assert pair_slots(old, old, 2) == []
+    assert pair_slots([0, 1, 2, 3], [1, 0, 2, 3], 2) == [(1, 0), (0, 1)]
+    assert pair_slots(old, [0, 0, 2, 3, 0, 1], 2) == [(0, 1)]
+    assert pair_slots(old, [0, 1, 0, 0, 0, 1], 2) == [(0, 2), (4, 3)]
+    with pytest.raises(KeyError):
+        pair_slots(old, [9, 1, 2, 3, 0, 1], 2)
+    with pytest.raises(ValueError):
+        pair_slots(old, old[:-1], 2)
