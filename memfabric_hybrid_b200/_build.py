@@ -68,18 +68,33 @@ def _build_objs(srcs: list[Path], cmd: list[str], flags: list[str], tag: str, jo
     return objs
 
 
-def build_host(jobs: int | None = None) -> Path:
+SAN_FLAGS = ["-fsanitize=address,undefined,pointer-compare,pointer-subtract", "-fno-omit-frame-pointer", "-fno-sanitize-recover=undefined"]
+
+
+def build_host(jobs: int | None = None, asan: bool = False) -> Path:
+    """``asan=True``: the same sources under AddressSanitizer + UndefinedBehaviorSanitizer into ``lib_asan/``
+    (load it with MF_NATIVE_LIB_DIR and LD_PRELOAD of the compiler's libasan.so)."""
     jobs = jobs or os.cpu_count() or 4
     srcs = [p for d in HOST_DIRS for p in sorted((CSRC / d).glob("*.cpp"))]
     flags = CXXFLAGS + [f"-I{CSRC / 'include'}", f"-I{CSRC}"]
-    objs = _build_objs(srcs, ["g++"], flags, "host", jobs)
-    LIB.mkdir(exist_ok=True)
-    out = LIB / "libmf_smem.so"
+    libdir = LIB
+    if asan:
+        flags = [f for f in flags if f not in ("-O2", "-D_FORTIFY_SOURCE=2")] + ["-O1"] + SAN_FLAGS
+        libdir = PKG / "lib_asan"
+    objs = _build_objs(srcs, ["g++"], flags, "asan" if asan else "host", jobs)
+    libdir.mkdir(exist_ok=True)
+    out = libdir / "libmf_smem.so"
     tmp = out.with_suffix(".so.tmp")
-    subprocess.run(["g++", "-shared", "-o", str(tmp)] + [str(o) for o in objs] +
+    subprocess.run(["g++", "-shared", "-o", str(tmp)] + [str(o) for o in objs] + (SAN_FLAGS if asan else []) +
                    ["-pthread", "-ldl", "-lrt", "-Wl,-z,relro,-z,now"], check=True)
     tmp.replace(out)
     return out
+
+
+def asan_runtime() -> str | None:
+    """Path of the compiler's libasan.so (to LD_PRELOAD under Python), or None."""
+    p = subprocess.run(["gcc", "-print-file-name=libasan.so"], capture_output=True, text=True).stdout.strip()
+    return p if p and os.path.isabs(p) and os.path.exists(p) else None
 
 
 def build_cuda(jobs: int | None = None) -> Path | None:
@@ -143,6 +158,11 @@ def build_all() -> None:
 
 if __name__ == "__main__":
     args = set(sys.argv[1:])
+    if "--asan" in args:
+        print(build_host(asan=True))
+        args.discard("--asan")
+        if not args:
+            sys.exit(0)
     if not args or "--host" in args:
         print(build_host())
     if not args or "--cuda" in args:

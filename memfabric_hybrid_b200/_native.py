@@ -13,7 +13,8 @@ import threading
 from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
-_LIB_DIR = _PKG / "lib"
+# MF_NATIVE_LIB_DIR selects another build of the libraries (the ASAN + UBSAN build lives in lib_asan/)
+_LIB_DIR = Path(os.environ["MF_NATIVE_LIB_DIR"]).resolve() if os.environ.get("MF_NATIVE_LIB_DIR") else _PKG / "lib"
 _lock = threading.Lock()
 _host = None
 _cuda = None
@@ -133,6 +134,8 @@ def _ensure_built(which: str) -> None:
     target = _LIB_DIR / ("libmf_smem.so" if which == "host" else "libmf_cuda.so")
     if target.exists():
         return
+    if _LIB_DIR != _PKG / "lib":
+        raise RuntimeError(f"{target} is missing (MF_NATIVE_LIB_DIR points at a build that does not exist)")
     from . import _build
     (_build.build_host if which == "host" else _build.build_cuda)()
 

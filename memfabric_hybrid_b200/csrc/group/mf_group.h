@@ -43,7 +43,7 @@ struct GroupInfo {
     uint32_t Count() const
     {
         uint32_t n = 0;
-        for (auto w : bitmap) n += (uint32_t)__builtin_popcountll(w);
+        for (uint32_t i = 0; i < kBitmapWords; i++) n += (uint32_t)__builtin_popcountll(bitmap[i]);  // packed: no references
         return n;
     }
 };

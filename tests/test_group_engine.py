@@ -110,9 +110,9 @@ def test_dynamic_join_leave_and_link_down(server):
         assert l.mf_t_group_join(groups[r]) == 0 and l.mf_t_group_joined(groups[r]) == 1
         return True
     _run(n, rank)
-    wait_for(lambda: all(info(g)[1] == n and info(g)[3] == 0b111 for g in groups), "all three members visible everywhere")
-    versions = {info(g)[0] for g in groups}
-    assert len(versions) == 1 and versions.pop() % 2 == 0          # an even version: no event in flight
+    # the joiner's record is visible (odd version: event in flight) before the closing update (even version) reaches everyone
+    wait_for(lambda: all(info(g)[1] == n and info(g)[3] == 0b111 and info(g)[0] % 2 == 0 for g in groups) and
+             len({info(g)[0] for g in groups}) == 1, "all three members visible everywhere, no event in flight")
     assert (0, 2) in events[0] and (0, 2) in events[1]              # the earlier members were told about rank 2
 
     # rank 1 leaves in an orderly way

@@ -1,0 +1,27 @@
+"""The host library under AddressSanitizer + UndefinedBehaviorSanitizer: the control-plane and host-pool tests run
+once more against ``lib_asan/libmf_smem.so`` (the reference runs its unit tests under the same sanitizers)."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+FILES = ["test_config_store.py", "test_group_engine.py", "test_ha_store.py", "test_trace_failpoints.py", "test_transfer_cpu.py",
+         "test_shm_api_cpu.py", "test_bm_host_pool.py", "test_fake_device_pool.py", "test_zbal_cpu.py"]
+
+
+def test_host_tests_are_clean_under_asan_and_ubsan():
+    from memfabric_hybrid_b200 import _build
+    rt = _build.asan_runtime()
+    if rt is None:
+        pytest.skip("the compiler ships no libasan.so")
+    lib = _build.build_host(asan=True)
+    env = dict(os.environ, LD_PRELOAD=rt, MF_NATIVE_LIB_DIR=os.path.dirname(str(lib)),
+               ASAN_OPTIONS="detect_leaks=0:halt_on_error=1:abort_on_error=0", UBSAN_OPTIONS="print_stacktrace=1")
+    # -s: a sanitizer report must reach this process's pipe; the c10d extension is not part of the sanitizer build
+    r = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-s", "-p", "no:cacheprovider", "-k", "not native"] +
+                       [os.path.join(ROOT, "tests", f) for f in FILES], env=env, capture_output=True, text=True, timeout=1500, cwd=ROOT)
+    out = r.stdout + r.stderr
+    assert "runtime error:" not in out and "ERROR: AddressSanitizer" not in out, out[-4000:]
+    assert r.returncode == 0, out[-4000:]
