@@ -1,7 +1,9 @@
 // Example user kernel on the public device API of the symmetric shared memory: an all-reduce (sum) of
 // fp32 vectors that live in the ranks' slices. Every rank reads all peers' inputs over NVLink after a
 // barrier and writes its own output; a closing barrier keeps the inputs intact until all have read.
-// The counterpart of the reference's examples/hbm_share_memory/AllReduce. The tuned collectives are
+// The counterpart of the reference's examples/hbm_share_memory/AllReduce; k_example_shift below is the
+// counterpart of examples/hbm_share_memory/ShiftPutGet (neighbour put with a one-way signal, neighbour get
+// between barriers). The tuned collectives are
 // in mf_coll.cu; this file shows what a few lines of user code on smem_shm_device.cuh look like.
 #include <cooperative_groups.h>
 
@@ -33,7 +35,54 @@ __global__ void __launch_bounds__(256) k_example_allreduce(smem_shm_device_ctx_t
     if (blockIdx.x == 0) smem_shm_barrier(ctx, 2 * epoch);        // nobody overwrites its input before all have read it
 }
 
+// Shift: rank r hands its vector to rank r + 1 (mod size).
+//   put (mode 0): stores `src` into the NEXT rank's `box` over NVLink, then raises a flag there; waits for the flag
+//                 that the previous rank raises here. No barrier: a one-way signal per neighbour is enough.
+//   get (mode 1): after a barrier (every rank's `src` is in place) loads the PREVIOUS rank's `src` into the own `box`;
+//                 a closing barrier keeps `src` intact until the reader is done.
+__global__ void __launch_bounds__(256) k_example_shift(smem_shm_device_ctx_t ctx, const float *src, float *box, uint64_t n, int mode,
+                                                        uint32_t epoch, int *status)
+{
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    const uint32_t next = (ctx.rank + 1) % ctx.rank_size, prev = (ctx.rank + ctx.rank_size - 1) % ctx.rank_size;
+    const uint64_t tid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x, step = (uint64_t)gridDim.x * blockDim.x;
+    if (mode == 0) {
+        float *remote = smem_shm_peer_ptr(ctx, box, next);
+        for (uint64_t i = tid; i < n; i += step) remote[i] = src[i];
+        grid.sync();                                              // all stores of this grid are issued ...
+        if (blockIdx.x == 0 && threadIdx.x == 0) {
+            smem_shm_signal(ctx, next, 33, 0, epoch);             // ... and made visible before the flag (fence inside)
+            if (!smem_shm_wait(ctx, 33, 0, epoch)) atomicExch(status, 1);
+        }
+    } else {
+        if (blockIdx.x == 0 && !smem_shm_barrier(ctx, 2 * epoch - 1, 34) && threadIdx.x == 0) atomicExch(status, 1);
+        grid.sync();
+        if (*reinterpret_cast<volatile int *>(status) == 0) {
+            const float *remote = smem_shm_peer_ptr(ctx, src, prev);
+            for (uint64_t i = tid; i < n; i += step) box[i] = __ldcg(remote + i);
+        }
+        grid.sync();
+        if (blockIdx.x == 0) smem_shm_barrier(ctx, 2 * epoch, 34);
+    }
+}
+
 }  // namespace
+
+// src, box: inside this rank's slice, at the same offsets on every rank. mode 0 = put to the next rank, 1 = get from the
+// previous rank. epoch: 1, 2, 3, ... per mode, the same on every rank. status: device int, 0 on entry; 1 = a wait ran out.
+extern "C" int mf_example_shm_shift(const smem_shm_device_ctx_t *ctx, const float *src, float *box, uint64_t n, int mode, uint32_t epoch,
+                                    int *status, void *stream)
+{
+    if (ctx == nullptr || ctx->rank_size == 0 || ctx->rank_size > 16 || (mode != 0 && mode != 1)) return -1;
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    smem_shm_device_ctx_t c = *ctx;
+    void *params[] = {&c, &src, &box, &n, &mode, &epoch, &status};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(k_example_shift), dim3(sms > 0 ? sms : 64), dim3(256), params,
+                                                0, (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : (int)e;
+}
 
 // in: inside this rank's slice (at the same offset on every rank); out: anywhere on this device.
 // epoch: 1, 2, 3, ... one per call, the same on every rank. status: device int, 0 on entry; 1 = a peer did not arrive.

@@ -33,6 +33,20 @@ def test_shm_user_kernel_multi_gpu():
     assert run_ranks(_shm_allreduce, n, (f"tcp://127.0.0.1:{free_port()}",), timeout=240) == [0.0] * n
 
 
+def _shm_shift(rank, world, url):
+    return _load("examples/hbm_share_memory/shift_put_get.py").run(rank, world, rank % torch.cuda.device_count(), url, n=300_000)
+
+
+def test_shm_shift_single_gpu():
+    assert run_ranks(_shm_shift, 1, (f"tcp://127.0.0.1:{free_port()}",), timeout=180) == [0.0]
+
+
+@pytest.mark.multigpu
+def test_shm_shift_multi_gpu():
+    n = min(torch.cuda.device_count(), 4)
+    assert run_ranks(_shm_shift, n, (f"tcp://127.0.0.1:{free_port()}",), timeout=240) == [0.0] * n
+
+
 def test_hbm_pool_example():
     import subprocess
     import sys
