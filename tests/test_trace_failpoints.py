@@ -69,3 +69,29 @@ def test_fault_points_by_call_and_by_file(tmp_path):
         l.mf_t_server_stop(srv)
     finally:
         l.mf_t_fip_exit()
+
+
+def test_prometheus_exporter_serves_trace_table_and_allocator(tmp_path):
+    import urllib.request
+    from memfabric_hybrid_b200.utils import metrics
+    from memfabric_hybrid_b200.zbal import _capi as K
+    l = H.lib()
+    assert l.mf_t_trace_start(str(tmp_path).encode(), 60_000) == 0
+    try:
+        for ret in (0, 0, -1):
+            l.mf_t_trace_hit(3, ret, 200)
+        K.lib().zbal_simulate_init(0x7000_0000_0000, 64 << 20)
+        p = K.lib().zbal_pluggable_malloc(3 << 20, 0, None)
+        text = metrics.render()
+        name = l.mf_t_trace_name(3).decode()
+        assert f'mf_trace_calls_total{{point="{name}"}} 3' in text
+        assert f'mf_trace_failed_total{{point="{name}"}} 1' in text and f'mf_trace_in_flight{{point="{name}"}} 0' in text
+        assert "# TYPE mf_trace_seconds_total counter" in text and "zbal_heap_in_use_bytes 4194304" in text
+        port = metrics.serve(0)
+        body = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=10).read().decode()
+        assert "zbal_heap_heap_size 67108864" in body and body.endswith("\n")
+        K.lib().zbal_pluggable_free(p, 0, 0, None)
+    finally:
+        metrics.stop()
+        K.lib().zbal_sma_uninit(0)
+        l.mf_t_trace_stop()
