@@ -263,12 +263,17 @@ class Buffer:
     def fused_deep_moe(self, x: torch.Tensor, topk_idx: torch.Tensor, gmm1_permuted_weight: torch.Tensor,
                        gmm1_permuted_weight_scale: torch.Tensor, gmm2_weight: torch.Tensor, gmm2_weight_scale: torch.Tensor,
                        topk_weights: torch.Tensor, num_experts: int, shared_expert_num: int = 0, shared_expert_rank_num: int = 0,
-                       quant_mode: int = 0, num_max_dispatch_tokens_per_rank: int = 0, **unused) -> Tuple[torch.Tensor, torch.Tensor]:
+                       quant_mode: int = 0, num_max_dispatch_tokens_per_rank: int = 0, x_active_mask: Optional[torch.Tensor] = None,
+                       **unused) -> Tuple[torch.Tensor, torch.Tensor]:
         """dispatch (fp8 quant fused) -> grouped GEMM1 + SwiGLU -> requant -> grouped GEMM2 with the weighted
         push home fused into its epilogue -> slot reduce. gmm1 weights: [local experts, 2I, H] fp8, gate/up
         tile-interleaved (``ops.moe.interleave_gate_up_fp8``) with [.., 2I/128, H/128] scales; gmm2: [.., H, I].
+        ``x_active_mask`` ([T] bool): rows that are False take no part (padding of a decode batch): they are sent to no
+        expert and their output rows are zero.
         -> (output [T, H] bf16, tokens received per local expert)"""
         assert self.use_fp8, "the fused path runs on fp8 rows"
+        if x_active_mask is not None:
+            topk_idx = topk_idx.masked_fill(~x_active_mask.to(torch.bool).view(-1, 1), -1)   # the kernels skip negative ids
         moe = self._moe
         st = moe.dispatch(x, topk_idx, topk_weights)
         moe.expert_ffn(st, gmm1_permuted_weight, gmm1_permuted_weight_scale, gmm2_weight, gmm2_weight_scale)

@@ -253,6 +253,23 @@ def _buffer_scenario(rank, world, port, sync):
             ly = lrecv[:n].clone()
         lout, _, _ = buf.low_latency_combine(ly, idx, w, lh)
         torch.testing.assert_close(lout.float(), expect, rtol=0.06, atol=0.06)
+        if use_fp8:
+            # fused path with an activity mask: masked rows come back as zeros, the others are unchanged by the mask
+            from memfabric_hybrid_b200.ops import moe as M
+            El, I = E // world, 256
+            gw = torch.Generator("cuda").manual_seed(99)          # the same expert weights on every rank's copy of the experts
+            w1 = (torch.randn(El, 2 * I, H, device="cuda", generator=gw) * 0.03).to(torch.bfloat16)
+            w2 = (torch.randn(El, H, I, device="cuda", generator=gw) * 0.03).to(torch.bfloat16)
+            w1q, w1s = M.quantize_weight_fp8(w1)
+            w1q = M.interleave_gate_up_fp8(w1q)
+            w2q, w2s = M.quantize_weight_fp8(w2)
+            full, _ = buf.fused_deep_moe(x, idx, w1q, w1s, w2q, w2s, w, E)
+            full = full.clone()
+            mask = torch.ones(T, dtype=torch.bool, device="cuda")
+            mask[T // 2:] = False
+            part, _ = buf.fused_deep_moe(x, idx, w1q, w1s, w2q, w2s, w, E, x_active_mask=mask)
+            assert float(part[T // 2:].abs().max()) == 0.0 and float(full[T // 2:].abs().max()) > 0.0
+            torch.testing.assert_close(part[:T // 2].float(), full[:T // 2].float(), rtol=1e-2, atol=1e-3)
         torch.cuda.synchronize()
         gemm.check_status()
         buf.destroy()
