@@ -150,7 +150,7 @@ public:
             strided_ = step > 0;
             for (int i = 0; strided_ && i + 1 < size; i++) strided_ = ranks_[i + 1] - ranks_[i] == step;
         }
-        std::stringstream forced(EnvOr("ZBAL_NCCL_OP", ""));
+        std::stringstream forced(EnvOr("ZBAL_NCCL_OP", EnvOr("ZBAL_HCCL_OP", "").c_str()));  // the second name is the reference's
         for (std::string item; std::getline(forced, item, ',');) {
             size_t a = item.find_first_not_of(' '), b = item.find_last_not_of(' ');
             if (a != std::string::npos) forced_.insert(item.substr(a, b - a + 1));

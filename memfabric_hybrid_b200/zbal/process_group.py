@@ -10,7 +10,7 @@ _reduce_scatter_base, barrier, alltoall_base, send, recv (the method set of the 
 app/zbal/src/csrc/adaptor/pytorch_npu/zbal_pytorch_process_group.h:130-166). Everything else, tensors of
 types the kernels cannot reduce, and groups whose ranks are not evenly spaced go to an internal NCCL
 process group (the reference falls back to its vendor library in the same way, selected by an
-environment list; here the list is ZBAL_NCCL_OP, comma separated op names, for forcing the fallback).
+environment list; here the list is ZBAL_NCCL_OP, or the reference's name ZBAL_HCCL_OP: comma separated op names, for forcing the fallback).
 
 Stream discipline (zbal_pytorch_process_group.cpp:312-367 of the reference): one side stream per group;
 it first waits on an event recorded on the caller's stream, the operation is enqueued, an end event is
@@ -99,7 +99,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         self._gloo = None
         self._stream = None
         self._strided = self._check_strided()
-        self._forced = {s.strip() for s in os.environ.get("ZBAL_NCCL_OP", "").split(",") if s.strip()}
+        self._forced = {s.strip() for s in os.environ.get("ZBAL_NCCL_OP", os.environ.get("ZBAL_HCCL_OP", "")).split(",") if s.strip()}
         self._own_stream = os.environ.get("ZBAL_OP_DEFAULT_STREAM", os.environ.get("ZBAL_OP_DEFUALT_STREAM", "0")) != "1"
         _live.append(self)
         if M.is_initialized():
@@ -418,6 +418,21 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         return tuple(int(v) for v in st)
 
 
+def _build_native(path) -> None:
+    """Builds the extension in-tree when it is missing (a fresh checkout); ranks that start together take turns."""
+    import fcntl
+    try:
+        path.parent.mkdir(exist_ok=True)
+        with open(path.parent / ".c10d.lock", "w") as lock:
+            fcntl.flock(lock, fcntl.LOCK_EX)
+            if not path.exists():
+                from .. import _build
+                _build.build_c10d()
+    except Exception as e:  # noqa: BLE001 - no compiler or headers: the Python implementation serves
+        import warnings
+        warnings.warn(f"zbal: could not build the native c10d extension ({e}); using the Python process group")
+
+
 def native_extension():
     """The C++ ``c10d::Backend`` module (csrc/c10d/zbal_process_group.cpp), or None when it was not built."""
     global _native_ext
@@ -425,6 +440,8 @@ def native_extension():
         import importlib.util
         from .. import _native as N
         path = N._LIB_DIR / "_zbal_c10d.so"
+        if not path.exists() and os.environ.get("ZBAL_PG_IMPL", "native").lower() != "python":
+            _build_native(path)
         if not path.exists():
             _native_ext = False
         else:
