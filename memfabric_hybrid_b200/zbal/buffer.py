@@ -272,6 +272,9 @@ class Buffer:
         expert and their output rows are zero.
         -> (output [T, H] bf16, tokens received per local expert)"""
         assert self.use_fp8, "the fused path runs on fp8 rows"
+        if shared_expert_rank_num:
+            raise NotImplementedError("fused_deep_moe: ranks dedicated to shared experts are not supported; run the shared expert as a "
+                                      "dense MLP beside this call (its output adds to the returned rows)")
         if x_active_mask is not None:
             topk_idx = topk_idx.masked_fill(~x_active_mask.to(torch.bool).view(-1, 1), -1)   # the kernels skip negative ids
         moe = self._moe
