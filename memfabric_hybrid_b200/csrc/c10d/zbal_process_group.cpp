@@ -117,7 +117,10 @@ public:
     {
         if (!future_) {
             // Completed at once, as in the reference (cpp:352-355): consumers order themselves by wait().
-            future_ = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()));
+            // The future is told which device its tensors live on: it records an event on the current stream when it
+            // is completed (after that stream was made to wait for the operation) and its consumers wait on that event.
+            future_ = c10::make_intrusive<c10::ivalue::Future>(c10::ListType::create(c10::TensorType::get()),
+                                                               std::vector<c10::Device>{c10::Device(c10::kCUDA, dev_)});
             wait();
             future_->markCompleted(c10::IValue(outputs_));
         }

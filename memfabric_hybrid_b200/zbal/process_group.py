@@ -81,7 +81,10 @@ class WorkZBAL(dist._Work):
 
     def get_future(self):
         if self._future is None:
-            self._future = torch.futures.Future()
+            devs = sorted({t.device for t in (self._result if isinstance(self._result, (list, tuple)) else [self._result])
+                           if isinstance(t, torch.Tensor) and t.is_cuda}, key=str)
+            self._future = torch.futures.Future(devices=devs) if devs else torch.futures.Future()
+            self.wait()                            # the current stream waits for the operation, then the future records it
             self._future.set_result(self._result)  # marked complete at once, like the reference (cpp:352-355)
         return self._future
 

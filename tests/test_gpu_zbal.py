@@ -109,6 +109,21 @@ def _pg_scenario(rank, world, port, impl, sync):
             assert torch.equal(y, torch.full_like(y, float(sum(members))))
     dist.barrier()
 
+    # DistributedDataParallel on top of the backend: parameter broadcast, bucketed all-reduce through Work futures
+    from torch.nn.parallel import DistributedDataParallel as DDP
+
+    def make():
+        torch.manual_seed(1234)
+        return torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.ReLU(), torch.nn.Linear(128, 8)).cuda()
+    ddp = DDP(make(), device_ids=[dev])
+    ddp(_draw(rank, 32 * 64).view(32, 64)).square().mean().backward()
+    ref_model = make()
+    for r in range(world):
+        (ref_model(_draw(r, 32 * 64).view(32, 64)).square().mean() / world).backward()
+    for p, q in zip(ddp.module.parameters(), ref_model.parameters()):
+        torch.testing.assert_close(p.grad, q.grad, rtol=1e-4, atol=1e-5)
+    del ddp
+
     # tensors from the symmetric allocator: same offset on every rank, usable by torch, reused after free
     with zbal.switch_to_allocator():
         t = torch.arange(1 << 20, device="cuda", dtype=torch.float32)
