@@ -1,7 +1,7 @@
 """Device timeline of the low-latency MoE pair (one cooperative launch per direction) on N GPUs.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29531 \
-        -m memfabric_hybrid_b200.utils.ll_timeline --out-dir gpurun_out
+        -m memfabric_hybrid_b200.utils.ll_timeline --out-dir out
 
 Every rank writes ``ll_trace_<rank>.json`` (Chrome trace) and rank 0 prints, per phase, the number of events, the
 median and the longest duration, and the (start, duration) pairs of CTA 0 in microseconds.
