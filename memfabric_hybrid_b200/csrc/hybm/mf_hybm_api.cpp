@@ -150,7 +150,7 @@ int32_t hybm_wait(hybm_entity_t e) { return E(e) ? ToBm(E(e)->Wait()) : BM_INVAL
 int32_t hybm_data_quant_copy(hybm_entity_t e, hybm_quant_copy_params *params)
 {
     if (E(e) == nullptr || params == nullptr) return BM_INVALID_PARAM;
-    return ToBm(E(e)->QuantCopy(*params, 0));
+    return ToBm(E(e)->QuantCopy(*params, (params->flags & HYBM_QUANT_FP8_E4M3) ? 1 : 0));
 }
 
 }  // extern "C"

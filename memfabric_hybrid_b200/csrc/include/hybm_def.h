@@ -163,8 +163,10 @@ typedef struct {
     uint32_t unitNum;   /* elements per quantisation unit */
     void *stream;
     uint32_t inputType; /* 0 bf16, 1 fp16 */
-    uint32_t flags;
+    uint32_t flags;     /* HYBM_QUANT_FP8_E4M3: fp8 e4m3 with one factor per 128 elements (unitNum must be 128) instead of int8 */
 } hybm_quant_copy_params;
+
+#define HYBM_QUANT_FP8_E4M3 (1u << 0)
 
 #ifdef __cplusplus
 }

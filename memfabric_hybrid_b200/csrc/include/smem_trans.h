@@ -25,6 +25,8 @@ typedef enum {
     SMEM_TRANS_BUTT
 } smem_trans_role_t;
 
+#define SMEM_TRANS_QUANT_FP8_E4M3 (1u << 0) /* extension: output format of smem_trans_batch_quant_write */
+
 typedef struct {
     smem_trans_role_t role;
     uint32_t initTimeout; /* seconds, default 120 */
@@ -46,7 +48,7 @@ typedef struct {
     uint32_t unitNum;
     void *stream;
     uint32_t inputType; /* 0 bf16, 1 fp16 */
-    uint32_t flags;
+    uint32_t flags;     /* SMEM_TRANS_QUANT_FP8_E4M3: fp8 e4m3 with one factor per 128 elements instead of int8 */
 } smem_trans_quant_copy_param_t;
 
 typedef void (*smem_trans_peer_down_callback_t)(const char *peerUniqueId, void *userData);

@@ -85,50 +85,98 @@ __global__ void __launch_bounds__(kCopyThreads) mf_xcopy_batch_kernel(const Copy
     }
 }
 
-// One CTA per (item, unit). Two passes over the unit: absolute maximum, then scale + round + store.
+// One WARP per (item, unit); a CTA of 8 warps walks the units of its item. The unit is read once when it fits in
+// the lanes' registers (unit <= 512 elements with 16-byte loads), else twice (the second pass hits L1 / L2):
+// absolute maximum by warp shuffles, then scale + round + 8-byte stores to the (peer) destination.
 // mode 0: int8, q = rint(x * 127 / amax), dequant factor amax / 127 written to scale[unitIndex]
 // mode 1: fp8 e4m3 (satfinite), q = x * 448 / amax, dequant factor amax / 448
+// Vector path: source 16-byte aligned, destination 8-byte aligned, unit a multiple of 8; anything else takes
+// the element-wise path of the same warp layout.
 template <typename In> __device__ __forceinline__ float to_f32(In v);
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 
+template <typename In> __device__ __forceinline__ void unpack8(const uint4 &raw, float *f)
+{
+    const In *h = reinterpret_cast<const In *>(&raw);
+#pragma unroll
+    for (int k = 0; k < 8; k++) f[k] = to_f32<In>(h[k]);
+}
+
+template <int MODE> __device__ __forceinline__ uint8_t quant1(float x, float mul)
+{
+    if (MODE == 0) {
+        const float q = fminf(127.f, fmaxf(-127.f, rintf(x * mul)));
+        return (uint8_t)(int8_t)q;
+    }
+    return (uint8_t)__nv_cvt_float_to_fp8(x * mul, __NV_SATFINITE, __NV_E4M3);
+}
+
+template <int MODE> __device__ __forceinline__ uint2 quant8(const float *f, float mul)
+{
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        lo |= (uint32_t)quant1<MODE>(f[k], mul) << (8 * k);
+        hi |= (uint32_t)quant1<MODE>(f[4 + k], mul) << (8 * k);
+    }
+    return make_uint2(lo, hi);
+}
+
 template <typename In, int MODE>
 __global__ void __launch_bounds__(256) mf_xcopy_quant_kernel(const QuantItem *__restrict__ items, uint32_t unit)
 {
-    __shared__ float red[8];
     __shared__ QuantItem it;
     if (threadIdx.x == 0) it = items[blockIdx.y];
     __syncthreads();
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint64_t units = (it.elems + unit - 1) / unit;
     const In *src = reinterpret_cast<const In *>(it.src);
+    uint8_t *dst = reinterpret_cast<uint8_t *>(it.dst);
     float *scales = reinterpret_cast<float *>(it.scale);
-    for (uint64_t u = blockIdx.x; u < units; u += gridDim.x) {
+    const float qmax = MODE == 0 ? 127.f : 448.f;
+    const bool vec = (unit % 8) == 0 && (it.src & 15) == 0 && (it.dst & 7) == 0;
+    for (uint64_t u = (uint64_t)blockIdx.x * 8 + warp; u < units; u += (uint64_t)gridDim.x * 8) {
         const uint64_t b = u * unit;
         const uint64_t e = min(it.elems, b + (uint64_t)unit);
-        float amax = 0.f;
-        for (uint64_t k = b + threadIdx.x; k < e; k += blockDim.x) amax = fmaxf(amax, fabsf(to_f32<In>(src[k])));
+        const uint64_t nv = vec ? (e - b) / 8 : 0;                 // whole 8-element vectors of this unit
+        const uint4 *src16 = reinterpret_cast<const uint4 *>(src + b);
+        uint4 keep[2];
+        float amax = 0.f, f[8];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const uint64_t v = lane + 32u * i;
+            if (v < nv) {
+                keep[i] = __ldg(src16 + v);
+                unpack8<In>(keep[i], f);
+#pragma unroll
+                for (int k = 0; k < 8; k++) amax = fmaxf(amax, fabsf(f[k]));
+            }
+        }
+        for (uint64_t v = lane + 64; v < nv; v += 32) {
+            unpack8<In>(__ldg(src16 + v), f);
+#pragma unroll
+            for (int k = 0; k < 8; k++) amax = fmaxf(amax, fabsf(f[k]));
+        }
+        for (uint64_t k = b + nv * 8 + lane; k < e; k += 32) amax = fmaxf(amax, fabsf(to_f32<In>(src[k])));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
-        __syncthreads();
-        amax = red[0];
-#pragma unroll
-        for (int w = 1; w < 8; w++) amax = fmaxf(amax, red[w]);
-        const float qmax = MODE == 0 ? 127.f : 448.f;
         const float mul = amax > 0.f ? qmax / amax : 1.f;
-        if (threadIdx.x == 0) scales[u] = amax > 0.f ? amax / qmax : 1.f;
-        if (MODE == 0) {
-            int8_t *dst = reinterpret_cast<int8_t *>(it.dst);
-            for (uint64_t k = b + threadIdx.x; k < e; k += blockDim.x) {
-                float q = rintf(to_f32<In>(src[k]) * mul);
-                dst[k] = (int8_t)fminf(127.f, fmaxf(-127.f, q));
+        if (lane == 0) scales[u] = amax > 0.f ? amax / qmax : 1.f;
+        uint2 *dst8 = reinterpret_cast<uint2 *>(dst + b);
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const uint64_t v = lane + 32u * i;
+            if (v < nv) {
+                unpack8<In>(keep[i], f);
+                dst8[v] = quant8<MODE>(f, mul);
             }
-        } else {
-            __nv_fp8_storage_t *dst = reinterpret_cast<__nv_fp8_storage_t *>(it.dst);
-            for (uint64_t k = b + threadIdx.x; k < e; k += blockDim.x)
-                dst[k] = __nv_cvt_float_to_fp8(to_f32<In>(src[k]) * mul, __NV_SATFINITE, __NV_E4M3);
         }
-        __syncthreads();
+        for (uint64_t v = lane + 64; v < nv; v += 32) {
+            unpack8<In>(__ldg(src16 + v), f);
+            dst8[v] = quant8<MODE>(f, mul);
+        }
+        for (uint64_t k = b + nv * 8 + lane; k < e; k += 32) dst[k] = quant1<MODE>(to_f32<In>(src[k]), mul);
     }
 }
 

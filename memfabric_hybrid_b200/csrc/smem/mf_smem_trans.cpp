@@ -220,7 +220,7 @@ public:
             if (rc != OK) return MF_FAIL(ERR_INVALID_PARAM, "quant write item %u: destination or scale is not a registered device buffer of %s", i, p.remoteUniqueId);
             items[i] = QuantItem{reinterpret_cast<uint64_t>(p.localAddrs[i]), dst, sc, elems};
         }
-        return entity_->SubmitQuant(items, p.unitNum, p.inputType == 1, 0, p.stream);
+        return entity_->SubmitQuant(items, p.unitNum, p.inputType == 1, (p.flags & SMEM_TRANS_QUANT_FP8_E4M3) ? 1 : 0, p.stream);
     }
 
     void SetPeerDown(smem_trans_peer_down_callback_t cb, void *ud)
