@@ -176,6 +176,24 @@ class BigMemory:
     def wait(self) -> int:
         return N.lib().smem_bm_wait(self._h)
 
+    def quant_copy_batch(self, src_addrs, dst_addrs, sizes, scale_addrs, unit: int, fp8: bool = False, fp16_input: bool = False,
+                         stream: int = 0) -> int:
+        """Extension: quantise-while-copy. ``sizes`` are the SOURCE bytes (bf16, or fp16 with ``fp16_input``); each item
+        writes ``size / 2`` quantised bytes to its destination and one fp32 dequantisation factor per ``unit`` elements
+        to its scale address. int8 by default; ``fp8=True``: e4m3 with ``unit`` 128. Destinations may be peer slices."""
+        n = len(sizes)
+
+        class _P(C.Structure):
+            _fields_ = [("sources", C.POINTER(C.c_void_p)), ("destinations", C.POINTER(C.c_void_p)), ("dataSizes", C.POINTER(C.c_uint64)),
+                        ("scale", C.POINTER(C.c_void_p)), ("offset", C.POINTER(C.c_void_p)), ("batchSize", C.c_uint32), ("unitNum", C.c_uint32),
+                        ("stream", C.c_void_p), ("inputType", C.c_uint32), ("flags", C.c_uint32)]
+        keep = (_ptr_array(src_addrs[:n]), _ptr_array(dst_addrs[:n]), (C.c_uint64 * n)(*[int(v) for v in sizes]), _ptr_array(scale_addrs[:n]),
+                _ptr_array([0] * n))
+        p = _P(keep[0], keep[1], keep[2], keep[3], keep[4], n, unit, stream or None, 1 if fp16_input else 0, 1 if fp8 else 0)
+        f = N.lib().mf_bm_quant_copy
+        f.restype, f.argtypes = C.c_int32, [C.c_void_p, C.c_void_p]
+        return f(self._h, C.byref(p))
+
     def copy_stats(self) -> dict:
         """Counters of the copy paths (extension): kernel launches/chunks, engine, host, process-VM copies."""
         out = (C.c_uint64 * 6)()

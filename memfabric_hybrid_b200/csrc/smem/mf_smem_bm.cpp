@@ -311,6 +311,16 @@ uint32_t smem_bm_get_rank_id_by_gva(smem_bm_t handle, void *gva)
     return e ? e->RankOfGva(gva) : UINT32_MAX;
 }
 
+// Extension (not in the reference ABI): quantise-while-copy on a pool object (the reference reaches this kernel only
+// through smem_trans_batch_quant_write). Sources are bf16 / fp16 device buffers, destinations and factor arrays device
+// addresses of this rank or of a peer's slice; params->flags & HYBM_QUANT_FP8_E4M3 selects fp8 e4m3 with 1 x 128 factors.
+int32_t mf_bm_quant_copy(smem_bm_t handle, hybm_quant_copy_params *params)
+{
+    auto e = H(handle);
+    if (!e || params == nullptr) return SMEM_INVALID_PARAM;
+    return Pub(e->Entity()->QuantCopy(*params, (params->flags & HYBM_QUANT_FP8_E4M3) ? 1 : 0));
+}
+
 // Extension (not in the reference ABI): counters of what the copy paths did since creation, in the order
 // kernel launches, kernel work chunks, copy-engine copies, host memcpys, process-VM copies, coalesced items.
 int32_t mf_bm_copy_stats(smem_bm_t handle, uint64_t out[6])

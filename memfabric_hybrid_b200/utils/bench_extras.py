@@ -239,6 +239,19 @@ def xcopy_sweep(h, rank, world, flush):
         bu.barrier()
         out.append({"op": "kv_blocks", "blocks": blocks, "bytes": nbytes, "put_us": round(p_ms * 1e3, 1), "put_GBps": round(nbytes / p_ms / 1e6, 1),
                     "get_us": round(g_ms * 1e3, 1), "get_GBps": round(nbytes / g_ms / 1e6, 1)})
+    # quantising put: bf16 rows become fp8 e4m3 with one factor per 128 elements on their way to the next GPU
+    items, per = 1024, 128 * 1024                                   # 1024 pieces of 256 KiB bf16, the size of a KV segment pair
+    xb = torch.randn(items * per, dtype=torch.bfloat16, device="cuda")
+    q_base, s_base = theirs, theirs + items * per                    # fp8 bytes, then the factors, inside the peer's slice
+    side.wait_stream(torch.cuda.current_stream())
+    srcs = [xb.data_ptr() + i * per * 2 for i in range(items)]
+    dsts = [q_base + i * per for i in range(items)]
+    scs = [s_base + i * (per // 128) * 4 for i in range(items)]
+    q_ms = timed(lambda: h.quant_copy_batch(srcs, dsts, [per * 2] * items, scs, 128, fp8=True, stream=stream))
+    bu.barrier()
+    out.append({"op": "quant_put_fp8_1x128", "bytes_in": items * per * 2, "us": round(q_ms * 1e3, 1),
+                "in_GBps": round(items * per * 2 / q_ms / 1e6, 1), "wire_GBps": round(items * per * (1 + 4 / 128) / q_ms / 1e6, 1)})
+    del xb
     p_ms = timed(lambda: h.copy_data(src.data_ptr(), theirs, big, bm.BmCopyType.L2G, fl, stream))
     bu.barrier()
     g_ms = timed(lambda: h.copy_data(theirs, dst.data_ptr(), big, bm.BmCopyType.G2L, fl, stream))

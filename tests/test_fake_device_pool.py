@@ -82,3 +82,52 @@ def test_fake_device_two_ranks():
     url = f"tcp://127.0.0.1:{free_port()}"
     ranks = run_ranks(_rank, 2, (url,), timeout=180, env={"MF_DEVICE_BACKEND": "fake"}, with_barrier=True)
     assert sorted(ranks) == [0, 1]
+
+
+def _quant_rank(rank, world, url):
+    import torch
+    import memfabric_hybrid as mf
+    from memfabric_hybrid import bm
+    assert mf.initialize() == 0
+    cfg = bm.BmConfig()
+    cfg.rank_id, cfg.start_store, cfg.auto_ranking = 0, True, False
+    assert bm.initialize(url, 1, 0, cfg) == 0, mf.get_last_err_msg()
+    h = bm.create2(id=4, local_dram_size=0, max_dram_size=0, local_hbm_size=8 * MiB, max_hbm_size=8 * MiB)
+    assert h.join() == 0, mf.get_last_err_msg()
+    base = h.peer_rank_ptr(0, bm.BmMemType.DEVICE)
+    rows, unit, cols = 3, 64, 200                                     # 200 = 3 units of 64 + a tail of 8
+    x = (torch.randn(rows, cols) * 4).to(torch.bfloat16)
+    x[1, :64] = 0
+    units = (cols + unit - 1) // unit
+    q_at, s_at = base, base + MiB
+    rc = h.quant_copy_batch([x[i].data_ptr() for i in range(rows)], [q_at + i * 256 for i in range(rows)], [cols * 2] * rows,
+                            [s_at + i * units * 4 for i in range(rows)], unit)
+    assert rc == 0, mf.get_last_err_msg()
+    q = np.zeros((rows, 256), dtype=np.int8)
+    s = np.zeros((rows, units), dtype=np.float32)
+    assert h.copy_data(q_at, q.ctypes.data, q.nbytes, bm.BmCopyType.G2H, 0) == 0
+    assert h.copy_data(s_at, s.ctypes.data, s.nbytes, bm.BmCopyType.G2H, 0) == 0
+    xf = x.float().numpy()
+    for i in range(rows):
+        for u in range(units):
+            seg = xf[i, u * unit:min(cols, (u + 1) * unit)]
+            am = np.abs(seg).max()
+            if am == 0:
+                assert s[i, u] == 1.0 and not q[i, u * unit:u * unit + len(seg)].any()
+                continue
+            assert abs(s[i, u] - am / 127.0) < 1e-6
+            assert np.abs(q[i, u * unit:u * unit + len(seg)] - np.rint(seg * np.float32(127.0 / am))).max() <= 1
+    assert not q[:, cols:].any()                                      # nothing written past the row
+    # the fp8 format needs the device: refused by the host oracle, with a message
+    assert h.quant_copy_batch([x[0].data_ptr()], [q_at], [128 * 2], [s_at], 128, fp8=True) != 0
+    mf.get_and_clear_last_err_msg()
+    h.leave()
+    h.destroy()
+    bm.uninitialize(0)
+    mf.uninitialize()
+    return 0
+
+
+def test_quantising_copy_against_the_host_oracle():
+    url = f"tcp://127.0.0.1:{free_port()}"
+    assert run_ranks(_quant_rank, 1, (url,), timeout=120, env={"MF_DEVICE_BACKEND": "fake"}) == [0]
