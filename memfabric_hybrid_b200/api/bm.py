@@ -92,6 +92,12 @@ def _ptr_array(values: Sequence[int]):
     return (C.c_void_p * len(values))(*[int(v) for v in values])
 
 
+class _QuantParamsC(C.Structure):   # hybm_quant_copy_params
+    _fields_ = [("sources", C.POINTER(C.c_void_p)), ("destinations", C.POINTER(C.c_void_p)), ("dataSizes", C.POINTER(C.c_uint64)),
+                ("scale", C.POINTER(C.c_void_p)), ("offset", C.POINTER(C.c_void_p)), ("batchSize", C.c_uint32), ("unitNum", C.c_uint32),
+                ("stream", C.c_void_p), ("inputType", C.c_uint32), ("flags", C.c_uint32)]
+
+
 class BigMemory:
     def __init__(self, handle: int):
         self._h = handle
@@ -176,23 +182,28 @@ class BigMemory:
     def wait(self) -> int:
         return N.lib().smem_bm_wait(self._h)
 
+    def prepare_quant_batch(self, src_addrs, dst_addrs, sizes, scale_addrs, unit: int, fp8: bool = False, fp16_input: bool = False):
+        """Extension: marshals a quantising batch once (see ``quant_copy_batch``) for repeated submission."""
+        n = len(sizes)
+        keep = (_ptr_array(src_addrs[:n]), _ptr_array(dst_addrs[:n]), (C.c_uint64 * n)(*[int(v) for v in sizes]), _ptr_array(scale_addrs[:n]),
+                _ptr_array([0] * n))
+        p = _QuantParamsC(keep[0], keep[1], keep[2], keep[3], keep[4], n, unit, None, 1 if fp16_input else 0, 1 if fp8 else 0)
+        return p, keep
+
+    def quant_copy_prepared(self, prepared, stream: int = 0) -> int:
+        p, _keep = prepared
+        p.stream = stream or None
+        f = N.lib().mf_bm_quant_copy
+        f.restype, f.argtypes = C.c_int32, [C.c_void_p, C.c_void_p]
+        return f(self._h, C.byref(p))
+
     def quant_copy_batch(self, src_addrs, dst_addrs, sizes, scale_addrs, unit: int, fp8: bool = False, fp16_input: bool = False,
                          stream: int = 0) -> int:
         """Extension: quantise-while-copy. ``sizes`` are the SOURCE bytes (bf16, or fp16 with ``fp16_input``); each item
         writes ``size / 2`` quantised bytes to its destination and one fp32 dequantisation factor per ``unit`` elements
-        to its scale address. int8 by default; ``fp8=True``: e4m3 with ``unit`` 128. Destinations may be peer slices."""
-        n = len(sizes)
-
-        class _P(C.Structure):
-            _fields_ = [("sources", C.POINTER(C.c_void_p)), ("destinations", C.POINTER(C.c_void_p)), ("dataSizes", C.POINTER(C.c_uint64)),
-                        ("scale", C.POINTER(C.c_void_p)), ("offset", C.POINTER(C.c_void_p)), ("batchSize", C.c_uint32), ("unitNum", C.c_uint32),
-                        ("stream", C.c_void_p), ("inputType", C.c_uint32), ("flags", C.c_uint32)]
-        keep = (_ptr_array(src_addrs[:n]), _ptr_array(dst_addrs[:n]), (C.c_uint64 * n)(*[int(v) for v in sizes]), _ptr_array(scale_addrs[:n]),
-                _ptr_array([0] * n))
-        p = _P(keep[0], keep[1], keep[2], keep[3], keep[4], n, unit, stream or None, 1 if fp16_input else 0, 1 if fp8 else 0)
-        f = N.lib().mf_bm_quant_copy
-        f.restype, f.argtypes = C.c_int32, [C.c_void_p, C.c_void_p]
-        return f(self._h, C.byref(p))
+        to its scale address. int8 by default; ``fp8=True``: e4m3 with ``unit`` 128. Destinations may be peer slices.
+        Without a stream the call returns when the data has arrived."""
+        return self.quant_copy_prepared(self.prepare_quant_batch(src_addrs, dst_addrs, sizes, scale_addrs, unit, fp8, fp16_input), stream)
 
     def copy_stats(self) -> dict:
         """Counters of the copy paths (extension): kernel launches/chunks, engine, host, process-VM copies."""

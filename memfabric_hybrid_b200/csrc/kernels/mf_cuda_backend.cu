@@ -428,7 +428,13 @@ public:
         auto *q = reinterpret_cast<const mfk::QuantItem *>(items);
         for (uint32_t off = 0; off < count; off += 65535) {
             uint32_t n = std::min<uint32_t>(65535, count - off);
-            dim3 grid((unsigned)std::max(1, grid_ / 2), n);
+            // Every CTA fetches its descriptor from the pinned host ring (a PCIe read), so the grid is kept near the
+            // number of CTAs the GPU can hold: with many items one CTA walks all units of its item, with few items the
+            // units of an item are spread over several CTAs (8 units, one per warp, per CTA and step).
+            uint64_t maxUnits = 1;
+            for (uint32_t i = 0; i < n; i++) maxUnits = std::max<uint64_t>(maxUnits, (items[off + i].elems + unit - 1) / unit);
+            const uint64_t perItem = std::max<uint64_t>(1, (2ull * (uint64_t)std::max(1, grid_) + n - 1) / n);
+            dim3 grid((unsigned)std::min<uint64_t>({perItem, (maxUnits + 15) / 16, 65535ull}), n);  // a CTA takes at least 16 units per step
             cudaStream_t st = (cudaStream_t)s;
             if (inputFp16) {
                 if (mode == 0) mfk::mf_xcopy_quant_kernel<__half, 0><<<grid, 256, 0, st>>>(q + off, unit);

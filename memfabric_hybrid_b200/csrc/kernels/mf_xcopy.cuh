@@ -136,47 +136,65 @@ __global__ void __launch_bounds__(256) mf_xcopy_quant_kernel(const QuantItem *__
     float *scales = reinterpret_cast<float *>(it.scale);
     const float qmax = MODE == 0 ? 127.f : 448.f;
     const bool vec = (unit % 8) == 0 && (it.src & 15) == 0 && (it.dst & 7) == 0;
-    for (uint64_t u = (uint64_t)blockIdx.x * 8 + warp; u < units; u += (uint64_t)gridDim.x * 8) {
-        const uint64_t b = u * unit;
-        const uint64_t e = min(it.elems, b + (uint64_t)unit);
-        const uint64_t nv = vec ? (e - b) / 8 : 0;                 // whole 8-element vectors of this unit
-        const uint4 *src16 = reinterpret_cast<const uint4 *>(src + b);
-        uint4 keep[2];
-        float amax = 0.f, f[8];
+    // Lanes per unit: a unit of up to 128 elements is 16 vectors, so two units share a warp. Each group of lanes
+    // works on J units per step, all loads issued before the first reduction (latency hiding).
+    const uint32_t W = (vec && unit <= 128) ? 16u : 32u;
+    const uint32_t upw = 32u / W, sub = lane / W, sl = lane % W;
+    constexpr int J = 2;
+    const uint64_t per_cta = 8ull * upw * J;
+    for (uint64_t base = (uint64_t)blockIdx.x * per_cta + (uint64_t)warp * upw * J; base < units; base += (uint64_t)gridDim.x * per_cta) {
+        uint64_t ub[J], ue[J], nv[J];
+        uint4 keep[J][2];
+        float amax[J], f[8];
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const uint64_t v = lane + 32u * i;
-            if (v < nv) {
-                keep[i] = __ldg(src16 + v);
-                unpack8<In>(keep[i], f);
+        for (int j = 0; j < J; j++) {
+            const uint64_t u = base + (uint64_t)j * upw + sub;
+            const bool on = u < units;
+            ub[j] = on ? u * unit : 0;
+            ue[j] = on ? min(it.elems, ub[j] + (uint64_t)unit) : 0;   // off: an empty range, the lanes only take part in the shuffles
+            nv[j] = vec ? (ue[j] - ub[j]) / 8 : 0;                     // whole 8-element vectors of this unit
+            const uint4 *src16 = reinterpret_cast<const uint4 *>(src + ub[j]);
+            amax[j] = 0.f;
 #pragma unroll
-                for (int k = 0; k < 8; k++) amax = fmaxf(amax, fabsf(f[k]));
+            for (int i = 0; i < 2; i++) {
+                const uint64_t v = sl + (uint64_t)W * i;
+                if (v < nv[j]) {
+                    keep[j][i] = __ldg(src16 + v);
+                    unpack8<In>(keep[j][i], f);
+#pragma unroll
+                    for (int k = 0; k < 8; k++) amax[j] = fmaxf(amax[j], fabsf(f[k]));
+                }
             }
+            for (uint64_t v = sl + 2ull * W; v < nv[j]; v += W) {
+                unpack8<In>(__ldg(src16 + v), f);
+#pragma unroll
+                for (int k = 0; k < 8; k++) amax[j] = fmaxf(amax[j], fabsf(f[k]));
+            }
+            for (uint64_t k = ub[j] + nv[j] * 8 + sl; k < ue[j]; k += W) amax[j] = fmaxf(amax[j], fabsf(to_f32<In>(src[k])));
         }
-        for (uint64_t v = lane + 64; v < nv; v += 32) {
-            unpack8<In>(__ldg(src16 + v), f);
 #pragma unroll
-            for (int k = 0; k < 8; k++) amax = fmaxf(amax, fabsf(f[k]));
-        }
-        for (uint64_t k = b + nv * 8 + lane; k < e; k += 32) amax = fmaxf(amax, fabsf(to_f32<In>(src[k])));
+        for (int j = 0; j < J; j++)
+            for (uint32_t o = W / 2; o > 0; o >>= 1) amax[j] = fmaxf(amax[j], __shfl_xor_sync(0xffffffffu, amax[j], o));
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const float mul = amax > 0.f ? qmax / amax : 1.f;
-        if (lane == 0) scales[u] = amax > 0.f ? amax / qmax : 1.f;
-        uint2 *dst8 = reinterpret_cast<uint2 *>(dst + b);
+        for (int j = 0; j < J; j++) {
+            const float mul = amax[j] > 0.f ? qmax / amax[j] : 1.f;
+            if (sl == 0 && ue[j] > ub[j]) scales[ub[j] / unit] = amax[j] > 0.f ? amax[j] / qmax : 1.f;
+            const uint4 *src16 = reinterpret_cast<const uint4 *>(src + ub[j]);
+            uint2 *dst8 = reinterpret_cast<uint2 *>(dst + ub[j]);
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const uint64_t v = lane + 32u * i;
-            if (v < nv) {
-                unpack8<In>(keep[i], f);
+            for (int i = 0; i < 2; i++) {
+                const uint64_t v = sl + (uint64_t)W * i;
+                if (v < nv[j]) {
+                    unpack8<In>(keep[j][i], f);
+                    dst8[v] = quant8<MODE>(f, mul);
+                }
+            }
+            for (uint64_t v = sl + 2ull * W; v < nv[j]; v += W) {
+                unpack8<In>(__ldg(src16 + v), f);
                 dst8[v] = quant8<MODE>(f, mul);
             }
+            for (uint64_t k = ub[j] + nv[j] * 8 + sl; k < ue[j]; k += W) dst[k] = quant1<MODE>(to_f32<In>(src[k]), mul);
         }
-        for (uint64_t v = lane + 64; v < nv; v += 32) {
-            unpack8<In>(__ldg(src16 + v), f);
-            dst8[v] = quant8<MODE>(f, mul);
-        }
-        for (uint64_t k = b + nv * 8 + lane; k < e; k += 32) dst[k] = quant1<MODE>(to_f32<In>(src[k]), mul);
     }
 }
 

@@ -247,7 +247,8 @@ def xcopy_sweep(h, rank, world, flush):
     srcs = [xb.data_ptr() + i * per * 2 for i in range(items)]
     dsts = [q_base + i * per for i in range(items)]
     scs = [s_base + i * (per // 128) * 4 for i in range(items)]
-    q_ms = timed(lambda: h.quant_copy_batch(srcs, dsts, [per * 2] * items, scs, 128, fp8=True, stream=stream))
+    qb = h.prepare_quant_batch(srcs, dsts, [per * 2] * items, scs, 128, fp8=True)
+    q_ms = timed(lambda: h.quant_copy_prepared(qb, stream))
     bu.barrier()
     out.append({"op": "quant_put_fp8_1x128", "bytes_in": items * per * 2, "us": round(q_ms * 1e3, 1),
                 "in_GBps": round(items * per * 2 / q_ms / 1e6, 1), "wire_GBps": round(items * per * (1 + 4 / 128) / q_ms / 1e6, 1)})
