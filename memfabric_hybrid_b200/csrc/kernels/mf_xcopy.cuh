@@ -115,6 +115,15 @@ template <int MODE> __device__ __forceinline__ uint8_t quant1(float x, float mul
 template <int MODE> __device__ __forceinline__ uint2 quant8(const float *f, float mul)
 {
     uint32_t lo = 0, hi = 0;
+    if (MODE == 1) {
+        // two values per conversion instruction (cvt.rn.satfinite.e4m3x2.f32)
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            lo |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f[2 * k] * mul, f[2 * k + 1] * mul), __NV_SATFINITE, __NV_E4M3) << (16 * k);
+            hi |= (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(f[4 + 2 * k] * mul, f[5 + 2 * k] * mul), __NV_SATFINITE, __NV_E4M3) << (16 * k);
+        }
+        return make_uint2(lo, hi);
+    }
 #pragma unroll
     for (int k = 0; k < 4; k++) {
         lo |= (uint32_t)quant1<MODE>(f[k], mul) << (8 * k);
