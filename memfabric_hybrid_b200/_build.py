@@ -41,8 +41,14 @@ def _hash(src: Path, flags: list[str]) -> str:
 
 
 def _compile(cmd: list[str], src: Path, obj: Path, log: Path) -> tuple[Path, int, str]:
-    p = subprocess.run(cmd + ["-c", str(src), "-o", str(obj)], capture_output=True, text=True)
+    # compile to a name of this process and move it into place: a second builder never sees a half-written object
+    tmp = obj.with_name(f"{obj.name}.{os.getpid()}.tmp")
+    p = subprocess.run(cmd + ["-c", str(src), "-o", str(tmp)], capture_output=True, text=True)
     log.write_text(p.stdout + p.stderr)
+    if p.returncode == 0:
+        tmp.replace(obj)
+    elif tmp.exists():
+        tmp.unlink()
     return src, p.returncode, p.stdout + p.stderr
 
 
@@ -84,7 +90,7 @@ def build_host(jobs: int | None = None, asan: bool = False) -> Path:
     objs = _build_objs(srcs, ["g++"], flags, "asan" if asan else "host", jobs)
     libdir.mkdir(exist_ok=True)
     out = libdir / "libmf_smem.so"
-    tmp = out.with_suffix(".so.tmp")
+    tmp = out.with_suffix(f".so.{os.getpid()}.tmp")
     subprocess.run(["g++", "-shared", "-o", str(tmp)] + [str(o) for o in objs] + (SAN_FLAGS if asan else []) +
                    ["-pthread", "-ldl", "-lrt", "-Wl,-z,relro,-z,now"], check=True)
     tmp.replace(out)
@@ -109,7 +115,7 @@ def build_cuda(jobs: int | None = None) -> Path | None:
     objs = _build_objs(srcs, [nvcc], flags, "cuda", jobs)
     LIB.mkdir(exist_ok=True)
     out = LIB / "libmf_cuda.so"
-    tmp = out.with_suffix(".so.tmp")
+    tmp = out.with_suffix(f".so.{os.getpid()}.tmp")
     subprocess.run([nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(tmp)] + [str(o) for o in objs] +
                    ["-cudart", "static", f"-L{LIB}", "-lmf_smem", "-Xlinker", "-rpath=$ORIGIN", "-Xlinker", "-z,relro",
                     "-lpthread", "-ldl", "-lrt"], check=True)
@@ -141,7 +147,7 @@ def build_c10d() -> Path | None:
     LIB.mkdir(exist_ok=True)
     build_host()
     out = LIB / "_zbal_c10d.so"
-    tmp = out.with_suffix(".so.tmp")
+    tmp = out.with_suffix(f".so.{os.getpid()}.tmp")
     tlib = tdir / "lib"
     subprocess.run(["g++", "-shared", "-o", str(tmp)] + [str(o) for o in objs] +
                    [f"-L{tlib}", "-ltorch_python", "-ltorch", "-ltorch_cpu", "-ltorch_cuda", "-lc10", "-lc10_cuda",

@@ -136,8 +136,18 @@ def _ensure_built(which: str) -> None:
         return
     if _LIB_DIR != _PKG / "lib":
         raise RuntimeError(f"{target} is missing (MF_NATIVE_LIB_DIR points at a build that does not exist)")
-    from . import _build
-    (_build.build_host if which == "host" else _build.build_cuda)()
+    # Several ranks of one job may arrive here at the same moment on a fresh checkout: one of them builds, the
+    # others wait on the file lock and find the library in place.
+    import fcntl
+    _LIB_DIR.mkdir(exist_ok=True)
+    with open(_LIB_DIR / ".build.lock", "w") as lk:
+        fcntl.flock(lk, fcntl.LOCK_EX)
+        try:
+            if not target.exists():
+                from . import _build
+                (_build.build_host if which == "host" else _build.build_cuda)()
+        finally:
+            fcntl.flock(lk, fcntl.LOCK_UN)
 
 
 def lib():

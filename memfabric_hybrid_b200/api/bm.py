@@ -92,6 +92,19 @@ def _ptr_array(values: Sequence[int]):
     return (C.c_void_p * len(values))(*[int(v) for v in values])
 
 
+def _u64_view(values, n: int, ctype):
+    """``values`` as a C array of ``n`` 64-bit words plus the object that keeps it alive. A contiguous numpy array of
+    64-bit integers is passed as it is (no copy: the cost of a call on a large descriptor list is then the C call
+    alone); any other sequence is converted once."""
+    import numpy as np
+    a = values if isinstance(values, np.ndarray) else np.asarray(values[:n], dtype=np.uint64)
+    if a.dtype not in (np.uint64, np.int64) or not a.flags["C_CONTIGUOUS"]:
+        a = np.ascontiguousarray(a, dtype=np.uint64)
+    if a.shape[0] < n:
+        raise ValueError(f"batch of {n} items but only {a.shape[0]} values")
+    return a.ctypes.data_as(C.POINTER(ctype)), a
+
+
 class _QuantParamsC(C.Structure):   # hybm_quant_copy_params
     _fields_ = [("sources", C.POINTER(C.c_void_p)), ("destinations", C.POINTER(C.c_void_p)), ("dataSizes", C.POINTER(C.c_uint64)),
                 ("scale", C.POINTER(C.c_void_p)), ("offset", C.POINTER(C.c_void_p)), ("batchSize", C.c_uint32), ("unitNum", C.c_uint32),
@@ -151,12 +164,15 @@ class BigMemory:
 
     def _batch(self, src_addrs, dst_addrs, sizes, count, stream):
         n = int(count)
-        srcs, dsts = _ptr_array(src_addrs[:n]), _ptr_array(dst_addrs[:n])
-        lens = (C.c_uint64 * n)(*[int(s) for s in sizes[:n]])
+        srcs, k0 = _u64_view(src_addrs, n, C.c_void_p)
+        dsts, k1 = _u64_view(dst_addrs, n, C.c_void_p)
+        lens, k2 = _u64_view(sizes, n, C.c_uint64)
         p = N.BatchCopyParamsC(srcs, dsts, lens, n, stream or None)
-        return p, (srcs, dsts, lens)
+        return p, (k0, k1, k2)
 
     def copy_data_batch(self, src_addrs, dst_addrs, sizes, count, type: BmCopyType, flags: int = 0, stream: int = 0) -> int:
+        """``smem_bm_copy_batch``. The three lists may be any sequences of integers; contiguous numpy arrays of
+        uint64 / int64 are handed to the C call without conversion."""
         p, _keep = self._batch(src_addrs, dst_addrs, sizes, count, stream)
         return N.lib().smem_bm_copy_batch(self._h, C.byref(p), int(type), flags)
 

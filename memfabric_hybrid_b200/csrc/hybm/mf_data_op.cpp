@@ -63,6 +63,14 @@ void *ComposeDataOp::StreamFor(void *userStream, uint32_t flags)
     return stream_;
 }
 
+int ComposeDataOp::CheckCopyStatus()
+{
+    if (dev_ == nullptr) return OK;
+    const uint32_t code = dev_->CopyStatus(true);
+    if (code == 0) return OK;
+    return MF_FAIL(ERR_TIMEOUT, "copy kernel gave up a bounded wait (code %#x): the data of that batch is incomplete", code);
+}
+
 int ComposeDataOp::RunHost(const ResolvedCopy &c)
 {
     char *d = reinterpret_cast<char *>(c.dst.addr);
@@ -144,8 +152,14 @@ int ComposeDataOp::RunKernel(const std::vector<const ResolvedCopy *> &items, voi
 {
     int rc = EnsureRing();
     if (rc != OK) return rc;
-    uint64_t total = 0;
-    for (auto *c : items) total += c->len;
+    uint64_t total = 0, alignMask = 0;
+    bool allDevice = true;
+    for (auto *c : items) {
+        total += c->len;
+        alignMask |= c->src.addr | c->dst.addr | c->len;
+        allDevice = allDevice && c->src.kind == EP_DEVICE && c->dst.kind == EP_DEVICE;
+    }
+    const bool bulkOk = allDevice && (alignMask & 15) == 0;
     // Equal work chunks: small enough to fill every SM a few times over, large enough to amortise the
     // descriptor fetch. Multiples of 4 KiB keep the alignment of every chunk equal to that of its item.
     uint64_t sms = std::max(1, dev_->Caps().smCount);
@@ -173,7 +187,7 @@ int ComposeDataOp::RunKernel(const std::vector<const ResolvedCopy *> &items, voi
             }
         }
         if (n == 0) continue;
-        rc = dev_->LaunchBatchCopy(ring_ + first, (uint32_t)n, stream);
+        rc = dev_->LaunchBatchCopy(ring_ + first, (uint32_t)n, stream, bulkOk);
         if (rc != OK) break;
         ringHead_ = first + n;
         if (std::find(ringUsers_.begin(), ringUsers_.end(), stream) == ringUsers_.end()) ringUsers_.push_back(stream);
@@ -278,6 +292,7 @@ int ComposeDataOp::Submit(std::vector<ResolvedCopy> &items, void *userStream, ui
             pending_ = true;
         } else if (dev_ != nullptr) {
             int r = dev_->StreamSync(stream);
+            if (r == OK) r = CheckCopyStatus();
             if (r != OK && firstErr == OK) firstErr = r;
             if (stream == stream_) {
                 ringUsers_.erase(std::remove(ringUsers_.begin(), ringUsers_.end(), stream), ringUsers_.end());
@@ -311,7 +326,7 @@ int KernelBatch::Launch()
 {
     uint64_t n = op_.ringHead_ - first_;
     if (n == 0) return OK;
-    int rc = op_.dev_->LaunchBatchCopy(op_.ring_ + first_, (uint32_t)n, stream_);
+    int rc = op_.dev_->LaunchBatchCopy(op_.ring_ + first_, (uint32_t)n, stream_, (alignMask_ & 15) == 0);
     if (rc != OK) return rc;
     if (std::find(op_.ringUsers_.begin(), op_.ringUsers_.end(), stream_) == op_.ringUsers_.end()) op_.ringUsers_.push_back(stream_);
     op_.stats_.kernelLaunches++;
@@ -343,6 +358,7 @@ int KernelBatch::Finish()
             op_.pending_ = true;
         } else {
             rc = op_.dev_->StreamSync(stream_);
+            if (rc == OK) rc = op_.CheckCopyStatus();
             if (stream_ == op_.stream_) {
                 auto &u = op_.ringUsers_;
                 u.erase(std::remove(u.begin(), u.end(), stream_), u.end());
@@ -398,6 +414,7 @@ int ComposeDataOp::Wait()
     ringUsers_.clear();
     ringHead_ = 0;
     pending_ = false;
+    if (rc == OK) rc = CheckCopyStatus();
     MF_TRACE_END(TP_HYBM_WAIT, rc);
     return rc;
 }

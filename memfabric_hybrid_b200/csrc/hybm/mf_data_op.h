@@ -62,6 +62,7 @@ private:
     int RunKernel(const std::vector<const ResolvedCopy *> &items, void *stream);
     int RunEngine(const ResolvedCopy &c, void *stream);
     int EnsureRing();
+    int CheckCopyStatus();  // ERR_TIMEOUT when a copy kernel reported a wait that ran out since the last check
     void *StreamFor(void *userStream, uint32_t flags);
 
     DeviceBackend *dev_;
@@ -93,9 +94,11 @@ public:
         if (pendLen_ != 0 && pendSrc_ + pendLen_ == src && pendDst_ + pendLen_ == dst) {
             pendLen_ += len;
             op_.stats_.coalesced++;
+            alignMask_ |= len;
             return;
         }
         if (pendLen_ != 0) Emit();
+        alignMask_ |= src | dst | len;
         pendSrc_ = src;
         pendDst_ = dst;
         pendLen_ = len;
@@ -123,6 +126,7 @@ private:
     uint64_t chunk_ = 0;
     uint64_t first_ = 0;
     uint64_t pendSrc_ = 0, pendDst_ = 0, pendLen_ = 0;
+    uint64_t alignMask_ = 0;  // OR of every address and length handed in: low four bits clear = bulk-copy kernel allowed
     int rc_ = OK;
 };
 

@@ -150,7 +150,7 @@ public:
         memset(reinterpret_cast<void *>(dst), value, len);
         return OK;
     }
-    int LaunchBatchCopy(const CopyItem *items, uint32_t count, void *) override
+    int LaunchBatchCopy(const CopyItem *items, uint32_t count, void *, bool) override
     {
         for (uint32_t i = 0; i < count; i++)
             memmove(reinterpret_cast<void *>(items[i].dst), reinterpret_cast<const void *>(items[i].src), items[i].len);

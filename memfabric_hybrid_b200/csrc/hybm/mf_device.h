@@ -101,7 +101,14 @@ public:
     virtual int MemcpyAsync(uint64_t dst, uint64_t src, uint64_t len, MemcpyKind kind, void *stream) = 0;
     virtual int MemsetAsync(uint64_t dst, int value, uint64_t len, void *stream) = 0;
     // items live in pinned, device-visible memory (ring slots) until the stream passes this launch.
-    virtual int LaunchBatchCopy(const CopyItem *items, uint32_t count, void *stream) = 0;
+    // bulkOk: every item has source, destination and length in multiples of 16 bytes and both ends in device
+    // memory, so the backend may move it with the bulk-copy (TMA) variant of the kernel.
+    virtual int LaunchBatchCopy(const CopyItem *items, uint32_t count, void *stream, bool bulkOk = false) = 0;
+    // Code left by a copy kernel whose bounded wait ran out (0: none); `clear` resets it.
+    virtual uint32_t CopyStatus(bool clear) { (void)clear; return 0; }
+    // Shape of the bulk-copy kernel (pipelines per CTA, stages per pipeline, KiB per stage); 0 pipelines
+    // switches it off. Takes effect for the launches that follow.
+    virtual int ConfigureBulkCopy(int pipes, int stages, int pieceKb) { (void)pipes, (void)stages, (void)pieceKb; return -1; }
     // mode 0: int8 with scale = absmax/127 per `unit` elements; mode 1: fp8 e4m3 with scale = absmax/448 per 128.
     virtual int LaunchQuantCopy(const QuantItem *items, uint32_t count, uint32_t unit, int inputFp16, int mode,
                                 void *stream) = 0;

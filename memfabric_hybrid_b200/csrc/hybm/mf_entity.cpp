@@ -470,8 +470,9 @@ bool Entity::InPool(const SegmentPtr &seg, uint64_t addr, uint64_t len, int &err
     uint32_t rank = (uint32_t)(rel / slot);
     if (rank >= opt_.rankCount) return false;
     uint64_t off = rel - (uint64_t)rank * slot;
-    if (off + len > seg->MappedBytes(rank)) {
-        err = seg->MappedBytes(rank) == 0 ? ERR_NOT_CONNECTED : ERR_INVALID_PARAM;
+    const uint64_t mapped = seg->MappedBytes(rank);
+    if (len > mapped || off > mapped - len) {  // written so that a huge len cannot wrap the sum
+        err = mapped == 0 ? ERR_NOT_CONNECTED : ERR_INVALID_PARAM;
         return true;
     }
     err = OK;
@@ -536,7 +537,8 @@ int Entity::BatchCopyData(const hybm_batch_copy_params &p, hybm_data_copy_direct
             if (a < base || a >= end) return false;
             uint64_t rel = a - base;
             uint32_t r = (uint32_t)(rel / slot);
-            return rel - (uint64_t)r * slot + len <= seg->MappedBytes(r);
+            const uint64_t mapped = seg->MappedBytes(r);
+            return len <= mapped && rel - (uint64_t)r * slot <= mapped - len;  // no sum that a huge len could wrap
         };
         uint64_t total = 0;
         for (uint32_t i = 0; i < p.batchSize; i++) {
@@ -585,9 +587,25 @@ int Entity::QuantCopy(const hybm_quant_copy_params &p, int mode)
         p.unitNum == 0 || p.unitNum > 32768)
         return MF_FAIL(ERR_INVALID_PARAM, "quant copy: null array, empty batch or unit %u out of (0, 32768]", p.unitNum);
     std::vector<QuantItem> items(p.batchSize);
+    // An address inside a pool window must lie in a mapped slice for the whole range the kernel touches:
+    // elems * 2 bytes read, elems bytes written, one float per unit written. Addresses outside every
+    // window (the caller's own device buffers) are taken as given, as in the copy paths.
+    auto pooled = [&](uint64_t addr, uint64_t len, const char *what, uint32_t i) -> int {
+        int err = OK;
+        if ((InPool(hbm_, addr, len, err) || InPool(dram_, addr, len, err)) && err != OK)
+            return MF_FAIL(err, "quant copy item %u: %s %#lx (+%lu bytes) %s", i, what, (unsigned long)addr, (unsigned long)len,
+                           err == ERR_NOT_CONNECTED ? "lies in the slice of a rank that is not mapped here" : "runs past the mapped part of the pool");
+        return OK;
+    };
     for (uint32_t i = 0; i < p.batchSize; i++) {
         if (p.sources[i] == nullptr || p.destinations[i] == nullptr || p.scale[i] == nullptr || (p.dataSizes[i] & 1))
             return MF_FAIL(ERR_INVALID_PARAM, "quant copy item %u: null address or odd byte count", i);
+        const uint64_t elems = p.dataSizes[i] / 2;
+        const uint64_t units = (elems + p.unitNum - 1) / p.unitNum;
+        int rc = pooled(reinterpret_cast<uint64_t>(p.sources[i]), p.dataSizes[i], "source", i);
+        if (rc == OK) rc = pooled(reinterpret_cast<uint64_t>(p.destinations[i]), elems, "destination", i);
+        if (rc == OK) rc = pooled(reinterpret_cast<uint64_t>(p.scale[i]), units * sizeof(float), "factor array", i);
+        if (rc != OK) return rc;
         items[i] = QuantItem{reinterpret_cast<uint64_t>(p.sources[i]), reinterpret_cast<uint64_t>(p.destinations[i]),
                              reinterpret_cast<uint64_t>(p.scale[i]), p.dataSizes[i] / 2};
     }

@@ -1128,6 +1128,7 @@ const char *mf_noalloc_strerror(int code)
         case MF_NOALLOC_E_TOO_LARGE: return "vector larger than MF_NOALLOC_MAX_BYTES (1 MiB): the built-in scratch cannot stage it";
         case MF_NOALLOC_E_SETUP: return "could not obtain the device address of the built-in scratch array";
         case MF_NOALLOC_E_LAUNCH: return "kernel launch refused";
+        case MF_NOALLOC_E_TIMEOUT: return "a bounded wait inside an earlier call ran out: that call did not write its output";
         default: return "unknown code";
     }
 }
@@ -1147,17 +1148,13 @@ int mf_allreduce_stacked_noalloc(const void *in, void *out, int world, uint64_t 
         NaDevice &d = g_na_dev[dev];
         if (d.base == nullptr) {
             // first call on this device: resolve the symbol here (its host-side name is not a device
-            // pointer) and start from clean status words and flags
+            // pointer). A file-scope __device__ array is zero when the module is loaded, so the status
+            // words and flags need no clearing, and nothing is queued on any stream but the caller's.
             void *p = nullptr;
             if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) {
                 (void)cudaGetLastError();
                 return MF_NOALLOC_E_SETUP;
             }
-            for (int r = 0; r < MF_NOALLOC_MAX_WORLD; r++)
-                if (cudaMemset(static_cast<unsigned char *>(p) + r * kNaSlot, 0, kSignalBytes) != cudaSuccess) {
-                    (void)cudaGetLastError();
-                    return MF_NOALLOC_E_SETUP;
-                }
             d.base = p;
         }
         base = d.base;
@@ -1187,6 +1184,41 @@ int mf_allreduce_stacked_noalloc(const void *in, void *out, int world, uint64_t 
     const int ctas = n * es <= (32u << 10) ? 1 : (n * es <= (256u << 10) ? 4 : 8);
     int rc = mf_coll_launch(0, dtype, dtype, &a, ctas, 512, stream);
     return rc == 0 ? MF_NOALLOC_OK : MF_NOALLOC_E_LAUNCH;
+}
+
+int mf_noalloc_status(uint32_t out[4], int clear)
+{
+    if (out == nullptr) return MF_NOALLOC_E_ARG;
+    out[0] = out[1] = out[2] = out[3] = 0;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MF_NOALLOC_E_SETUP;
+    void *base;
+    {
+        std::lock_guard<std::mutex> lock(g_na_mu);
+        base = g_na_dev[dev].base;
+    }
+    if (base == nullptr) return MF_NOALLOC_OK;  // no call on this device yet: nothing can have gone wrong
+    for (int r = 0; r < MF_NOALLOC_MAX_WORLD; r++) {
+        uint32_t w[4] = {0, 0, 0, 0};
+        unsigned char *st = static_cast<unsigned char *>(base) + r * kNaSlot + kStatusOff;
+        if (cudaMemcpy(w, st, sizeof(w), cudaMemcpyDeviceToHost) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return MF_NOALLOC_E_SETUP;
+        }
+        if (w[0] != 0) {
+            if (out[0] == 0) {
+                out[0] = w[0];
+                out[1] = w[1];
+                out[2] = w[2];
+            }
+            out[3] += w[3];
+            if (clear && cudaMemset(st, 0, sizeof(w)) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return MF_NOALLOC_E_SETUP;
+            }
+        }
+    }
+    return out[0] == 0 ? MF_NOALLOC_OK : MF_NOALLOC_E_TIMEOUT;
 }
 
 }  // extern "C"

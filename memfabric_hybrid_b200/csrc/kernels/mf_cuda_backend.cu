@@ -133,6 +133,47 @@ public:
                 caps_.granularity = g;
         }
         grid_ = (int)EnvInt("MF_XCOPY_CTAS_PER_SM", nullptr, 2, 1, 4) * caps_.smCount;
+        SetupBulk();
+        return OK;
+    }
+
+    // Shape of the bulk-copy kernel: MF_XCOPY_BULK = "pipelines per CTA, stages, piece KiB" (0 pipelines: use the
+    // register-copy kernel only). As many CTAs per SM as the stage rings leave room for.
+    void SetupBulk()
+    {
+        int pipes = 2, stages = 4, pieceKb = 16;
+        if (const char *e = getenv("MF_XCOPY_BULK")) {
+            if (sscanf(e, "%d,%d,%d", &pipes, &stages, &pieceKb) < 1) pipes = 0;
+        }
+        ConfigureBulkCopy(pipes, stages, pieceKb);
+    }
+    int ConfigureBulkCopy(int pipes, int stages, int pieceKb) override
+    {
+        bulkPipes_ = 0;
+        if (pipes <= 0) return OK;
+        pipes = std::min(pipes, 4);
+        stages = std::min(std::max(stages, 4), mfk::kBulkMaxStages);
+        pieceKb = std::min(std::max(pieceKb, 1), 48);
+        const uint32_t smem = (uint32_t)pipes * stages * pieceKb * 1024u;
+        if (smem > 220u * 1024u) return ERR_INVALID_PARAM;
+        if (cudaFuncSetAttribute(mfk::mf_xcopy_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return ERR_NO_RESOURCES;
+        }
+        if (copyStatus_ == nullptr) {
+            void *st = nullptr;
+            if (cudaHostAlloc(&st, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return ERR_MALLOC;
+            }
+            memset(st, 0, 64);
+            copyStatus_ = static_cast<uint32_t *>(st);
+        }
+        bulkStages_ = (uint32_t)stages;
+        bulkPiece_ = (uint32_t)pieceKb * 1024u;
+        const int perSm = std::max(1, std::min(8, (int)((227u * 1024u) / (smem + 1024u))));
+        bulkGrid_ = perSm * caps_.smCount;
+        bulkPipes_ = (uint32_t)pipes;
         return OK;
     }
 
@@ -411,14 +452,29 @@ public:
         RT_CHECK(cudaMemsetAsync((void *)dst, value, len, (cudaStream_t)s), "cudaMemsetAsync");
         return OK;
     }
-    int LaunchBatchCopy(const CopyItem *items, uint32_t count, void *s) override
+    int LaunchBatchCopy(const CopyItem *items, uint32_t count, void *s, bool bulkOk) override
     {
         if (count == 0) return OK;
         static_assert(sizeof(CopyItem) == sizeof(mfk::CopyItem), "descriptor layout");
+        if (bulkOk && bulkPipes_ > 0 && copyStatus_ != nullptr) {
+            const uint32_t smem = bulkPipes_ * bulkStages_ * bulkPiece_;
+            const uint32_t grid = std::min<uint32_t>((count + bulkPipes_ - 1) / bulkPipes_, (uint32_t)bulkGrid_);
+            mfk::mf_xcopy_bulk_kernel<<<grid, 32 * bulkPipes_, smem, (cudaStream_t)s>>>(reinterpret_cast<const mfk::CopyItem *>(items), count,
+                                                                                      bulkStages_, bulkPiece_, copyStatus_);
+            RT_CHECK(cudaGetLastError(), "xcopy bulk launch");
+            return OK;
+        }
         int grid = (int)std::min<uint32_t>(count, (uint32_t)grid_);
         mfk::mf_xcopy_batch_kernel<<<grid, mfk::kCopyThreads, 0, (cudaStream_t)s>>>(reinterpret_cast<const mfk::CopyItem *>(items), count);
         RT_CHECK(cudaGetLastError(), "xcopy batch launch");
         return OK;
+    }
+    uint32_t CopyStatus(bool clear) override
+    {
+        if (copyStatus_ == nullptr) return 0;
+        const uint32_t v = *reinterpret_cast<volatile uint32_t *>(copyStatus_);
+        if (clear && v != 0) *reinterpret_cast<volatile uint32_t *>(copyStatus_) = 0;
+        return v;
     }
     int LaunchQuantCopy(const QuantItem *items, uint32_t count, uint32_t unit, int inputFp16, int mode, void *s) override
     {
@@ -464,6 +520,9 @@ private:
     };
     int dev_ = 0;
     int grid_ = 296;
+    uint32_t bulkPipes_ = 0, bulkStages_ = 4, bulkPiece_ = 16384;
+    int bulkGrid_ = 148;
+    uint32_t *copyStatus_ = nullptr;
     DeviceCaps caps_;
     DriverApi drv_;
     std::mutex mu_;

@@ -85,6 +85,109 @@ __global__ void __launch_bounds__(kCopyThreads) mf_xcopy_batch_kernel(const Copy
     }
 }
 
+// ---- bulk-copy engine variant ---------------------------------------------------------------------
+// The same descriptor list, moved by the TMA unit instead of by registers: one lane per pipeline issues
+// `cp.async.bulk` loads of `piece` bytes from the source into a ring of shared-memory stages and, as each
+// lands (mbarrier), a `cp.async.bulk` store from that stage to the destination. No multicast; source and
+// destination may be local HBM or a peer's mapped HBM. A pipeline keeps (stages - 2) loads and up to two
+// stores in flight and runs on across chunk boundaries, so neither a CTA barrier nor a drain separates
+// two items. Needs every chunk's source, destination and length to be multiples of 16 bytes (the host
+// checks that and otherwise launches mf_xcopy_batch_kernel).
+// A wait that runs out stores its code into *status (pinned host memory) and the pipeline stops after
+// the copies it has in flight.
+constexpr uint64_t kBulkWaitNs = 2000000000ull;  // a load that has not landed after 2 s is given up
+constexpr int kBulkMaxStages = 8;
+
+__device__ __forceinline__ uint32_t xc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__global__ void __launch_bounds__(128) mf_xcopy_bulk_kernel(const CopyItem *__restrict__ items, uint32_t count, uint32_t stages,
+                                                            uint32_t piece, uint32_t *status)
+{
+    extern __shared__ __align__(128) uint8_t xc_smem[];
+    __shared__ __align__(8) uint64_t full[4][kBulkMaxStages];
+    __shared__ uint64_t st_dst[4][kBulkMaxStages];
+    __shared__ uint32_t st_len[4][kBulkMaxStages];
+    if ((threadIdx.x & 31) != 0) return;
+    const uint32_t w = threadIdx.x >> 5, W = blockDim.x >> 5;
+    const uint32_t pipe = blockIdx.x * W + w, pipes = gridDim.x * W;
+    if (pipe >= count) return;
+    uint8_t *ring = xc_smem + (size_t)w * stages * piece;
+    for (uint32_t s = 0; s < stages; s++)
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(xc_smem_u32(&full[w][s])));
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the initialised barriers as the copy unit sees them
+
+    const uint32_t look = stages - 2;  // loads issued ahead of the store front
+    uint32_t ci = pipe;                // chunk whose pieces are being loaded
+    CopyItem cur = items[ci];
+    CopyItem nxt = ci + pipes < count ? items[ci + pipes] : CopyItem{0, 0, 0};
+    uint64_t off = 0;
+    bool more = true, fine = true;
+    uint32_t loaded = 0, stored = 0;
+    while (fine && (more || stored < loaded)) {
+        if (more) {
+            const uint32_t s = loaded % stages;
+            // the store that last read this stage is at least two store groups back
+            asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            const uint64_t left = cur.len - off;
+            const uint32_t n = left < piece ? (uint32_t)left : piece;
+            const uint32_t bar = xc_smem_u32(&full[w][s]);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(n) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                             xc_smem_u32(ring + (size_t)s * piece)),
+                         "l"(cur.src + off), "r"(n), "r"(bar)
+                         : "memory");
+            st_dst[w][s] = cur.dst + off;
+            st_len[w][s] = n;
+            loaded++;
+            off += n;
+            if (off >= cur.len) {
+                ci += pipes;
+                if (ci < count) {
+                    cur = nxt;
+                    off = 0;
+                    if (ci + pipes < count) nxt = items[ci + pipes];
+                } else {
+                    more = false;
+                }
+            }
+        }
+        if (loaded >= stored + look + 1 || (!more && stored < loaded)) {
+            const uint32_t s = stored % stages, parity = (stored / stages) & 1;
+            const uint32_t bar = xc_smem_u32(&full[w][s]);
+            uint32_t ok = 0;
+            uint64_t t0 = 0;
+            for (uint32_t spin = 0; !ok; spin++) {
+                asm volatile(
+                    "{\n\t.reg .pred P;\n\t"
+                    "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+                    "selp.b32 %0, 1, 0, P;\n\t}"
+                    : "=r"(ok)
+                    : "r"(bar), "r"(parity)
+                    : "memory");
+                if (!ok && (spin & 255u) == 255u) {  // time limit, not an iteration count: a try_wait may suspend for a while
+                    uint64_t now;
+                    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+                    if (t0 == 0) t0 = now;
+                    else if (now - t0 > kBulkWaitNs) break;
+                }
+            }
+            if (!ok) {
+                *reinterpret_cast<volatile uint32_t *>(status) = 0x701u;
+                __threadfence_system();
+                fine = false;
+                break;
+            }
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(st_dst[w][s]),
+                         "r"(xc_smem_u32(ring + (size_t)s * piece)), "r"(st_len[w][s])
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            stored++;
+        }
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 // One WARP per (item, unit); a CTA of 8 warps walks the units of its item. The unit is read once when it fits in
 // the lanes' registers (unit <= 512 elements with 16-byte loads), else twice (the second pass hits L1 / L2):
 // absolute maximum by warp shuffles, then scale + round + 8-byte stores to the (peer) destination.

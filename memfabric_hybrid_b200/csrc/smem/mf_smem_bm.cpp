@@ -337,4 +337,14 @@ int32_t mf_bm_copy_stats(smem_bm_t handle, uint64_t out[6])
     return SMEM_OK;
 }
 
+// Extension: shape of the bulk-copy (TMA) variant of the xcopy kernel for the launches that follow:
+// pipelines per CTA (0: register-copy kernel only), stages per pipeline (>= 4), KiB per stage.
+int32_t mf_xcopy_bulk_config(int pipes, int stages, int pieceKb)
+{
+    auto *dev = mf::hybm::CurrentBackend();
+    if (dev == nullptr) return SMEM_NOT_INIT;
+    dev->BindThread();
+    return dev->ConfigureBulkCopy(pipes, stages, pieceKb) == 0 ? SMEM_OK : SMEM_INVALID_PARAM;
+}
+
 }  // extern "C"

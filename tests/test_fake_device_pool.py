@@ -70,6 +70,13 @@ def _rank(rank, world, url, sync):
         assert (1, 1) in events, events
         assert h.copy_data(src.ctypes.data, pdev, 4096, bm.BmCopyType.H2G, 0) != 0
         mf.get_and_clear_last_err_msg()
+        # the quantising copy checks its pooled addresses like every other copy: the slice of the rank that left is
+        # refused as "not connected" instead of being handed to the kernel
+        import torch
+        row = torch.randn(128).to(torch.bfloat16)
+        rc = h.quant_copy_batch([row.data_ptr()], [pdev], [256], [pdev + MiB], 64)
+        assert rc == -2014, rc
+        assert "not mapped" in mf.get_and_clear_last_err_msg()
         assert h.leave() == 0
     sync.wait(60)  # whichever process hosts the config store must not tear it down while the other still leaves
     h.destroy()
@@ -118,6 +125,18 @@ def _quant_rank(rank, world, url):
             assert abs(s[i, u] - am / 127.0) < 1e-6
             assert np.abs(q[i, u * unit:u * unit + len(seg)] - np.rint(seg * np.float32(127.0 / am))).max() <= 1
     assert not q[:, cols:].any()                                      # nothing written past the row
+    # a destination or a factor array that runs past the mapped slice is refused before anything is launched
+    assert h.quant_copy_batch([x[0].data_ptr()], [base + 8 * MiB - 64], [cols * 2], [s_at], unit) == -2000
+    assert "runs past" in mf.get_and_clear_last_err_msg()
+    assert h.quant_copy_batch([x[0].data_ptr()], [q_at], [cols * 2], [base + 8 * MiB - 8], unit) == -2000
+    mf.get_and_clear_last_err_msg()
+    # a length that would wrap the range check is refused too
+    probe = np.zeros(16, dtype=np.uint8)
+    assert h.copy_data(base, probe.ctypes.data, (1 << 64) - 8, bm.BmCopyType.G2H, 0) != 0
+    mf.get_and_clear_last_err_msg()
+    rc, res = h.copy_data_batch_partial_succeed([base], [probe.ctypes.data], [(1 << 64) - 8], 1, bm.BmCopyType.G2H, 0)
+    assert rc != 0 and res[0] != 0
+    mf.get_and_clear_last_err_msg()
     # the fp8 format needs the device: refused by the host oracle, with a message
     assert h.quant_copy_batch([x[0].data_ptr()], [q_at], [128 * 2], [s_at], 128, fp8=True) != 0
     mf.get_and_clear_last_err_msg()
