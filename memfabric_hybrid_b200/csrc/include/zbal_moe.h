@@ -77,11 +77,14 @@ int32_t zbal_dispatch_low_latency(zbal_moe_t moe, const void *x, int64_t tokens,
 int32_t zbal_combine_low_latency(zbal_moe_t moe, const void *expandX, int64_t ld, const int32_t *rowsDev, int32_t weighted,
                                  const int32_t *topkIndex, const float *homeWeights, int64_t tokens, void *xOut, zbal_stream_t stream);
 
-/* dispatch + GEMM1 (gate/up, SwiGLU) + requantisation + GEMM2 with the weighted push home in its epilogue + slot
- * reduce. gmm1Weight [localExperts, 2 * inter, hidden] fp8 with gate/up rows interleaved per 64, gmm1Scale
- * [localExperts, 2 * inter / 128, hidden / 128]; gmm2Weight [localExperts, hidden, inter], gmm2Scale [.., hidden / 128,
- * inter / 128]. workspace: device memory of zbal_fused_deep_moe_workspace(moe, inter) bytes. */
+/* dispatch + GEMM1 (gate/up, SwiGLU, requantisation to fp8) + GEMM2 with the weighted push home in its epilogue + slot
+ * reduce. gmm1Weight [localExperts, 2 * inter, hidden] fp8 with gate/up rows interleaved per
+ * zbal_fused_deep_moe_gate_up_tile() rows (128 when hidden is a multiple of 256: the block-scaled tensor-core kernel;
+ * else 64), gmm1Scale [localExperts, 2 * inter / 128, hidden / 128]; gmm2Weight [localExperts, hidden, inter], gmm2Scale
+ * [.., hidden / 128, inter / 128]. Every scale is a power of two (the smallest with amax / scale <= 448).
+ * workspace: device memory of zbal_fused_deep_moe_workspace(moe, inter) bytes. */
 uint64_t zbal_fused_deep_moe_workspace(zbal_moe_t moe, uint32_t inter);
+int32_t zbal_fused_deep_moe_gate_up_tile(zbal_moe_t moe, uint32_t inter);
 int32_t zbal_fused_deep_moe(zbal_moe_t moe, const void *x, int64_t tokens, const int32_t *topkIndex, const float *topkWeights,
                             const void *gmm1Weight, const float *gmm1Scale, const void *gmm2Weight, const float *gmm2Scale, uint32_t inter,
                             void *workspace, void *xOut, zbal_stream_t stream);

@@ -17,6 +17,7 @@
 #include <cuda_fp8.h>
 
 #include "mf_devtrace.cuh"
+#include "mf_fp8.cuh"
 #include "mf_team.cuh"
 
 namespace mfk {
@@ -244,8 +245,8 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs &a, uint4 nxt_l
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-            const float mul = amax > 0.f ? 448.f / amax : 1.f;
-            scale = amax > 0.f ? amax / 448.f : 1.f;
+            scale = pow2_scale_e4m3(amax);   // a power of two: the expert GEMM feeds it to the tensor core as a UE8M0 byte
+            const float mul = 1.f / scale;
             uint32_t w[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
@@ -336,7 +337,7 @@ __global__ void __launch_bounds__(256) k_moe_combine_reduce(Team t, MoeHeap hp, 
     combine_reduce_body(t, hp, sh, topk_idx, out, nullptr);
 }
 
-// Rows of bf16 -> fp8 e4m3 with one scale per 128 elements (the activation format of the expert GEMMs).
+// Rows of bf16 -> fp8 e4m3 with one power-of-two scale per 128 elements (the activation format of the expert GEMMs).
 // rows_dev: device int with the number of valid rows (the receive count), read here so the host never waits.
 __global__ void __launch_bounds__(256) k_quant_rows_fp8(const __nv_bfloat16 *__restrict__ x, int64_t ldx, const int *rows_dev, int cols,
                                                         uint8_t *__restrict__ q, float *__restrict__ scales)
@@ -354,13 +355,14 @@ __global__ void __launch_bounds__(256) k_quant_rows_fp8(const __nv_bfloat16 *__r
         float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const float mul = amax > 0.f ? 448.f / amax : 1.f;
+        const float scale = pow2_scale_e4m3(amax);
+        const float mul = 1.f / scale;
         uint32_t w = (uint32_t)__nv_cvt_float_to_fp8(a.x * mul, __NV_SATFINITE, __NV_E4M3) |
                      (uint32_t)__nv_cvt_float_to_fp8(a.y * mul, __NV_SATFINITE, __NV_E4M3) << 8 |
                      (uint32_t)__nv_cvt_float_to_fp8(b.x * mul, __NV_SATFINITE, __NV_E4M3) << 16 |
                      (uint32_t)__nv_cvt_float_to_fp8(b.y * mul, __NV_SATFINITE, __NV_E4M3) << 24;
         reinterpret_cast<uint32_t *>(q + r * cols + gi * kQuantGroup)[lane] = w;
-        if (lane == 0) scales[r * groups + gi] = amax > 0.f ? amax / 448.f : 1.f;
+        if (lane == 0) scales[r * groups + gi] = scale;
     }
 }
 

@@ -153,6 +153,40 @@ __device__ __forceinline__ void umma_fp8(uint32_t tmem_d, uint64_t desc_a, uint6
         : "memory");
 }
 
+// ---- block-scaled fp8 (kind::mxf8f6f4): D += (A * 2^(sfa - 127)) . (B * 2^(sfb - 127))^T, one UE8M0 scale byte
+// per operand row per 32 elements of K, read by the tensor core from TMEM ---------------------------------
+// Instruction descriptor of the block-scaled kind: e4m3 x e4m3, K-major, scale format E8M0; sf ids pick the
+// byte (0..3) of each row's 32-bit scale word that this K step uses.
+__host__ __device__ constexpr uint32_t umma_idesc_bs(uint32_t M, uint32_t N, uint32_t a_sf_id, uint32_t b_sf_id)
+{
+    return (b_sf_id << 4) | ((N >> 3) << 17) | (1u << 23) | ((M >> 4) << 24) | (a_sf_id << 29);
+}
+__device__ __forceinline__ void umma_fp8_bs(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate,
+                                            uint32_t tmem_sfa, uint32_t tmem_sfb)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+// Shared-memory descriptor of one scale chunk: 128 rows x 4 scale bytes laid out as 32 rows of 16 bytes
+// (byte (r % 32) * 16 + (r / 32) * 4 + k), no swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_sf(const void *smem_chunk)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_u32(smem_chunk) & 0x3FFFF) >> 4);
+    d |= (uint64_t)(128 >> 4) << 32;  // stride byte offset
+    d |= (uint64_t)1 << 46;           // descriptor version
+    return d;
+}
+// Copies one scale chunk (32 x 128 bits) into 4 TMEM columns, replicated over the four lane quadrants.
+__device__ __forceinline__ void tmem_cp_sf(uint32_t tmem_col, uint64_t desc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_col), "l"(desc) : "memory");
+}
+
 // 32 lanes x 32 consecutive 32-bit columns -> 32 registers per thread (thread i holds lane i of the
 // warp's quadrant). taddr = (lane << 16) | column.
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])

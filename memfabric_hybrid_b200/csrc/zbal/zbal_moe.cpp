@@ -55,6 +55,9 @@ struct MoeLaunchers {
     int (*quantRows)(const void *, int64_t, const int *, int, void *, float *, int, void *) = nullptr;
     int (*groupedGemm)(const void *, const float *, int, const void *, const float *, const int *, int, int, int, void *, int64_t, int,
                        const MfTeam *, const void *, uint64_t, int, int *, int, void *) = nullptr;
+    int (*groupedGemmMx)(const void *, const float *, int, const void *, const float *, const int *, int, int, int, void *, int64_t, float *, int,
+                         const MfTeam *, const void *, uint64_t, int, int *, int, void *) = nullptr;
+    int (*mxSupported)(int, int, int, int) = nullptr;
     int (*smCount)() = nullptr;
     bool ok = false;
 };
@@ -77,6 +80,8 @@ const MoeLaunchers *Moe()
         SYM(llCombine, "mf_moe_ll_combine");
         SYM(quantRows, "mf_quant_rows_fp8");
         SYM(groupedGemm, "mf_grouped_gemm_fp8");
+        SYM(groupedGemmMx, "mf_grouped_gemm_fp8_mx");
+        SYM(mxSupported, "mf_grouped_gemm_fp8_mx_supported");
         SYM(smCount, "mf_cuda_sm_count");
 #undef SYM
         l.ok = l.layout && l.notify && l.dispatch && l.waitAll && l.signalAll && l.combineReduce && l.combinePush && l.llDispatch &&
@@ -352,6 +357,16 @@ uint64_t zbal_fused_deep_moe_workspace(zbal_moe_t moe, uint32_t inter)
            R * inter * 2 + R * inter + R * (inter / 128) * 4 + 3 * 256;
 }
 
+int32_t zbal_fused_deep_moe_gate_up_tile(zbal_moe_t moe, uint32_t inter)
+{
+    MoeCtx *c = Find(moe);
+    const MoeLaunchers *L = Moe();
+    if (c == nullptr || L == nullptr || inter == 0 || inter % 128 != 0) return 0;
+    const bool mx = L->groupedGemmMx != nullptr && L->mxSupported != nullptr && L->mxSupported((int)c->El, (int)(2 * inter), c->sh.H, 3) != 0 &&
+                    L->mxSupported((int)c->El, c->sh.H, (int)inter, 2) != 0;
+    return mx ? 128 : 64;
+}
+
 int32_t zbal_fused_deep_moe(zbal_moe_t moe, const void *x, int64_t tokens, const int32_t *topkIndex, const float *topkWeights, const void *gmm1Weight,
                             const float *gmm1Scale, const void *gmm2Weight, const float *gmm2Scale, uint32_t inter, void *workspace, void *xOut,
                             zbal_stream_t stream)
@@ -391,12 +406,21 @@ int32_t zbal_fused_deep_moe(zbal_moe_t moe, const void *x, int64_t tokens, const
     const void *recvX = reinterpret_cast<const void *>(c->slotBase + c->hp.recv_x);
     const float *recvS = reinterpret_cast<const float *>(c->slotBase + c->hp.recv_scale);
     const void *recvInfo = reinterpret_cast<const void *>(c->slotBase + c->hp.recv_info);
-    rc = Launched(L->groupedGemm(recvX, recvS, (int)R, gmm1Weight, gmm1Scale, rowOff, (int)El, (int)(2 * inter), c->sh.H, h, inter, 1, nullptr, nullptr, 0,
-                                 c->sh.K, c->status, c->grid, stream), "grouped GEMM (gate/up)");
-    if (rc == Z_OK) rc = Launched(L->quantRows(h, inter, rowOff + El, (int)inter, hq, hs, c->grid * 4, stream), "requantisation");
-    if (rc == Z_OK)
-        rc = Launched(L->groupedGemm(hq, hs, (int)R, gmm2Weight, gmm2Scale, rowOff, (int)El, c->sh.H, (int)inter, nullptr, 0, 2, &c->comm->team, recvInfo,
-                                     c->hp.comb, c->sh.K, c->status, c->grid, stream), "grouped GEMM (down + combine)");
+    if (zbal_fused_deep_moe_gate_up_tile(moe, inter) == 128) {
+        // block-scaled tensor-core path: SwiGLU and the re-quantisation to fp8 are the first GEMM's epilogue
+        rc = Launched(L->groupedGemmMx(recvX, recvS, (int)R, gmm1Weight, gmm1Scale, rowOff, (int)El, (int)(2 * inter), c->sh.H, hq, inter, hs, 3, nullptr,
+                                       nullptr, 0, c->sh.K, c->status, c->grid, stream), "grouped GEMM (gate/up + requantisation)");
+        if (rc == Z_OK)
+            rc = Launched(L->groupedGemmMx(hq, hs, (int)R, gmm2Weight, gmm2Scale, rowOff, (int)El, c->sh.H, (int)inter, nullptr, 0, nullptr, 2, &c->comm->team,
+                                           recvInfo, c->hp.comb, c->sh.K, c->status, c->grid, stream), "grouped GEMM (down + combine)");
+    } else {
+        rc = Launched(L->groupedGemm(recvX, recvS, (int)R, gmm1Weight, gmm1Scale, rowOff, (int)El, (int)(2 * inter), c->sh.H, h, inter, 1, nullptr, nullptr, 0,
+                                     c->sh.K, c->status, c->grid, stream), "grouped GEMM (gate/up)");
+        if (rc == Z_OK) rc = Launched(L->quantRows(h, inter, rowOff + El, (int)inter, hq, hs, c->grid * 4, stream), "requantisation");
+        if (rc == Z_OK)
+            rc = Launched(L->groupedGemm(hq, hs, (int)R, gmm2Weight, gmm2Scale, rowOff, (int)El, c->sh.H, (int)inter, nullptr, 0, 2, &c->comm->team, recvInfo,
+                                         c->hp.comb, c->sh.K, c->status, c->grid, stream), "grouped GEMM (down + combine)");
+    }
     if (rc == Z_OK) rc = Launched(L->signalAll(&c->comm->team, &c->hp, 1, c->epoch, stream), "combine signal");
     if (rc == Z_OK) rc = Launched(L->waitAll(&c->comm->team, &c->hp, 1, c->epoch, c->status, stream), "combine wait");
     if (rc != Z_OK) return rc;

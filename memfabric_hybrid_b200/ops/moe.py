@@ -67,6 +67,10 @@ def _cu():
         l.mf_quant_rows_fp8.argtypes = [vp, C.c_int64, vp, ci, vp, vp, ci, vp]
         l.mf_grouped_gemm_fp8.restype = ci
         l.mf_grouped_gemm_fp8.argtypes = [vp, vp, ci, vp, vp, vp, ci, ci, ci, vp, C.c_int64, ci, P(TeamC), vp, C.c_uint64, ci, vp, ci, vp]
+        l.mf_grouped_gemm_fp8_mx.restype = ci
+        l.mf_grouped_gemm_fp8_mx.argtypes = [vp, vp, ci, vp, vp, vp, ci, ci, ci, vp, C.c_int64, vp, ci, P(TeamC), vp, C.c_uint64, ci, vp, ci, vp]
+        l.mf_grouped_gemm_fp8_mx_supported.restype = ci
+        l.mf_grouped_gemm_fp8_mx_supported.argtypes = [ci, ci, ci, ci]
         _lib = l
     return _lib
 
@@ -81,20 +85,37 @@ def _ok(rc: int, what: str) -> None:
 
 
 def quantize_weight_fp8(w: torch.Tensor):
-    """[..., N, K] bf16/fp32 -> (fp8 e4m3 [..., N, K], fp32 scales [..., N/128, K/128]); 128 x 128 blocks."""
+    """[..., N, K] bf16/fp32 -> (fp8 e4m3 [..., N, K], fp32 scales [..., N/128, K/128]); 128 x 128 blocks.
+    Every scale is a power of two (the smallest with amax / scale <= 448): the block-scaled tensor-core MMA takes
+    such a scale as one UE8M0 byte, and the activation quantisers of this library produce the same kind."""
     *lead, Nn, K = w.shape
     assert Nn % 128 == 0 and K % 128 == 0
     blk = w.float().reshape(*lead, Nn // 128, 128, K // 128, 128)
-    amax = blk.abs().amax(dim=(-3, -1), keepdim=True).clamp_min(1e-12)
-    scale = amax / 448.0
+    amax = blk.abs().amax(dim=(-3, -1), keepdim=True).clamp_min(1e-30)
+    scale = torch.exp2(torch.ceil(torch.log2(amax / 448.0))).clamp_min(2.0 ** -126)
     q = (blk / scale).clamp(-448, 448).to(torch.float8_e4m3fn).reshape(*lead, Nn, K)
     return q.contiguous(), scale.reshape(*lead, Nn // 128, K // 128).contiguous()
 
 
-def interleave_gate_up_fp8(w1q: torch.Tensor, tile: int = 64) -> torch.Tensor:
-    """[G, 2I, K] (gate rows then up rows) -> per 128 rows: 64 gate rows followed by their 64 up rows."""
+def gate_up_tile(experts: int, intermediate: int, hidden: int) -> int:
+    """Rows per gate / up run that ``expert_ffn`` expects in the first GEMM's weights: 128 when the 128 x 256
+    block-scaled kernel takes the layer's shapes, else 64 (the 128 x 128 kernel that applies the scales in registers)."""
+    try:
+        cu = _cu()
+    except (RuntimeError, OSError):
+        return 128
+    ok = cu.mf_grouped_gemm_fp8_mx_supported(experts, 2 * intermediate, hidden, 3) and \
+        cu.mf_grouped_gemm_fp8_mx_supported(experts, hidden, intermediate, 2)
+    return 128 if ok else 64
+
+
+def interleave_gate_up_fp8(w1q: torch.Tensor, tile: int | None = None) -> torch.Tensor:
+    """[G, 2I, K] (gate rows then up rows) -> per 2 x tile rows: tile gate rows followed by their tile up rows.
+    ``tile`` defaults to what ``expert_ffn`` expects for these shapes (``gate_up_tile``)."""
     G, two_i, K = w1q.shape
     i = two_i // 2
+    if tile is None:
+        tile = gate_up_tile(G, i, K)
     assert i % tile == 0
     gate = w1q[:, :i].reshape(G, i // tile, tile, K)
     up = w1q[:, i:].reshape(G, i // tile, tile, K)
@@ -203,13 +224,29 @@ class MoEComm:
         El, two_i, H = w1q.shape
         I = two_i // 2
         assert El == self.El and H == self.H and w2q.shape == (El, H, I)
-        if self._h is None or self._h.shape[1] != I:
-            self._h = torch.empty((self.max_recv, I), dtype=torch.bfloat16, device=self.dev)
+        if self._hq is None or self._hq.shape[1] != I:
+            self._h = None
             self._hq = torch.empty((self.max_recv, I), dtype=torch.uint8, device=self.dev)
             self._hs = torch.empty((self.max_recv, I // 128), dtype=torch.float32, device=self.dev)
         team = self.heap.team()
         stw = status_word(self.dev).data_ptr()
         cu = _cu()
+        if cu.mf_grouped_gemm_fp8_mx_supported(El, two_i, H, 3) and cu.mf_grouped_gemm_fp8_mx_supported(El, H, I, 2):
+            # two launches: gate/up + SwiGLU + re-quantisation to fp8 in the first GEMM's epilogue, down projection +
+            # weighted push to the tokens' home ranks in the second's; w1q interleaved with tile 128
+            _ok(cu.mf_grouped_gemm_fp8_mx(self.heap.ptr(self.rank, self.hp.recv_x), self.heap.ptr(self.rank, self.hp.recv_scale), self.max_recv,
+                                          w1q.data_ptr(), w1s.data_ptr(), st.row_off.data_ptr(), El, two_i, H, self._hq.data_ptr(), I,
+                                          self._hs.data_ptr(), 3, None, None, 0, self.K, stw, self._grid, _s()), "grouped_gemm_fp8_mx (gate/up)")
+            _ok(cu.mf_grouped_gemm_fp8_mx(self._hq.data_ptr(), self._hs.data_ptr(), self.max_recv, w2q.data_ptr(), w2s.data_ptr(),
+                                          st.row_off.data_ptr(), El, H, I, None, 0, None, 2, C.byref(team),
+                                          self.heap.ptr(self.rank, self.hp.recv_info), self.hp.comb, self.K, stw, self._grid, _s()),
+                "grouped_gemm_fp8_mx (down+combine)")
+            _ok(cu.mf_moe_signal_all(C.byref(team), C.byref(self.hp), 1, st.epoch, _s()), "moe_signal")
+            return
+        # shapes the 128 x 256 kernel does not take (N not a multiple of 256): the 128 x 128 kernel that applies the
+        # scales in registers, with w1q interleaved with tile 64 and a separate re-quantisation pass
+        if self._h is None:
+            self._h = torch.empty((self.max_recv, I), dtype=torch.bfloat16, device=self.dev)
         _ok(cu.mf_grouped_gemm_fp8(self.heap.ptr(self.rank, self.hp.recv_x), self.heap.ptr(self.rank, self.hp.recv_scale), self.max_recv,
                                    w1q.data_ptr(), w1s.data_ptr(), st.row_off.data_ptr(), El, two_i, H, self._h.data_ptr(), I, 1, None, None,
                                    0, self.K, stw, self._grid, _s()), "grouped_gemm_fp8 (gate/up)")

@@ -47,7 +47,7 @@ def test_grouped_gemm_fp8_plain_and_swiglu():
     ref = torch.cat([xd[off[g]:off[g + 1]] @ wd[g].t() for g in range(G)])
     assert (out.float() - ref).abs().max() <= 2e-2 * ref.abs().max() + 1e-3
     # SwiGLU: B rows are [gate (N/2) | up (N/2)]; the kernel takes the tile-interleaved copy
-    wi = M.interleave_gate_up_fp8(wq)
+    wi = M.interleave_gate_up_fp8(wq, tile=64)   # the 128 x 128 kernel pairs 64 gate rows with 64 up rows
     out2 = torch.zeros(R, N // 2, dtype=torch.bfloat16, device="cuda")
     rc = cu.mf_grouped_gemm_fp8(xq.data_ptr(), xs.data_ptr(), R, wi.data_ptr(), ws.data_ptr(), off.data_ptr(), G, N, K, out2.data_ptr(), N // 2,
                                 1, None, None, 0, 1, st.data_ptr(), gemm.sm_count(), torch.cuda.current_stream().cuda_stream)
@@ -56,6 +56,66 @@ def test_grouped_gemm_fp8_plain_and_swiglu():
     gemm.check_status()
     ref2 = torch.nn.functional.silu(ref[:, :N // 2]) * ref[:, N // 2:]
     assert (out2.float() - ref2).abs().max() <= 3e-2 * ref2.abs().max() + 1e-3
+
+
+@pytest.mark.parametrize("G,N,K,counts", [(4, 256, 512, [130, 0, 7, 300]), (3, 512, 768, [1, 257, 128]), (2, 1024, 2048, [640, 513])])
+def test_grouped_gemm_fp8_block_scaled(G, N, K, counts):
+    """The 128 x 256 kernel whose scales are applied by the tensor core (UE8M0 bytes in TMEM): plain, SwiGLU, and
+    SwiGLU + re-quantisation epilogues against fp32 references on the dequantised operands. K = 768 has a partial
+    group of K blocks (6 = 4 + 2)."""
+    from memfabric_hybrid_b200.ops import gemm, moe as M
+    cu = M._cu()
+    torch.manual_seed(G * N + K)
+    s = torch.cuda.current_stream().cuda_stream
+    off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device="cuda")
+    R = sum(counts)
+    # rows of very different magnitude, so that a wrong scale byte or a wrong row shows
+    x = (torch.randn(R, K, device="cuda") * torch.logspace(-2, 2, R, device="cuda")[:, None]).to(torch.bfloat16)
+    xq = torch.empty(R, K, dtype=torch.uint8, device="cuda")
+    xs = torch.empty(R, K // 128, dtype=torch.float32, device="cuda")
+    assert cu.mf_quant_rows_fp8(x.data_ptr(), K, off[G:].data_ptr(), K, xq.data_ptr(), xs.data_ptr(), 64, s) == 0
+    assert torch.equal(xs, torch.exp2(torch.round(torch.log2(xs)))), "activation scales must be powers of two"
+    xd = _deq(xq.view(torch.float8_e4m3fn), xs)
+    w = (torch.randn(G, N, K, device="cuda") * 0.05 * torch.logspace(-1, 1, N // 128, device="cuda").repeat_interleave(128)[None, :, None]).to(torch.bfloat16)
+    wq, ws = M.quantize_weight_fp8(w)
+    assert torch.equal(ws, torch.exp2(torch.round(torch.log2(ws))))
+    wd = _deq_w(wq, ws)
+    ref = torch.cat([xd[off[g]:off[g + 1]] @ wd[g].t() for g in range(G)])
+    st = gemm.status_word()
+    assert cu.mf_grouped_gemm_fp8_mx_supported(G, N, K, 0) == 1
+    out = torch.zeros(R, N, dtype=torch.bfloat16, device="cuda")
+    assert cu.mf_grouped_gemm_fp8_mx(xq.data_ptr(), xs.data_ptr(), R, wq.data_ptr(), ws.data_ptr(), off.data_ptr(), G, N, K, out.data_ptr(), N, None, 0,
+                                     None, None, 0, 1, st.data_ptr(), gemm.sm_count(), s) == 0
+    torch.cuda.synchronize()
+    gemm.check_status()
+    rowmax = ref.abs().amax(dim=1, keepdim=True)
+    assert ((out.float() - ref).abs() <= 2e-2 * rowmax + 1e-5).all(), float(((out.float() - ref).abs() / (rowmax + 1e-9)).max())
+    # SwiGLU (bf16 out) and SwiGLU + re-quantisation (fp8 + power-of-two scale per 128 outputs)
+    wi = M.interleave_gate_up_fp8(wq, tile=128)
+    ref2 = torch.nn.functional.silu(ref[:, :N // 2]) * ref[:, N // 2:]
+    rowmax2 = ref2.abs().amax(dim=1, keepdim=True)
+    out2 = torch.zeros(R, N // 2, dtype=torch.bfloat16, device="cuda")
+    assert cu.mf_grouped_gemm_fp8_mx(xq.data_ptr(), xs.data_ptr(), R, wi.data_ptr(), ws.data_ptr(), off.data_ptr(), G, N, K, out2.data_ptr(), N // 2, None,
+                                     1, None, None, 0, 1, st.data_ptr(), gemm.sm_count(), s) == 0
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert ((out2.float() - ref2).abs() <= 3e-2 * rowmax2 + 1e-5).all()
+    hq = torch.zeros(R, N // 2, dtype=torch.uint8, device="cuda")
+    hs = torch.zeros(R, N // 256, dtype=torch.float32, device="cuda")
+    assert cu.mf_grouped_gemm_fp8_mx(xq.data_ptr(), xs.data_ptr(), R, wi.data_ptr(), ws.data_ptr(), off.data_ptr(), G, N, K, hq.data_ptr(), N // 2,
+                                     hs.data_ptr(), 3, None, None, 0, 1, st.data_ptr(), gemm.sm_count(), s) == 0
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert torch.equal(hs, torch.exp2(torch.round(torch.log2(hs))))
+    hd = _deq(hq.view(torch.float8_e4m3fn), hs)
+    # fp8 e4m3 keeps 3 mantissa bits: each value is within 1/16 of itself plus the block's smallest step
+    blockmax = ref2.view(R, N // 256, 128).abs().amax(dim=2, keepdim=True).expand(R, N // 256, 128).reshape(R, N // 2)
+    assert ((hd - ref2).abs() <= 0.07 * ref2.abs() + 0.02 * blockmax + 1e-6).all()
+    # the same bytes as the stand-alone quantiser produces from the bf16 SwiGLU output of the kernel above
+    hq2, hs2 = torch.empty_like(hq), torch.empty_like(hs)
+    assert cu.mf_quant_rows_fp8(out2.data_ptr(), N // 2, off[G:].data_ptr(), N // 2, hq2.data_ptr(), hs2.data_ptr(), 64, s) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(hs, hs2) and torch.equal(hq, hq2)
 
 
 def _moe_ranks(rank, world, url, T, H, I, E, K, sync):
