@@ -21,6 +21,15 @@
 //   EPI 3  gate/up + SwiGLU + re-quantisation: the 128 outputs of a tile row are one 1 x 128 block of the next
 //                             GEMM's fp8 input: amax, power-of-two scale, e4m3 bytes and the scale are written
 //                             here, so the activation never exists in bf16 in memory
+// The same mainloop also runs the two tensor-parallel fusions on dense operands (MODE 1 / MODE 2):
+//   MODE 1  all-gather -> GEMM : warp 3 of every CTA quantises its rows of this rank's bf16 sequence shard to
+//                                fp8 + 1 x 128 scales into the rank's own gather buffer (first, so the first
+//                                tiles can start), then copies those bytes into every peer's gather buffer,
+//                                nearest consumer first; the TMA and scale warps wait for a shard's flag
+//                                before they touch its rows. Operands are read from THIS GPU's buffer only.
+//   MODE 2  GEMM -> reduce-scatter : the epilogue stores each partial tile (bf16) into the landing zone of the
+//                                rank that owns the rows and counts it there; after its tiles a CTA adds up
+//                                the landed partials of the tiles it owns.
 // Parity of role: app/zbal/doc/fused_deep_moe.md:106-127,213-281 (GMM1 -> dequant + SwiGLU + dynamic re-quant
 // -> GMM2 -> combine) of the reference.
 #include <cuda_bf16.h>
@@ -83,15 +92,32 @@ struct XArgs {
     int64_t ldo;           // elements per output row
     float *out_scale;      // EPI 3: [rows, N/256]
     int *status;
-    Team team;             // EPI 2
+    Team team;             // EPI 2, MODE 1, MODE 2
     const int4 *recv_info;
     uint64_t comb_off;
     int topk;
+    uint32_t epoch;        // flag value of this call (grows by one per call)
+    uint32_t seq;          // number of fused calls so far on these counters, including this one
+    // MODE 1
+    const __nv_bfloat16 *x_local;  // this rank's shard [shard_rows, K] bf16
+    int64_t ldx;
+    int shard_rows;
+    uint64_t ag_buf_off;     // slot offset of the gather buffer [W * shard_rows, K] e4m3
+    uint64_t ag_scale_off;   // slot offset of its scales [W * shard_rows, K / 128] fp32
+    uint64_t ag_ready_off;   // slot offset of W ready flags (u32)
+    uint32_t *push_count;    // local device counters [W], monotonic
+    // MODE 2
+    uint64_t rs_land_off;    // slot offset of the landing zone [W][rows_per_rank][N] bf16
+    uint64_t rs_count_off;   // slot offset of per-owned-tile arrival counters (u32), monotonic
+    int rows_per_rank;
+    __nv_bfloat16 *y_out;    // [rows_per_rank, N]
+    int64_t ldy;
+    float scale;
 };
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory"); }
 
-template <int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_grouped_fp8_mx(const __grid_constant__ XArgs g)
+template <int MODE, int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_grouped_fp8_mx(const __grid_constant__ XArgs g)
 {
     extern __shared__ uint8_t smem_raw[];
     XSmem sm(smem_raw);
@@ -119,12 +145,19 @@ template <int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_grouped_fp8
         mbar_fence_init();
         tma_prefetch_desc(&g.tm.a);
         tma_prefetch_desc(&g.tm.b);
-        int run = 0;
-        for (int i = 0; i <= g.G; i++) {
-            const int ro = min(g.row_off[i], g.max_rows);
-            s_row_off[i] = ro;
-            tile_start[i] = run;
-            if (i < g.G) run += ((min(g.row_off[i + 1], g.max_rows) - ro + BM - 1) / BM) * n_tiles;
+        if (MODE == 0) {
+            int run = 0;
+            for (int i = 0; i <= g.G; i++) {
+                const int ro = min(g.row_off[i], g.max_rows);
+                s_row_off[i] = ro;
+                tile_start[i] = run;
+                if (i < g.G) run += ((min(g.row_off[i + 1], g.max_rows) - ro + BM - 1) / BM) * n_tiles;
+            }
+        } else {
+            s_row_off[0] = 0;
+            s_row_off[1] = g.max_rows;
+            tile_start[0] = 0;
+            tile_start[1] = (g.max_rows / BM) * n_tiles;
         }
     }
     if (warp == 1) {
@@ -135,10 +168,26 @@ template <int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_grouped_fp8
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *sm.tmem_slot();
-    const int total = tile_start[g.G];
+    const int total = tile_start[MODE == 0 ? g.G : 1];
+    const uint32_t me = g.team.rank;
 
     // linear tile -> (group, first row, row limit, column tile); inside a group the row tile varies fastest
     auto locate = [&](int t, int &grp, int &row0, int &row_end, int &nt) {
+        if (MODE != 0) {
+            // blocks of rows owned by one rank, visited starting with this rank (MODE 1: the order in which the shards
+            // arrive) or with the next rank (MODE 2: remote owners first, own rows last)
+            const int rows = MODE == 1 ? g.shard_rows : g.rows_per_rank;
+            const int mt_per = rows / BM;
+            const int per_block = mt_per * n_tiles;
+            const int i = t / per_block;
+            const int owner = (int)((me + (MODE == 2 ? 1 : 0) + i) % g.team.world);
+            const int r = t - i * per_block;
+            grp = 0;
+            nt = r / mt_per;
+            row0 = (owner * mt_per + r % mt_per) * BM;
+            row_end = g.max_rows;
+            return;
+        }
         int lo = 0;
         while (lo + 1 < g.G && tile_start[lo + 1] <= t) lo++;
         grp = lo;
@@ -156,6 +205,16 @@ template <int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_grouped_fp8
             for (int t = blockIdx.x; t < total && fine; t += gridDim.x) {
                 int grp, row0, row_end, nt;
                 locate(t, grp, row0, row_end, nt);
+                if (MODE == 1) {
+                    // the shard holding this tile's rows must have landed in this GPU's gather buffer
+                    const uint32_t *ready = reinterpret_cast<const uint32_t *>(peer_ptr(g.team, me, g.ag_ready_off)) + row0 / g.shard_rows;
+                    if (!wait_flag(ready, g.epoch, g.team.spin_limit)) {
+                        *ac.abort_smem = 1;
+                        atomicCAS(g.status, 0, 0x601);
+                        break;
+                    }
+                    asm volatile("fence.proxy.async.global;" ::: "memory");  // peers' generic-proxy stores before our TMA reads
+                }
                 for (int kb = 0; kb < k_blocks; kb++) {
                     fine = mbar_wait(sm.empty(ps.stage), ps.phase ^ 1, ac, 0x602);
                     if (!fine) break;
@@ -224,6 +283,23 @@ template <int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_grouped_fp8
             }
             const float *bs0 = g.b_scale + ((int64_t)grp * nblocks + nb0) * k_blocks;
             const float *bs1 = g.b_scale + ((int64_t)grp * nblocks + nb1) * k_blocks;
+            if (MODE == 1) {
+                // the scales of a shard arrive with its rows
+                int ok = 1;
+                if (lane == 0) {
+                    const uint32_t *ready = reinterpret_cast<const uint32_t *>(peer_ptr(g.team, me, g.ag_ready_off)) + row0 / g.shard_rows;
+                    ok = wait_flag(ready, g.epoch, g.team.spin_limit) ? 1 : 0;
+                    if (!ok) {
+                        *ac.abort_smem = 1;
+                        atomicCAS(g.status, 0, 0x608);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) {
+                    fine = false;
+                    break;
+                }
+            }
             for (int gq = 0; gq < sf_groups; gq++) {
                 int ok = 1;
                 if (lane == 0) ok = mbar_wait(sm.sf_empty(sf.stage), sf.phase ^ 1, ac, 0x607) ? 1 : 0;
@@ -248,7 +324,8 @@ template <int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_grouped_fp8
 #pragma unroll
                     for (int j = 0; j < 4; j++) {
                         const int kb = gq * 4 + j;
-                        w |= (kb < k_blocks ? ue8m0_byte(__ldg(as + kb)) : 127u) << (8 * j);
+                        // MODE 1: written by peers during this kernel, so not through the read-only path
+                        w |= (kb < k_blocks ? ue8m0_byte(MODE == 1 ? __ldcg(as + kb) : __ldg(as + kb)) : 127u) << (8 * j);
                     }
                     wa[r1] = w;
                 }
@@ -353,6 +430,11 @@ template <int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_grouped_fp8
                         w = __int_as_float(info.w);
                         dst = reinterpret_cast<unsigned long long>(reinterpret_cast<__nv_bfloat16 *>(peer_ptr(g.team, (uint32_t)info.x, g.comb_off)) +
                                                                    ((int64_t)info.y * g.topk + info.z) * g.N + nt * XBN + half * 128);
+                    } else if (MODE == 2) {
+                        // the partial tile goes to the landing zone of the rank that owns these rows
+                        const int owner = row0 / g.rows_per_rank;
+                        dst = reinterpret_cast<unsigned long long>(reinterpret_cast<__nv_bfloat16 *>(peer_ptr(g.team, (uint32_t)owner, g.rs_land_off)) +
+                                                                   ((int64_t)me * g.rows_per_rank + (row - owner * g.rows_per_rank)) * g.N + nt * XBN + half * 128);
                     } else {
                         dst = reinterpret_cast<unsigned long long>(static_cast<__nv_bfloat16 *>(g.out) + (int64_t)row * g.ldo + nt * XBN + half * 128);
                     }
@@ -378,8 +460,111 @@ template <int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_grouped_fp8
                     }
                     __syncwarp();
                 }
+                if (MODE == 2) {
+                    // all eight epilogue warps have stored their part of the tile: tell the owner
+                    __threadfence_system();
+                    named_bar_sync(9, 256);
+                    if (warp == 4 && lane == 0) {
+                        const int owner = row0 / g.rows_per_rank;
+                        const int ltile = ((row0 - owner * g.rows_per_rank) / BM) * n_tiles + nt;
+                        uint32_t *cnt = reinterpret_cast<uint32_t *>(peer_ptr(g.team, (uint32_t)owner, g.rs_count_off)) + ltile;
+                        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+                    }
+                }
             }
             tphase ^= 1;
+        }
+    } else if (MODE == 1 && warp == 3) {
+        // all-gather side. Pass 1: this CTA's rows of the rank's bf16 shard -> e4m3 + one power-of-two scale per 128
+        // elements, into the rank's OWN gather buffer (lane = 16 elements, 8 lanes = one 128-group, four steps of 512
+        // elements in flight). Pass 2: those bytes and scales to every peer, nearest consumer first.
+        const int per = (g.shard_rows + (int)gridDim.x - 1) / (int)gridDim.x;
+        const int r0 = min(g.shard_rows, (int)blockIdx.x * per), r1 = min(g.shard_rows, r0 + per);
+        const int K = g.K, kg = K / 128;
+        const int64_t shard_q = (int64_t)me * g.shard_rows * K, shard_s = (int64_t)me * g.shard_rows * kg;
+        uint8_t *own_q = peer_ptr(g.team, me, g.ag_buf_off) + shard_q;
+        float *own_s = reinterpret_cast<float *>(peer_ptr(g.team, me, g.ag_scale_off)) + shard_s;
+        for (int row = r0; row < r1; row++) {
+            const __nv_bfloat16 *src = g.x_local + (int64_t)row * g.ldx;
+            for (int c0 = 0; c0 < K; c0 += 2048) {
+                uint4 raw[4][2];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int c = c0 + u * 512 + lane * 16;
+                    if (c < K) {
+                        raw[u][0] = __ldg(reinterpret_cast<const uint4 *>(src + c));
+                        raw[u][1] = __ldg(reinterpret_cast<const uint4 *>(src + c) + 1);
+                    } else {
+                        raw[u][0] = raw[u][1] = make_uint4(0, 0, 0, 0);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int c = c0 + u * 512 + lane * 16;
+                    float f[16];
+                    const __nv_bfloat162 *h0 = reinterpret_cast<const __nv_bfloat162 *>(&raw[u][0]);
+                    const __nv_bfloat162 *h1 = reinterpret_cast<const __nv_bfloat162 *>(&raw[u][1]);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        float2 pr = __bfloat1622float2(h0[i]);
+                        f[2 * i] = pr.x;
+                        f[2 * i + 1] = pr.y;
+                        pr = __bfloat1622float2(h1[i]);
+                        f[8 + 2 * i] = pr.x;
+                        f[8 + 2 * i + 1] = pr.y;
+                    }
+                    float amax = 0.f;
+#pragma unroll
+                    for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(f[i]));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                    const float scale = pow2_scale_e4m3(amax);
+                    const float mul = 1.f / scale;
+                    if (c < K) {
+                        uint4 q;
+                        q.x = pack4_e4m3(f[0], f[1], f[2], f[3], mul);
+                        q.y = pack4_e4m3(f[4], f[5], f[6], f[7], mul);
+                        q.z = pack4_e4m3(f[8], f[9], f[10], f[11], mul);
+                        q.w = pack4_e4m3(f[12], f[13], f[14], f[15], mul);
+                        *reinterpret_cast<uint4 *>(own_q + (int64_t)row * K + c) = q;
+                        if ((lane & 7) == 0) own_s[(int64_t)row * kg + c / 128] = scale;
+                    }
+                }
+            }
+        }
+        auto raise = [&](uint32_t p) {
+            // the CTA that completes this rank's shard in the buffer of rank p raises the flag there
+            __threadfence_system();
+            __syncwarp();
+            if (lane == 0) {
+                const uint32_t done = atomicAdd(g.push_count + p, 1u) + 1;
+                if (done == gridDim.x * g.seq) {
+                    __threadfence_system();
+                    st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(g.team, p, g.ag_ready_off)) + me, g.epoch);
+                }
+            }
+            __syncwarp();
+        };
+        raise(me);
+        const int64_t nq = (int64_t)(r1 - r0) * K / 16, ns = (int64_t)(r1 - r0) * kg;
+        const uint4 *from_q = reinterpret_cast<const uint4 *>(own_q + (int64_t)r0 * K);
+        const float *from_s = own_s + (int64_t)r0 * kg;
+        for (uint32_t i = 1; i < g.team.world; i++) {
+            const uint32_t p = (me + g.team.world - i) % g.team.world;
+            uint4 *to_q = reinterpret_cast<uint4 *>(peer_ptr(g.team, p, g.ag_buf_off) + shard_q + (int64_t)r0 * K);
+            float *to_s = reinterpret_cast<float *>(peer_ptr(g.team, p, g.ag_scale_off)) + shard_s + (int64_t)r0 * kg;
+            int64_t v = lane;
+            for (; v + 7 * 32 < nq; v += 8 * 32) {  // eight independent 16-byte loads in flight per lane, then eight peer stores
+                uint4 val[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) val[u] = __ldcg(from_q + v + u * 32);
+#pragma unroll
+                for (int u = 0; u < 8; u++) to_q[v + u * 32] = val[u];
+            }
+            for (; v < nq; v += 32) to_q[v] = __ldcg(from_q + v);
+            for (int64_t e = lane; e < ns; e += 32) to_s[e] = __ldcg(from_s + e);
+            raise(p);
         }
     }
     if (EPI == 2) __threadfence_system();
@@ -389,6 +574,55 @@ template <int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_grouped_fp8
         tc_fence_after();
         tmem_dealloc(tmem_base, kXTmemCols);
     }
+    if (MODE == 2) {
+        // add up the W partial tiles of every tile whose rows this rank owns
+        __shared__ int ok_sh;
+        const int own_tiles = (g.rows_per_rank / BM) * n_tiles;
+        const uint32_t *cnt = reinterpret_cast<const uint32_t *>(peer_ptr(g.team, me, g.rs_count_off));
+        const __nv_bfloat16 *land = reinterpret_cast<const __nv_bfloat16 *>(peer_ptr(g.team, me, g.rs_land_off));
+        for (int t = blockIdx.x; t < own_tiles; t += gridDim.x) {
+            if (threadIdx.x == 0) {
+                ok_sh = (!*ac.abort_smem && wait_flag(cnt + t, g.team.world * g.seq, g.team.spin_limit)) ? 1 : 0;
+                if (!ok_sh) atomicCAS(g.status, 0, 0x609);
+            }
+            __syncthreads();
+            if (!ok_sh) break;
+            const int ml = t / n_tiles, nt = t % n_tiles;
+            constexpr int kVecRow = XBN / 8;
+            for (int v = threadIdx.x; v < BM * kVecRow; v += blockDim.x) {
+                const int lr = ml * BM + v / kVecRow;
+                const int col = nt * XBN + (v % kVecRow) * 8;
+                float accv[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) accv[e] = 0.f;
+                // partials are fetched eight at a time (independent loads in flight), added in rank order
+                for (uint32_t s0 = 0; s0 < g.team.world; s0 += 8) {
+                    uint4 raw[8];
+#pragma unroll
+                    for (int u = 0; u < 8; u++)
+                        if (s0 + u < g.team.world)
+                            raw[u] = __ldcg(reinterpret_cast<const uint4 *>(land + ((int64_t)(s0 + u) * g.rows_per_rank + lr) * g.N + col));
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        if (s0 + u >= g.team.world) continue;
+                        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[u]);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float2 f = __bfloat1622float2(h[e]);
+                            accv[2 * e] += f.x;
+                            accv[2 * e + 1] += f.y;
+                        }
+                    }
+                }
+                uint4 pk;
+                __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+                for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(accv[2 * e] * g.scale, accv[2 * e + 1] * g.scale);
+                *reinterpret_cast<uint4 *>(g.y_out + (int64_t)lr * g.ldy + col) = pk;
+            }
+            __syncthreads();
+        }
+    }
 }
 
 }  // namespace mfk
@@ -396,9 +630,9 @@ template <int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_grouped_fp8
 using namespace mfk;
 
 namespace {
-template <int EPI> int launch_mx(const XArgs &g, int grid, cudaStream_t s)
+template <int MODE, int EPI> int launch_mx(const XArgs &g, int grid, cudaStream_t s)
 {
-    auto kern = k_grouped_fp8_mx<EPI>;
+    auto kern = k_grouped_fp8_mx<MODE, EPI>;
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, XSmem::kDynBytes) != cudaSuccess) {
@@ -452,12 +686,94 @@ int mf_grouped_gemm_fp8_mx(const void *A, const float *a_scale, int max_rows, co
     g.topk = topk;
     cudaStream_t s = (cudaStream_t)stream;
     switch (epi) {
-        case 0: return launch_mx<0>(g, sms, s);
-        case 1: return launch_mx<1>(g, sms, s);
-        case 2: return launch_mx<2>(g, sms, s);
-        case 3: return launch_mx<3>(g, sms, s);
+        case 0: return launch_mx<0, 0>(g, sms, s);
+        case 1: return launch_mx<0, 1>(g, sms, s);
+        case 2: return launch_mx<0, 2>(g, sms, s);
+        case 3: return launch_mx<0, 3>(g, sms, s);
         default: return -1;
     }
+}
+
+// All-gather -> GEMM in fp8. x_local [shard_rows, K] bf16 is this rank's sequence shard; it is quantised (e4m3, one
+// power-of-two scale per 128 elements) on its way into the gather buffers ([world * shard_rows, K] bytes at ag_buf_off,
+// scales [world * shard_rows, K / 128] fp32 at ag_scale_off of every slot). B [N, K] e4m3 with b_scale [N/128, K/128].
+// epi 0: out bf16 [world * shard_rows, N]; 1: SwiGLU, out bf16 [.., N/2] (B interleaved per 128 rows); 3: SwiGLU +
+// re-quantisation, out e4m3 [.., N/2] with out_scale [.., N/256].
+int mf_ag_gemm_fp8(const Team *team, const void *x_local, int64_t ldx, int shard_rows, const void *B, const float *b_scale, void *out, int64_t ldo,
+                   float *out_scale, int N, int K, uint64_t ag_buf_off, uint64_t ag_scale_off, uint64_t ag_ready_off, uint32_t *push_count,
+                   uint32_t epoch, uint32_t seq, int *status, int sms, int epi, void *stream)
+{
+    if (team == nullptr || team->emu || shard_rows <= 0 || (shard_rows % BM) != 0 || (K % 512) != 0 || (ldx & 7) != 0 ||
+        !mf_grouped_gemm_fp8_mx_supported(1, N, K, epi) || epi == 2)
+        return -1;
+    if (epi == 3 && (out_scale == nullptr || (ldo & 15) != 0)) return -1;
+    XArgs g{};
+    const int M = shard_rows * (int)team->world;
+    const uint64_t slot = team->heap_base + (uint64_t)team->rank * team->stride;
+    int rc = make_tmap_2d(&g.tm.a, reinterpret_cast<const void *>(slot + ag_buf_off), 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, true);
+    if (rc == 0) rc = make_tmap_2d(&g.tm.b, B, 1, (uint64_t)N, (uint64_t)K, (uint64_t)K, XBN, true);
+    if (rc != 0) return rc;
+    g.a_scale = reinterpret_cast<const float *>(slot + ag_scale_off);
+    g.b_scale = b_scale;
+    g.G = 1;
+    g.N = N;
+    g.K = K;
+    g.max_rows = M;
+    g.out = out;
+    g.ldo = ldo;
+    g.out_scale = out_scale;
+    g.status = status;
+    g.team = *team;
+    g.epoch = epoch;
+    g.seq = seq;
+    g.x_local = static_cast<const __nv_bfloat16 *>(x_local);
+    g.ldx = ldx;
+    g.shard_rows = shard_rows;
+    g.ag_buf_off = ag_buf_off;
+    g.ag_scale_off = ag_scale_off;
+    g.ag_ready_off = ag_ready_off;
+    g.push_count = push_count;
+    cudaStream_t s = (cudaStream_t)stream;
+    // every CTA carries a copy warp whose work peers wait for: the grid must be fully resident (one CTA per SM)
+    switch (epi) {
+        case 0: return launch_mx<1, 0>(g, sms, s);
+        case 1: return launch_mx<1, 1>(g, sms, s);
+        case 3: return launch_mx<1, 3>(g, sms, s);
+        default: return -1;
+    }
+}
+
+// GEMM -> reduce-scatter in fp8. A [M, K] e4m3 (M = world * rows_per_rank) with a_scale [M, K/128], B [N, K] e4m3 with
+// b_scale [N/128, K/128]; y_out [rows_per_rank, N] bf16 = scale * sum over ranks of A . B^T.
+int mf_gemm_rs_fp8(const Team *team, const void *A, const float *a_scale, const void *B, const float *b_scale, void *y_out, int64_t ldy,
+                   int rows_per_rank, int N, int K, uint64_t rs_land_off, uint64_t rs_count_off, uint32_t epoch, uint32_t seq, float scale,
+                   int *status, int sms, void *stream)
+{
+    if (team == nullptr || team->emu || rows_per_rank <= 0 || (rows_per_rank % BM) != 0 || (ldy & 7) != 0 ||
+        !mf_grouped_gemm_fp8_mx_supported(1, N, K, 0))
+        return -1;
+    XArgs g{};
+    const int M = rows_per_rank * (int)team->world;
+    int rc = make_tmap_2d(&g.tm.a, A, 1, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, true);
+    if (rc == 0) rc = make_tmap_2d(&g.tm.b, B, 1, (uint64_t)N, (uint64_t)K, (uint64_t)K, XBN, true);
+    if (rc != 0) return rc;
+    g.a_scale = a_scale;
+    g.b_scale = b_scale;
+    g.G = 1;
+    g.N = N;
+    g.K = K;
+    g.max_rows = M;
+    g.status = status;
+    g.team = *team;
+    g.epoch = epoch;
+    g.seq = seq;
+    g.rs_land_off = rs_land_off;
+    g.rs_count_off = rs_count_off;
+    g.rows_per_rank = rows_per_rank;
+    g.y_out = static_cast<__nv_bfloat16 *>(y_out);
+    g.ldy = ldy;
+    g.scale = scale;
+    return launch_mx<2, 0>(g, sms, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -14,7 +14,7 @@ from ..ops.tp import TensorParallel
 
 
 class TensorParallelMLP:
-    def __init__(self, heap, hidden: int, ffn: int, max_tokens: int, seed: int = 0, dtype=torch.bfloat16):
+    def __init__(self, heap, hidden: int, ffn: int, max_tokens: int, seed: int = 0, dtype=torch.bfloat16, fp8: bool = False):
         self.world, self.rank = heap.world, heap.rank
         assert ffn % self.world == 0 and (ffn // self.world) % 128 == 0
         self.hidden, self.ffn, self.f_local = hidden, ffn, ffn // self.world
@@ -24,7 +24,21 @@ class TensorParallelMLP:
         self.w_up = (torch.randn(self.f_local, hidden, device=dev, generator=g) * 0.02).to(dtype)
         self.w_down = (torch.randn(hidden, self.f_local, device=dev, generator=g) * 0.02).to(dtype)
         self.w_gate_up = gemm.interleave_gate_up(self.w_gate, self.w_up)
-        self.tp = TensorParallel(heap, max_tokens, hidden, max_out=hidden)
+        self.tp = TensorParallel(heap, max_tokens, hidden, max_out=hidden, fp8=fp8)
+        self.fp8 = fp8
+        if fp8:
+            # e4m3 weights with 128 x 128 power-of-two block scales; gate / up rows interleaved per 128 for the SwiGLU epilogue
+            from ..ops import moe as M
+            gu = torch.cat([self.w_gate, self.w_up])                      # [2 F/W, H], gate rows then up rows
+            q, self.ws_gate_up = M.quantize_weight_fp8(gu)
+            self.wq_gate_up = M.interleave_gate_up_fp8(q[None], 128)[0]
+            self.wq_down, self.ws_down = M.quantize_weight_fp8(self.w_down)
+
+    def forward_fp8(self, x_shard: torch.Tensor) -> torch.Tensor:
+        """The same layer with fp8 tensor-core math: the shard is quantised on its way into the gather buffers, SwiGLU and
+        the re-quantisation are the first GEMM's epilogue, the second GEMM's partial tiles are reduce-scattered in bf16."""
+        hq, hs = self.tp.ag_gemm_fp8(x_shard, self.wq_gate_up, self.ws_gate_up)
+        return self.tp.gemm_rs_fp8(hq, hs, self.wq_down, self.ws_down)
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
         """x_shard [T/W, hidden] -> y_shard [T/W, hidden]."""

@@ -194,9 +194,11 @@ def tp_mlp(heap, world, flush):
     S, H, F = 8192, 8192, 28672
     if world == 1:
         F = 28672 // 8 * 2  # one GPU cannot hold the full layer's work in a short run: use a 1/4-width slice
-    mlp = TensorParallelMLP(heap, H, F, S, seed=2)
+    mlp = TensorParallelMLP(heap, H, F, S, seed=2, fp8=True)
     x = torch.randn(S // world, H, device="cuda").to(torch.bfloat16)
     ms = _timed(lambda: mlp.forward(x), 6, 3, flush)
+    gemm.check_status()
+    ms8 = _timed(lambda: mlp.forward_fp8(x), 6, 3, flush)
     gemm.check_status()
     base = _timed(lambda: mlp.forward_baseline(x), 6, 3, flush)
     flops = 2.0 * S * H * (3 * F // world)
@@ -206,7 +208,8 @@ def tp_mlp(heap, world, flush):
     gemm.check_status()
     return {"tokens": S, "hidden": H, "ffn": F, "fused_us": round(ms * 1e3, 1), "nccl_cublas_us": round(base * 1e3, 1),
             "fused_tflops_per_gpu": round(flops / (ms * 1e-3) / 1e12, 1), "ag_gemm_swiglu_us": round(ag * 1e3, 1),
-            "gemm_rs_us": round(rs * 1e3, 1)}
+            "gemm_rs_us": round(rs * 1e3, 1), "fused_fp8_us": round(ms8 * 1e3, 1),
+            "fused_fp8_tflops_per_gpu": round(flops / (ms8 * 1e-3) / 1e12, 1)}
 
 
 def xcopy_sweep(h, rank, world, flush):
