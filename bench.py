@@ -4,8 +4,11 @@
 One step = one batched put of BLOCKS KV blocks (one block = 61 layers x (128 KiB K/V + 16 KiB rope) =
 122 discrete segments, 8784 KiB) from a private device buffer into the NEXT rank's slice of the pool
 (rank r -> (r + 1) % N; with one GPU the target is the rank's own slice), through the public API
-``BigMemory.copy_data_batch``. The value is the whole-job aggregate GB/s (10^9 B/s). Device-timed with
-CUDA events on the launching stream, max over ranks. The per-step input (549 MiB) is larger than L2.
+``BigMemory.copy_data_batch`` = the C call ``smem_bm_copy_batch``: every step hands the library the 7808
+(source, destination, size) triples again, so the validation of every triple, the merging of neighbours,
+the cutting into work chunks and the writing of the descriptor ring are inside the timed region. The
+value is the whole-job aggregate GB/s (10^9 B/s). Device-timed with CUDA events on the launching stream,
+max over ranks. The per-step input (549 MiB) is larger than L2.
 
     python bench.py --gpus 1 --steps 20 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port P \
@@ -87,7 +90,9 @@ def main() -> int:
 
     nblk = args.blocks
     step_bytes = nblk * bu.KV_BLOCK_BYTES
-    pool_bytes = ((step_bytes + (64 << 20)) + (2 << 20) - 1) // (2 << 20) * (2 << 20)
+    # the extras put up to 1024 KV blocks (8.6 GiB) and one 2 GiB run into the slice
+    want_bytes = max(step_bytes, (1024 * bu.KV_BLOCK_BYTES) if args.extras else 0)
+    pool_bytes = ((want_bytes + (64 << 20)) + (2 << 20) - 1) // (2 << 20) * (2 << 20)
     h = bm.create2(id=0, local_dram_size=0, max_dram_size=0, local_hbm_size=pool_bytes, max_hbm_size=pool_bytes,
                    data_op_type=bm.BmDataOpType.SDMA)
     assert h.join() == 0, mf.get_last_err_msg()
@@ -109,18 +114,18 @@ def main() -> int:
     peer = (rank + 1) % world
     dst_base = h.peer_rank_ptr(peer, bm.BmMemType.DEVICE)
     src = torch.randn(step_bytes // 2, dtype=torch.bfloat16, device="cuda", generator=torch.Generator("cuda").manual_seed(rank))
+    import numpy as np
     segs = bu.kv_block_segments(nblk)
-    srcs = [src.data_ptr() + off for off, _ in segs]
-    dsts = [dst_base + off for off, _ in segs]
-    sizes = [sz for _, sz in segs]
+    # the descriptor lists as a serving engine keeps them: arrays of 64-bit addresses and sizes
+    srcs = np.array([src.data_ptr() + off for off, _ in segs], dtype=np.uint64)
+    dsts = np.array([dst_base + off for off, _ in segs], dtype=np.uint64)
+    sizes = np.array([sz for _, sz in segs], dtype=np.uint64)
     n = len(segs)
     stream = torch.cuda.Stream()
     flags = bm.ASYNC_COPY_FLAG | bm.FLAG_USE_EXTERNAL_STREAM
 
-    batch = h.prepare_batch(srcs, dsts, sizes, n)  # marshal the 7808 descriptors once, submit many times
-
     def put():
-        rc = h.copy_prepared(batch, bm.BmCopyType.L2G, flags, stream.cuda_stream)
+        rc = h.copy_data_batch(srcs, dsts, sizes, n, bm.BmCopyType.L2G, flags, stream.cuda_stream)
         assert rc == 0, mf.get_last_err_msg()
 
     # ---- correctness of one put before timing: the peer's slice must equal the source bit for bit
@@ -142,11 +147,13 @@ def main() -> int:
     sampler = bu.ClockSampler(local).start()
     bu.barrier()
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    host_t0 = time.perf_counter()
     with torch.cuda.stream(stream):
         ev[0].record(stream)
         for _ in range(args.steps):
             put()
         ev[1].record(stream)
+    host_us_per_call = (time.perf_counter() - host_t0) / args.steps * 1e6   # what the calling thread spends inside the API per step
     stream.synchronize()
     bu.barrier()
     clocks = sampler.stop()
@@ -193,13 +200,18 @@ def main() -> int:
         out = {
             "metric": "kv_block_xcopy_d2rd_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": round(value / PUBLISHED_D2RD_GBS, 3), "dtype": "bf16", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": round(value / world / PUBLISHED_D2RD_GBS, 3), "dtype": "bf16", "data": "synthetic",
             "config": {"model": "DeepSeek-R1 KV block: 61 layers x (128 KiB + 16 KiB) = 122 segments, 8784 KiB",
                        "global_batch": world * nblk, "seq_len": bu.KV_SEGMENTS, "parallelism": f"ring-put x{world}",
                        "blocks_per_step": nblk, "bytes_per_step_per_gpu": step_bytes,
-                       "l2": "inputs larger than L2 (549 MiB per step)", "api": "smem_bm_copy_batch L2G, async on a CUDA stream",
-                       "scaling_note": "with 1 GPU the 'remote' slice is the GPU's own HBM (no NVLink); from 2 GPUs on every put "
-                                       "crosses NVLink and the per-GPU rate is flat (about 670 GB/s of the 770 GB/s measured peer copy)"},
+                       "l2": "inputs larger than L2 (549 MiB per step)",
+                       "api": "memfabric_hybrid.bm.BigMemory.copy_data_batch = smem_bm_copy_batch (L2G, ASYNC_COPY_FLAG on a CUDA stream); "
+                              "all 7808 triples are validated and marshalled by the library on every step",
+                       "host_us_per_call": round(host_us_per_call, 1), "descriptors_per_call": n,
+                       "per_gpu_GBps": round(value / world, 2),
+                       "vs_baseline_note": "per-GPU rate / 138.01 GB/s (reference D2RD, one 1 GB transfer on Ascend A3)",
+                       "scaling_note": "with 1 GPU the 'remote' slice is the GPU's own HBM (no NVLink); from 2 GPUs on every put crosses "
+                                       "NVLink, where stores issued by SMs reach 709 GB/s per direction between two B200s and copy engines 772"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": step_bytes, "d2h_bytes_per_step": 8,
                     "ms_per_step": round(e2e_ms, 4)},

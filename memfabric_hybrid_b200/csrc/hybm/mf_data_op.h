@@ -53,7 +53,7 @@ public:
     int Quant(const std::vector<QuantItem> &items, uint32_t unit, int inputFp16, int mode, void *userStream);
     int Wait();
     DataOpStats Stats() const { return stats_; }
-    // Tunables (env MF_XCOPY_CHUNK_KB, MF_XCOPY_RING_MB, MF_HOST_COPY_THREADS).
+    // Tunables (env MF_XCOPY_CHUNK_KB, MF_XCOPY_RING_MB, MF_HOST_COPY_THREADS, MF_XCOPY_ENGINE_MIN_MB).
     uint64_t ChunkBytes() const { return chunk_; }
 
 private:
@@ -75,6 +75,7 @@ private:
     std::vector<void *> ringUsers_;  // streams with launches that may still read ring slots
     uint64_t chunk_;
     uint64_t hostSplit_;
+    uint64_t engineMin_ = 0;  // device<->device items of at least this many bytes go to a copy engine (0: never)
     std::unique_ptr<ThreadPool> pool_;
     DataOpStats stats_;
     bool pending_ = false;

@@ -91,6 +91,9 @@ public:
     virtual int IpcOpen(const uint8_t blob[64], uint64_t *ptr) = 0;
     virtual int IpcClose(uint64_t ptr) = 0;
     virtual bool IsDevicePointer(uint64_t ptr) = 0;
+    // True when [ptr, ptr + len) is pinned host memory that kernels of this device can address at the same
+    // value (cudaHostAlloc / cudaHostRegister under unified addressing).
+    virtual bool IsPinnedHost(uint64_t ptr, uint64_t len) { (void)ptr, (void)len; return false; }
     virtual int EnablePeerAccess(int peerDevice) = 0;
     virtual int CanAccessPeer(int peerDevice) = 0;  // 1 yes, 0 no
 

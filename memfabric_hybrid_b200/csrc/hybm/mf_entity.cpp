@@ -1,5 +1,7 @@
 #include "mf_entity.h"
 
+#include <chrono>
+
 #include <sys/prctl.h>
 #include <unistd.h>
 
@@ -479,6 +481,30 @@ bool Entity::InPool(const SegmentPtr &seg, uint64_t addr, uint64_t len, int &err
     return true;
 }
 
+// A caller's host buffer that is pinned and device-addressable can be read and written by the copy kernel
+// directly: a batch of many small pieces between it and the pool then costs one launch instead of one
+// copy-engine submission per piece. The last range that answered yes is remembered (the pieces of a batch
+// usually lie in one buffer), so a batch pays for a couple of driver queries, not two per piece.
+bool Entity::PinnedHost(uint64_t addr, uint64_t len)
+{
+    std::lock_guard<std::mutex> g(pinMu_);
+    // what is remembered is trusted for 50 ms only: the buffer may have been freed and the addresses reused
+    const uint64_t now = (uint64_t)std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now().time_since_epoch()).count();
+    if (now - pinStampMs_ > 50) pinLo_ = pinHi_ = 0;
+    if (pinHi_ > pinLo_ && addr >= pinLo_ && len <= pinHi_ - pinLo_ && addr - pinLo_ <= (pinHi_ - pinLo_) - len) return true;
+    if (len == 0 || addr + len < addr || !dev_->IsPinnedHost(addr, len)) return false;
+    // grow the remembered range when this piece touches or extends it, else start a new one
+    if (pinHi_ > pinLo_ && addr <= pinHi_ && addr + len >= pinLo_) {
+        pinLo_ = std::min(pinLo_, addr);
+        pinHi_ = std::max(pinHi_, addr + len);
+    } else {
+        pinLo_ = addr;
+        pinHi_ = addr + len;
+        pinStampMs_ = now;
+    }
+    return true;
+}
+
 int Entity::Resolve(uint64_t addr, uint64_t len, bool isSrc, hybm_data_copy_direction dir, Endpoint &ep)
 {
     ep.addr = addr;
@@ -499,7 +525,7 @@ int Entity::Resolve(uint64_t addr, uint64_t len, bool isSrc, hybm_data_copy_dire
     }
     if (want == AC_GD || want == AC_GH) return ERR_INVALID_PARAM;  // named a pooled side but the address is outside
     if (want == AC_LD) ep.kind = EP_DEVICE;
-    else if (want == AC_LH) ep.kind = EP_HOST;
+    else if (want == AC_LH) ep.kind = (dev_ != nullptr && PinnedHost(addr, len)) ? EP_HOST_PINNED : EP_HOST;
     else ep.kind = (dev_ != nullptr && dev_->IsDevicePointer(addr)) ? EP_DEVICE : EP_HOST;
     return OK;
 }

@@ -85,6 +85,9 @@ private:
     // Resolves one side of a copy to how it can be accessed. Returns OK or an error for a bad range.
     int Resolve(uint64_t addr, uint64_t len, bool isSrc, hybm_data_copy_direction dir, Endpoint &ep);
     bool InPool(const SegmentPtr &seg, uint64_t addr, uint64_t len, int &err) const;
+    bool PinnedHost(uint64_t addr, uint64_t len);
+    std::mutex pinMu_;
+    uint64_t pinLo_ = 0, pinHi_ = 0, pinStampMs_ = 0;  // last host range found pinned and device-addressable, and when
 
     uint16_t id_;
     hybm_options opt_;

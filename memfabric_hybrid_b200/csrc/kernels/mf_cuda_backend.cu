@@ -405,6 +405,19 @@ public:
         }
         return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
     }
+    bool IsPinnedHost(uint64_t ptr, uint64_t len) override
+    {
+        if (!caps_.hostPtrForRegistered || len == 0) return false;
+        auto pinned = [](uint64_t a) {
+            cudaPointerAttributes at;
+            if (cudaPointerGetAttributes(&at, (const void *)a) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return false;
+            }
+            return at.type == cudaMemoryTypeHost && at.devicePointer == (void *)a;
+        };
+        return pinned(ptr) && pinned(ptr + len - 1);
+    }
     int EnablePeerAccess(int peer) override
     {
         if (peer == dev_) return OK;
