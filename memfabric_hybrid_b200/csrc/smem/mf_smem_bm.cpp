@@ -40,8 +40,8 @@ int32_t smem_bm_config_init(smem_bm_config_t *config)
     config->startConfigStoreOnly = false;
     config->dynamicWorldSize = false;
     config->unifiedAddressSpace = true;
-    config->autoRanking = false;
-    config->rankId = UINT32_MAX;
+    config->autoRanking = true;   // the reference's default (smem_bm.cpp:38-39): ranks come from the store ...
+    config->rankId = UINT16_MAX;  // ... unless the caller names one (see smem_bm_init)
     config->flags = 0;
     return SMEM_OK;
 }
@@ -54,7 +54,11 @@ int32_t smem_bm_init(const char *storeURL, uint32_t worldSize, uint16_t deviceId
     if (config->initTimeout == 0 || config->createTimeout == 0 || config->controlOperationTimeout == 0)
         return MF_FAIL(SMEM_INVALID_PARAM, "timeouts must be at least 1 second");
     if (!config->unifiedAddressSpace) return MF_FAIL(SMEM_INVALID_PARAM, "unifiedAddressSpace must be true");
-    if (!config->autoRanking && !config->startConfigStoreOnly && config->rankId >= worldSize)
+    // autoRanking is on by default. A caller that also names a valid rank wants that rank (the reference's own
+    // examples set rank_id and leave auto_ranking alone, then address slices by that rank): the store assigns
+    // ranks only when none was named.
+    const bool autoRank = config->autoRanking && config->rankId >= worldSize;
+    if (!autoRank && !config->startConfigStoreOnly && config->rankId >= worldSize)
         return MF_FAIL(SMEM_INVALID_PARAM, "rank id %u outside world %u (or enable autoRanking)", config->rankId, worldSize);
     if (!SmemInited()) return MF_FAIL(SMEM_NOT_INIT, "smem_init has not been called");
     std::lock_guard<std::mutex> g(g_mu);
@@ -71,8 +75,8 @@ int32_t smem_bm_init(const char *storeURL, uint32_t worldSize, uint16_t deviceId
     }
     // Who serves the store: with fixed ranks, rank 0 when allowed to; with auto-ranking every process
     // that is allowed to races for the port and the losers become clients.
-    bool serve = config->startConfigStoreServer && (config->autoRanking || config->rankId == 0);
-    uint32_t linkRank = config->autoRanking ? store::kAutoRank : config->rankId;
+    bool serve = config->startConfigStoreServer && (autoRank || config->rankId == 0);
+    uint32_t linkRank = autoRank ? store::kAutoRank : config->rankId;
     store::StorePtr base;
     int err = OK;
     for (uint32_t attempt = 0; attempt < kInitTries && !base; attempt++) {
@@ -82,7 +86,7 @@ int32_t smem_bm_init(const char *storeURL, uint32_t worldSize, uint16_t deviceId
     }
     if (!base) return MF_FAIL(Pub(err), "cannot reach the config store at %s (%d)", storeURL, err);
     uint32_t rank = config->rankId;
-    if (config->autoRanking) {
+    if (autoRank) {
         int rc = base->AutoRank(rank);
         if (rc != OK) {
             store::StoreFactory::DestroyStore(storeURL);
