@@ -30,16 +30,33 @@ if ROOT not in sys.path:
 PUBLISHED_D2RD_GBS = 138.01  # reference README.md:128-129, xcopy D2RD 1 GB on Ascend A3
 
 
+def host_pool_cfg1(impl: str) -> dict:
+    """The CPU-only configuration both implementations can run: 2 processes, 64 MiB of pooled DRAM each, copy_data of
+    4 KiB - 8 MiB to and from the peer's slice with CRC32 (baseline/host_pool_cfg1.py, its own process: it must import
+    only ONE of the two ``memfabric_hybrid`` packages)."""
+    import subprocess
+    try:
+        p = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "host_pool_cfg1.py"), "--impl", impl, "--iters", "1024"],
+                           capture_output=True, text=True, timeout=600, cwd=os.path.join(ROOT, "baseline"))
+        line = [l for l in p.stdout.splitlines() if l.startswith("{")]
+        return json.loads(line[-1]) if line else {"impl": impl, "unavailable": (p.stderr or "no output")[-300:]}
+    except Exception as e:  # noqa: BLE001
+        return {"impl": impl, "unavailable": repr(e)[:300]}
+
+
 def reference_arm(args) -> int:
-    # The reference ships no installable package at its root (pip: "Neither 'setup.py' nor 'pyproject.toml'
-    # found"), its -DXPU_TYPE=GPU build does not compile unmodified (dl_cuda_api.cpp: 'FileUtil' has not been
-    # declared), and on every non-NPU build smem_bm_create rejects all device data paths, so the metric of
-    # this benchmark (device -> remote-device copies on pooled HBM) has no reference implementation to run.
+    # Headline metric (device -> remote-device copies on pooled HBM): the reference ships no installable package at its
+    # root (pip: "Neither 'setup.py' nor 'pyproject.toml' found"), its -DXPU_TYPE=GPU build does not compile unmodified
+    # (dl_cuda_api.cpp: 'FileUtil' has not been declared), and on every non-NPU build smem_bm_create rejects all device
+    # data paths, so that metric has no reference implementation to run. What the unmodified reference DOES run on this
+    # box is its CPU-only flavour (-DXPU_TYPE=NONE, built into baseline/_ref): the host DRAM pool configuration is
+    # measured through its own Python API and printed under "extras" for a same-box comparison.
     rank = int(os.environ.get("RANK", "0"))
     if rank == 0:
         print(json.dumps({"impl": "reference", "unavailable":
                           "reference is not pip-installable (no setup.py/pyproject.toml at its root); its XPU_TYPE=GPU build "
-                          "fails to compile unmodified and non-NPU builds reject every device data path"}))
+                          "fails to compile unmodified and non-NPU builds reject every device data path",
+                          "extras": {"host_pool_cfg1": host_pool_cfg1("reference")}}))
     return 0
 
 
@@ -196,6 +213,8 @@ def main() -> int:
         except Exception as e:  # noqa: BLE001  (the headline number must not depend on the extras)
             extras = {"error": repr(e)[:200]}
 
+    if rank == 0 and args.extras:
+        extras["host_pool_cfg1"] = host_pool_cfg1("ours")
     if rank == 0:
         out = {
             "metric": "kv_block_xcopy_d2rd_GBps", "value": round(value, 2), "unit": "GB/s", "n_gpus": world,

@@ -3,6 +3,7 @@ from __future__ import annotations
 
 import ctypes as C
 import enum
+import threading
 from typing import Callable, Sequence
 
 from .. import _native as N
@@ -42,6 +43,8 @@ class BmGroupEvent(enum.IntEnum):
     JOIN_EVENT = 0
     LEAVE_EVENT = 1
 
+
+_TLS = threading.local()
 
 ASYNC_COPY_FLAG = 1 << 0
 COPY_EXTEND_FLAG = 1 << 1
@@ -159,8 +162,14 @@ class BigMemory:
         not ordered with PyTorch's streams: a tensor that a PyTorch kernel is still filling (``torch.zeros``,
         ``randn``, the output of a layer) must be complete first (synchronise its stream), or pass that stream
         with the flag so that the copy is enqueued behind the producer."""
-        p = N.CopyParamsC(src_ptr, dst_ptr, size, stream or None)
-        return N.lib().smem_bm_copy(self._h, C.byref(p), int(type), flags)
+        tl = _TLS
+        p = getattr(tl, "copy_params", None)
+        if p is None:     # one parameter block per thread: the call releases the GIL, so threads must not share one
+            p = tl.copy_params = N.CopyParamsC()
+            tl.copy_ref = C.byref(p)
+            tl.copy_fn = N.lib().smem_bm_copy
+        p.src, p.dest, p.dataSize, p.stream = src_ptr, dst_ptr, size, stream or None
+        return tl.copy_fn(self._h, tl.copy_ref, int(type), flags)
 
     def _batch(self, src_addrs, dst_addrs, sizes, count, stream):
         n = int(count)

@@ -72,6 +72,17 @@ int ComposeDataOp::CheckCopyStatus()
     return MF_FAIL(ERR_TIMEOUT, "copy kernel gave up a bounded wait (code %#x): the data of that batch is incomplete", code);
 }
 
+bool ComposeDataOp::HostFast(const ResolvedCopy &c)
+{
+    const bool devPresent = dev_ != nullptr && dev_->Caps().present;
+    if (c.len >= 2 * hostSplit_ || !HostAddressable(c.src, devPresent) || !HostAddressable(c.dst, devPresent)) return false;
+    MF_TRACE_BEGIN(TP_HYBM_LH_TO_GH);
+    memmove(reinterpret_cast<void *>(c.dst.addr), reinterpret_cast<const void *>(c.src.addr), c.len);
+    MF_TRACE_END(TP_HYBM_LH_TO_GH, 0);
+    fastHost_.fetch_add(1, std::memory_order_relaxed);
+    return true;
+}
+
 int ComposeDataOp::RunHost(const ResolvedCopy &c)
 {
     char *d = reinterpret_cast<char *>(c.dst.addr);

@@ -11,6 +11,7 @@
 // hybm_data_op_sdma.cpp:403-463,590-805 (coalescing, param ring, async/wait),
 // hybm_data_op_host_shm.cpp:41-178 (host memcpy leg).
 #pragma once
+#include <atomic>
 #include <memory>
 #include <mutex>
 #include <vector>
@@ -52,7 +53,15 @@ public:
     int Submit(std::vector<ResolvedCopy> &items, void *userStream, uint32_t flags, int32_t *perItem);
     int Quant(const std::vector<QuantItem> &items, uint32_t unit, int inputFp16, int mode, void *userStream);
     int Wait();
-    DataOpStats Stats() const { return stats_; }
+    // Runs the copy right here when it is a host-to-host memcpy below the size at which it would be split over the
+    // thread pool, and says whether it did. Takes no lock: nothing of the operator's state is involved.
+    bool HostFast(const ResolvedCopy &c);
+    DataOpStats Stats() const
+    {
+        DataOpStats s = stats_;
+        s.hostCopies += fastHost_.load(std::memory_order_relaxed);
+        return s;
+    }
     // Tunables (env MF_XCOPY_CHUNK_KB, MF_XCOPY_RING_MB, MF_HOST_COPY_THREADS, MF_XCOPY_ENGINE_MIN_MB).
     uint64_t ChunkBytes() const { return chunk_; }
 
@@ -78,6 +87,7 @@ private:
     uint64_t engineMin_ = 0;  // device<->device items of at least this many bytes go to a copy engine (0: never)
     std::unique_ptr<ThreadPool> pool_;
     DataOpStats stats_;
+    std::atomic<uint64_t> fastHost_{0};
     bool pending_ = false;
     friend class KernelBatch;
 };

@@ -534,13 +534,18 @@ int Entity::CopyData(const hybm_copy_params &p, hybm_data_copy_direction dir, vo
 {
     if (p.src == nullptr || p.dest == nullptr || p.dataSize == 0 || dir >= HYBM_DATA_COPY_DIRECTION_BUTT)
         return MF_FAIL(ERR_INVALID_PARAM, "copy: null address, zero size or bad direction %d", (int)dir);
-    std::vector<ResolvedCopy> one(1);
+    // (the one-element vector is thread-local: a copy call is often a few microseconds of work in total)
+    static thread_local std::vector<ResolvedCopy> one(1);
+    one.resize(1);
+    one[0] = ResolvedCopy();
     one[0].len = p.dataSize;
     int rc = Resolve(reinterpret_cast<uint64_t>(p.src), p.dataSize, true, dir, one[0].src);
     if (rc == OK) rc = Resolve(reinterpret_cast<uint64_t>(p.dest), p.dataSize, false, dir, one[0].dst);
     if (rc != OK)
         return MF_FAIL(rc, "copy %p -> %p (%lu bytes, direction %d): address outside the mapped pool", p.src, p.dest,
                        (unsigned long)p.dataSize, (int)dir);
+    // A short host-to-host copy (pooled DRAM on either side, no device involved) is a memcpy: skip the operator's queue.
+    if (ops_->HostFast(one[0])) return OK;
     return ops_->Submit(one, stream, flags, nullptr);
 }
 

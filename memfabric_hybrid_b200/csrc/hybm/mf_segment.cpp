@@ -1,5 +1,7 @@
 #include "mf_segment.h"
 
+#include <dirent.h>
+
 #include <fcntl.h>
 #include <poll.h>
 #include <sys/file.h>
@@ -10,7 +12,9 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <mutex>
 #include <random>
+#include <set>
 
 #include "../util/mf_trace.h"
 
@@ -416,6 +420,63 @@ protected:
         mmap(reinterpret_cast<void *>(va), size, PROT_NONE, MAP_PRIVATE | MAP_ANONYMOUS | MAP_NORESERVE | MAP_FIXED, -1, 0);
     }
 
+    // Backing files this process created and has not unlinked yet: whatever is left when the process exits normally
+    // (a pool that was never destroyed) is unlinked then.
+    struct OwnedFiles {
+        std::mutex mu;
+        std::set<std::string> paths;
+        void Add(const std::string &p)
+        {
+            std::lock_guard<std::mutex> g(mu);
+            paths.insert(p);
+        }
+        void Drop(const std::string &p)
+        {
+            std::lock_guard<std::mutex> g(mu);
+            paths.erase(p);
+        }
+        ~OwnedFiles()
+        {
+            for (auto &p : paths) unlink(p.c_str());
+        }
+    };
+    static OwnedFiles &Owned()
+    {
+        static OwnedFiles o;
+        return o;
+    }
+
+    // Backing files of this user whose owner no longer lives (it held an exclusive flock for its lifetime and never
+    // got to unlink them: killed, or exited without destroying its pool) are removed, once per process. Peers that
+    // still map such a file keep their mapping. Parity: src/hybm/csrc/mm/hybm_host_shm_segment.cpp:390-466 (stale cleanup).
+    static void RemoveStaleFiles(const char *dir)
+    {
+        static std::once_flag once;
+        std::call_once(once, [dir] {
+            DIR *d = opendir(dir);
+            if (d == nullptr) return;
+            const std::string prefix = "memfabric_b200_" + std::to_string(geteuid()) + "_";
+            while (struct dirent *e = readdir(d)) {
+                if (strncmp(e->d_name, prefix.c_str(), prefix.size()) != 0) continue;
+                const std::string path = std::string(dir) + "/" + e->d_name;
+                int fd = open(path.c_str(), O_RDWR | O_CLOEXEC);
+                if (fd < 0) continue;
+                struct stat st;
+                // a file younger than a minute may belong to a process that has created it and not locked it yet
+                if (fstat(fd, &st) != 0 || time(nullptr) - st.st_ctime < 60) {
+                    close(fd);
+                    continue;
+                }
+                if (flock(fd, LOCK_EX | LOCK_NB) == 0) {
+                    unlink(path.c_str());
+                    MF_INFO("removed the stale pool file %s", path.c_str());
+                }
+                close(fd);
+            }
+            closedir(d);
+        });
+    }
+
     int MapLocal(MemSlice &s, std::string &source, uint64_t &token) override
     {
         int fd = -1;
@@ -429,9 +490,23 @@ protected:
             }
             source = "@" + FdChannel::Get().Name();
             token = FdChannel::Get().Publish(fcntl(fd, F_DUPFD_CLOEXEC, 0));
+        } else if (EnvInt("MF_DRAM_POOL_FILES", nullptr, 0, 0, 1) == 0) {
+            // Default: an anonymous memory file handed to the peers as a descriptor through the fd channel. It has no
+            // name, so nothing can be left behind in /dev/shm however the process ends (children of Python's
+            // multiprocessing leave through _exit and run no destructor).
+            fd = memfd_create("memfabric_b200_pool", MFD_CLOEXEC);
+            if (fd < 0) return MF_FAIL(ERR_NO_RESOURCES, "memfd_create: %s", strerror(errno));
+            if (ftruncate(fd, (off_t)s.size) != 0) {
+                int e = errno;
+                close(fd);
+                return MF_FAIL(ERR_MALLOC, "cannot size the pool's memory file to %lu bytes: %s", (unsigned long)s.size, strerror(e));
+            }
+            source = "@" + FdChannel::Get().Name();
+            token = FdChannel::Get().Publish(fcntl(fd, F_DUPFD_CLOEXEC, 0));
         } else {
             std::random_device rd;
             const char *dir = access("/dev/shm", W_OK) == 0 ? "/dev/shm" : "/tmp";
+            RemoveStaleFiles(dir);
             for (int attempt = 0; attempt < 8 && fd < 0; attempt++) {
                 source = std::string(dir) + "/memfabric_b200_" + std::to_string(geteuid()) + "_" + std::to_string(opt_.entityId) +
                          "_" + std::to_string(opt_.rank) + "_" + std::to_string(s.index) + "_" + std::to_string(rd());
@@ -446,7 +521,7 @@ protected:
                 return MF_FAIL(ERR_MALLOC, "cannot size %s to %lu bytes: %s", source.c_str(), (unsigned long)s.size, strerror(e));
             }
         }
-        int rc = MapAt(s.gva, s.size, fd, true);
+        int rc = MapAt(s.gva, s.size, fd, s.size <= (4ULL << 30));  // larger slices fault in on first touch
         if (rc != OK) {
             close(fd);
             if (source[0] != '@') unlink(source.c_str());
@@ -454,6 +529,7 @@ protected:
         }
         ownFds_[s.index] = fd;
         ownFiles_[s.index] = source;
+        if (source[0] != '@') Owned().Add(source);
         return OK;
     }
     int UnmapLocal(MemSlice &s) override
@@ -466,7 +542,10 @@ protected:
         }
         auto n = ownFiles_.find(s.index);
         if (n != ownFiles_.end()) {
-            if (!n->second.empty() && n->second[0] != '@') unlink(n->second.c_str());
+            if (!n->second.empty() && n->second[0] != '@') {
+                unlink(n->second.c_str());
+                Owned().Drop(n->second);
+            }
             ownFiles_.erase(n);
         }
         return OK;
@@ -485,7 +564,10 @@ protected:
             if (fd < 0) return MF_FAIL(ERR_NOT_EXIST, "peer rank %u DRAM file %s: %s", p.rank, p.source.c_str(), strerror(errno));
         }
         uint64_t va = base_ + opt_.slot * p.rank + p.offset;
-        int rc = MapAt(va, p.size, fd, false);
+        // the owner has touched every page already: filling this process's page table now (as the reference does on
+        // import, hybm_host_shm_segment.cpp:468-540) keeps minor faults out of the first copies; very large slices are
+        // left to fault in on demand so that a join does not stall
+        int rc = MapAt(va, p.size, fd, p.size <= (4ULL << 30));
         close(fd);
         return rc;
     }
