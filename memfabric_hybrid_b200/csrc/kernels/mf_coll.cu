@@ -57,12 +57,13 @@ __device__ __forceinline__ bool aligned16(const void *p) { return (reinterpret_c
 
 // dst[i] = (TD)(src[i] * scale) for i in [beg, end): 16-byte vectors where both ends allow it
 template <typename TS, typename TD>
-__device__ __forceinline__ void cta_convert_copy(const TS *src, TD *dst, uint64_t beg, uint64_t end, float scale)
+__device__ __forceinline__ void cta_convert_copy(const TS *__restrict__ src, TD *__restrict__ dst, uint64_t beg, uint64_t end, float scale)
 {
     constexpr int G = 8;  // elements per step: one 16-byte vector of the narrower type
     uint64_t vend = beg;
     if (aligned16(src + beg) && aligned16(dst + beg)) {
         vend = beg + (end - beg) / G * G;
+#pragma unroll 4
         for (uint64_t i = beg + (uint64_t)threadIdx.x * G; i < vend; i += (uint64_t)blockDim.x * G) {
             float f[G];
             if (Vec<TS>::N == G) {
@@ -118,6 +119,40 @@ template <typename T> __device__ __forceinline__ void cta_raw_copy(const T *src,
         for (; i < vend; i += step) *reinterpret_cast<uint4 *>(dst + i) = __ldcg(reinterpret_cast<const uint4 *>(src + i));
     }
     for (uint64_t i = vend + threadIdx.x; i < end; i += blockDim.x) dst[i] = src[i];
+}
+
+// One source range to several destinations (all-gather, broadcast): every 16-byte vector is loaded ONCE, four
+// independent loads in flight per thread, and stored to each destination in turn, so that all peers fill at the same
+// time and the source is not re-read per peer. Same element type on both sides, no scaling; falls back to
+// element-wise copies when an address is not 16-byte aligned.
+template <typename T> __device__ __forceinline__ void cta_fanout_copy(const T *src, T *const *dsts, uint32_t ndst, uint64_t beg, uint64_t end)
+{
+    constexpr int VN = 16 / sizeof(T);
+    bool al = aligned16(src + beg);
+    for (uint32_t k = 0; k < ndst; k++) al = al && aligned16(dsts[k] + beg);
+    uint64_t vend = beg;
+    if (al) {
+        vend = beg + (end - beg) / VN * VN;
+        const uint64_t step = (uint64_t)blockDim.x * VN;
+        uint64_t i = beg + (uint64_t)threadIdx.x * VN;
+        for (; i + 3 * step < vend; i += 4 * step) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = __ldcs(reinterpret_cast<const uint4 *>(src + i + u * step));
+            for (uint32_t k = 0; k < ndst; k++) {
+#pragma unroll
+                for (int u = 0; u < 4; u++) *reinterpret_cast<uint4 *>(dsts[k] + i + u * step) = v[u];
+            }
+        }
+        for (; i < vend; i += step) {
+            const uint4 v = __ldcs(reinterpret_cast<const uint4 *>(src + i));
+            for (uint32_t k = 0; k < ndst; k++) *reinterpret_cast<uint4 *>(dsts[k] + i) = v;
+        }
+    }
+    for (uint64_t i = vend + threadIdx.x; i < end; i += blockDim.x) {
+        const T v = src[i];
+        for (uint32_t k = 0; k < ndst; k++) dsts[k][i] = v;
+    }
 }
 
 // Reduces element range [beg, end) of staging A across all ranks (offset `base` elements into A) and
@@ -609,10 +644,21 @@ template <typename T, typename TO> __global__ void __launch_bounds__(512) k_allg
     const T *in = reinterpret_cast<const T *>(a.in);
     const uint64_t ps = a.part_stride ? a.part_stride : a.n;
     const Range sub = cta_range<8>(a.n);
-    for (uint32_t k = 0; k < world; k++) {
-        const uint32_t r = (me + k) % world;
-        TO *dst = reinterpret_cast<TO *>(peer_ptr(t, r, p_out[r])) + (uint64_t)me * ps;
-        cta_convert_copy<T, TO>(in, dst, sub.beg, sub.end, a.scale);
+    if (sizeof(T) == sizeof(TO) && a.scale == 1.f) {
+        // same type, no scaling: the shard is read once and fanned out to every rank's output
+        __shared__ TO *dsts[kMaxRanks];
+        if (threadIdx.x < world) {
+            const uint32_t r = (me + threadIdx.x) % world;
+            dsts[threadIdx.x] = reinterpret_cast<TO *>(peer_ptr(t, r, p_out[r])) + (uint64_t)me * ps;
+        }
+        __syncthreads();
+        cta_fanout_copy<TO>(reinterpret_cast<const TO *>(in), dsts, world, sub.beg, sub.end);
+    } else {
+        for (uint32_t k = 0; k < world; k++) {
+            const uint32_t r = (me + k) % world;
+            TO *dst = reinterpret_cast<TO *>(peer_ptr(t, r, p_out[r])) + (uint64_t)me * ps;
+            cta_convert_copy<T, TO>(in, dst, sub.beg, sub.end, a.scale);
+        }
     }
     lane_sync(t, me, 1, a.epoch, 0x185);
 }

@@ -323,9 +323,9 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
             tc_fence_before();
             if (MODE == 2) {
                 // all four epilogue warps have stored their rows of the tile: tell the owner
-                __threadfence_system();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 128;" ::: "memory");  // orders all four warps' stores before the counting thread, whose fence + release publishes them
                 if (warp == 2 && lane == 0) {
+                    __threadfence_system();
                     const int owner = mt * BM / g.rows_per_rank;
                     const int ltile = (mt - owner * (g.rows_per_rank / BM)) * n_tiles + nt;
                     uint32_t *cnt = reinterpret_cast<uint32_t *>(peer_ptr(g.team, owner, g.rs_count_off)) + ltile;
@@ -370,10 +370,11 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
                 const uint4 val = __ldg(reinterpret_cast<const uint4 *>(g.x_local + (int64_t)rr * g.ldx + cc));
                 *reinterpret_cast<uint4 *>(dst + (int64_t)rr * g.K + cc) = val;
             }
-            __threadfence_system();
             asm volatile("bar.sync 2, 128;" ::: "memory");
             if (ct == 0) {
-                // the CTA that completes the shard for peer p raises the flag there
+                // the CTA that completes the shard for peer p raises the flag there; this thread's fence covers the copy
+                // warps' stores (ordered before it by the barrier), and the counter links the CTAs' fences together
+                __threadfence_system();
                 const uint32_t done = atomicAdd(g.push_count + p, 1u) + 1;
                 if (done == gridDim.x * g.seq) {
                     __threadfence_system();

@@ -462,9 +462,9 @@ template <int MODE, int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_g
                 }
                 if (MODE == 2) {
                     // all eight epilogue warps have stored their part of the tile: tell the owner
-                    __threadfence_system();
-                    named_bar_sync(9, 256);
+                    named_bar_sync(9, 256);  // orders all eight warps' stores before the counting thread, whose fence + release publishes them
                     if (warp == 4 && lane == 0) {
+                        __threadfence_system();
                         const int owner = row0 / g.rows_per_rank;
                         const int ltile = ((row0 - owner * g.rows_per_rank) / BM) * n_tiles + nt;
                         uint32_t *cnt = reinterpret_cast<uint32_t *>(peer_ptr(g.team, (uint32_t)owner, g.rs_count_off)) + ltile;
@@ -535,9 +535,9 @@ template <int MODE, int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_g
         }
         auto raise = [&](uint32_t p) {
             // the CTA that completes this rank's shard in the buffer of rank p raises the flag there
-            __threadfence_system();
             __syncwarp();
             if (lane == 0) {
+                __threadfence_system();  // covers the whole warp's stores (ordered before it by the warp barrier)
                 const uint32_t done = atomicAdd(g.push_count + p, 1u) + 1;
                 if (done == gridDim.x * g.seq) {
                     __threadfence_system();

@@ -98,7 +98,9 @@ __device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t epoch, 
 __device__ __forceinline__ bool lane_sync(const Team &t, uint32_t me, int phase, uint32_t epoch, uint32_t where)
 {
     __shared__ int ok_sh;
-    __threadfence_system();  // this thread's earlier stores (possibly to peers) before the flag
+    // The CTA barrier orders every thread's earlier stores (possibly to peers) before the signalling threads; their
+    // system-scope fence + release store then publishes all of them (release is cumulative). Only the few signalling
+    // threads pay for a system fence: one per thread of a 512-thread CTA cost several microseconds per handshake.
     __syncthreads();
     const uint32_t lane = blockIdx.x;
     const uint64_t off = kLaneOff + (((uint64_t)phase * kMaxCtas + lane) * kMaxRanks) * sizeof(uint32_t);
@@ -106,6 +108,7 @@ __device__ __forceinline__ bool lane_sync(const Team &t, uint32_t me, int phase,
     __syncthreads();
     if (threadIdx.x < t.world) {
         const uint32_t r = threadIdx.x;
+        __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, off)) + me, epoch);
         const uint32_t *mine = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, off)) + r;
         if (!wait_flag(mine, epoch, t.spin_limit)) {
@@ -126,8 +129,7 @@ __device__ __forceinline__ bool lane_sync_xchg(const Team &t, uint32_t me, int p
                                                uint64_t my_b, uint64_t *peer_a, uint64_t *peer_b)
 {
     __shared__ int ok_sh;
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();  // see lane_sync: the signalling threads fence for the whole CTA
     const uint32_t lane = blockIdx.x;
     const uint64_t off = kLaneOff + (((uint64_t)phase * kMaxCtas + lane) * kMaxRanks) * sizeof(uint32_t);
     const uint64_t xoff = kXchgOff + ((uint64_t)lane * kMaxRanks) * sizeof(ulonglong2);
@@ -136,6 +138,7 @@ __device__ __forceinline__ bool lane_sync_xchg(const Team &t, uint32_t me, int p
     if (threadIdx.x < t.world) {
         const uint32_t r = threadIdx.x;
         *(reinterpret_cast<ulonglong2 *>(peer_ptr(t, r, xoff)) + me) = make_ulonglong2(my_a, my_b);
+        __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, off)) + me, epoch);
         const uint32_t *mine = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, off)) + r;
         if (!wait_flag(mine, epoch, t.spin_limit)) {
@@ -157,13 +160,13 @@ __device__ __forceinline__ bool lane_sync_xchg(const Team &t, uint32_t me, int p
 __device__ __forceinline__ bool team_barrier(const Team &t, uint32_t me, uint32_t channel, uint32_t epoch)
 {
     __shared__ int ok_sh;
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();  // see lane_sync: the signalling threads fence for the whole CTA
     const uint64_t off = kBarrierOff + (uint64_t)channel * 256;
     if (threadIdx.x == 0) ok_sh = 1;
     __syncthreads();
     if (threadIdx.x < t.world) {
         const uint32_t r = threadIdx.x;
+        __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, off)) + me, epoch);
         const uint32_t *mine = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, off)) + r;
         if (!wait_flag(mine, epoch, t.spin_limit)) {
