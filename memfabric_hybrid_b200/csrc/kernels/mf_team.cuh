@@ -33,7 +33,7 @@ constexpr uint32_t kStatusOff = 0;
 constexpr uint32_t kBarrierOff = 4096;
 constexpr uint32_t kLaneOff = 128 * 1024;
 constexpr int kPhases = 4;
-//   [256 KiB, 256 KiB + 64 KiB)  address exchange [cta 0..255][rank 0..15] x {u64, u64}
+//   [256 KiB, 256 KiB + 128 KiB) address exchange [cta 0..255][rank 0..15] x 4 words {epoch, 32 bits of payload}
 constexpr uint32_t kXchgOff = 256 * 1024;
 
 enum MfStatus : uint32_t { ST_OK = 0, ST_TIMEOUT = 1, ST_BAD_ARG = 2 };
@@ -98,9 +98,10 @@ __device__ __forceinline__ bool wait_flag(const uint32_t *flag, uint32_t epoch, 
 __device__ __forceinline__ bool lane_sync(const Team &t, uint32_t me, int phase, uint32_t epoch, uint32_t where)
 {
     __shared__ int ok_sh;
-    // The CTA barrier orders every thread's earlier stores (possibly to peers) before the signalling threads; their
-    // system-scope fence + release store then publishes all of them (release is cumulative). Only the few signalling
-    // threads pay for a system fence: one per thread of a 512-thread CTA cost several microseconds per handshake.
+    // The CTA barrier orders every thread's earlier stores (possibly to peers) before the signalling threads, whose
+    // system-scope release store then publishes all of them (release is cumulative). Only the few signalling threads
+    // pay for system-scope ordering: a fence in every thread of a 512-thread CTA cost several microseconds per
+    // handshake, and a separate fence in front of the release store about three more.
     __syncthreads();
     const uint32_t lane = blockIdx.x;
     const uint64_t off = kLaneOff + (((uint64_t)phase * kMaxCtas + lane) * kMaxRanks) * sizeof(uint32_t);
@@ -108,7 +109,6 @@ __device__ __forceinline__ bool lane_sync(const Team &t, uint32_t me, int phase,
     __syncthreads();
     if (threadIdx.x < t.world) {
         const uint32_t r = threadIdx.x;
-        __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, off)) + me, epoch);
         const uint32_t *mine = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, off)) + r;
         if (!wait_flag(mine, epoch, t.spin_limit)) {
@@ -120,36 +120,59 @@ __device__ __forceinline__ bool lane_sync(const Team &t, uint32_t me, int phase,
     return ok_sh != 0;
 }
 
-// lane_sync that also swaps two 64-bit values (buffer offsets inside the senders' slots) between the
-// CTAs of one lane: thread r stores this rank's pair into rank r's exchange row before it raises the
-// flag there (the release orders the two), and reads rank r's pair from the own row after the acquire.
-// peer_a / peer_b are shared-memory arrays of kMaxRanks entries, valid for every thread on return.
-// The row is reused by the next call: callers end with another lane_sync, after which nobody reads it.
+// Swaps two 64-bit values (buffer offsets inside the senders' slots) between the CTAs of one lane, and with that tells
+// every peer that this rank has entered the call. Nothing here needs release ordering (no data written by this call
+// has to be visible yet), so it is done with flag-carrying words: each value travels as two 8-byte words
+// {epoch, 32 bits of payload} written with relaxed system-scope stores (an aligned 8-byte store arrives whole), and the
+// receiver polls its own row until all four words of a peer carry this call's epoch. One NVLink crossing, no fence.
+// peer_a / peer_b are shared-memory arrays of kMaxRanks entries, valid for every thread on return. A row is rewritten
+// by the next call only: callers end with a lane_sync, which a peer passes after it has read its row.
+__device__ __forceinline__ void st_relaxed_sys_u64(uint64_t *p, uint64_t v)
+{
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_relaxed_sys_u64(const uint64_t *p)
+{
+    uint64_t v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
 __device__ __forceinline__ bool lane_sync_xchg(const Team &t, uint32_t me, int phase, uint32_t epoch, uint32_t where, uint64_t my_a,
                                                uint64_t my_b, uint64_t *peer_a, uint64_t *peer_b)
 {
+    (void)phase;
     __shared__ int ok_sh;
-    __syncthreads();  // see lane_sync: the signalling threads fence for the whole CTA
     const uint32_t lane = blockIdx.x;
-    const uint64_t off = kLaneOff + (((uint64_t)phase * kMaxCtas + lane) * kMaxRanks) * sizeof(uint32_t);
-    const uint64_t xoff = kXchgOff + ((uint64_t)lane * kMaxRanks) * sizeof(ulonglong2);
+    const uint64_t xoff = kXchgOff + ((uint64_t)lane * kMaxRanks) * 32;  // 4 words of 8 bytes per (lane, sender)
     if (threadIdx.x == 0) ok_sh = 1;
     __syncthreads();
     if (threadIdx.x < t.world) {
         const uint32_t r = threadIdx.x;
-        *(reinterpret_cast<ulonglong2 *>(peer_ptr(t, r, xoff)) + me) = make_ulonglong2(my_a, my_b);
-        __threadfence_system();
-        st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, off)) + me, epoch);
-        const uint32_t *mine = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, off)) + r;
-        if (!wait_flag(mine, epoch, t.spin_limit)) {
+        const uint64_t tag = (uint64_t)epoch << 32;
+        uint64_t *to = reinterpret_cast<uint64_t *>(peer_ptr(t, r, xoff)) + (uint64_t)me * 4;
+        st_relaxed_sys_u64(to + 0, tag | (uint32_t)my_a);
+        st_relaxed_sys_u64(to + 1, tag | (uint32_t)(my_a >> 32));
+        st_relaxed_sys_u64(to + 2, tag | (uint32_t)my_b);
+        st_relaxed_sys_u64(to + 3, tag | (uint32_t)(my_b >> 32));
+        const uint64_t *row = reinterpret_cast<const uint64_t *>(peer_ptr(t, me, xoff)) + (uint64_t)r * 4;
+        uint64_t w[4] = {0, 0, 0, 0};
+        bool got = false;
+        for (uint32_t i = 0; i < t.spin_limit && !got; i++) {
+#pragma unroll
+            for (int k = 0; k < 4; k++) w[k] = ld_relaxed_sys_u64(row + k);
+            got = (uint32_t)(w[0] >> 32) == epoch && (uint32_t)(w[1] >> 32) == epoch && (uint32_t)(w[2] >> 32) == epoch &&
+                  (uint32_t)(w[3] >> 32) == epoch;
+            if (!got && i > 64) __nanosleep(i > 4096 ? 256 : 32);
+        }
+        if (!got) {
             ok_sh = 0;
             report_timeout(t, me, where, epoch);
             peer_a[r] = 0;
             peer_b[r] = 0;
         } else {
-            const volatile ulonglong2 *row = reinterpret_cast<const volatile ulonglong2 *>(peer_ptr(t, me, xoff)) + r;
-            peer_a[r] = row->x;
-            peer_b[r] = row->y;
+            peer_a[r] = (w[0] & 0xFFFFFFFFull) | (w[1] << 32);
+            peer_b[r] = (w[2] & 0xFFFFFFFFull) | (w[3] << 32);
         }
     }
     __syncthreads();
@@ -166,7 +189,6 @@ __device__ __forceinline__ bool team_barrier(const Team &t, uint32_t me, uint32_
     __syncthreads();
     if (threadIdx.x < t.world) {
         const uint32_t r = threadIdx.x;
-        __threadfence_system();
         st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, off)) + me, epoch);
         const uint32_t *mine = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, off)) + r;
         if (!wait_flag(mine, epoch, t.spin_limit)) {

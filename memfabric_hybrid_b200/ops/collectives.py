@@ -96,7 +96,9 @@ class Communicator:
             # a cooperative launch of world x ctas blocks must be co-resident
             self.max_ctas = max(1, min(self.max_ctas, sms // heap.world))  # one 512-thread CTA per SM is always resident
         self._meta = None
-        self.no_multicast = False  # set to keep all-reduce on peer loads/stores even when the heap has a multicast alias
+        # Variant choice when the heap has an NVLink multicast alias: None = by size and world (see _multicast), True /
+        # False = always / never (the benchmark measures both).
+        self.multicast = None
 
     # ------------------------------------------------------------------ helpers
     def _next(self):
@@ -117,6 +119,27 @@ class Communicator:
         else:
             c = self.max_ctas
         return max(1, min(c, self.max_ctas))
+
+    @property
+    def no_multicast(self) -> bool:
+        return self.multicast is False
+
+    @no_multicast.setter
+    def no_multicast(self, v: bool) -> None:
+        self.multicast = False if v else None
+
+    def _multicast(self, kind: str, nbytes: int) -> bool:
+        """Whether a direct-mode collective goes through the multicast alias (in-switch reduction / one store reaching
+        every rank) or through peer loads and stores. Measured on B200 + NVSwitch: with 2 GPUs the switch has nothing to
+        save (one peer) and the peer kernels are faster at every size; from 4 GPUs on the in-switch all-reduce wins once
+        the message is large enough to be bandwidth-bound; reduce-scatter and all-gather move the same bytes either way."""
+        if self.heap.mc_base == 0:
+            return False
+        if self.multicast is not None:
+            return bool(self.multicast)
+        if kind == "all_reduce":
+            return self.world >= 4 and nbytes >= (1 << 20)
+        return False
 
     def _local(self, t: torch.Tensor):
         """(address of rank 0's buffer, per-rank stride in bytes, per-rank element count)."""
@@ -161,7 +184,7 @@ class Communicator:
             epoch, stage = self._next()
             args = self._args(x, out, n, epoch, stage, scale, op, 0, 1)
             # with a multicast alias of the heap the switch does the adding (sum of one floating type, no cast)
-            mc = self.heap.mc_base != 0 and op == "sum" and od == x.dtype and x.dtype != torch.int32 and not self.no_multicast
+            mc = op == "sum" and od == x.dtype and x.dtype != torch.int32 and self._multicast("all_reduce", n * es)
             args.zero_copy = 3 if mc else 2
             _check(_cu().mf_coll_launch(0, DT[x.dtype], DT[od], C.byref(args), self._ctas(n * es), 512, _stream()), "all_reduce (direct)")
             return out
@@ -193,7 +216,7 @@ class Communicator:
         if n * es > DIRECT_MIN and self._in_heap(x):
             epoch, stage = self._next()
             args = self._args(x, out, n, epoch, stage, scale, op)
-            mc = self.heap.mc_base != 0 and op == "sum" and x.dtype != torch.int32 and not self.no_multicast and \
+            mc = op == "sum" and x.dtype != torch.int32 and self._multicast("reduce_scatter", n * es) and \
                 (od == x.dtype or (x.dtype == torch.float32 and od == torch.bfloat16))
             args.zero_copy = 3 if mc else 2
             _check(_cu().mf_coll_launch(1, DT[x.dtype], DT[od], C.byref(args), self._ctas(n * es), 512, _stream()), "reduce_scatter (direct)")
@@ -226,7 +249,7 @@ class Communicator:
         if m * self.world * oes > DIRECT_MIN and self._in_heap(out):
             epoch, stage = self._next()
             args = self._args(x, out, m, epoch, stage, scale)
-            args.zero_copy = 3 if (self.heap.mc_base != 0 and not self.no_multicast) else 2
+            args.zero_copy = 3 if self._multicast("all_gather", m * self.world * oes) else 2
             _check(_cu().mf_coll_launch(2, DT[x.dtype], DT[od], C.byref(args), self._ctas(m * self.world * oes), 512, _stream()),
                    "all_gather (direct)")
             return out

@@ -66,10 +66,10 @@ def _close(got: torch.Tensor, want: torch.Tensor, rel: float) -> bool:
 
 def collectives(comm, world, flush, max_bytes=1 << 30):
     """all-reduce (+ fused 1/N scale), reduce-scatter and all-gather, bf16 and fp32, 1 KiB - 1 GiB in powers of two, tensors
-    inside the symmetric heap (what the zbal allocator hands out: peers read and write them in place). "us" is the default
-    path of the library (through the NVLink multicast alias when the heap has one); "peer_us" the same call on plain peer
-    loads and stores when both exist; "nccl_us" torch.distributed NCCL on the same bytes (with the separate scale kernel
-    that the fused epilogue replaces)."""
+    inside the symmetric heap (what the zbal allocator hands out: peers read and write them in place). "us" is what the
+    library's selector runs; when the heap has an NVLink multicast alias, "peer_us" and "mc_us" are the same call forced onto
+    plain peer loads / stores and onto the multicast alias; "nccl_us" torch.distributed NCCL on the same bytes (with the
+    separate scale kernel that the fused epilogue replaces)."""
     out = []
     heap = comm.heap
     mark = heap.mark()
@@ -140,14 +140,16 @@ def collectives(comm, world, flush, max_bytes=1 << 30):
                     row["verified"] = _close(ho[:m] if op == "reduce_scatter" else ho, want, tol)
                 us = _timed(ours, iters, 2, fl) * 1e3
                 row["us"] = round(us, 1)
-                if mc:
-                    comm.no_multicast = True
+                if mc and nbytes > (256 << 10):
+                    # both variants forced, next to what the library's selector chose ("us")
+                    comm.multicast = False
                     row["peer_us"] = round(_timed(ours, iters, 2, fl) * 1e3, 1)
-                    comm.no_multicast = False
-                    row["multicast"] = True
+                    comm.multicast = True
+                    row["mc_us"] = round(_timed(ours, iters, 2, fl) * 1e3, 1)
+                    comm.multicast = None
                 if nccl is not None:
                     row["nccl_us"] = round(_timed(nccl, iters, 2, fl) * 1e3, 1)
-                    best = min(row["us"], row.get("peer_us", row["us"]))
+                    best = row["us"]
                     row["vs_nccl"] = round(row["nccl_us"] / best, 3)
                     row["roofline_frac"] = round(floor_us / best, 3)
                     if op == "allreduce_scaled":

@@ -161,6 +161,8 @@ def _real_ranks(rank, world, url, sync):
     from memfabric_hybrid_b200.ops.collectives import Communicator
     heap = SymmetricHeap(url, world, rank, rank % torch.cuda.device_count(), 128 << 20)
     c = Communicator(heap, stage_bytes=8 << 20)
+    if os.environ.get("MF_SHM_MULTICAST"):
+        c.multicast = True      # force the multicast kernels whatever the world size (the selector prefers peer loads / stores on 2 GPUs)
     def draw(r, n):
         return torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(1000 * r + n % 997)).to(torch.bfloat16)
 
