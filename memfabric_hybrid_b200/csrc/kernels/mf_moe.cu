@@ -182,6 +182,8 @@ __device__ __forceinline__ void dispatch_preload(const DispatchArgs &a, uint4 &l
     }
 }
 
+constexpr int kTokBatch = 32;  // tokens whose routing table a CTA resolves in one pass
+
 __device__ __forceinline__ void dispatch_body(const DispatchArgs &a, uint4 nxt_lo, uint4 nxt_hi)
 {
     const Team &t = a.team;
@@ -190,101 +192,120 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs &a, uint4 nxt_l
     const int groups = H / kQuantGroup;
     const int vec = threadIdx.x;          // 16-element vector index inside the row
     const int vecs = H / 16;
-    __shared__ int dst_rank[16];
-    __shared__ int dst_pos[16];
-    __shared__ float dst_w[16];
-    // the row of the NEXT token is fetched while the stores of the current one drain: the loop is otherwise a chain
-    // of HBM latency (row load) and NVLink issue (eight peer stores per thread)
-    for (int tok = blockIdx.x; tok < a.sh.T; tok += gridDim.x) {
-        if (threadIdx.x < K) {
-            const int e = a.topk_idx[tok * K + threadIdx.x];
-            if (e >= 0) {
-                const int pos = a.put_off[e] + a.send_idx[tok * K + threadIdx.x];
-                dst_rank[threadIdx.x] = pos < a.sh.max_recv ? e / El : -1;
-                if (pos >= a.sh.max_recv) atomicCAS(a.status, 0, 0x401);  // receive buffer too small: dropped, reported
-                dst_pos[threadIdx.x] = pos;
-                dst_w[threadIdx.x] = a.topk_w[tok * K + threadIdx.x];
-            } else {
-                dst_rank[threadIdx.x] = -1;
+    // Routing table of the next kTokBatch tokens of this CTA (destination rank, row there, weight), resolved by all
+    // threads at once: the chain expert id -> put offset -> position is two dependent global loads, which would
+    // otherwise sit in front of every single token.
+    __shared__ int dst_rank[kTokBatch][16];
+    __shared__ int dst_pos[kTokBatch][16];
+    __shared__ float dst_w[kTokBatch][16];
+    __shared__ __align__(16) float s_scale[2][64];  // the row's 1 x 128 scales, leaving as one burst per destination
+    const int stride = (int)gridDim.x;
+    for (int base = blockIdx.x; base < a.sh.T; base += stride * kTokBatch) {
+        __syncthreads();  // the previous batch's table is no longer read
+        for (int e = threadIdx.x; e < kTokBatch * K; e += blockDim.x) {
+            const int j = e / K, k = e - j * K;
+            const int tok = base + j * stride;
+            int rk = -1;
+            if (tok < a.sh.T) {
+                const int ex = a.topk_idx[tok * K + k];
+                if (ex >= 0) {
+                    const int pos = a.put_off[ex] + a.send_idx[tok * K + k];
+                    rk = pos < a.sh.max_recv ? ex / El : -1;
+                    if (pos >= a.sh.max_recv) atomicCAS(a.status, 0, 0x401);  // receive buffer too small: dropped, reported
+                    dst_pos[j][k] = pos;
+                    dst_w[j][k] = a.topk_w[tok * K + k];
+                }
             }
+            dst_rank[j][k] = rk;
         }
         __syncthreads();
-        uint4 q;
-        uint4 raw_lo = make_uint4(0, 0, 0, 0), raw_hi = make_uint4(0, 0, 0, 0);
-        float scale;
-        {
-            float f[16];
+        // the row of the NEXT token is fetched while the stores of the current one drain
+        for (int j = 0; j < kTokBatch; j++) {
+            const int tok = base + j * stride;
+            if (tok >= a.sh.T) break;
+            uint4 q;
+            uint4 raw_lo = make_uint4(0, 0, 0, 0), raw_hi = make_uint4(0, 0, 0, 0);
+            float *sc = s_scale[j & 1];
+            {
+                float f[16];
 #pragma unroll
-            for (int i = 0; i < 16; i++) f[i] = 0.f;
-            if (vec < vecs) {
-                const uint4 lo = nxt_lo, hi = nxt_hi;
-                raw_lo = lo;
-                raw_hi = hi;
-                const int nxt = tok + (int)gridDim.x;
-                if (nxt < a.sh.T) {
-                    const uint4 *src = reinterpret_cast<const uint4 *>(a.x + (int64_t)nxt * H + vec * 16);
-                    nxt_lo = __ldg(src);
-                    nxt_hi = __ldg(src + 1);
+                for (int i = 0; i < 16; i++) f[i] = 0.f;
+                if (vec < vecs) {
+                    const uint4 lo = nxt_lo, hi = nxt_hi;
+                    raw_lo = lo;
+                    raw_hi = hi;
+                    const int nxt = tok + stride;
+                    if (nxt < a.sh.T) {
+                        const uint4 *src = reinterpret_cast<const uint4 *>(a.x + (int64_t)nxt * H + vec * 16);
+                        nxt_lo = __ldg(src);
+                        nxt_hi = __ldg(src + 1);
+                    }
+                    const __nv_bfloat162 *h0 = reinterpret_cast<const __nv_bfloat162 *>(&lo);
+                    const __nv_bfloat162 *h1 = reinterpret_cast<const __nv_bfloat162 *>(&hi);
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        float2 p = __bfloat1622float2(h0[i]);
+                        f[2 * i] = p.x;
+                        f[2 * i + 1] = p.y;
+                        p = __bfloat1622float2(h1[i]);
+                        f[8 + 2 * i] = p.x;
+                        f[8 + 2 * i + 1] = p.y;
+                    }
                 }
-                const __nv_bfloat162 *h0 = reinterpret_cast<const __nv_bfloat162 *>(&lo);
-                const __nv_bfloat162 *h1 = reinterpret_cast<const __nv_bfloat162 *>(&hi);
+                float amax = 0.f;
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    float2 p = __bfloat1622float2(h0[i]);
-                    f[2 * i] = p.x;
-                    f[2 * i + 1] = p.y;
-                    p = __bfloat1622float2(h1[i]);
-                    f[8 + 2 * i] = p.x;
-                    f[8 + 2 * i + 1] = p.y;
+                for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(f[i]));
+                // the 8 threads of a 128-group are consecutive lanes of one warp; every lane takes part
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                const float scale = pow2_scale_e4m3(amax);   // a power of two: the expert GEMM feeds it to the tensor core as a UE8M0 byte
+                const float mul = 1.f / scale;
+                q.x = pack4_e4m3(f[0], f[1], f[2], f[3], mul);
+                q.y = pack4_e4m3(f[4], f[5], f[6], f[7], mul);
+                q.z = pack4_e4m3(f[8], f[9], f[10], f[11], mul);
+                q.w = pack4_e4m3(f[12], f[13], f[14], f[15], mul);
+                if (!a.raw_bf16 && vec < vecs && (vec & 7) == 0) sc[vec >> 3] = scale;
+            }
+            if (!a.raw_bf16) __syncthreads();  // the row's scales are complete (the buffers alternate: one barrier per token)
+            for (int k = 0; k < K; k++) {
+                const int d = dst_rank[j][k];
+                if (d < 0) continue;
+                const int64_t pos = dst_pos[j][k];
+                if (vec < vecs) {
+                    if (a.raw_bf16) {
+                        uint4 *row = reinterpret_cast<uint4 *>(peer_ptr(t, d, a.hp.recv_x) + pos * H * 2 + vec * 32);
+                        row[0] = raw_lo;
+                        row[1] = raw_hi;
+                    } else {
+                        *reinterpret_cast<uint4 *>(peer_ptr(t, d, a.hp.recv_x) + pos * H + vec * 16) = q;
+                    }
+                }
+                if (!a.raw_bf16) {
+                    // scales: groups * 4 bytes, contiguous in the receiver's array: 16-byte stores from the last warp's lanes
+                    // (one or two NVLink packets per row instead of one partial write per 128-group)
+                    const int sv = threadIdx.x - ((int)blockDim.x - 32);
+                    float *srow = reinterpret_cast<float *>(peer_ptr(t, d, a.hp.recv_scale)) + pos * groups;
+                    if (sv >= 0) {
+                        if (((pos * groups) & 3) == 0 && (groups & 3) == 0) {
+                            if (sv < groups / 4) reinterpret_cast<float4 *>(srow)[sv] = reinterpret_cast<const float4 *>(sc)[sv];
+                        } else {
+                            for (int g = sv; g < groups; g += 32) srow[g] = sc[g];
+                        }
+                    }
+                }
+                if (threadIdx.x == 0) {
+                    int4 info = make_int4((int)me, tok, k, __float_as_int(dst_w[j][k]));
+                    reinterpret_cast<int4 *>(peer_ptr(t, d, a.hp.recv_info))[pos] = info;
                 }
             }
-            float amax = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(f[i]));
-            // the 8 threads of a 128-group are consecutive lanes of one warp; every lane takes part
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-            scale = pow2_scale_e4m3(amax);   // a power of two: the expert GEMM feeds it to the tensor core as a UE8M0 byte
-            const float mul = 1.f / scale;
-            uint32_t w[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                uint32_t b = 0;
-#pragma unroll
-                for (int j = 0; j < 4; j++)
-                    b |= (uint32_t)__nv_cvt_float_to_fp8(f[4 * i + j] * mul, __NV_SATFINITE, __NV_E4M3) << (8 * j);
-                w[i] = b;
-            }
-            q = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        for (int k = 0; k < K; k++) {
-            const int d = dst_rank[k];
-            if (d < 0) continue;
-            const int64_t pos = dst_pos[k];
-            if (vec < vecs) {
-                if (a.raw_bf16) {
-                    uint4 *row = reinterpret_cast<uint4 *>(peer_ptr(t, d, a.hp.recv_x) + pos * H * 2 + vec * 32);
-                    row[0] = raw_lo;
-                    row[1] = raw_hi;
-                } else {
-                    uint8_t *row = peer_ptr(t, d, a.hp.recv_x) + pos * H;
-                    *reinterpret_cast<uint4 *>(row + vec * 16) = q;
-                    if ((vec & 7) == 0)
-                        reinterpret_cast<float *>(peer_ptr(t, d, a.hp.recv_scale))[pos * groups + (vec >> 3)] = scale;
-                }
-            }
-            if (threadIdx.x == 0) {
-                int4 info = make_int4((int)me, tok, k, __float_as_int(dst_w[k]));
-                reinterpret_cast<int4 *>(peer_ptr(t, d, a.hp.recv_info))[pos] = info;
-            }
-        }
-        __syncthreads();
     }
-    // the CTA that finishes last tells every peer that all of this rank's rows have been stored
-    __threadfence_system();
+    // the CTA that finishes last tells every peer that all of this rank's rows have been stored (the barrier orders the
+    // CTA's stores before thread 0, whose system fence covers them; the counter links the CTAs' fences)
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();
         const uint32_t done = atomicAdd(a.done_count, 1u) + 1;
         // seq > 0: the counter only grows and the host numbers the calls; seq == 0: the last CTA puts it back
         // to zero, so the same launch parameters work again (CUDA-graph replay)
