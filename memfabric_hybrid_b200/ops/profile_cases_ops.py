@@ -120,3 +120,62 @@ def case_moe(args) -> None:
     torch.cuda.synchronize()
     heap.close()
     SymmetricHeap.shutdown()
+
+
+def case_gemm_fp8(args) -> None:
+    """Grouped fp8 GEMMs of the DeepSeek-V3 expert FFN (gate/up: N 4096, K 7168; down: N 7168, K 2048) on --tokens rows per
+    expert and 8 experts (operands 290 MB / 130 MB: larger than L2): the 128 x 256 kernel with tensor-core block scaling
+    (SwiGLU + re-quantisation epilogue, plain epilogue) next to the 128 x 128 kernel that applies the scales in registers.
+    A band of rows is checked against an fp32 reference of the dequantised operands."""
+    from . import gemm, moe as M
+    cu = M._cu()
+    s = torch.cuda.current_stream().cuda_stream
+    st = gemm.status_word()
+    G, per = 8, max(128, args.tokens)
+    R = G * per
+    off = (torch.arange(0, G + 1, dtype=torch.int32, device="cuda") * per).contiguous()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    gen = torch.Generator("cuda").manual_seed(1)
+    out = []
+    for name, N, K, epi in (("gate_up_swiglu_requant", 4096, 7168, 3), ("down_plain", 7168, 2048, 0)):
+        aq = (torch.randn(R, K, device="cuda", generator=gen) * 4).to(torch.float8_e4m3fn)
+        bq = (torch.randn(G, N, K, device="cuda", generator=gen) * 4).to(torch.float8_e4m3fn)
+        a_s = torch.exp2(torch.randint(-3, 4, (R, K // 128), device="cuda", generator=gen).float())
+        b_s = torch.exp2(torch.randint(-3, 4, (G, N // 128, K // 128), device="cuda", generator=gen).float())
+        flops = 2.0 * R * N * K
+        if epi == 3:
+            bi = M.interleave_gate_up_fp8(bq.view(torch.uint8), 128)
+            hq = torch.empty(R, N // 2, dtype=torch.uint8, device="cuda")
+            hs = torch.empty(R, N // 256, dtype=torch.float32, device="cuda")
+            new = lambda: cu.mf_grouped_gemm_fp8_mx(aq.data_ptr(), a_s.data_ptr(), R, bi.data_ptr(), b_s.data_ptr(), off.data_ptr(), G, N, K, hq.data_ptr(),
+                                                    N // 2, hs.data_ptr(), 3, None, None, 0, 1, st.data_ptr(), gemm.sm_count(), s)
+        else:
+            o_new = torch.empty(R, N, dtype=torch.bfloat16, device="cuda")
+            new = lambda: cu.mf_grouped_gemm_fp8_mx(aq.data_ptr(), a_s.data_ptr(), R, bq.data_ptr(), b_s.data_ptr(), off.data_ptr(), G, N, K, o_new.data_ptr(), N,
+                                                    None, 0, None, None, 0, 1, st.data_ptr(), gemm.sm_count(), s)
+        o_old = torch.empty(R, N, dtype=torch.bfloat16, device="cuda")
+        old = lambda: cu.mf_grouped_gemm_fp8(aq.data_ptr(), a_s.data_ptr(), R, bq.data_ptr(), b_s.data_ptr(), off.data_ptr(), G, N, K, o_old.data_ptr(), N, 0,
+                                             None, None, 0, 1, st.data_ptr(), gemm.sm_count(), s)
+        assert new() == 0 and old() == 0
+        torch.cuda.synchronize()
+        gemm.check_status()
+        # reference on the first 64 rows of the last expert
+        r0 = (G - 1) * per
+        ad = (aq[r0:r0 + 64].float().view(64, K // 128, 128) * a_s[r0:r0 + 64, :, None]).view(64, K)
+        bd = (bq[G - 1].float().view(N // 128, 128, K // 128, 128) * b_s[G - 1][:, None, :, None]).view(N, K)
+        ref = ad @ bd.t()
+        if epi == 3:
+            ref = torch.nn.functional.silu(ref[:, :N // 2]) * ref[:, N // 2:]
+            got = (hq[r0:r0 + 64].view(torch.float8_e4m3fn).float().view(64, N // 256, 128) * hs[r0:r0 + 64, :, None]).view(64, N // 2)
+            tol = 0.08
+        else:
+            got = o_new[r0:r0 + 64].float()
+            tol = 0.02
+        rm = ref.abs().amax(dim=1, keepdim=True)
+        assert ((got - ref).abs() <= tol * rm + 1e-3).all(), float(((got - ref).abs() / (rm + 1e-9)).max())
+        ms_new = _time(new, args.iters, 2, flush)
+        ms_old = _time(old, args.iters, 2, flush)
+        gemm.check_status()
+        out.append({"gemm": name, "rows": R, "N": N, "K": K, "block_scaled_ms": round(ms_new, 4), "block_scaled_tflops": round(flops / ms_new / 1e9, 1),
+                    "scales_in_registers_ms": round(ms_old, 4), "scales_in_registers_tflops": round(flops / ms_old / 1e9, 1)})
+    print(json.dumps({"case": "gemm_fp8", "results": out}))
