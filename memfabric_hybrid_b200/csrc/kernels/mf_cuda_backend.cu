@@ -505,6 +505,25 @@ public:
             const uint64_t perItem = std::max<uint64_t>(1, (2ull * (uint64_t)std::max(1, grid_) + n - 1) / n);
             dim3 grid((unsigned)std::min<uint64_t>({perItem, (maxUnits + 15) / 16, 65535ull}), n);  // a CTA takes at least 16 units per step
             cudaStream_t st = (cudaStream_t)s;
+            // units of 128 elements on aligned addresses (the fp8 1 x 128 format, and int8 with that unit): the kernel
+            // that keeps eight loads per lane in flight
+            bool fast = unit == 128;
+            for (uint32_t i = 0; i < n && fast; i++) {
+                const QuantItem &q0 = items[off + i];
+                fast = (q0.src & 15) == 0 && (q0.dst & 7) == 0 && (q0.scale & 3) == 0 && (q0.elems % 128) == 0 && q0.elems != 0;
+            }
+            if (fast) {
+                dim3 g2((unsigned)std::min<uint64_t>({perItem, (maxUnits + 127) / 128, 65535ull}), n);  // a CTA takes 128 units per step
+                if (inputFp16) {
+                    if (mode == 0) mfk::mf_xcopy_quant128_kernel<__half, 0><<<g2, 256, 0, st>>>(q + off);
+                    else mfk::mf_xcopy_quant128_kernel<__half, 1><<<g2, 256, 0, st>>>(q + off);
+                } else {
+                    if (mode == 0) mfk::mf_xcopy_quant128_kernel<__nv_bfloat16, 0><<<g2, 256, 0, st>>>(q + off);
+                    else mfk::mf_xcopy_quant128_kernel<__nv_bfloat16, 1><<<g2, 256, 0, st>>>(q + off);
+                }
+                RT_CHECK(cudaGetLastError(), "xcopy quant launch");
+                continue;
+            }
             if (inputFp16) {
                 if (mode == 0) mfk::mf_xcopy_quant_kernel<__half, 0><<<grid, 256, 0, st>>>(q + off, unit);
                 else mfk::mf_xcopy_quant_kernel<__half, 1><<<grid, 256, 0, st>>>(q + off, unit);

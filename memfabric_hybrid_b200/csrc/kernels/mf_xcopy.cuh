@@ -310,4 +310,70 @@ __global__ void __launch_bounds__(256) mf_xcopy_quant_kernel(const QuantItem *__
     }
 }
 
+// Fast path of the quantising copy for the common shape: units of 128 elements, source 16-byte aligned, destination
+// 8-byte aligned, element count a multiple of 128. A half-warp (16 lanes x 16 bytes = one unit per load instruction)
+// takes EIGHT consecutive units per step: eight independent loads per lane are in flight before the first reduction,
+// the eight maxima are reduced by interleaved shuffles, the eight factors leave as two 16-byte stores. The kernel above
+// keeps two loads per lane in flight and is bound by the latency of each step, not by memory or instruction issue.
+template <typename In, int MODE>
+__global__ void __launch_bounds__(256) mf_xcopy_quant128_kernel(const QuantItem *__restrict__ items)
+{
+    __shared__ QuantItem it;
+    if (threadIdx.x == 0) it = items[blockIdx.y];
+    __syncthreads();
+    constexpr int J = 8;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t sub = lane >> 4, sl = lane & 15;
+    const uint64_t units = it.elems / 128;
+    const uint4 *src = reinterpret_cast<const uint4 *>(it.src);   // 16 vectors per unit
+    uint2 *dst = reinterpret_cast<uint2 *>(it.dst);               // 16 x 8 bytes per unit
+    float *scales = reinterpret_cast<float *>(it.scale);
+    const float qmax = MODE == 0 ? 127.f : 448.f;
+    const bool s16 = (it.scale & 15) == 0;
+    const uint64_t per_cta = 8ull * 2 * J;  // warps x half-warps x units
+    for (uint64_t base = (uint64_t)blockIdx.x * per_cta + ((uint64_t)warp * 2 + sub) * J; base < units; base += (uint64_t)gridDim.x * per_cta) {
+        uint4 raw[J];
+        float amax[J];
+#pragma unroll
+        for (int j = 0; j < J; j++) {
+            const uint64_t u = base + j;
+            raw[j] = u < units ? __ldcs(src + u * 16 + sl) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int j = 0; j < J; j++) {
+            float f[8];
+            unpack8<In>(raw[j], f);
+            float m = 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; k++) m = fmaxf(m, fabsf(f[k]));
+            amax[j] = m;
+        }
+#pragma unroll
+        for (uint32_t o = 8; o > 0; o >>= 1) {
+#pragma unroll
+            for (int j = 0; j < J; j++) amax[j] = fmaxf(amax[j], __shfl_xor_sync(0xffffffffu, amax[j], o));
+        }
+        float fac[J];
+#pragma unroll
+        for (int j = 0; j < J; j++) {
+            const float mul = amax[j] > 0.f ? qmax / amax[j] : 1.f;
+            fac[j] = amax[j] > 0.f ? amax[j] / qmax : 1.f;
+            const uint64_t u = base + j;
+            if (u < units) {
+                float f[8];
+                unpack8<In>(raw[j], f);
+                __stcs(dst + u * 16 + sl, quant8<MODE>(f, mul));
+            }
+        }
+        // the eight factors of this half-warp are consecutive in the factor array
+        if (s16 && base + J <= units) {
+            if (sl < 2) reinterpret_cast<float4 *>(scales + base)[sl] = sl == 0 ? make_float4(fac[0], fac[1], fac[2], fac[3]) : make_float4(fac[4], fac[5], fac[6], fac[7]);
+        } else if (sl == 0) {
+#pragma unroll
+            for (int j = 0; j < J; j++)
+                if (base + j < units) scales[base + j] = fac[j];
+        }
+    }
+}
+
 }  // namespace mfk

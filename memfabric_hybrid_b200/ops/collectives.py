@@ -138,7 +138,9 @@ class Communicator:
         if self.multicast is not None:
             return bool(self.multicast)
         if kind == "all_reduce":
-            return self.world >= 4 and nbytes >= (1 << 20)
+            # 8 GPUs: ahead from 1 MiB on (1 MiB 25 vs 27 us, 256 MiB 645 vs 799 us); 4 GPUs: from 64 MiB on (32 MiB 119 vs 113 us,
+            # 256 MiB 641 vs 711 us)
+            return (self.world >= 8 and nbytes >= (1 << 20)) or (self.world >= 4 and nbytes >= (64 << 20))
         return False
 
     def _local(self, t: torch.Tensor):
