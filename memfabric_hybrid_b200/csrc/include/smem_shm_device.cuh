@@ -24,6 +24,10 @@
 #include <stdint.h>
 
 #define SMEM_SHM_USER_OFFSET (1u << 20)
+/* The extra context that the host set with smem_shm_set_extra_context lives inside the flag area of the rank's own
+ * slice: a 32-bit size at this offset, the bytes (at most 64 KiB) 64 bytes further on. */
+#define SMEM_SHM_EXTRA_CTX_OFFSET (896u << 10)
+#define SMEM_SHM_EXTRA_CTX_MAX 65536u
 
 typedef struct {
     uint64_t base;           /* address of rank 0's slice */
@@ -51,6 +55,18 @@ template <typename T> __device__ __forceinline__ T *smem_shm_peer_ptr(const smem
 __device__ __forceinline__ void *smem_shm_slice_ptr(const smem_shm_device_ctx_t &c, uint32_t rank, uint64_t offset)
 {
     return reinterpret_cast<void *>(c.base + (uint64_t)rank * c.symmetric_size + offset);
+}
+
+/* The user's extra context of THIS rank (set on the host with smem_shm_set_extra_context; every rank sets its own) and
+ * its size in bytes, 0 when none was set. Parity: smem_shm_get_extra_context_addr / _size of the reference's device API
+ * (src/smem/include/device/smem_shm_aicore_base_api.h:44-53). */
+__device__ __forceinline__ const void *smem_shm_get_extra_context_addr(const smem_shm_device_ctx_t &c)
+{
+    return smem_shm_slice_ptr(c, c.rank, SMEM_SHM_EXTRA_CTX_OFFSET + 64);
+}
+__device__ __forceinline__ uint32_t smem_shm_get_extra_context_size(const smem_shm_device_ctx_t &c)
+{
+    return *reinterpret_cast<const volatile uint32_t *>(smem_shm_slice_ptr(c, c.rank, SMEM_SHM_EXTRA_CTX_OFFSET));
 }
 
 __device__ __forceinline__ mfk::Team smem_shm_team(const smem_shm_device_ctx_t &c)

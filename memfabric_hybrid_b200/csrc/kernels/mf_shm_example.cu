@@ -99,3 +99,23 @@ extern "C" int mf_example_shm_allreduce(const smem_shm_device_ctx_t *ctx, const 
                                                 params, 0, (cudaStream_t)stream);
     return e == cudaSuccess ? 0 : (int)e;
 }
+
+namespace {
+__global__ void k_example_read_context(smem_shm_device_ctx_t ctx, uint8_t *out, uint32_t cap, uint32_t *size_out)
+{
+    const uint32_t n = smem_shm_get_extra_context_size(ctx);
+    const uint8_t *p = static_cast<const uint8_t *>(smem_shm_get_extra_context_addr(ctx));
+    if (threadIdx.x == 0) *size_out = n;
+    for (uint32_t i = threadIdx.x; i < n && i < cap; i += blockDim.x) out[i] = p[i];
+}
+}  // namespace
+
+// Copies this rank's extra context (smem_shm_set_extra_context) as a kernel sees it into out[0 .. cap) and its size into
+// *size_out (both device memory).
+extern "C" int mf_example_shm_read_context(const smem_shm_device_ctx_t *ctx, void *out, uint32_t cap, uint32_t *size_out, void *stream)
+{
+    if (ctx == nullptr || out == nullptr || size_out == nullptr) return -1;
+    k_example_read_context<<<1, 256, 0, (cudaStream_t)stream>>>(*ctx, static_cast<uint8_t *>(out), cap, size_out);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : (int)e;
+}

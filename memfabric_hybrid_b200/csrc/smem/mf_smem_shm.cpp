@@ -354,6 +354,19 @@ smem_shm_t smem_shm_create(uint32_t id, uint32_t rankSize, uint32_t rankId, uint
         if (LastError::Code() == 0) LastError::Set(Pub(rc), "shm %u: create failed with %d", id, rc);
         return nullptr;
     }
+    // no extra context yet: a kernel that asks for its size must read 0
+    {
+        const uint64_t at = reinterpret_cast<uint64_t>(e->gva_) + (uint64_t)e->rank_ * e->symmetric_ + SMEM_SHM_EXTRA_CTX_OFFSET;
+        hybm::DeviceBackend *dev = hybm::CurrentBackend();
+        if (localSize >= SMEM_SHM_USER_OFFSET) {   // a slice smaller than the flag area has no room for it (host-side copy only)
+            if (dev != nullptr && dev->Caps().present) {
+                dev->BindThread();
+                if (dev->MemsetAsync(at, 0, 64, nullptr) == OK) dev->StreamSync(nullptr);
+            } else {
+                memset(reinterpret_cast<void *>(at), 0, 64);
+            }
+        }
+    }
     *gva = e->gva_;
     return g_handles.Add(e);
 }
@@ -393,7 +406,23 @@ int32_t smem_shm_set_extra_context(smem_shm_t handle, const void *context, uint3
     auto e = H(handle);
     if (!e) return SMEM_INVALID_PARAM;
     if (context == nullptr || size == 0 || size > 65536) return MF_FAIL(SMEM_INVALID_PARAM, "context must be 1..65536 bytes");
-    return Pub(e->entity_->SetExtraContext(context, size));
+    int rc = e->entity_->SetExtraContext(context, size);
+    if (rc != OK) return Pub(rc);
+    // kernels read it through smem_shm_get_extra_context_addr / _size (smem_shm_device.cuh): bytes first, then the size
+    const uint64_t at = reinterpret_cast<uint64_t>(e->gva_) + (uint64_t)e->rank_ * e->symmetric_ + SMEM_SHM_EXTRA_CTX_OFFSET;
+    hybm::DeviceBackend *dev = hybm::CurrentBackend();
+    if (e->localSize_ < SMEM_SHM_USER_OFFSET) return SMEM_OK;  // no flag area in such a small slice: kernels cannot read it
+    if (dev != nullptr && dev->Caps().present) {
+        dev->BindThread();
+        alignas(16) uint32_t hdr[4] = {size, 0, 0, 0};
+        rc = dev->MemcpyAsync(at + 64, reinterpret_cast<uint64_t>(context), size, hybm::CPY_H2D, nullptr);
+        if (rc == OK) rc = dev->MemcpyAsync(at, reinterpret_cast<uint64_t>(hdr), sizeof(hdr), hybm::CPY_H2D, nullptr);
+        if (rc == OK) rc = dev->StreamSync(nullptr);
+    } else {
+        memcpy(reinterpret_cast<void *>(at + 64), context, size);
+        *reinterpret_cast<volatile uint32_t *>(at) = size;
+    }
+    return Pub(rc);
 }
 
 uint32_t smem_shm_get_global_rank(smem_shm_t handle)
