@@ -109,6 +109,9 @@ public:
     virtual int LaunchBatchCopy(const CopyItem *items, uint32_t count, void *stream, bool bulkOk = false) = 0;
     // Code left by a copy kernel whose bounded wait ran out (0: none); `clear` resets it.
     virtual uint32_t CopyStatus(bool clear) { (void)clear; return 0; }
+    // Debug aid (MF_XCOPY_DEBUG=1): the pool window the copy kernels check every descriptor against before their first
+    // access (base 0 switches the check off). Returns false when the backend has no such check.
+    virtual bool SetCopyWindow(uint64_t base, uint64_t slot, uint32_t ranks, const uint64_t *mapped) { (void)base, (void)slot, (void)ranks, (void)mapped; return false; }
     // Shape of the bulk-copy kernel (pipelines per CTA, stages per pipeline, KiB per stage); 0 pipelines
     // switches it off. Takes effect for the launches that follow.
     virtual int ConfigureBulkCopy(int pipes, int stages, int pieceKb) { (void)pipes, (void)stages, (void)pieceKb; return -1; }

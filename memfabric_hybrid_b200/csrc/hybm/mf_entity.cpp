@@ -534,6 +534,7 @@ int Entity::CopyData(const hybm_copy_params &p, hybm_data_copy_direction dir, vo
 {
     if (p.src == nullptr || p.dest == nullptr || p.dataSize == 0 || dir >= HYBM_DATA_COPY_DIRECTION_BUTT)
         return MF_FAIL(ERR_INVALID_PARAM, "copy: null address, zero size or bad direction %d", (int)dir);
+    PublishCopyWindow();
     // (the one-element vector is thread-local: a copy call is often a few microseconds of work in total)
     static thread_local std::vector<ResolvedCopy> one(1);
     one.resize(1);
@@ -549,12 +550,22 @@ int Entity::CopyData(const hybm_copy_params &p, hybm_data_copy_direction dir, vo
     return ops_->Submit(one, stream, flags, nullptr);
 }
 
+void Entity::PublishCopyWindow()
+{
+    static const bool debug = EnvInt("MF_XCOPY_DEBUG", nullptr, 0, 0, 1) != 0;
+    if (!debug || dev_ == nullptr || !hbm_ || hbm_->Base() == 0 || opt_.rankCount > 64) return;
+    uint64_t mapped[64];
+    for (uint32_t r = 0; r < opt_.rankCount; r++) mapped[r] = hbm_->MappedBytes(r);
+    dev_->SetCopyWindow(hbm_->Base(), hbm_->Slot(), opt_.rankCount, mapped);
+}
+
 int Entity::BatchCopyData(const hybm_batch_copy_params &p, hybm_data_copy_direction dir, void *stream, uint32_t flags,
                           int32_t *perItem)
 {
     if (p.sources == nullptr || p.destinations == nullptr || p.dataSizes == nullptr || p.batchSize == 0 ||
         dir >= HYBM_DATA_COPY_DIRECTION_BUTT)
         return MF_FAIL(ERR_INVALID_PARAM, "batch copy: null array, empty batch or bad direction %d", (int)dir);
+    PublishCopyWindow();
     // Hot path: every item is device<->device with at least one side in the HBM pool (KV-block put/get).
     // Pass 1 validates with arithmetic only; pass 2 streams the items into the descriptor ring.
     if (perItem == nullptr && dev_ != nullptr && hbm_ && hbm_->Base() != 0 &&

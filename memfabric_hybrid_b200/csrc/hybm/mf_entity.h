@@ -86,6 +86,7 @@ private:
     int Resolve(uint64_t addr, uint64_t len, bool isSrc, hybm_data_copy_direction dir, Endpoint &ep);
     bool InPool(const SegmentPtr &seg, uint64_t addr, uint64_t len, int &err) const;
     bool PinnedHost(uint64_t addr, uint64_t len);
+    void PublishCopyWindow();  // MF_XCOPY_DEBUG=1: hands the copy kernels the pool window they check descriptors against
     std::mutex pinMu_;
     uint64_t pinLo_ = 0, pinHi_ = 0, pinStampMs_ = 0;  // last host range found pinned and device-addressable, and when
 

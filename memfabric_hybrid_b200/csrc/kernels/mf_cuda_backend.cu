@@ -473,14 +473,35 @@ public:
             const uint32_t smem = bulkPipes_ * bulkStages_ * bulkPiece_;
             const uint32_t grid = std::min<uint32_t>((count + bulkPipes_ - 1) / bulkPipes_, (uint32_t)bulkGrid_);
             mfk::mf_xcopy_bulk_kernel<<<grid, 32 * bulkPipes_, smem, (cudaStream_t)s>>>(reinterpret_cast<const mfk::CopyItem *>(items), count,
-                                                                                      bulkStages_, bulkPiece_, copyStatus_);
+                                                                                      bulkStages_, bulkPiece_, copyStatus_, window_);
             RT_CHECK(cudaGetLastError(), "xcopy bulk launch");
             return OK;
         }
         int grid = (int)std::min<uint32_t>(count, (uint32_t)grid_);
-        mfk::mf_xcopy_batch_kernel<<<grid, mfk::kCopyThreads, 0, (cudaStream_t)s>>>(reinterpret_cast<const mfk::CopyItem *>(items), count);
+        mfk::mf_xcopy_batch_kernel<<<grid, mfk::kCopyThreads, 0, (cudaStream_t)s>>>(reinterpret_cast<const mfk::CopyItem *>(items), count,
+                                                                                    copyStatus_ != nullptr ? window_ : nullptr, copyStatus_);
         RT_CHECK(cudaGetLastError(), "xcopy batch launch");
         return OK;
+    }
+    bool SetCopyWindow(uint64_t base, uint64_t slot, uint32_t ranks, const uint64_t *mapped) override
+    {
+        if (copyStatus_ == nullptr || ranks > 64) return false;
+        if (window_ == nullptr) {
+            if (base == 0) return true;
+            void *p = nullptr;
+            if (cudaHostAlloc(&p, sizeof(mfk::CopyWindow), cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return false;
+            }
+            memset(p, 0, sizeof(mfk::CopyWindow));
+            window_ = static_cast<mfk::CopyWindow *>(p);
+        }
+        // launches already queued read the table when they run: callers change it between batches, not under them
+        window_->slot = slot;
+        window_->ranks = ranks;
+        for (uint32_t r = 0; r < 64; r++) window_->mapped[r] = (mapped != nullptr && r < ranks) ? mapped[r] : 0;
+        window_->base = base;
+        return true;
     }
     uint32_t CopyStatus(bool clear) override
     {
@@ -555,6 +576,7 @@ private:
     uint32_t bulkPipes_ = 0, bulkStages_ = 4, bulkPiece_ = 16384;
     int bulkGrid_ = 148;
     uint32_t *copyStatus_ = nullptr;
+    mfk::CopyWindow *window_ = nullptr;  // debug table of the copy kernels (pinned, device-visible), null unless MF_XCOPY_DEBUG is on
     DeviceCaps caps_;
     DriverApi drv_;
     std::mutex mu_;
@@ -581,4 +603,42 @@ extern "C" int mf_cuda_sm_count(void)
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     return sms;
+}
+
+// Self-check of the copy kernels' debug window (see mfk::CopyWindow): runs `n` descriptors (src, dst, len triples) through
+// the register-copy kernel (bulk == 0) or the bulk-copy kernel (bulk != 0) against a window described by the caller, on
+// the default stream, and returns the status word the kernel left (0: every descriptor passed, 0x7D1: at least one was
+// refused and skipped). Descriptors that fail are never dereferenced, so a test may name an address in an unmapped part
+// of the window. Returns a negative number when the launch could not be made.
+extern "C" int mf_xcopy_debug_probe(const uint64_t *triples, uint32_t n, uint64_t win_base, uint64_t slot, uint32_t ranks,
+                                    const uint64_t *mapped, int bulk)
+{
+    if (triples == nullptr || n == 0 || n > 1024 || ranks > 64) return -1;
+    void *mem = nullptr;
+    const size_t bytes = sizeof(mfk::CopyWindow) + 64 + (size_t)n * sizeof(mfk::CopyItem);
+    if (cudaHostAlloc(&mem, bytes, cudaHostAllocMapped) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return -2;
+    }
+    memset(mem, 0, bytes);
+    auto *w = static_cast<mfk::CopyWindow *>(mem);
+    auto *status = reinterpret_cast<uint32_t *>(static_cast<char *>(mem) + sizeof(mfk::CopyWindow));
+    auto *items = reinterpret_cast<mfk::CopyItem *>(static_cast<char *>(mem) + sizeof(mfk::CopyWindow) + 64);
+    w->base = win_base;
+    w->slot = slot;
+    w->ranks = ranks;
+    for (uint32_t r = 0; r < ranks; r++) w->mapped[r] = mapped != nullptr ? mapped[r] : 0;
+    for (uint32_t i = 0; i < n; i++) items[i] = mfk::CopyItem{triples[3 * i], triples[3 * i + 1], triples[3 * i + 2]};
+    int rc = 0;
+    if (bulk) {
+        const uint32_t smem = 4 * 16384;
+        if (cudaFuncSetAttribute(mfk::mf_xcopy_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess) rc = -3;
+        if (rc == 0) mfk::mf_xcopy_bulk_kernel<<<2, 32, smem>>>(items, n, 4, 16384, status, w);
+    } else {
+        mfk::mf_xcopy_batch_kernel<<<2, mfk::kCopyThreads>>>(items, n, w, status);
+    }
+    if (rc == 0 && (cudaGetLastError() != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess)) rc = -4;
+    if (rc == 0) rc = (int)*reinterpret_cast<volatile uint32_t *>(status);
+    cudaFreeHost(mem);
+    return rc;
 }

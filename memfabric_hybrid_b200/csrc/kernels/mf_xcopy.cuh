@@ -26,6 +26,37 @@ struct QuantItem {
     uint64_t elems;
 };
 
+// Debug aid (MF_XCOPY_DEBUG=1): the pool's address window as the copy kernels check it. An address inside the window must
+// lie, with its whole length, in the part of a rank's slot that is mapped here; addresses outside the window are the
+// caller's own buffers and are taken as given. A descriptor that fails is skipped (nothing is read or written) and
+// reported through the status word. The host validates every item before it builds descriptors; this second check
+// sits in front of the first access of the kernel itself, where a sanitizer would otherwise be the only witness.
+struct CopyWindow {
+    uint64_t base;        // 0: no window, nothing is checked
+    uint64_t slot;        // bytes between consecutive ranks' slots
+    uint32_t ranks;
+    uint32_t pad;
+    uint64_t mapped[64];  // bytes mapped of every rank's slot
+};
+constexpr uint32_t kCopyBadDescriptor = 0x7D1u;
+
+__device__ __forceinline__ bool xc_in_window(const CopyWindow *w, uint64_t a, uint64_t len)
+{
+    if (w == nullptr || w->base == 0 || a < w->base || a >= w->base + w->slot * w->ranks) return true;
+    const uint64_t rel = a - w->base;
+    const uint32_t r = (uint32_t)(rel / w->slot);
+    const uint64_t off = rel - (uint64_t)r * w->slot;
+    const uint64_t m = r < 64 ? w->mapped[r] : 0;
+    return len <= m && off <= m - len;
+}
+__device__ __forceinline__ bool xc_check(const CopyWindow *w, const uint64_t src, const uint64_t dst, const uint64_t len, uint32_t *status)
+{
+    if (xc_in_window(w, src, len) && xc_in_window(w, dst, len)) return true;
+    *reinterpret_cast<volatile uint32_t *>(status) = kCopyBadDescriptor;
+    __threadfence_system();
+    return false;
+}
+
 constexpr int kCopyThreads = 512;
 constexpr int kCopyUnroll = 4;
 
@@ -67,7 +98,8 @@ __device__ __forceinline__ void cta_copy(const uint8_t *__restrict__ src, uint8_
     if (tid < tail) dst[head + body + tid] = src[head + body + tid];
 }
 
-__global__ void __launch_bounds__(kCopyThreads) mf_xcopy_batch_kernel(const CopyItem *__restrict__ items, uint32_t count)
+__global__ void __launch_bounds__(kCopyThreads) mf_xcopy_batch_kernel(const CopyItem *__restrict__ items, uint32_t count,
+                                                                      const CopyWindow *__restrict__ window, uint32_t *status)
 {
     __shared__ CopyItem sh[2];
     uint32_t i = blockIdx.x;
@@ -79,7 +111,8 @@ __global__ void __launch_bounds__(kCopyThreads) mf_xcopy_batch_kernel(const Copy
         const CopyItem it = sh[buf];
         // descriptor of the next chunk is fetched (from pinned host memory) while this one is copied
         if (threadIdx.x == 0 && i + gridDim.x < count) sh[buf ^ 1] = items[i + gridDim.x];
-        cta_copy(reinterpret_cast<const uint8_t *>(it.src), reinterpret_cast<uint8_t *>(it.dst), it.len);
+        if (window == nullptr || xc_check(window, it.src, it.dst, it.len, status))
+            cta_copy(reinterpret_cast<const uint8_t *>(it.src), reinterpret_cast<uint8_t *>(it.dst), it.len);
         __syncthreads();
         buf ^= 1;
     }
@@ -101,7 +134,7 @@ constexpr int kBulkMaxStages = 8;
 __device__ __forceinline__ uint32_t xc_smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __global__ void __launch_bounds__(128) mf_xcopy_bulk_kernel(const CopyItem *__restrict__ items, uint32_t count, uint32_t stages,
-                                                            uint32_t piece, uint32_t *status)
+                                                            uint32_t piece, uint32_t *status, const CopyWindow *__restrict__ window)
 {
     extern __shared__ __align__(128) uint8_t xc_smem[];
     __shared__ __align__(8) uint64_t full[4][kBulkMaxStages];
@@ -123,6 +156,21 @@ __global__ void __launch_bounds__(128) mf_xcopy_bulk_kernel(const CopyItem *__re
     CopyItem nxt = ci + pipes < count ? items[ci + pipes] : CopyItem{0, 0, 0};
     uint64_t off = 0;
     bool more = true, fine = true;
+    // debug window: a chunk that fails the check is emptied (its pieces are never issued)
+    if (window != nullptr && !xc_check(window, cur.src, cur.dst, cur.len, status)) off = cur.len;
+    if (off >= cur.len) {
+        // walk on to the first chunk of this pipeline that has bytes to move
+        while (more && off >= cur.len) {
+            ci += pipes;
+            if (ci < count) {
+                cur = nxt;
+                off = (window != nullptr && !xc_check(window, cur.src, cur.dst, cur.len, status)) ? cur.len : 0;
+                if (ci + pipes < count) nxt = items[ci + pipes];
+            } else {
+                more = false;
+            }
+        }
+    }
     uint32_t loaded = 0, stored = 0;
     while (fine && (more || stored < loaded)) {
         if (more) {
@@ -141,11 +189,11 @@ __global__ void __launch_bounds__(128) mf_xcopy_bulk_kernel(const CopyItem *__re
             st_len[w][s] = n;
             loaded++;
             off += n;
-            if (off >= cur.len) {
+            while (more && off >= cur.len) {
                 ci += pipes;
                 if (ci < count) {
                     cur = nxt;
-                    off = 0;
+                    off = (window != nullptr && !xc_check(window, cur.src, cur.dst, cur.len, status)) ? cur.len : 0;
                     if (ci + pipes < count) nxt = items[ci + pipes];
                 } else {
                     more = false;

@@ -43,12 +43,33 @@
 namespace zbal {
 namespace {
 
+// Keys of ZBAL_ALLOC_CONF / ZBAL_NPU_ALLOC_CONF (the reference's set, app/zbal/src/csrc/sma/zbal_sma_config.h:20-102,
+// app/zbal/doc/user_guide/env.md, plus round_large_mb):
+//   max_split_size_mb            cached blocks above this size are only reused whole
+//   garbage_collection_threshold fraction of the heap in use above which cached blocks are returned first
+//   segment_size_mb              granule that large requests are rounded to (alias: round_large_mb), default 2
+//   small_heap_threshold         requests below it come from the low end of the heap, default 1 MiB
+//   small_heap_size              bytes of the low end that such requests may occupy, default 512000 KiB
+//   use_sma_allocator            False: the pluggable entry points bypass the heap (plain device allocations)
+//   use_vmm_for_static_memory    True: requests above max_split_size_mb (weights, KV cache: large and long-lived)
+//                                get their own device allocation outside the heap and never fragment it
 struct Config {
     uint64_t smallThreshold = 1ull << 20;
     uint64_t maxSplit = 20ull << 20;
     uint64_t roundLarge = 2ull << 20;
+    uint64_t smallHeapSize = 524288000ull;
     double gcThreshold = 0.0;
+    bool useSma = true;
+    bool vmmForStatic = false;
 };
+
+bool ParseBool(const std::string &v, bool &out)
+{
+    if (v == "True" || v == "true" || v == "1") out = true;
+    else if (v == "False" || v == "false" || v == "0") out = false;
+    else return false;
+    return true;
+}
 
 Config ParseConf(uint64_t optThreshold)
 {
@@ -62,7 +83,10 @@ Config ParseConf(uint64_t optThreshold)
         uint64_t u = 0;
         if (k == "small_heap_threshold" && mf::ParseU64(v, u) && u >= 4096) c.smallThreshold = u;
         else if (k == "max_split_size_mb" && mf::ParseU64(v, u) && u >= 1) c.maxSplit = u << 20;
-        else if (k == "round_large_mb" && mf::ParseU64(v, u) && u >= 1 && u <= 1024) c.roundLarge = u << 20;
+        else if ((k == "round_large_mb" || k == "segment_size_mb") && mf::ParseU64(v, u) && u >= 1 && u <= 1024) c.roundLarge = u << 20;
+        else if (k == "small_heap_size" && mf::ParseU64(v, u)) c.smallHeapSize = u;
+        else if (k == "use_sma_allocator" && ParseBool(v, c.useSma)) {}
+        else if (k == "use_vmm_for_static_memory" && ParseBool(v, c.vmmForStatic)) {}
         else if (k == "garbage_collection_threshold") c.gcThreshold = atof(v.c_str());
         else MF_WARN("ZBAL_ALLOC_CONF: ignoring '%s'", kv.c_str());
     }
@@ -95,7 +119,11 @@ public:
     Sma(uint64_t base, uint64_t size, const Config &cfg, int device, bool simulated)
         : heap_(base, size, cfg.smallThreshold), cfg_(cfg), device_(device), simulated_(simulated)
     {
+        // the small side may take at most half of a heap that is smaller than twice the configured size
+        heap_.SetSmallLimit(std::min<uint64_t>(cfg.smallHeapSize, size / 2));
     }
+    const Config &Conf() const { return cfg_; }
+    bool Simulated() const { return simulated_; }
 
     uint64_t Round(uint64_t size) const
     {
@@ -394,6 +422,11 @@ using namespace zbal;
 
 extern "C" {
 
+namespace {
+std::mutex g_outside_mu;
+std::map<uint64_t, uint64_t> g_outside;  // device allocations handed out by the pluggable entry points outside the heap
+}  // namespace
+
 int32_t zbal_sma_init(zbal_allocator_options_t *options, int32_t flags)
 {
     (void)flags;
@@ -431,6 +464,19 @@ void *zbal_pluggable_malloc(size_t size, int32_t device, zbal_stream_t stream)
         mf::LastError::Set(Z_NOT_INITIALIZED, "zbal_pluggable_malloc before zbal_sma_init");
         return nullptr;
     }
+    // outside the heap: the whole allocator switched off, or "static" (large, long-lived) memory kept out of it
+    const Config &c = s->Conf();
+    if (!s->Simulated() && (!c.useSma || (c.vmmForStatic && size > c.maxSplit))) {
+        mf::hybm::DeviceBackend *dev = mf::hybm::CurrentBackend();
+        uint64_t p = 0;
+        if (dev == nullptr || dev->Malloc(size, &p) != 0 || p == 0) {
+            MF_FAIL(Z_NO_MEMORY, "device allocation of %zu bytes outside the heap failed", size);
+            return nullptr;
+        }
+        std::lock_guard<std::mutex> g(g_outside_mu);
+        g_outside[p] = size;
+        return reinterpret_cast<void *>(p);
+    }
     return s->Malloc(size, reinterpret_cast<uint64_t>(stream));
 }
 
@@ -440,7 +486,18 @@ void zbal_pluggable_free(void *ptr, size_t size, int32_t device, zbal_stream_t s
     (void)device;
     (void)stream;
     auto s = Get();
-    if (!s || ptr == nullptr) return;
+    if (ptr == nullptr) return;
+    {
+        std::unique_lock<std::mutex> g(g_outside_mu);
+        auto it = g_outside.find(reinterpret_cast<uint64_t>(ptr));
+        if (it != g_outside.end()) {
+            g_outside.erase(it);
+            g.unlock();
+            if (mf::hybm::DeviceBackend *dev = mf::hybm::CurrentBackend()) dev->Free(reinterpret_cast<uint64_t>(ptr));
+            return;
+        }
+    }
+    if (!s) return;
     if (!s->Free(ptr)) MF_WARN("zbal_pluggable_free: %p was not allocated by this allocator", ptr);
 }
 

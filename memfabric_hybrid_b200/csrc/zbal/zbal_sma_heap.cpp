@@ -36,6 +36,7 @@ bool SplitMemoryHeap::Pick(uint64_t size, uint64_t align, bool low, uint64_t &bl
         if (low) {
             pos = (addr + align - 1) & ~(align - 1);
             if (pos + size > addr + bsz) return false;
+            if (smallLimit_ != 0 && pos + size > base_ + smallLimit_) return false;   // the small side is full
         } else {
             if (bsz < size) return false;
             pos = (addr + bsz - size) & ~(align - 1);
@@ -75,7 +76,9 @@ uint64_t SplitMemoryHeap::AlignedAllocate(uint64_t size, uint64_t align)
     std::lock_guard<std::mutex> g(mu_);
     const bool low = size < threshold_;
     uint64_t baddr = 0, bsize = 0, at = 0;
-    if (!Pick(size, align, low, baddr, bsize, at)) return 0;
+    if (!Pick(size, align, low, baddr, bsize, at)) {
+        if (!(low && smallLimit_ != 0 && Pick(size, align, false, baddr, bsize, at))) return 0;
+    }
     EraseFree(baddr, bsize);
     if (at > baddr) InsertFree(baddr, at - baddr);
     const uint64_t end = at + size, bend = baddr + bsize;

@@ -37,6 +37,10 @@ public:
     uint64_t LargestFree() const;
     size_t FreeBlocks() const;
     uint64_t Threshold() const { return threshold_; }
+    // Bytes from the low end that blocks below the threshold may occupy (0: no limit). A small request that no longer
+    // fits below the limit is carved from the high end like a large one.
+    void SetSmallLimit(uint64_t bytes) { smallLimit_ = bytes; }
+    uint64_t SmallLimit() const { return smallLimit_; }
     // (addr, size, used) of every block in address order
     struct BlockInfo {
         uint64_t addr, size;
@@ -57,6 +61,7 @@ private:
     std::set<uint64_t> buckets_[kBuckets];     // addresses of the free blocks of each size class
     std::map<uint64_t, uint64_t> used_;        // addr -> size
     uint64_t inUse_ = 0;
+    uint64_t smallLimit_ = 0;
 };
 
 }  // namespace zbal

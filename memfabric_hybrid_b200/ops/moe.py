@@ -13,6 +13,7 @@ Kernels: csrc/kernels/mf_moe.cu, csrc/kernels/mf_gemm_fp8.cu.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 
 import torch
@@ -20,6 +21,10 @@ import torch
 from .. import _native as N
 from .gemm import sm_count, status_word
 from .heap import TeamC, _HeapBase
+
+
+_CANARY_BYTES = 4096
+_CANARY_WORD = 0x5AFEC0DE - (1 << 32) if 0x5AFEC0DE >= (1 << 31) else 0x5AFEC0DE
 
 
 class MoeShapeC(C.Structure):
@@ -150,10 +155,26 @@ class MoEComm:
         hp.counts = heap.alloc(self.world * experts * 4, 256)
         hp.flags = heap.alloc(4 * 16 * 4, 256)
         self.raw_bf16 = raw_bf16  # rows travel as bf16 instead of block-scaled fp8
+        # Debug aid (MF_MOE_CANARY=1): guard words between the receive areas that peers write into. A peer that stores past
+        # the end of a row, a scale array or a combine slot lands in a guard first; check_canaries() finds it.
+        self._canary = os.environ.get("MF_MOE_CANARY", "0") not in ("", "0")
+        self._guards = []
+
+        def guard():
+            if self._canary:
+                self._guards.append(heap.alloc(_CANARY_BYTES, 256))
+
+        guard()
         hp.recv_x = heap.alloc(self.max_recv * hidden * (2 if raw_bf16 else 1), 1024)
+        guard()
         hp.recv_scale = heap.alloc(self.max_recv * (hidden // 128) * 4, 256)
+        guard()
         hp.recv_info = heap.alloc(self.max_recv * 16, 256)
+        guard()
         hp.comb = heap.alloc(max_tokens * topk * hidden * 2, 1024)
+        guard()
+        for off in self._guards:
+            heap.view(off, (_CANARY_BYTES // 4,), torch.int32).fill_(_CANARY_WORD)
         self.hp = hp
         heap.view(hp.flags, (4 * 16,), torch.int32).zero_()
         heap.view(hp.counts, (self.world * experts,), torch.int32).zero_()
@@ -168,6 +189,15 @@ class MoEComm:
         torch.cuda.synchronize()
         if hasattr(heap, "host_barrier"):
             heap.host_barrier()
+
+    def check_canaries(self) -> None:
+        """Raises when a guard word between the receive areas of THIS rank was overwritten (MF_MOE_CANARY=1)."""
+        for i, off in enumerate(self._guards):
+            g = self.heap.view(off, (_CANARY_BYTES // 4,), torch.int32)
+            bad = (g != _CANARY_WORD).nonzero()
+            if bad.numel():
+                raise RuntimeError(f"MoE receive area: guard {i} (slot offset {off:#x}) was overwritten at word {int(bad[0])}: "
+                                   "a peer stored outside its row, scale or combine slot")
 
     # views of the receive area (valid rows: state.row_off[-1])
     def recv_x(self) -> torch.Tensor:
@@ -265,6 +295,9 @@ class MoEComm:
         sh = self._shape(st.T)
         _ok(_cu().mf_moe_combine_reduce(C.byref(team), C.byref(self.hp), C.byref(sh), st.topk_idx.data_ptr(), out.data_ptr(),
                                         min(st.T, self._grid * 4), _s()), "moe_combine_reduce")
+        if self._canary:
+            torch.cuda.synchronize()
+            self.check_canaries()
         return out
 
     # ------------------------------------------------------------------ standalone combine (caller ran its own expert FFN)

@@ -235,3 +235,60 @@ def test_real_ranks_with_nvlink_multicast():
     res = run_ranks(_real_ranks, n, (url,), timeout=300, with_barrier=True, env={"MF_SHM_MULTICAST": "1"})
     assert [r[0] for r in res] == [0] * n
     assert len({r[1] for r in res}) == 1      # every rank took the same decision about the alias
+
+
+def _busy_ranks(rank, world, url, sync):
+    """An all-reduce issued while matrix multiplications on another stream keep every SM busy: the collective's CTAs may
+    have to queue behind them while the peer's CTAs already poll. It must either complete correctly or end with the clean
+    time-out status of a bounded wait; it must not hang, and the context must stay usable."""
+    import torch
+    from memfabric_hybrid_b200.ops.heap import SymmetricHeap
+    from memfabric_hybrid_b200.ops.collectives import Communicator
+    heap = SymmetricHeap(url, world, rank, rank % torch.cuda.device_count(), 64 << 20)
+    c = Communicator(heap, stage_bytes=8 << 20)
+    side = torch.cuda.Stream()
+    a = torch.randn(8192, 8192, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(8192, 8192, device="cuda", dtype=torch.bfloat16)
+    n = 1 << 20
+    hx = heap.view(heap.alloc(n * 2), (n,), torch.bfloat16)
+    ho = heap.view(heap.alloc(n * 2), (n,), torch.bfloat16)
+    hx.fill_(float(rank + 1))
+    small = torch.full((1000,), float(rank + 1), device="cuda")
+    torch.cuda.synchronize()
+    heap.host_barrier()
+    outcomes = []
+    for it in range(3):
+        with torch.cuda.stream(side):
+            for _ in range(12 if rank % 2 == 0 else 4):      # ranks are busy for different lengths of time (about 10 and 3 ms)
+                torch.matmul(a, b)
+        out_small = c.all_reduce(small)                       # staged path
+        c.all_reduce(hx, out=ho)                              # direct path, peers read and write the heap tensors in place
+        torch.cuda.synchronize()
+        st = heap.status()
+        if st[0] == 0:
+            want = float(sum(range(1, world + 1)))
+            assert torch.equal(out_small, torch.full_like(out_small, want))
+            assert torch.equal(ho.float(), torch.full((n,), want, device="cuda"))
+            outcomes.append("ok")
+        else:
+            assert st[0] == 1, st                             # ST_TIMEOUT of a bounded wait, nothing else
+            heap.clear_status()
+            outcomes.append("timeout")
+        heap.host_barrier()
+    # the context is still good for an undisturbed call
+    got = c.all_reduce(small)
+    torch.cuda.synchronize()
+    ok = heap.status()[0] == 0 and torch.equal(got, torch.full_like(got, float(sum(range(1, world + 1)))))
+    heap.close()
+    SymmetricHeap.shutdown()
+    return outcomes, bool(ok)
+
+
+@pytest.mark.multigpu
+def test_collective_while_compute_occupies_the_sms():
+    n = 2
+    url = f"127.0.0.1:{free_port()}"
+    res = run_ranks(_busy_ranks, n, (url,), timeout=300, with_barrier=True)
+    for outcomes, ok in res:
+        assert ok and all(o in ("ok", "timeout") for o in outcomes), res
+    assert any("ok" in o for o, _ in res), res   # 10 ms of queueing is far inside the waits' budget: it completes

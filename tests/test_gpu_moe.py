@@ -188,3 +188,35 @@ def test_moe_layer_multi_gpu():
     res = run_ranks(_moe_ranks, n, (url, 256, 512, 256, 16, 4), timeout=300, with_barrier=True)
     for worst, st in res:
         assert st == 0 and worst < 4e-2, res
+
+
+def _canary_rank(rank, world, url, sync):
+    import torch
+    from memfabric_hybrid_b200.ops import gemm
+    from memfabric_hybrid_b200.ops.heap import SymmetricHeap
+    from memfabric_hybrid_b200.models.deepseek_moe import ExpertParallelMoE
+    T, H, I, E, K = 128, 512, 256, 8, 4
+    heap = SymmetricHeap(url, 1, 0, 0, (2 << 20) + T * K * (H + H // 128 * 4 + 16) + T * K * H * 2 + (4 << 20))
+    layer = ExpertParallelMoE(heap, H, I, E, K, max_tokens=T, seed=5)
+    assert len(layer.comm._guards) == 5
+    g = torch.Generator("cuda").manual_seed(1)
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+    logits = torch.randn(T, E, device="cuda", generator=g)
+    layer.forward(x, logits)            # checks the guards at the end of combine
+    layer.forward(x, logits)
+    gemm.check_status()
+    # a store that runs past the token rows lands in the guard behind them
+    heap.view(layer.comm._guards[1], (4,), torch.int32)[2] = 7
+    try:
+        layer.comm.check_canaries()
+        caught = False
+    except RuntimeError as e:
+        caught = "guard 1" in str(e)
+    heap.close()
+    SymmetricHeap.shutdown()
+    return caught
+
+
+def test_moe_receive_areas_are_guarded_by_canaries():
+    url = f"127.0.0.1:{free_port()}"
+    assert run_ranks(_canary_rank, 1, (url,), timeout=300, with_barrier=True, env={"MF_MOE_CANARY": "1"}) == [True]

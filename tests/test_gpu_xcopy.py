@@ -90,3 +90,41 @@ def test_two_process_hbm_pool():
     url = f"tcp://127.0.0.1:{free_port()}"
     launches = run_ranks(_two_ranks, 2, (url,), timeout=300, with_barrier=True)
     assert all(l > 0 for l in launches), f"SM copy kernel did not run: {launches}"
+
+
+@pytest.mark.parametrize("bulk", [0, 1])
+def test_copy_kernels_refuse_descriptors_outside_the_mapped_window(bulk):
+    """The debug window of the copy kernels (MF_XCOPY_DEBUG=1 publishes the pool's window; here it is handed in directly):
+    a descriptor whose pooled side runs past the mapped part of a slot is skipped before its first access and reported;
+    its neighbours are copied."""
+    import ctypes as C
+    import torch
+    from memfabric_hybrid_b200 import _native as N
+    cu = N.cuda()
+    cu.mf_xcopy_debug_probe.restype = C.c_int
+    cu.mf_xcopy_debug_probe.argtypes = [C.POINTER(C.c_uint64), C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint32, C.POINTER(C.c_uint64), C.c_int]
+    n = 64 << 10
+    src = torch.arange(n, device="cuda", dtype=torch.int32)
+    pool = torch.zeros(4 * n, device="cuda", dtype=torch.int32)       # stands for a window of 4 slots of n ints, 3/4 of each mapped
+    other = torch.zeros(n, device="cuda", dtype=torch.int32)
+    torch.cuda.synchronize()
+    slot = n * 4
+    base = pool.data_ptr()
+    mapped = (C.c_uint64 * 4)(*[slot * 3 // 4] * 4)
+    half = n * 2                                                      # bytes of half a slot
+    trip = [src.data_ptr(), base, half,                               # into the mapped part of slot 0
+            src.data_ptr(), base + slot + slot // 2, half,            # slot 1: starts inside, ends past the mapped 3/4: refused
+            src.data_ptr(), other.data_ptr(), half,                   # neither side in the window: taken as given
+            src.data_ptr(), base + 4 * slot - 4096, 4096 * 2]         # runs out of the window's last slot: refused
+    arr = (C.c_uint64 * len(trip))(*trip)
+    rc = cu.mf_xcopy_debug_probe(arr, len(trip) // 3, base, slot, 4, mapped, bulk)
+    assert rc == 0x7D1, hex(rc & 0xFFFFFFFF)
+    torch.cuda.synchronize()
+    q = n // 2
+    assert torch.equal(pool[:q], src[:q]) and torch.equal(other[:q], src[:q])
+    assert int(pool[n + q:2 * n].abs().max()) == 0 and int(pool[4 * n - 1024:].abs().max()) == 0   # the refused ones wrote nothing
+    # all descriptors fine: status 0
+    ok = (C.c_uint64 * 3)(src.data_ptr(), base + 2 * slot, half)
+    assert cu.mf_xcopy_debug_probe(ok, 1, base, slot, 4, mapped, bulk) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(pool[2 * n:2 * n + q], src[:q])

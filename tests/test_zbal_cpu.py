@@ -42,6 +42,28 @@ def test_small_low_large_high_and_rounding(sma):
     assert _stats(sma).inUseBytes == 0 and _stats(sma).cachedBytes == 1024 + 512 + 4 * MiB
 
 
+def test_allocator_configuration_keys(monkeypatch):
+    """segment_size_mb (rounding granule of large requests) and small_heap_size (bytes of the low end that small requests
+    may occupy; further small requests are carved from the high end) from ZBAL_ALLOC_CONF; unknown keys are ignored."""
+    from memfabric_hybrid_b200.zbal import _capi as K
+    monkeypatch.setenv("ZBAL_ALLOC_CONF", "segment_size_mb:8,small_heap_size:4096,small_heap_threshold:65536,use_sma_allocator:True,"
+                                            "use_vmm_for_static_memory:False,bogus_key:1")
+    l = K.lib()
+    l.zbal_simulate_init(BASE, 256 * MiB)
+    try:
+        big = l.zbal_pluggable_malloc(3 * MiB, 0, None)
+        assert big == BASE + 256 * MiB - 8 * MiB            # 3 MiB rounded to the 8 MiB segment granule
+        smalls = [l.zbal_pluggable_malloc(1024, 0, None) for _ in range(5)]
+        assert smalls[:4] == [BASE + i * 1024 for i in range(4)]     # 4096 bytes of small heap
+        assert BASE + 4096 <= smalls[4] and smalls[4] >= BASE + 128 * MiB   # the fifth no longer fits below the limit: high end
+        mid = l.zbal_pluggable_malloc(32768, 0, None)       # below the (lowered) threshold of 64 KiB: small, and too big for what is left
+        assert mid >= BASE + 128 * MiB
+        for p in smalls + [big, mid]:
+            l.zbal_pluggable_free(p, 0, 0, None)
+    finally:
+        l.zbal_sma_uninit(0)
+
+
 def test_cache_is_per_stream_and_flush_on_exhaustion(sma):
     s1, s2 = C.c_void_p(0x10), C.c_void_p(0x20)
     p = sma.zbal_pluggable_malloc(8 * MiB, 0, s1)
