@@ -141,6 +141,10 @@ class Communicator:
             # 8 GPUs: ahead from 1 MiB on (1 MiB 25 vs 27 us, 256 MiB 645 vs 799 us); 4 GPUs: from 64 MiB on (32 MiB 119 vs 113 us,
             # 256 MiB 641 vs 711 us)
             return (self.world >= 8 and nbytes >= (1 << 20)) or (self.world >= 4 and nbytes >= (64 << 20))
+        if kind == "reduce_scatter":
+            # 8 GPUs: the in-switch load-reduce is ahead between 1 MiB and 256 MiB (16 MiB 45 vs 49 us, 256 MiB 410 vs 430 us) and
+            # behind at 1 GiB (1501 vs 1477 us); at 4 GPUs the peer loads win from 16 MiB on
+            return self.world >= 8 and (1 << 20) <= nbytes <= (256 << 20)
         return False
 
     def _local(self, t: torch.Tensor):
