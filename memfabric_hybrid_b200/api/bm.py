@@ -186,7 +186,8 @@ class BigMemory:
         return N.lib().smem_bm_copy_batch(self._h, C.byref(p), int(type), flags)
 
     def prepare_batch(self, src_addrs, dst_addrs, sizes, count=None):
-        """Extension: marshals a batch once so that repeated submissions skip the Python-side conversion."""
+        """Extension: marshals a batch once so that repeated submissions skip the Python-side conversion (every submission
+        still runs the library's validation and descriptor marshalling: see ``create_batch`` for the path that does not)."""
         n = int(count if count is not None else len(sizes))
         return self._batch(src_addrs, dst_addrs, sizes, n, 0)
 
@@ -194,6 +195,21 @@ class BigMemory:
         p, _keep = prepared
         p.stream = stream or None
         return N.lib().smem_bm_copy_batch(self._h, C.byref(p), int(type), flags)
+
+    def create_batch(self, src_addrs, dst_addrs, sizes, type: BmCopyType, count=None) -> "PreparedBatch":
+        """Extension (``mf_bm_batch_create``): a device-to-device batch (L2G, G2L, G2G) validated, merged and cut into work
+        chunks ONCE, with its descriptors in pinned memory of its own. ``launch(stream)`` is then a single kernel launch that
+        may be recorded into a CUDA graph. Re-create it after a member of the pool leaves."""
+        n = int(count if count is not None else len(sizes))
+        p, _keep = self._batch(src_addrs, dst_addrs, sizes, n, 0)
+        out = C.c_void_p()
+        l = N.lib()
+        l.mf_bm_batch_create.restype = C.c_int32
+        l.mf_bm_batch_create.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.POINTER(C.c_void_p)]
+        rc = l.mf_bm_batch_create(self._h, C.byref(p), int(type), C.byref(out))
+        if rc != 0:
+            raise RuntimeError(f"mf_bm_batch_create failed ({rc}): {N.last_error()}")
+        return PreparedBatch(out.value)
 
     def copy_data_batch_partial_succeed(self, src_addrs, dst_addrs, sizes, count, type: BmCopyType, flags: int = 0,
                                         stream: int = 0):
@@ -247,6 +263,34 @@ class BigMemory:
     @property
     def handle(self) -> int:
         return self._h
+
+
+class PreparedBatch:
+    """Handle of ``BigMemory.create_batch``."""
+
+    def __init__(self, handle: int):
+        self._b = handle
+        l = N.lib()
+        l.mf_bm_batch_launch.restype = C.c_int32
+        l.mf_bm_batch_launch.argtypes = [C.c_void_p, C.c_void_p]
+        l.mf_bm_batch_bytes.restype = C.c_uint64
+        l.mf_bm_batch_bytes.argtypes = [C.c_void_p]
+        l.mf_bm_batch_destroy.restype = C.c_int32
+        l.mf_bm_batch_destroy.argtypes = [C.c_void_p]
+        self._launch = l.mf_bm_batch_launch
+
+    def launch(self, stream: int) -> int:
+        """Enqueues the batch on ``stream`` (asynchronous; capturable)."""
+        return self._launch(self._b, stream or None)
+
+    @property
+    def nbytes(self) -> int:
+        return int(N.lib().mf_bm_batch_bytes(self._b))
+
+    def destroy(self) -> None:
+        if self._b:
+            N.lib().mf_bm_batch_destroy(self._b)
+            self._b = None
 
 
 def create(id: int, local_dram_size: int, local_hbm_size: int = 0, data_op_type: BmDataOpType = BmDataOpType.SDMA,

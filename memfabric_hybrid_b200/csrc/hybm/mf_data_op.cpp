@@ -385,6 +385,60 @@ int KernelBatch::Finish()
     return rc;
 }
 
+int ComposeDataOp::Prepare(const std::vector<ResolvedCopy> &items, PreparedBatch &out)
+{
+    if (dev_ == nullptr) return ERR_NOT_INIT;
+    // merge neighbours, then cut into equal work chunks exactly as RunKernel does
+    std::vector<CopyItem> runs;
+    uint64_t total = 0, alignMask = 0;
+    for (const auto &c : items) {
+        if (c.len == 0) continue;
+        if (c.src.kind != EP_DEVICE || c.dst.kind != EP_DEVICE) return MF_FAIL(ERR_INVALID_PARAM, "a prepared batch holds device-to-device copies only");
+        total += c.len;
+        alignMask |= c.src.addr | c.dst.addr | c.len;
+        if (!runs.empty() && runs.back().src + runs.back().len == c.src.addr && runs.back().dst + runs.back().len == c.dst.addr) runs.back().len += c.len;
+        else runs.push_back(CopyItem{c.src.addr, c.dst.addr, c.len});
+    }
+    if (runs.empty()) return MF_FAIL(ERR_INVALID_PARAM, "a prepared batch needs at least one non-empty copy");
+    const uint64_t sms = std::max(1, dev_->Caps().smCount);
+    uint64_t chunk = AlignUp(std::max<uint64_t>(total / (sms * 8), 1), 4096);
+    chunk = std::min(std::max<uint64_t>(chunk, 16 * kKiB), chunk_);
+    uint64_t n = 0;
+    for (const auto &r : runs) n += (r.len + chunk - 1) / chunk;
+    if (n > UINT32_MAX) return MF_FAIL(ERR_INVALID_PARAM, "batch too large");
+    dev_->BindThread();
+    void *mem = nullptr;
+    int rc = dev_->HostAlloc(n * sizeof(CopyItem), &mem);
+    if (rc != OK) return MF_FAIL(rc, "cannot allocate %lu pinned descriptors", (unsigned long)n);
+    auto *d = static_cast<CopyItem *>(mem);
+    uint64_t w = 0;
+    for (const auto &r : runs)
+        for (uint64_t off = 0; off < r.len; off += chunk) d[w++] = CopyItem{r.src + off, r.dst + off, std::min(chunk, r.len - off)};
+    out.desc = d;
+    out.count = (uint32_t)n;
+    out.bytes = total;
+    out.bulkOk = (alignMask & 15) == 0;
+    return OK;
+}
+
+int ComposeDataOp::LaunchPrepared(const PreparedBatch &b, void *stream)
+{
+    if (dev_ == nullptr || b.desc == nullptr) return ERR_INVALID_PARAM;
+    // no lock, no shared state: the descriptors belong to the batch; the launch is all there is (graph-capturable)
+    int rc = dev_->LaunchBatchCopy(b.desc, b.count, stream, b.bulkOk);
+    if (rc == OK) {
+        fastLaunches_.fetch_add(1, std::memory_order_relaxed);
+        fastItems_.fetch_add(b.count, std::memory_order_relaxed);
+    }
+    return rc;
+}
+
+void ComposeDataOp::ReleasePrepared(PreparedBatch &b)
+{
+    if (dev_ != nullptr && b.desc != nullptr) dev_->HostFree(b.desc);
+    b = PreparedBatch();
+}
+
 int ComposeDataOp::Quant(const std::vector<QuantItem> &items, uint32_t unit, int inputFp16, int mode, void *userStream)
 {
     if (dev_ == nullptr) return ERR_NOT_INIT;

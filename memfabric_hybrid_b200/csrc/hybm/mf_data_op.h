@@ -45,6 +45,19 @@ struct DataOpStats {
     uint64_t kernelLaunches = 0, kernelItems = 0, engineCopies = 0, hostCopies = 0, vmCopies = 0, coalesced = 0;
 };
 
+// A batch whose descriptors were validated, merged and cut into work chunks ONCE and live in pinned memory of their
+// own: submitting it again is one kernel launch with no host work per descriptor, and because nothing is written at
+// submission time the launch may be recorded into a CUDA graph (the low-latency submission path: the counterpart of the
+// reference's own task-scheduler stream, src/hybm/csrc/ts_engine/hybm_stream.cpp, whose point is to cut the per-copy
+// host cost).
+struct PreparedBatch {
+    CopyItem *desc = nullptr;  // pinned, device-visible
+    uint32_t count = 0;
+    uint64_t bytes = 0;
+    bool bulkOk = false;
+    uint64_t mapGen = 0;       // membership generation of the entity when it was built
+};
+
 class ComposeDataOp {
 public:
     ComposeDataOp(DeviceBackend *dev, uint32_t opMask);
@@ -53,6 +66,10 @@ public:
     int Submit(std::vector<ResolvedCopy> &items, void *userStream, uint32_t flags, int32_t *perItem);
     int Quant(const std::vector<QuantItem> &items, uint32_t unit, int inputFp16, int mode, void *userStream);
     int Wait();
+    // items: device<->device copies, already validated. Builds the descriptor block of a PreparedBatch.
+    int Prepare(const std::vector<ResolvedCopy> &items, PreparedBatch &out);
+    int LaunchPrepared(const PreparedBatch &b, void *stream);
+    void ReleasePrepared(PreparedBatch &b);
     // Runs the copy right here when it is a host-to-host memcpy below the size at which it would be split over the
     // thread pool, and says whether it did. Takes no lock: nothing of the operator's state is involved.
     bool HostFast(const ResolvedCopy &c);
@@ -60,6 +77,8 @@ public:
     {
         DataOpStats s = stats_;
         s.hostCopies += fastHost_.load(std::memory_order_relaxed);
+        s.kernelLaunches += fastLaunches_.load(std::memory_order_relaxed);
+        s.kernelItems += fastItems_.load(std::memory_order_relaxed);
         return s;
     }
     // Tunables (env MF_XCOPY_CHUNK_KB, MF_XCOPY_RING_MB, MF_HOST_COPY_THREADS, MF_XCOPY_ENGINE_MIN_MB).
@@ -87,7 +106,7 @@ private:
     uint64_t engineMin_ = 0;  // device<->device items of at least this many bytes go to a copy engine (0: never)
     std::unique_ptr<ThreadPool> pool_;
     DataOpStats stats_;
-    std::atomic<uint64_t> fastHost_{0};
+    std::atomic<uint64_t> fastHost_{0}, fastLaunches_{0}, fastItems_{0};
     bool pending_ = false;
     friend class KernelBatch;
 };

@@ -397,6 +397,7 @@ void Entity::Unmap()
 
 int Entity::RemoveImported(uint32_t rank)
 {
+    mapGen_.fetch_add(1);
     ops_->Wait();
     if (hbm_) hbm_->RemoveImported(rank);
     if (dram_) dram_->RemoveImported(rank);
@@ -621,6 +622,38 @@ int Entity::BatchCopyData(const hybm_batch_copy_params &p, hybm_data_copy_direct
     }
     int rc = ops_->Submit(items, stream, flags, perItem);
     return rc != OK ? rc : firstErr;
+}
+
+int Entity::PrepareBatch(const hybm_batch_copy_params &p, hybm_data_copy_direction dir, PreparedBatch &out)
+{
+    if (p.sources == nullptr || p.destinations == nullptr || p.dataSizes == nullptr || p.batchSize == 0)
+        return MF_FAIL(ERR_INVALID_PARAM, "prepared batch: null array or empty batch");
+    if (dir != HYBM_LOCAL_DEVICE_TO_GLOBAL_DEVICE && dir != HYBM_GLOBAL_DEVICE_TO_GLOBAL_DEVICE && dir != HYBM_GLOBAL_DEVICE_TO_LOCAL_DEVICE)
+        return MF_FAIL(ERR_INVALID_PARAM, "prepared batch: device-to-device directions only (L2G, G2G, G2L)");
+    if (dev_ == nullptr || !dev_->Caps().present) return MF_FAIL(ERR_NOT_INIT, "prepared batch: no device");
+    const uint64_t gen = mapGen_.load();
+    std::vector<ResolvedCopy> items(p.batchSize);
+    for (uint32_t i = 0; i < p.batchSize; i++) {
+        ResolvedCopy &c = items[i];
+        c.index = i;
+        c.len = p.dataSizes[i];
+        int rc = (p.sources[i] == nullptr || p.destinations[i] == nullptr || c.len == 0) ? (int)ERR_INVALID_PARAM : (int)OK;
+        if (rc == OK) rc = Resolve(reinterpret_cast<uint64_t>(p.sources[i]), c.len, true, dir, c.src);
+        if (rc == OK) rc = Resolve(reinterpret_cast<uint64_t>(p.destinations[i]), c.len, false, dir, c.dst);
+        if (rc != OK)
+            return MF_FAIL(rc, "prepared batch item %u (%p -> %p, %lu bytes): null, empty or outside the mapped pool", i, p.sources[i],
+                           p.destinations[i], (unsigned long)c.len);
+    }
+    int rc = ops_->Prepare(items, out);
+    if (rc == OK) out.mapGen = gen;
+    return rc;
+}
+
+int Entity::LaunchPrepared(const PreparedBatch &b, void *stream)
+{
+    // a member left (its slice is unmapped) since the batch was validated: the descriptors may name memory that is gone
+    if (b.mapGen != mapGen_.load()) return MF_FAIL(ERR_NOT_CONNECTED, "prepared batch is stale: the pool's membership changed since it was built");
+    return ops_->LaunchPrepared(b, stream);
 }
 
 int Entity::QuantCopy(const hybm_quant_copy_params &p, int mode)

@@ -5,6 +5,8 @@
 // Parity: src/hybm/csrc/entity/hybm_entity_default.{h,cpp}:42-129,186-327,343-466,531-667,709-849,
 // src/hybm/csrc/entity/hybm_entity_tag_info.h:24-56, src/hybm/csrc/hybm_data_op_entry.cpp:22-140.
 #pragma once
+#include <atomic>
+
 #include "mf_data_op.h"
 #include "mf_segment.h"
 
@@ -65,6 +67,10 @@ public:
                       int32_t *perItem = nullptr);
     int QuantCopy(const hybm_quant_copy_params &p, int mode = 0);
     int Wait();
+    // Prepared batches (device-to-device directions): validated once, submitted by one launch each time.
+    int PrepareBatch(const hybm_batch_copy_params &p, hybm_data_copy_direction dir, PreparedBatch &out);
+    int LaunchPrepared(const PreparedBatch &b, void *stream);
+    void ReleasePrepared(PreparedBatch &b) { ops_->ReleasePrepared(b); }
     // Runs copies whose two ends the caller already resolved (the Trans layer, after translating a
     // peer's addresses).
     int SubmitResolved(std::vector<ResolvedCopy> &items, void *stream, uint32_t flags)
@@ -103,6 +109,7 @@ private:
     std::string extraCtx_;
     std::unique_ptr<ComposeDataOp> ops_;
     uint64_t transCursor_ = 0;
+    std::atomic<uint64_t> mapGen_{1};  // grows whenever a mapping goes away: prepared batches built before are refused
 };
 using EntityPtr = std::shared_ptr<Entity>;
 

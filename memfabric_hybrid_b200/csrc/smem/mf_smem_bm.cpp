@@ -341,6 +341,42 @@ int32_t mf_bm_copy_stats(smem_bm_t handle, uint64_t out[6])
     return SMEM_OK;
 }
 
+// Extension: prepared batches (see include/mf_bm_ext.h).
+struct mf_bm_batch {
+    std::shared_ptr<mf::smem::BmEntry> entry;
+    mf::hybm::PreparedBatch batch;
+};
+
+int32_t mf_bm_batch_create(smem_bm_t handle, const smem_batch_copy_params_t *params, smem_bm_copy_type_t t, mf_bm_batch **out)
+{
+    auto e = H(handle);
+    if (!e || out == nullptr) return SMEM_INVALID_PARAM;
+    int32_t rc = BatchCheck(params, t);
+    if (rc != SMEM_OK) return rc;
+    auto b = std::make_unique<mf_bm_batch>();
+    b->entry = e;
+    rc = Pub(e->PrepareBatch(*params, t, b->batch));
+    if (rc != SMEM_OK) return rc;
+    *out = b.release();
+    return SMEM_OK;
+}
+
+int32_t mf_bm_batch_launch(mf_bm_batch *b, void *stream)
+{
+    if (b == nullptr || !b->entry) return SMEM_INVALID_PARAM;
+    return Pub(b->entry->Entity()->LaunchPrepared(b->batch, stream));
+}
+
+uint64_t mf_bm_batch_bytes(mf_bm_batch *b) { return b != nullptr ? b->batch.bytes : 0; }
+
+int32_t mf_bm_batch_destroy(mf_bm_batch *b)
+{
+    if (b == nullptr) return SMEM_INVALID_PARAM;
+    if (b->entry) b->entry->Entity()->ReleasePrepared(b->batch);
+    delete b;
+    return SMEM_OK;
+}
+
 // Extension: shape of the bulk-copy (TMA) variant of the xcopy kernel for the launches that follow:
 // pipelines per CTA (0: register-copy kernel only), stages per pipeline (>= 4), KiB per stage.
 int32_t mf_xcopy_bulk_config(int pipes, int stages, int pieceKb)

@@ -34,6 +34,7 @@ public:
     int Copy(const smem_copy_params_t &p, smem_bm_copy_type_t t, uint32_t flags);
     int CopyBatch(const smem_batch_copy_params_t &p, smem_bm_copy_type_t t, uint32_t flags, int32_t *perItem);
     int Wait();
+    int PrepareBatch(const smem_batch_copy_params_t &p, smem_bm_copy_type_t t, hybm::PreparedBatch &out);
     int RegisterUser(uint64_t addr, uint64_t size);
     int UnregisterUser(uint64_t addr);
     uint32_t RankOfGva(const void *gva);

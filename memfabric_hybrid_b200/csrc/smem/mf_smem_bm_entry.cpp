@@ -380,6 +380,16 @@ int BmEntry::CopyBatch(const smem_batch_copy_params_t &p, smem_bm_copy_type_t t,
 
 int BmEntry::Wait() { return entity_->Wait(); }
 
+int BmEntry::PrepareBatch(const smem_batch_copy_params_t &p, smem_bm_copy_type_t t, hybm::PreparedBatch &out)
+{
+    if (!Joined()) return MF_FAIL(ERR_NOT_STARTED, "pool %u: prepared batch before join", id_);
+    hybm_data_copy_direction dir = DirectionFor(t, p.sources[0], p.destinations[0], p.dataSizes[0]);
+    if (dir == HYBM_DATA_COPY_DIRECTION_BUTT)
+        return MF_FAIL(ERR_INVALID_PARAM, "copy type %d does not fit addresses %p -> %p", (int)t, p.sources[0], p.destinations[0]);
+    hybm_batch_copy_params hp{p.sources, p.destinations, p.dataSizes, p.batchSize};
+    return entity_->PrepareBatch(hp, dir, out);
+}
+
 int BmEntry::RegisterUser(uint64_t addr, uint64_t size)
 {
     MemSlice *s = nullptr;

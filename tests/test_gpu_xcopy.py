@@ -128,3 +128,77 @@ def test_copy_kernels_refuse_descriptors_outside_the_mapped_window(bulk):
     assert cu.mf_xcopy_debug_probe(ok, 1, base, slot, 4, mapped, bulk) == 0
     torch.cuda.synchronize()
     assert torch.equal(pool[2 * n:2 * n + q], src[:q])
+
+
+def _prepared_rank(rank, world, url):
+    import numpy as np
+    import torch
+    import memfabric_hybrid as mf
+    from memfabric_hybrid import bm
+    from memfabric_hybrid_b200.utils import benchutil as bu
+    torch.cuda.set_device(0)
+    assert mf.initialize() == 0
+    cfg = bm.BmConfig()
+    cfg.auto_ranking = False
+    cfg.rank_id, cfg.start_store = 0, True
+    assert bm.initialize(url, 1, 0, cfg) == 0, mf.get_last_err_msg()
+    blocks = 4
+    nbytes = blocks * bu.KV_BLOCK_BYTES
+    pool = (nbytes + (4 << 20)) // (2 << 20) * (2 << 20)
+    h = bm.create2(id=0, local_dram_size=0, max_dram_size=0, local_hbm_size=pool, max_hbm_size=pool)
+    assert h.join() == 0, mf.get_last_err_msg()
+    base = h.peer_rank_ptr(0, bm.BmMemType.DEVICE)
+    src = torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device="cuda")
+    back = torch.zeros_like(src)
+    segs = bu.kv_block_segments(blocks)
+    offs = np.array([o for o, _ in segs], dtype=np.uint64)
+    sizes = np.array([s for _, s in segs], dtype=np.uint64)
+    put = h.create_batch(offs + np.uint64(src.data_ptr()), offs + np.uint64(base), sizes, bm.BmCopyType.L2G)
+    get = h.create_batch(offs + np.uint64(base), offs + np.uint64(back.data_ptr()), sizes, bm.BmCopyType.G2L)
+    assert put.nbytes == nbytes and get.nbytes == nbytes
+    s = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    # eager: two launches in stream order
+    assert put.launch(s.cuda_stream) == 0 and get.launch(s.cuda_stream) == 0, mf.get_last_err_msg()
+    s.synchronize()
+    eager_ok = bool(torch.equal(back, src))
+    # recorded into a CUDA graph and replayed on new data: submission writes nothing on the host
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        assert put.launch(torch.cuda.current_stream().cuda_stream) == 0
+        assert get.launch(torch.cuda.current_stream().cuda_stream) == 0
+    graph_ok = True
+    for seed in (1, 2):
+        src.copy_(torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device="cuda", generator=torch.Generator("cuda").manual_seed(seed)))
+        back.zero_()
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        graph_ok = graph_ok and bool(torch.equal(back, src))
+    del g
+    # a triple outside the pool is refused when the batch is built, host-to-pool types are refused
+    bad = None
+    try:
+        h.create_batch([src.data_ptr()], [base + pool + 4096], [4096], bm.BmCopyType.L2G)
+    except RuntimeError as e:
+        bad = str(e)
+    host = np.zeros(4096, dtype=np.uint8)
+    bad2 = None
+    try:
+        h.create_batch([host.ctypes.data], [base], [4096], bm.BmCopyType.H2G)
+    except RuntimeError as e:
+        bad2 = str(e)
+    mf.get_and_clear_last_err_msg()
+    put.destroy()
+    get.destroy()
+    h.leave()
+    h.destroy()
+    bm.uninitialize(0)
+    mf.uninitialize()
+    return eager_ok, graph_ok, bad is not None, bad2 is not None
+
+
+def test_prepared_batch_launches_and_replays_in_a_cuda_graph():
+    """mf_bm_batch_create / _launch: validated once, one launch per submission, capturable."""
+    url = f"tcp://127.0.0.1:{free_port()}"
+    assert run_ranks(_prepared_rank, 1, (url,), timeout=180) == [(True, True, True, True)]
