@@ -17,6 +17,8 @@
 // epilogue writes silu(gate) * up (128 columns per tile).
 #include <cuda_bf16.h>
 
+#include <stdlib.h>
+
 #include "mf_gemm.cuh"
 #include "mf_team.cuh"
 
@@ -480,10 +482,10 @@ int fill_common(GemmArgs &g, const void *A, const void *B, int M, int N, int K, 
 
 extern "C" {
 
-// C = A[M,K] . B[N,K]^T (bf16, K contiguous). swiglu != 0: B is tile-interleaved (128 gate rows, 128 up rows per
-// 256) and C is [M, N/2] = silu(gate) * up. status: device int, zero on entry; non-zero = a pipeline wait gave up.
-int mf_gemm_bf16(const void *A, const void *B, void *C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int *status,
-                 int sms, int swiglu, void *stream)
+// C = A[M,K] . B[N,K]^T (bf16, K contiguous) with one CTA per 128 x 256 tile. swiglu != 0: B is tile-interleaved (128 gate rows,
+// 128 up rows per 256) and C is [M, N/2] = silu(gate) * up. status: device int, zero on entry; non-zero = a pipeline wait gave up.
+int mf_gemm_bf16_one(const void *A, const void *B, void *C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int *status,
+                     int sms, int swiglu, void *stream)
 {
     GemmArgs g{};
     int rc = fill_common(g, A, B, M, N, K, lda, ldb, status);
@@ -494,6 +496,28 @@ int mf_gemm_bf16(const void *A, const void *B, void *C, int M, int N, int K, int
     const int tiles = ((M + BM - 1) / BM) * ((N + kBN - 1) / kBN);
     const int grid = tiles < sms ? tiles : sms;
     return swiglu ? launch_gemm<0, 1>(g, grid, (cudaStream_t)stream) : launch_gemm<0, 0>(g, grid, (cudaStream_t)stream);
+}
+
+// The same product; picks the CTA-pair kernel (256 x 256 tiles on two SMs, mf_gemm_2sm.cu) when its tiles fill the
+// SM pairs about as well as the 128 x 256 tiles fill the SMs, else the one-CTA kernel. MF_GEMM_PAIR=0 / 1 forces the choice.
+int mf_gemm_bf16(const void *A, const void *B, void *C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int *status,
+                 int sms, int swiglu, void *stream)
+{
+    static const int forced = [] {
+        const char *e = getenv("MF_GEMM_PAIR");
+        return e == nullptr || *e == 0 ? -1 : atoi(e) != 0;
+    }();
+    bool pair = forced == 1;
+    if (forced < 0 && sms >= 2 && M > 0 && N > 0) {
+        const long t1 = (long)((M + BM - 1) / BM) * ((N + kBN - 1) / kBN), s1 = sms;
+        const long t2 = (long)((M + 2 * BM - 1) / (2 * BM)) * ((N + kBN - 1) / kBN), s2 = sms / 2;
+        // share of the last wave's slots that do work, weighted by how much of each tile is inside the matrix
+        const double fill1 = (double)M * N / ((double)((t1 + s1 - 1) / s1) * s1 * BM * kBN);
+        const double fill2 = (double)M * N / ((double)((t2 + s2 - 1) / s2) * s2 * 2 * BM * kBN);
+        pair = fill2 * 1.04 >= fill1;
+    }
+    if (pair) return mf_gemm_bf16_pair(A, B, C, M, N, K, lda, ldb, ldc, status, sms, swiglu, stream);
+    return mf_gemm_bf16_one(A, B, C, M, N, K, lda, ldb, ldc, status, sms, swiglu, stream);
 }
 
 // All-gather -> GEMM. x_local [shard_rows, K] is this rank's sequence shard; the gather buffer

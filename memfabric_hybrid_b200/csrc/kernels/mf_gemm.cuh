@@ -68,3 +68,7 @@ int make_tmap_2d(CUtensorMap *out, const void *base, int elem_bytes, uint64_t ro
                  uint32_t box_rows, bool is_fp8);
 
 }  // namespace mfk
+
+// CTA-pair bf16 GEMM (mf_gemm_2sm.cu); same arguments as mf_gemm_bf16.
+extern "C" int mf_gemm_bf16_pair(const void *A, const void *B, void *C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
+                                 int *status, int sms, int swiglu, void *stream);

@@ -36,11 +36,13 @@ def case_gemm(args) -> None:
         a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
         b = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
         c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-        ms_ours = _time(lambda: gemm.gemm_bf16(a, b, c), args.iters, 3, flush)
+        ms_ours = _time(lambda: gemm.gemm_bf16(a, b, c, pair=False), args.iters, 3, flush)
+        ms_pair = _time(lambda: gemm.gemm_bf16(a, b, c, pair=True), args.iters, 3, flush)
         gemm.check_status()
         ms_lib = _time(lambda: torch.matmul(a, b.t(), out=c), args.iters, 3, flush)
         fl = 2.0 * M * N * K
         out.append({"M": M, "N": N, "K": K, "ours_ms": round(ms_ours, 4), "ours_tflops": round(fl / ms_ours / 1e9, 1),
+                    "pair_ms": round(ms_pair, 4), "pair_tflops": round(fl / ms_pair / 1e9, 1),
                     "cublas_ms": round(ms_lib, 4), "cublas_tflops": round(fl / ms_lib / 1e9, 1)})
     print(json.dumps({"case": "gemm_bf16", "results": out}))
 

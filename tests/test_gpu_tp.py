@@ -8,7 +8,7 @@ from mp_util import run_ranks
 pytestmark = pytest.mark.gpu
 
 
-def _ranks(rank, world, url, T, H, F, sync):
+def _ranks(rank, world, url, T, H, F, fused1, sync):
     import torch
     from memfabric_hybrid_b200.ops import gemm
     from memfabric_hybrid_b200.ops.heap import SymmetricHeap
@@ -17,6 +17,7 @@ def _ranks(rank, world, url, T, H, F, sync):
     need = (1 << 20) + 2 * T * H * 2 + 2 * T * H * 2 + (8 << 20)
     heap = SymmetricHeap(url, world, rank, dev, need)
     mlp = TensorParallelMLP(heap, H, F, T, seed=3)
+    mlp.tp.plain_at_world1 = not fused1
     rows = T // world
     worst = 0.0
     for it in range(3):  # several calls: exercises the double buffering and the monotonic counters
@@ -44,9 +45,10 @@ def _ranks(rank, world, url, T, H, F, sync):
     return worst, st
 
 
-def test_tp_mlp_world1():
+@pytest.mark.parametrize("fused1", [True, False], ids=["fused_kernels", "plain_gemm"])
+def test_tp_mlp_world1(fused1):
     url = f"127.0.0.1:{free_port()}"
-    (worst, st), = run_ranks(_ranks, 1, (url, 512, 512, 1024), timeout=300, with_barrier=True)
+    (worst, st), = run_ranks(_ranks, 1, (url, 512, 512, 1024, fused1), timeout=300, with_barrier=True)
     assert st == 0 and worst < 3e-2, (worst, st)
 
 
@@ -54,7 +56,7 @@ def test_tp_mlp_world1():
 def test_tp_mlp_multi_gpu():
     n = 2 if torch.cuda.device_count() < 4 else 4
     url = f"127.0.0.1:{free_port()}"
-    res = run_ranks(_ranks, n, (url, 1024, 512, 2048), timeout=300, with_barrier=True)
+    res = run_ranks(_ranks, n, (url, 1024, 512, 2048, True), timeout=300, with_barrier=True)
     for worst, st in res:
         assert st == 0 and worst < 3e-2, res
 
