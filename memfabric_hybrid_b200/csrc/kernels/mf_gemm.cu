@@ -1,6 +1,15 @@
 // bf16 GEMM on the 5th-generation tensor cores: C[M,N] = A[M,K] . B[N,K]^T, fp32 accumulation in TMEM.
-// Persistent kernel, one CTA per SM, 128 x 256 tiles, 4-stage TMA ring, two TMEM accumulators so that
-// the epilogue of tile i overlaps the main loop of tile i+1.
+// Persistent kernel, one CTA per SM, two TMEM accumulators so that the epilogue of tile i overlaps the main loop of
+// tile i+1. Two tilings (template parameter PAIR):
+//   PAIR false: every CTA works alone on 128 x 256 tiles (cta_group::1), 4-stage TMA ring of 48 KiB stages.
+//   PAIR true : the two CTAs of a cluster (the two SMs of one TPC) share one 256 x 256 tile (cta_group::2). Each CTA loads
+//       its own 128 rows of A and its own 128 of the tile's 256 rows of B (half the B bytes per SM), 6 stages of 32 KiB.
+//       The leader CTA's MMA thread issues the MMAs, which read both CTAs' shared memory and write 128 rows x 256 columns
+//       of accumulators into EACH CTA's tensor memory; each CTA's epilogue warps store their own 128 rows. The pair form
+//       of the TMA load counts its bytes on the LEADER's "full" barrier (every CTA fetches its own tiles; the leader's
+//       producer expects the bytes of both); the leader commits each stage's MMAs to its own "empty" barrier and to the
+//       peer's (two plain commits, the second on the peer's barrier address from mapa), likewise the accumulator's
+//       "full" barrier; the peer's epilogue warps release the accumulator on the leader's barrier with a remote arrive.
 //
 // The same kernel carries the two tensor-parallel fusions (template parameter MODE):
 //   MODE 1, all-gather -> GEMM : the A operand is a gather buffer in THIS GPU's slot of the symmetric
@@ -84,7 +93,8 @@ struct GemmArgs {
 constexpr int kCopyWarps = 4;
 
 // Maps the t-th tile of this CTA's walk to (row tile, column tile).
-template <int MODE, int BN> __device__ __forceinline__ void tile_mn(const GemmArgs &g, int t, int m_tiles, int n_tiles, int &mt, int &nt)
+// Row tiles are TM rows high (128, or 256 for a CTA pair).
+template <int MODE, int BN, int TM> __device__ __forceinline__ void tile_mn(const GemmArgs &g, int t, int m_tiles, int n_tiles, int &mt, int &nt)
 {
     if (MODE == 0) {
         // bands of 8 row tiles; inside a band the column varies slowest so that CTAs running together share B tiles
@@ -99,7 +109,7 @@ template <int MODE, int BN> __device__ __forceinline__ void tile_mn(const GemmAr
         // blocks of rows owned by one rank, visited starting with this rank (MODE 1: the order in which shards
         // arrive) or with the next rank (MODE 2: remote owners first, own rows last)
         const int rows = MODE == 1 ? g.shard_rows : g.rows_per_rank;
-        const int mt_per = rows / BM;
+        const int mt_per = rows / TM;
         const int per_block = mt_per * n_tiles;
         const int i = t / per_block;
         const int owner = (int)((g.team.rank + (MODE == 2 ? 1 : 0) + i) % g.team.world);
@@ -109,14 +119,19 @@ template <int MODE, int BN> __device__ __forceinline__ void tile_mn(const GemmAr
     }
 }
 
-template <int MODE, int EPI, int BN, int STAGES>
+template <int MODE, int EPI, int BN, int STAGES, bool PAIR>
 __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 0), 1) k_gemm_bf16(const __grid_constant__ GemmArgs g)
 {
     extern __shared__ uint8_t smem_raw[];
-    GemmSmem<BN, STAGES> sm(smem_raw);
+    using SM = GemmSmem<BN, STAGES, PAIR ? BN / 2 : BN>;
+    constexpr int TM = PAIR ? 2 * BM : BM;  // rows of one tile
+    SM sm(smem_raw);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int m_tiles = (g.M + BM - 1) / BM;
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0;          // 0: the CTA that issues the MMAs
+    const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;  // tile walkers: CTAs, or CTA pairs
+    const int walkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int m_tiles = (g.M + TM - 1) / TM;
     const int n_tiles = (g.N + BN - 1) / BN;
     const int total = m_tiles * n_tiles;
     const int k_iters = (g.K * 2 + KSPAN - 1) / KSPAN;
@@ -131,30 +146,36 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
         }
         for (int i = 0; i < 2; i++) {
             mbar_init(sm.tfull(i), 1);
-            mbar_init(sm.tempty(i), 4);
+            mbar_init(sm.tempty(i), PAIR ? 8 : 4);  // the epilogue warps of every CTA of the tile (counted in the leader)
         }
         mbar_fence_init();
         tma_prefetch_desc(&g.tm.a);
         tma_prefetch_desc(&g.tm.b);
     }
     if (warp == 1) {
-        tmem_alloc(sm.tmem_slot(), 2 * BN);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(sm.tmem_slot(), 2 * BN);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(sm.tmem_slot(), 2 * BN);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // both CTAs' barriers are initialised and both halves of the tensor memory are allocated
     tc_fence_after();
     const uint32_t tmem_base = *sm.tmem_slot();
 
     if (warp == 0) {
         if (elect_one()) {
             PipeState ps;
-            for (int t = blockIdx.x; t < total; t += gridDim.x) {
+            for (int t = walker; t < total; t += walkers) {
                 int mt, nt;
-                tile_mn<MODE, BN>(g, t, m_tiles, n_tiles, mt, nt);
+                tile_mn<MODE, BN, TM>(g, t, m_tiles, n_tiles, mt, nt);
                 if (MODE == 1) {
                     // the shard holding this tile's rows must have landed in this GPU's gather buffer
-                    const int r = mt * BM / g.shard_rows;
+                    const int r = mt * TM / g.shard_rows;
                     const uint32_t *ready = reinterpret_cast<const uint32_t *>(peer_ptr(g.team, me, g.ag_ready_off)) + r;
                     if (!wait_flag(ready, g.epoch, g.team.spin_limit)) {
                         *ac.abort_smem = 1;
@@ -167,22 +188,30 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
                 for (int kb = 0; kb < k_iters; kb++) {
                     fine = mbar_wait(sm.empty(ps.stage), ps.phase ^ 1, ac, 0x302);
                     if (!fine) break;
-                    mbar_expect_tx(sm.full(ps.stage), GemmSmem<BN, STAGES>::kStageBytes);
-                    tma_load_2d(sm.a(ps.stage), &g.tm.a, kb * (KSPAN / 2), mt * BM, sm.full(ps.stage));
-                    tma_load_2d(sm.b(ps.stage), &g.tm.b, kb * (KSPAN / 2), nt * BN, sm.full(ps.stage));
+                    if (PAIR) {
+                        // both CTAs' tiles are counted on the leader's barrier
+                        if (crank == 0) mbar_expect_tx(sm.full(ps.stage), 2 * SM::kStageBytes);
+                        const uint32_t lead_full = mapa_u32(smem_u32(sm.full(ps.stage)), 0);
+                        tma_load_2d_pair(sm.a(ps.stage), &g.tm.a, kb * (KSPAN / 2), mt * TM + (int)crank * BM, lead_full);
+                        tma_load_2d_pair(sm.b(ps.stage), &g.tm.b, kb * (KSPAN / 2), nt * BN + (int)crank * (BN / 2), lead_full);
+                    } else {
+                        mbar_expect_tx(sm.full(ps.stage), SM::kStageBytes);
+                        tma_load_2d(sm.a(ps.stage), &g.tm.a, kb * (KSPAN / 2), mt * BM, sm.full(ps.stage));
+                        tma_load_2d(sm.b(ps.stage), &g.tm.b, kb * (KSPAN / 2), nt * BN, sm.full(ps.stage));
+                    }
                     ps.advance<STAGES>();
                 }
                 if (!fine) break;
             }
         }
     } else if (warp == 1) {
-        if (elect_one()) {
+        if (crank == 0 && elect_one()) {
             PipeState ps;
             int acc = 0;
             uint32_t acc_phase = 0;
-            const uint32_t idesc = umma_idesc(1, 1, BM, BN);
+            const uint32_t idesc = umma_idesc(1, 1, TM, BN);
             bool fine = true;
-            for (int t = blockIdx.x; t < total && fine; t += gridDim.x) {
+            for (int t = walker; t < total && fine; t += walkers) {
                 fine = mbar_wait(sm.tempty(acc), acc_phase ^ 1, ac, 0x303);
                 if (!fine) break;
                 tc_fence_after();
@@ -194,13 +223,28 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
                     const uint64_t da = umma_desc_sw128(sm.a(ps.stage));
                     const uint64_t db = umma_desc_sw128(sm.b(ps.stage));
 #pragma unroll
-                    for (int k = 0; k < KSPAN / 32; k++)  // 32 bytes = 16 bf16 = one UMMA K step
-                        umma_bf16(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) != 0);
-                    umma_commit(sm.empty(ps.stage));
+                    for (int k = 0; k < KSPAN / 32; k++) {  // 32 bytes = 16 bf16 = one UMMA K step
+                        if (PAIR) umma_bf16_pair(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) != 0);
+                        else umma_bf16(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb | k) != 0);
+                    }
+                    if (PAIR) {
+                        // the stage is free in both CTAs once these MMAs have read it
+                        const uint32_t e = smem_u32(sm.empty(ps.stage));
+                        umma_commit_pair(e);
+                        umma_commit_pair(mapa_u32(e, 1));
+                    } else {
+                        umma_commit(sm.empty(ps.stage));
+                    }
                     ps.advance<STAGES>();
                 }
                 if (!fine) break;
-                umma_commit(sm.tfull(acc));
+                if (PAIR) {
+                    const uint32_t f = smem_u32(sm.tfull(acc));
+                    umma_commit_pair(f);
+                    umma_commit_pair(mapa_u32(f, 1));
+                } else {
+                    umma_commit(sm.tfull(acc));
+                }
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1;
             }
@@ -209,9 +253,10 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
         const int quad = warp & 3;  // TMEM lane quadrant this warp may read
         int acc = 0;
         uint32_t acc_phase = 0;
-        for (int t = blockIdx.x; t < total; t += gridDim.x) {
+        for (int t = walker; t < total; t += walkers) {
             int mt, nt;
-            tile_mn<MODE, BN>(g, t, m_tiles, n_tiles, mt, nt);
+            tile_mn<MODE, BN, TM>(g, t, m_tiles, n_tiles, mt, nt);
+            if (PAIR) mt = 2 * mt + (int)crank;  // from here on: this CTA's 128-row tile
             // the whole warp must take the same branch: the TMEM loads below are warp-collective
             if (!__all_sync(0xffffffffu, mbar_wait(sm.tfull(acc), acc_phase, ac, 0x305))) break;
             tc_fence_after();
@@ -256,7 +301,6 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
                 if (vec_ok && nt * BN + BN <= g.N) {
                     // full tile: 64 columns at a time through shared memory, so that every store instruction
                     // writes 4 rows x 128 contiguous bytes instead of 32 rows x 16 bytes (what counts on NVLink)
-                    using SM = GemmSmem<BN, STAGES>;
                     uint8_t *stg = sm.out_stage(warp - 2);
                     const int64_t ld = MODE == 2 ? (int64_t)g.N : g.ldc;
                     __nv_bfloat16 *tile_dst;
@@ -335,7 +379,11 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
                 }
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(sm.tempty(acc));
+            if (lane == 0) {
+                // this CTA's half of the accumulator is out of tensor memory: tell the MMA thread (in the leader)
+                if (!PAIR || crank == 0) mbar_arrive(sm.tempty(acc));
+                else mbar_arrive_cluster(mapa_u32(smem_u32(sm.tempty(acc)), 0));
+            }
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
         }
@@ -387,9 +435,11 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
     }
     tc_fence_before();
     __syncthreads();
+    if (PAIR) cluster_sync_all();  // nobody signals a barrier of a CTA that has left, and both halves are freed together
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 2 * BN);
+        if (PAIR) tmem_dealloc_pair(tmem_base, 2 * BN);
+        else tmem_dealloc(tmem_base, 2 * BN);
     }
     if (MODE == 2) {
         // reduce the W partial tiles of every tile whose rows this rank owns
@@ -448,30 +498,59 @@ __global__ void __launch_bounds__(kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 
 using namespace mfk;
 
 namespace {
-constexpr int kBN = 256, kStages = 4;
+constexpr int kBN = 256, kStages = 4, kPairStages = 6;
 
-template <int MODE, int EPI> int launch_gemm(const GemmArgs &g, int grid, cudaStream_t s)
+template <int MODE, int EPI, bool PAIR> int launch_gemm(const GemmArgs &g, int grid, cudaStream_t s)
 {
-    auto kern = k_gemm_bf16<MODE, EPI, kBN, kStages>;
+    using SM = GemmSmem<kBN, PAIR ? kPairStages : kStages, PAIR ? kBN / 2 : kBN>;
+    static_assert(SM::kDynBytes <= 227 * 1024, "shared memory of the bf16 GEMM");
+    auto kern = k_gemm_bf16<MODE, EPI, kBN, PAIR ? kPairStages : kStages, PAIR>;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmem<kBN, kStages>::kDynBytes) != cudaSuccess) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SM::kDynBytes) != cudaSuccess) {
             (void)cudaGetLastError();
             return -2;
         }
         attr_set = true;
     }
     const int threads = kGemmThreads + (MODE == 1 ? kCopyWarps * 32 : 0);
-    kern<<<grid, threads, GemmSmem<kBN, kStages>::kDynBytes, s>>>(g);
-    cudaError_t e = cudaGetLastError();
+    if (!PAIR) {
+        kern<<<grid, threads, SM::kDynBytes, s>>>(g);
+        cudaError_t e = cudaGetLastError();
+        return e == cudaSuccess ? 0 : (int)e;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((unsigned)grid);  // even: CTAs 2c and 2c + 1 form cluster c
+    cfg.blockDim = dim3((unsigned)threads);
+    cfg.dynamicSmemBytes = SM::kDynBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, g);
+    if (e != cudaSuccess) (void)cudaGetLastError();
     return e == cudaSuccess ? 0 : (int)e;
 }
 
-int fill_common(GemmArgs &g, const void *A, const void *B, int M, int N, int K, int64_t lda, int64_t ldb, int *status)
+// MF_GEMM_PAIR: 0 never pairs, 1 pairs wherever the shape allows, unset: the library decides.
+int pair_forced()
+{
+    static const int forced = [] {
+        const char *e = getenv("MF_GEMM_PAIR");
+        return e == nullptr || *e == 0 ? -1 : (atoi(e) != 0 ? 1 : 0);
+    }();
+    return forced;
+}
+
+int fill_common(GemmArgs &g, const void *A, const void *B, int M, int N, int K, int64_t lda, int64_t ldb, int *status, bool pair = false)
 {
     if (M <= 0 || N <= 0 || K <= 0 || (K & 7) != 0) return -1;
     int rc = make_tmap_2d(&g.tm.a, A, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, BM, false);
-    if (rc == 0) rc = make_tmap_2d(&g.tm.b, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, kBN, false);
+    if (rc == 0) rc = make_tmap_2d(&g.tm.b, B, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, pair ? kBN / 2 : kBN, false);
     g.M = M;
     g.N = N;
     g.K = K;
@@ -495,19 +574,32 @@ int mf_gemm_bf16_one(const void *A, const void *B, void *C, int M, int N, int K,
     g.ldc = ldc;
     const int tiles = ((M + BM - 1) / BM) * ((N + kBN - 1) / kBN);
     const int grid = tiles < sms ? tiles : sms;
-    return swiglu ? launch_gemm<0, 1>(g, grid, (cudaStream_t)stream) : launch_gemm<0, 0>(g, grid, (cudaStream_t)stream);
+    return swiglu ? launch_gemm<0, 1, false>(g, grid, (cudaStream_t)stream) : launch_gemm<0, 0, false>(g, grid, (cudaStream_t)stream);
 }
 
-// The same product; picks the CTA-pair kernel (256 x 256 tiles on two SMs, mf_gemm_2sm.cu) when its tiles fill the
+// The same product on CTA pairs (256 x 256 tiles). Needs at least two SMs.
+int mf_gemm_bf16_pair(const void *A, const void *B, void *C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int *status,
+                      int sms, int swiglu, void *stream)
+{
+    if (sms < 2) return -1;
+    GemmArgs g{};
+    int rc = fill_common(g, A, B, M, N, K, lda, ldb, status, true);
+    if (rc != 0) return rc;
+    if (swiglu && (N % kBN) != 0) return -3;
+    g.C = static_cast<__nv_bfloat16 *>(C);
+    g.ldc = ldc;
+    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + kBN - 1) / kBN);
+    const int grid = 2 * (tiles < sms / 2 ? tiles : sms / 2);
+    return swiglu ? launch_gemm<0, 1, true>(g, grid, (cudaStream_t)stream) : launch_gemm<0, 0, true>(g, grid, (cudaStream_t)stream);
+}
+
+// The same product; picks the CTA-pair tiling (256 x 256 tiles on two SMs) when its tiles fill the
 // SM pairs about as well as the 128 x 256 tiles fill the SMs, else the one-CTA kernel. MF_GEMM_PAIR=0 / 1 forces the choice.
 int mf_gemm_bf16(const void *A, const void *B, void *C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int *status,
                  int sms, int swiglu, void *stream)
 {
-    static const int forced = [] {
-        const char *e = getenv("MF_GEMM_PAIR");
-        return e == nullptr || *e == 0 ? -1 : atoi(e) != 0;
-    }();
-    bool pair = forced == 1;
+    const int forced = pair_forced();
+    bool pair = forced == 1 && sms >= 2;
     if (forced < 0 && sms >= 2 && M > 0 && N > 0) {
         const long t1 = (long)((M + BM - 1) / BM) * ((N + kBN - 1) / kBN), s1 = sms;
         const long t2 = (long)((M + 2 * BM - 1) / (2 * BM)) * ((N + kBN - 1) / kBN), s2 = sms / 2;
@@ -530,7 +622,9 @@ int mf_ag_gemm_bf16(const Team *team, const void *x_local, int64_t ldx, int shar
     GemmArgs g{};
     const int M = shard_rows * (int)team->world;
     const void *A = reinterpret_cast<const void *>(team->heap_base + (uint64_t)team->rank * team->stride + ag_buf_off);
-    int rc = fill_common(g, A, B, M, N, K, K, ldb, status);
+    // pairs need every shard to be whole 256-row tiles, and a grid of whole clusters
+    const bool pair = pair_forced() != 0 && (shard_rows % (2 * BM)) == 0 && (sms & 1) == 0 && sms >= 2;
+    int rc = fill_common(g, A, B, M, N, K, K, ldb, status, pair);
     if (rc != 0) return rc;
     if (swiglu && (N % kBN) != 0) return -3;
     g.C = static_cast<__nv_bfloat16 *>(C);
@@ -545,7 +639,8 @@ int mf_ag_gemm_bf16(const Team *team, const void *x_local, int64_t ldx, int shar
     g.ag_ready_off = ag_ready_off;
     g.push_count = push_count;
     // every CTA carries copy warps whose work peers wait for: the grid must be fully resident
-    return swiglu ? launch_gemm<1, 1>(g, sms, (cudaStream_t)stream) : launch_gemm<1, 0>(g, sms, (cudaStream_t)stream);
+    if (pair) return swiglu ? launch_gemm<1, 1, true>(g, sms, (cudaStream_t)stream) : launch_gemm<1, 0, true>(g, sms, (cudaStream_t)stream);
+    return swiglu ? launch_gemm<1, 1, false>(g, sms, (cudaStream_t)stream) : launch_gemm<1, 0, false>(g, sms, (cudaStream_t)stream);
 }
 
 // GEMM -> reduce-scatter. A [M, K] (M = world * rows_per_rank), B [N, K]; y_out [rows_per_rank, N] = scale * sum over ranks.
@@ -556,7 +651,8 @@ int mf_gemm_rs_bf16(const Team *team, const void *A, int64_t lda, const void *B,
     if (team == nullptr || rows_per_rank <= 0 || (rows_per_rank % BM) != 0 || (N & 7) != 0 || team->emu) return -1;
     GemmArgs g{};
     const int M = rows_per_rank * (int)team->world;
-    int rc = fill_common(g, A, B, M, N, K, lda, ldb, status);
+    const bool pair = pair_forced() != 0 && (rows_per_rank % (2 * BM)) == 0 && (sms & 1) == 0 && sms >= 2;
+    int rc = fill_common(g, A, B, M, N, K, lda, ldb, status, pair);
     if (rc != 0) return rc;
     g.team = *team;
     g.epoch = epoch;
@@ -567,7 +663,7 @@ int mf_gemm_rs_bf16(const Team *team, const void *A, int64_t lda, const void *B,
     g.y_out = static_cast<__nv_bfloat16 *>(y_out);
     g.ldy = ldy;
     g.scale = scale;
-    return launch_gemm<2, 0>(g, sms, (cudaStream_t)stream);
+    return pair ? launch_gemm<2, 0, true>(g, sms, (cudaStream_t)stream) : launch_gemm<2, 0, false>(g, sms, (cudaStream_t)stream);
 }
 
 }  // extern "C"

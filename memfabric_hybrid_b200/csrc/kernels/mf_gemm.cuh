@@ -23,10 +23,10 @@ struct alignas(64) TmaPair {
     CUtensorMap b;
 };
 
-// dynamic shared memory: [stage][A 16 KiB | B BN*128 B] then barriers
-template <int BN, int STAGES> struct GemmSmem {
+// dynamic shared memory: [stage][A 16 KiB | B BROWS*128 B] then barriers. BROWS = BN, or BN / 2 where a CTA pair shares the tile
+template <int BN, int STAGES, int BROWS = BN> struct GemmSmem {
     static constexpr int kABytes = BM * KSPAN;
-    static constexpr int kBBytes = BN * KSPAN;
+    static constexpr int kBBytes = BROWS * KSPAN;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarOff = STAGES * kStageBytes;
     // epilogue staging: each of the 4 epilogue warps turns 32 rows x 64 columns of bf16 around (one row per lane
@@ -68,7 +68,3 @@ int make_tmap_2d(CUtensorMap *out, const void *base, int elem_bytes, uint64_t ro
                  uint32_t box_rows, bool is_fp8);
 
 }  // namespace mfk
-
-// CTA-pair bf16 GEMM (mf_gemm_2sm.cu); same arguments as mf_gemm_bf16.
-extern "C" int mf_gemm_bf16_pair(const void *A, const void *B, void *C, int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc,
-                                 int *status, int sms, int swiglu, void *stream);

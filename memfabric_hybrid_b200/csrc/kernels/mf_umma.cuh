@@ -153,6 +153,65 @@ __device__ __forceinline__ void umma_fp8(uint32_t tmem_d, uint64_t desc_a, uint6
         : "memory");
 }
 
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster on the two SMs of one TPC share one MMA -----------------
+// The leader (cluster rank 0) issues tcgen05.mma.cta_group::2 with M = 256: it reads 128 rows of A and half of the B tile
+// from EACH CTA's shared memory (same offsets in both) and writes 128 rows x N columns into each CTA's tensor memory.
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of `local` (a shared-memory address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2-D tile load of the CTA-pair form into this CTA's shared memory; the bytes are counted on the barrier at cluster address
+// `bar_cluster` (the leader's). Every CTA fetches its own tiles.
+__device__ __forceinline__ void tma_load_2d_pair(void *smem_dst, const CUtensorMap *m, int x, int y, uint32_t bar_cluster)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     smem_u32(smem_dst)),
+                 "l"(m), "r"(x), "r"(y), "r"(bar_cluster)
+                 : "memory");
+}
+// Both CTAs' allocating warps execute these; the pair gets the same columns in both tensor memories.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the barrier at `cluster_addr` (either CTA of the pair) once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+
 // ---- block-scaled fp8 (kind::mxf8f6f4): D += (A * 2^(sfa - 127)) . (B * 2^(sfb - 127))^T, one UE8M0 scale byte
 // per operand row per 32 elements of K, read by the tensor core from TMEM ---------------------------------
 // Instruction descriptor of the block-scaled kind: e4m3 x e4m3, K-major, scale format E8M0; sf ids pick the

@@ -1,4 +1,4 @@
-"""tcgen05 / TMEM GEMMs (csrc/kernels/mf_gemm.cu, mf_gemm_2sm.cu, mf_gemm_fp8.cu).
+"""tcgen05 / TMEM GEMMs (csrc/kernels/mf_gemm.cu, mf_gemm_fp8.cu, mf_gemm_fp8_mx.cu).
 
     gemm_bf16(a, b)                  C[M,N] = A[M,K] . B[N,K]^T   (bf16 in, fp32 accumulate in TMEM, bf16 out)
 

@@ -545,7 +545,11 @@ def run(rank, world, local, _bm_handle):
         os.environ.setdefault("MF_SHM_MULTICAST", "1")
     out = {"peaks": _peaks()}
 
+    only = [x for x in os.environ.get("MF_BENCH_SECTIONS", "").split(",") if x]   # e.g. "tp_mlp,moe_ep"; empty: all
+
     def section(name, fn):
+        if only and name not in only:
+            return
         try:
             out[name] = fn()
         except Exception as e:  # noqa: BLE001  (one failing section must not take the others, or the headline, with it)
