@@ -92,6 +92,7 @@ def _declare_host(l):
     _sig(l, "smem_set_extern_logger", i32, LOG_FN)
     _sig(l, "smem_set_log_level", i32, C.c_int)
     _sig(l, "smem_set_conf_store_tls", i32, C.c_bool, cp, u32)
+    _sig(l, "smem_set_config_store_tls_key", i32, cp, u32, cp, u32, C.c_void_p)
     _sig(l, "smem_get_last_err_msg", cp)
     _sig(l, "smem_get_last_err_code", i32)
     _sig(l, "smem_get_and_clear_last_err_msg", cp)

@@ -51,9 +51,16 @@ def set_conf_store_tls(enable: bool, tls_info: str = "") -> int:
     return N.lib().smem_set_conf_store_tls(bool(enable), b, len(b))
 
 
-def set_conf_store_tls_key(tls_pk: str, tls_pk_pw: str, py_decrypt_func=None) -> int:
-    # Key material is accepted for call compatibility; TLS itself is refused when switched on.
-    return 0 if tls_pk else -2000
+def set_conf_store_tls_key(tls_pk: str, tls_pk_pw: str = "", py_decrypt_func: Callable[[str], str] | None = None) -> int:
+    """Private key of this process's store links: PEM text or the path of a PEM file; tls_pk_pw is its pass phrase, turned
+    into plain text by py_decrypt_func when one is given. Applies to stores created afterwards."""
+    if not tls_pk:
+        return -2000
+    pw = tls_pk_pw or ""
+    if pw and py_decrypt_func is not None:
+        pw = py_decrypt_func(pw)
+    k, w = tls_pk.encode(), pw.encode()
+    return N.lib().smem_set_config_store_tls_key(k, len(k), w if w else None, len(w), None)
 
 
 def get_last_err_msg() -> str:

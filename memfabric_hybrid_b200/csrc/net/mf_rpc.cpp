@@ -77,7 +77,14 @@ bool MakeAddr(const std::string &ip, uint16_t port, sockaddr_in &sa)
 
 Link::~Link()
 {
+    tls_.reset();  // close_notify goes out while the socket is still open
     if (fd_ >= 0) ::close(fd_);
+}
+
+bool Link::WriteRaw(const void *buf, size_t len) { return tls_ ? tls_->WriteAll(buf, len) : WriteAll(fd_, buf, len); }
+bool Link::ReadRawTimed(void *buf, size_t len, uint32_t timeoutMs)
+{
+    return tls_ ? tls_->ReadAll(buf, len, timeoutMs) : ReadAllTimed(fd_, buf, len, timeoutMs);
 }
 
 int Link::Send(int16_t type, int16_t result, uint32_t seqNo, const void *body, uint32_t len)
@@ -94,13 +101,13 @@ int Link::Send(int16_t type, int16_t result, uint32_t seqNo, const void *body, u
         char tmp[sizeof(MsgHeader) + 1024];
         memcpy(tmp, &h, sizeof(h));
         if (len > 0) memcpy(tmp + sizeof(h), body, len);
-        if (!WriteAll(fd_, tmp, sizeof(h) + len)) {
+        if (!WriteRaw(tmp, sizeof(h) + len)) {
             Shutdown();
             return ERR_NOT_CONNECTED;
         }
         return OK;
     }
-    if (!WriteAll(fd_, &h, sizeof(h)) || !WriteAll(fd_, body, len)) {
+    if (!WriteRaw(&h, sizeof(h)) || !WriteRaw(body, len)) {
         Shutdown();
         return ERR_NOT_CONNECTED;
     }
@@ -180,20 +187,32 @@ void Endpoint::AcceptLoop()
         int fd = accept4(listenFd_, nullptr, nullptr, SOCK_CLOEXEC);
         if (fd < 0) continue;
         TuneSocket(fd);
+        std::unique_ptr<TlsSession> session;
+        if (opt_.tls) {
+            std::string why;
+            session = opt_.tls->Handshake(fd, true, 5000, why);
+            if (!session) {
+                MF_WARN("refused a connection: %s", why.c_str());
+                ::close(fd);
+                continue;
+            }
+        }
         ConnReq req;
-        if (!ReadAllTimed(fd, &req, sizeof(req), 5000)) {
+        if (!(session ? session->ReadAll(&req, sizeof(req), 5000) : ReadAllTimed(fd, &req, sizeof(req), 5000))) {
+            session.reset();
             ::close(fd);
             continue;
         }
         ConnResp resp;
         auto link = std::make_shared<Link>(fd, nextLinkId_.fetch_add(1), req.rankId, true);
+        link->tls_ = std::move(session);
         link->lastSeenMs = NowMs();
         if (req.magic != opt_.magic || req.version != opt_.version) {
             resp.result = -1;
         } else if (newLink_) {
             resp.result = (int16_t)newLink_(req, link);
         }
-        if (!WriteAll(fd, &resp, sizeof(resp)) || resp.result != 0) {
+        if (!link->WriteRaw(&resp, sizeof(resp)) || resp.result != 0) {
             link->closed_ = true;
             if (resp.result == 0 && broken_) broken_(link);  // admitted but the peer vanished
             continue;  // link destructor closes fd
@@ -247,16 +266,30 @@ int Endpoint::Connect(const std::string &ip, uint16_t port, const ConnReq &req, 
     r.magic = opt_.magic;
     r.version = opt_.version;
     ConnResp resp;
-    if (!WriteAll(fd, &r, sizeof(r)) || !ReadAllTimed(fd, &resp, sizeof(resp), timeoutMs == 0 ? 5000 : timeoutMs)) {
+    std::unique_ptr<TlsSession> session;
+    if (opt_.tls) {
+        std::string why;
+        session = opt_.tls->Handshake(fd, false, timeoutMs == 0 ? 5000 : timeoutMs, why);
+        if (!session) {
+            ::close(fd);
+            return MF_FAIL(ERR_NOT_CONNECTED, "TLS to %s:%u: %s", ip.c_str(), (unsigned)port, why.c_str());
+        }
+    }
+    const uint32_t respMs = timeoutMs == 0 ? 5000 : timeoutMs;
+    const bool sent = session ? session->WriteAll(&r, sizeof(r)) : WriteAll(fd, &r, sizeof(r));
+    if (!sent || !(session ? session->ReadAll(&resp, sizeof(resp), respMs) : ReadAllTimed(fd, &resp, sizeof(resp), respMs))) {
+        session.reset();
         ::close(fd);
         return ERR_NOT_CONNECTED;
     }
     if (resp.result != 0) {
+        session.reset();
         ::close(fd);
         if (refused != nullptr) *refused = resp.result;
         return ERR_RECONNECT;
     }
     out = std::make_shared<Link>(fd, nextLinkId_.fetch_add(1), req.rankId, false);
+    out->tls_ = std::move(session);
     out->lastSeenMs = NowMs();
     Attach(out);
     return OK;
@@ -266,12 +299,19 @@ bool Endpoint::Drain(Worker *, const LinkPtr &l)
 {
     for (;;) {
         if (l->in_.size() - l->inUsed_ < 65536) l->in_.resize(std::max<size_t>(l->in_.size() * 2, 131072));
-        ssize_t n = ::recv(l->fd_, l->in_.data() + l->inUsed_, l->in_.size() - l->inUsed_, MSG_DONTWAIT);
-        if (n == 0) return false;
-        if (n < 0) {
-            if (errno == EINTR) continue;
-            if (errno == EAGAIN || errno == EWOULDBLOCK) break;
-            return false;
+        ssize_t n;
+        if (l->tls_) {
+            n = l->tls_->ReadSome(l->in_.data() + l->inUsed_, l->in_.size() - l->inUsed_);
+            if (n == 0) break;  // everything the socket and the TLS layer held has been taken
+            if (n < 0) return false;
+        } else {
+            n = ::recv(l->fd_, l->in_.data() + l->inUsed_, l->in_.size() - l->inUsed_, MSG_DONTWAIT);
+            if (n == 0) return false;
+            if (n < 0) {
+                if (errno == EINTR) continue;
+                if (errno == EAGAIN || errno == EWOULDBLOCK) break;
+                return false;
+            }
         }
         l->inUsed_ += (size_t)n;
         l->lastSeenMs.store(NowMs(), std::memory_order_relaxed);

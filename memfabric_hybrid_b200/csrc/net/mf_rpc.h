@@ -10,6 +10,8 @@
 #include <map>
 #include <unordered_map>
 
+#include "mf_tls.h"
+
 #include "../util/mf_util.h"
 
 namespace mf {
@@ -58,7 +60,10 @@ public:
 
 private:
     friend class Endpoint;
+    bool WriteRaw(const void *buf, size_t len);                   // through TLS when the link has a session
+    bool ReadRawTimed(void *buf, size_t len, uint32_t timeoutMs);
     int fd_;
+    std::unique_ptr<TlsSession> tls_;  // set once, before the link is shared between threads
     uint64_t id_;
     uint64_t peerTag_;
     bool accepted_;
@@ -76,6 +81,7 @@ struct EndpointOptions {
     int16_t version = 0;
     uint32_t pollMs = 500;
     bool reusePort = false;
+    std::shared_ptr<TlsContext> tls;  // set: every link is TLS 1.3 with mutual certificate verification
 };
 
 class Endpoint {

@@ -83,13 +83,11 @@ int32_t smem_set_conf_store_tls(bool enable, const char *tls_info, const uint32_
 int32_t smem_set_config_store_tls_key(const char *tls_pk, const uint32_t tls_pk_len, const char *tls_pk_pw,
                                       const uint32_t tls_pk_pw_len, const smem_decrypt_handler h)
 {
-    (void)tls_pk_pw;
-    (void)tls_pk_pw_len;
-    (void)h;
-    if (tls_pk == nullptr || tls_pk_len == 0) return MF_FAIL(SMEM_INVALID_PARAM, "private key is empty");
-    // Key material is accepted so that callers' start-up code runs unchanged; it only matters once TLS is
-    // switched on, which this build refuses (see StoreFactory::SetTls).
-    return SMEM_OK;
+    if (tls_pk == nullptr || tls_pk_len == 0) return smem::Pub(store::StoreFactory::SetTlsKey("", "", nullptr));  // forget the key
+    // tls_pk: the key as PEM text, or the path of a PEM file. tls_pk_pw: its pass phrase (cipher text when a decrypt
+    // handler is given). Takes effect for stores created after this call.
+    std::string pass = (tls_pk_pw != nullptr && tls_pk_pw_len > 0) ? std::string(tls_pk_pw, tls_pk_pw_len) : std::string();
+    return smem::Pub(store::StoreFactory::SetTlsKey(std::string(tls_pk, tls_pk_len), pass, h));
 }
 
 const char *smem_get_last_err_msg(void) { return LastError::Msg(); }

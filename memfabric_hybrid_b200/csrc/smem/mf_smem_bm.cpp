@@ -65,6 +65,24 @@ int32_t smem_bm_init(const char *storeURL, uint32_t worldSize, uint16_t deviceId
     if (g_bm.inited) return MF_FAIL(SMEM_REPEAT_INVOKE, "smem_bm_init called twice");
     FaultPoints::RegisterBuiltins();
 
+    if (config->storeTlsConfig.tlsEnable) {
+        // the path fields of the config select TLS for this process's store links (same effect as smem_set_conf_store_tls)
+        const smem_tls_config &t = config->storeTlsConfig;
+        auto str = [](const char *a, size_t n) { return std::string(a, strnlen(a, n)); };
+        net::TlsSettings ts;
+        ts.enable = true;
+        ts.caPath = str(t.caPath, sizeof(t.caPath));
+        ts.crlPath = str(t.crlPath, sizeof(t.crlPath));
+        if (!ts.crlPath.empty()) ts.crlFiles.push_back(ts.crlPath);  // the config names one CRL file
+        ts.certPath = str(t.certPath, sizeof(t.certPath));
+        ts.keyPath = str(t.keyPath, sizeof(t.keyPath));
+        ts.keyPassPath = str(t.keyPassPath, sizeof(t.keyPassPath));
+        ts.packagePath = str(t.packagePath, sizeof(t.packagePath));
+        ts.decrypterLibPath = str(t.decrypterLibPath, sizeof(t.decrypterLibPath));
+        int rc = store::StoreFactory::SetTlsConfig(ts);
+        if (rc != OK) return Pub(rc);
+    }
+
     if (config->startConfigStoreOnly) {
         int rc = store::StoreFactory::CreateServerOnly(storeURL, worldSize, 0);
         if (rc != OK) return Pub(rc);

@@ -320,6 +320,7 @@ struct StoreUrl {
 struct TlsOptions {
     bool enable = false;
     std::string info;
+    net::TlsSettings settings;
 };
 
 class StoreFactory {
@@ -332,8 +333,14 @@ public:
     static void DestroyServer(const std::string &url);  // counterpart of CreateServerOnly
     static void DestroyAll();
     static StorePtr Prefixed(const StorePtr &base, const std::string &prefix);
+    // TLS for every store link of this process: SetTls takes the "key: value; ..." info string, SetTlsConfig the path
+    // fields of a smem_tls_config, SetTlsKey the private key (a PEM text or a file path) with its pass phrase.
     static int SetTls(bool enable, const std::string &info);
+    static int SetTlsConfig(const net::TlsSettings &s);
+    static int SetTlsKey(const std::string &pk, const std::string &pass, net::TlsDecryptFn decrypt);
     static const TlsOptions &Tls();
+    // The shared TLS context (built on first use), nullptr with rc == OK when TLS is off.
+    static std::shared_ptr<net::TlsContext> TlsContextFor(int &rc);
     static std::shared_ptr<StoreServer> ServerOf(const std::string &url);
 };
 

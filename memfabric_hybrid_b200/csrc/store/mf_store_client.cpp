@@ -38,6 +38,12 @@ int TcpStoreClient::Startup(uint32_t timeoutMs, uint32_t maxRetry)
     if (running_.exchange(true)) return OK;
     net::EndpointOptions opt;
     opt.workers = 1;
+    int tlsRc = OK;
+    opt.tls = StoreFactory::TlsContextFor(tlsRc);
+    if (tlsRc != OK) {
+        running_ = false;
+        return tlsRc;
+    }
     ep_ = std::make_unique<net::Endpoint>(opt);
     std::weak_ptr<TcpStoreClient> weak = weak_from_this();
     ep_->OnMessage([this](const net::LinkPtr &, const net::MsgHeader &h, std::string &b) { OnMessage(h, b); });

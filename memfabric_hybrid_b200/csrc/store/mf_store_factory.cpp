@@ -47,19 +47,67 @@ struct Entry {
 std::mutex g_mu;
 std::map<std::string, Entry> g_stores;
 TlsOptions g_tls;
+std::mutex g_tlsMu;  // g_tls and the context below (taken alone, never while g_mu is wanted)
+std::shared_ptr<net::TlsContext> g_tlsCtx;
+std::string g_tlsKey, g_tlsKeyPass;
+net::TlsDecryptFn g_tlsDecrypt = nullptr;
 }  // namespace
 
 int StoreFactory::SetTls(bool enable, const std::string &info)
 {
-    std::lock_guard<std::mutex> g(g_mu);
-    g_tls.enable = enable;
+    std::lock_guard<std::mutex> g(g_tlsMu);
+    g_tlsCtx.reset();
+    g_tls.enable = false;
     g_tls.info = info;
-    if (enable) {
-        // The TLS handshake would need OpenSSL, which is not linked; a caller that insists on TLS gets
-        // a clear refusal at store creation instead of a silent plaintext link.
-        MF_WARN("config-store TLS requested: not available in this build, stores will refuse to start");
-    }
+    if (!enable) return OK;
+    std::string err;
+    if (!net::TlsSettings::Parse(info, g_tls.settings, err)) return MF_FAIL(ERR_INVALID_PARAM, "%s", err.c_str());
+    if (!net::TlsAvailable(g_tls.settings.packagePath, err)) return MF_FAIL(ERR, "%s", err.c_str());
+    g_tls.enable = true;
     return OK;
+}
+
+int StoreFactory::SetTlsConfig(const net::TlsSettings &s)
+{
+    std::lock_guard<std::mutex> g(g_tlsMu);
+    g_tlsCtx.reset();
+    g_tls.enable = false;
+    if (!s.enable) return OK;
+    std::string err;
+    if (s.certPath.empty() || s.caPath.empty()) return MF_FAIL(ERR_INVALID_PARAM, "TLS config needs caPath and certPath");
+    if (!net::TlsAvailable(s.packagePath, err)) return MF_FAIL(ERR, "%s", err.c_str());
+    g_tls.settings = s;
+    g_tls.enable = true;
+    return OK;
+}
+
+int StoreFactory::SetTlsKey(const std::string &pk, const std::string &pass, net::TlsDecryptFn decrypt)
+{
+    std::lock_guard<std::mutex> g(g_tlsMu);
+    g_tlsCtx.reset();
+    g_tlsKey = pk;
+    g_tlsKeyPass = pass;
+    g_tlsDecrypt = decrypt;
+    return OK;
+}
+
+std::shared_ptr<net::TlsContext> StoreFactory::TlsContextFor(int &rc)
+{
+    std::lock_guard<std::mutex> g(g_tlsMu);
+    rc = OK;
+    if (!g_tls.enable) return nullptr;
+    if (g_tlsCtx) return g_tlsCtx;
+    net::TlsSettings s = g_tls.settings;
+    if (!g_tlsKey.empty()) {  // the key given through the key call wins over a path in the info string
+        if (g_tlsKey.find("-----BEGIN") != std::string::npos) s.keyPem = g_tlsKey;
+        else s.keyPath = g_tlsKey;
+        s.keyPass = g_tlsKeyPass;
+        s.decrypt = g_tlsDecrypt;
+    }
+    std::string err;
+    g_tlsCtx = net::TlsContext::Create(s, err);
+    if (!g_tlsCtx) rc = MF_FAIL(ERR, "config-store TLS: %s", err.c_str());
+    return g_tlsCtx;
 }
 
 const TlsOptions &StoreFactory::Tls() { return g_tls; }
@@ -76,7 +124,6 @@ int StoreFactory::CreateServerOnly(const std::string &url, uint32_t worldSize, u
     StoreUrl u;
     if (!StoreUrl::Parse(url, u) || u.scheme != StoreUrl::TCP) return MF_FAIL(ERR_INVALID_PARAM, "bad store url %s", url.c_str());
     std::lock_guard<std::mutex> g(g_mu);
-    if (g_tls.enable) return MF_FAIL(ERR, "TLS is enabled but not available in this build");
     Entry &e = g_stores[url];
     if (e.server) return OK;
     auto s = std::make_shared<StoreServer>(u.ip, u.port, worldSize, flags);
@@ -121,10 +168,6 @@ StorePtr StoreFactory::CreateStore(const std::string &url, bool isServer, uint32
         return fail(ERR_INVALID_PARAM);
     }
     std::unique_lock<std::mutex> g(g_mu);
-    if (g_tls.enable) {
-        MF_FAIL(ERR, "TLS is enabled but not available in this build");
-        return fail(ERR);
-    }
     Entry &e = g_stores[url];
     if (e.client) {
         e.refs++;

@@ -57,6 +57,12 @@ int StoreServer::Startup()
     if (running_.exchange(true)) return OK;
     net::EndpointOptions opt;
     opt.workers = 2;
+    int tlsRc = OK;
+    opt.tls = StoreFactory::TlsContextFor(tlsRc);
+    if (tlsRc != OK) {
+        running_ = false;
+        return tlsRc;
+    }
     ep_ = std::make_unique<net::Endpoint>(opt);
     ep_->OnNewLink([this](const net::ConnReq &r, const net::LinkPtr &l) { return OnNewLink(r, l); });
     ep_->OnMessage([this](const net::LinkPtr &l, const net::MsgHeader &h, std::string &b) { OnMessage(l, h, b); });
