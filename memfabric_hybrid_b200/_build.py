@@ -123,6 +123,26 @@ def build_cuda(jobs: int | None = None) -> Path | None:
     return out
 
 
+def build_bench() -> list[Path]:
+    """The native benchmark tools (benchmark/bm, benchmark/transfer) into memfabric_hybrid_b200/bin/. They use the public C
+    API of libmf_smem.so plus the CUDA runtime for their private buffers."""
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    bench = PKG.parent / "benchmark"
+    if not Path(nvcc).exists() or not bench.exists():
+        return []
+    bindir = PKG / "bin"
+    bindir.mkdir(exist_ok=True)
+    outs = []
+    for src in (bench / "bm" / "bm_perf_benchmark.cpp", bench / "transfer" / "transfer_perf.cpp"):
+        out = bindir / src.stem
+        tmp = out.with_suffix(f".{os.getpid()}.tmp")
+        subprocess.run([nvcc, "-O2", "-std=c++17", "-x", "cu", "-gencode", "arch=compute_100a,code=sm_100a", f"-I{CSRC / 'include'}", "-o", str(tmp), str(src), "-cudart", "static",
+                        f"-L{LIB}", "-lmf_smem", "-Xlinker", "-rpath=$ORIGIN/../lib", "-lpthread", "-ldl", "-lrt"], check=True)
+        tmp.replace(out)
+        outs.append(out)
+    return outs
+
+
 def build_c10d() -> Path | None:
     """The c10d extension module. Needs PyTorch's headers and a CUDA include tree; returns None without them."""
     try:
@@ -160,6 +180,7 @@ def build_all() -> None:
     build_host()
     build_cuda()
     build_c10d()
+    build_bench()
 
 
 if __name__ == "__main__":
@@ -175,3 +196,5 @@ if __name__ == "__main__":
         print(build_cuda())
     if not args or "--c10d" in args:
         print(build_c10d())
+    if not args or "--bench" in args:
+        print(build_bench())
