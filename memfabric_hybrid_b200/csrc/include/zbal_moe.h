@@ -89,6 +89,11 @@ int32_t zbal_fused_deep_moe(zbal_moe_t moe, const void *x, int64_t tokens, const
                             const void *gmm1Weight, const float *gmm1Scale, const void *gmm2Weight, const float *gmm2Scale, uint32_t inter,
                             void *workspace, void *xOut, zbal_stream_t stream);
 
+/* Smooth quantisation (the reference's SMOOTH_QUANT execution flag): every token row is multiplied by scales[hidden]
+ * (device fp32, caller-owned, must stay valid) before the dispatch kernels quantise it; the expert weights carry the
+ * inverse factors. NULL switches it off. Applies to normal, low-latency and fused dispatch of this object. */
+int32_t zbal_moe_set_smooth_scales(zbal_moe_t moe, const float *scales);
+
 /* Host-side plan of the reference's load balancing (which helper rank pushes which range of which rank's tokens);
  * counts: [ranks, experts] send counts, matrix: [ranks, ranks * 2] int32 out. Not used by the kernels here. */
 int32_t zbal_moe_balance_matrix(const int32_t *counts, uint32_t ranks, uint32_t experts, uint32_t topk, float factorHigh, float factorLow,

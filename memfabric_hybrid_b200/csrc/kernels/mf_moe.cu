@@ -166,6 +166,7 @@ struct DispatchArgs {
     uint32_t seq;
     int *status;
     int raw_bf16;               // 1: rows travel as bf16 (receive rows are 2 H bytes, no scales)
+    const float *smooth;        // optional [H]: every row is multiplied by it before quantisation (smooth quant); fp8 rows only
 };
 
 // Loads this thread's 32 bytes of the first token row a CTA will handle (callers may do it early, e.g. while
@@ -200,6 +201,18 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs &a, uint4 nxt_l
     __shared__ float dst_w[kTokBatch][16];
     __shared__ __align__(16) float s_scale[2][64];  // the row's 1 x 128 scales, leaving as one burst per destination
     const int stride = (int)gridDim.x;
+    // smooth-quant factors of this thread's 16 columns: the same for every token
+    float smooth[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) smooth[i] = 1.f;
+    const bool smoothed = a.smooth != nullptr && !a.raw_bf16;
+    if (smoothed && vec < vecs) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const float4 s4 = __ldg(reinterpret_cast<const float4 *>(a.smooth + vec * 16) + i);
+            smooth[4 * i] = s4.x, smooth[4 * i + 1] = s4.y, smooth[4 * i + 2] = s4.z, smooth[4 * i + 3] = s4.w;
+        }
+    }
     for (int base = blockIdx.x; base < a.sh.T; base += stride * kTokBatch) {
         __syncthreads();  // the previous batch's table is no longer read
         for (int e = threadIdx.x; e < kTokBatch * K; e += blockDim.x) {
@@ -251,6 +264,10 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs &a, uint4 nxt_l
                         f[8 + 2 * i] = p.x;
                         f[8 + 2 * i + 1] = p.y;
                     }
+                }
+                if (smoothed) {
+#pragma unroll
+                    for (int i = 0; i < 16; i++) f[i] *= smooth[i];
                 }
                 float amax = 0.f;
 #pragma unroll

@@ -39,6 +39,7 @@ struct DispatchArgs {
     uint32_t epoch, seq;
     int *status;
     int raw_bf16;
+    const float *smooth;
 };
 
 struct MoeLaunchers {
@@ -107,6 +108,7 @@ struct MoeCtx {
     uint32_t epoch = 0, dispatches = 0;
     int grid = 148, llGrid = 128;
     bool rawBf16 = false;
+    const float *smooth = nullptr;    // smooth-quant factors applied by the dispatch kernels (device, [hidden]); caller-owned
     std::mutex mu;
 };
 
@@ -291,6 +293,7 @@ int32_t zbal_dispatch_normal(zbal_moe_t moe, const void *srcTokens, int64_t toke
     a.seq = ++c->dispatches;
     a.status = c->status;
     a.raw_bf16 = c->rawBf16 ? 1 : 0;
+    a.smooth = c->smooth;
     int rc = Launched(Moe()->dispatch(&a, c->grid, stream), "dispatch");
     if (rc != Z_OK) return rc;
     return Launched(Moe()->waitAll(&c->comm->team, &c->hp, 0, c->epoch, c->status, stream), "dispatch wait");
@@ -332,6 +335,7 @@ int32_t zbal_dispatch_low_latency(zbal_moe_t moe, const void *x, int64_t tokens,
     a.epoch = 0, a.seq = 0;  // the kernel numbers its calls in device memory
     a.status = c->status;
     a.raw_bf16 = c->rawBf16 ? 1 : 0;
+    a.smooth = c->smooth;
     return Launched(Moe()->llDispatch(&a, tokensPerExpert, recvTokensPerExpert, rowOffsets, srcOffsets, c->epochLL, c->llGrid, stream), "low-latency dispatch");
 }
 
@@ -441,6 +445,16 @@ int32_t zbal_fused_deep_moe(zbal_moe_t moe, const void *x, int64_t tokens, const
 // own and the overflow of overloaded ranks goes, in rank order, to ranks with spare capacity.
 // The dispatch kernels of this library do not use the plan (on NVSwitch a token routed through a helper crosses
 // NVLink twice); the function exists for schedulers that want the same numbers the reference would produce.
+extern "C" int32_t zbal_moe_set_smooth_scales(zbal_moe_t moe, const float *scales)
+{
+    MoeCtx *c = Find(moe);
+    if (c == nullptr) return Z_INVALID_PARAM;
+    if (scales != nullptr && c->rawBf16) return MF_FAIL(Z_INVALID_PARAM, "smooth-quant factors apply to fp8 rows; this object sends raw bf16");
+    std::lock_guard<std::mutex> g(c->mu);
+    c->smooth = scales;
+    return Z_OK;
+}
+
 extern "C" int32_t zbal_moe_balance_matrix(const int32_t *counts, uint32_t ranks, uint32_t experts, uint32_t topk, float factorHigh, float factorLow,
                                            uint32_t minTokens, int32_t *matrix)
 {

@@ -39,7 +39,8 @@ class MoeHeapC(C.Structure):
 class DispatchArgsC(C.Structure):
     _fields_ = [("team", TeamC), ("hp", MoeHeapC), ("sh", MoeShapeC), ("x", C.c_void_p), ("topk_idx", C.c_void_p),
                 ("topk_w", C.c_void_p), ("send_idx", C.c_void_p), ("put_off", C.c_void_p), ("done_count", C.c_void_p),
-                ("epoch", C.c_uint32), ("seq", C.c_uint32), ("status", C.c_void_p), ("raw_bf16", C.c_int)]
+                ("epoch", C.c_uint32), ("seq", C.c_uint32), ("status", C.c_void_p), ("raw_bf16", C.c_int),
+                ("smooth", C.c_void_p)]
 
 
 _lib = None
@@ -125,6 +126,38 @@ def interleave_gate_up_fp8(w1q: torch.Tensor, tile: int | None = None) -> torch.
     gate = w1q[:, :i].reshape(G, i // tile, tile, K)
     up = w1q[:, i:].reshape(G, i // tile, tile, K)
     return torch.stack([gate, up], dim=2).reshape(G, two_i, K).contiguous()
+
+
+def dense_ffn_fp8(x: torch.Tensor, w1q: torch.Tensor, w1s: torch.Tensor, w2q: torch.Tensor, w2s: torch.Tensor,
+                  smooth: torch.Tensor | None = None, sms: int | None = None) -> torch.Tensor:
+    """One dense SwiGLU expert on every row of x (the shared expert of a DeepSeek-style layer):
+    y = (silu(x W1g^T) * (x W1u^T)) W2^T with block-scaled fp8 tensor-core GEMMs. x [T, H] bf16;
+    w1q [2I, H] e4m3 with gate / up rows interleaved per 128 (``interleave_gate_up_fp8(w[None], 128)[0]``), w1s [2I/128, H/128]
+    in original row order; w2q [H, I], w2s [H/128, I/128]. Three launches: row quantisation, gate/up GEMM whose epilogue
+    applies SwiGLU and re-quantises, down GEMM. ``smooth`` ([H] fp32) multiplies the rows before quantisation."""
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.is_contiguous()
+    T, H = x.shape
+    two_i = w1q.shape[0]
+    I = two_i // 2
+    assert w1q.shape == (two_i, H) and w2q.shape == (H, I) and two_i % 256 == 0 and H % 256 == 0 and I % 128 == 0
+    cu = _cu()
+    dev = x.device
+    stw = status_word(dev).data_ptr()
+    sms = sms or sm_count(dev)
+    if smooth is not None:
+        x = (x.float() * smooth.view(1, H)).to(torch.bfloat16)
+    rows = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    xq = torch.empty((T, H), dtype=torch.uint8, device=dev)
+    xs = torch.empty((T, H // 128), dtype=torch.float32, device=dev)
+    _ok(cu.mf_quant_rows_fp8(x.data_ptr(), H, rows[1:].data_ptr(), H, xq.data_ptr(), xs.data_ptr(), sms * 4, _s()), "quant_rows_fp8")
+    hq = torch.empty((T, I), dtype=torch.uint8, device=dev)
+    hs = torch.empty((T, I // 128), dtype=torch.float32, device=dev)
+    _ok(cu.mf_grouped_gemm_fp8_mx(xq.data_ptr(), xs.data_ptr(), T, w1q.data_ptr(), w1s.data_ptr(), rows.data_ptr(), 1, two_i, H,
+                                  hq.data_ptr(), I, hs.data_ptr(), 3, None, None, 0, 1, stw, sms, _s()), "grouped_gemm_fp8_mx (shared gate/up)")
+    y = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+    _ok(cu.mf_grouped_gemm_fp8_mx(hq.data_ptr(), hs.data_ptr(), T, w2q.data_ptr(), w2s.data_ptr(), rows.data_ptr(), 1, H, I,
+                                  y.data_ptr(), H, None, 0, None, None, 0, 1, stw, sms, _s()), "grouped_gemm_fp8_mx (shared down)")
+    return y
 
 
 @dataclass
@@ -226,8 +259,12 @@ class MoEComm:
                                 inr.data_ptr(), _s()), "moe_layout")
         return idx, tpe, tpr, sidx, inr
 
-    def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor) -> DispatchState:
+    def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, smooth: torch.Tensor | None = None) -> DispatchState:
+        """smooth: optional [H] fp32 factors every row is multiplied by before it is quantised (smooth quant; the matching
+        weights carry the inverse factors). fp8 rows only."""
         assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == self.H and x.shape[0] <= self.T
+        if smooth is not None:
+            assert not self.raw_bf16 and smooth.dtype == torch.float32 and smooth.is_contiguous() and smooth.numel() == self.H
         T = x.shape[0]
         idx, tpe, tpr, sidx, inr = self.get_dispatch_layout(topk_idx)
         self._epoch += 1
@@ -241,8 +278,9 @@ class MoEComm:
         w = topk_w.to(torch.float32).contiguous()
         self._dispatches += 1
         a = DispatchArgsC(team, self.hp, self._shape(T), x.data_ptr(), idx.data_ptr(), w.data_ptr(), sidx.data_ptr(), put_off.data_ptr(),
-                          self._done.data_ptr(), self._epoch, self._dispatches, status_word(self.dev).data_ptr(), 1 if self.raw_bf16 else 0)
-        self._keep = (w, idx)
+                          self._done.data_ptr(), self._epoch, self._dispatches, status_word(self.dev).data_ptr(), 1 if self.raw_bf16 else 0,
+                          smooth.data_ptr() if smooth is not None else None)
+        self._keep = (w, idx, smooth)
         # one CTA per SM on every call: the completion counter of the kernel counts CTAs
         _ok(_cu().mf_moe_dispatch(C.byref(a), self._grid, _s()), "moe_dispatch")
         _ok(_cu().mf_moe_wait_all(C.byref(team), C.byref(self.hp), 0, self._epoch, status_word(self.dev).data_ptr(), _s()), "moe_wait")
@@ -324,7 +362,7 @@ class MoEComm:
             hp.flags += 2 * 16 * 4  # flag rows 2 and 3 belong to the low-latency pair
             self._ll_hp = hp
 
-    def ll_dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor) -> DispatchState:
+    def ll_dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_w: torch.Tensor, smooth: torch.Tensor | None = None) -> DispatchState:
         """One cooperative launch. The outputs live in buffers owned by this object (overwritten by the next call)
         and nothing depends on host-side counters, so the call may be captured in a CUDA graph and replayed."""
         assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == self.H and x.shape[0] <= self.T
@@ -335,8 +373,8 @@ class MoEComm:
         b = self._ll_bufs
         a = DispatchArgsC(self.heap.team(), self._ll_hp, self._shape(T), x.data_ptr(), idx.data_ptr(), w.data_ptr(), b["sidx"].data_ptr(),
                           b["put_off"].data_ptr(), self._ll_done.data_ptr(), 0, 0, status_word(self.dev).data_ptr(),
-                          1 if self.raw_bf16 else 0)
-        self._keep = (w, idx)
+                          1 if self.raw_bf16 else 0, smooth.data_ptr() if smooth is not None else None)
+        self._keep = (w, idx, smooth)
         _ok(_cu().mf_moe_ll_dispatch(C.byref(a), b["tpe"].data_ptr(), b["rpe"].data_ptr(), b["row_off"].data_ptr(), b["src_off"].data_ptr(),
                                      self._ll_epoch.data_ptr(), self._ll_grid, _s()), "moe_ll_dispatch")
         return DispatchState(T, idx, b["sidx"], b["tpe"], None, None, b["rpe"], b["row_off"], b["put_off"], b["src_off"], -1)

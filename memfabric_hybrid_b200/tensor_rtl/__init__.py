@@ -5,3 +5,4 @@ from .executor import (All2AllVExcutor, All2AllVExecutor, BatchP2PExecutor, Exec
 from .pack import pack_tensors, unpack_tensors  # noqa: F401
 from .plan import MFCommTask, P2PCommTask, PTensor, PTensorSet, overlaps, shard_bounds  # noqa: F401
 from .eplb import ExpertMigrator, pair_slots  # noqa: F401
+from .rl_reshard import InferLayout, ParamSpec, TrainLayout, TrainToInferResharder, decoder_specs  # noqa: F401

@@ -32,6 +32,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops.heap import TeamC, _HeapBase, tensor_at
+from ..ops import moe as moe_ops
 from ..ops.moe import DispatchState, MoEComm
 from . import _capi as K
 from . import module as M
@@ -108,6 +109,7 @@ class Buffer:
         self.hidden, self.num_experts, self.num_topk, self.num_max_tokens = hidden, num_experts, num_topk, num_max_tokens
         self.use_fp8 = use_fp8
         self._moe = MoEComm(self._heap, num_max_tokens, hidden, num_experts, num_topk, max_recv=num_max_recv_tokens, raw_bf16=not use_fp8)
+        self._side = None   # second stream: the shared expert of fused_deep_moe runs there while the routed rows travel
         self._state: Optional[DispatchState] = None
 
     # ------------------------------------------------------------------ configuration helpers (DeepEP names)
@@ -263,21 +265,55 @@ class Buffer:
     def fused_deep_moe(self, x: torch.Tensor, topk_idx: torch.Tensor, gmm1_permuted_weight: torch.Tensor,
                        gmm1_permuted_weight_scale: torch.Tensor, gmm2_weight: torch.Tensor, gmm2_weight_scale: torch.Tensor,
                        topk_weights: torch.Tensor, num_experts: int, shared_expert_num: int = 0, shared_expert_rank_num: int = 0,
-                       quant_mode: int = 0, num_max_dispatch_tokens_per_rank: int = 0, x_active_mask: Optional[torch.Tensor] = None,
+                       quant_mode: int = 0, num_max_dispatch_tokens_per_rank: int = 0, is_tensor_list: bool = False,
+                       expert_smooth_scales: Optional[torch.Tensor] = None, share_gmm1_weight: Optional[torch.Tensor] = None,
+                       share_gmm1_scale: Optional[torch.Tensor] = None, share_gmm2_weight: Optional[torch.Tensor] = None,
+                       share_gmm2_scale: Optional[torch.Tensor] = None, share_smooth_scales: Optional[torch.Tensor] = None,
+                       x_active_mask: Optional[torch.Tensor] = None, share_gmm1_h_len: int = 0, fuse_mode: int = 0,
                        **unused) -> Tuple[torch.Tensor, torch.Tensor]:
         """dispatch (fp8 quant fused) -> grouped GEMM1 + SwiGLU -> requant -> grouped GEMM2 with the weighted
         push home fused into its epilogue -> slot reduce. gmm1 weights: [local experts, 2I, H] fp8, gate/up
         tile-interleaved (``ops.moe.interleave_gate_up_fp8``) with [.., 2I/128, H/128] scales; gmm2: [.., H, I].
         ``x_active_mask`` ([T] bool): rows that are False take no part (padding of a decode batch): they are sent to no
         expert and their output rows are zero.
+        ``expert_smooth_scales`` ([H] fp32, the reference's SMOOTH_QUANT flag): every row is multiplied by it inside the
+        dispatch kernel, before quantisation; gmm1's weights carry the inverse factors.
+        ``share_gmm1_weight`` .. ``share_gmm2_scale`` (the SHARED_EXPERT flag): one dense expert applied to every active row
+        of x on this rank, in the expert weights' format (share_gmm1_weight [2 Is, H] tile-interleaved per 128 with
+        [2 Is/128, H/128] scales, share_gmm2_weight [H, Is] with [H/128, Is/128]); it runs on a second stream while the
+        routed rows travel, and its result is added to the combined rows. ``share_smooth_scales`` is its smooth-quant vector.
+        ``is_tensor_list``: the routed weights arrive as lists of per-expert tensors. shared_expert_num,
+        shared_expert_rank_num, share_gmm1_h_len (read from the weight's shape) and fuse_mode are accepted and ignored, as
+        the reference's wrapper does (app/zbal/src/python/zbal/zbal_buffer.py:611-700).
         -> (output [T, H] bf16, tokens received per local expert)"""
         assert self.use_fp8, "the fused path runs on fp8 rows"
-        if shared_expert_rank_num:
-            raise NotImplementedError("fused_deep_moe: ranks dedicated to shared experts are not supported; run the shared expert as a "
-                                      "dense MLP beside this call (its output adds to the returned rows)")
+        if is_tensor_list:
+            gmm1_permuted_weight, gmm1_permuted_weight_scale, gmm2_weight, gmm2_weight_scale = (
+                torch.stack(list(t)) if isinstance(t, (list, tuple)) else t
+                for t in (gmm1_permuted_weight, gmm1_permuted_weight_scale, gmm2_weight, gmm2_weight_scale))
         if x_active_mask is not None:
             topk_idx = topk_idx.masked_fill(~x_active_mask.to(torch.bool).view(-1, 1), -1)   # the kernels skip negative ids
         moe = self._moe
-        st = moe.dispatch(x, topk_idx, topk_weights)
+        smooth = None
+        if expert_smooth_scales is not None:
+            smooth = expert_smooth_scales.to(torch.float32).contiguous().view(-1)
+        shared = None
+        if share_gmm1_weight is not None and share_gmm1_weight.numel() > 0:
+            assert share_gmm1_scale is not None and share_gmm2_weight is not None and share_gmm2_scale is not None, \
+                "the shared expert needs both weights and both scale tensors"
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream()
+            self._side.wait_stream(main)
+            with torch.cuda.stream(self._side):
+                ssm = None if share_smooth_scales is None else share_smooth_scales.to(torch.float32).contiguous().view(-1)
+                shared = moe_ops.dense_ffn_fp8(x, share_gmm1_weight, share_gmm1_scale, share_gmm2_weight, share_gmm2_scale, smooth=ssm)
+                if x_active_mask is not None:
+                    shared.masked_fill_(~x_active_mask.to(torch.bool).view(-1, 1), 0)
+        st = moe.dispatch(x, topk_idx, topk_weights, smooth=smooth)
         moe.expert_ffn(st, gmm1_permuted_weight, gmm1_permuted_weight_scale, gmm2_weight, gmm2_weight_scale)
-        return moe.combine(st), st.recv_per_expert
+        out = moe.combine(st)
+        if shared is not None:
+            torch.cuda.current_stream().wait_stream(self._side)
+            out.add_(shared)
+        return out, st.recv_per_expert

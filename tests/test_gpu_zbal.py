@@ -285,6 +285,35 @@ def _buffer_scenario(rank, world, port, sync):
             part, _ = buf.fused_deep_moe(x, idx, w1q, w1s, w2q, w2s, w, E, x_active_mask=mask)
             assert float(part[T // 2:].abs().max()) == 0.0 and float(full[T // 2:].abs().max()) > 0.0
             torch.testing.assert_close(part[:T // 2].float(), full[:T // 2].float(), rtol=1e-2, atol=1e-3)
+            # shared expert: a dense SwiGLU FFN on every row, added to the routed result; against fp32 math on the
+            # dequantised weights (activations are quantised per 1 x 128 on the way, hence the tolerance)
+            Is = 256
+            sw1 = (torch.randn(2 * Is, H, device="cuda", generator=gw) * 0.03).to(torch.bfloat16)
+            sw2 = (torch.randn(H, Is, device="cuda", generator=gw) * 0.03).to(torch.bfloat16)
+            s1q, s1s = M.quantize_weight_fp8(sw1)
+            s2q, s2s = M.quantize_weight_fp8(sw2)
+
+            def deq(q, sc):
+                Nn, Kk = q.shape
+                return (q.float().reshape(Nn // 128, 128, Kk // 128, 128) * sc[:, None, :, None]).reshape(Nn, Kk)
+
+            pre = x.float() @ deq(s1q, s1s).t()
+            ref_shared = (torch.nn.functional.silu(pre[:, :Is]) * pre[:, Is:]) @ deq(s2q, s2s).t()
+            both, _ = buf.fused_deep_moe(x, idx, w1q, w1s, w2q, w2s, w, E, share_gmm1_weight=M.interleave_gate_up_fp8(s1q[None], 128)[0],
+                                         share_gmm1_scale=s1s, share_gmm2_weight=s2q, share_gmm2_scale=s2s, share_gmm1_h_len=2 * Is)
+            got_shared = both.float() - full.float()
+            err = (got_shared - ref_shared).abs().max().item()
+            assert err <= 0.06 * ref_shared.abs().max().item() + 2e-2, (err, ref_shared.abs().max().item())
+            # smooth quant: rows times s before quantisation, weights divided by s: the product is unchanged (up to rounding)
+            sm = torch.exp2(torch.randint(-1, 2, (H,), device="cuda", generator=gw).float())     # powers of two: exact in bf16 / fp8
+            w1_s = (w1.float() / sm.view(1, 1, H)).to(torch.bfloat16)
+            w1q_s, w1s_s = M.quantize_weight_fp8(w1_s)
+            smoothed, _ = buf.fused_deep_moe(x, idx, M.interleave_gate_up_fp8(w1q_s), w1s_s, w2q, w2s, w, E, expert_smooth_scales=sm)
+            err = (smoothed.float() - full.float()).abs().max().item()
+            assert err <= 0.06 * full.float().abs().max().item() + 2e-2, (err, full.float().abs().max().item())
+            # weights as lists of per-expert tensors
+            listed, _ = buf.fused_deep_moe(x, idx, list(w1q), list(w1s), list(w2q), list(w2s), w, E, is_tensor_list=True)
+            torch.testing.assert_close(listed.float(), full.float(), rtol=0, atol=0)
         torch.cuda.synchronize()
         gemm.check_status()
         buf.destroy()

@@ -104,3 +104,31 @@ def test_eplb_slot_pairing():
         pair_slots(old, [9, 1, 2, 3, 0, 1], 2)
     with pytest.raises(ValueError):
         pair_slots(old, old[:-1], 2)
+
+
+def test_rl_reshard_splits_fused_training_shards():
+    """The block splitter of the train -> inference resharder: a Megatron linear_qkv shard (q, k, v interleaved per query
+    group) and a linear_fc1 shard (gate, up) come apart into the separately sharded blocks, on every tensor-parallel rank."""
+    from memfabric_hybrid_b200.tensor_rtl.rl_reshard import (InferLayout, TrainLayout, TrainToInferResharder, decoder_specs,
+                                                              train_shard_of)
+    specs, meta = decoder_specs(num_layers=2, hidden=32, ffn=48, heads=8, kv_heads=4, head_dim=4, vocab=64)
+    qkv = next(s for s in specs if s.train_name.endswith("layers.0.self_attention.linear_qkv.weight"))
+    fc1 = next(s for s in specs if s.train_name.endswith("layers.1.mlp.linear_fc1.weight"))
+    g = torch.Generator().manual_seed(1)
+    for spec in (qkv, fc1):
+        full = [torch.randn(b.size, 32, generator=g) for b in spec.the_blocks()]
+        for tp in (1, 2, 4):
+            for t in range(tp):
+                job = TrainToInferResharder(specs, TrainLayout(tp=tp, pp=1), InferLayout(tp=1, ranks=[0]), rank=t, executor=None, meta=meta)
+                local = train_shard_of(spec, full, tp, t)
+                assert local.shape[0] == sum(b.size for b in spec.the_blocks()) // tp
+                parts = job._local_blocks(spec, local, list(range(tp)))
+                for blk, whole in zip(parts, full):
+                    n = whole.shape[0] // tp
+                    assert torch.equal(blk, whole[t * n:(t + 1) * n])
+    # stages and expert placement
+    tl = TrainLayout(tp=4, pp=2, ep=2)
+    assert tl.stage_ranks(1) == [4, 5, 6, 7] and tl.stage_of_layer(3, 8) == 0 and tl.stage_of_layer(4, 8) == 1
+    assert tl.expert_ranks(1, 5, 8) == [6, 7] and InferLayout(tp=2, ranks=[3, 9], ep=2).expert_ranks(5, 8) == [9]
+    with pytest.raises(ValueError):
+        TrainLayout(tp=4, pp=1, ep=3)
