@@ -20,6 +20,13 @@ const char *zbal_version(void);
 int32_t zbal_set_logger(void (*func)(int, const char *));
 /* 0 debug, 1 info, 2 warn, 3 error */
 int32_t zbal_set_logger_level(int level);
+/* Collective: adds one more segment (deviceMemorySize bytes per rank) to the symmetric heap. Every rank must call it at
+ * the same point of its allocation sequence. With ZBAL_ALLOC_CONF=expandable_segments:True the allocator calls it by
+ * itself when a request does not fit; since symmetric allocation already requires the same sequence of requests on
+ * every rank, all ranks reach that point together. */
+int32_t zbal_heap_expand(uint64_t *segmentBase, uint64_t *segmentBytes);
+/* 1 when [ptr, ptr + bytes) lies inside this rank's part of the symmetric memory (any segment), else 0. */
+int32_t zbal_is_symmetric(const void *ptr, uint64_t bytes);
 const char *zbal_get_last_error_msg(void);
 const char *zbal_get_and_clear_last_error_msg(void);
 

@@ -38,7 +38,16 @@ typedef struct {
     uint64_t failedMallocs;
     uint64_t poolCount;        /* private pools that exist (capturing or kept alive by a CUDA graph) */
     uint64_t poolCachedBytes;  /* free blocks parked in private pools (not counted in cachedBytes) */
+    uint64_t segments;         /* address ranges the heap spans (1 until it was expanded) */
+    uint64_t segmentsAdded;    /* of those, added by the grow hook on exhaustion */
 } zbal_sma_stats_t;
+
+/* Expandable segments. zbal_sma_add_segment hands the allocator another address range; with
+ * ZBAL_ALLOC_CONF=expandable_segments:True a request that the heap cannot serve calls the grow hook (set by
+ * zbal_bootstrap to the collective zbal_heap_expand), which returns 0 after it added a segment, and is tried again. */
+typedef int (*zbal_sma_grow_hook_t)(uint64_t need_bytes, void *ctx);
+int32_t zbal_sma_add_segment(uint64_t base, uint64_t size);
+void zbal_sma_set_grow_hook(zbal_sma_grow_hook_t hook, void *ctx);
 
 /* Private pools for CUDA-graph capture. A graph replays with the addresses it saw while it was captured, so
  * what it allocated must never be handed to anyone else while the graph exists:

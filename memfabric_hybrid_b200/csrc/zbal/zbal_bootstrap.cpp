@@ -101,6 +101,8 @@ int32_t zbal_bootstrap_get_output(zbal_bootstrap_output_t *output)
     return Z_OK;
 }
 
+static int GrowHook(uint64_t need, void *ctx);
+
 int32_t zbal_bootstrap(zbal_bootstrap_options_t *o, zbal_bootstrap_output_t *output)
 {
     if (o == nullptr) return MF_FAIL(Z_INVALID_PARAM, "options is NULL");
@@ -174,6 +176,7 @@ int32_t zbal_bootstrap(zbal_bootstrap_options_t *o, zbal_bootstrap_output_t *out
     ao.size = out.heapSize;
     ao.deviceId = o->deviceId;
     const bool ownSma = zbal_sma_init(&ao, 0) == Z_OK;
+    if (ownSma) zbal_sma_set_grow_hook(GrowHook, nullptr);  // used only with ZBAL_ALLOC_CONF=expandable_segments:True
     {
         std::lock_guard<std::mutex> g(st.mu);
         st.opts = *o;
@@ -203,10 +206,68 @@ int32_t zbal_bootstrap(zbal_bootstrap_options_t *o, zbal_bootstrap_output_t *out
     return Z_OK;
 }
 
+// Collective: every rank adds one more symmetric segment to the allocator's heap. The segment is another symmetric object
+// with the slot size of the first one, so that rank r's copy of an address p of this rank is p + (r - me) * symmetricSize
+// in every segment, and the kernels' one-stride addressing holds across them.
+int32_t zbal_heap_expand(uint64_t *segmentBase, uint64_t *segmentBytes)
+{
+    State &st = S();
+    zbal_bootstrap_options_t o;
+    zbal_bootstrap_output_t out;
+    smem_shm_t first;
+    uint32_t id;
+    {
+        std::lock_guard<std::mutex> g(st.mu);
+        if (!st.up) return MF_FAIL(Z_NOT_INITIALIZED, "zbal_heap_expand before zbal_bootstrap");
+        if (!st.ownSma) return MF_FAIL(Z_NOT_SUPPORTED, "the heap belongs to an allocator that zbal_bootstrap did not create");
+        o = st.opts;
+        out = st.out;
+        first = st.shm;
+        id = 1 + (uint32_t)st.extraShm.size();
+    }
+    void *gva = nullptr;
+    smem_shm_t shm = smem_shm_create(id, o.worldSize, o.rankId, o.deviceMemorySize, SMEMS_DATA_OP_MTE, 0, &gva);
+    if (shm == nullptr) return MF_FAIL(Z_NO_MEMORY, "zbal_heap_expand: segment %u could not be created: %s", id, mf::LastError::Msg());
+    // one stride for all segments needs the same slot size and, on every rank, the same distance between the objects
+    const uint64_t base = reinterpret_cast<uint64_t>(gva);
+    int64_t delta = (int64_t)(base - out.baseGva);
+    std::vector<int64_t> all(o.worldSize, 0);
+    int rc = smem_shm_control_allgather(first, reinterpret_cast<const char *>(&delta), sizeof(delta), reinterpret_cast<char *>(all.data()),
+                                        (uint32_t)(sizeof(delta) * o.worldSize));
+    bool same = rc == 0 && smem_shm_get_symmetric_size(shm) == out.symmetricSize;
+    for (uint32_t r = 0; same && r < o.worldSize; r++) same = all[r] == delta;
+    if (!same) {
+        smem_shm_destroy(shm, 0);
+        return MF_FAIL(Z_ERROR, "zbal_heap_expand: segment %u does not line up with the first one on every rank", id);
+    }
+    const uint64_t local = base + (uint64_t)o.rankId * out.symmetricSize;
+    rc = zbal_sma_add_segment(local, o.deviceMemorySize);
+    if (rc != Z_OK) {
+        smem_shm_destroy(shm, 0);
+        return rc;
+    }
+    {
+        std::lock_guard<std::mutex> g(st.mu);
+        st.extraShm.push_back(shm);
+        st.extraLocal.push_back(local);
+    }
+    if (segmentBase != nullptr) *segmentBase = local;
+    if (segmentBytes != nullptr) *segmentBytes = o.deviceMemorySize;
+    MF_INFO("zbal heap: segment %u of %lu MiB added", id, (unsigned long)(o.deviceMemorySize >> 20));
+    return Z_OK;
+}
+
+static int GrowHook(uint64_t need, void *)
+{
+    if (need > S().opts.deviceMemorySize) return -1;  // one more segment would still not hold it
+    return zbal_heap_expand(nullptr, nullptr) == Z_OK ? 0 : -1;
+}
+
 int32_t zbal_unbootstrap(uint32_t flags)
 {
     State &st = S();
     smem_shm_t shm = nullptr;
+    std::vector<smem_shm_t> extra;
     bool ownSma = false;
     {
         std::lock_guard<std::mutex> g(st.mu);
@@ -214,16 +275,20 @@ int32_t zbal_unbootstrap(uint32_t flags)
         st.up = false;
         shm = st.shm;
         st.shm = nullptr;
+        extra.swap(st.extraShm);
+        st.extraLocal.clear();
         ownSma = st.ownSma;
         st.comms.clear();
         st.world.reset();
     }
+    zbal_sma_set_grow_hook(nullptr, nullptr);
     if (ownSma) zbal_sma_uninit(0);
     auto *be = mf::hybm::CurrentBackend();
     if (be != nullptr) be->StreamSync(nullptr);
     if (shm != nullptr) {
         // nobody unmaps its slice while a peer may still be writing flags into it
         smem_shm_control_barrier(shm);
+        for (smem_shm_t e : extra) smem_shm_destroy(e, flags);
         smem_shm_destroy(shm, flags);
     }
     smem_shm_uninit(flags);

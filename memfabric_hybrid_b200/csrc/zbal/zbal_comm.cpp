@@ -132,6 +132,19 @@ bool InSlice(const void *p, uint64_t bytes)
 {
     State &st = S();
     const uint64_t a = reinterpret_cast<uint64_t>(p);
+    if (p == nullptr) return false;
+    if (a >= st.out.localGva && a + bytes <= st.out.localGva + st.opts.deviceMemorySize) return true;
+    // expansion segments: rank r's slot of segment k starts at the segment's base + r * symmetricSize
+    std::lock_guard<std::mutex> g(st.mu);
+    for (uint64_t segLocal : st.extraLocal)
+        if (a >= segLocal && a + bytes <= segLocal + st.opts.deviceMemorySize) return true;
+    return false;
+}
+// The multicast alias covers the first segment only: a buffer of an expansion segment is reached by peer loads / stores.
+bool InFirstSegment(const void *p, uint64_t bytes)
+{
+    State &st = S();
+    const uint64_t a = reinterpret_cast<uint64_t>(p);
     return p != nullptr && a >= st.out.localGva && a + bytes <= st.out.localGva + st.opts.deviceMemorySize;
 }
 uint64_t DirectMin()
@@ -147,7 +160,8 @@ int AllReduce(Comm &c, const void *in, void *out, uint64_t n, int kdt, int odt, 
     std::lock_guard<std::mutex> g(c.mu);
     if (n * es > DirectMin() && InSlice(in, n * es) && InSlice(out, n * oes)) {
         MfCollArgs a = BaseArgs(c, in, out, n, scale, op, 0, 1);
-        a.zero_copy = (c.team.mc_base != 0 && op == 0 && kdt == odt && kdt != 3) ? 3 : 2;  // the switch adds when it can
+        const bool mc = c.team.mc_base != 0 && InFirstSegment(in, n * es) && InFirstSegment(out, n * oes);
+        a.zero_copy = (mc && op == 0 && kdt == odt && kdt != 3) ? 3 : 2;  // the switch adds when it can
         return Launched(L->coll(0, kdt, odt, &a, c.Ctas(n * es), 512, stream), "all_reduce (direct)");
     }
     uint64_t piece = c.stageBytes / std::max(es, oes);
@@ -177,7 +191,7 @@ int AllGatherBytes(Comm &c, const void *in, void *out, uint64_t bytes, void *str
     const uint64_t m = bytes / unit;
     if (bytes * c.size > DirectMin() && InSlice(out, bytes * c.size)) {
         MfCollArgs a = BaseArgs(c, in, out, m, 1.f, 0, 0, 0);
-        a.zero_copy = c.team.mc_base != 0 ? 3 : 2;  // one multicast store per 16 bytes instead of one store per peer
+        a.zero_copy = (c.team.mc_base != 0 && InFirstSegment(out, bytes * c.size)) ? 3 : 2;  // one multicast store per 16 bytes instead of one store per peer
         return Launched(L->coll(2, kdt, kdt, &a, c.Ctas(bytes * c.size), 512, stream), "all_gather (direct)");
     }
     uint64_t piece = c.stageBytes / unit / c.size;
@@ -208,7 +222,7 @@ int BroadcastBytes(Comm &c, const void *in, void *out, uint64_t bytes, uint32_t 
     const uint64_t total = bytes / unit;
     if (bytes > DirectMin() && InSlice(out, bytes)) {
         MfCollArgs a = BaseArgs(c, in, out, total, 1.f, 0, root, 0);
-        a.zero_copy = c.team.mc_base != 0 ? 3 : 2;
+        a.zero_copy = (c.team.mc_base != 0 && InFirstSegment(out, bytes)) ? 3 : 2;
         return Launched(L->coll(3, kdt, kdt, &a, c.Ctas(bytes), 512, stream), "broadcast (direct)");
     }
     uint64_t piece = c.stageBytes / unit;
@@ -254,6 +268,8 @@ int P2P(Comm &c, void *buf, uint64_t bytes, uint32_t peer, bool sending, void *s
 }  // namespace zbal
 
 using namespace zbal;
+
+extern "C" int32_t zbal_is_symmetric(const void *ptr, uint64_t bytes) { return S().up && InSlice(ptr, bytes) ? 1 : 0; }
 
 extern "C" {
 
@@ -467,7 +483,8 @@ int32_t zbal_reduce_scatter(const void *send, void *recv, size_t recv_count, zba
     const uint64_t m = recv_count;
     if (m * c->size * ti.size > DirectMin() && InSlice(send, m * c->size * ti.size)) {
         MfCollArgs a = BaseArgs(*c, send, recv, m * c->size, 1.f, kop, 0, 0);
-        a.zero_copy = (c->team.mc_base != 0 && kop == 0 && ti.kdt != 3) ? 3 : 2;  // the switch adds when it can
+        const bool mc = c->team.mc_base != 0 && InFirstSegment(send, m * c->size * ti.size);
+        a.zero_copy = (mc && kop == 0 && ti.kdt != 3) ? 3 : 2;  // the switch adds when it can
         return Launched(L->coll(1, ti.kdt, ti.kdt, &a, c->Ctas(m * c->size * ti.size), 512, stream), "reduce_scatter (direct)");
     }
     uint64_t piece = c->stageBytes / ti.size / c->size;

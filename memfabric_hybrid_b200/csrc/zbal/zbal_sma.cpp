@@ -53,6 +53,9 @@ namespace {
 //   use_sma_allocator            False: the pluggable entry points bypass the heap (plain device allocations)
 //   use_vmm_for_static_memory    True: requests above max_split_size_mb (weights, KV cache: large and long-lived)
 //                                get their own device allocation outside the heap and never fragment it
+//   expandable_segments          True: a request that the heap cannot serve (after the caches were returned) asks the grow
+//                                hook for another segment and is tried again; the heap then spans several address ranges
+//   max_segments                 ranges the heap may grow to (the first one included), default 8
 struct Config {
     uint64_t smallThreshold = 1ull << 20;
     uint64_t maxSplit = 20ull << 20;
@@ -61,7 +64,14 @@ struct Config {
     double gcThreshold = 0.0;
     bool useSma = true;
     bool vmmForStatic = false;
+    bool expandable = false;
+    uint64_t maxSegments = 8;
 };
+
+// Asked for another segment when the heap is exhausted: returns 0 after it added one with zbal_sma_add_segment.
+std::mutex g_hookMu;
+zbal_sma_grow_hook_t g_growHook = nullptr;
+void *g_growCtx = nullptr;
 
 bool ParseBool(const std::string &v, bool &out)
 {
@@ -87,6 +97,8 @@ Config ParseConf(uint64_t optThreshold)
         else if (k == "small_heap_size" && mf::ParseU64(v, u)) c.smallHeapSize = u;
         else if (k == "use_sma_allocator" && ParseBool(v, c.useSma)) {}
         else if (k == "use_vmm_for_static_memory" && ParseBool(v, c.vmmForStatic)) {}
+        else if (k == "expandable_segments" && ParseBool(v, c.expandable)) {}
+        else if (k == "max_segments" && mf::ParseU64(v, u) && u >= 1 && u <= 64) c.maxSegments = u;
         else if (k == "garbage_collection_threshold") c.gcThreshold = atof(v.c_str());
         else MF_WARN("ZBAL_ALLOC_CONF: ignoring '%s'", kv.c_str());
     }
@@ -135,7 +147,7 @@ public:
     void *Malloc(uint64_t requested, uint64_t stream)
     {
         const uint64_t size = Round(requested);
-        std::lock_guard<std::mutex> g(mu_);
+        std::unique_lock<std::mutex> g(mu_);
         st_.mallocCalls++;
         const PoolId pool = RoutedPool(stream);
         if (pool != kNoPool) return PoolMalloc(pool, size, requested, stream);
@@ -161,6 +173,26 @@ public:
             DeviceWait();
             FlushLocked();
             addr = heap_.AlignedAllocate(size, size < cfg_.smallThreshold ? 512 : 4096);
+        }
+        if (addr == 0 && cfg_.expandable && heap_.Regions() < cfg_.maxSegments) {
+            // another segment: the hook runs without the allocator's lock (it calls back into AddSegment, and with a
+            // symmetric heap it is a collective step that may take a while)
+            zbal_sma_grow_hook_t hook;
+            void *ctx;
+            {
+                std::lock_guard<std::mutex> h(g_hookMu);
+                hook = g_growHook;
+                ctx = g_growCtx;
+            }
+            if (hook != nullptr) {
+                g.unlock();
+                const int rc = hook(size, ctx);
+                g.lock();
+                if (rc == 0) {
+                    st_.segmentsAdded++;
+                    addr = heap_.AlignedAllocate(size, size < cfg_.smallThreshold ? 512 : 4096);
+                }
+            }
         }
         if (addr == 0) {
             st_.failedMallocs++;
@@ -257,10 +289,13 @@ public:
             mf::LastError::Set(Z_ERROR, "empty_cache: %zu blocks (%lu bytes) are still in use", live_.size(), (unsigned long)inUse_);
     }
 
+    bool AddSegment(uint64_t base, uint64_t size) { return heap_.AddRegion(base, size); }
+
     void Stats(zbal_sma_stats_t &o)
     {
         std::lock_guard<std::mutex> g(mu_);
         o = st_;
+        o.segments = heap_.Regions();
         o.heapSize = heap_.TotalSize();
         o.inUseBytes = inUse_;
         o.cachedBytes = cached_;
@@ -443,6 +478,22 @@ void zbal_sma_uninit(int32_t flags)
     (void)flags;
     std::lock_guard<std::mutex> g(g_mu);
     g_sma.reset();
+}
+
+int32_t zbal_sma_add_segment(uint64_t base, uint64_t size)
+{
+    auto s = Get();
+    if (!s) return MF_FAIL(Z_NOT_INITIALIZED, "zbal_sma_add_segment before zbal_sma_init");
+    if (base == 0 || size < (1ull << 20)) return MF_FAIL(Z_INVALID_PARAM, "a segment needs a base address and at least 1 MiB");
+    if (!s->AddSegment(base, size)) return MF_FAIL(Z_INVALID_PARAM, "segment [%lx, +%lu) overlaps the heap or is misaligned", (unsigned long)base, (unsigned long)size);
+    return Z_OK;
+}
+
+void zbal_sma_set_grow_hook(zbal_sma_grow_hook_t hook, void *ctx)
+{
+    std::lock_guard<std::mutex> h(g_hookMu);
+    g_growHook = hook;
+    g_growCtx = ctx;
 }
 
 void zbal_simulate_init(int64_t addr, int64_t size)

@@ -8,6 +8,47 @@ SplitMemoryHeap::SplitMemoryHeap(uint64_t base, uint64_t size, uint64_t threshol
     : base_(base), size_(size / kMinBlock * kMinBlock), threshold_(threshold == 0 ? (1ull << 20) : threshold)
 {
     if (size_ > 0) InsertFree(base_, size_);
+    regions_.emplace_back(base_, size_);
+}
+
+void SplitMemoryHeap::InsertFreeMerged(uint64_t addr, uint64_t size)
+{
+    auto next = free_.lower_bound(addr);
+    if (next != free_.begin()) {
+        auto prev = std::prev(next);
+        if (prev->first + prev->second == addr) {
+            const uint64_t pa = prev->first, ps = prev->second;
+            EraseFree(pa, ps);
+            addr = pa;
+            size += ps;
+        }
+    }
+    next = free_.find(addr + size);
+    if (next != free_.end()) {
+        const uint64_t na = next->first, ns = next->second;
+        EraseFree(na, ns);
+        size += ns;
+    }
+    InsertFree(addr, size);
+}
+
+bool SplitMemoryHeap::AddRegion(uint64_t base, uint64_t size)
+{
+    size = size / kMinBlock * kMinBlock;
+    if (size == 0 || (base % kMinBlock) != 0) return false;
+    std::lock_guard<std::mutex> g(mu_);
+    for (const auto &r : regions_)
+        if (base < r.first + r.second && r.first < base + size) return false;
+    regions_.emplace_back(base, size);
+    size_ += size;
+    InsertFreeMerged(base, size);
+    return true;
+}
+
+size_t SplitMemoryHeap::Regions() const
+{
+    std::lock_guard<std::mutex> g(mu_);
+    return regions_.size();
 }
 
 int SplitMemoryHeap::BucketOf(uint64_t size)
@@ -97,24 +138,7 @@ uint64_t SplitMemoryHeap::Release(uint64_t addr)
     const uint64_t released = size;
     used_.erase(it);
     inUse_ -= size;
-    // merge with the free block that ends at addr and the one that starts at addr + size
-    auto next = free_.lower_bound(addr);
-    if (next != free_.begin()) {
-        auto prev = std::prev(next);
-        if (prev->first + prev->second == addr) {
-            const uint64_t pa = prev->first, ps = prev->second;
-            EraseFree(pa, ps);
-            addr = pa;
-            size += ps;
-        }
-    }
-    next = free_.find(addr + size);
-    if (next != free_.end()) {
-        const uint64_t na = next->first, ns = next->second;
-        EraseFree(na, ns);
-        size += ns;
-    }
-    InsertFree(addr, size);
+    InsertFreeMerged(addr, size);  // with the free block that ends at addr and the one that starts at addr + size
     return released;
 }
 

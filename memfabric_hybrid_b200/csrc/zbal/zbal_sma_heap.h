@@ -30,6 +30,10 @@ public:
     // Returns the size of the released block, 0 if addr was not handed out by this heap.
     uint64_t Release(uint64_t addr);
     uint64_t AllocatedSize(uint64_t addr) const;
+    // Adds another range [base, base + size) of usable addresses (an expansion segment). It may or may not touch a
+    // range the heap already has; free space that touches is merged. False when it overlaps what the heap manages.
+    bool AddRegion(uint64_t base, uint64_t size);
+    size_t Regions() const;
 
     uint64_t Base() const { return base_; }
     uint64_t TotalSize() const { return size_; }
@@ -52,10 +56,14 @@ private:
     static int BucketOf(uint64_t size);
     void InsertFree(uint64_t addr, uint64_t size);
     void EraseFree(uint64_t addr, uint64_t size);
+    void InsertFreeMerged(uint64_t addr, uint64_t size);  // joins the free neighbours that touch [addr, addr + size)
     // picks a free block for (size, align); low=true prefers the lowest address, else the highest
     bool Pick(uint64_t size, uint64_t align, bool low, uint64_t &blockAddr, uint64_t &blockSize, uint64_t &at) const;
 
-    const uint64_t base_, size_, threshold_;
+    const uint64_t base_;
+    uint64_t size_;
+    const uint64_t threshold_;
+    std::vector<std::pair<uint64_t, uint64_t>> regions_;  // (base, size) in the order they were added
     mutable std::mutex mu_;
     std::map<uint64_t, uint64_t> free_;        // addr -> size
     std::set<uint64_t> buckets_[kBuckets];     // addresses of the free blocks of each size class

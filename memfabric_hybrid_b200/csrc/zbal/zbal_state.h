@@ -87,6 +87,8 @@ struct State {
     zbal_bootstrap_options_t opts{};
     zbal_bootstrap_output_t out{};
     smem_shm_t shm = nullptr;
+    std::vector<smem_shm_t> extraShm;  // expansion segments of the heap (zbal_heap_expand), destroyed with the first one
+    std::vector<uint64_t> extraLocal;  // address of this rank's slot in each of them
     uint64_t commSlotBytes = 0;
     bool ownSmem = false, ownShm = false, ownSma = false;
     std::map<std::string, std::shared_ptr<Comm>> comms;

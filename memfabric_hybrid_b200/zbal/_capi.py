@@ -54,7 +54,8 @@ class MoeBuffersC(C.Structure):
 
 class SmaStatsC(C.Structure):
     _fields_ = [(n, u64) for n in ("heapSize", "inUseBytes", "cachedBytes", "peakInUseBytes", "largestFreeBlock", "mallocCalls",
-                                   "freeCalls", "cacheHits", "heapCarves", "failedMallocs", "poolCount", "poolCachedBytes")]
+                                   "freeCalls", "cacheHits", "heapCarves", "failedMallocs", "poolCount", "poolCachedBytes", "segments",
+                                   "segmentsAdded")]
 
 
 _declared = False
@@ -83,6 +84,9 @@ def _declare(l):
     s(l, "zbal_sma_end_pool", i32, u64, u64)
     s(l, "zbal_sma_release_pool", i32, u64, u64)
     s(l, "zbal_sma_get_stats", i32, P(SmaStatsC))
+    s(l, "zbal_sma_add_segment", i32, u64, u64)
+    s(l, "zbal_heap_expand", i32, P(u64), P(u64))
+    s(l, "zbal_is_symmetric", i32, C.c_void_p, u64)
     s(l, "zbal_sma_reset_peak", None)
     s(l, "zbal_sma_record_history", None, C.c_bool, u32)
     s(l, "zbal_sma_snapshot", i64, C.c_char_p, i64)

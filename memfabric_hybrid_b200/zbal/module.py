@@ -162,7 +162,18 @@ def in_symmetric_heap(t: torch.Tensor) -> bool:
     if out is None or not t.is_cuda:
         return False
     p = t.data_ptr()
-    return out.heapGva <= p < out.heapGva + out.heapSize
+    if out.heapGva <= p < out.heapGva + out.heapSize:
+        return True
+    return bool(K.lib().zbal_is_symmetric(p, max(1, t.numel() * t.element_size())))   # expansion segments
+
+
+def expand_heap() -> tuple:
+    """Collective: one more segment of ``device_memory_size`` bytes per rank for the symmetric heap; every rank calls it
+    at the same point. -> (address of this rank's part of the new segment, its size). With
+    ``ZBAL_ALLOC_CONF=expandable_segments:True`` the allocator does this by itself when a request does not fit."""
+    base, size = C.c_uint64(), C.c_uint64()
+    K.check(K.lib().zbal_heap_expand(C.byref(base), C.byref(size)), "zbal_heap_expand")
+    return int(base.value), int(size.value)
 
 
 def get_heap_stats():

@@ -426,3 +426,55 @@ def test_moe_c_api_single_gpu():
 def test_moe_c_api_multi_gpu():
     n = min(torch.cuda.device_count(), 4)
     assert run_ranks(_moe_capi_scenario, n, (free_port(),), timeout=420, with_barrier=True) == [0] * n
+
+
+def _expand_scenario(rank, world, port, sync):
+    """The symmetric heap grows by a segment while tensors live in it; a tensor of the NEW segment is all-reduced in direct
+    mode (peers read it in place: p + (r - me) * stride must hold across segments) against an fp32 sum."""
+    import os
+    os.environ["ZBAL_ALLOC_CONF"] = "expandable_segments:True,max_segments:3"
+    import torch
+    import torch.distributed as dist
+    import memfabric_hybrid_b200.zbal as zbal
+    dev = rank % torch.cuda.device_count()
+    torch.cuda.set_device(dev)
+    assert zbal.zbal_init(world, dev, rank, 256 << 20, ip_port=f"127.0.0.1:{port}", start_config_server=True)
+    dist.init_process_group("zbal", init_method=f"tcp://127.0.0.1:{port + 1}", rank=rank, world_size=world)
+    first = zbal.heap_stats()
+    assert first["segments"] == 1
+    n = 24 << 20   # 96 MiB of fp32 per tensor: the third one cannot fit into what is left of the first 256 MiB segment
+    with zbal.switch_to_allocator():
+        keep = [torch.full((n,), float(rank + 1 + i), device="cuda") for i in range(2)]
+        grown = torch.full((n,), float(rank + 1), device="cuda")     # makes the allocator add a segment, on every rank
+        st = zbal.heap_stats()
+        assert st["segments"] == 2 and st["segmentsAdded"] == 1 and st["heapSize"] > first["heapSize"]
+        base = zbal.zbal_get_symm_base_addr()
+        assert zbal.in_symmetric_heap(grown) and zbal.in_symmetric_heap(keep[0])
+        g = torch.Generator("cuda").manual_seed(rank)
+        grown.copy_(torch.randn(n, device="cuda", generator=g))
+        ref = sum(torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(r)) for r in range(world))
+        dist.all_reduce(grown)
+        torch.testing.assert_close(grown, ref, rtol=1e-5, atol=1e-5)
+        dist.all_reduce(keep[1])
+        assert float(keep[1][7]) == float(sum(r + 2 for r in range(world)))
+        off = grown.data_ptr() - base
+    offs = [None] * world
+    dist.all_gather_object(offs, off) if world > 1 else offs.__setitem__(0, off)
+    assert len(set(offs)) == 1, f"offsets in the new segment differ across ranks: {offs}"
+    del keep, grown
+    torch.cuda.synchronize()
+    dist.destroy_process_group()
+    zbal.zbal_uninit()
+    return 0
+
+
+def test_heap_expands_single_gpu():
+    port = free_port()
+    assert run_ranks(_expand_scenario, 1, (port,), timeout=300, with_barrier=True) == [0]
+
+
+@pytest.mark.multigpu
+def test_heap_expands_multi_gpu():
+    n = min(torch.cuda.device_count(), 4)
+    port = free_port()
+    assert run_ranks(_expand_scenario, n, (port,), timeout=420, with_barrier=True) == [0] * n

@@ -280,3 +280,77 @@ def test_native_c10d_backend_routing_and_group_names():
     res = run_ranks(_native_pg, 4, (free_port(),), timeout=180)
     assert res[0] == ["zbal_0:2:2_group_0", "irregular"] and res[2] == ["zbal_0:2:2_group_0"]
     assert res[1] == ["zbal_1:3:2_group_0", "irregular"] and res[3] == ["zbal_1:3:2_group_0", "irregular"]
+
+
+def test_heap_grows_by_segments(monkeypatch):
+    """Expandable segments on the simulated heap: a second address range is added by hand, and by the grow hook when a
+    request no longer fits (ZBAL_ALLOC_CONF=expandable_segments:True)."""
+    from memfabric_hybrid_b200.zbal import _capi as K
+    l = K.lib()
+    HOOK = C.CFUNCTYPE(C.c_int, C.c_uint64, C.c_void_p)
+    l.zbal_sma_set_grow_hook.argtypes = [HOOK, C.c_void_p]
+    l.zbal_sma_set_grow_hook.restype = None
+    calls = []
+
+    def grow(need, _ctx):
+        calls.append(need)
+        if len(calls) > 2:
+            return -1
+        return l.zbal_sma_add_segment(BASE + (1 << 32) * len(calls), 64 * MiB)
+
+    cb = HOOK(grow)
+    try:
+        # off: exhaustion is an error, a segment can still be added by hand
+        monkeypatch.setenv("ZBAL_ALLOC_CONF", "expandable_segments:False")
+        l.zbal_simulate_init(BASE, 64 * MiB)
+        l.zbal_sma_set_grow_hook(cb, None)
+        a = l.zbal_pluggable_malloc(48 * MiB, 0, None)
+        assert a and not l.zbal_pluggable_malloc(32 * MiB, 0, None) and calls == []
+        assert l.zbal_sma_add_segment(BASE + (1 << 40), 64 * MiB) == 0
+        assert l.zbal_sma_add_segment(BASE + (1 << 40) + MiB, 4 * MiB) != 0          # overlaps
+        b = l.zbal_pluggable_malloc(32 * MiB, 0, None)
+        assert BASE + (1 << 40) <= b < BASE + (1 << 40) + 64 * MiB
+        s = _stats(l)
+        assert s.segments == 2 and s.segmentsAdded == 0 and s.heapSize == 128 * MiB
+        l.zbal_sma_uninit(0)
+        # on: the hook is asked, at most max_segments - 1 times
+        monkeypatch.setenv("ZBAL_ALLOC_CONF", "expandable_segments:True,max_segments:3")
+        l.zbal_simulate_init(BASE, 64 * MiB)
+        got = [l.zbal_pluggable_malloc(40 * MiB, 0, None) for _ in range(4)]
+        assert all(got[:3]) and not got[3]
+        assert got[1] >= BASE + (1 << 32) and got[2] >= BASE + (2 << 32) and len(calls) == 2
+        s = _stats(l)
+        assert s.segments == 3 and s.segmentsAdded == 2 and s.failedMallocs == 1
+        # released memory of a segment is reused like any other
+        l.zbal_pluggable_free(got[1], 40 * MiB, 0, None)
+        l.zbal_pluggable_empty_cache(False)
+        assert l.zbal_pluggable_malloc(40 * MiB, 0, None) == got[1]
+    finally:
+        l.zbal_sma_set_grow_hook(HOOK(0), None)
+        l.zbal_sma_uninit(0)
+
+
+def _boot_expand(rank, world, port):
+    os.environ["MF_DEVICE_BACKEND"] = "fake"
+    os.environ["ZBAL_ALLOC_CONF"] = "expandable_segments:True,max_segments:3"
+    import memfabric_hybrid_b200.zbal as z
+    from memfabric_hybrid_b200.zbal import _capi as K
+    l = K.lib()
+    assert z.zbal_init(world, 0, rank, 64 << 20, ip_port=f"127.0.0.1:{port}", start_config_server=True, comm_group_cap=2)
+    out = z.module.bootstrap_output()
+    # explicit, collective
+    base, size = z.expand_heap()
+    assert size == 64 << 20
+    delta = base - out.localGva
+    # automatic: the same request sequence on every rank runs out of room at the same call
+    blocks = [l.zbal_pluggable_malloc(30 << 20, 0, None) for _ in range(5)]
+    assert all(blocks), blocks
+    st = z.heap_stats()
+    z.zbal_uninit()
+    return delta, [b - out.localGva for b in blocks], st["segments"], st["segmentsAdded"]
+
+
+def test_symmetric_heap_expands_collectively_over_fake_backend():
+    res = run_ranks(_boot_expand, 2, (free_port(),), timeout=120)
+    assert res[0] == res[1]                      # same distance to the new segment, same offsets of every block
+    assert res[0][2] == 3 and res[0][3] == 1     # one segment by hand, one by the hook
