@@ -443,21 +443,20 @@ def _expand_scenario(rank, world, port, sync):
     first = zbal.heap_stats()
     assert first["segments"] == 1
     n = 24 << 20   # 96 MiB of fp32 per tensor: the third one cannot fit into what is left of the first 256 MiB segment
-    with zbal.switch_to_allocator():
+    with zbal.switch_to_allocator():   # only the three tensors come from the symmetric heap; temporaries below do not
         keep = [torch.full((n,), float(rank + 1 + i), device="cuda") for i in range(2)]
-        grown = torch.full((n,), float(rank + 1), device="cuda")     # makes the allocator add a segment, on every rank
-        st = zbal.heap_stats()
-        assert st["segments"] == 2 and st["segmentsAdded"] == 1 and st["heapSize"] > first["heapSize"]
-        base = zbal.zbal_get_symm_base_addr()
-        assert zbal.in_symmetric_heap(grown) and zbal.in_symmetric_heap(keep[0])
-        g = torch.Generator("cuda").manual_seed(rank)
-        grown.copy_(torch.randn(n, device="cuda", generator=g))
-        ref = sum(torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(r)) for r in range(world))
-        dist.all_reduce(grown)
-        torch.testing.assert_close(grown, ref, rtol=1e-5, atol=1e-5)
-        dist.all_reduce(keep[1])
-        assert float(keep[1][7]) == float(sum(r + 2 for r in range(world)))
-        off = grown.data_ptr() - base
+        grown = torch.empty((n,), device="cuda")     # makes the allocator add a segment, on every rank
+    st = zbal.heap_stats()
+    assert st["segments"] == 2 and st["segmentsAdded"] == 1 and st["heapSize"] > first["heapSize"]
+    base = zbal.zbal_get_symm_base_addr()
+    assert zbal.in_symmetric_heap(grown) and zbal.in_symmetric_heap(keep[0])
+    grown.copy_(torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(rank)))
+    ref = sum(torch.randn(n, device="cuda", generator=torch.Generator("cuda").manual_seed(r)) for r in range(world))
+    dist.all_reduce(grown)
+    torch.testing.assert_close(grown, ref, rtol=1e-5, atol=1e-5)
+    dist.all_reduce(keep[1])
+    assert float(keep[1][7]) == float(sum(r + 2 for r in range(world)))
+    off = grown.data_ptr() - base
     offs = [None] * world
     dist.all_gather_object(offs, off) if world > 1 else offs.__setitem__(0, off)
     assert len(set(offs)) == 1, f"offsets in the new segment differ across ranks: {offs}"
