@@ -14,6 +14,11 @@
 // zbal_kernel_{dispatch_layout,notify_dispatch,dispatch_normal,combine_normal}.h of the reference.
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
+#include <stdlib.h>
+
+#include <map>
+#include <mutex>
+#include <utility>
 #include <cuda_fp8.h>
 
 #include "mf_devtrace.cuh"
@@ -71,6 +76,56 @@ __global__ void __launch_bounds__(1024) k_moe_layout_expert(const int *__restric
         __syncthreads();
     }
     if (threadIdx.x == 0) tokens_per_expert[e] = running;
+}
+
+// The same positions in O(entries) work: chunk c (1024 consecutive entries = one CTA) ranks its entries per expert in token
+// order and leaves its per-expert counts in chunk_cnt[c][E]; the second kernel turns the counts of the earlier chunks into
+// offsets and adds them. Entry ids outside [0, E) (unselected slots) get position 0 and count nowhere.
+constexpr int kLayoutChunk = 1024;
+__global__ void __launch_bounds__(kLayoutChunk) k_moe_layout_chunk_rank(const int *__restrict__ topk_idx, int n_entries, int E, int *send_idx,
+                                                                        int *chunk_cnt)
+{
+    extern __shared__ uint16_t warp_cnt[];  // [32 warps][E]: hits of expert e in warp w, then their exclusive prefix over w
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < 32 * E; i += blockDim.x) warp_cnt[i] = 0;
+    __syncthreads();
+    const int i = (int)blockIdx.x * kLayoutChunk + threadIdx.x;
+    int e = i < n_entries ? topk_idx[i] : -1;
+    if (e >= E) e = -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank_in_warp = __popc(peers & ((1u << lane) - 1));
+    if (e >= 0 && rank_in_warp == 0) warp_cnt[warp * E + e] = (uint16_t)__popc(peers);
+    __syncthreads();
+    for (int x = threadIdx.x; x < E; x += blockDim.x) {
+        int run = 0;
+        for (int w = 0; w < 32; w++) {
+            const int c = warp_cnt[w * E + x];
+            warp_cnt[w * E + x] = (uint16_t)run;
+            run += c;
+        }
+        chunk_cnt[(int64_t)blockIdx.x * E + x] = run;
+    }
+    __syncthreads();
+    if (i < n_entries) send_idx[i] = e >= 0 ? (int)warp_cnt[warp * E + e] + rank_in_warp : 0;
+}
+
+__global__ void __launch_bounds__(kLayoutChunk) k_moe_layout_chunk_offset(const int *__restrict__ topk_idx, int n_entries, int E, int *send_idx,
+                                                                          const int *__restrict__ chunk_cnt, int *tokens_per_expert)
+{
+    extern __shared__ int before[];  // [E]: hits of expert e in the chunks before this one
+    const int c = blockIdx.x;
+    for (int x = threadIdx.x; x < E; x += blockDim.x) {
+        int run = 0;
+        for (int q = 0; q < c; q++) run += __ldg(chunk_cnt + (int64_t)q * E + x);
+        before[x] = run;
+        if (c == (int)gridDim.x - 1) tokens_per_expert[x] = run + __ldg(chunk_cnt + (int64_t)c * E + x);
+    }
+    __syncthreads();
+    const int i = c * kLayoutChunk + threadIdx.x;
+    if (i < n_entries) {
+        const int e = topk_idx[i];
+        if (e >= 0 && e < E) send_idx[i] += before[e];
+    }
 }
 
 __global__ void k_moe_layout_rank(const int *__restrict__ topk_idx, int T, int K, int experts_per_rank, int world, int *tokens_per_rank,
@@ -336,6 +391,143 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs &a, uint4 nxt_l
     }
 }
 
+// ---- warp-per-token dispatch ------------------------------------------------------------------------------
+// Every warp takes whole tokens: it quantises the row into its own shared-memory buffer (e4m3 row, then the row's scales),
+// and for every destination its lane 0 hands the copy unit ONE bulk store of the whole row, the scales leave as one
+// 16-byte store per lane and the info record as one store from the lane that resolved the destination. Nothing in the
+// loop involves another warp, so there is no CTA barrier per token, and a row costs one copy instruction per destination
+// instead of one 16-byte store per thread per destination. Two buffers per warp: the copy unit reads the previous token's
+// buffer while the next row is quantised.
+constexpr int kDwWarps = 12;
+constexpr int kDwLoads = 14;  // independent 16-byte loads per lane in flight (256 elements per warp load)
+__host__ __device__ constexpr int dw_buf_bytes(int H, int K) { return H + (H / kQuantGroup) * 4 + 0 * K; }
+__host__ __device__ constexpr int dw_smem_bytes(int H, int K) { return kDwWarps * 2 * ((dw_buf_bytes(H, K) + 127) / 128 * 128); }
+
+__device__ __forceinline__ void bulk_store(void *gdst, const void *ssrc, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"((uint32_t)__cvta_generic_to_shared(ssrc)), "r"(bytes)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(kDwWarps * 32) k_moe_dispatch_warp(DispatchArgs a)
+{
+    extern __shared__ __align__(128) uint8_t dw_smem[];
+    const Team &t = a.team;
+    const uint32_t me = team_rank(t);
+    const int H = a.sh.H, K = a.sh.K, El = a.sh.E / (int)t.world;
+    const int groups = H / kQuantGroup;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int stride_buf = (dw_buf_bytes(H, K) + 127) / 128 * 128;
+    uint8_t *bufs = dw_smem + (size_t)warp * 2 * stride_buf;
+    const int wid = (int)blockIdx.x * kDwWarps + warp, wtotal = (int)gridDim.x * kDwWarps;
+    const bool smoothed = a.smooth != nullptr;
+    int which = 0;
+    for (int tok = wid; tok < a.sh.T; tok += wtotal, which ^= 1) {
+        uint8_t *buf = bufs + which * stride_buf;
+        float *sc = reinterpret_cast<float *>(buf + H);
+        // routing of this token: lane k resolves destination k (two dependent loads, overlapped with the row loads below)
+        int d_rank = -1, d_pos = 0;
+        float d_w = 0.f;
+        if (lane < K) {
+            const int ex = a.topk_idx[tok * K + lane];
+            if (ex >= 0) {
+                const int pos = a.put_off[ex] + a.send_idx[tok * K + lane];
+                if (pos < a.sh.max_recv) {
+                    d_rank = ex / El;
+                    d_pos = pos;
+                    d_w = a.topk_w[tok * K + lane];
+                } else {
+                    atomicCAS(a.status, 0, 0x401);  // receive buffer too small: dropped, reported
+                }
+            }
+        }
+        // the copy unit must be done READING this buffer (the token before the previous one)
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
+        // quantise: one warp load covers 256 elements = two 128-groups (lanes 0-15 and 16-31); half a row of 7168 elements
+        // is requested before the first conversion (14 independent 16-byte loads per lane), so a token costs two memory
+        // latencies, not one per chunk.
+        const __nv_bfloat16 *row = a.x + (int64_t)tok * H;
+        for (int c0 = 0; c0 < H; c0 += kDwLoads * 256) {
+            uint4 raw[kDwLoads];
+#pragma unroll
+            for (int u = 0; u < kDwLoads; u++) {
+                const int col = c0 + u * 256 + lane * 8;
+                raw[u] = col < H ? __ldg(reinterpret_cast<const uint4 *>(row + col)) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < kDwLoads; u++) {
+                const int col = c0 + u * 256 + lane * 8;
+                if (c0 + u * 256 >= H) break;  // uniform over the warp
+                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[u]);
+                float f[8];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float2 p = __bfloat1622float2(h[i]);
+                    f[2 * i] = p.x;
+                    f[2 * i + 1] = p.y;
+                }
+                if (smoothed && col < H) {
+                    const float4 s0 = __ldg(reinterpret_cast<const float4 *>(a.smooth + col));
+                    const float4 s1 = __ldg(reinterpret_cast<const float4 *>(a.smooth + col) + 1);
+                    f[0] *= s0.x, f[1] *= s0.y, f[2] *= s0.z, f[3] *= s0.w;
+                    f[4] *= s1.x, f[5] *= s1.y, f[6] *= s1.z, f[7] *= s1.w;
+                }
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+                for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                const float scale = pow2_scale_e4m3(amax);
+                const float mul = 1.f / scale;
+                if (col < H) {
+                    uint2 q;
+                    q.x = pack4_e4m3(f[0], f[1], f[2], f[3], mul);
+                    q.y = pack4_e4m3(f[4], f[5], f[6], f[7], mul);
+                    *reinterpret_cast<uint2 *>(buf + col) = q;
+                    if ((lane & 15) == 0) sc[col / kQuantGroup] = scale;
+                }
+            }
+        }
+        // the info record of destination k leaves from lane k as a plain store
+        if (lane < K && d_rank >= 0)
+            reinterpret_cast<int4 *>(peer_ptr(t, d_rank, a.hp.recv_info))[d_pos] = make_int4((int)me, tok, lane, __float_as_int(d_w));
+        // generic-proxy writes to shared memory before the copy unit reads them
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        const float4 my_sc = lane < groups / 4 ? reinterpret_cast<const float4 *>(sc)[lane] : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 my_sc2 = lane + 32 < groups / 4 ? reinterpret_cast<const float4 *>(sc)[lane + 32] : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < K; k++) {
+            const int d = __shfl_sync(0xffffffffu, d_rank, k);
+            const int pos = __shfl_sync(0xffffffffu, d_pos, k);
+            if (d < 0) continue;
+            // the row goes through the copy unit (one instruction for 7 KiB), its scales as one 16-byte store per lane
+            if (lane == 0) bulk_store(peer_ptr(t, d, a.hp.recv_x) + (int64_t)pos * H, buf, (uint32_t)H);
+            float4 *srow = reinterpret_cast<float4 *>(reinterpret_cast<float *>(peer_ptr(t, d, a.hp.recv_scale)) + (int64_t)pos * groups);
+            if (lane < groups / 4) srow[lane] = my_sc;
+            if (lane + 32 < groups / 4) srow[lane + 32] = my_sc2;
+        }
+        if (lane == 0) asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+    // every bulk store of this warp has been performed before the CTA reports in
+    if (lane == 0) {
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        asm volatile("fence.proxy.async;" ::: "memory");  // the copy unit's writes, as the generic proxy (the fences below) sees them
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const uint32_t done = atomicAdd(a.done_count, 1u) + 1;
+        const bool last = a.seq != 0 ? done == gridDim.x * a.seq : done == gridDim.x;
+        if (last) {
+            if (a.seq == 0) *a.done_count = 0;
+            __threadfence_system();
+            for (uint32_t r = 0; r < t.world; r++)
+                st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, a.hp.flags)) + me, a.epoch);
+        }
+    }
+}
+
 __global__ void __launch_bounds__(448) k_moe_dispatch(DispatchArgs a)
 {
     uint4 lo, hi;
@@ -370,7 +562,7 @@ __global__ void k_moe_signal_all(Team t, MoeHeap hp, int which, uint32_t epoch)
 // routing weights when they were pushed.
 __device__ __forceinline__ void combine_reduce_body(const Team &t, const MoeHeap &hp, const MoeShape &sh, const int *topk_idx, __nv_bfloat16 *out,
                                                     const float *topk_w);
-__global__ void __launch_bounds__(256) k_moe_combine_reduce(Team t, MoeHeap hp, MoeShape sh, const int *topk_idx, __nv_bfloat16 *out)
+__global__ void __launch_bounds__(256, 4) k_moe_combine_reduce(Team t, MoeHeap hp, MoeShape sh, const int *topk_idx, __nv_bfloat16 *out)
 {
     combine_reduce_body(t, hp, sh, topk_idx, out, nullptr);
 }
@@ -466,37 +658,46 @@ __device__ __forceinline__ void combine_reduce_body(const Team &t, const MoeHeap
     const uint32_t me = team_rank(t);
     const __nv_bfloat16 *comb = reinterpret_cast<const __nv_bfloat16 *>(peer_ptr(t, me, hp.comb));
     const int vecs = sh.H / 8;
-    for (int tok = blockIdx.x; tok < sh.T; tok += gridDim.x) {
-        for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            // the slots of a token are fetched eight at a time (independent loads in flight), then added in slot order
-            for (int k0 = 0; k0 < sh.K; k0 += 8) {
-                uint4 raw[8];
-                float wk[8];
+    // One work item = one 16-byte column vector of one token; items are dealt out grid-wide, so every thread stays busy
+    // whatever T is. The slot loads do not wait for the routing table: every slot of the combine area exists, so all of a
+    // token's slots are fetched at once and the ones that were not selected are dropped by a select afterwards (never by
+    // a multiplication: a stale slot may hold anything).
+    const int64_t items = (int64_t)sh.T * vecs;
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t it = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; it < items; it += step) {
+        const int tok = (int)(it / vecs), v = (int)(it - (int64_t)tok * vecs);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int k0 = 0; k0 < sh.K; k0 += 8) {
+            uint4 raw[8];
+            float wk[8];
 #pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    const int k = k0 + u;
-                    const bool on = k < sh.K && topk_idx[tok * sh.K + k] >= 0;
-                    wk[u] = on ? (topk_w != nullptr ? topk_w[tok * sh.K + k] : 1.f) : 0.f;
-                    raw[u] = on ? __ldcg(reinterpret_cast<const uint4 *>(comb + ((int64_t)tok * sh.K + k) * sh.H) + v) : make_uint4(0, 0, 0, 0);
-                }
+            for (int u = 0; u < 8; u++) {
+                const int k = min(k0 + u, sh.K - 1);
+                raw[u] = __ldcs(reinterpret_cast<const uint4 *>(comb + ((int64_t)tok * sh.K + k) * sh.H) + v);   // read once: streaming
+            }
 #pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[u]);
+            for (int u = 0; u < 8; u++) {
+                const int k = k0 + u;
+                const bool on = k < sh.K && __ldg(topk_idx + tok * sh.K + k) >= 0;
+                wk[u] = on ? (topk_w != nullptr ? __ldg(topk_w + tok * sh.K + k) : 1.f) : 0.f;
+                if (!on) raw[u] = make_uint4(0, 0, 0, 0);
+            }
 #pragma unroll
-                    for (int e = 0; e < 4; e++) {
-                        const float2 f = __bfloat1622float2(h[e]);
-                        acc[2 * e] += f.x * wk[u];
-                        acc[2 * e + 1] += f.y * wk[u];
-                    }
+            for (int u = 0; u < 8; u++) {
+                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw[u]);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __bfloat1622float2(h[e]);
+                    acc[2 * e] += f.x * wk[u];
+                    acc[2 * e + 1] += f.y * wk[u];
                 }
             }
-            uint4 pk;
-            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
-#pragma unroll
-            for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
-            *(reinterpret_cast<uint4 *>(out + (int64_t)tok * sh.H) + v) = pk;
         }
+        uint4 pk;
+        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+        *(reinterpret_cast<uint4 *>(out + (int64_t)tok * sh.H) + v) = pk;
     }
 }
 
@@ -616,13 +817,49 @@ MF_DEVTRACE_DEFINE_SETTER(mf_moe_set_devtrace)
 
 extern "C" {
 
+// Counter scratch of the chunked layout: one buffer per (device, stream), grown on demand and kept for the life of the process
+// (work on one stream is ordered, so consecutive layouts on it may share the buffer; different streams never do).
+static int *layout_scratch(cudaStream_t s, size_t bytes)
+{
+    static std::mutex mu;
+    static std::map<std::pair<int, cudaStream_t>, std::pair<int *, size_t>> bufs;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    std::lock_guard<std::mutex> g(mu);
+    auto &b = bufs[{dev, s}];
+    if (b.second < bytes) {
+        // the old buffer may still be read by work in flight on the stream: it is left to the process (a few hundred KB)
+        int *p = nullptr;
+        const size_t want = bytes < (256u << 10) ? (256u << 10) : bytes * 2;
+        if (cudaMalloc(reinterpret_cast<void **>(&p), want) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        b = {p, want};
+    }
+    return b.first;
+}
+
 int mf_moe_layout(const int *topk_idx, int T, int K, int E, int world, int *tokens_per_expert, int *tokens_per_rank, int *send_idx,
                   uint8_t *is_token_in_rank, void *stream)
 {
     if (T <= 0 || K <= 0 || K > 16 || E <= 0 || E > 1024 || world <= 0 || E % world != 0) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     cudaMemsetAsync(tokens_per_rank, 0, sizeof(int) * world, s);
-    k_moe_layout_expert<<<E, 1024, 0, s>>>(topk_idx, T * K, tokens_per_expert, send_idx);
+    // chunked ranking needs chunks x E counters; very large problems keep the one-CTA-per-expert kernel
+    const int n = T * K, chunks = (n + kLayoutChunk - 1) / kLayoutChunk;
+    int *chunk_cnt = (int64_t)chunks * E <= (4 << 20) ? layout_scratch(s, sizeof(int) * (size_t)chunks * E) : nullptr;
+    if (chunk_cnt != nullptr) {
+        static bool attr = false;
+        if (!attr) {
+            cudaFuncSetAttribute(k_moe_layout_chunk_rank, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * 2);
+            attr = true;
+        }
+        k_moe_layout_chunk_rank<<<chunks, kLayoutChunk, 32 * E * sizeof(uint16_t), s>>>(topk_idx, n, E, send_idx, chunk_cnt);
+        k_moe_layout_chunk_offset<<<chunks, kLayoutChunk, E * sizeof(int), s>>>(topk_idx, n, E, send_idx, chunk_cnt, tokens_per_expert);
+    } else {
+        k_moe_layout_expert<<<E, 1024, 0, s>>>(topk_idx, T * K, tokens_per_expert, send_idx);
+    }
     k_moe_layout_rank<<<(T + 255) / 256, 256, 0, s>>>(topk_idx, T, K, E / world, world, tokens_per_rank, is_token_in_rank);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : (int)e;
@@ -640,6 +877,25 @@ int mf_moe_notify(const Team *team, const MoeHeap *hp, int E, const int *tokens_
 int mf_moe_dispatch(const DispatchArgs *a, int ctas, void *stream)
 {
     if (a == nullptr || a->team.emu || a->sh.H % 128 != 0 || a->sh.H / 16 > 448 || a->sh.K > 16) return -1;
+    // fp8 rows whose scales make whole 16-byte units: every warp pushes whole tokens through the copy unit
+    static const bool warp_ok = [] {
+        const char *e = getenv("MF_MOE_DISPATCH_WARP");
+        return e == nullptr || atoi(e) != 0;
+    }();
+    const int smem = dw_smem_bytes(a->sh.H, a->sh.K);
+    if (warp_ok && !a->raw_bf16 && a->sh.H % 512 == 0 && smem <= 220 * 1024) {
+        static int attr_for = 0;
+        if (smem > attr_for) {
+            if (cudaFuncSetAttribute(k_moe_dispatch_warp, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+                (void)cudaGetLastError();
+                return -2;
+            }
+            attr_for = smem;
+        }
+        k_moe_dispatch_warp<<<ctas, kDwWarps * 32, smem, (cudaStream_t)stream>>>(*a);
+        cudaError_t e = cudaGetLastError();
+        return e == cudaSuccess ? 0 : (int)e;
+    }
     k_moe_dispatch<<<ctas, 448, 0, (cudaStream_t)stream>>>(*a);
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? 0 : (int)e;

@@ -91,7 +91,7 @@ def case_moe(args) -> None:
     combine push), slot reduce; checked against an fp32 reference of the same quantised computation."""
     from . import gemm
     from .heap import SymmetricHeap
-    T, H, I, E, K = args.tokens, 2048, 1024, 16, 4
+    T, H, I, E, K = (args.tokens, 7168, 2048, 32, 8) if getattr(args, "shape", "small") == "dsv3" else (args.tokens, 2048, 1024, 16, 4)
     heap, layer, x, idx, w = _moe_single(T, H, I, E, K)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     td, tf, tc = [], [], []

@@ -113,6 +113,7 @@ def main() -> int:
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--tokens", type=int, default=512)
     ap.add_argument("--size-mb", type=int, default=256)
+    ap.add_argument("--shape", default="small", choices=["small", "dsv3"], help="moe: 2048/1024/16 experts/top-4, or the DeepSeek-V3 layer")
     args, _ = ap.parse_known_args()
     fn = globals().get("case_" + args.case)
     if fn is None:
