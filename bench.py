@@ -82,6 +82,9 @@ def main() -> int:
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
+    # host staging buffers next to this rank's GPU: one process per GPU, each on the CPUs and memory of its GPU's NUMA node
+    from memfabric_hybrid_b200.utils import numa
+    numa_info = numa.bind_to_gpu(local) if os.environ.get("MF_NUMA_BIND", "1") != "0" else {"node": None}
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
@@ -227,7 +230,7 @@ def main() -> int:
                        "api": "memfabric_hybrid.bm.BigMemory.copy_data_batch = smem_bm_copy_batch (L2G, ASYNC_COPY_FLAG on a CUDA stream); "
                               "all 7808 triples are validated and marshalled by the library on every step",
                        "host_us_per_call": round(host_us_per_call, 1), "descriptors_per_call": n,
-                       "per_gpu_GBps": round(value / world, 2),
+                       "per_gpu_GBps": round(value / world, 2), "numa": numa_info,
                        "vs_baseline_note": "per-GPU rate / 138.01 GB/s (reference D2RD, one 1 GB transfer on Ascend A3)",
                        "scaling_note": "with 1 GPU the 'remote' slice is the GPU's own HBM (no NVLink); from 2 GPUs on every put crosses "
                                        "NVLink, where stores issued by SMs reach 709 GB/s per direction between two B200s and copy engines 772"},
