@@ -265,7 +265,13 @@ def moe(heap, world, rank, flush, skew: bool = True):
             y0 = layer.comm.combine(st0)
         yb = base_run()
         torch.cuda.synchronize()
-        verified = _all_ranks(_close(y0, yb, 0.08))
+        # fp8 against bf16 is a statistical comparison: the error over the whole output (Frobenius norm) must stay below
+        # 5 % and no single element may be off by more than 15 % of the largest value (e4m3 keeps 3 mantissa bits: single
+        # elements sit at 6-8 %); worst rank of both
+        d0 = (y0.float() - yb.float())
+        rel_err = bu.max_over_ranks(float(d0.abs().max() / yb.float().abs().max().clamp_min(1e-9)))
+        fro_err = bu.max_over_ranks(float(d0.norm() / yb.float().norm().clamp_min(1e-9)))
+        verified = bool(fro_err < 0.05 and rel_err < 0.15)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
         td, tf, tc = [], [], []
         for it in range(6):
@@ -336,7 +342,7 @@ def moe(heap, world, rank, flush, skew: bool = True):
         rows_max = int(bu.max_over_ranks(float(rows)))
         # floor of the dispatch: the fp8 rows + scales + origins that leave this GPU over the measured NVLink rate
         wire = rows * (world - 1) / max(world, 1) * (H + H // 128 * 4 + 16)
-        res[name] = {**extra, "verified": verified, "dispatch_us": round(med(td) * 1e3, 1), "expert_ffn_us": round(f_ms * 1e3, 1),
+        res[name] = {**extra, "verified": verified, "max_rel_err": round(rel_err, 4), "fro_rel_err": round(fro_err, 4), "dispatch_us": round(med(td) * 1e3, 1), "expert_ffn_us": round(f_ms * 1e3, 1),
                      "combine_us": round(med(tc) * 1e3, 1), "layer_us": round(total_ms * 1e3, 1), "recv_rows": rows, "recv_rows_max_rank": rows_max,
                      "ffn_tflops_fp8": round(flops / (f_ms * 1e-3) / 1e12, 1),
                      "ffn_frac_of_bf16_cublas_peak": round(flops / (f_ms * 1e-3) / 1e12 / _peaks()["bf16_tflops"], 3),
