@@ -420,8 +420,7 @@ template <int MODE, int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_g
                     }
                 }
             } else {
-                // rows leave through shared memory: lane = row on the way in, 4 lanes x 16 bytes per row on the way
-                // out, so that one store instruction writes 8 rows x 64 contiguous bytes
+                // rows leave through shared memory: lane = row on the way in, 16 lanes x 16 bytes per row on the way out
                 unsigned long long dst = 0;
                 float w = 1.f;
                 if (row_ok) {
@@ -439,24 +438,36 @@ template <int MODE, int EPI> __global__ void __launch_bounds__(kXThreads, 1) k_g
                         dst = reinterpret_cast<unsigned long long>(static_cast<__nv_bfloat16 *>(g.out) + (int64_t)row * g.ldo + nt * XBN + half * 128);
                     }
                 }
+                // Eight rows at a time: the lanes that own them write their whole 256-byte row segments (this warp's 128
+                // columns) into the staging buffer, then the warp stores them 2 rows x 256 contiguous bytes per instruction
+                // (16 lanes x 16 bytes per row). Over NVLink a write carries up to 256 bytes of payload: 64-byte pieces spent
+                // almost half of the link on packet overhead.
+                constexpr int kWideRowB = 272;  // 256 + 16: both the row writes and the 16-lanes-per-row reads stay conflict-free
+                static_assert(8 * kWideRowB <= 32 * kRowB, "staging buffer of an epilogue warp");
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
+                for (int p = 0; p < 4; p++) {
+                    if ((lane >> 3) == p) {
+                        uint8_t *mine = stg + (lane & 7) * kWideRowB;
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        uint4 pk;
-                        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+                        for (int c = 0; c < 4; c++) {
 #pragma unroll
-                        for (int e = 0; e < 4; e++)
-                            h[e] = __floats2bfloat162_rn(__uint_as_float(v[c][q * 8 + 2 * e]) * w, __uint_as_float(v[c][q * 8 + 2 * e + 1]) * w);
-                        *reinterpret_cast<uint4 *>(stg + lane * kRowB + q * 16) = pk;
+                            for (int q = 0; q < 4; q++) {
+                                uint4 pk;
+                                __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+                                for (int e = 0; e < 4; e++)
+                                    h[e] = __floats2bfloat162_rn(__uint_as_float(v[c][q * 8 + 2 * e]) * w, __uint_as_float(v[c][q * 8 + 2 * e + 1]) * w);
+                                *reinterpret_cast<uint4 *>(mine + c * 64 + q * 16) = pk;
+                            }
+                        }
                     }
                     __syncwarp();
 #pragma unroll
                     for (int it = 0; it < 4; it++) {
-                        const int r = it * 8 + (lane >> 2);
-                        const unsigned long long d = __shfl_sync(0xffffffffu, dst, r);
-                        const uint4 val = *reinterpret_cast<const uint4 *>(stg + r * kRowB + (lane & 3) * 16);
-                        if (d != 0) *reinterpret_cast<uint4 *>(d + (unsigned long long)(c * 64 + (lane & 3) * 16)) = val;
+                        const int r = it * 2 + (lane >> 4);
+                        const unsigned long long d = __shfl_sync(0xffffffffu, dst, p * 8 + r);
+                        const uint4 val = *reinterpret_cast<const uint4 *>(stg + r * kWideRowB + (lane & 15) * 16);
+                        if (d != 0) *reinterpret_cast<uint4 *>(d + (unsigned long long)((lane & 15) * 16)) = val;
                     }
                     __syncwarp();
                 }

@@ -265,13 +265,14 @@ def moe(heap, world, rank, flush, skew: bool = True):
             y0 = layer.comm.combine(st0)
         yb = base_run()
         torch.cuda.synchronize()
-        # fp8 against bf16 is a statistical comparison: the error over the whole output (Frobenius norm) must stay below
-        # 5 % and no single element may be off by more than 15 % of the largest value (e4m3 keeps 3 mantissa bits: single
-        # elements sit at 6-8 %); worst rank of both
+        # fp8 against bf16 is a statistical comparison. With random zero-mean data a dot product of e4m3 operands (3 mantissa
+        # bits each) is off by about 5 % of its own size whatever its length, two GEMMs in a row by 6-7 %: the error over the
+        # whole output (Frobenius norm) must stay below 10 % and no element may be off by more than 15 % of the largest
+        # value; worst rank of both. (The unit tests compare with an fp32 computation on the SAME quantised operands, to 1e-2.)
         d0 = (y0.float() - yb.float())
         rel_err = bu.max_over_ranks(float(d0.abs().max() / yb.float().abs().max().clamp_min(1e-9)))
         fro_err = bu.max_over_ranks(float(d0.norm() / yb.float().norm().clamp_min(1e-9)))
-        verified = bool(fro_err < 0.05 and rel_err < 0.15)
+        verified = bool(fro_err < 0.10 and rel_err < 0.15)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
         td, tf, tc = [], [], []
         for it in range(6):
