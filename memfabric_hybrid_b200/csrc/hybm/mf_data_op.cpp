@@ -44,7 +44,7 @@ int ComposeDataOp::EnsureRing()
 {
     if (ring_ != nullptr) return OK;
     if (dev_ == nullptr) return ERR_NOT_INIT;
-    uint64_t bytes = (uint64_t)EnvInt("MF_XCOPY_RING_MB", nullptr, 8, 1, 1024) << 20;
+    uint64_t bytes = (uint64_t)EnvInt("MF_XCOPY_RING_MB", nullptr, 32, 1, 1024) << 20;  // 1.4 M descriptors: a dozen of the largest batches between wraps
     void *p = nullptr;
     int rc = dev_->HostAlloc(bytes, &p);
     if (rc != OK) return MF_FAIL(rc, "cannot allocate the %lu-byte pinned descriptor ring", (unsigned long)bytes);
