@@ -400,8 +400,8 @@ __device__ __forceinline__ void dispatch_body(const DispatchArgs &a, uint4 nxt_l
 // buffer while the next row is quantised.
 constexpr int kDwWarps = 12;
 constexpr int kDwLoads = 14;  // independent 16-byte loads per lane in flight (256 elements per warp load)
-__host__ __device__ constexpr int dw_buf_bytes(int H, int K) { return H + (H / kQuantGroup) * 4 + 0 * K; }
-__host__ __device__ constexpr int dw_smem_bytes(int H, int K) { return kDwWarps * 2 * ((dw_buf_bytes(H, K) + 127) / 128 * 128); }
+__host__ __device__ constexpr int dw_buf_bytes(int H) { return (H + (H / kQuantGroup) * 4 + 127) / 128 * 128; }  // e4m3 row + its scales
+__host__ __device__ constexpr int dw_smem_bytes(int H) { return kDwWarps * 2 * dw_buf_bytes(H); }
 
 __device__ __forceinline__ void bulk_store(void *gdst, const void *ssrc, uint32_t bytes)
 {
@@ -417,7 +417,7 @@ __global__ void __launch_bounds__(kDwWarps * 32) k_moe_dispatch_warp(DispatchArg
     const int H = a.sh.H, K = a.sh.K, El = a.sh.E / (int)t.world;
     const int groups = H / kQuantGroup;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int stride_buf = (dw_buf_bytes(H, K) + 127) / 128 * 128;
+    const int stride_buf = dw_buf_bytes(H);
     uint8_t *bufs = dw_smem + (size_t)warp * 2 * stride_buf;
     const int wid = (int)blockIdx.x * kDwWarps + warp, wtotal = (int)gridDim.x * kDwWarps;
     const bool smoothed = a.smooth != nullptr;
@@ -882,7 +882,7 @@ int mf_moe_dispatch(const DispatchArgs *a, int ctas, void *stream)
         const char *e = getenv("MF_MOE_DISPATCH_WARP");
         return e == nullptr || atoi(e) != 0;
     }();
-    const int smem = dw_smem_bytes(a->sh.H, a->sh.K);
+    const int smem = dw_smem_bytes(a->sh.H);
     if (warp_ok && !a->raw_bf16 && a->sh.H % 512 == 0 && smem <= 220 * 1024) {
         static int attr_for = 0;
         if (smem > attr_for) {

@@ -187,38 +187,70 @@ void Endpoint::AcceptLoop()
         int fd = accept4(listenFd_, nullptr, nullptr, SOCK_CLOEXEC);
         if (fd < 0) continue;
         TuneSocket(fd);
-        std::unique_ptr<TlsSession> session;
-        if (opt_.tls) {
-            std::string why;
-            session = opt_.tls->Handshake(fd, true, 5000, why);
-            if (!session) {
-                MF_WARN("refused a connection: %s", why.c_str());
-                ::close(fd);
-                continue;
-            }
-        }
-        ConnReq req;
-        if (!(session ? session->ReadAll(&req, sizeof(req), 5000) : ReadAllTimed(fd, &req, sizeof(req), 5000))) {
-            session.reset();
-            ::close(fd);
+        if (!opt_.tls) {
+            Admit(fd);
             continue;
         }
-        ConnResp resp;
-        auto link = std::make_shared<Link>(fd, nextLinkId_.fetch_add(1), req.rankId, true);
-        link->tls_ = std::move(session);
-        link->lastSeenMs = NowMs();
-        if (req.magic != opt_.magic || req.version != opt_.version) {
-            resp.result = -1;
-        } else if (newLink_) {
-            resp.result = (int16_t)newLink_(req, link);
+        // TLS: the handshake (several round trips, up to 5 s for a slow or silent peer) runs beside the accept loop, so that
+        // one stalled client cannot hold up the others; at most kMaxHandshakes at a time
+        {
+            std::unique_lock<std::mutex> g(hsMu_);
+            if (handshakes_ >= kMaxHandshakes) {
+                g.unlock();
+                ::close(fd);
+                MF_WARN("refused a connection: %u TLS handshakes are already in progress", kMaxHandshakes);
+                continue;
+            }
+            handshakes_++;
         }
-        if (!link->WriteRaw(&resp, sizeof(resp)) || resp.result != 0) {
-            link->closed_ = true;
-            if (resp.result == 0 && broken_) broken_(link);  // admitted but the peer vanished
-            continue;  // link destructor closes fd
-        }
-        Attach(link);
+        std::thread([this, fd] {
+            pthread_setname_np(pthread_self(), "mf-rpc-tls");
+            Admit(fd);
+            std::lock_guard<std::mutex> g(hsMu_);
+            handshakes_--;
+            hsCv_.notify_all();
+        }).detach();
     }
+    // no admission thread may outlive the endpoint
+    std::unique_lock<std::mutex> g(hsMu_);
+    hsCv_.wait(g, [this] { return handshakes_ == 0; });
+}
+
+// Handshake (TLS when configured), admission request / reply, hand-over to a worker. Owns fd until a Link does.
+void Endpoint::Admit(int fd)
+{
+    std::unique_ptr<TlsSession> session;
+    if (opt_.tls) {
+        std::string why;
+        session = opt_.tls->Handshake(fd, true, 5000, why);
+        if (!session) {
+            MF_WARN("refused a connection: %s", why.c_str());
+            ::close(fd);
+            return;
+        }
+    }
+    ConnReq req;
+    if (!(session ? session->ReadAll(&req, sizeof(req), 5000) : ReadAllTimed(fd, &req, sizeof(req), 5000))) {
+        session.reset();
+        ::close(fd);
+        return;
+    }
+    ConnResp resp;
+    auto link = std::make_shared<Link>(fd, nextLinkId_.fetch_add(1), req.rankId, true);
+    link->tls_ = std::move(session);
+    link->lastSeenMs = NowMs();
+    if (!running_) return;  // the endpoint is stopping: the link's destructor closes the socket
+    if (req.magic != opt_.magic || req.version != opt_.version) {
+        resp.result = -1;
+    } else if (newLink_) {
+        resp.result = (int16_t)newLink_(req, link);
+    }
+    if (!link->WriteRaw(&resp, sizeof(resp)) || resp.result != 0) {
+        link->closed_ = true;
+        if (resp.result == 0 && broken_) broken_(link);  // admitted but the peer vanished
+        return;  // link destructor closes fd
+    }
+    Attach(link);
 }
 
 void Endpoint::Attach(const LinkPtr &l)

@@ -7,6 +7,7 @@
 // Parity: src/acc_links/include/acc_def.h:45-115, src/acc_links/include/acc_tcp_server.h:64-166,
 // src/acc_links/csrc/acc_tcp_listener.cpp:189-240, src/acc_links/csrc/acc_tcp_worker.cpp.
 #pragma once
+#include <condition_variable>
 #include <map>
 #include <unordered_map>
 
@@ -117,6 +118,7 @@ private:
     };
     void WorkerLoop(Worker *w);
     void AcceptLoop();
+    void Admit(int fd);
     void Attach(const LinkPtr &l);
     bool Drain(Worker *w, const LinkPtr &l);  // false => link finished
     void Drop(Worker *w, const LinkPtr &l);
@@ -127,6 +129,10 @@ private:
     BrokenFn broken_;
     std::vector<std::unique_ptr<Worker>> workers_;
     std::thread acceptor_;
+    static constexpr uint32_t kMaxHandshakes = 64;
+    std::mutex hsMu_;
+    std::condition_variable hsCv_;
+    uint32_t handshakes_ = 0;  // TLS admissions in flight (their threads are detached; the accept loop waits for them before it ends)
     int listenFd_ = -1;
     uint16_t listenPort_ = 0;
     std::atomic<bool> running_{false};

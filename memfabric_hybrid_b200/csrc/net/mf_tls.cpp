@@ -199,6 +199,14 @@ std::string Join(const std::string &dir, const std::string &name)
     return dir.back() == '/' ? dir + name : dir + "/" + name;
 }
 
+bool IsDir(const std::string &p)
+{
+    int fd = open(p.c_str(), O_RDONLY | O_DIRECTORY | O_CLOEXEC);
+    if (fd < 0) return false;
+    close(fd);
+    return true;
+}
+
 uint64_t NowMsMono()
 {
     struct timespec ts;
@@ -283,16 +291,7 @@ std::shared_ptr<TlsContext> TlsContext::Create(const TlsSettings &s, std::string
     }
     if (loaded == 0) {
         // one path: a PEM file, or a directory in OpenSSL's hashed layout
-        struct stat_like {
-            static bool IsDir(const std::string &p)
-            {
-                int fd = open(p.c_str(), O_RDONLY | O_DIRECTORY | O_CLOEXEC);
-                if (fd < 0) return false;
-                close(fd);
-                return true;
-            }
-        };
-        const bool dir = stat_like::IsDir(s.caPath);
+        const bool dir = IsDir(s.caPath);
         if (A.SSL_CTX_load_verify_locations(c->ctx_, dir ? nullptr : s.caPath.c_str(), dir ? s.caPath.c_str() : nullptr) != 1) {
             err = "cannot load CA from " + s.caPath + ": " + LastSslError();
             return nullptr;

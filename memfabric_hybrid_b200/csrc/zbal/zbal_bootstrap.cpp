@@ -223,7 +223,9 @@ int32_t zbal_heap_expand(uint64_t *segmentBase, uint64_t *segmentBytes)
         o = st.opts;
         out = st.out;
         first = st.shm;
-        id = 1 + (uint32_t)st.extraShm.size();
+        // object 0 is the first segment; expansions count down from the highest id, away from ids an application may use
+        if (st.extraShm.size() >= 32) return MF_FAIL(Z_NO_MEMORY, "the symmetric heap already has %zu expansion segments", st.extraShm.size());
+        id = 63u - (uint32_t)st.extraShm.size();
     }
     void *gva = nullptr;
     smem_shm_t shm = smem_shm_create(id, o.worldSize, o.rankId, o.deviceMemorySize, SMEMS_DATA_OP_MTE, 0, &gva);

@@ -128,6 +128,21 @@ def interleave_gate_up_fp8(w1q: torch.Tensor, tile: int | None = None) -> torch.
     return torch.stack([gate, up], dim=2).reshape(G, two_i, K).contiguous()
 
 
+_row_bounds_cache: dict = {}
+
+
+def _row_bounds(T: int, dev) -> torch.Tensor:
+    """[0, T] on the device (the one-group row offsets of ``dense_ffn_fp8``), made once per T: building it is a synchronous copy."""
+    key = (T, str(dev))
+    t = _row_bounds_cache.get(key)
+    if t is None:
+        if len(_row_bounds_cache) > 64:
+            _row_bounds_cache.clear()
+        t = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        _row_bounds_cache[key] = t
+    return t
+
+
 def dense_ffn_fp8(x: torch.Tensor, w1q: torch.Tensor, w1s: torch.Tensor, w2q: torch.Tensor, w2s: torch.Tensor,
                   smooth: torch.Tensor | None = None, sms: int | None = None) -> torch.Tensor:
     """One dense SwiGLU expert on every row of x (the shared expert of a DeepSeek-style layer):
@@ -146,7 +161,7 @@ def dense_ffn_fp8(x: torch.Tensor, w1q: torch.Tensor, w1s: torch.Tensor, w2q: to
     sms = sms or sm_count(dev)
     if smooth is not None:
         x = (x.float() * smooth.view(1, H)).to(torch.bfloat16)
-    rows = torch.tensor([0, T], dtype=torch.int32, device=dev)
+    rows = _row_bounds(T, dev)
     xq = torch.empty((T, H), dtype=torch.uint8, device=dev)
     xs = torch.empty((T, H // 128), dtype=torch.float32, device=dev)
     _ok(cu.mf_quant_rows_fp8(x.data_ptr(), H, rows[1:].data_ptr(), H, xq.data_ptr(), xs.data_ptr(), sms * 4, _s()), "quant_rows_fp8")

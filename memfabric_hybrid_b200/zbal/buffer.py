@@ -315,5 +315,6 @@ class Buffer:
         out = moe.combine(st)
         if shared is not None:
             torch.cuda.current_stream().wait_stream(self._side)
+            shared.record_stream(torch.cuda.current_stream())   # allocated under the side stream, last used on this one
             out.add_(shared)
         return out, st.recv_per_expert
