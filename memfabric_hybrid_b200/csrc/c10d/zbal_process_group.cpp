@@ -395,7 +395,8 @@ public:
     {
         TensorList both{output, input};
         const int n = getSize();
-        const uint64_t es = input.element_size(), nbytes = (uint64_t)input.numel() * es;
+        // the pieces land in the receiver's staging area: the larger of the two buffers sizes the call
+        const uint64_t es = input.element_size(), nbytes = (uint64_t)std::max(input.numel(), output.numel()) * es;
         bool ok = DtypeOf(input.scalar_type()) >= 0 && UseZbal("alltoall_base", both) && nbytes % 2 == 0 && input.dim() >= 1 &&
                   output.dim() >= 1 && (inSplits.empty() || (int)inSplits.size() == n) && (outSplits.empty() || (int)outSplits.size() == n);
         if (ok) ok = nbytes + 4096 <= StageBytes();

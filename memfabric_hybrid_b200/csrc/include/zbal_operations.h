@@ -38,9 +38,10 @@ int32_t zbal_reduce_scatter(const void *sendBuff, void *recvBuff, size_t recv_co
 int32_t zbal_all_gather(const void *sendBuff, void *recvBuff, size_t send_count, zbal_datatype_t dataType, zbal_comm_t comm,
                         zbal_stream_t stream);
 /* meta: DEVICE array [groupSize][4] of uint64 {send offset, send bytes, recv offset, recv bytes} for each
- * peer; send_bytes: size of the whole send buffer. (The reference passes cumulative sums and counts in
- * three device arrays; here one table carries the same information.) */
-int32_t zbal_all_to_all_v(const void *sendBuff, void *recvBuff, const uint64_t *meta, uint64_t send_bytes, zbal_comm_t comm,
+ * peer; buffer_bytes: size of the larger of the two buffers (the pieces land in the receiver's staging area, which must
+ * hold the whole receive buffer). (The reference passes cumulative sums and counts in three device arrays; here one
+ * table carries the same information.) */
+int32_t zbal_all_to_all_v(const void *sendBuff, void *recvBuff, const uint64_t *meta, uint64_t buffer_bytes, zbal_comm_t comm,
                           zbal_stream_t stream);
 int32_t zbal_broadcast(void *buf, uint64_t data_count, zbal_datatype_t dataType, uint16_t root, zbal_comm_t comm, zbal_stream_t stream);
 /* root's sendBuff holds groupSize * data_count elements; every member receives its data_count elements */

@@ -792,6 +792,11 @@ struct A2AArgs {
 };
 constexpr uint64_t kA2AHeader = 4096;
 
+// Push model: (1) every receiver tells every sender where in the RECEIVER's staging area its piece goes and how many bytes
+// it expects (two 8-byte words per pair, written into the sender's header); (2) the senders store their pieces straight
+// into the receivers' staging areas over NVLink (the piece for the rank itself goes from `in` to `out` directly); (3) every
+// rank copies what landed in its staging area to `out`. The data crosses memory once on the sending side (no local staging
+// copy), once over NVLink, and once more locally on the receiving side.
 __global__ void __launch_bounds__(512) k_alltoallv(A2AArgs a)
 {
     const Team &t = a.team;
@@ -802,28 +807,42 @@ __global__ void __launch_bounds__(512) k_alltoallv(A2AArgs a)
     const uint64_t *meta = reinterpret_cast<const uint64_t *>(a.meta + (uint64_t)me * a.meta_rank_stride);
     uint8_t *myA = peer_ptr(t, me, a.stage_a);
     cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    // (1) header of sender p, slot `me`: {offset of p's piece in my staging area, bytes I expect from p}
     if (blockIdx.x == 0 && threadIdx.x < world) {
-        uint64_t *hdr = reinterpret_cast<uint64_t *>(myA);
-        hdr[2 * threadIdx.x] = meta[4 * threadIdx.x];
-        hdr[2 * threadIdx.x + 1] = meta[4 * threadIdx.x + 1];
+        const uint32_t p = threadIdx.x;
+        uint64_t *hdr = reinterpret_cast<uint64_t *>(peer_ptr(t, p, a.stage_a));
+        hdr[2 * me] = meta[4 * p + 2];
+        hdr[2 * me + 1] = meta[4 * p + 3];
     }
-    const Range sub = cta_range<16>(a.in_bytes);
-    cta_raw_copy<uint8_t>(in, myA + kA2AHeader, sub.beg, sub.end);
-    // Lane b passing the handshake means lane b of every peer finished staging. A piece pulled below may
-    // have been staged by ANY lane of the peer, so all local lanes must have passed before anyone pulls:
-    // the grid-wide sync of this (cooperative) launch provides exactly that. A lane that timed out still
-    // joins the grid sync (leaving it would hang the others) and skips its pulls.
-    const bool ok = lane_sync(t, me, 0, a.epoch, 0x150);
+    // Lane 0's handshake carries the header stores (its CTA wrote them); the grid-wide sync of this cooperative launch hands
+    // what lane 0 acquired to the other CTAs. A lane that timed out still joins every grid sync (leaving would hang the
+    // others) and skips its copies.
+    bool ok = lane_sync(t, me, 0, a.epoch, 0x150);
+    grid.sync();
+    // (2) push
+    const uint64_t *hdr = reinterpret_cast<const uint64_t *>(myA);
+    if (ok) {
+        for (uint32_t k = 0; k < world; k++) {
+            const uint32_t r = (me + k) % world;
+            const uint64_t soff = meta[4 * r], scnt = meta[4 * r + 1];
+            const uint64_t roff = __ldcg(hdr + 2 * r), rcnt = __ldcg(hdr + 2 * r + 1);
+            const uint64_t bytes = min(scnt, rcnt);
+            const Range pr = cta_range<16>(bytes);
+            uint8_t *dst = r == me ? out + roff : peer_ptr(t, r, a.stage_a) + kA2AHeader + roff;
+            cta_raw_copy<uint8_t>(in + soff, dst, pr.beg, pr.end);
+        }
+    }
+    // Lane b passing the second handshake means lane b of every peer finished pushing; a piece copied out below may have
+    // been pushed by ANY lane of the peer, so all local lanes must have passed before anyone copies: the grid sync again.
+    ok = lane_sync(t, me, 1, a.epoch, 0x151) && ok;
     grid.sync();
     if (!ok) return;
-    for (uint32_t k = 0; k < world; k++) {
-        const uint32_t r = (me + k) % world;
-        const uint64_t *hdr = reinterpret_cast<const uint64_t *>(peer_ptr(t, r, a.stage_a));
-        const uint64_t soff = __ldcg(hdr + 2 * me), scnt = __ldcg(hdr + 2 * me + 1);
-        const uint64_t roff = meta[4 * r + 2], rcnt = meta[4 * r + 3];
-        const uint64_t bytes = min(scnt, rcnt);
-        const Range pr = cta_range<16>(bytes);
-        cta_raw_copy<uint8_t>(peer_ptr(t, r, a.stage_a) + kA2AHeader + soff, out + roff, pr.beg, pr.end);
+    // (3) staging area -> out
+    for (uint32_t k = 1; k < world; k++) {
+        const uint32_t p = (me + k) % world;
+        const uint64_t roff = meta[4 * p + 2], rcnt = meta[4 * p + 3];
+        const Range pr = cta_range<16>(rcnt);
+        cta_raw_copy<uint8_t>(myA + kA2AHeader + roff, out + roff, pr.beg, pr.end);
     }
 }
 

@@ -514,7 +514,7 @@ int32_t zbal_all_gather(const void *send, void *recv, size_t send_count, zbal_da
     return AllGatherBytes(*c, send, recv, (uint64_t)send_count * ti.size, stream);
 }
 
-int32_t zbal_all_to_all_v(const void *send, void *recv, const uint64_t *meta, uint64_t send_bytes, zbal_comm_t comm, zbal_stream_t stream)
+int32_t zbal_all_to_all_v(const void *send, void *recv, const uint64_t *meta, uint64_t buffer_bytes, zbal_comm_t comm, zbal_stream_t stream)
 {
     auto c = FindComm(comm);
     if (!c) return Z_INVALID_PARAM;
@@ -523,18 +523,18 @@ int32_t zbal_all_to_all_v(const void *send, void *recv, const uint64_t *meta, ui
     const Launchers *L = GetLaunchers();
     if (L == nullptr) return Z_NOT_SUPPORTED;
     std::lock_guard<std::mutex> g(c->mu);
-    if (send_bytes + 4096 > c->stageBytes)
-        return MF_FAIL(Z_NOT_SUPPORTED, "all_to_all_v: %lu bytes to send exceed the staging capacity of %lu", (unsigned long)send_bytes,
+    if (buffer_bytes + 4096 > c->stageBytes)
+        return MF_FAIL(Z_NOT_SUPPORTED, "all_to_all_v: buffers of %lu bytes exceed the staging capacity of %lu", (unsigned long)buffer_bytes,
                        (unsigned long)(c->stageBytes - 4096));
     MfA2AArgs a{};
     a.team = c->team;
     a.in = reinterpret_cast<uint64_t>(send);
     a.out = reinterpret_cast<uint64_t>(recv);
     a.meta = reinterpret_cast<uint64_t>(meta);
-    a.in_bytes = send_bytes;
+    a.in_bytes = buffer_bytes;
     uint64_t b;
     a.epoch = c->Next(a.stage_a, b);
-    return Launched(L->a2a(&a, std::min(c->Ctas(send_bytes), 64), 512, stream), "all_to_all_v");
+    return Launched(L->a2a(&a, c->Ctas(buffer_bytes), 512, stream), "all_to_all_v");
 }
 
 int32_t zbal_broadcast(void *buf, uint64_t count, zbal_datatype_t dt, uint16_t root, zbal_comm_t comm, zbal_stream_t stream)

@@ -160,6 +160,50 @@ def collectives(comm, world, flush, max_bytes=1 << 30):
     return out
 
 
+def alltoallv(heap, world, rank, flush):
+    """all-to-all-v of bf16 rows, 16 / 128 MiB of input per rank (the size of the reference's published All2Allv table), even
+    splits and splits skewed 3 : 1 towards the next rank, against torch.distributed all_to_all_single (NCCL) on the same splits.
+    Checked against NCCL's output before timing."""
+    from ..ops.collectives import Communicator
+    import torch.distributed as dist
+    out = []
+    if world < 2:
+        return out
+    mark = heap.mark()
+    comm = Communicator(heap, stage_bytes=(128 << 20) + (1 << 20))
+    for nbytes in (16 << 20, 128 << 20):
+        n = nbytes // 2
+        for skew in (False, True):
+            weights = [3.0 if (skew and p == (rank + 1) % world) else 1.0 for p in range(world)]
+            unit = 64   # elements: pieces stay 128-byte aligned
+            send = [int(n * w / sum(weights)) // unit * unit for w in weights]
+            # what every peer sends to me: the same rule seen from its side
+            recv = []
+            for p in range(world):
+                wp = [3.0 if (skew and q == (p + 1) % world) else 1.0 for q in range(world)]
+                recv.append(int(n * wp[rank] / sum(wp)) // unit * unit)
+            soff = [sum(send[:i]) for i in range(world)]
+            roff = [sum(recv[:i]) for i in range(world)]
+            x = torch.randn(sum(send), device="cuda").to(torch.bfloat16)
+            y = torch.empty(sum(recv), device="cuda", dtype=torch.bfloat16)
+            yn = torch.empty_like(y)
+            ours = lambda: comm.all_to_all_v(x, y, send, soff, recv, roff)
+            nccl = lambda: dist.all_to_all_single(yn, x, recv, send)
+            ours()
+            nccl()
+            torch.cuda.synchronize()
+            ok = _all_ranks(bool(torch.equal(y, yn)))
+            iters = 6
+            us = _timed(ours, iters, 2, flush) * 1e3
+            nus = _timed(nccl, iters, 2, flush) * 1e3
+            wire = 2 * max(sum(send) - send[rank], sum(recv) - recv[rank])
+            out.append({"op": "all_to_all_v_bf16", "bytes_in": sum(send) * 2, "skewed": skew, "verified": ok, "us": round(us, 1),
+                        "nccl_us": round(nus, 1), "vs_nccl": round(nus / us, 3), "roofline_frac": round(wire / NVLINK_GBS / 1e3 / us, 3)})
+            del x, y, yn
+    heap.release_to(mark)
+    return out
+
+
 def _moe_nccl_layer(layer, x, idx, w, world, rank):
     """The stock way to run the same layer: tokens sorted by destination rank, NCCL all_to_all_single of bf16 rows, the
     library's grouped GEMM (torch._grouped_mm on bf16 weights; a loop of cuBLAS matmuls where it is missing), SwiGLU,
@@ -569,6 +613,7 @@ def run(rank, world, local, _bm_handle):
     out["multicast_alias"] = bool(heap.mc_base)
     comm = Communicator(heap, stage_bytes=64 << 20)
     section("collectives", lambda: collectives(comm, world, flush))
+    section("alltoallv", lambda: alltoallv(heap, world, rank, flush))
     mark = heap.mark()
     section("tp_mlp", lambda: tp_mlp(heap, world, flush))
     heap.release_to(mark)

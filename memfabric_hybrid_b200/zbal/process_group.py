@@ -362,7 +362,7 @@ class ProcessGroupZBAL(dist.ProcessGroup):
         row_out = output[0].numel() if output.dim() > 1 else 1
         ins = list(input_split_sizes) if input_split_sizes else [input.shape[0] // self._size] * self._size
         outs = list(output_split_sizes) if output_split_sizes else [output.shape[0] // self._size] * self._size
-        nbytes = input.numel() * es
+        nbytes = max(input.numel(), output.numel()) * es   # the pieces land in the receiver's staging area
         stage = self._stage_bytes()
         if nbytes + 4096 > stage or nbytes % 2:
             return self._fallback(input).alltoall_base(output, input, output_split_sizes, input_split_sizes, opts)
