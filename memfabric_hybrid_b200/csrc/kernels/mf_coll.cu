@@ -793,10 +793,13 @@ struct A2AArgs {
 constexpr uint64_t kA2AHeader = 4096;
 
 // Push model: (1) every receiver tells every sender where in the RECEIVER's staging area its piece goes and how many bytes
-// it expects (two 8-byte words per pair, written into the sender's header); (2) the senders store their pieces straight
-// into the receivers' staging areas over NVLink (the piece for the rank itself goes from `in` to `out` directly); (3) every
-// rank copies what landed in its staging area to `out`. The data crosses memory once on the sending side (no local staging
-// copy), once over NVLink, and once more locally on the receiving side.
+// it expects (two 8-byte words per pair, written into the sender's header); (2) a rank stores its piece for rank me + k,
+// k = 1 .. W - 1, straight into that rank's staging area over NVLink and raises a per-(lane, sender) flag there after each;
+// (3) it then copies the pieces that arrived in its own staging area to `out`, in their order of arrival. CTA b of the sender and
+// CTA b of the receiver work on the same byte range of a piece, so one flag per lane and sender is all the ordering the
+// copy needs: no grid-wide sync between pushing and copying, and the local copies overlap the NVLink stores that are
+// still draining. The piece for the rank itself goes from `in` to `out` directly. The data crosses memory once on the
+// sending side (no local staging copy), once over NVLink, once more locally on the receiving side.
 __global__ void __launch_bounds__(512) k_alltoallv(A2AArgs a)
 {
     const Team &t = a.team;
@@ -807,6 +810,7 @@ __global__ void __launch_bounds__(512) k_alltoallv(A2AArgs a)
     const uint64_t *meta = reinterpret_cast<const uint64_t *>(a.meta + (uint64_t)me * a.meta_rank_stride);
     uint8_t *myA = peer_ptr(t, me, a.stage_a);
     cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    __shared__ int arrived_sh;
     // (1) header of sender p, slot `me`: {offset of p's piece in my staging area, bytes I expect from p}
     if (blockIdx.x == 0 && threadIdx.x < world) {
         const uint32_t p = threadIdx.x;
@@ -815,34 +819,42 @@ __global__ void __launch_bounds__(512) k_alltoallv(A2AArgs a)
         hdr[2 * me + 1] = meta[4 * p + 3];
     }
     // Lane 0's handshake carries the header stores (its CTA wrote them); the grid-wide sync of this cooperative launch hands
-    // what lane 0 acquired to the other CTAs. A lane that timed out still joins every grid sync (leaving would hang the
-    // others) and skips its copies.
-    bool ok = lane_sync(t, me, 0, a.epoch, 0x150);
-    grid.sync();
-    // (2) push
-    const uint64_t *hdr = reinterpret_cast<const uint64_t *>(myA);
-    if (ok) {
-        for (uint32_t k = 0; k < world; k++) {
-            const uint32_t r = (me + k) % world;
-            const uint64_t soff = meta[4 * r], scnt = meta[4 * r + 1];
-            const uint64_t roff = __ldcg(hdr + 2 * r), rcnt = __ldcg(hdr + 2 * r + 1);
-            const uint64_t bytes = min(scnt, rcnt);
-            const Range pr = cta_range<16>(bytes);
-            uint8_t *dst = r == me ? out + roff : peer_ptr(t, r, a.stage_a) + kA2AHeader + roff;
-            cta_raw_copy<uint8_t>(in + soff, dst, pr.beg, pr.end);
-        }
-    }
-    // Lane b passing the second handshake means lane b of every peer finished pushing; a piece copied out below may have
-    // been pushed by ANY lane of the peer, so all local lanes must have passed before anyone copies: the grid sync again.
-    ok = lane_sync(t, me, 1, a.epoch, 0x151) && ok;
+    // what lane 0 acquired to the other CTAs. A lane that timed out still joins the grid sync (leaving would hang the others).
+    const bool ok = lane_sync(t, me, 0, a.epoch, 0x150);
     grid.sync();
     if (!ok) return;
-    // (3) staging area -> out
-    for (uint32_t k = 1; k < world; k++) {
-        const uint32_t p = (me + k) % world;
-        const uint64_t roff = meta[4 * p + 2], rcnt = meta[4 * p + 3];
+    const uint64_t *hdr = reinterpret_cast<const uint64_t *>(myA);
+    const uint64_t flag_off = kLaneOff + (((uint64_t)1 * kMaxCtas + blockIdx.x) * kMaxRanks) * sizeof(uint32_t);  // phase 1 flags of this lane
+    // (2) all pieces leave first, nearest rank last (rank me + 1 copies my piece first: see the order of (3)). The byte range
+    // of this CTA is cut from the RECEIVER's count, so that the receiver's CTA of the same index finds exactly its range
+    // complete when the flag is up.
+    for (uint32_t k = 0; k < world; k++) {
+        const uint32_t r = (me + k) % world;
+        const uint64_t soff = meta[4 * r], scnt = meta[4 * r + 1];
+        const uint64_t roff = __ldcg(hdr + 2 * r), rcnt = __ldcg(hdr + 2 * r + 1);
         const Range pr = cta_range<16>(rcnt);
-        cta_raw_copy<uint8_t>(myA + kA2AHeader + roff, out + roff, pr.beg, pr.end);
+        const uint64_t end = min(pr.end, min(scnt, rcnt));
+        uint8_t *dst = r == me ? out + roff : peer_ptr(t, r, a.stage_a) + kA2AHeader + roff;
+        if (pr.beg < end) cta_raw_copy<uint8_t>(in + soff, dst, pr.beg, end);
+        if (k == 0) continue;
+        __syncthreads();  // every thread's stores of the piece are ordered before the signalling thread's release
+        if (threadIdx.x == 0) st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, flag_off)) + me, a.epoch);
+    }
+    // (3) the pieces pushed to me, in the order in which their senders sent them: rank me - 1 pushed to me first
+    for (uint32_t k = 1; k < world; k++) {
+        const uint32_t p = (me + world - k) % world;
+        if (threadIdx.x == 0) {
+            const uint32_t *f = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, flag_off)) + p;
+            arrived_sh = wait_flag(f, a.epoch, t.spin_limit) ? 1 : 0;
+            if (!arrived_sh) report_timeout(t, me, 0x151, a.epoch);
+        }
+        __syncthreads();
+        if (arrived_sh) {
+            const uint64_t poff = meta[4 * p + 2], pcnt = meta[4 * p + 3];
+            const Range cr = cta_range<16>(pcnt);
+            cta_raw_copy<uint8_t>(myA + kA2AHeader + poff, out + poff, cr.beg, cr.end);
+        }
+        __syncthreads();  // arrived_sh is rewritten in the next step
     }
 }
 
