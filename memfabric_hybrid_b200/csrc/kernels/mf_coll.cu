@@ -794,11 +794,10 @@ constexpr uint64_t kA2AHeader = 4096;
 
 // Push model: (1) every receiver tells every sender where in the RECEIVER's staging area its piece goes and how many bytes
 // it expects (two 8-byte words per pair, written into the sender's header); (2) a rank stores its piece for rank me + k,
-// k = 1 .. W - 1, straight into that rank's staging area over NVLink and raises a per-(lane, sender) flag there after each;
-// (3) it then copies the pieces that arrived in its own staging area to `out`, in their order of arrival. CTA b of the sender and
-// CTA b of the receiver work on the same byte range of a piece, so one flag per lane and sender is all the ordering the
-// copy needs: no grid-wide sync between pushing and copying, and the local copies overlap the NVLink stores that are
-// still draining. The piece for the rank itself goes from `in` to `out` directly. The data crosses memory once on the
+// k = 1 .. W - 1, straight into that rank's staging area over NVLink; (3) it then copies the pieces that arrived in its own
+// staging area to `out`. CTA b of the sender and CTA b of the receiver work on the same byte range of a piece, so with two
+// ranks one flag per lane and sender is all the ordering the copy needs; with more ranks one handshake follows all pushes
+// (see per_piece below). The piece for the rank itself goes from `in` to `out` directly. The data crosses memory once on the
 // sending side (no local staging copy), once over NVLink, once more locally on the receiving side.
 __global__ void __launch_bounds__(512) k_alltoallv(A2AArgs a)
 {
@@ -825,6 +824,11 @@ __global__ void __launch_bounds__(512) k_alltoallv(A2AArgs a)
     if (!ok) return;
     const uint64_t *hdr = reinterpret_cast<const uint64_t *>(myA);
     const uint64_t flag_off = kLaneOff + (((uint64_t)1 * kMaxCtas + blockIdx.x) * kMaxRanks) * sizeof(uint32_t);  // phase 1 flags of this lane
+    // How the receiver learns that a piece is complete. Two ranks: one flag per piece (measured 43 / 170 us for 16 / 128 MiB
+    // against 45 / 178 us). More ranks: every release has to wait until the CTA's earlier stores are performed at the
+    // peer, and one such drain per piece cost more than it saved (8 GPUs: 94 / 280 us against 66 / 272 us), so there the
+    // pieces are all pushed first and ONE handshake per lane plus a grid-wide sync follows.
+    const bool per_piece = world <= 2;
     // (2) all pieces leave first, nearest rank last (rank me + 1 copies my piece first: see the order of (3)). The byte range
     // of this CTA is cut from the RECEIVER's count, so that the receiver's CTA of the same index finds exactly its range
     // complete when the flag is up.
@@ -836,17 +840,27 @@ __global__ void __launch_bounds__(512) k_alltoallv(A2AArgs a)
         const uint64_t end = min(pr.end, min(scnt, rcnt));
         uint8_t *dst = r == me ? out + roff : peer_ptr(t, r, a.stage_a) + kA2AHeader + roff;
         if (pr.beg < end) cta_raw_copy<uint8_t>(in + soff, dst, pr.beg, end);
-        if (k == 0) continue;
+        if (k == 0 || !per_piece) continue;
         __syncthreads();  // every thread's stores of the piece are ordered before the signalling thread's release
         if (threadIdx.x == 0) st_release_sys(reinterpret_cast<uint32_t *>(peer_ptr(t, r, flag_off)) + me, a.epoch);
+    }
+    if (!per_piece) {
+        // Lane b passing this handshake means lane b of every peer finished pushing; the grid sync extends that to all lanes
+        // (a lane that timed out still joins it).
+        const bool landed = lane_sync(t, me, 1, a.epoch, 0x151);
+        grid.sync();
+        if (!landed) return;
     }
     // (3) the pieces pushed to me, in the order in which their senders sent them: rank me - 1 pushed to me first
     for (uint32_t k = 1; k < world; k++) {
         const uint32_t p = (me + world - k) % world;
         if (threadIdx.x == 0) {
-            const uint32_t *f = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, flag_off)) + p;
-            arrived_sh = wait_flag(f, a.epoch, t.spin_limit) ? 1 : 0;
-            if (!arrived_sh) report_timeout(t, me, 0x151, a.epoch);
+            arrived_sh = 1;
+            if (per_piece) {
+                const uint32_t *f = reinterpret_cast<const uint32_t *>(peer_ptr(t, me, flag_off)) + p;
+                arrived_sh = wait_flag(f, a.epoch, t.spin_limit) ? 1 : 0;
+                if (!arrived_sh) report_timeout(t, me, 0x151, a.epoch);
+            }
         }
         __syncthreads();
         if (arrived_sh) {
