@@ -7,8 +7,14 @@
 #include <time.h>
 #include <unistd.h>
 
+#include <pthread.h>
+
+#include <algorithm>
+#include <chrono>
+#include <climits>
 #include <fstream>
 #include <sstream>
+#include <thread>
 
 #include "../util/mf_util.h"
 
@@ -225,6 +231,27 @@ int EnvInt(const char *name, int lo, int hi, int dflt)
 }
 }  // namespace
 
+// ---- periodic certificate check: one detached thread per process, started with the first context -------------------
+std::mutex g_checkMu;
+std::vector<std::weak_ptr<TlsContext>> g_contexts;
+bool g_checkerStarted = false;
+
+void RegisterForChecks(const std::shared_ptr<TlsContext> &c)
+{
+    std::lock_guard<std::mutex> g(g_checkMu);
+    g_contexts.push_back(c);
+    if (g_checkerStarted) return;
+    g_checkerStarted = true;
+    std::thread([] {
+        pthread_setname_np(pthread_self(), "mf-tls-check");
+        for (;;) {
+            const int hours = EnvInt("MF_ACC_CHECK_PERIOD_HOURS", 24, 24 * 30, 7 * 24);
+            std::this_thread::sleep_for(std::chrono::hours(hours));
+            (void)TlsCheckAllNow();
+        }
+    }).detach();  // sleeps for days and touches only objects it keeps alive: it ends with the process
+}
+
 bool TlsSettings::Parse(const std::string &info, TlsSettings &out, std::string &err)
 {
     TlsSettings s;
@@ -319,6 +346,8 @@ std::shared_ptr<TlsContext> TlsContext::Create(const TlsSettings &s, std::string
         int days = 0, secs = 0;
         if (A.ASN1_TIME_diff(&days, &secs, nullptr, A.X509_get0_notAfter(cert)) == 1) {
             c->certDaysLeft_ = (days < 0 || secs < 0) ? -1 : days;
+            c->notAfterUnix_ = (int64_t)time(nullptr) + (int64_t)days * 86400 + secs;
+            c->certPath_ = s.certPath;
             const int ahead = EnvInt("MF_ACC_CERT_CHECK_AHEAD_DAYS", 7, 180, 30);
             if (c->certDaysLeft_ < 0) {
                 err = "certificate " + s.certPath + " has expired";
@@ -388,7 +417,43 @@ std::shared_ptr<TlsContext> TlsContext::Create(const TlsSettings &s, std::string
         return nullptr;
     }
     A.SSL_CTX_set_verify(c->ctx_, kVerifyPeer | kVerifyFailIfNoPeerCert, nullptr);
+    RegisterForChecks(c);
     return c;
+}
+
+int TlsContext::CheckExpiry()
+{
+    if (notAfterUnix_ == 0) return certDaysLeft_;
+    const int64_t left = notAfterUnix_ - (int64_t)time(nullptr);
+    certDaysLeft_ = left < 0 ? -1 : (int)(left / 86400);
+    const int ahead = EnvInt("MF_ACC_CERT_CHECK_AHEAD_DAYS", 7, 180, 30);
+    if (certDaysLeft_ < 0) {
+        MF_ERROR("TLS certificate %s has expired", certPath_.c_str());
+        Logger::Get().Alarm(0x7101, "TLS certificate expired");
+    } else if (certDaysLeft_ < ahead) {
+        MF_WARN("TLS certificate %s expires in %d days", certPath_.c_str(), certDaysLeft_);
+        Logger::Get().Alarm(0x7100, "TLS certificate close to expiry");
+    }
+    return certDaysLeft_;
+}
+
+int TlsCheckAllNow()
+{
+    int least = INT32_MAX;
+    std::vector<std::shared_ptr<TlsContext>> live;
+    {
+        std::lock_guard<std::mutex> g(g_checkMu);
+        for (auto it = g_contexts.begin(); it != g_contexts.end();) {
+            if (auto c = it->lock()) {
+                live.push_back(c);
+                ++it;
+            } else {
+                it = g_contexts.erase(it);
+            }
+        }
+    }
+    for (auto &c : live) least = std::min(least, c->CheckExpiry());
+    return least;
 }
 
 TlsContext::~TlsContext()

@@ -46,13 +46,19 @@ public:
     ~TlsContext();
     // Handshake over a connected socket (made non-blocking here). nullptr + err when it fails or runs out of time.
     std::unique_ptr<TlsSession> Handshake(int fd, bool asServer, uint32_t timeoutMs, std::string &err);
-    // Days until this end's certificate expires (negative: expired).
+    // Days until this end's certificate expires (negative: expired), as of the last check.
     int CertDaysLeft() const { return certDaysLeft_; }
+    // Re-computes the days left from the certificate's end date and warns (log + alarm hook) inside the warning window
+    // (MF_ACC_CERT_CHECK_AHEAD_DAYS, default 30) or after expiry. Run every MF_ACC_CHECK_PERIOD_HOURS (default 168) by a
+    // process-wide thread for every live context; tests call it directly. -> days left.
+    int CheckExpiry();
 
 private:
     TlsContext() = default;
     void *ctx_ = nullptr;  // SSL_CTX
     int certDaysLeft_ = 0;
+    int64_t notAfterUnix_ = 0;  // end of the certificate's validity, seconds since the epoch (0: unknown)
+    std::string certPath_;
     std::string keyPassPlain_;
     friend class TlsSession;
 };
@@ -82,6 +88,8 @@ private:
 
 // True when libssl / libcrypto could be opened and every entry point resolved (packagePath: see TlsSettings).
 bool TlsAvailable(const std::string &packagePath, std::string &err);
+// For tests: runs the periodic certificate check of every live context now; -> the smallest number of days left (INT_MAX: none).
+int TlsCheckAllNow();
 
 }  // namespace net
 }  // namespace mf

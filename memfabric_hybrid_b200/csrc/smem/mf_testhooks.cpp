@@ -6,6 +6,7 @@
 #include <memory>
 #include <thread>
 
+#include "../net/mf_tls.h"
 #include "../group/mf_group.h"
 #include "../store/mf_store.h"
 #include "../store/mf_store_backend.h"
@@ -290,6 +291,9 @@ const char *mf_t_trace_name(uint32_t id) { return TracePointName(id); }
 uint32_t mf_t_trace_count(void) { return TP_COUNT; }
 
 // ---- fault points -------------------------------------------------------------------------------------
+// Runs the periodic TLS certificate check now; -> the smallest number of days left over the live contexts.
+int mf_t_tls_check_now(void) { return mf::net::TlsCheckAllNow(); }
+
 void mf_t_fip_init(const char *confPath)
 {
     FaultPoints::Init(confPath ? confPath : "");

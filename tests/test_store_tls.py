@@ -102,6 +102,10 @@ def test_store_over_tls(pki, tls_off):
     try:
         a, b = H.Store.connect(port, rank=0), H.Store.connect(port, rank=1)
         assert a.set("k", b"over tls") == 0 and b.get("k") == b"over tls"
+        # the periodic certificate check, run by hand: the leaf certificates of this test are valid for 90 days
+        check = H.lib().mf_t_tls_check_now
+        check.restype = H.C.c_int
+        assert 85 <= check() <= 90
         big = os.urandom(3 << 20)   # several TLS records and more than one socket buffer
         assert a.set("big", big) == 0 and b.get("big", cap=4 << 20) == big
         assert b.add("n", 7) == 7
