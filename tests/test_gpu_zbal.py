@@ -411,6 +411,18 @@ def _moe_capi_scenario(rank, world, port, sync):
             ref[t] += w[t, k] * (a2 @ (torch.nn.functional.silu(h[:I]) * h[I:]))
     err = (out.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-6)
     assert err < 0.1, f"fused MoE differs from the fp32 reference: {err}"
+    # smooth-quant factors through the C entry point: with factors of 1 the result is bit-identical (the arithmetic of
+    # the factors themselves is checked against fp32 math in the Buffer test)
+    l.zbal_moe_set_smooth_scales.argtypes = [C.c_void_p, C.c_void_p]
+    l.zbal_moe_set_smooth_scales.restype = C.c_int32
+    ones = torch.ones(H, device="cuda")
+    K.check(l.zbal_moe_set_smooth_scales(moe, ones.data_ptr()), "smooth scales")
+    out1 = torch.empty_like(out)
+    K.check(l.zbal_fused_deep_moe(moe, x.data_ptr(), T, idx.data_ptr(), w.data_ptr(), w1q.data_ptr(), w1s.data_ptr(), w2q.data_ptr(), w2s.data_ptr(), I,
+                                  ws.data_ptr(), out1.data_ptr(), s), "fused with unit factors")
+    torch.cuda.synchronize()
+    assert torch.equal(out1, out)
+    K.check(l.zbal_moe_set_smooth_scales(moe, None), "smooth scales off")
     st = C.c_int32(-1)
     K.check(l.zbal_moe_get_status(moe, C.byref(st)), "status")
     K.check(l.zbal_moe_destroy(moe), "destroy")
