@@ -32,19 +32,60 @@ def kv_block_segments(n_blocks: int):
 
 
 class ClockSampler:
-    """Samples SM clock, power and throttle reasons with nvidia-smi every 200 ms on a thread."""
+    """Reads SM clock and throttle reasons of one GPU while a timed region runs (reads only: nothing is ever set).
+    NVML from a thread every 2 ms, so that a region of a few milliseconds still gets samples of its own; nvidia-smi every
+    200 ms where NVML cannot be loaded. ``stop()`` -> {"sm_mhz": median, "sm_max_mhz", "reasons": [...], "samples": n}."""
 
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # bits of nvmlDeviceGetCurrentClocksEventReasons (same values as the older ...ThrottleReasons call)
+    REASON_BITS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
 
     def __init__(self, gpu_index: int = 0):
         self.gpu = gpu_index
-        self.samples = []
+        self.samples = []          # nvidia-smi rows
+        self._sm, self._reasons, self._max = [], set(), None
         self._proc = None
         self._thread = None
+        self._stop = threading.Event()
+        self._nvml = None
+
+    def _nvml_handle(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            # LOCAL_RANK indexes the devices this process may see: honour CUDA_VISIBLE_DEVICES when it lists plain indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            ids = [v for v in vis.split(",") if v.strip().isdigit()]
+            phys = int(ids[self.gpu]) if self.gpu < len(ids) else self.gpu
+            h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self._max = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+            return h
+        except Exception:  # noqa: BLE001  (no NVML: fall back to nvidia-smi)
+            return None
+
+    def _poll_nvml(self, h):
+        nv = self._nvml
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self._stop.is_set():
+            try:
+                self._sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                bits = int(reasons_fn(h))
+                for name, bit in self.REASON_BITS.items():
+                    if bits & bit:
+                        self._reasons.add(name)
+            except Exception:  # noqa: BLE001
+                break
+            time.sleep(0.002)
 
     def start(self):
+        h = self._nvml_handle()
+        if h is not None:
+            self._thread = threading.Thread(target=self._poll_nvml, args=(h,), daemon=True)
+            self._thread.start()
+            return self
         try:
             self._proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
@@ -63,6 +104,13 @@ class ClockSampler:
                 self.samples.append(parts)
 
     def stop(self) -> dict:
+        if self._nvml is not None:
+            self._stop.set()
+            if self._thread is not None:
+                self._thread.join(timeout=1)
+            sm = self._sm
+            return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": self._max, "reasons": sorted(self._reasons),
+                    "samples": len(sm), "source": "nvml, 2 ms"}
         if self._proc is not None:
             time.sleep(0.25)
             self._proc.terminate()
@@ -82,7 +130,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": "nvidia-smi, 200 ms"}
 
 
 def max_over_ranks(value: float) -> float:
