@@ -301,6 +301,24 @@ class MoEComm:
         _ok(_cu().mf_moe_wait_all(C.byref(team), C.byref(self.hp), 0, self._epoch, status_word(self.dev).data_ptr(), _s()), "moe_wait")
         return DispatchState(T, idx, sidx, tpe, tpr, inr, rpe, row_off, put_off, src_off, self._epoch)
 
+    def dispatch_cached(self, x: torch.Tensor, st: DispatchState, topk_w: torch.Tensor) -> DispatchState:
+        """Pushes another tensor along the routing of an earlier ``dispatch`` (same top-k table, same positions in the
+        receivers' buffers): no layout pass and no count exchange. Every rank must make the same call. -> a state for
+        ``expert_ffn`` / ``combine`` that shares the first call's tables."""
+        assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape == (st.T, self.H)
+        import dataclasses
+        self._epoch += 1
+        self._dispatches += 1
+        team = self.heap.team()
+        w = topk_w.to(torch.float32).contiguous()   # the weights travel with the rows again
+        a = DispatchArgsC(team, self.hp, self._shape(st.T), x.data_ptr(), st.topk_idx.data_ptr(), w.data_ptr(), st.send_idx.data_ptr(),
+                          st.put_off.data_ptr(), self._done.data_ptr(), self._epoch, self._dispatches, status_word(self.dev).data_ptr(),
+                          1 if self.raw_bf16 else 0, None)
+        self._keep = (w, st.topk_idx, None)
+        _ok(_cu().mf_moe_dispatch(C.byref(a), self._grid, _s()), "moe_dispatch")
+        _ok(_cu().mf_moe_wait_all(C.byref(team), C.byref(self.hp), 0, self._epoch, status_word(self.dev).data_ptr(), _s()), "moe_wait")
+        return dataclasses.replace(st, epoch=self._epoch)
+
     def expert_ffn(self, st: DispatchState, w1q: torch.Tensor, w1s: torch.Tensor, w2q: torch.Tensor, w2s: torch.Tensor) -> None:
         """w1q [El, 2I, H] fp8 tile-interleaved (interleave_gate_up_fp8), w1s [El, 2I/128, H/128] in ORIGINAL row order;
         w2q [El, H, I] fp8, w2s [El, H/128, I/128]. The result rows are pushed, weighted, to the tokens' home ranks."""

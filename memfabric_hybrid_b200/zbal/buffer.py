@@ -77,6 +77,17 @@ class _CommHeap(_HeapBase):
         torch.cuda.synchronize()
 
 
+def pack_ue8m0(scales: torch.Tensor) -> torch.Tensor:
+    """Power-of-two fp32 scales [rows, groups] -> their exponent bytes (UE8M0), four per int32: [rows, ceil(groups / 4)] int32,
+    byte j of word w = exponent of group 4 w + j."""
+    rows, groups = scales.shape
+    e = ((scales.contiguous().view(torch.int32) >> 23) & 0xFF).to(torch.uint8)
+    pad = (-groups) % 4
+    if pad:
+        e = torch.nn.functional.pad(e, (0, pad))
+    return e.contiguous().view(torch.int32)
+
+
 class Buffer:
     num_sms: int = 148
 
@@ -179,14 +190,23 @@ class Buffer:
         """-> (recv_x or (recv_x_fp8, recv_scales), recv_expert_idx [rows] int64, recv_weights [rows] fp32,
                num_recv_tokens_per_expert_list, handle, event). Rows are grouped by local expert."""
         if isinstance(x, tuple):
-            raise NotImplementedError("pre-quantised input is not supported: pass bf16 and let the push kernel quantise")
-        if handle is not None:
-            raise NotImplementedError("cached-layout dispatch is not supported")
-        if topk_idx is None or topk_weights is None:
-            raise ValueError("topk_idx and topk_weights must be given")
+            # pre-quantised rows (e4m3 + one scale per 128 elements): turned back into bf16, which is exact for e4m3 values
+            # times a power-of-two scale, and quantised again by the push kernel (the same values come out when the scales
+            # follow this library's rule: the smallest power of two that brings the group's largest value under 448)
+            xq, xs = x
+            T0, H0 = xq.shape
+            x = (xq.view(torch.float8_e4m3fn).float().view(T0, H0 // 128, 128) * xs.float().view(T0, H0 // 128, 1)).view(T0, H0).to(torch.bfloat16)
         self._before(previous_event)
         moe = self._moe
-        st = moe.dispatch(x, topk_idx, topk_weights)
+        if handle is not None:
+            # cached layout: the routing of an earlier dispatch is reused for another tensor (DeepEP's handle argument);
+            # no layout, no count exchange, the rows land where the first call's rows landed
+            st = moe.dispatch_cached(x, handle[4], handle[2])
+            topk_weights = handle[2]
+        else:
+            if topk_idx is None or topk_weights is None:
+                raise ValueError("topk_idx and topk_weights must be given")
+            st = moe.dispatch(x, topk_idx, topk_weights)
         self._state = st
         El = moe.El
         if num_worst_tokens > 0:
@@ -212,12 +232,14 @@ class Buffer:
         weights that travelled with them and summed per token on the token's home rank (the reference's combine
         does the same weighted sum, ops/dispatch_combine_normal/zbal_kernel_combine_normal.h:180-606).
         -> (combined_x [T, hidden] bf16, None, event)"""
-        if bias is not None:
-            raise NotImplementedError("bias is not supported")
         self._before(previous_event)
         st: DispatchState = handle[4]
         self._moe.combine_push(x, st, weighted=True)
         out = self._moe.combine(st)
+        if bias is not None:   # one tensor or a pair, [T, hidden], added to the combined rows (DeepEP's bias argument)
+            for b in (bias if isinstance(bias, (tuple, list)) else (bias,)):
+                if b is not None:
+                    out.add_(b.to(out.dtype))
         return out, None, self._after(async_finish)
 
     # ------------------------------------------------------------------ low-latency mode
@@ -234,8 +256,8 @@ class Buffer:
         given here (they travel with the rows) or later to ``low_latency_combine``."""
         assert num_experts == self.num_experts and x.shape[0] <= min(num_max_dispatch_tokens_per_rank, self.num_max_tokens)
         assert use_fp8 == self.use_fp8, "the row format is fixed when the Buffer is built"
-        if round_scale or use_ue8m0:
-            raise NotImplementedError("power-of-two scales are not supported")
+        # round_scale: the scales of this library are always powers of two, nothing to switch. use_ue8m0: they are handed
+        # out as their exponent bytes, four per int32 along the last dimension (DeepEP's packed form)
         moe = self._moe
         w = topk_weights if topk_weights is not None else torch.ones(topk_idx.shape, dtype=torch.float32, device=x.device)
         st = moe.ll_dispatch(x, topk_idx, w)
@@ -243,6 +265,8 @@ class Buffer:
         if cumulative_local_expert_recv_stats is not None:
             cumulative_local_expert_recv_stats.add_(st.recv_per_expert)
         recv_x = (moe.recv_x(), moe.recv_scale()) if self.use_fp8 else moe.recv_x()
+        if use_ue8m0 and self.use_fp8:
+            recv_x = (recv_x[0], pack_ue8m0(recv_x[1]))
         handle = (st, st.row_off, num_max_dispatch_tokens_per_rank, self.hidden, num_experts, topk_weights is not None)
         hook: Callable = (lambda: None)
         return recv_x, st.recv_per_expert, handle, self._after(async_finish), hook

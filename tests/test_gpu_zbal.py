@@ -248,6 +248,30 @@ def _buffer_scenario(rank, world, port, sync):
         out, _, _ = buf.combine(rx.to(torch.bfloat16), handle)
         torch.testing.assert_close(out.float(), expect, rtol=0.06, atol=0.06)
 
+        # cached layout: a second tensor along the same routing (no layout pass), and a bias pair added by combine
+        snap = (recv[0][:rows].clone(), recv[1][:rows].clone()) if use_fp8 else None   # the receive buffers are reused below
+        x2 = (x.float() * 0.5).to(torch.bfloat16)
+        recv2, recv_e2, _, _, handle2, _ = buf.dispatch(x2, handle=handle)
+        assert torch.equal(recv_e2, recv_e)
+        rx2 = (recv2[0][:rows].float().view(rows, H // 128, 128) * recv2[1][:rows].view(rows, H // 128, 1)).view(rows, H) if use_fp8 else recv2[:rows].float()
+        bias = torch.full((T, H), 0.25, device="cuda", dtype=torch.bfloat16)
+        out2, _, _ = buf.combine(rx2.to(torch.bfloat16), handle2, bias=(bias, bias))
+        torch.testing.assert_close(out2.float(), expect * 0.5 + 0.5, rtol=0.06, atol=0.06)
+        if use_fp8:
+            # pre-quantised input (e4m3 rows + one power-of-two scale per 128 elements, made by the library's row quantiser):
+            # the receivers get the same values as from the bf16 rows
+            from memfabric_hybrid_b200.ops import moe as M
+            xq = torch.empty((T, H), dtype=torch.uint8, device="cuda")
+            xs = torch.empty((T, H // 128), dtype=torch.float32, device="cuda")
+            nrows = torch.tensor([T], dtype=torch.int32, device="cuda")
+            assert M._cu().mf_quant_rows_fp8(x.data_ptr(), H, nrows.data_ptr(), H, xq.data_ptr(), xs.data_ptr(), 64,
+                                             torch.cuda.current_stream().cuda_stream) == 0
+            first_q, first_s = snap
+            again, _, _, _, _, _ = buf.dispatch((xq.view(torch.float8_e4m3fn), xs), topk_idx=idx, topk_weights=w)
+            # same VALUES (a group whose largest value rounded down to 224 is re-quantised with half the scale and doubled bytes)
+            deq = lambda q, sc: q.float().view(rows, H // 128, 128) * sc.view(rows, H // 128, 1)
+            assert torch.equal(deq(again[0][:rows], again[1][:rows]), deq(first_q, first_s))
+
         # low-latency pair, weights travelling with the rows and weights applied at home
         (lrecv, lcount, lh, _, _) = buf.low_latency_dispatch(x, idx, 128, E, use_fp8=use_fp8, topk_weights=w)
         n = int(lh[1][-1])
@@ -259,6 +283,14 @@ def _buffer_scenario(rank, world, port, sync):
             ly = lrecv[:n].clone()
         lout, _, _ = buf.low_latency_combine(ly, idx, w, lh)
         torch.testing.assert_close(lout.float(), expect, rtol=0.06, atol=0.06)
+        if use_fp8:
+            # scales as exponent bytes (UE8M0), four per int32
+            (pk, _, ph, _, _) = buf.low_latency_dispatch(x, idx, 128, E, use_fp8=True, round_scale=True, use_ue8m0=True)
+            n8 = int(ph[1][-1])
+            words = pk[1][:n8]
+            assert words.dtype == torch.int32 and words.shape[1] == (H // 128 + 3) // 4
+            expo = words.contiguous().view(torch.uint8)[:, :H // 128].to(torch.int32)
+            torch.testing.assert_close(torch.exp2((expo - 127).float()), buf._moe.recv_scale()[:n8], rtol=0, atol=0)
         (lrecv, lcount, lh, _, _) = buf.low_latency_dispatch(x, idx, 128, E, use_fp8=use_fp8)
         n = int(lh[1][-1])
         if use_fp8:
