@@ -45,10 +45,11 @@ def _ranks(rank, world, url, T, H, F, fused1, sync):
     return worst, st
 
 
-@pytest.mark.parametrize("fused1", [True, False], ids=["fused_kernels", "plain_gemm"])
-def test_tp_mlp_world1(fused1):
+@pytest.mark.parametrize("fused1,T", [(True, 512), (True, 384), (False, 512)], ids=["fused_cta_pairs", "fused_single_ctas", "plain_gemm"])
+def test_tp_mlp_world1(fused1, T):
+    """512 rows: whole 256-row tiles, the fused kernels run on CTA pairs; 384 rows: they fall back to one CTA per tile."""
     url = f"127.0.0.1:{free_port()}"
-    (worst, st), = run_ranks(_ranks, 1, (url, 512, 512, 1024, fused1), timeout=300, with_barrier=True)
+    (worst, st), = run_ranks(_ranks, 1, (url, T, 512, 1024, fused1), timeout=300, with_barrier=True)
     assert st == 0 and worst < 3e-2, (worst, st)
 
 
@@ -57,6 +58,11 @@ def test_tp_mlp_multi_gpu():
     n = 2 if torch.cuda.device_count() < 4 else 4
     url = f"127.0.0.1:{free_port()}"
     res = run_ranks(_ranks, n, (url, 1024, 512, 2048, True), timeout=300, with_barrier=True)
+    for worst, st in res:
+        assert st == 0 and worst < 3e-2, res
+    # shards of 384 rows are not whole 256-row tiles: the one-CTA tiling of the fused kernels
+    url = f"127.0.0.1:{free_port()}"
+    res = run_ranks(_ranks, n, (url, 384 * n, 512, 2048, True), timeout=300, with_barrier=True)
     for worst, st in res:
         assert st == 0 and worst < 3e-2, res
 
