@@ -48,3 +48,17 @@ def test_transfer_perf_fork_mode(tools):
     assert out.returncode == 0, out.stdout + out.stderr
     lines = [l for l in out.stdout.splitlines() if l.startswith("Test completed")]
     assert len(lines) == 3 and all("verified yes" in l for l in lines), out.stdout
+
+
+def test_transfer_performance_python_tool():
+    """The Python twin (benchmark/transfer/transfer_performance.py): both ranks from one command, host buffers."""
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    e = _env()
+    e["MF_DEVICE_BACKEND"] = "none"
+    out = subprocess.run([sys.executable, os.path.join(root, "benchmark", "transfer", "transfer_performance.py"), "--both",
+                          "--store-url", f"tcp://127.0.0.1:{free_port()}", "--max-block-kb", "64", "--num-threads", "2"],
+                         capture_output=True, text=True, timeout=180, env=e)
+    assert out.returncode == 0, out.stdout + out.stderr
+    lines = [l for l in out.stdout.splitlines() if l.startswith("Test completed")]
+    assert len(lines) == 2 and all("verified yes" in l for l in lines), out.stdout
