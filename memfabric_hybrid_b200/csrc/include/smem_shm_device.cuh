@@ -99,5 +99,72 @@ __device__ __forceinline__ bool smem_shm_wait(const smem_shm_device_ctx_t &c, ui
     mfk::report_timeout(smem_shm_team(c), c.rank, 0x2000 | channel, epoch);
     return false;
 }
+
+/* ---- data movement helpers (the reference's smem_shm_copy_ub2gm / gm2ub and smem_shm_roce_write / read) -------------
+ * "ub" is the on-chip buffer of the calling block: shared memory here. The global side may be any address of any rank's
+ * slice (smem_shm_peer_ptr / smem_shm_slice_ptr): stores and loads to a peer travel over NVLink. All threads of the CTA
+ * call these together; 16-byte vectors when both addresses allow it, bytes otherwise. The calls return when the calling
+ * thread's part is issued: put a __syncthreads() (and, before telling a peer, smem_shm_signal, whose release covers the
+ * CTA's stores after a barrier) behind them as with any other store. */
+template <typename T> __device__ __forceinline__ void smem_shm_copy_ub2gm(T *dst_gva, const T *src_smem, uint32_t bytes)
+{
+    const uint8_t *s = reinterpret_cast<const uint8_t *>(src_smem);
+    uint8_t *d = reinterpret_cast<uint8_t *>(dst_gva);
+    uint32_t done = 0;
+    if (((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d)) & 15) == 0) {
+        const uint32_t vecs = bytes / 16;
+        for (uint32_t i = threadIdx.x; i < vecs; i += blockDim.x) reinterpret_cast<uint4 *>(d)[i] = reinterpret_cast<const uint4 *>(s)[i];
+        done = vecs * 16;
+    }
+    for (uint32_t i = done + threadIdx.x; i < bytes; i += blockDim.x) d[i] = s[i];
+}
+template <typename T> __device__ __forceinline__ void smem_shm_copy_gm2ub(T *dst_smem, const T *src_gva, uint32_t bytes)
+{
+    const uint8_t *s = reinterpret_cast<const uint8_t *>(src_gva);
+    uint8_t *d = reinterpret_cast<uint8_t *>(dst_smem);
+    uint32_t done = 0;
+    if (((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d)) & 15) == 0) {
+        const uint32_t vecs = bytes / 16;
+        for (uint32_t i = threadIdx.x; i < vecs; i += blockDim.x)
+            reinterpret_cast<uint4 *>(d)[i] = __ldcg(reinterpret_cast<const uint4 *>(s) + i);  // a peer may have just written it: not through L1
+        done = vecs * 16;
+    }
+    for (uint32_t i = done + threadIdx.x; i < bytes; i += blockDim.x) d[i] = *reinterpret_cast<const volatile uint8_t *>(s + i);
+}
+/* Remote write / read between this rank's memory and rank `peer`'s slice: `remote` is the address the object has in THIS
+ * rank's slice (the symmetric address), as with smem_shm_peer_ptr. The whole grid shares the range: CTA b moves its part.
+ * No queue pairs and no work requests on this hardware: the SMs store (load) through NVLink directly. */
+template <typename T> __device__ __forceinline__ void smem_shm_roce_write(const smem_shm_device_ctx_t &c, const T *local_src, T *remote, uint32_t peer,
+                                                                         uint64_t bytes)
+{
+    const uint8_t *s = reinterpret_cast<const uint8_t *>(local_src);
+    uint8_t *d = reinterpret_cast<uint8_t *>(smem_shm_peer_ptr(c, remote, peer));
+    const uint64_t per = ((bytes + gridDim.x - 1) / gridDim.x + 15) / 16 * 16;
+    const uint64_t beg = min(bytes, (uint64_t)blockIdx.x * per), end = min(bytes, beg + per);
+    uint64_t i = beg;
+    if (((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d)) & 15) == 0) {
+        const uint64_t vend = beg + (end - beg) / 16 * 16;
+        for (i = beg + (uint64_t)threadIdx.x * 16; i < vend; i += (uint64_t)blockDim.x * 16)
+            *reinterpret_cast<uint4 *>(d + i) = __ldg(reinterpret_cast<const uint4 *>(s + i));
+        i = vend;
+    }
+    for (i += threadIdx.x; i < end; i += blockDim.x) d[i] = s[i];
+}
+template <typename T> __device__ __forceinline__ void smem_shm_roce_read(const smem_shm_device_ctx_t &c, const T *remote, T *local_dst, uint32_t peer,
+                                                                        uint64_t bytes)
+{
+    const uint8_t *s = reinterpret_cast<const uint8_t *>(smem_shm_peer_ptr(c, const_cast<T *>(remote), peer));
+    uint8_t *d = reinterpret_cast<uint8_t *>(local_dst);
+    const uint64_t per = ((bytes + gridDim.x - 1) / gridDim.x + 15) / 16 * 16;
+    const uint64_t beg = min(bytes, (uint64_t)blockIdx.x * per), end = min(bytes, beg + per);
+    uint64_t i = beg;
+    if (((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(d)) & 15) == 0) {
+        const uint64_t vend = beg + (end - beg) / 16 * 16;
+        for (i = beg + (uint64_t)threadIdx.x * 16; i < vend; i += (uint64_t)blockDim.x * 16)
+            *reinterpret_cast<uint4 *>(d + i) = __ldcg(reinterpret_cast<const uint4 *>(s + i));
+        i = vend;
+    }
+    for (i += threadIdx.x; i < end; i += blockDim.x) d[i] = *reinterpret_cast<const volatile uint8_t *>(s + i);
+}
 #endif /* __CUDACC__ */
 #endif

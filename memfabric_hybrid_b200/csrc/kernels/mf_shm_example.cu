@@ -110,6 +110,42 @@ __global__ void k_example_read_context(smem_shm_device_ctx_t ctx, uint8_t *out, 
 }
 }  // namespace
 
+namespace {
+// A round trip through every data-movement helper of the device header: `src` goes to rank `peer`'s copy of `box` with
+// smem_shm_roce_write, comes back into `back` with smem_shm_roce_read, and CTA 0 takes the first `tile` bytes of the peer's
+// box through shared memory (gm2ub, then ub2gm into `via_smem`). A barrier between the steps makes the peer's box complete.
+__global__ void k_example_copy_helpers(smem_shm_device_ctx_t ctx, const uint8_t *src, uint8_t *box, uint8_t *back, uint8_t *via_smem, uint64_t bytes,
+                                       uint32_t tile, uint32_t peer, int *ok)
+{
+    extern __shared__ __align__(16) uint8_t ub[];
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    smem_shm_roce_write(ctx, src, box, peer, bytes);
+    __threadfence_system();
+    grid.sync();
+    smem_shm_roce_read(ctx, box, back, peer, bytes);
+    if (blockIdx.x == 0) {
+        smem_shm_copy_gm2ub(ub, smem_shm_peer_ptr(ctx, box, peer), tile);
+        __syncthreads();
+        smem_shm_copy_ub2gm(via_smem, ub, tile);
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) *ok = 1;
+}
+}  // namespace
+
+// Runs the helper round trip above on one rank (peer may be the rank itself). Cooperative launch of `ctas` blocks.
+extern "C" int mf_example_shm_copy_helpers(const smem_shm_device_ctx_t *ctx, const void *src, void *box, void *back, void *via_smem, uint64_t bytes,
+                                           uint32_t tile, uint32_t peer, int *ok, int ctas, void *stream)
+{
+    if (ctx == nullptr || src == nullptr || box == nullptr || back == nullptr || via_smem == nullptr || tile > 48 * 1024 || peer >= ctx->rank_size) return -1;
+    smem_shm_device_ctx_t c = *ctx;
+    const uint8_t *s = static_cast<const uint8_t *>(src);
+    uint8_t *b = static_cast<uint8_t *>(box), *k = static_cast<uint8_t *>(back), *v = static_cast<uint8_t *>(via_smem);
+    void *params[] = {&c, &s, &b, &k, &v, &bytes, &tile, &peer, &ok};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(k_example_copy_helpers), dim3((unsigned)ctas), dim3(256), params, tile,
+                                                (cudaStream_t)stream);
+    return e == cudaSuccess ? 0 : (int)e;
+}
+
 // Copies this rank's extra context (smem_shm_set_extra_context) as a kernel sees it into out[0 .. cap) and its size into
 // *size_out (both device memory).
 extern "C" int mf_example_shm_read_context(const smem_shm_device_ctx_t *ctx, void *out, uint32_t cap, uint32_t *size_out, void *stream)
