@@ -3,7 +3,7 @@
 its Python bindings) from a copy under /tmp and lays its Python package out under baseline/_ref/memfabric_hybrid, the way
 the reference's own wheel does (package sources + the two extension modules + lib/*.so).
 
-    python baseline/build_reference.py [path of the reference tree, default /root/reference]
+    python baseline/build_reference.py [path of the reference tree; default: $MF_REFERENCE_TREE, else the tree beside this repository]
 
 `pip install <reference>` does not work (the tree has no setup.py / pyproject.toml at its root); the CMake build needs no
 network with these options. Returns 0 when baseline/_ref is usable afterwards.
@@ -24,7 +24,10 @@ def usable() -> bool:
     return (DEST / "__init__.py").is_file() and (DEST / ("_pymf_hybrid" + tag)).is_file() and (DEST / "lib" / "libmf_smem.so").is_file()
 
 
-def build(ref: str = "/root/reference", jobs: int | None = None, log=None) -> bool:
+DEFAULT_REF = os.environ.get("MF_REFERENCE_TREE") or str(Path(__file__).resolve().parents[2] / "reference")
+
+
+def build(ref: str = DEFAULT_REF, jobs: int | None = None, log=None) -> bool:
     if usable():
         return True
     ref_path = Path(ref)
@@ -58,6 +61,6 @@ def build(ref: str = "/root/reference", jobs: int | None = None, log=None) -> bo
 
 
 if __name__ == "__main__":
-    ok = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", log=str(HERE / "_ref_build.log"))
+    ok = build(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REF, log=str(HERE / "_ref_build.log"))
     print("baseline/_ref is", "ready" if ok else "NOT available")
     sys.exit(0 if ok else 1)

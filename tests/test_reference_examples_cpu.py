@@ -19,7 +19,7 @@ from pathlib import Path
 import pytest
 
 ROOT = Path(__file__).resolve().parent.parent
-REF = Path(os.environ.get("MF_REFERENCE_TREE", "/root/reference")) / "examples" / "memory_pool"
+REF = Path(os.environ.get("MF_REFERENCE_TREE") or Path(__file__).resolve().parents[2] / "reference") / "examples" / "memory_pool"
 
 CASES = [
     ("01_basic/01_single_device_dram_pool/01_single_device_dram_pool.py", [], "01_single_device_dram_pool ok"),
