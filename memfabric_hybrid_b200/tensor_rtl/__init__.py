@@ -4,5 +4,5 @@ from .executor import (All2AllVExcutor, All2AllVExecutor, BatchP2PExecutor, Exec
                        Planner)
 from .pack import pack_tensors, unpack_tensors  # noqa: F401
 from .plan import MFCommTask, P2PCommTask, PTensor, PTensorSet, overlaps, shard_bounds  # noqa: F401
-from .eplb import ExpertMigrator, pair_slots  # noqa: F401
+from .eplb import ExpertMigrator, balanced_placement, pair_slots, remap_topk, replica_table  # noqa: F401
 from .rl_reshard import InferLayout, ParamSpec, TrainLayout, TrainToInferResharder, decoder_specs  # noqa: F401

@@ -49,6 +49,57 @@ def pair_slots(old: Sequence[int], new: Sequence[int], local: int) -> List[Tuple
     return pairs
 
 
+def balanced_placement(load: Sequence[float], ep_size: int, slots_per_rank: int) -> List[int]:
+    """The planner of the EPLB flow: from the tokens each LOGICAL expert received (``load[e]``, e.g. a moving average of the
+    router's counts summed over ranks) to a placement ``placement[slot] = logical expert`` over ``ep_size * slots_per_rank``
+    physical slots that evens out the expert work per rank. Spare slots (slots beyond the number of logical experts) become
+    extra copies of the hottest experts: a copy is added, one at a time, to the expert with the largest load per copy. The
+    copies are then packed onto ranks heaviest first, each onto the rank with the least work so far that still has a free
+    slot (and, when possible, no copy of the same expert yet). Deterministic: every rank computes the same placement."""
+    E, P = len(load), ep_size * slots_per_rank
+    if E == 0 or P < E:
+        raise ValueError(f"{P} physical slots cannot hold {E} logical experts")
+    copies = [1] * E
+    for _ in range(P - E):
+        e = max(range(E), key=lambda i: (load[i] / copies[i], -i))
+        copies[e] += 1
+    items = sorted(((load[e] / copies[e], e) for e in range(E) for _ in range(copies[e])), key=lambda t: (-t[0], t[1]))
+    work = [0.0] * ep_size
+    held: List[List[int]] = [[] for _ in range(ep_size)]
+    for w, e in items:
+        free = [r for r in range(ep_size) if len(held[r]) < slots_per_rank]
+        fresh = [r for r in free if e not in held[r]] or free
+        r = min(fresh, key=lambda q: (work[q], q))
+        held[r].append(e)
+        work[r] += w
+    return [e for r in range(ep_size) for e in held[r]]
+
+
+def replica_table(placement: Sequence[int], num_logical: int, device=None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(table [num_logical, max copies] int32 of physical slots, -1 padded; counts [num_logical] int32)."""
+    slots: List[List[int]] = [[] for _ in range(num_logical)]
+    for slot, e in enumerate(placement):
+        slots[e].append(slot)
+    if any(not s for s in slots):
+        raise ValueError("a logical expert has no physical slot")
+    width = max(len(s) for s in slots)
+    table = torch.tensor([s + [-1] * (width - len(s)) for s in slots], dtype=torch.int32, device=device)
+    counts = torch.tensor([len(s) for s in slots], dtype=torch.int32, device=device)
+    return table, counts
+
+
+def remap_topk(topk_idx: torch.Tensor, table: torch.Tensor, counts: torch.Tensor, token_offset: int = 0) -> torch.Tensor:
+    """Logical expert ids [T, K] -> physical slot ids: token t uses copy (t + token_offset) mod copies(e), so the tokens of a
+    replicated expert spread evenly over its copies. Negative ids (unselected) pass through."""
+    T = topk_idx.shape[0]
+    valid = topk_idx >= 0
+    e = topk_idx.clamp_min(0).long()
+    tok = (torch.arange(T, device=topk_idx.device) + token_offset).view(T, 1)
+    which = tok % counts[e].long()
+    phys = table[e, which]
+    return torch.where(valid, phys, topk_idx.to(phys.dtype)).to(torch.int32)
+
+
 class ExpertMigrator:
     def __init__(self, rank: int, ep_size: int, experts_per_rank: int, backend: str = "nccl"):
         self.rank, self.ep_size, self.local = rank, ep_size, experts_per_rank

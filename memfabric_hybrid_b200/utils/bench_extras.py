@@ -286,13 +286,38 @@ def moe(heap, world, rank, flush, skew: bool = True):
     cases = [("prefill_4096", T, 0.0), ("decode_128", 128, 0.0)]
     if skew and world > 1:
         cases.append(("prefill_4096_zipf", T, 0.2))   # a skewed router: logits - 0.2 ln(expert index); the first GPU receives 2.2x the mean at 8 GPUs
+        # the same kind of router over 28 logical experts per GPU, the 4 spare slots per GPU holding copies of the hottest
+        # ones (tensor_rtl.balanced_placement from the measured loads, tokens spread over the copies by remap_topk)
+        cases.append(("prefill_4096_zipf_28_logical", T, 0.2))
+        cases.append(("prefill_4096_zipf_28_logical_replicated", T, 0.2))
+    pick = [c for c in os.environ.get("MF_BENCH_MOE_CASES", "").split(",") if c]   # e.g. "prefill_4096_zipf"; empty: all
     for name, tokens, zipf in cases:
+        if pick and name not in pick:
+            continue
         g = torch.Generator("cuda").manual_seed(rank)
         x = torch.randn(tokens, H, device="cuda", generator=g).to(torch.bfloat16)
-        logits = torch.randn(tokens, E, device="cuda", generator=g)
+        logical = "28_logical" in name
+        El_log = 28 if logical else E // world
+        logits = torch.randn(tokens, El_log * world, device="cuda", generator=g)
         if zipf > 0:
-            logits = logits - zipf * torch.log(torch.arange(1, E + 1, device="cuda", dtype=torch.float32))[None, :]
+            logits = logits - zipf * torch.log(torch.arange(1, El_log * world + 1, device="cuda", dtype=torch.float32))[None, :]
         idx, w = layer.route(logits, K)
+        if logical:
+            from ..tensor_rtl import balanced_placement, remap_topk, replica_table
+            load = torch.bincount(idx.reshape(-1).long(), minlength=El_log * world).float()
+            if world > 1:
+                dist.all_reduce(load)
+            try:   # host-side planning on the same loads on every rank: it fails on all of them or on none
+                if name.endswith("replicated"):
+                    placement = balanced_placement(load.tolist(), world, E // world)
+                    table, counts = replica_table(placement, El_log * world, device="cuda")
+                    idx = remap_topk(idx, table, counts, token_offset=rank).contiguous()
+                else:   # no planner: logical expert e sits in slot e % 28 of rank e // 28, the spare slots stay empty
+                    idx = ((idx // El_log) * (E // world) + idx % El_log).to(torch.int32).contiguous()
+                assert int(idx.min()) >= 0 and int(idx.max()) < E
+            except Exception as e:  # noqa: BLE001
+                res[name] = {"error": repr(e)[:200]}
+                continue
         # rows every rank will receive (a receive buffer that is too small drops rows and reports it: skip such a case)
         per_rank = torch.bincount(idx.reshape(-1).long() // (E // world), minlength=world).float()
         if world > 1:
@@ -302,7 +327,7 @@ def moe(heap, world, rank, flush, skew: bool = True):
             continue
         # correctness before timing: this layer (fp8) against the stock NCCL + bf16 grouped-GEMM layer on the same routing
         base_run, base_rows, base_gemm = _moe_nccl_layer(layer, x, idx, w, world, rank)
-        y0 = layer.forward(x, logits) if zipf == 0 else None
+        y0 = layer.forward(x, logits) if (zipf == 0 and not logical) else None
         if y0 is None:
             st0 = layer.comm.dispatch(x, idx, w)
             layer.comm.expert_ffn(st0, layer.w1q, layer.w1s, layer.w2q, layer.w2s)

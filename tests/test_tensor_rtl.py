@@ -132,3 +132,36 @@ def test_rl_reshard_splits_fused_training_shards():
     assert tl.expert_ranks(1, 5, 8) == [6, 7] and InferLayout(tp=2, ranks=[3, 9], ep=2).expert_ranks(5, 8) == [9]
     with pytest.raises(ValueError):
         TrainLayout(tp=4, pp=1, ep=3)
+
+
+def test_eplb_planner_evens_out_a_skewed_router():
+    """balanced_placement + remap_topk: a Zipf-like router that sends 2.4 x the mean to one rank ends within 10 % of the mean
+    once the hottest experts have copies on spare slots; every token still reaches a copy of the expert it chose."""
+    from memfabric_hybrid_b200.tensor_rtl import balanced_placement, remap_topk, replica_table
+    world, local, spare, K, T = 8, 28, 4, 8, 4096
+    E = world * local
+    g = torch.Generator().manual_seed(0)
+    logits = torch.randn(T, E, generator=g) - 0.4 * torch.log(torch.arange(1, E + 1, dtype=torch.float32))[None, :]
+    idx = torch.topk(torch.softmax(logits, -1), K, dim=-1).indices.to(torch.int32)
+    idx[3, 2] = -1
+    load = torch.bincount(idx[idx >= 0].long(), minlength=E).float()
+    before = load.view(world, local).sum(1)
+    assert float(before.max() / before.mean()) > 1.8
+    placement = balanced_placement(load.tolist(), world, local + spare)
+    assert len(placement) == world * (local + spare) and set(placement) == set(range(E))
+    table, counts = replica_table(placement, E)
+    assert int(counts.sum()) == len(placement) and int(counts.max()) > 1
+    phys = remap_topk(idx, table, counts)
+    assert phys[3, 2] == -1 and phys.shape == idx.shape
+    # every physical slot a token was sent to holds the logical expert the router chose
+    pl = torch.tensor(placement)
+    sel = phys >= 0
+    assert torch.equal(pl[phys[sel].long()], idx[sel].long())
+    after = torch.bincount(phys[sel].long() // (local + spare), minlength=world).float()
+    assert float(after.max() / after.mean()) < 1.10, after
+    # no rank holds two copies of one expert while another rank could have taken it
+    for r in range(world):
+        held = placement[r * (local + spare):(r + 1) * (local + spare)]
+        assert len(set(held)) == len(held)
+    with pytest.raises(ValueError):
+        balanced_placement([1.0] * 10, 2, 4)
