@@ -10,6 +10,7 @@
 #include "../group/mf_group.h"
 #include "../store/mf_store.h"
 #include "../store/mf_store_backend.h"
+#include "../store/mf_store_etcd.h"
 #include "../store/mf_store_ha.h"
 #include "../util/mf_trace.h"
 #include "../util/mf_util.h"
@@ -116,7 +117,7 @@ int mf_t_store_get(void *h, const char *key, char *buf, int cap, int64_t timeout
 {
     std::string v;
     int rc = static_cast<StoreBox *>(h)->s->Get(key, v, timeoutMs);
-    if (rc != OK) return rc < 0 ? rc : -rc;
+    if (rc != OK) return rc < 0 ? rc : -1;
     return CopyOut(v, buf, cap);
 }
 int mf_t_store_add(void *h, const char *key, int64_t inc, int64_t *result) { return static_cast<StoreBox *>(h)->s->Add(key, inc, *result); }
@@ -143,7 +144,7 @@ int mf_t_store_prefix_get(void *h, const char *prefix, char *buf, int cap)
 {
     std::vector<std::string> ks, vs;
     int rc = static_cast<StoreBox *>(h)->s->PrefixGet(prefix, ks, vs);
-    if (rc != OK) return rc < 0 ? rc : -rc;
+    if (rc != OK) return rc < 0 ? rc : -1;
     std::string joined;
     for (auto &k : ks) joined += k + "\n";
     if (buf != nullptr && cap > 0) {
@@ -195,6 +196,56 @@ int mf_t_ha_leader_addr(void *h, char *buf, int cap)
     return n;
 }
 void mf_t_ha_kill_leader(void *h) { static_cast<StoreBox *>(h)->ha->KillLeaderServer(); }
+// the same store on an etcd backend (native v3 client)
+void *mf_t_ha_new_etcd(const char *ip, uint16_t basePort, uint32_t world, uint32_t rank, const char *etcdIp, uint16_t etcdPort,
+                       const char *instance, int candidate)
+{
+    auto be = std::make_shared<EtcdBackend>(etcdIp, etcdPort, instance ? instance : "");
+    auto ha = std::make_shared<HaConfigStore>(ip, basePort, world, rank, be, candidate != 0);
+    return new StoreBox{ha, nullptr, ha};
+}
+// ---- etcd backend on its own ----------------------------------------------------------------------------
+void *mf_t_etcd_new(const char *ip, uint16_t port, const char *instance, const char *user, const char *password, uint32_t timeoutMs)
+{
+    auto *b = new EtcdBackend(ip, port, instance ? instance : "", user ? user : "", password ? password : "");
+    if (timeoutMs != 0) b->SetTimeoutMs(timeoutMs);
+    return b;
+}
+void mf_t_etcd_free(void *h) { delete static_cast<EtcdBackend *>(h); }
+int mf_t_etcd_connect(void *h) { return static_cast<EtcdBackend *>(h)->Connect(); }
+int mf_t_etcd_put(void *h, const char *key, const void *val, int len, uint32_t ttlMs)
+{
+    return static_cast<EtcdBackend *>(h)->Put(key, std::string((const char *)val, (size_t)len), ttlMs);
+}
+int mf_t_etcd_get(void *h, const char *key, char *buf, int cap)  // -> length (>= 0) or a negative error code
+{
+    std::string v;
+    int rc = static_cast<EtcdBackend *>(h)->Get(key, v);
+    if (rc != OK) return rc < 0 ? rc : -1;
+    return CopyOut(v, buf, cap);
+}
+int mf_t_etcd_prefix_get(void *h, const char *prefix, char *buf, int cap)  // "key=value\n" lines -> length or a negative code
+{
+    std::vector<std::pair<std::string, std::string>> kvs;
+    int rc = static_cast<EtcdBackend *>(h)->PrefixGet(prefix, kvs);
+    if (rc != OK) return rc < 0 ? rc : -1;
+    std::string all;
+    for (auto &kv : kvs) all += kv.first + "=" + kv.second + "\n";
+    return CopyOut(all, buf, cap);
+}
+int mf_t_etcd_delete(void *h, const char *key) { return static_cast<EtcdBackend *>(h)->Delete(key); }
+int mf_t_etcd_clear(void *h, const char *prefix) { return static_cast<EtcdBackend *>(h)->Clear(prefix); }
+int mf_t_etcd_exist(void *h, const char *key) { return static_cast<EtcdBackend *>(h)->Exist(key) ? 1 : 0; }
+int mf_t_etcd_lock(void *h, const char *name) { return static_cast<EtcdBackend *>(h)->Lock(name); }
+int mf_t_etcd_try_lock(void *h, const char *name) { return static_cast<EtcdBackend *>(h)->TryLock(name); }
+int mf_t_etcd_unlock(void *h, const char *name) { return static_cast<EtcdBackend *>(h)->Unlock(name); }
+int mf_t_etcd_last_error(void *h, char *buf, int cap)
+{
+    int n = CopyOut(static_cast<EtcdBackend *>(h)->LastError(), buf, cap - 1);
+    if (buf != nullptr && cap > 0) buf[std::min(n, cap - 1)] = 0;
+    return n;
+}
+
 void mf_t_backend_set_reachable(const char *name, int reachable) { LocalMemoryBackend::SetReachable(name, reachable != 0); }
 void mf_t_backend_reset(const char *name) { LocalMemoryBackend::Reset(name); }
 

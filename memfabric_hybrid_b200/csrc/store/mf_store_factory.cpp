@@ -1,9 +1,11 @@
 // URL parsing and per-URL store singletons.
 // tcp://ip:port            plain TCP store (server started by whoever asks for it)
-// etcd://ip:port[#inst]    HA store over the user-registered op table (the etcd client is supplied by the caller)
+// etcd://ip:port[#inst]    HA store over etcd v3 at ip:port (native client, mf_store_etcd.h), or over the user-registered op
+//                          table when one is set; the store leader listens at MF_CONFIG_STORE_IP : MF_CONFIG_STORE_PORT (or above)
 // reg://name[#inst]        HA store over the user-registered op table, or over the in-process backend `name`
 // Parity: src/smem/csrc/config_store/smem_store_factory.cpp:50-125,174-251,292-310.
 #include "mf_store_backend.h"
+#include "mf_store_etcd.h"
 #include "mf_store_ha.h"
 
 namespace mf {
@@ -180,12 +182,17 @@ StorePtr StoreFactory::CreateStore(const std::string &url, bool isServer, uint32
         if (GetExternalBackendOps(ops)) backend = std::make_shared<ExternalBackend>(ops, u.ip, u.instance);
         else if (u.scheme == StoreUrl::REG) backend = std::make_shared<LocalMemoryBackend>(u.ip, true);
         else {
-            g_stores.erase(url);
-            MF_FAIL(ERR_NOT_EXIST, "etcd:// needs a backend op table (smem_config_store_set_backend_op)");
-            return fail(ERR_NOT_EXIST);
+            auto etcd = std::make_shared<EtcdBackend>(u.ip, u.port, u.instance);
+            if (etcd->Connect() != OK) {
+                g_stores.erase(url);
+                MF_FAIL(ERR_NOT_CONNECTED, "etcd backend of %s: %s", url.c_str(), etcd->LastError().c_str());
+                return fail(ERR_NOT_CONNECTED);
+            }
+            backend = etcd;
         }
         std::string ip = EnvStr("MF_CONFIG_STORE_IP", nullptr, "127.0.0.1");
-        uint16_t port = u.port != 0 ? u.port : (uint16_t)EnvInt("MF_CONFIG_STORE_PORT", nullptr, 36100, 1024, 65000);
+        // the port of an etcd:// URL is etcd's own: the store leader listens elsewhere
+        uint16_t port = (u.port != 0 && u.scheme != StoreUrl::ETCD) ? u.port : (uint16_t)EnvInt("MF_CONFIG_STORE_PORT", nullptr, 36100, 1024, 65000);
         auto ha = std::make_shared<HaConfigStore>(ip, port, worldSize, rank, backend, isServer);
         g.unlock();
         int rc = ha->Startup(timeoutMs);

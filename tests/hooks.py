@@ -7,7 +7,7 @@ WATCH_CB = C.CFUNCTYPE(None, C.c_int, C.c_char_p, C.POINTER(C.c_char), C.c_int)
 RANK_CB = C.CFUNCTYPE(None, C.c_uint32)
 CHANGE_CB = C.CFUNCTYPE(C.c_int, C.c_int, C.c_uint32)
 
-ERR_TIMEOUT, ERR_NOT_EXIST, ERR_IN_USE = -2004, -2007, -2009
+ERR_TIMEOUT, ERR_NOT_EXIST, ERR_IN_USE, ERR_NOT_CONNECTED = -2004, -2007, -2009, -2014
 
 _done = False
 
@@ -52,6 +52,20 @@ def lib():
     s(l, "mf_t_ha_is_leader", i32, vp)
     s(l, "mf_t_ha_leader_addr", i32, vp, cp, i32)
     s(l, "mf_t_ha_kill_leader", None, vp)
+    s(l, "mf_t_ha_new_etcd", vp, cp, u16, u32, u32, cp, u16, cp, i32)
+    s(l, "mf_t_etcd_new", vp, cp, u16, cp, cp, cp, u32)
+    s(l, "mf_t_etcd_free", None, vp)
+    s(l, "mf_t_etcd_connect", i32, vp)
+    s(l, "mf_t_etcd_put", i32, vp, cp, cp, i32, u32)
+    s(l, "mf_t_etcd_get", i32, vp, cp, cp, i32)
+    s(l, "mf_t_etcd_prefix_get", i32, vp, cp, cp, i32)
+    s(l, "mf_t_etcd_delete", i32, vp, cp)
+    s(l, "mf_t_etcd_clear", i32, vp, cp)
+    s(l, "mf_t_etcd_exist", i32, vp, cp)
+    s(l, "mf_t_etcd_lock", i32, vp, cp)
+    s(l, "mf_t_etcd_try_lock", i32, vp, cp)
+    s(l, "mf_t_etcd_unlock", i32, vp, cp)
+    s(l, "mf_t_etcd_last_error", i32, vp, cp, i32)
     s(l, "mf_t_backend_set_reachable", None, cp, i32)
     s(l, "mf_t_backend_reset", None, cp)
     s(l, "mf_t_group_new", vp, vp, u32, u32, u64, i32, CHANGE_CB)
