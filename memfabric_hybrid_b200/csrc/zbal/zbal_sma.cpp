@@ -325,8 +325,14 @@ public:
         o << "{\"heap\":{\"base\":" << heap_.Base() << ",\"size\":" << heap_.TotalSize() << ",\"threshold\":" << heap_.Threshold()
           << ",\"round_large\":" << cfg_.roundLarge << ",\"max_split\":" << cfg_.maxSplit << ",\"device\":" << device_
           << ",\"simulated\":" << (simulated_ ? "true" : "false") << ",\"in_use\":" << inUse_ << ",\"cached\":" << cached_
-          << ",\"peak\":" << peak_ << "},\"blocks\":[";
+          << ",\"peak\":" << peak_ << "},\"segments\":[";
         bool first = true;
+        for (const auto &r : heap_.RegionList()) {
+            o << (first ? "" : ",") << "{\"base\":" << r.first << ",\"size\":" << r.second << "}";
+            first = false;
+        }
+        o << "],\"blocks\":[";
+        first = true;
         for (const auto &b : heap_.Blocks()) {
             const char *state = "free";
             uint64_t stream = 0;

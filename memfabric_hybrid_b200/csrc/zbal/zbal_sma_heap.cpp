@@ -51,6 +51,12 @@ size_t SplitMemoryHeap::Regions() const
     return regions_.size();
 }
 
+std::vector<std::pair<uint64_t, uint64_t>> SplitMemoryHeap::RegionList() const
+{
+    std::lock_guard<std::mutex> g(mu_);
+    return regions_;
+}
+
 int SplitMemoryHeap::BucketOf(uint64_t size)
 {
     return size == 0 ? 0 : 63 - __builtin_clzll(size);

@@ -34,6 +34,7 @@ public:
     // range the heap already has; free space that touches is merged. False when it overlaps what the heap manages.
     bool AddRegion(uint64_t base, uint64_t size);
     size_t Regions() const;
+    std::vector<std::pair<uint64_t, uint64_t>> RegionList() const;  // (base, size) in the order they were added
 
     uint64_t Base() const { return base_; }
     uint64_t TotalSize() const { return size_; }

@@ -12,38 +12,19 @@ second class ``All2AllVExcutor``; that name is kept as an alias).
 from __future__ import annotations
 
 import enum
-from abc import ABC, abstractmethod
 from dataclasses import dataclass
 from typing import List, Optional
 
 import torch
 import torch.distributed as dist
 
+from .abc import BaseCommTask, Executor, Planner  # noqa: F401
 from .plan import MFCommTask, P2PCommTask
-
-
-class Executor(ABC):
-    @abstractmethod
-    def execute(self, tasks: List) -> None:
-        ...
-
-    @abstractmethod
-    def wait(self) -> None:
-        ...
-
-
-class Planner(ABC):
-    """Reorders tasks before execution (e.g. to balance links); the default keeps the order."""
-
-    def __init__(self, topology=None):
-        self.topology = topology
-
-    def build_ordered_comm_ops(self, op_list: List) -> List:
-        return list(op_list)
 
 
 class BatchP2PExecutor(Executor):
     def __init__(self, group: Optional[dist.ProcessGroup] = None):
+        super().__init__()
         self.group = group
         self._reqs = []
 
@@ -63,6 +44,7 @@ class BatchP2PExecutor(Executor):
 
 class All2AllVExecutor(Executor):
     def __init__(self, group: Optional[dist.ProcessGroup] = None):
+        super().__init__()
         self.group = group
         self._pending = None
 
@@ -149,6 +131,7 @@ class MemoryFabricExecutor(Executor):
 
     def __init__(self, bm_config: MfBmConfig, rank_id: Optional[int] = None, executor_type: "MemoryFabricExecutor.ExecutorType" = None,
                  device_id: Optional[int] = None):
+        super().__init__()
         from .. import api as mf
         from ..api import bm
         self.bm = bm

@@ -19,9 +19,13 @@ from typing import List, Optional, Sequence, Tuple
 
 import torch
 
+from .abc import BaseCommTask
+from .buffer_pool import BufferPool
+from .utils import get_dtype_size
+
 
 @dataclass
-class P2PCommTask:
+class P2PCommTask(BaseCommTask):
     """One send (``is_send``: src_rank = me, dst_rank = receiver) or receive (src_rank = me, dst_rank = sender),
     the orientation the reference uses."""
     idx: int = 0
@@ -35,7 +39,7 @@ class P2PCommTask:
 
 
 @dataclass
-class MFCommTask:
+class MFCommTask(BaseCommTask):
     """One copy through a BigMemory pool: writers put ``buffer`` at ``gva_ptr`` of ``pool_rank``'s slice,
     readers fetch from there."""
     idx: int = 0
@@ -69,8 +73,14 @@ def overlaps(size: int, old_mesh: Sequence[int], new_mesh: Sequence[int]):
 
 class PTensor:
     def __init__(self, tensor: Optional[torch.Tensor], dtype: torch.dtype, ndim: int, device_mesh: Sequence[int],
-                 global_size: Sequence[int], shard_dim: int, rank: Optional[int] = None, backend: str = "nccl", check_sanity: bool = True):
+                 global_size: Sequence[int], shard_dim: int, rank: Optional[int] = None, backend: str = "nccl", check_sanity: bool = True,
+                 reuse_buffers: bool = False):
+        """``reuse_buffers``: staging and receive buffers live in ``self.buffer_pool`` and are used again by every later
+        ``transfer_map`` with the same mesh sizes (a plan that repeats allocates once; each ``transfer_map`` then starts a
+        new plan, and the tensor returned by ``collect_tensor`` is overwritten by the next round)."""
         self.tensor, self.dtype, self.ndim = tensor, dtype, ndim
+        self.buffer_pool = BufferPool()
+        self.reuse_buffers = reuse_buffers
         self.device_mesh = list(device_mesh)
         self.global_size = torch.Size(global_size)
         self.shard_dim = shard_dim
@@ -149,26 +159,44 @@ class PTensor:
             if torch.cuda.is_available() else torch.device("cpu")
         ops = []
         pool_off = {}
+        lengths = (len(self.device_mesh), len(new_mesh))
+        if self.reuse_buffers:
+            self._op_list, self._recv = [], []
         for idx, (src, dst, lo, hi) in enumerate(self._pieces(new_mesh)):
             shape = self._recv_shape(lo, hi)
             numel = 1
             for s in shape:
                 numel *= s
-            nbytes = numel * torch.empty((), dtype=self.dtype).element_size()
+            nbytes = numel * get_dtype_size(self.dtype)
             off = self.pool_offset + pool_off.get(src, 0)          # position of this piece inside src's pool slice
             pool_off[src] = pool_off.get(src, 0) + (nbytes + 255) // 256 * 256
             if src == dst:
                 if self.rank == src:
-                    self._recv.append((lo, self._slice_of_mine(lo, hi).clone()))
+                    if self.reuse_buffers:
+                        keep = self.buffer_pool.get_or_create(lengths, ("keep", lo, hi), lambda: torch.empty(shape, dtype=self.dtype, device=dev))
+                        keep.copy_(self._slice_of_mine(lo, hi))
+                    else:
+                        keep = self._slice_of_mine(lo, hi).clone()
+                    self._recv.append((lo, keep))
                 continue
             if self.rank == src:
-                buf = self._slice_of_mine(lo, hi).contiguous()
+                mine = self._slice_of_mine(lo, hi)
+                if mine.is_contiguous():
+                    buf = mine                                   # sent from where it lies
+                elif self.reuse_buffers:
+                    buf = self.buffer_pool.get_or_create(lengths, ("send", lo, hi), lambda: torch.empty(shape, dtype=self.dtype, device=dev))
+                    buf.copy_(mine)
+                else:
+                    buf = mine.contiguous()
                 if self.backend == "mf":
                     ops.append(MFCommTask(idx, nbytes, True, src, dst, src, off, buf, (lo, hi)))
                 else:
                     ops.append(P2PCommTask(idx, numel, True, src, dst, buf, None, (lo, hi)))
             if self.rank == dst:
-                buf = torch.empty(shape, dtype=self.dtype, device=dev)
+                if self.reuse_buffers:
+                    buf = self.buffer_pool.get_or_create(lengths, ("recv", src, lo, hi), lambda: torch.empty(shape, dtype=self.dtype, device=dev))
+                else:
+                    buf = torch.empty(shape, dtype=self.dtype, device=dev)
                 self._recv.append((lo, buf))
                 if self.backend == "mf":
                     ops.append(MFCommTask(idx, nbytes, False, dst, src, src, off, buf, (lo, hi)))

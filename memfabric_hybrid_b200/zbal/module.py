@@ -19,6 +19,7 @@ import ctypes as C
 import enum
 import json
 import os
+from typing import Optional
 
 import torch
 
@@ -199,11 +200,13 @@ def empty_cache(check_error: bool = False) -> None:
     K.lib().zbal_pluggable_empty_cache(check_error)
 
 
-def record_memory_history(enabled: bool = True, max_entries: int = 65536) -> None:
-    K.lib().zbal_sma_record_history(enabled, max_entries)
+def record_memory_history(enabled=True, max_entries: int = 65536) -> None:
+    """Starts (any true value: True, "all", "state") or stops (False / None) recording the allocator's malloc / free history."""
+    K.lib().zbal_sma_record_history(bool(enabled), max(0, min(int(max_entries), 0xFFFFFFFF)))
 
 
 def snapshot() -> dict:
+    """The allocator's own snapshot: heap settings, address segments, every block with its state, the recorded history."""
     l = K.lib()
     need = l.zbal_sma_snapshot(None, 0)
     if need <= 0:
@@ -213,9 +216,59 @@ def snapshot() -> dict:
     return json.loads(buf.value.decode())
 
 
-def dump_snapshot(path: str) -> None:
+def memviz_snapshot(snap: Optional[dict] = None) -> dict:
+    """The snapshot in the layout of PyTorch's memory visualiser (``torch.cuda.memory._snapshot()``): ``segments`` (one per
+    address segment of the heap, each with its blocks in address order) and ``device_traces`` (one list per device:
+    segment_alloc for every segment, then alloc / free_requested / free_completed / empty_cache / oom from the recorded
+    history). Pickle it and open it at pytorch.org/memory_viz, or feed it to ``zbal.snapshot_utils``.
+    Parity: app/zbal/src/csrc/sma/zbal_sma_pybind.cpp:21-150 of the reference."""
+    snap = snap if snap is not None else snapshot()
+    heap = snap["heap"]
+    dev = int(heap.get("device", 0))
+    regions = snap.get("segments") or [{"base": heap["base"], "size": heap["size"]}]
+    state = {"active": "active_allocated", "cached": "inactive", "free": "inactive"}
+    segments, trace = [], []
+    blocks = sorted(snap["blocks"], key=lambda b: b["addr"])
+    for r in sorted(regions, key=lambda r: r["base"]):
+        lo, hi = r["base"], r["base"] + r["size"]
+        mine = [b for b in blocks if lo <= b["addr"] < hi]
+        active = sum(b["size"] for b in mine if b["state"] == "active")
+        segments.append({"device": dev, "address": lo, "total_size": r["size"], "allocated_size": active, "active_size": active,
+                         "requested_size": active, "stream": 0, "segment_type": "large", "segment_pool_id": 0, "is_expandable": False,
+                         "frames": [], "blocks": [{"address": b["addr"], "size": b["size"], "requested_size": b["size"],
+                                                   "state": state[b["state"]], "frames": []} for b in mine]})
+    for r in regions:   # in the order the heap got them
+        trace.append({"action": "segment_alloc", "addr": r["base"], "size": r["size"], "stream": 0})
+    for ev in snap.get("history", []):
+        op = ev["op"]
+        if op in ("malloc_heap", "malloc_cache"):
+            trace.append({"action": "alloc", "addr": ev["addr"], "size": ev["size"], "stream": ev["stream"]})
+        elif op in ("free_cache", "free_heap"):
+            trace.append({"action": "free_requested", "addr": ev["addr"], "size": ev["size"], "stream": ev["stream"]})
+            trace.append({"action": "free_completed", "addr": ev["addr"], "size": ev["size"], "stream": ev["stream"]})
+        elif op == "empty_cache":
+            trace.append({"action": "empty_cache", "addr": 0, "size": 0, "stream": 0})
+        elif op == "malloc_failed":
+            trace.append({"action": "oom", "device_free": heap["size"] - heap.get("in_use", 0), "size": ev.get("requested", ev["size"]),
+                          "stream": ev["stream"]})
+    traces = [[] for _ in range(dev)] + [trace]
+    return {"segments": segments, "device_traces": traces}
+
+
+def dump_snapshot(path: Optional[str] = None):
+    """Without a path: returns the snapshot in the memory visualiser's layout (the reference's call). With a path: writes
+    it there, a ``.pkl`` / ``.pickle`` file in the visualiser's layout, anything else as JSON in the allocator's own layout
+    (what ``python -m memfabric_hybrid_b200.zbal.simulator`` reads)."""
+    if path is None:
+        return memviz_snapshot()
+    if path.endswith((".pkl", ".pickle")):
+        import pickle
+        with open(path, "wb") as f:
+            pickle.dump(memviz_snapshot(), f)
+        return None
     with open(path, "w") as f:
         json.dump(snapshot(), f)
+    return None
 
 
 def simulate_init(addr: int, size: int) -> None:

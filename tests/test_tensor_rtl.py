@@ -92,6 +92,69 @@ def test_reshard_executors(kind):
     assert run_ranks(_reshard, 4, (free_port(), kind), timeout=180) == [True] * 4
 
 
+def _reshard_twice(rank, world, port):
+    import torch.distributed as dist
+    from memfabric_hybrid_b200.tensor_rtl import BatchP2PExecutor, BufferPool, PTensor
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    # columns TP2 (ranks 0, 1) -> TP4 (all ranks): the senders' column slices are not contiguous, rank 0 and 1 keep a part
+    shape, old, new = (4, 8), [0, 1], [0, 1, 2, 3]
+    shard = torch.zeros(4, 4) if rank in old else None
+    pt = PTensor(shard, torch.float32, 2, old, shape, 1, rank=rank, backend="gloo", reuse_buffers=True)
+    assert isinstance(pt.buffer_pool, BufferPool)
+    ptrs, ex = [], BatchP2PExecutor()
+    for step in range(3):
+        full = _global(shape, step)
+        if rank in old:
+            shard.copy_(full.chunk(2, 1)[old.index(rank)])       # the weights changed in place, as after an optimizer step
+        pt.transfer_map(new)                                       # the same plan again
+        ex.execute(pt.get_transfer_list())
+        ex.wait()
+        got = pt.collect_tensor()
+        assert torch.equal(got, full.narrow(1, 2 * rank, 2)), (rank, step, got)
+        ptrs.append((got.data_ptr(), tuple(sorted(b.data_ptr() for d in pt.buffer_pool.send_buffer_dict.values() for b in d.values()))))
+        dist.barrier()
+    assert ptrs[0] == ptrs[1] == ptrs[2]                            # nothing was allocated after the first round
+    assert list(pt.buffer_pool.get_keys()) == [(2, 4)] and pt.buffer_pool.nbytes() > 0
+    n_ops = len(pt.get_transfer_list())
+    pt.transfer_map(new)
+    assert len(pt.get_transfer_list()) == n_ops                     # a new plan replaces the old one instead of growing it
+    dist.destroy_process_group()
+    return True
+
+
+def test_repeating_plan_reuses_its_buffers():
+    assert run_ranks(_reshard_twice, 4, (free_port(),), timeout=120) == [True] * 4
+
+
+def test_buffer_pool_and_small_helpers():
+    from memfabric_hybrid_b200.tensor_rtl import (BaseCommTask, BatchP2PExecutor, BufferPool, Executor, MFCommTask, P2PCommTask, Planner,
+                                                  get_dtype_size)
+    import tensor_rtl
+    assert tensor_rtl.BufferPool is BufferPool and tensor_rtl.get_dtype_size is get_dtype_size
+    bp = BufferPool()
+    a, b = torch.zeros(3), torch.ones(3)
+    assert bp.get((2, 4), (0, 3)) is None
+    bp.register((2, 4), (0, 3), a)
+    bp.register((2, 4), (0, 3), b)                                 # the first registration wins
+    assert bp.get((2, 4), (0, 3)) is a and list(bp.get_keys()) == [(2, 4)]
+    assert bp.get_or_create((2, 4), (3, 6), lambda: b) is b and bp.get_or_create((2, 4), (3, 6), lambda: a) is b
+    assert bp.nbytes() == 24
+    bp.clear()
+    assert bp.get((2, 4), (0, 3)) is None
+    assert [get_dtype_size(d) for d in (torch.bool, torch.int8, torch.float8_e4m3fn, torch.bfloat16, torch.float32, torch.int64,
+                                        torch.complex64)] == [1, 1, 1, 2, 4, 8, 8]
+    assert issubclass(P2PCommTask, BaseCommTask) and issubclass(MFCommTask, BaseCommTask) and issubclass(BatchP2PExecutor, Executor)
+    assert BatchP2PExecutor().batch_comm_list == []
+    with pytest.raises(TypeError):
+        Executor()                                                  # abstract
+
+    class Reverse(Planner):
+        def build_ordered_comm_ops(self, op_list):
+            return list(reversed(op_list))
+    t = [P2PCommTask(idx=i) for i in range(3)]
+    assert [x.idx for x in Reverse(topology="ring").build_ordered_comm_ops(t)] == [2, 1, 0] and Planner().build_ordered_comm_ops(t) == t
+
+
 def test_eplb_slot_pairing():
     from memfabric_hybrid_b200.tensor_rtl import pair_slots
     old = [0, 1, 2, 3, 0, 1]

@@ -167,6 +167,101 @@ def test_replay_tool_reports_fragmentation(tmp_path, sma):
     assert "#" in txt and "." in txt
 
 
+def test_visualiser_layout_snapshot_model_replay_and_exports(tmp_path, sma):
+    """zbal.dump_snapshot() in the memory visualiser's layout, the address-ordered model built from its trace, a replay
+    through the allocator, the drawings and the Chrome-trace export (names of the reference's snapshot_utils)."""
+    import pickle
+
+    import zbal
+    from snapshot_utils.gva_layout_analyzer import Block, MemoryAllocatorSimulator
+    from snapshot_utils.gva_layout_viz import (parse_mem_to_profile, parser_file_ops, visualize_file_memory, visualize_file_snapshot,
+                                               visualize_sim_memory)
+    from snapshot_utils.gva_snapshot_replay import replay_snapshot
+    zbal.record_memory_history("all", 1 << 40)          # the reference's spelling; an over-long limit is clamped
+    ps = [sma.zbal_pluggable_malloc(3 * MiB, 0, None) for _ in range(6)]
+    small = sma.zbal_pluggable_malloc(4096, 0, None)
+    for p in ps[1::2]:
+        sma.zbal_pluggable_free(p, 0, 0, None)
+    sma.zbal_pluggable_empty_cache(False)
+    snap = zbal.dump_snapshot()
+    assert set(snap) == {"segments", "device_traces"} and len(snap["segments"]) == 1
+    seg = snap["segments"][0]
+    assert seg["address"] == BASE and seg["total_size"] == 256 * MiB and seg["allocated_size"] == 3 * 4 * MiB + 4096
+    assert sum(b["size"] for b in seg["blocks"]) == 256 * MiB                        # the blocks tile the segment
+    assert [b["address"] for b in seg["blocks"]] == sorted(b["address"] for b in seg["blocks"])
+    assert sum(1 for b in seg["blocks"] if b["state"] == "active_allocated") == 4
+    trace = snap["device_traces"][0]
+    acts = [te["action"] for te in trace]
+    assert acts[0] == "segment_alloc" and acts.count("alloc") == 7 and acts.count("free_completed") == 3 and "empty_cache" in acts
+
+    # the model of the trace agrees with the snapshot's block list
+    sim = MemoryAllocatorSimulator(gva_size=256 * MiB).simulate(trace)
+    assert sim.gva_base_addr == BASE and sim.get_all_segments() == [(BASE, BASE + 256 * MiB)]
+    used = sim.get_used_blocks()
+    assert {(b.addr, b.size) for b in used} == {(b["address"], b["size"]) for b in seg["blocks"] if b["state"] == "active_allocated"}
+    assert sum(b.size for b in sim.get_all_blocks()) == 256 * MiB and sim.used_bytes() == seg["allocated_size"]
+    assert all(isinstance(b, Block) and b.status == "FREE" for b in sim.get_free_blocks()) and 0.0 <= sim.fragmentation() < 1.0
+    assert sim.get_free_space() == [0]                                                # one segment covers the whole range
+    # misuse is refused
+    with pytest.raises(ValueError):
+        sim._alloc(used[0].addr, 512)
+    with pytest.raises(ValueError):
+        sim._free(BASE + 12345)
+    with pytest.raises(ValueError):
+        sim._segment_free(BASE)                                                       # still has blocks in use
+    # holes between segments
+    two = MemoryAllocatorSimulator(gva_base_addr=0, gva_size=100)
+    two.simulate([{"action": "segment_alloc", "addr": 10, "size": 20}, {"action": "segment_alloc", "addr": 50, "size": 10},
+                  {"action": "alloc", "addr": 12, "size": 4}, {"action": "alloc", "addr": 16, "size": 4}, {"action": "free_completed", "addr": 12},
+                  {"action": "free_completed", "addr": 16}])
+    assert two.get_free_space() == [10, 20, 40] and [(b.addr, b.size) for b in two.get_all_blocks()] == [(10, 20), (50, 10)]
+    two.simulate([{"action": "segment_free", "addr": 50, "size": 10}])
+    assert two.get_free_space() == [10, 70]
+
+    # files: pickle in the visualiser's layout, JSON in the allocator's own; both load as a trace
+    zbal.dump_snapshot(str(tmp_path / "s.pkl"))
+    zbal.dump_snapshot(str(tmp_path / "s.json"))
+    assert pickle.loads((tmp_path / "s.pkl").read_bytes())["segments"][0]["address"] == BASE
+    assert [te["action"] for te in parser_file_ops(str(tmp_path / "s.pkl"))] == acts
+    assert [te["action"] for te in parser_file_ops(str(tmp_path / "s.json"))] == acts
+    assert parser_file_ops(str(tmp_path / "s.pkl"), get_traces=False)[0]["total_size"] == 256 * MiB
+    with pytest.raises(ValueError):
+        parser_file_ops(str(tmp_path / "s.txt"))
+
+    # drawings
+    svg = visualize_sim_memory(sim, display_segments=True, output=str(tmp_path / "sim.svg"))
+    assert svg.startswith("<svg") and svg.count("<rect") >= 1 + 1 + 4 and (tmp_path / "sim.svg").read_text() == svg
+    svg2 = visualize_file_memory(0.25, hex(BASE), trace)
+    assert svg2.count(_used_colour()) >= 4
+    gaps = visualize_file_snapshot(0, BASE, [{"address": 0, "total_size": 10, "blocks": []}, {"address": 30, "total_size": 10, "blocks": []},
+                                             {"address": 45, "total_size": 5, "blocks": [{"address": 45, "size": 5, "state": "inactive"}]}],
+                                   output=str(tmp_path / "gaps.svg"))
+    assert [(g["gap_start"], g["size"]) for g in gaps] == [(10, 20), (40, 5)] and (tmp_path / "gaps.svg").exists()
+    assert visualize_file_snapshot(0.25, BASE, snap["segments"]) == []
+
+    # Chrome trace: 3 lifetimes that ended, 4 still alive
+    n = parse_mem_to_profile(trace, str(tmp_path / "prof.json"), export_segments=False, with_unfree=True)
+    ev = json.loads((tmp_path / "prof.json").read_text())["traceEvents"]
+    assert len(ev) == n and sum(1 for e in ev if e["ph"] == "X" and e["name"].startswith("Block_")) == 3
+    assert sum(1 for e in ev if e["name"].startswith("Unfreed_")) == 4 and {e["tid"] for e in ev if e["ph"] == "X"} == {"< 16MB (Small)"}
+    assert [e["args"]["Allocated_MB"] for e in ev if e["ph"] == "C"][-1] == pytest.approx((3 * 4 * MiB + 4096) / MiB)
+    parse_mem_to_profile(trace, str(tmp_path / "seg.json"))
+    assert sum(1 for e in json.loads((tmp_path / "seg.json").read_text())["traceEvents"] if e["ph"] == "C") == 1
+
+    # replay through the allocator on another base: the same layout, shifted
+    out = replay_snapshot(snap, shmem_size=256 * MiB, base_addr=BASE + (1 << 40))
+    assert out["replay"] == {"events": 11, "failed": 0, "moved": 0, "live": 4}
+    again = MemoryAllocatorSimulator(gva_size=256 * MiB).simulate(out["device_traces"][0])
+    assert again == sim and again.gva_base_addr == BASE + (1 << 40)
+    assert not (again == MemoryAllocatorSimulator(gva_size=256 * MiB).simulate(trace[:5]))
+    del small
+
+
+def _used_colour():
+    from memfabric_hybrid_b200.zbal.snapshot_utils.gva_layout_viz import _COL
+    return _COL["used"]
+
+
 def _boot(rank, world, port):
     os.environ["MF_DEVICE_BACKEND"] = "fake"
     import memfabric_hybrid_b200.zbal as z
