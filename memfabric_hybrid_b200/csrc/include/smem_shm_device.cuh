@@ -166,5 +166,21 @@ template <typename T> __device__ __forceinline__ void smem_shm_roce_read(const s
     }
     for (i += threadIdx.x; i < end; i += blockDim.x) d[i] = *reinterpret_cast<const volatile uint8_t *>(s + i);
 }
+/* Completion of remote writes (the reference's smem_shm_roce_quiet / smem_shm_roce_poll_cq, which drain a queue pair's
+ * completion queue). There is no queue here: a store to a peer is complete for every observer once a system-scope fence
+ * issued after it has returned. quiet() is that fence for the calling thread; all threads that wrote call it (or a
+ * __syncthreads() follows and one thread fences, as smem_shm_signal does). poll_cq() reports how many work requests are
+ * still in flight after a fence: always 0. */
+__device__ __forceinline__ void smem_shm_roce_quiet(const smem_shm_device_ctx_t &c, uint32_t peer)
+{
+    (void)c;
+    (void)peer;
+    __threadfence_system();
+}
+__device__ __forceinline__ uint32_t smem_shm_roce_poll_cq(const smem_shm_device_ctx_t &c, uint32_t peer)
+{
+    smem_shm_roce_quiet(c, peer);
+    return 0;
+}
 #endif /* __CUDACC__ */
 #endif

@@ -120,7 +120,7 @@ __global__ void k_example_copy_helpers(smem_shm_device_ctx_t ctx, const uint8_t 
     extern __shared__ __align__(16) uint8_t ub[];
     cooperative_groups::grid_group grid = cooperative_groups::this_grid();
     smem_shm_roce_write(ctx, src, box, peer, bytes);
-    __threadfence_system();
+    smem_shm_roce_quiet(ctx, peer);   // this thread's writes are complete at the peer
     grid.sync();
     smem_shm_roce_read(ctx, box, back, peer, bytes);
     if (blockIdx.x == 0) {
