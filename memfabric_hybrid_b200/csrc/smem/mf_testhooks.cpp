@@ -338,6 +338,13 @@ void mf_t_trace_row(uint32_t id, uint64_t out[6])
     auto r = PTracer::Snapshot(id);
     out[0] = r.begin, out[1] = r.goodEnd, out[2] = r.badEnd, out[3] = r.minNs, out[4] = r.maxNs, out[5] = r.totalNs;
 }
+// out[0 .. buckets) per-bucket counts (bucket i: at most 1 us * 2^i), out[buckets] the slower ones, out[buckets + 1] the
+// sum of the durations in ns; -> number of buckets (call with out == NULL to size the array: buckets + 2 entries).
+uint32_t mf_t_trace_hist(uint32_t id, uint64_t *out)
+{
+    if (out != nullptr) PTracer::Histogram(id, out, out + PTracer::kHistBuckets + 1);
+    return PTracer::kHistBuckets;
+}
 const char *mf_t_trace_name(uint32_t id) { return TracePointName(id); }
 uint32_t mf_t_trace_count(void) { return TP_COUNT; }
 

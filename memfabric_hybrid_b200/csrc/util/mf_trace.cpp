@@ -23,6 +23,8 @@ namespace {
 struct Cell {
     std::atomic<uint64_t> begin{0}, good{0}, bad{0}, total{0};
     std::atomic<uint64_t> mn{UINT64_MAX}, mx{0};
+    std::atomic<uint64_t> hist[PTracer::kHistBuckets + 1] = {};
+    std::atomic<uint64_t> histSum{0};
 };
 Cell g_cells[TP_COUNT];
 Tracer g_tracer;
@@ -41,6 +43,10 @@ void DefEnd(uint32_t id, uint64_t t0, uint64_t t1, int32_t ret)
     uint64_t d = t1 > t0 ? t1 - t0 : 0;
     (ret == 0 ? c.good : c.bad).fetch_add(1, std::memory_order_relaxed);
     c.total.fetch_add(d, std::memory_order_relaxed);
+    uint32_t b = 0;   // smallest i with d <= 1000 ns << i
+    while (b < PTracer::kHistBuckets && d > (1000ULL << b)) b++;
+    c.hist[b].fetch_add(1, std::memory_order_relaxed);
+    c.histSum.fetch_add(d, std::memory_order_relaxed);
     uint64_t cur = c.mn.load(std::memory_order_relaxed);
     while (d < cur && !c.mn.compare_exchange_weak(cur, d)) {}
     cur = c.mx.load(std::memory_order_relaxed);
@@ -64,6 +70,17 @@ PTracer::Row PTracer::Snapshot(uint32_t id)
     r.maxNs = c.mx.load();
     r.totalNs = c.total.load();
     return r;
+}
+
+uint64_t PTracer::Histogram(uint32_t id, uint64_t counts[kHistBuckets + 1], uint64_t *sumNs)
+{
+    uint64_t n = 0;
+    for (uint32_t i = 0; i <= kHistBuckets; i++) {
+        counts[i] = id < TP_COUNT ? g_cells[id].hist[i].load(std::memory_order_relaxed) : 0;
+        n += counts[i];
+    }
+    if (sumNs != nullptr) *sumNs = id < TP_COUNT ? g_cells[id].histSum.load(std::memory_order_relaxed) : 0;
+    return n;
 }
 
 std::string PTracer::DumpTable(bool reset)

@@ -82,6 +82,11 @@ public:
         uint64_t begin, goodEnd, badEnd, minNs, maxNs, totalNs;
     };
     static Row Snapshot(uint32_t id);
+    // Latency histogram of a point since the tracer started (never reset by the periodic table): counts[i] for
+    // i < kHistBuckets = completed operations that took at most 1 us * 2^i, counts[kHistBuckets] = the slower ones.
+    // Not cumulative over buckets. -> number of completed operations; *sumNs their total duration.
+    static constexpr uint32_t kHistBuckets = 24;
+    static uint64_t Histogram(uint32_t id, uint64_t counts[kHistBuckets + 1], uint64_t *sumNs);
 };
 
 struct TraceScope {

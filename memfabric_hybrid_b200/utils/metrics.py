@@ -46,6 +46,33 @@ def _trace_rows() -> List[Tuple[str, Tuple[int, ...]]]:
     return rows
 
 
+def _trace_histograms() -> List[Tuple[Dict[str, str], float]]:
+    """Samples of the histogram family mf_trace_duration_seconds (cumulative ``le`` buckets, ``_sum``, ``_count``) for every
+    point that has completed an operation. The buckets double from 1 us; they cover the whole run (the periodic table,
+    which resets its own columns, leaves them alone)."""
+    l = N.lib()
+    l.mf_t_trace_count.restype = C.c_uint32
+    l.mf_t_trace_name.restype, l.mf_t_trace_name.argtypes = C.c_char_p, [C.c_uint32]
+    l.mf_t_trace_hist.restype, l.mf_t_trace_hist.argtypes = C.c_uint32, [C.c_uint32, C.POINTER(C.c_uint64)]
+    nb = l.mf_t_trace_hist(0, None)
+    out = []
+    for pid in range(l.mf_t_trace_count()):
+        buf = (C.c_uint64 * (nb + 2))()
+        l.mf_t_trace_hist(pid, buf)
+        if not any(buf[i] for i in range(nb + 1)):
+            continue
+        p = (l.mf_t_trace_name(pid) or b"?").decode()
+        acc = 0
+        for i in range(nb):
+            acc += buf[i]
+            out.append(({"point": p, "le": f"{1e-6 * (1 << i):.9g}", "__suffix__": "_bucket"}, float(acc)))
+        acc += buf[nb]
+        out.append(({"point": p, "le": "+Inf", "__suffix__": "_bucket"}, float(acc)))
+        out.append(({"point": p, "__suffix__": "_sum"}, buf[nb + 1] * 1e-9))
+        out.append(({"point": p, "__suffix__": "_count"}, float(acc)))
+    return out
+
+
 def collect() -> List[Tuple[str, str, str, List[Tuple[Dict[str, str], float]]]]:
     """[(family, type, help, [(labels, value)])]."""
     fams = []
@@ -62,6 +89,9 @@ def collect() -> List[Tuple[str, str, str, List[Tuple[Dict[str, str], float]]]]:
         fams.append(("mf_trace_min_seconds", "gauge", "fastest completed operation",
                      [({"point": p}, r[3] * 1e-9) for p, r in rows if r[1] + r[2]]))
         fam("mf_trace_max_seconds", "gauge", "slowest completed operation", 4, 1e-9)
+    hist = _trace_histograms()
+    if hist:
+        fams.append(("mf_trace_duration_seconds", "histogram", "duration of completed operations (buckets double from 1 us)", hist))
     if _pools:
         per_key: Dict[str, List[Tuple[Dict[str, str], float]]] = {}
         for name, h in list(_pools.items()):
@@ -73,6 +103,18 @@ def collect() -> List[Tuple[str, str, str, List[Tuple[Dict[str, str], float]]]]:
                 per_key.setdefault(k, []).append(({"pool": name}, float(v)))
         for k, vals in per_key.items():
             fams.append((f"mf_pool_{k}_total", "counter", f"copy path counter {k}", vals))
+        cap = []
+        for name, h in list(_pools.items()):
+            try:
+                from ..api import bm
+                for mem, label in ((bm.BmMemType.DEVICE, "device"), (bm.BmMemType.HOST, "host")):
+                    n = int(h.local_mem_size(mem))
+                    if n > 0:
+                        cap.append(({"pool": name, "mem": label}, float(n)))
+            except Exception:  # noqa: BLE001
+                continue
+        if cap:
+            fams.append(("mf_pool_local_bytes", "gauge", "bytes this rank contributes to the pool", cap))
     try:
         from ..zbal import _capi as K
         s = K.SmaStatsC()
@@ -103,8 +145,10 @@ def render() -> str:
         lines.append(f"# HELP {name} {hlp}")
         lines.append(f"# TYPE {name} {typ}")
         for labels, value in samples:
+            labels = dict(labels)
+            suffix = labels.pop("__suffix__", "")          # histogram samples: _bucket / _sum / _count
             lab = "{" + ",".join(f'{k}="{_esc(str(v))}"' for k, v in sorted(labels.items())) + "}" if labels else ""
-            lines.append(f"{name}{lab} {value:.9g}")
+            lines.append(f"{name}{suffix}{lab} {value:.9g}")
     return "\n".join(lines) + "\n"
 
 

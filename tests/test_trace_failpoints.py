@@ -78,6 +78,28 @@ def test_prometheus_exporter_serves_trace_table_and_allocator(tmp_path):
     l = H.lib()
     assert l.mf_t_trace_start(str(tmp_path).encode(), 60_000) == 0
     try:
+        def hist():
+            out = {}
+            for line in metrics.render().splitlines():
+                if line.startswith("mf_trace_duration_seconds") and f'point="{l.mf_t_trace_name(3).decode()}"' in line:
+                    key, val = line.rsplit(" ", 1)
+                    out[key.replace(f'point="{l.mf_t_trace_name(3).decode()}"', "").replace("{,", "{").replace(",}", "}").replace("{}", "")] = float(val)
+            return out
+        l.mf_t_trace_hit(3, 0, 1)                            # the point exists in the table from here on
+        before = hist()
+        for ret in (0, 0, -1):
+            l.mf_t_trace_hit(3, ret, 200)
+        after = hist()
+        d = {k: after[k] - before.get(k, 0) for k in after}
+        # three operations of at least 200 us each: none in the buckets up to 128 us, all of them counted at the top
+        assert d["mf_trace_duration_seconds_count"] == 3 and d['mf_trace_duration_seconds_bucket{le="+Inf"}'] == 3
+        assert d['mf_trace_duration_seconds_bucket{le="0.000128"}'] == 0 and d["mf_trace_duration_seconds_sum"] >= 600e-6
+        les = [float(k.split('le="')[1].rstrip('"}')) for k in after if "_bucket" in k and "+Inf" not in k]
+        assert les == sorted(les) and les[0] == 1e-6 and len(les) == 24
+        vals = [after[k] for k in after if "_bucket" in k]
+        assert vals == sorted(vals)                           # cumulative
+        l.mf_t_trace_dump(None, 0, 1)                         # the periodic table resets its own columns, not the histogram
+        assert hist()["mf_trace_duration_seconds_count"] == after["mf_trace_duration_seconds_count"]
         for ret in (0, 0, -1):
             l.mf_t_trace_hit(3, ret, 200)
         K.lib().zbal_simulate_init(0x7000_0000_0000, 64 << 20)
@@ -86,6 +108,7 @@ def test_prometheus_exporter_serves_trace_table_and_allocator(tmp_path):
         name = l.mf_t_trace_name(3).decode()
         assert f'mf_trace_calls_total{{point="{name}"}} 3' in text
         assert f'mf_trace_failed_total{{point="{name}"}} 1' in text and f'mf_trace_in_flight{{point="{name}"}} 0' in text
+        assert "# TYPE mf_trace_duration_seconds histogram" in text
         assert "# TYPE mf_trace_seconds_total counter" in text and "zbal_heap_in_use_bytes 4194304" in text
         port = metrics.serve(0)
         body = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=10).read().decode()
