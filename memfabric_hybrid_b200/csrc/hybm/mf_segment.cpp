@@ -302,7 +302,8 @@ int Segment::Import(const hybm_exchange_info &in, uint64_t *addr)
         !r.Take(p.token) || !r.TakeStr(p.source))
         return MF_FAIL(ERR_INVALID_PARAM, "malformed slice exchange blob");
     if (type != (uint32_t)opt_.type) return ERR_NOT_EXIST;  // belongs to the entity's other segment
-    if (h.rank >= opt_.rankCount || slot != opt_.slot || p.offset + p.size > opt_.slot)
+    // offset and size come from another process: compared one by one, their sum could wrap
+    if (h.rank >= opt_.rankCount || slot != opt_.slot || p.size == 0 || p.offset > opt_.slot || p.size > opt_.slot - p.offset)
         return MF_FAIL(ERR_INVALID_PARAM, "slice of rank %u does not match this pool's layout (slot %lu vs %lu)", h.rank,
                        (unsigned long)slot, (unsigned long)opt_.slot);
     if (base != base_)
@@ -525,11 +526,13 @@ protected:
         if (rc != OK) {
             close(fd);
             if (source[0] != '@') unlink(source.c_str());
+            else FdChannel::Get().Withdraw(token);
             return rc;
         }
         ownFds_[s.index] = fd;
         ownFiles_[s.index] = source;
-        if (source[0] != '@') Owned().Add(source);
+        if (source[0] == '@') ownTokens_[s.index] = token;
+        else Owned().Add(source);
         return OK;
     }
     int UnmapLocal(MemSlice &s) override
@@ -539,6 +542,11 @@ protected:
         if (f != ownFds_.end()) {
             close(f->second);
             ownFds_.erase(f);
+        }
+        auto t = ownTokens_.find(s.index);
+        if (t != ownTokens_.end()) {
+            FdChannel::Get().Withdraw(t->second);  // the descriptor kept for peers: without this the memory file outlives the pool
+            ownTokens_.erase(t);
         }
         auto n = ownFiles_.find(s.index);
         if (n != ownFiles_.end()) {
@@ -580,6 +588,7 @@ protected:
 private:
     std::map<uint32_t, int> ownFds_;
     std::map<uint32_t, std::string> ownFiles_;
+    std::map<uint32_t, uint64_t> ownTokens_;  // fd-channel tokens of the descriptors published for peers
 };
 
 class VmmSegment : public Segment {

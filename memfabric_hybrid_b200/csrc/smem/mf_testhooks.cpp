@@ -8,6 +8,7 @@
 
 #include "../net/mf_tls.h"
 #include "../group/mf_group.h"
+#include "../hybm/mf_entity.h"
 #include "../store/mf_store.h"
 #include "../store/mf_store_backend.h"
 #include "../store/mf_store_etcd.h"
@@ -347,6 +348,76 @@ uint32_t mf_t_trace_hist(uint32_t id, uint64_t *out)
 }
 const char *mf_t_trace_name(uint32_t id) { return TracePointName(id); }
 uint32_t mf_t_trace_count(void) { return TP_COUNT; }
+
+// ---- exchange records of the memory layer ------------------------------------------------------------------
+// A host-memory entity that stands for rank `rank` of `ranks`; its own exchange records can be read out and records
+// from elsewhere (a peer's, or damaged ones) imported and mapped.
+struct ExBox {
+    hybm::EntityPtr e;
+    hybm::MemSlice *slice = nullptr;
+};
+void *mf_t_ex_new(uint16_t id, uint32_t rank, uint32_t ranks, uint64_t slot, uint64_t local)
+{
+    if (hybm::HybmInit(0xFFFF, 0) != OK) return nullptr;
+    hybm_options ho{};
+    ho.bmType = HYBM_TYPE_HOST_INITIATE;
+    ho.memType = HYBM_MEM_TYPE_HOST;
+    ho.bmDataOpType = HYBM_DOP_TYPE_HOST_SHM;
+    ho.rankCount = ranks;
+    ho.rankId = rank;
+    ho.maxDRAMSize = slot;
+    ho.scene = HYBM_SCENE_DEFAULT;
+    ho.role = HYBM_ROLE_PEER;
+    ho.dramShmFd = -1;
+    auto e = hybm::Entity::Create(id, ho);
+    if (!e || e->ReserveMemSpace(0) != OK) {
+        hybm::HybmUninit();
+        return nullptr;
+    }
+    auto *b = new ExBox{e, nullptr};
+    if (local != 0 && e->AllocLocal(HYBM_MEM_TYPE_HOST, local, 0, &b->slice) != OK) {
+        e->UnreserveMemSpace();
+        delete b;
+        hybm::HybmUninit();
+        return nullptr;
+    }
+    return b;
+}
+void mf_t_ex_free(void *h)
+{
+    auto *b = static_cast<ExBox *>(h);
+    b->e->Unmap();
+    b->e->UnreserveMemSpace();
+    delete b;
+    hybm::HybmUninit();
+}
+uint32_t mf_t_ex_record_size(void) { return (uint32_t)sizeof(hybm_exchange_info); }
+// out: room for two records (the entity's and its slice's); -> number of records written or a negative code
+int mf_t_ex_export(void *h, uint8_t *out)
+{
+    auto *b = static_cast<ExBox *>(h);
+    auto *recs = reinterpret_cast<hybm_exchange_info *>(out);
+    int rc = b->e->Export(nullptr, &recs[0]);
+    if (rc != OK) return rc;
+    if (b->slice == nullptr) return 1;
+    rc = b->e->Export(b->slice, &recs[1]);
+    return rc != OK ? rc : 2;
+}
+// records: count * mf_t_ex_record_size() bytes. map != 0: maps what was imported as well. -> the first error code
+int mf_t_ex_import(void *h, const uint8_t *records, uint32_t count, int map)
+{
+    auto *b = static_cast<ExBox *>(h);
+    std::vector<hybm_exchange_info> v(count);
+    memcpy(v.data(), records, (size_t)count * sizeof(hybm_exchange_info));
+    int rc = b->e->Import(v.data(), count, nullptr);
+    if (rc == OK && map != 0) rc = b->e->Mmap();
+    return rc;
+}
+uint64_t mf_t_ex_mapped_bytes(void *h, uint32_t rank)
+{
+    auto seg = static_cast<ExBox *>(h)->e->SegmentOf(HYBM_MEM_TYPE_HOST);
+    return seg ? seg->MappedBytes(rank) : 0;
+}
 
 // ---- fault points -------------------------------------------------------------------------------------
 // Runs the periodic TLS certificate check now; -> the smallest number of days left over the live contexts.

@@ -66,6 +66,12 @@ def lib():
     s(l, "mf_t_etcd_try_lock", i32, vp, cp)
     s(l, "mf_t_etcd_unlock", i32, vp, cp)
     s(l, "mf_t_etcd_last_error", i32, vp, cp, i32)
+    s(l, "mf_t_ex_new", vp, u16, u32, u32, u64, u64)
+    s(l, "mf_t_ex_free", None, vp)
+    s(l, "mf_t_ex_record_size", u32)
+    s(l, "mf_t_ex_export", i32, vp, cp)
+    s(l, "mf_t_ex_import", i32, vp, cp, u32, i32)
+    s(l, "mf_t_ex_mapped_bytes", u64, vp, u32)
     s(l, "mf_t_backend_set_reachable", None, cp, i32)
     s(l, "mf_t_backend_reset", None, cp)
     s(l, "mf_t_group_new", vp, vp, u32, u32, u64, i32, CHANGE_CB)

@@ -8,7 +8,7 @@ import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 FILES = ["test_config_store.py", "test_group_engine.py", "test_ha_store.py", "test_trace_failpoints.py", "test_transfer_cpu.py",
-         "test_shm_api_cpu.py", "test_bm_host_pool.py", "test_fake_device_pool.py", "test_zbal_cpu.py", "test_store_tls.py", "test_etcd_backend.py"]
+         "test_shm_api_cpu.py", "test_bm_host_pool.py", "test_fake_device_pool.py", "test_zbal_cpu.py", "test_store_tls.py", "test_etcd_backend.py", "test_fuzz_cpu.py"]
 
 
 def test_host_tests_are_clean_under_asan_and_ubsan():
