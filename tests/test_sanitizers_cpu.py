@@ -21,7 +21,7 @@ def test_host_tests_are_clean_under_asan_and_ubsan():
                ASAN_OPTIONS="detect_leaks=0:halt_on_error=1:abort_on_error=0", UBSAN_OPTIONS="print_stacktrace=1")
     # -s: a sanitizer report must reach this process's pipe; the c10d extension is not part of the sanitizer build
     r = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-s", "-p", "no:cacheprovider", "-k", "not native"] +
-                       [os.path.join(ROOT, "tests", f) for f in FILES], env=env, capture_output=True, text=True, timeout=1500, cwd=ROOT)
+                       [os.path.join(ROOT, "tests", f) for f in FILES], env=env, capture_output=True, text=True, errors="replace", timeout=1500, cwd=ROOT)   # log lines may quote fuzzed bytes
     out = r.stdout + r.stderr
     assert "runtime error:" not in out and "ERROR: AddressSanitizer" not in out, out[-4000:]
     assert r.returncode == 0, out[-4000:]
