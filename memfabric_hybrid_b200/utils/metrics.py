@@ -36,11 +36,11 @@ def _trace_rows() -> List[Tuple[str, Tuple[int, ...]]]:
     l = N.lib()
     l.mf_t_trace_count.restype = C.c_uint32
     l.mf_t_trace_name.restype, l.mf_t_trace_name.argtypes = C.c_char_p, [C.c_uint32]
-    l.mf_t_trace_row.restype, l.mf_t_trace_row.argtypes = None, [C.c_uint32, C.POINTER(C.c_uint64)]
+    l.mf_t_trace_row.restype, l.mf_t_trace_row.argtypes = None, [C.c_uint32, C.POINTER(C.c_uint64 * 6)]
     rows = []
     for i in range(l.mf_t_trace_count()):
         out = (C.c_uint64 * 6)()
-        l.mf_t_trace_row(i, out)
+        l.mf_t_trace_row(i, C.byref(out))
         if out[0]:
             rows.append(((l.mf_t_trace_name(i) or b"?").decode(), tuple(int(v) for v in out)))
     return rows
