@@ -5,6 +5,7 @@ truncation, inflated length fields, splices, noise). Whatever arrives, the proce
 service must keep working for well-behaved peers. The sanitizer tier runs this file against the ASAN + UBSAN build.
 Seeds are fixed: a failure reproduces."""
 import ctypes as C
+import os
 import random
 import socket
 import threading
@@ -12,6 +13,8 @@ import time
 
 import hooks as H  # noqa: E402
 from conftest import free_port  # noqa: E402
+
+SEED = int(os.environ.get("MF_FUZZ_SEED", "0"))   # other values explore other mutations
 
 
 class RecordingProxy:
@@ -114,7 +117,7 @@ def _record_conversation():
 def test_store_server_survives_malformed_frames():
     port, srv, up, _ = _record_conversation()
     assert len(up) > 100
-    rng = random.Random(20240611)
+    rng = random.Random(20240611 + SEED)
     try:
         for i in range(400):
             payload = _mutate(rng, up)
@@ -150,7 +153,7 @@ def test_store_client_survives_malformed_replies():
     port, srv, _, down = _record_conversation()
     H.lib().mf_t_server_stop(srv)
     assert len(down) > 50
-    rng = random.Random(77)
+    rng = random.Random(77 + SEED)
     lsock = socket.socket()
     lsock.bind(("127.0.0.1", 0))
     lsock.listen(16)
@@ -199,7 +202,7 @@ def test_parsers_refuse_garbage_without_crashing(tmp_path):
     """Store URLs, TLS settings, fail-point files and the etcd gateway's replies."""
     from memfabric_hybrid_b200 import api
     from fake_etcd import FakeEtcd
-    rng = random.Random(5)
+    rng = random.Random(5 + SEED)
     alphabet = "tcpetdrg:/#.0123456789[]-_@ ;,=\\\x00\xff"
     for _ in range(300):
         url = "".join(rng.choice(alphabet) for _ in range(rng.randint(0, 40)))
@@ -291,7 +294,7 @@ def _exchange_records(rank, world):
         assert l.mf_t_ex_import(me, good, 2, 0) == 0      # well-formed records are accepted ...
         assert l.mf_t_ex_import(me, good, 2, 1) != 0      # ... and mapping the vanished peer fails cleanly
         assert l.mf_t_ex_mapped_bytes(me, 1) == 0 and l.mf_t_ex_mapped_bytes(me, 0) == 2 * MiB
-        rng = random.Random(99)
+        rng = random.Random(99 + SEED)
         used = C.c_uint32.from_buffer_copy(good[rs - 4:rs]).value      # descLen of the first record
         assert 0 < used <= rs - 4
         # every 64-bit field of the slice record pushed to extremes (offsets and sizes that wrap when added among them)
