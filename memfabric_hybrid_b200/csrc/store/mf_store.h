@@ -171,6 +171,7 @@ private:
     std::vector<BrokenFn> brokenFns_;
     std::thread hb_;
     std::thread reconnector_;
+    std::mutex reMu_;  // reconnector_: started by a link's worker thread when the link breaks, joined by Shutdown
     std::mutex hbMu_;
     std::condition_variable hbCv_;
     std::atomic<bool> running_{false};

@@ -90,7 +90,16 @@ void TcpStoreClient::Shutdown()
         hbCv_.notify_all();
     }
     JoinOrDetach(hb_);
-    JoinOrDetach(reconnector_);
+    {
+        // A link that breaks right now may be about to start the reconnector on its worker thread: take the thread out
+        // under the lock (whoever gets the lock after us sees running_ == false and starts nothing).
+        std::thread re;
+        {
+            std::lock_guard<std::mutex> g(reMu_);
+            re.swap(reconnector_);
+        }
+        JoinOrDetach(re);
+    }
     {
         std::lock_guard<std::mutex> g(linkMu_);
         if (link_) link_->Shutdown();
@@ -192,6 +201,7 @@ void TcpStoreClient::OnBroken()
         fns = brokenFns_;
     }
     for (auto &f : fns) f();
+    std::lock_guard<std::mutex> rg(reMu_);
     if (!running_ || reconnectTries_ == 0 || reconnecting_.exchange(true)) return;
     JoinOrDetach(reconnector_);
     reconnector_ = std::thread([this] {

@@ -193,6 +193,17 @@ def test_store_client_survives_malformed_replies():
             st.set("x", b"y")
             st.close()
             assert time.monotonic() - t0 < 8.0
+        # a link that breaks at the very moment its owner lets go of the client (the worker thread starts a redial while
+        # the caller shuts down): many quick rounds of "handshake answered, connection dropped, client closed at once"
+        state["payload"] = down
+        for i in range(60):
+            try:
+                st = H.Store.connect(fport, world=4, rank=1, timeout_ms=400)
+            except ConnectionError:
+                continue
+            if i % 3 == 0:
+                time.sleep(0.001 * (i % 7))
+            st.close()
     finally:
         state["run"] = False
         lsock.close()
