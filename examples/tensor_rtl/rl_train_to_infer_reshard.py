@@ -38,7 +38,7 @@ def main(rank: int, world: int, port: int, moe: bool) -> str:
                                                               train_shard_of)
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     cfg = dict(MODEL, num_experts=4, moe_ffn=32) if moe else MODEL
-    specs, meta = decoder_specs(**cfg, fuse_for_inference=moe)
+    specs, meta = decoder_specs(**cfg, fuse_for_inference=moe, qkv_bias=not moe, qk_norm=moe)   # dense: Qwen2-like, routed: Qwen3-like
     train = TrainLayout(tp=2, pp=2, ep=2 if moe else 1)
     infer = InferLayout(tp=2, ranks=[1, 3], ep=2 if moe else 1)
     job = TrainToInferResharder(specs, train, infer, rank, All2AllVExecutor(), meta, backend="gloo", bucket_bytes=64 << 10)

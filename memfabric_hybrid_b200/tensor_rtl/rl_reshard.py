@@ -108,9 +108,12 @@ class ParamSpec:
 
 
 def decoder_specs(num_layers: int, hidden: int, ffn: int, heads: int, kv_heads: int, head_dim: int, vocab: int,
-                  num_experts: int = 0, moe_ffn: int = 0, tie_embeddings: bool = False, fuse_for_inference: bool = False) -> Tuple[List[ParamSpec], dict]:
+                  num_experts: int = 0, moe_ffn: int = 0, tie_embeddings: bool = False, fuse_for_inference: bool = False,
+                  qkv_bias: bool = False, qk_norm: bool = False) -> Tuple[List[ParamSpec], dict]:
     """Parameter table of a Llama / Qwen style decoder in Megatron-core naming on the training side and Hugging Face
     naming on the inference side. With ``num_experts`` the MLP of every layer is a routed mixture (router + experts).
+    ``qkv_bias``: the attention projections carry a bias (Qwen2; fused and interleaved per query group like the weight);
+    ``qk_norm``: a per-head RMS norm on queries and keys (Qwen3; replicated).
     -> (specs, meta) where meta carries num_layers / num_experts for the layouts."""
     specs: List[ParamSpec] = []
     q, kv = heads * head_dim, kv_heads * head_dim
@@ -122,6 +125,14 @@ def decoder_specs(num_layers: int, hidden: int, ffn: int, heads: int, kv_heads: 
                                blocks=[Block(h + "self_attn.q_proj.weight", q), Block(h + "self_attn.k_proj.weight", kv),
                                        Block(h + "self_attn.v_proj.weight", kv)],
                                infer_fused_name=h + "self_attn.qkv_proj.weight" if fuse_for_inference else None))
+        if qkv_bias:
+            specs.append(ParamSpec(t + "self_attention.linear_qkv.bias", (q + 2 * kv,), 0, layer=i, groups=kv_heads,
+                                   blocks=[Block(h + "self_attn.q_proj.bias", q), Block(h + "self_attn.k_proj.bias", kv),
+                                           Block(h + "self_attn.v_proj.bias", kv)],
+                                   infer_fused_name=h + "self_attn.qkv_proj.bias" if fuse_for_inference else None))
+        if qk_norm:
+            specs.append(ParamSpec(t + "self_attention.q_layernorm.weight", (head_dim,), -1, infer_name=h + "self_attn.q_norm.weight", layer=i))
+            specs.append(ParamSpec(t + "self_attention.k_layernorm.weight", (head_dim,), -1, infer_name=h + "self_attn.k_norm.weight", layer=i))
         specs.append(ParamSpec(t + "self_attention.linear_proj.weight", (hidden, q), 1, infer_name=h + "self_attn.o_proj.weight", layer=i))
         if num_experts == 0:
             specs.append(ParamSpec(t + "mlp.linear_fc1.layer_norm_weight", (hidden,), -1, infer_name=h + "post_attention_layernorm.weight", layer=i))

@@ -174,12 +174,16 @@ def test_rl_reshard_splits_fused_training_shards():
     group) and a linear_fc1 shard (gate, up) come apart into the separately sharded blocks, on every tensor-parallel rank."""
     from memfabric_hybrid_b200.tensor_rtl.rl_reshard import (InferLayout, TrainLayout, TrainToInferResharder, decoder_specs,
                                                               train_shard_of)
-    specs, meta = decoder_specs(num_layers=2, hidden=32, ffn=48, heads=8, kv_heads=4, head_dim=4, vocab=64)
+    specs, meta = decoder_specs(num_layers=2, hidden=32, ffn=48, heads=8, kv_heads=4, head_dim=4, vocab=64, qkv_bias=True, qk_norm=True)
     qkv = next(s for s in specs if s.train_name.endswith("layers.0.self_attention.linear_qkv.weight"))
+    bias = next(s for s in specs if s.train_name.endswith("layers.0.self_attention.linear_qkv.bias"))
     fc1 = next(s for s in specs if s.train_name.endswith("layers.1.mlp.linear_fc1.weight"))
+    norms = [s for s in specs if "layernorm.weight" in s.train_name and ("q_layernorm" in s.train_name or "k_layernorm" in s.train_name)]
+    assert len(norms) == 4 and all(s.shard_dim == -1 and s.shape == (4,) for s in norms)
+    assert [b.infer_name.rsplit(".", 2)[-2:] for b in bias.the_blocks()] == [["q_proj", "bias"], ["k_proj", "bias"], ["v_proj", "bias"]]
     g = torch.Generator().manual_seed(1)
-    for spec in (qkv, fc1):
-        full = [torch.randn(b.size, 32, generator=g) for b in spec.the_blocks()]
+    for spec in (qkv, fc1, bias):
+        full = [torch.randn(*((b.size, 32) if len(spec.shape) == 2 else (b.size,)), generator=g) for b in spec.the_blocks()]
         for tp in (1, 2, 4):
             for t in range(tp):
                 job = TrainToInferResharder(specs, TrainLayout(tp=tp, pp=1), InferLayout(tp=1, ranks=[0]), rank=t, executor=None, meta=meta)
