@@ -77,24 +77,35 @@ def _build_objs(srcs: list[Path], cmd: list[str], flags: list[str], tag: str, jo
 SAN_FLAGS = ["-fsanitize=address,undefined,pointer-compare,pointer-subtract", "-fno-omit-frame-pointer", "-fno-sanitize-recover=undefined"]
 
 
-def build_host(jobs: int | None = None, asan: bool = False) -> Path:
+TSAN_FLAGS = ["-fsanitize=thread", "-fno-omit-frame-pointer"]
+
+
+def build_host(jobs: int | None = None, asan: bool = False, tsan: bool = False) -> Path:
     """``asan=True``: the same sources under AddressSanitizer + UndefinedBehaviorSanitizer into ``lib_asan/``
-    (load it with MF_NATIVE_LIB_DIR and LD_PRELOAD of the compiler's libasan.so)."""
+    (load it with MF_NATIVE_LIB_DIR and LD_PRELOAD of the compiler's libasan.so). ``tsan=True``: under ThreadSanitizer
+    into ``lib_tsan/`` (LD_PRELOAD of libtsan.so)."""
     jobs = jobs or os.cpu_count() or 4
     srcs = [p for d in HOST_DIRS for p in sorted((CSRC / d).glob("*.cpp"))]
     flags = CXXFLAGS + [f"-I{CSRC / 'include'}", f"-I{CSRC}"]
-    libdir = LIB
-    if asan:
-        flags = [f for f in flags if f not in ("-O2", "-D_FORTIFY_SOURCE=2")] + ["-O1"] + SAN_FLAGS
-        libdir = PKG / "lib_asan"
-    objs = _build_objs(srcs, ["g++"], flags, "asan" if asan else "host", jobs)
+    libdir, san, tag = LIB, [], "host"
+    if asan or tsan:
+        san = SAN_FLAGS if asan else TSAN_FLAGS
+        flags = [f for f in flags if f not in ("-O2", "-D_FORTIFY_SOURCE=2")] + ["-O1"] + san
+        libdir, tag = (PKG / "lib_asan", "asan") if asan else (PKG / "lib_tsan", "tsan")
+    objs = _build_objs(srcs, ["g++"], flags, tag, jobs)
     libdir.mkdir(exist_ok=True)
     out = libdir / "libmf_smem.so"
     tmp = out.with_suffix(f".so.{os.getpid()}.tmp")
-    subprocess.run(["g++", "-shared", "-o", str(tmp)] + [str(o) for o in objs] + (SAN_FLAGS if asan else []) +
+    subprocess.run(["g++", "-shared", "-o", str(tmp)] + [str(o) for o in objs] + san +
                    ["-pthread", "-ldl", "-lrt", "-Wl,-z,relro,-z,now"], check=True)
     tmp.replace(out)
     return out
+
+
+def tsan_runtime() -> str | None:
+    """Path of the compiler's libtsan.so (to LD_PRELOAD under Python), or None."""
+    p = subprocess.run(["gcc", "-print-file-name=libtsan.so"], capture_output=True, text=True).stdout.strip()
+    return p if os.path.isabs(p) and os.path.exists(p) else None
 
 
 def asan_runtime() -> str | None:
@@ -188,6 +199,9 @@ if __name__ == "__main__":
     if "--asan" in args:
         print(build_host(asan=True))
         args.discard("--asan")
+    if "--tsan" in args:
+        print(build_host(tsan=True))
+        args.discard("--tsan")
         if not args:
             sys.exit(0)
     if not args or "--host" in args:

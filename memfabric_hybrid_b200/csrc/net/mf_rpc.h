@@ -56,7 +56,7 @@ public:
     // Sends one frame; thread-safe. Returns OK or ERR_NOT_CONNECTED.
     int Send(int16_t type, int16_t result, uint32_t seqNo, const void *body, uint32_t len);
     void Shutdown();  // wakes the worker which then reports the link as broken
-    void *userData = nullptr;
+    std::atomic<void *> userData{nullptr};  // set by a handler thread, read by timers
     std::atomic<uint64_t> lastSeenMs{0};
 
 private:

@@ -122,7 +122,11 @@ public:
     int AutoRank(uint32_t &rank) override;
     void RegisterReconnectHandler(ReconnectFn fn) override;
     void RegisterBrokenHandler(BrokenFn fn) override;
-    bool Connected() const override { return link_ && link_->Alive(); }
+    bool Connected() const override
+    {
+        std::lock_guard<std::mutex> g(linkMu_);  // the reconnector replaces link_ under this lock
+        return link_ && link_->Alive();
+    }
     uint32_t Rank() const override { return rank_; }
     void SetReconnectPolicy(uint32_t tries, uint32_t intervalMs)
     {
@@ -160,7 +164,7 @@ private:
     uint32_t rank_;
     std::unique_ptr<net::Endpoint> ep_;
     net::LinkPtr link_;
-    std::mutex linkMu_;
+    mutable std::mutex linkMu_;
     std::atomic<uint32_t> seq_{1};
     std::mutex pendMu_;
     std::unordered_map<uint32_t, std::shared_ptr<Pending>> pending_;

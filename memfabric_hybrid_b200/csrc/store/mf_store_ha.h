@@ -62,7 +62,7 @@ private:
     uint32_t worldSize_;
     uint32_t rank_;
     BackendPtr backend_;
-    bool candidate_;
+    std::atomic<bool> candidate_;
     std::atomic<bool> leader_{false};
     std::atomic<bool> running_{false};
     std::mutex mu_;

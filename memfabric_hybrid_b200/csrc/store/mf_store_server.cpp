@@ -37,6 +37,7 @@ StoreServer::~StoreServer() { Shutdown(); }
 
 void StoreServer::SetBackend(std::shared_ptr<StoreBackend> b, bool firstLeader)
 {
+    std::lock_guard<std::mutex> g(rankMu_);  // a server that is already accepting links reads all of this under the same lock
     backend_ = std::move(b);
     if (!backend_ || firstLeader) return;
     std::string v;
@@ -457,7 +458,7 @@ void StoreServer::HWatchRank(const net::LinkPtr &l, const net::MsgHeader &h, Sto
 
 void StoreServer::HHeartbeat(const net::LinkPtr &l, const net::MsgHeader &, StoreMessage &)
 {
-    l->userData = reinterpret_cast<void *>(1);  // this peer heartbeats: the checker may judge it
+    l->userData.store(reinterpret_cast<void *>(1), std::memory_order_relaxed);  // this peer heartbeats: the checker may judge it
 }
 
 void StoreServer::HUnwatch(const net::LinkPtr &l, const net::MsgHeader &, StoreMessage &m)
@@ -511,7 +512,7 @@ void StoreServer::TimerLoop()
                     MF_INFO("store recovery window closed");
                 }
                 for (auto &kv : allLinks_) {
-                    if (kv.second->userData == nullptr) continue;
+                    if (kv.second->userData.load(std::memory_order_relaxed) == nullptr) continue;
                     if (now - kv.second->lastSeenMs.load() > (uint64_t)kMissedHeartbeats * hb) dead.push_back(kv.second);
                 }
             }

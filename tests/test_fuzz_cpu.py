@@ -15,6 +15,7 @@ import hooks as H  # noqa: E402
 from conftest import free_port  # noqa: E402
 
 SEED = int(os.environ.get("MF_FUZZ_SEED", "0"))   # other values explore other mutations
+LIGHT = 4 if os.environ.get("MF_FUZZ_LIGHT") else 1   # the ThreadSanitizer tier runs a quarter of the rounds (it is 10 x slower)
 
 
 class RecordingProxy:
@@ -119,7 +120,7 @@ def test_store_server_survives_malformed_frames():
     assert len(up) > 100
     rng = random.Random(20240611 + SEED)
     try:
-        for i in range(400):
+        for i in range(400 // LIGHT):
             payload = _mutate(rng, up)
             if rng.random() < 0.3:
                 payload = _mutate(rng, payload)
@@ -137,7 +138,7 @@ def test_store_server_survives_malformed_frames():
                 pass
             finally:
                 s.close()
-            if i % 100 == 99:      # the service is intact for a well-behaved client in between
+            if i % 50 == 49:      # the service is intact for a well-behaved client in between
                 st = H.Store.connect(port, world=4, rank=2)
                 assert st.set(f"ok/{i}", b"v") == 0 and st.get(f"ok/{i}") == b"v"
                 st.close()
@@ -180,7 +181,7 @@ def test_store_client_survives_malformed_replies():
                 c.close()
     threading.Thread(target=serve, daemon=True).start()
     try:
-        for i in range(120):
+        for i in range(120 // LIGHT):
             state["payload"] = down if i == 0 else _mutate(rng, down)
             t0 = time.monotonic()
             try:
@@ -196,7 +197,7 @@ def test_store_client_survives_malformed_replies():
         # a link that breaks at the very moment its owner lets go of the client (the worker thread starts a redial while
         # the caller shuts down): many quick rounds of "handshake answered, connection dropped, client closed at once"
         state["payload"] = down
-        for i in range(60):
+        for i in range(60 // LIGHT):
             try:
                 st = H.Store.connect(fport, world=4, rank=1, timeout_ms=400)
             except ConnectionError:
@@ -286,6 +287,7 @@ def _exchange_records(rank, world):
     rs = l.mf_t_ex_record_size()
     import os
     warm = l.mf_t_ex_new(21, 1, 2, 64 * MiB, 2 * MiB)     # first use starts the descriptor channel's listener
+    assert warm
     l.mf_t_ex_free(warm)
     fds = len(os.listdir("/proc/self/fd"))
     for _ in range(5):                                     # a pool that goes away takes its memory file with it

@@ -25,3 +25,27 @@ def test_host_tests_are_clean_under_asan_and_ubsan():
     out = r.stdout + r.stderr
     assert "runtime error:" not in out and "ERROR: AddressSanitizer" not in out, out[-4000:]
     assert r.returncode == 0, out[-4000:]
+
+
+TSAN_FILES = ["test_config_store.py", "test_ha_store.py", "test_group_engine.py", "test_etcd_backend.py", "test_fuzz_cpu.py", "test_store_tls.py",
+              "test_trace_failpoints.py"]
+
+
+def test_control_plane_is_free_of_data_races_under_tsan():
+    """The threaded part of the host library (RPC endpoints, store client / server, the highly available store, the etcd
+    backend, the group engine, tracer and fault points) once more against ``lib_tsan/libmf_smem.so``. The memory pools stay
+    out: their fixed address windows lie where ThreadSanitizer keeps its shadow memory."""
+    from memfabric_hybrid_b200 import _build
+    rt = _build.tsan_runtime()
+    if rt is None:
+        pytest.skip("the compiler ships no libtsan.so")
+    lib = _build.build_host(tsan=True)
+    env = dict(os.environ, LD_PRELOAD=rt, MF_NATIVE_LIB_DIR=os.path.dirname(str(lib)), MF_FUZZ_LIGHT="1",
+               OPENBLAS_NUM_THREADS="1", OMP_NUM_THREADS="1",       # no library threads around when a test forks
+               TSAN_OPTIONS="halt_on_error=0:report_signal_unsafe=0:history_size=4:exitcode=0")
+    r = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-s", "-p", "no:cacheprovider", "-k", "not native and not exchange_records"] +
+                       [os.path.join(ROOT, "tests", f) for f in TSAN_FILES], env=env, capture_output=True, text=True, errors="replace",
+                       timeout=2400, cwd=ROOT)
+    out = r.stdout + r.stderr
+    assert "WARNING: ThreadSanitizer" not in out, out[out.find("WARNING: ThreadSanitizer"):][:6000]
+    assert r.returncode == 0, out[-4000:]
