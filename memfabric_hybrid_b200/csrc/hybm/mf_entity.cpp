@@ -135,6 +135,16 @@ int Entity::ReserveMemSpace(uint32_t attempt)
     if ((opt_.memType & HYBM_MEM_TYPE_HOST) != 0 && opt_.maxDRAMSize != 0 && !dram_) {
         so.type = HYBM_MEM_TYPE_HOST;
         so.slot = AlignUp(opt_.maxDRAMSize, 2ULL << 20);
+        if (opt_.enable56BitsGva && so.slot > kCompactThreshold / so.rankCount) {
+            // too large to map whole: callers get 56-bit addresses, the process a compact window (mf_hybm_types.h)
+            if (so.slot > kGva56WindowStride / so.rankCount)
+                return MF_FAIL(ERR_INVALID_PARAM, "a DRAM pool of %u ranks x %lu bytes exceeds the 1 PiB of a 56-bit address window",
+                               so.rankCount, (unsigned long)so.slot);
+            so.publicSlot = so.slot;
+            so.slot = CompactSlot(so.rankCount);
+            MF_INFO("DRAM pool %u: 56-bit addresses, %lu bytes per rank for callers, %lu mapped per rank in this process", id_,
+                    (unsigned long)so.publicSlot, (unsigned long)so.slot);
+        }
         auto seg = Segment::Create(so);
         int rc = seg ? seg->Reserve(attempt) : ERR_NOT_INIT;
         if (rc != OK) {
@@ -163,7 +173,7 @@ int Entity::UnreserveMemSpace()
 void *Entity::MemoryPtr(hybm_mem_type t)
 {
     auto seg = SegmentOf(t);
-    return seg ? reinterpret_cast<void *>(seg->Base()) : nullptr;
+    return seg ? reinterpret_cast<void *>(seg->PubBase()) : nullptr;
 }
 
 uint64_t Entity::LocalBytes(hybm_mem_type t)
@@ -464,14 +474,15 @@ int Entity::TranslateRemote(uint32_t rank, uint64_t addr, uint64_t len, RemoteRe
 }
 
 // ------------------------------------------------------------------------------------------------
-bool Entity::InPool(const SegmentPtr &seg, uint64_t addr, uint64_t len, int &err) const
+bool Entity::InPool(const SegmentPtr &seg, uint64_t addr, uint64_t len, int &err, uint64_t *local) const
 {
     if (!seg || seg->Base() == 0) return false;
-    uint64_t base = seg->Base(), slot = seg->Slot();
+    uint64_t base = seg->PubBase(), slot = seg->PubSlot();
     if (addr < base) return false;
     uint64_t rel = addr - base;
-    uint32_t rank = (uint32_t)(rel / slot);
-    if (rank >= opt_.rankCount) return false;
+    uint64_t rank64 = rel / slot;
+    if (rank64 >= opt_.rankCount) return false;
+    uint32_t rank = (uint32_t)rank64;
     uint64_t off = rel - (uint64_t)rank * slot;
     const uint64_t mapped = seg->MappedBytes(rank);
     if (len > mapped || off > mapped - len) {  // written so that a huge len cannot wrap the sum
@@ -479,6 +490,7 @@ bool Entity::InPool(const SegmentPtr &seg, uint64_t addr, uint64_t len, int &err
         return true;
     }
     err = OK;
+    if (local != nullptr) *local = seg->Compact() ? seg->LocalOf(rank, off) : addr;  // 56-bit addresses are numbers: where it is mapped here
     return true;
 }
 
@@ -518,7 +530,7 @@ int Entity::Resolve(uint64_t addr, uint64_t len, bool isSrc, hybm_data_copy_dire
         ep.kind = EP_DEVICE;
         return OK;
     }
-    if (InPool(dram_, addr, len, err)) {
+    if (InPool(dram_, addr, len, err, &ep.addr)) {
         if (err != OK) return err;
         if (want != AC_NONE && want != AC_GH) return ERR_INVALID_PARAM;
         ep.kind = EP_HOST_PINNED;
@@ -667,6 +679,9 @@ int Entity::QuantCopy(const hybm_quant_copy_params &p, int mode)
     // window (the caller's own device buffers) are taken as given, as in the copy paths.
     auto pooled = [&](uint64_t addr, uint64_t len, const char *what, uint32_t i) -> int {
         int err = OK;
+        if (dram_ && dram_->Compact() && InPool(dram_, addr, len, err))
+            return MF_FAIL(ERR_INVALID_PARAM, "quant copy item %u: %s %#lx is a 56-bit DRAM pool address, which the quantising kernel cannot reach", i, what,
+                           (unsigned long)addr);
         if ((InPool(hbm_, addr, len, err) || InPool(dram_, addr, len, err)) && err != OK)
             return MF_FAIL(err, "quant copy item %u: %s %#lx (+%lu bytes) %s", i, what, (unsigned long)addr, (unsigned long)len,
                            err == ERR_NOT_CONNECTED ? "lies in the slice of a rank that is not mapped here" : "runs past the mapped part of the pool");

@@ -90,7 +90,8 @@ public:
 private:
     // Resolves one side of a copy to how it can be accessed. Returns OK or an error for a bad range.
     int Resolve(uint64_t addr, uint64_t len, bool isSrc, hybm_data_copy_direction dir, Endpoint &ep);
-    bool InPool(const SegmentPtr &seg, uint64_t addr, uint64_t len, int &err) const;
+    // local (optional): where the range is mapped in this process (the address itself unless the segment is compact)
+    bool InPool(const SegmentPtr &seg, uint64_t addr, uint64_t len, int &err, uint64_t *local = nullptr) const;
     bool PinnedHost(uint64_t addr, uint64_t len);
     void PublishCopyWindow();  // MF_XCOPY_DEBUG=1: hands the copy kernels the pool window they check descriptors against
     std::mutex pinMu_;

@@ -127,7 +127,9 @@ int32_t hybm_gva_to_va(uint64_t gva, hybm_mem_type, uint64_t *va)
     ReservedRange r;
     uint32_t rank = 0;
     if (!VaManager::Get().Locate(gva, r, rank)) return BM_INVALID_PARAM;
-    *va = gva;
+    // ... except in a window of 56-bit addresses, whose slots are mapped in a compact window of this process
+    *va = r.localSlot == 0 ? gva : r.localBase + (uint64_t)rank * r.localSlot + (gva - r.base - (uint64_t)rank * r.slot);
+    if (r.localSlot != 0 && gva - r.base - (uint64_t)rank * r.slot >= r.localSlot) return BM_INVALID_PARAM;
     return BM_OK;
 }
 

@@ -182,6 +182,22 @@ int Segment::Reserve(uint32_t attempt)
         if (rc != OK) VaManager::Get().RemoveReserved(hint);
         else base_ = hint;
     }
+    if (rc == OK && Compact()) {
+        // the window of 56-bit addresses callers see: registered so that classification and gva_to_va know it
+        ReservedRange pub = r;
+        pub.base = Gva56WindowBase(opt_.entityId, attempt);
+        pub.slot = opt_.publicSlot;
+        pub.localBase = base_;
+        pub.localSlot = opt_.slot;
+        rc = VaManager::Get().AddReserved(pub);
+        if (rc == OK) {
+            pubBase_ = pub.base;
+        } else {
+            ReleaseRange(base_, total);
+            VaManager::Get().RemoveReserved(base_);
+            base_ = 0;
+        }
+    }
     MF_TRACE_END(TP_HYBM_RESERVE, rc);
     return rc;
 }
@@ -219,6 +235,8 @@ int Segment::Unreserve()
     }
     ReleaseRange(base_, opt_.slot * opt_.rankCount);
     VaManager::Get().RemoveReserved(base_);
+    if (pubBase_ != 0) VaManager::Get().RemoveReserved(pubBase_);
+    pubBase_ = 0;
     base_ = 0;
     return OK;
 }
@@ -229,8 +247,9 @@ int Segment::AllocLocal(uint64_t size, std::shared_ptr<MemSlice> &out)
     uint64_t sz = AlignUp(size, Granule());
     std::lock_guard<std::mutex> g(mu_);
     if (size == 0 || localUsed_ + sz > opt_.slot)
-        return MF_FAIL(ERR_NO_RESOURCES, "local slice of %lu bytes does not fit the %lu-byte slot (used %lu)",
-                       (unsigned long)size, (unsigned long)opt_.slot, (unsigned long)localUsed_);
+        return MF_FAIL(ERR_NO_RESOURCES, "local slice of %lu bytes does not fit the %lu-byte slot (used %lu)%s",
+                       (unsigned long)size, (unsigned long)opt_.slot, (unsigned long)localUsed_,
+                       Compact() ? ": with 56-bit addresses a rank's slices share the compact slot of 16 TiB / ranks" : "");
     auto s = std::make_shared<MemSlice>();
     s->index = (uint32_t)locals_.size();
     s->memType = opt_.type;
@@ -310,7 +329,7 @@ int Segment::Import(const hybm_exchange_info &in, uint64_t *addr)
         return MF_FAIL(ERR_INVALID_PARAM, "rank %u reserved its pool at %#lx, this rank at %#lx", h.rank, (unsigned long)base,
                        (unsigned long)base_);
     p.rank = h.rank;
-    if (addr != nullptr) *addr = base_ + opt_.slot * p.rank + p.offset;
+    if (addr != nullptr) *addr = ToPublic(base_ + opt_.slot * p.rank + p.offset);
     if (p.rank == opt_.rank) return OK;  // our own slice is already mapped
     std::lock_guard<std::mutex> g(mu_);
     for (auto &e : peers_)

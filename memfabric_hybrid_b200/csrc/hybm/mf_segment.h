@@ -47,6 +47,7 @@ struct SegmentOptions {
     uint32_t rank = 0;
     uint32_t rankCount = 0;
     uint64_t slot = 0;  // per-rank bytes in the window
+    uint64_t publicSlot = 0;  // != 0: compact mode (56-bit addresses): callers see slots of this size, `slot` is what each rank gets in this process
     hybm_mem_type type = HYBM_MEM_TYPE_DEVICE;
     uint32_t flags = 0;
     int shmFd = -1;
@@ -82,6 +83,18 @@ public:
     int RemoveImported(uint32_t rank);
     uint64_t Base() const { return base_; }
     uint64_t Slot() const { return opt_.slot; }
+    // The window as callers see it: the same as Base() / Slot() unless the segment is compact (see kGva56Base).
+    bool Compact() const { return opt_.publicSlot != 0; }
+    uint64_t PubBase() const { return Compact() ? pubBase_ : base_; }
+    uint64_t PubSlot() const { return Compact() ? opt_.publicSlot : opt_.slot; }
+    // address inside this process of (rank, offset) / address a caller sees for an address of this process
+    uint64_t LocalOf(uint32_t rank, uint64_t offset) const { return base_ + opt_.slot * rank + offset; }
+    uint64_t ToPublic(uint64_t va) const
+    {
+        if (!Compact()) return va;
+        const uint64_t rel = va - base_, r = rel / opt_.slot;
+        return pubBase_ + r * opt_.publicSlot + (rel - r * opt_.slot);
+    }
     uint64_t LocalBytes() const { return localUsed_; }
     hybm_mem_type Type() const { return opt_.type; }
     bool RankMapped(uint32_t rank);
@@ -104,6 +117,7 @@ protected:
 
     SegmentOptions opt_;
     uint64_t base_ = 0;
+    uint64_t pubBase_ = 0;
     uint64_t localUsed_ = 0;
     std::mutex mu_;
     struct LocalRec {

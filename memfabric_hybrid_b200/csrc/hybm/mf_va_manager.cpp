@@ -11,6 +11,18 @@ uint64_t WindowBase(hybm_mem_type t, uint32_t entityId, uint32_t attempt)
     return base + (uint64_t)window * kWindowStride;
 }
 
+uint64_t Gva56WindowBase(uint32_t entityId, uint32_t attempt)
+{
+    return kGva56Base + (uint64_t)((entityId + attempt * 17u) % kGva56Windows) * kGva56WindowStride;
+}
+
+uint64_t CompactSlot(uint32_t ranks)
+{
+    uint64_t per = kCompactThreshold / (ranks == 0 ? 1 : ranks), slot = 2ULL << 20;
+    while (slot * 2 <= per) slot *= 2;
+    return slot;
+}
+
 VaManager &VaManager::Get()
 {
     static VaManager inst;

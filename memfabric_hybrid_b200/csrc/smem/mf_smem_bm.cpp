@@ -2,6 +2,7 @@
 // handle registry, dispatch to BmEntry.
 // Parity: src/smem/csrc/smem_bm/smem_bm.cpp:28-570, smem_bm_entry_manager.cpp:46-155.
 #include "../util/mf_trace.h"
+#include "../include/hybm.h"
 #include "mf_smem_bm.h"
 
 using namespace mf;
@@ -258,7 +259,11 @@ int32_t smem_bm_gva_to_va(smem_bm_t handle, void *gva, smem_bm_mem_type_t vaMemT
     if (vaMemType != SMEM_MEM_TYPE_LOCAL_DEVICE && vaMemType != SMEM_MEM_TYPE_LOCAL_HOST)
         return MF_FAIL(SMEM_INVALID_PARAM, "memory type must be LOCAL_DEVICE or LOCAL_HOST");
     if (e->RankOfGva(gva) == UINT32_MAX) return MF_FAIL(SMEM_ERROR, "%p is not inside this pool", gva);
-    *va = gva;  // the pool is mapped at its global address in every member
+    // the pool is mapped at its global address in every member; a window of 56-bit addresses is mapped elsewhere (compact)
+    uint64_t local = 0;
+    if (hybm_gva_to_va(reinterpret_cast<uint64_t>(gva), HYBM_MEM_TYPE_HOST, &local) != 0)
+        return MF_FAIL(SMEM_ERROR, "%p is not mapped in this process", gva);
+    *va = reinterpret_cast<void *>(local);
     return SMEM_OK;
 }
 

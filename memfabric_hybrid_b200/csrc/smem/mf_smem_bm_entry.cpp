@@ -298,7 +298,7 @@ void *BmEntry::PtrOf(smem_bm_mem_type_t t, uint16_t rank)
         MF_FAIL(ERR_NOT_EXIST, "pool %u has no %s space", id_, mt == HYBM_MEM_TYPE_HOST ? "DRAM" : "HBM");
         return nullptr;
     }
-    return reinterpret_cast<void *>(seg->Base() + seg->Slot() * rank);
+    return reinterpret_cast<void *>(seg->PubBase() + seg->PubSlot() * rank);
 }
 
 uint32_t BmEntry::RankOfGva(const void *gva)
@@ -306,8 +306,8 @@ uint32_t BmEntry::RankOfGva(const void *gva)
     uint64_t a = reinterpret_cast<uint64_t>(gva);
     for (auto mt : {HYBM_MEM_TYPE_DEVICE, HYBM_MEM_TYPE_HOST}) {
         auto seg = entity_->SegmentOf(mt);
-        if (!seg || seg->Base() == 0 || a < seg->Base()) continue;
-        uint64_t r = (a - seg->Base()) / seg->Slot();
+        if (!seg || seg->Base() == 0 || a < seg->PubBase()) continue;
+        uint64_t r = (a - seg->PubBase()) / seg->PubSlot();
         if (r < g_.worldSize) return (uint32_t)r;
     }
     return UINT32_MAX;
@@ -318,7 +318,7 @@ uint8_t BmEntry::PoolClass(const void *p, uint64_t len)
     uint64_t a = reinterpret_cast<uint64_t>(p);
     auto in = [&](hybm_mem_type mt) {
         auto seg = entity_->SegmentOf(mt);
-        return seg && seg->Base() != 0 && a >= seg->Base() && a + len <= seg->Base() + seg->Slot() * g_.worldSize;
+        return seg && seg->Base() != 0 && a >= seg->PubBase() && a + len <= seg->PubBase() + seg->PubSlot() * g_.worldSize;
     };
     if (in(HYBM_MEM_TYPE_DEVICE)) return AC_GD;
     if (in(HYBM_MEM_TYPE_HOST)) return AC_GH;

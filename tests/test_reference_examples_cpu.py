@@ -29,6 +29,10 @@ CASES = [
     ("03_optimization/02_register/02_register.py", [], "02_register ok"),
     ("03_optimization/03_device_sdma/03_device_sdma.py", [], "03_device_sdma ok"),
     ("04_features/02_extend_local_mem/02_extend_local_mem.py", ["--world_size", "2", "--local_ranks", "2"], "alloc extend memory test ok"),
+    # 2 of 1 024 ranks of a pool with 1 TiB per rank: a 1 PiB window of 56-bit addresses
+    ("04_features/03_enable_56bits_gva/03_enable_56bits_gva.py",
+     ["--world_size", "1024", "--local_ranks", "2", "--rank_start", "0", "--protocol", "device_sdma", "--url", "tcp://127.0.0.1:{port}"],
+     "rank:1, 56-bit GVA test ok."),
 ]
 
 
@@ -41,6 +45,13 @@ def test_reference_example_runs_unchanged(script, args, marker, tmp_path):
     env = dict(os.environ)
     env["PYTHONPATH"] = str(ROOT) + os.pathsep + env.get("PYTHONPATH", "")
     env["MF_DEVICE_BACKEND"] = "none"     # CPU tier: DRAM pools only
+    if any("{port}" in a for a in args):
+        import socket
+        sk = socket.socket()
+        sk.bind(("127.0.0.1", 0))
+        port = sk.getsockname()[1]
+        sk.close()
+        args = [a.replace("{port}", str(port)) for a in args]
     p = subprocess.run([sys.executable, str(path)] + args, cwd=tmp_path, env=env, capture_output=True, text=True, timeout=300)
     out = p.stdout + p.stderr
     assert p.returncode == 0, out[-3000:]
