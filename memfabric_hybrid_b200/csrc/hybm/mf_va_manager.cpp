@@ -5,7 +5,11 @@ namespace hybm {
 
 uint64_t WindowBase(hybm_mem_type t, uint32_t entityId, uint32_t attempt)
 {
-    uint64_t base = t == HYBM_MEM_TYPE_HOST ? kDramWindowBase : kHbmWindowBase;
+    // MF_GVA_DRAM_BASE / MF_GVA_HBM_BASE move a space (every process of the job must be given the same value): for
+    // address spaces in which the defaults are taken, e.g. under ThreadSanitizer, whose shadow memory covers them.
+    static const uint64_t dramBase = (uint64_t)EnvInt("MF_GVA_DRAM_BASE", nullptr, (int64_t)kDramWindowBase, 1LL << 32, 1LL << 47);
+    static const uint64_t hbmBase = (uint64_t)EnvInt("MF_GVA_HBM_BASE", nullptr, (int64_t)kHbmWindowBase, 1LL << 32, 1LL << 47);
+    uint64_t base = t == HYBM_MEM_TYPE_HOST ? dramBase : hbmBase;
     // A retry after a collision moves to another of the 64 windows, the same one in every process.
     uint32_t window = (entityId + attempt * 17u) % (kMaxEntityId + 1);
     return base + (uint64_t)window * kWindowStride;
