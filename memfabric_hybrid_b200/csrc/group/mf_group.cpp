@@ -418,6 +418,11 @@ void GroupEngine::HandleEvent(const GroupInfo &ev)
     changeEpoch_.fetch_add(1);
     if (ev.submitRank == opt_.rank) return;  // the submitting thread drives its own event
     if (!joined_) return;
+    if (ev.targetRank >= kMaxRanks || ev.submitRank >= kMaxRanks) {
+        MF_WARN("group event %u names rank %u (from rank %u): outside the %u ranks a group can have, ignored", ev.curEvent, ev.targetRank, ev.submitRank,
+                kMaxRanks);
+        return;
+    }
     ChangeFn cb;
     bool hadTarget;
     {

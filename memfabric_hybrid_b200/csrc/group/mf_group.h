@@ -38,8 +38,15 @@ struct GroupInfo {
     uint32_t submitRank = 0;
     uint64_t bitmap[kBitmapWords] = {0};
     bool Has(uint32_t r) const { return r < kMaxRanks && (bitmap[r / 64] >> (r % 64)) & 1ULL; }
-    void Put(uint32_t r) { bitmap[r / 64] |= 1ULL << (r % 64); }
-    void Drop(uint32_t r) { bitmap[r / 64] &= ~(1ULL << (r % 64)); }
+    // (rank numbers arrive in records written by other processes: one outside the bitmap changes nothing)
+    void Put(uint32_t r)
+    {
+        if (r < kMaxRanks) bitmap[r / 64] |= 1ULL << (r % 64);
+    }
+    void Drop(uint32_t r)
+    {
+        if (r < kMaxRanks) bitmap[r / 64] &= ~(1ULL << (r % 64));
+    }
     uint32_t Count() const
     {
         uint32_t n = 0;

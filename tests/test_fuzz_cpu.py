@@ -342,3 +342,58 @@ def _exchange_records(rank, world):
 def test_memory_layer_refuses_damaged_exchange_records():
     from mp_util import run_ranks
     assert run_ranks(_exchange_records, 1, (), timeout=240, env={"MF_DEVICE_BACKEND": "none"}) == [True]
+
+
+def test_group_engine_survives_damaged_membership_records():
+    """Members of a dynamic group watch the membership record in the store; a rogue client overwrites it with damaged
+    copies (wrong sizes, rank numbers far outside a group, flipped bits). Nobody may crash or stall."""
+    l = H.lib()
+    port = free_port()
+    srv = H.start_server(port, world=8)
+    rng = random.Random(4242 + SEED)
+    n = 2
+    stores, groups, cbs, events = [None] * n, [None] * n, [None] * n, []
+    try:
+        for r in range(n):
+            stores[r] = H.Store.connect(port, world=8, rank=r)
+            cbs[r] = H.CHANGE_CB(lambda ev, who: (events.append((ev, who)), 0)[1])
+            groups[r] = l.mf_t_group_new(stores[r].h, n, r, 3000, 1, cbs[r])
+            assert l.mf_t_group_start_listen(groups[r]) == 0
+            assert l.mf_t_group_join(groups[r]) == 0
+        rogue = H.Store.connect(port, world=8, rank=5)
+        good = rogue.get("EVENT")
+        assert isinstance(good, bytes) and len(good) >= 20
+        for i in range(200 // LIGHT):
+            rec = bytearray(good)
+            k = rng.randrange(5)
+            if k == 0:
+                for _ in range(rng.randint(1, 6)):
+                    rec[rng.randrange(len(rec))] ^= 1 << rng.randrange(8)
+            elif k == 1:
+                rec = rec[:rng.randrange(len(rec))]
+            elif k == 2:
+                rec += bytes(rng.getrandbits(8) for _ in range(rng.randint(1, 64)))
+            elif k == 3:                                   # version moves on, event and ranks are nonsense
+                rec[0:4] = (int.from_bytes(good[0:4], "little") + 2 * i + 1).to_bytes(4, "little")
+                rec[8:20] = bytes(rng.getrandbits(8) for _ in range(12))
+            else:
+                rec[12:16] = b"\\xff\\xff\\xff\\xff"
+                rec[16:20] = b"\\xff\\xff\\xff\\x7f"
+                rec[0:4] = (int.from_bytes(good[0:4], "little") + 2 * i + 1).to_bytes(4, "little")
+            assert rogue.set("EVENT", bytes(rec)) == 0
+            if i % 10 == 0:
+                time.sleep(0.01)
+        time.sleep(0.3)
+        v, s, e, b = C.c_uint32(), C.c_uint32(), C.c_uint32(), C.c_uint64()
+        for g in groups:
+            l.mf_t_group_info(g, C.byref(v), C.byref(s), C.byref(e), C.byref(b))      # still answers
+        rogue.set("EVENT", good)
+        rogue.close()
+    finally:
+        for g in groups:
+            if g:
+                l.mf_t_group_free(g)
+        for st in stores:
+            if st:
+                st.close()
+        l.mf_t_server_stop(srv)
