@@ -21,7 +21,7 @@ LOAD = [10, 10, 10, 10, 10, 90, 10, 60]            # tokens per logical expert i
 
 def new_placement():
     from tensor_rtl import balanced_placement
-    return balanced_placement(LOAD, 4, 3)           # the same list on every rank (a pure function of the load)
+    return balanced_placement(LOAD, 4, 3, previous=OLD)   # the same list on every rank; experts stay where they can
 
 
 def rank_loads(placement, world, local):

@@ -49,16 +49,23 @@ def pair_slots(old: Sequence[int], new: Sequence[int], local: int) -> List[Tuple
     return pairs
 
 
-def balanced_placement(load: Sequence[float], ep_size: int, slots_per_rank: int) -> List[int]:
+def balanced_placement(load: Sequence[float], ep_size: int, slots_per_rank: int, previous: Optional[Sequence[int]] = None,
+                       tolerance: float = 0.05) -> List[int]:
     """The planner of the EPLB flow: from the tokens each LOGICAL expert received (``load[e]``, e.g. a moving average of the
     router's counts summed over ranks) to a placement ``placement[slot] = logical expert`` over ``ep_size * slots_per_rank``
     physical slots that evens out the expert work per rank. Spare slots (slots beyond the number of logical experts) become
     extra copies of the hottest experts: a copy is added, one at a time, to the expert with the largest load per copy. The
     copies are then packed onto ranks heaviest first, each onto the rank with the least work so far that still has a free
-    slot (and, when possible, no copy of the same expert yet). Deterministic: every rank computes the same placement."""
+    slot (and, when possible, no copy of the same expert yet).
+    ``previous``: the placement in force. Weights that stay where they are cost nothing to migrate, so among the ranks whose
+    work is within ``tolerance`` (a fraction of the mean work per rank) of the least loaded one, a rank that already holds
+    the expert is preferred, and inside a rank an expert keeps its slot.
+    Deterministic: every rank computes the same placement."""
     E, P = len(load), ep_size * slots_per_rank
     if E == 0 or P < E:
         raise ValueError(f"{P} physical slots cannot hold {E} logical experts")
+    if previous is not None and len(previous) != P:
+        raise ValueError(f"the previous placement has {len(previous)} slots, this layout {P}")
     copies = [1] * E
     for _ in range(P - E):
         e = max(range(E), key=lambda i: (load[i] / copies[i], -i))
@@ -66,13 +73,38 @@ def balanced_placement(load: Sequence[float], ep_size: int, slots_per_rank: int)
     items = sorted(((load[e] / copies[e], e) for e in range(E) for _ in range(copies[e])), key=lambda t: (-t[0], t[1]))
     work = [0.0] * ep_size
     held: List[List[int]] = [[] for _ in range(ep_size)]
+    # copies of each expert that a rank holds today and that the new placement has not claimed yet
+    there: List[Dict[int, int]] = [{} for _ in range(ep_size)]
+    if previous is not None:
+        for slot, e in enumerate(previous):
+            d = there[slot // slots_per_rank]
+            d[e] = d.get(e, 0) + 1
+    slack = tolerance * (sum(load) / ep_size)
     for w, e in items:
         free = [r for r in range(ep_size) if len(held[r]) < slots_per_rank]
         fresh = [r for r in free if e not in held[r]] or free
-        r = min(fresh, key=lambda q: (work[q], q))
+        least = min(work[q] for q in fresh)
+        r = min(fresh, key=lambda q: (0 if (work[q] <= least + slack and there[q].get(e, 0) > 0) else 1, work[q], q))
         held[r].append(e)
         work[r] += w
-    return [e for r in range(ep_size) for e in held[r]]
+        if there[r].get(e, 0) > 0:
+            there[r][e] -= 1
+    if previous is None:
+        return [e for r in range(ep_size) for e in held[r]]
+    out: List[int] = []
+    for r in range(ep_size):                      # inside a rank: an expert that is here already keeps its slot
+        old = list(previous[r * slots_per_rank:(r + 1) * slots_per_rank])
+        row: List[Optional[int]] = [None] * slots_per_rank
+        rest = []
+        for e in held[r]:
+            spot = next((i for i, o in enumerate(old) if o == e and row[i] is None), None)
+            if spot is None:
+                rest.append(e)
+            else:
+                row[spot] = e
+        it = iter(rest)
+        out.extend(e if e is not None else next(it) for e in row)
+    return out
 
 
 def replica_table(placement: Sequence[int], num_logical: int, device=None) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -232,3 +232,35 @@ def test_eplb_planner_evens_out_a_skewed_router():
         assert len(set(held)) == len(held)
     with pytest.raises(ValueError):
         balanced_placement([1.0] * 10, 2, 4)
+
+
+def test_eplb_planner_keeps_weights_in_place_when_it_can():
+    """With the placement in force as a hint, a small change of the load moves few experts, a large one still rebalances,
+    and the balance is not worse than the tolerance allows."""
+    import random
+    from memfabric_hybrid_b200.tensor_rtl import balanced_placement, pair_slots
+    ep, per, E = 8, 8, 56
+    rng = random.Random(3)
+    load = [100.0 / (1 + e) ** 0.6 for e in range(E)]
+    rng.shuffle(load)
+    base = balanced_placement(load, ep, per)
+    assert balanced_placement(load, ep, per, previous=base) == base              # nothing changed: nothing moves
+
+    def imbalance(pl, ld):
+        cp = [pl.count(e) for e in range(E)]
+        w = [0.0] * ep
+        for s, e in enumerate(pl):
+            w[s // per] += ld[e] / cp[e]
+        return max(w) / (sum(w) / ep)
+    drift = [v * rng.uniform(0.9, 1.1) for v in load]                            # the router drifts a little
+    cold, warm = balanced_placement(drift, ep, per), balanced_placement(drift, ep, per, previous=base)
+    moved_cold, moved_warm = len(pair_slots(base, cold, per)), len(pair_slots(base, warm, per))
+    assert moved_warm < moved_cold // 2, (moved_warm, moved_cold)
+    assert imbalance(warm, drift) < imbalance(cold, drift) + 0.06 and imbalance(warm, drift) < 1.15
+    assert sorted(warm) == sorted(cold)                                           # the same copies, placed differently
+    hot = list(load)
+    hot[7] *= 12                                                                  # one expert becomes very hot
+    moved = balanced_placement(hot, ep, per, previous=base)
+    assert moved.count(7) > base.count(7) and imbalance(moved, hot) < imbalance(base, hot) - 0.3
+    with pytest.raises(ValueError):
+        balanced_placement(load, ep, per, previous=base[:-1])
