@@ -10,6 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 @pytest.mark.parametrize("script", ["examples/memory_pool/01_two_rank_dram_pool.py", "examples/memory_pool/02_copy_data_batch_and_register.py",
                                     "examples/memory_pool/04_extend_local_mem.py", "examples/memory_pool/05_observability/metrics_endpoint.py",
+                                    "examples/memory_pool/06_enable_56bits_gva.py",
                                     "examples/transfer/transfer_engine.py", "examples/tensor_rtl/reshard_tp4_to_tp2.py",
                                     "examples/tensor_rtl/eplb_expert_migration.py", "examples/tensor_rtl/rl_train_to_infer_reshard.py"])
 def test_example_runs(script):
