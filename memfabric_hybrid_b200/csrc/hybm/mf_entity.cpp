@@ -126,6 +126,16 @@ int Entity::ReserveMemSpace(uint32_t attempt)
     if ((opt_.memType & HYBM_MEM_TYPE_DEVICE) != 0 && opt_.maxHBMSize != 0 && !hbm_) {
         so.type = HYBM_MEM_TYPE_DEVICE;
         so.slot = AlignUp(opt_.maxHBMSize, kHbmGranule);
+        so.publicSlot = 0;
+        if (opt_.enable56BitsGva && so.slot > kCompactThreshold / so.rankCount) {  // as for pooled DRAM below
+            if (so.slot > kGva56WindowStride / so.rankCount)
+                return MF_FAIL(ERR_INVALID_PARAM, "an HBM pool of %u ranks x %lu bytes exceeds the 1 PiB of a 56-bit address window", so.rankCount,
+                               (unsigned long)so.slot);
+            so.publicSlot = so.slot;
+            so.slot = CompactSlot(so.rankCount);
+            MF_INFO("HBM pool %u: 56-bit addresses, %lu bytes per rank for callers, %lu mapped per rank in this process", id_,
+                    (unsigned long)so.publicSlot, (unsigned long)so.slot);
+        }
         auto seg = Segment::Create(so);
         if (!seg) return ERR_NOT_INIT;
         int rc = seg->Reserve(attempt);
@@ -135,6 +145,7 @@ int Entity::ReserveMemSpace(uint32_t attempt)
     if ((opt_.memType & HYBM_MEM_TYPE_HOST) != 0 && opt_.maxDRAMSize != 0 && !dram_) {
         so.type = HYBM_MEM_TYPE_HOST;
         so.slot = AlignUp(opt_.maxDRAMSize, 2ULL << 20);
+        so.publicSlot = 0;
         if (opt_.enable56BitsGva && so.slot > kCompactThreshold / so.rankCount) {
             // too large to map whole: callers get 56-bit addresses, the process a compact window (mf_hybm_types.h)
             if (so.slot > kGva56WindowStride / so.rankCount)
@@ -524,7 +535,7 @@ int Entity::Resolve(uint64_t addr, uint64_t len, bool isSrc, hybm_data_copy_dire
     ep.pid = 0;
     int err = OK;
     uint8_t want = SideClass(dir, isSrc);
-    if (InPool(hbm_, addr, len, err)) {
+    if (InPool(hbm_, addr, len, err, &ep.addr)) {
         if (err != OK) return err;
         if (want != AC_NONE && want != AC_GD) return ERR_INVALID_PARAM;
         ep.kind = EP_DEVICE;
@@ -581,7 +592,7 @@ int Entity::BatchCopyData(const hybm_batch_copy_params &p, hybm_data_copy_direct
     PublishCopyWindow();
     // Hot path: every item is device<->device with at least one side in the HBM pool (KV-block put/get).
     // Pass 1 validates with arithmetic only; pass 2 streams the items into the descriptor ring.
-    if (perItem == nullptr && dev_ != nullptr && hbm_ && hbm_->Base() != 0 &&
+    if (perItem == nullptr && dev_ != nullptr && hbm_ && hbm_->Base() != 0 && !hbm_->Compact() &&  // (56-bit addresses need translating: general path)
         (dir == HYBM_LOCAL_DEVICE_TO_GLOBAL_DEVICE || dir == HYBM_GLOBAL_DEVICE_TO_GLOBAL_DEVICE ||
          dir == HYBM_GLOBAL_DEVICE_TO_LOCAL_DEVICE)) {
         const uint64_t base = hbm_->Base(), slot = hbm_->Slot();
@@ -679,8 +690,8 @@ int Entity::QuantCopy(const hybm_quant_copy_params &p, int mode)
     // window (the caller's own device buffers) are taken as given, as in the copy paths.
     auto pooled = [&](uint64_t addr, uint64_t len, const char *what, uint32_t i) -> int {
         int err = OK;
-        if (dram_ && dram_->Compact() && InPool(dram_, addr, len, err))
-            return MF_FAIL(ERR_INVALID_PARAM, "quant copy item %u: %s %#lx is a 56-bit DRAM pool address, which the quantising kernel cannot reach", i, what,
+        if ((dram_ && dram_->Compact() && InPool(dram_, addr, len, err)) || (hbm_ && hbm_->Compact() && InPool(hbm_, addr, len, err)))
+            return MF_FAIL(ERR_INVALID_PARAM, "quant copy item %u: %s %#lx is a 56-bit pool address, which the quantising copy does not translate", i, what,
                            (unsigned long)addr);
         if ((InPool(hbm_, addr, len, err) || InPool(dram_, addr, len, err)) && err != OK)
             return MF_FAIL(err, "quant copy item %u: %s %#lx (+%lu bytes) %s", i, what, (unsigned long)addr, (unsigned long)len,

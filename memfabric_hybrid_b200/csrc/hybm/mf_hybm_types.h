@@ -36,7 +36,8 @@ constexpr uint32_t kShmEntityBase = 64;
 constexpr uint32_t kReserveAttempts = 4;
 uint64_t WindowBase(hybm_mem_type t, uint32_t entityId, uint32_t attempt);
 // 56-bit global addresses (enable56BitsGva) for pooled DRAM whose window (slot x ranks) does not fit the 32 TiB DRAM space
-// above, e.g. 1 024 ranks x 1 TiB. The addresses a caller sees then are NUMBERS in [2^55, 2^56), 32 windows of 1 PiB:
+// above, e.g. 1 024 ranks x 1 TiB. The addresses a caller sees then are NUMBERS in [2^55, 2^56), 32 windows of 1 PiB
+// (the lower 16 for pooled DRAM, the upper 16 for pooled HBM):
 // they name (rank, offset) and are only ever passed to the copy calls. Inside the process every rank's slice is mapped
 // in a compact window of the ordinary DRAM space whose slot is as large as 16 TiB / ranks allows (a power of two); the
 // copy paths and gva_to_va translate. A rank's slices together may not exceed the compact slot.
@@ -44,7 +45,7 @@ constexpr uint64_t kGva56Base = 1ULL << 55;
 constexpr uint64_t kGva56WindowStride = 1ULL << 50;
 constexpr uint32_t kGva56Windows = 32;
 constexpr uint64_t kCompactThreshold = 16 * kTiB;   // larger windows than this go compact when 56-bit addresses are enabled
-uint64_t Gva56WindowBase(uint32_t entityId, uint32_t attempt);
+uint64_t Gva56WindowBase(hybm_mem_type t, uint32_t entityId, uint32_t attempt);
 uint64_t CompactSlot(uint32_t ranks);               // bytes per rank of the compact window
 
 // Address classes (bit mask): local host / pooled host / local device / pooled device.

@@ -185,7 +185,7 @@ int Segment::Reserve(uint32_t attempt)
     if (rc == OK && Compact()) {
         // the window of 56-bit addresses callers see: registered so that classification and gva_to_va know it
         ReservedRange pub = r;
-        pub.base = Gva56WindowBase(opt_.entityId, attempt);
+        pub.base = Gva56WindowBase(opt_.type, opt_.entityId, attempt);
         pub.slot = opt_.publicSlot;
         pub.localBase = base_;
         pub.localSlot = opt_.slot;

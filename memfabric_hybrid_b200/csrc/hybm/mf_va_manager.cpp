@@ -15,9 +15,10 @@ uint64_t WindowBase(hybm_mem_type t, uint32_t entityId, uint32_t attempt)
     return base + (uint64_t)window * kWindowStride;
 }
 
-uint64_t Gva56WindowBase(uint32_t entityId, uint32_t attempt)
+uint64_t Gva56WindowBase(hybm_mem_type t, uint32_t entityId, uint32_t attempt)
 {
-    return kGva56Base + (uint64_t)((entityId + attempt * 17u) % kGva56Windows) * kGva56WindowStride;
+    const uint32_t half = kGva56Windows / 2;
+    return kGva56Base + (uint64_t)((entityId + attempt * 17u) % half + (t == HYBM_MEM_TYPE_HOST ? 0 : half)) * kGva56WindowStride;
 }
 
 uint64_t CompactSlot(uint32_t ranks)

@@ -150,3 +150,61 @@ def _quant_rank(rank, world, url):
 def test_quantising_copy_against_the_host_oracle():
     url = f"tcp://127.0.0.1:{free_port()}"
     assert run_ranks(_quant_rank, 1, (url,), timeout=120, env={"MF_DEVICE_BACKEND": "fake"}) == [0]
+
+
+def _rank_56(rank, world, url, sync):
+    """Windows of 1 024 ranks x 256 GiB of HBM and x 1 TiB of DRAM (two ranks present): 56-bit addresses on the device-memory path."""
+    import memfabric_hybrid as mf
+    from memfabric_hybrid import bm
+    WORLD, TiB = 1024, 1 << 40
+    assert mf.initialize() == 0
+    cfg = bm.BmConfig()
+    cfg.rank_id, cfg.start_store, cfg.auto_ranking = rank, rank == 0, False
+    cfg.operation_timeout = 30
+    assert bm.initialize(url, WORLD, 0, cfg) == 0, mf.get_last_err_msg()
+    h = bm.create2(id=5, local_dram_size=4 * MiB, max_dram_size=TiB, local_hbm_size=8 * MiB, max_hbm_size=TiB // 4, enable_56bits_gva=True)
+    assert h.join() == 0, mf.get_last_err_msg()
+    sync.wait(60)
+    peer = 1 - rank
+    mdev, pdev = h.peer_rank_ptr(rank, bm.BmMemType.DEVICE), h.peer_rank_ptr(peer, bm.BmMemType.DEVICE)
+    mhost = h.peer_rank_ptr(rank, bm.BmMemType.HOST)
+    assert mdev >= 1 << 55 and mhost >= 1 << 55 and abs(pdev - mdev) == TiB // 4 and not (mdev <= mhost < mdev + WORLD * TiB // 4)
+    assert h.get_rank_id_by_gva(pdev + 99) == peer
+    src = np.random.default_rng(50 + rank).integers(0, 256, 2 * MiB, dtype=np.uint8)
+    n, seg = 16, 128 * 1024
+    import time
+    end = time.time() + 30
+    while h.copy_data_batch([src.ctypes.data + i * seg for i in range(n)], [pdev + i * seg for i in range(n)], [seg] * n, n,
+                            bm.BmCopyType.H2G, 0) != 0:                      # host -> the peer's device slice, batched
+        assert time.time() < end, mf.get_last_err_msg()
+        time.sleep(0.05)
+    mf.get_and_clear_last_err_msg()
+    sync.wait(60)
+    want = np.random.default_rng(50 + peer).integers(0, 256, 2 * MiB, dtype=np.uint8)
+    # device pool -> device pool (own slice), device pool -> DRAM pool, DRAM pool -> host
+    assert h.copy_data_batch([mdev + i * seg for i in range(n)], [mdev + 4 * MiB + i * seg for i in range(n)], [seg] * n, n,
+                             bm.BmCopyType.G2G, 0) == 0, mf.get_last_err_msg()
+    assert h.copy_data(mdev + 4 * MiB, mhost, 2 * MiB, bm.BmCopyType.G2G, 0) == 0, mf.get_last_err_msg()
+    got = np.zeros(2 * MiB, dtype=np.uint8)
+    assert h.copy_data(mhost, got.ctypes.data, 2 * MiB, bm.BmCopyType.G2H, 0) == 0, mf.get_last_err_msg()
+    assert np.array_equal(got, want)
+    # a prepared batch (validated once, launched many times) translates too
+    pb = h.prepare_batch([pdev + i * seg for i in range(4)], [mdev + 6 * MiB + i * seg for i in range(4)], [seg] * 4, 4)
+    assert h.copy_prepared(pb, bm.BmCopyType.G2G, 0) == 0, mf.get_last_err_msg()
+    back = np.zeros(4 * seg, dtype=np.uint8)
+    assert h.copy_data(mdev + 6 * MiB, back.ctypes.data, back.nbytes, bm.BmCopyType.G2H, 0) == 0 and np.array_equal(back, src[:4 * seg])
+    assert h.copy_data(mdev + 8 * MiB, got.ctypes.data, 16, bm.BmCopyType.G2H, 0) != 0        # past what the rank contributed
+    assert h.copy_data(h.peer_rank_ptr(9, bm.BmMemType.DEVICE), got.ctypes.data, 16, bm.BmCopyType.G2H, 0) != 0
+    mf.get_and_clear_last_err_msg()
+    sync.wait(60)
+    assert h.leave() == 0
+    sync.wait(60)
+    h.destroy()
+    bm.uninitialize(0)
+    mf.uninitialize()
+    return True
+
+
+def test_fake_device_56_bit_addresses():
+    url = f"tcp://127.0.0.1:{free_port()}"
+    assert run_ranks(_rank_56, 2, (url,), timeout=180, env={"MF_DEVICE_BACKEND": "fake"}, with_barrier=True) == [True, True]
