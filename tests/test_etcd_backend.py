@@ -235,3 +235,51 @@ def test_store_url_with_the_etcd_scheme(etcd, monkeypatch):
     # nobody answers at the address: a clear refusal instead of a store
     dead = f"etcd://127.0.0.1:{free_port()}#urltest"
     assert api.create_config_store(dead) != 0
+
+
+def _pool_over_etcd(rank, world, url, port, sync):
+    """A two-rank DRAM pool whose config store is elected over etcd: the whole public path behind an etcd:// URL."""
+    import os
+    os.environ["MF_CONFIG_STORE_PORT"] = str(port)
+    os.environ["MF_DEVICE_BACKEND"] = "none"
+    import numpy as np
+    import memfabric_hybrid as mf
+    from memfabric_hybrid import bm
+    MiB = 1 << 20
+    assert mf.initialize() == 0
+    cfg = bm.BmConfig()
+    cfg.rank_id = rank
+    cfg.start_store = True                      # every rank may lead; etcd decides
+    cfg.operation_timeout = 30
+    assert bm.initialize(url, world, 0, cfg) == 0, mf.get_last_err_msg()
+    h = bm.create2(id=0, local_dram_size=8 * MiB, max_dram_size=8 * MiB, data_op_type=bm.BmDataOpType.HOST_SHM)
+    assert h.join() == 0, mf.get_last_err_msg()
+    sync.wait(60)
+    peer = h.peer_rank_ptr(1 - rank, bm.BmMemType.HOST)
+    me = h.peer_rank_ptr(rank, bm.BmMemType.HOST)
+    src = np.full(MiB, 0x30 + rank, dtype=np.uint8)
+    end = time.time() + 30
+    while h.copy_data(src.ctypes.data, peer, MiB, bm.BmCopyType.H2G, 0) != 0:
+        assert time.time() < end, mf.get_last_err_msg()
+        time.sleep(0.05)
+    mf.get_and_clear_last_err_msg()
+    sync.wait(60)
+    got = np.zeros(MiB, dtype=np.uint8)
+    assert h.copy_data(me, got.ctypes.data, MiB, bm.BmCopyType.G2H, 0) == 0, mf.get_last_err_msg()
+    ok = bool((got == 0x30 + (1 - rank)).all())
+    sync.wait(60)
+    assert h.leave() == 0
+    sync.wait(60)
+    h.destroy()
+    bm.uninitialize(0)
+    mf.uninitialize()
+    return ok
+
+
+def test_memory_pool_brought_up_over_an_etcd_url(etcd):
+    from mp_util import run_ranks
+    url = f"etcd://127.0.0.1:{etcd.port}#pooltest"
+    assert run_ranks(_pool_over_etcd, 2, (url, free_port()), timeout=180, with_barrier=True) == [True, True]
+    root = b"/memfabric_hybrid/config_store/clusters/pooltest/"
+    assert etcd.kv[root + b"memfabric_hybrid/config_store/data/world_size"]["value"] == b"2"
+    assert any(k.startswith(root + b"memfabric_hybrid/config_store/meta/leader") for k in etcd.kv)
