@@ -94,7 +94,11 @@ int32_t smem_bm_init(const char *storeURL, uint32_t worldSize, uint16_t deviceId
     }
     // Who serves the store: with fixed ranks, rank 0 when allowed to; with auto-ranking every process
     // that is allowed to races for the port and the losers become clients.
-    bool serve = config->startConfigStoreServer && (autoRank || config->rankId == 0);
+    // Behind an etcd:// or reg:// URL the store is highly available: every process that is allowed to serve stands for
+    // election, whatever its rank, so that one of them can take over when the leader's process dies.
+    store::StoreUrl parsed;
+    const bool ha = store::StoreUrl::Parse(storeURL, parsed) && parsed.scheme != store::StoreUrl::TCP;
+    bool serve = config->startConfigStoreServer && (autoRank || config->rankId == 0 || ha);
     uint32_t linkRank = autoRank ? store::kAutoRank : config->rankId;
     store::StorePtr base;
     int err = OK;

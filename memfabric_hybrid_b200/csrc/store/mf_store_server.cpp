@@ -504,17 +504,33 @@ void StoreServer::TimerLoop()
         if (now - lastCheck >= hb) {
             lastCheck = now;
             std::vector<net::LinkPtr> dead;
+            std::vector<uint32_t> missing;   // members of the previous leader's store that did not come back in time
+            std::vector<Watcher> subs;
             {
                 std::lock_guard<std::mutex> g(rankMu_);
                 if (state_ == RECOVER && (expectedBack_.empty() || now >= recoverDeadlineMs_)) {
+                    missing.assign(expectedBack_.begin(), expectedBack_.end());
                     expectedBack_.clear();
                     state_ = NORMAL;
-                    MF_INFO("store recovery window closed");
+                    MF_INFO("store recovery window closed, %zu member(s) did not return", missing.size());
+                    if (!missing.empty()) {
+                        PersistAlive();
+                        for (auto &kv : rankWatchers_) subs.push_back(kv.second);
+                    }
                 }
                 for (auto &kv : allLinks_) {
                     if (kv.second->userData.load(std::memory_order_relaxed) == nullptr) continue;
                     if (now - kv.second->lastSeenMs.load() > (uint64_t)kMissedHeartbeats * hb) dead.push_back(kv.second);
                 }
+            }
+            // whoever did not return is down for good (it may have died with the old leader: nobody else saw its link
+            // break): tell the subscribers, exactly as when a link breaks here
+            for (uint32_t r : missing) {
+                MF_INFO("rank %u did not return after the change of leader, notifying %zu subscribers", r, subs.size());
+                StoreMessage m(MT_WATCH_RANK_STATE);
+                m.values.emplace_back(reinterpret_cast<const char *>(&r), sizeof(r));
+                for (auto &w : subs)
+                    if (w.link->Alive()) ReplyMsg(w.link, w.seq, ST_OK, m);
             }
             for (auto &l : dead) {
                 MF_WARN("link %lu missed %u heartbeats: closing", (unsigned long)l->Id(), kMissedHeartbeats);

@@ -283,3 +283,100 @@ def test_memory_pool_brought_up_over_an_etcd_url(etcd):
     root = b"/memfabric_hybrid/config_store/clusters/pooltest/"
     assert etcd.kv[root + b"memfabric_hybrid/config_store/data/world_size"]["value"] == b"2"
     assert any(k.startswith(root + b"memfabric_hybrid/config_store/meta/leader") for k in etcd.kv)
+
+
+def _pool_survives_leader(rank, world, url, port, sync):
+    """Three ranks; the process that leads the config store dies without a word. The pool's data path keeps working and
+    the control path comes back on a newly elected leader."""
+    import os
+    os.environ["MF_CONFIG_STORE_PORT"] = str(port)
+    os.environ["MF_DEVICE_BACKEND"] = "none"
+    os.environ["MF_STORE_RECOVER_MS"] = "3000"   # how long a new leader waits for the old one's members (default 60 s)
+    import numpy as np
+    import memfabric_hybrid as mf
+    from memfabric_hybrid import bm
+    MiB = 1 << 20
+    if rank != 0:
+        sync.wait(60)                            # rank 0 goes first: it becomes the leader
+    assert mf.initialize() == 0
+    cfg = bm.BmConfig()
+    cfg.rank_id = rank
+    cfg.start_store = rank in (0, 1)             # ranks 0 and 1 may lead, rank 2 only follows
+    cfg.operation_timeout = 40
+    assert bm.initialize(url, world, 0, cfg) == 0, mf.get_last_err_msg()
+    if rank == 0:
+        sync.wait(60)
+    h = bm.create2(id=0, local_dram_size=4 * MiB, max_dram_size=4 * MiB, data_op_type=bm.BmDataOpType.HOST_SHM)
+    events = []
+    h.set_group_event_handler(lambda r, ev: events.append((r, int(ev))))
+    assert h.join() == 0, mf.get_last_err_msg()
+    sync.wait(60)
+    nxt = (rank + 1) % world
+    src = np.full(MiB, 0x40 + rank, dtype=np.uint8)
+    end = time.time() + 30
+    while h.copy_data(src.ctypes.data, h.peer_rank_ptr(nxt, bm.BmMemType.HOST), MiB, bm.BmCopyType.H2G, 0) != 0:
+        assert time.time() < end, mf.get_last_err_msg()
+        time.sleep(0.05)
+    mf.get_and_clear_last_err_msg()
+    sync.wait(60)
+    if rank == 0:
+        os._exit(0)                              # the leader's process is gone: no leave, no goodbye to the store
+    # the survivors' slices are mapped in each other: copies between them need no store
+    other = 3 - rank
+    got = np.zeros(MiB, dtype=np.uint8)
+    assert h.copy_data(src.ctypes.data, h.peer_rank_ptr(other, bm.BmMemType.HOST) + MiB, MiB, bm.BmCopyType.H2G, 0) == 0, mf.get_last_err_msg()
+    time.sleep(0.5)
+    assert h.copy_data(h.peer_rank_ptr(rank, bm.BmMemType.HOST) + MiB, got.ctypes.data, MiB, bm.BmCopyType.G2H, 0) == 0
+    assert (got == 0x40 + other).all()
+    # the control path returns with the new leader (elected once the dead leader's address stops answering; the followers
+    # notice their broken links, look the new address up in etcd and re-arm their watches): leaving is a membership change
+    # agreed through the store
+    time.sleep(6.0)
+    end = time.time() + 60
+    rc = -1
+    while time.time() < end:
+        rc = h.leave()
+        if rc == 0:
+            break
+        mf.get_and_clear_last_err_msg()
+        time.sleep(0.5)
+    assert rc == 0, f"leave after the leader died: {rc} {mf.get_last_err_msg()}"
+    assert any(r == 0 for r, _ in events), events    # the survivors were told that rank 0 is gone
+    time.sleep(1.0 if rank == 1 else 0.0)        # whoever leads now stays until the other has left
+    h.destroy()
+    bm.uninitialize(0)
+    mf.uninitialize()
+    return True
+
+
+def test_pool_survives_the_death_of_the_store_leader(etcd):
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    url = f"etcd://127.0.0.1:{etcd.port}#failover"
+    port = free_port()
+    sync = ctx.Barrier(3)
+    q = ctx.Queue()
+
+    def child(rank):
+        pass
+    from mp_util import _child
+    procs = [ctx.Process(target=_child, args=(_pool_survives_leader, r, 3, (url, port), q, {}, sync)) for r in range(3)]
+    [p.start() for p in procs]
+    key = b"/memfabric_hybrid/config_store/clusters/failover/memfabric_hybrid/config_store/meta/leader"
+    first = None
+    end = time.time() + 120
+    results = {}
+    while len(results) < 2 and time.time() < end:
+        if first is None and key in etcd.kv:
+            first = etcd.kv[key]["value"]
+        try:
+            r, st, val = q.get(timeout=0.5)
+            results[r] = (st, val)
+        except Exception:  # noqa: BLE001  (queue empty)
+            pass
+    for p in procs:
+        p.join(10)
+        if p.is_alive():
+            p.kill()
+    assert results.get(1) == ("ok", True) and results.get(2) == ("ok", True), results
+    assert procs[0].exitcode == 0 and first is not None
