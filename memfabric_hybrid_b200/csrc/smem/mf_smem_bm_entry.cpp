@@ -74,6 +74,18 @@ int BmEntry::Initialize()
         go.linkDownCb = [weak](uint32_t r) { auto s = weak.lock(); return s ? s->OnLinkDown(r) : OK; };
         group_ = group::GroupEngine::Create(store_, go);
         if (!group_) rc = ERR_INVALID_PARAM;
+        // A store that restarted (a new leader after the old one died) has lost this rank's exchange record; members
+        // have imported it long ago, but a rank that joins, or returns, later reads it from the store.
+        store_->RegisterReconnectHandler([weak]() -> int {
+            auto s = weak.lock();
+            if (!s || !s->group_ || !s->Joined()) return OK;
+            std::string mine;
+            {
+                std::lock_guard<std::mutex> g(s->mu_);
+                mine = PackInfos(s->blobs_);
+            }
+            return s->store_->Set("BMEX_" + std::to_string(s->g_.rank), mine);
+        });
     }
     if (rc == OK) rc = group_->StartListen();
     if (rc == OK) {

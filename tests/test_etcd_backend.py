@@ -285,7 +285,38 @@ def test_memory_pool_brought_up_over_an_etcd_url(etcd):
     assert any(k.startswith(root + b"memfabric_hybrid/config_store/meta/leader") for k in etcd.kv)
 
 
-def _pool_survives_leader(rank, world, url, port, sync):
+def _rank0_returns(rank, world, url, port, sync2):
+    """A new process takes the place of the rank that died with the store's first leader."""
+    import os
+    os.environ["MF_CONFIG_STORE_PORT"] = str(port)
+    os.environ["MF_DEVICE_BACKEND"] = "none"
+    import numpy as np
+    import memfabric_hybrid as mf
+    from memfabric_hybrid import bm
+    MiB = 1 << 20
+    assert mf.initialize() == 0
+    cfg = bm.BmConfig()
+    cfg.rank_id, cfg.start_store, cfg.operation_timeout = 0, False, 40
+    assert bm.initialize(url, world, 0, cfg) == 0, mf.get_last_err_msg()
+    h = bm.create2(id=0, local_dram_size=4 * MiB, max_dram_size=4 * MiB, data_op_type=bm.BmDataOpType.HOST_SHM)
+    assert h.join() == 0, mf.get_last_err_msg()           # imports the survivors' slices from the records they republished
+    sync2.wait(60)
+    src = np.full(MiB, 0x70, dtype=np.uint8)
+    for r in (1, 2):
+        assert h.copy_data(src.ctypes.data, h.peer_rank_ptr(r, bm.BmMemType.HOST) + 2 * MiB, MiB, bm.BmCopyType.H2G, 0) == 0, mf.get_last_err_msg()
+    sync2.wait(60)
+    got = np.zeros(MiB, dtype=np.uint8)
+    assert h.copy_data(h.peer_rank_ptr(0, bm.BmMemType.HOST), got.ctypes.data, MiB, bm.BmCopyType.G2H, 0) == 0
+    ok = bool((got[:MiB // 2] == 0x41).all() and (got[MiB // 2:] == 0x42).all())      # what ranks 1 and 2 wrote into the new slice
+    sync2.wait(60)
+    assert h.leave() == 0
+    h.destroy()
+    bm.uninitialize(0)
+    mf.uninitialize()
+    return ok
+
+
+def _pool_survives_leader(rank, world, url, port, sync2, sync):
     """Three ranks; the process that leads the config store dies without a word. The pool's data path keeps working and
     the control path comes back on a newly elected leader."""
     import os
@@ -329,9 +360,35 @@ def _pool_survives_leader(rank, world, url, port, sync):
     assert h.copy_data(h.peer_rank_ptr(rank, bm.BmMemType.HOST) + MiB, got.ctypes.data, MiB, bm.BmCopyType.G2H, 0) == 0
     assert (got == 0x40 + other).all()
     # the control path returns with the new leader (elected once the dead leader's address stops answering; the followers
-    # notice their broken links, look the new address up in etcd and re-arm their watches): leaving is a membership change
-    # agreed through the store
-    time.sleep(6.0)
+    # notice their broken links, look the new address up in etcd and re-arm their watches); the dead rank is evicted when
+    # the new leader's recovery window closes
+    end = time.time() + 60
+    while not any(r == 0 for r, _ in events) and time.time() < end:
+        time.sleep(0.05)
+    assert any(r == 0 for r, _ in events), events    # the survivors were told that rank 0 is gone
+    return _after_failover(h, bm, mf, np, rank, sync2, events)
+
+
+def _after_failover(h, bm, mf, np, rank, sync2, events):
+    MiB = 1 << 20
+    rc = 0
+    if sync2 is not None:
+        # a new rank 0 joins: it found this rank's exchange record in the new leader's store
+        seen = len(events)
+        end = time.time() + 60
+        while not any(r == 0 for r, _ in events[seen:]) and time.time() < end:   # the JOIN of the returning rank
+            time.sleep(0.05)
+        assert any(r == 0 for r, _ in events[seen:]), events
+        sync2.wait(60)
+        half = np.full(MiB // 2, 0x40 + rank, dtype=np.uint8)
+        assert h.copy_data(half.ctypes.data, h.peer_rank_ptr(0, bm.BmMemType.HOST) + (rank - 1) * (MiB // 2), MiB // 2, bm.BmCopyType.H2G, 0) == 0, mf.get_last_err_msg()
+        sync2.wait(60)
+        got = np.zeros(MiB, dtype=np.uint8)
+        assert h.copy_data(h.peer_rank_ptr(rank, bm.BmMemType.HOST) + 2 * MiB, got.ctypes.data, MiB, bm.BmCopyType.G2H, 0) == 0
+        assert (got == 0x70).all()
+        sync2.wait(60)
+        time.sleep(1.5)                          # the returned rank leaves first
+    # leaving is a membership change agreed through the store
     end = time.time() + 60
     rc = -1
     while time.time() < end:
@@ -341,7 +398,6 @@ def _pool_survives_leader(rank, world, url, port, sync):
         mf.get_and_clear_last_err_msg()
         time.sleep(0.5)
     assert rc == 0, f"leave after the leader died: {rc} {mf.get_last_err_msg()}"
-    assert any(r == 0 for r, _ in events), events    # the survivors were told that rank 0 is gone
     time.sleep(1.0 if rank == 1 else 0.0)        # whoever leads now stays until the other has left
     h.destroy()
     bm.uninitialize(0)
@@ -360,13 +416,18 @@ def test_pool_survives_the_death_of_the_store_leader(etcd):
     def child(rank):
         pass
     from mp_util import _child
-    procs = [ctx.Process(target=_child, args=(_pool_survives_leader, r, 3, (url, port), q, {}, sync)) for r in range(3)]
+    sync2 = ctx.Barrier(3)                      # the two survivors and the process that returns as rank 0
+    procs = [ctx.Process(target=_child, args=(_pool_survives_leader, r, 3, (url, port, sync2 if r else None), q, {}, sync)) for r in range(3)]
     [p.start() for p in procs]
+    procs[0].join(90)                           # the first leader's process has exited ...
+    time.sleep(7.0)                             # ... a new leader is elected and its recovery window (3 s) has closed
+    back = ctx.Process(target=_child, args=(_rank0_returns, 0, 3, (url, port, sync2), q, {}, None))
+    back.start()
     key = b"/memfabric_hybrid/config_store/clusters/failover/memfabric_hybrid/config_store/meta/leader"
     first = None
     end = time.time() + 120
     results = {}
-    while len(results) < 2 and time.time() < end:
+    while len(results) < 3 and time.time() < end:
         if first is None and key in etcd.kv:
             first = etcd.kv[key]["value"]
         try:
@@ -374,9 +435,9 @@ def test_pool_survives_the_death_of_the_store_leader(etcd):
             results[r] = (st, val)
         except Exception:  # noqa: BLE001  (queue empty)
             pass
-    for p in procs:
+    for p in procs + [back]:
         p.join(10)
         if p.is_alive():
             p.kill()
-    assert results.get(1) == ("ok", True) and results.get(2) == ("ok", True), results
+    assert results.get(1) == ("ok", True) and results.get(2) == ("ok", True) and results.get(0) == ("ok", True), results
     assert procs[0].exitcode == 0 and first is not None
