@@ -88,6 +88,17 @@ public:
         };
         group_ = group::GroupEngine::Create(store_, go);
         if (!group_) return ERR_INVALID_PARAM;
+        // A store that restarted (a new leader after the old one died) has lost this endpoint's identity and the records
+        // of its registered buffers: peers that look it up from then on need them again.
+        store_->RegisterReconnectHandler([weak]() -> int {
+            auto s = weak.lock();
+            if (!s || s->closed_.load()) return OK;
+            IdRecord me{s->rank_, (uint32_t)s->cfg_.role, (int32_t)getpid()};
+            int rc = s->store_->Set("ID_" + s->uid_, std::string(reinterpret_cast<const char *>(&me), sizeof(me)));
+            if (rc == OK) rc = s->store_->Set("RK_" + std::to_string(s->rank_), s->uid_);
+            std::lock_guard<std::mutex> g(s->mu_);
+            return rc == OK ? s->PublishLocked() : rc;
+        });
         rc = group_->Join();
         return rc;
     }
