@@ -204,8 +204,16 @@ void HaConfigStore::HealthLoop()
         }
         if (!running_) break;
         if (leader_) {
-            std::string addr = LeaderAddress();
-            if (backend_->Connect() != OK || backend_->Put(kBackendKeyLeader, addr, leaseMs_) != OK) {
+            std::string addr = LeaderAddress(), cur, ip;
+            uint16_t port = 0;
+            if (backend_->Connect() == OK && backend_->Get(kBackendKeyLeader, cur) == OK && cur != addr && net::ParseIpPort(cur, ip, port) &&
+                net::ProbeReachable(ip, port, 500)) {
+                // Somebody else was elected while this node could not be reached (it looked dead from there) and serves:
+                // two leaders would split the members between them. The key decides: follow it.
+                MF_WARN("config-store leader key names %s, which answers: stepping down at %s", cur.c_str(), addr.c_str());
+                Demote();
+                reelect_ = true;
+            } else if (backend_->Connect() != OK || backend_->Put(kBackendKeyLeader, addr, leaseMs_) != OK) {
                 Demote();
                 reelect_ = true;
             }
