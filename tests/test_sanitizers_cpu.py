@@ -50,7 +50,7 @@ def test_control_plane_is_free_of_data_races_under_tsan():
                OPENBLAS_NUM_THREADS="1", OMP_NUM_THREADS="1",       # no library threads around when a test forks
                MF_GVA_DRAM_BASE=str(0x560000000000),
                TSAN_OPTIONS="halt_on_error=0:report_signal_unsafe=0:history_size=4:exitcode=0")
-    r = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-s", "-p", "no:cacheprovider", "-k", "not native and not exchange_records and not 56_bit"] +
+    r = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-s", "-p", "no:cacheprovider", "-k", "not native and not exchange_records and not 56_bit and not survives_the_death"] +   # (the four-process failover scenario runs on lease and recovery timers: too slow under this sanitizer)
                        [os.path.join(ROOT, "tests", f) for f in TSAN_FILES], env=env, capture_output=True, text=True, errors="replace",
                        timeout=2400, cwd=ROOT)
     out = r.stdout + r.stderr
